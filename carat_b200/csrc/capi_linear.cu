@@ -1,0 +1,130 @@
+// C entry points for the FP8 linear kernels (declared in include/carat_b200.h).
+#include "../../include/carat_b200.h"
+#include "context.cuh"
+#include "fp8_linear.cuh"
+
+using namespace carat_b200;
+
+namespace {
+
+int plan_or_fail(LinearPlan *plan, const void *input, const void *weight, int rows, int input_width,
+                 int output_width, int splits) {
+  const char *message = "invalid FP8 linear shape";
+  const int status =
+      make_linear_plan(plan, input, weight, rows, input_width, output_width, splits, &message);
+  if (status != 0)
+    set_last_error(message);
+  return status;
+}
+
+int launch_status(int status, const char *what) {
+  if (status == 0)
+    return 0;
+  set_last_error(std::string(what) + " launch failed: " +
+                 cudaGetErrorString(cudaGetLastError()));
+  return status;
+}
+
+} // namespace
+
+extern "C" const char *carat_b200_last_error(void) { return last_error_text(); }
+
+extern "C" int carat_b200_abi_version(void) { return 1; }
+
+extern "C" int carat_b200_device_error(int *code) { return read_and_clear_device_error(code); }
+
+extern "C" size_t carat_b200_fp8_linear_workspace_bytes(int rows, int input_width,
+                                                        int output_width) {
+  if (rows <= 0 || rows > 128 || input_width <= 0 || output_width <= 0)
+    return 0;
+  // Same split choice as make_linear_plan, without touching tensor maps.
+  const int tiles = (output_width + 127) / 128;
+  const int k_blocks = (input_width + 127) / 128;
+  int splits = tiles >= 120 ? 1 : 148 / tiles;
+  splits = splits < 1 ? 1 : splits;
+  const int most = k_blocks / 4 < 1 ? 1 : k_blocks / 4;
+  splits = splits > most ? most : splits;
+  const int per_split = (k_blocks + splits - 1) / splits;
+  splits = (k_blocks + per_split - 1) / per_split;
+  return splits <= 1 ? 0 : sizeof(float) * static_cast<size_t>(splits) * rows * output_width;
+}
+
+extern "C" int carat_b200_fp8_linear(const void *fp8_input, const float *device_input_scale,
+                                     const void *fp8_weight, const float *device_weight_scale,
+                                     void *bf16_output, int rows, int input_width,
+                                     int output_width, void *workspace, size_t workspace_bytes,
+                                     void *stream) {
+  if (device_input_scale == nullptr || device_weight_scale == nullptr || bf16_output == nullptr) {
+    set_last_error("invalid FP8 linear shape");
+    return -1;
+  }
+  LinearPlan plan;
+  int status = plan_or_fail(&plan, fp8_input, fp8_weight, rows, input_width, output_width, 0);
+  if (status != 0)
+    return status;
+  const size_t needed = linear_partial_bytes(plan);
+  if (needed > 0 && (workspace == nullptr || workspace_bytes < needed)) {
+    set_last_error("FP8 linear workspace is too small");
+    return -6;
+  }
+  int *error_word = device_error_word();
+  if (error_word == nullptr) {
+    set_last_error("device error word is unavailable");
+    return -101;
+  }
+  status = launch_linear_bf16(plan, device_input_scale, device_weight_scale, bf16_output,
+                              static_cast<float *>(workspace), error_word,
+                              static_cast<cudaStream_t>(stream));
+  return launch_status(status, "FP8 linear");
+}
+
+extern "C" int carat_b200_fp8_linear_argmax(const void *fp8_input, const float *device_input_scale,
+                                            const void *fp8_weight,
+                                            const float *device_weight_scale, int *device_tokens,
+                                            void *device_keys, int rows, int input_width,
+                                            int output_width, void *stream) {
+  if (device_input_scale == nullptr || device_weight_scale == nullptr ||
+      device_tokens == nullptr || device_keys == nullptr) {
+    set_last_error("invalid FP8 linear shape");
+    return -1;
+  }
+  LinearPlan plan;
+  int status = plan_or_fail(&plan, fp8_input, fp8_weight, rows, input_width, output_width, 1);
+  if (status != 0)
+    return status;
+  int *error_word = device_error_word();
+  if (error_word == nullptr) {
+    set_last_error("device error word is unavailable");
+    return -101;
+  }
+  auto *keys = static_cast<unsigned long long *>(device_keys);
+  const auto cuda_stream = static_cast<cudaStream_t>(stream);
+  status = check_cuda(cudaMemsetAsync(keys, 0, sizeof(unsigned long long) * rows, cuda_stream),
+                      "clear argmax keys");
+  if (status != 0)
+    return status;
+  status = launch_linear_argmax(plan, device_input_scale, device_weight_scale, keys, error_word,
+                                cuda_stream);
+  if (status != 0)
+    return launch_status(status, "FP8 LM head");
+  return launch_status(launch_unpack_best(keys, device_tokens, rows, cuda_stream),
+                       "argmax unpack");
+}
+
+extern "C" int carat_b200_fp8_linear_check(const void *fp8_input, const float *device_input_scale,
+                                           const void *fp8_weight,
+                                           const float *device_weight_scale, void *bf16_output,
+                                           int rows, int input_width, int output_width,
+                                           void *stream) {
+  if (fp8_input == nullptr || fp8_weight == nullptr || device_input_scale == nullptr ||
+      device_weight_scale == nullptr || bf16_output == nullptr || rows <= 0 || input_width <= 0 ||
+      output_width <= 0) {
+    set_last_error("invalid FP8 linear shape");
+    return -1;
+  }
+  return launch_status(launch_linear_simt_check(fp8_input, device_input_scale, fp8_weight,
+                                                device_weight_scale, bf16_output, rows,
+                                                input_width, output_width,
+                                                static_cast<cudaStream_t>(stream)),
+                       "FP8 linear check");
+}

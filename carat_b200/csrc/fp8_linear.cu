@@ -1,0 +1,498 @@
+// Weight-streaming FP8 (e4m3 x e4m3 -> fp32 -> bf16) linear for the verify step's small row counts.
+//
+// Contract (reference: cuda/linear.cu:645-803 Fp8Linear::run, tensor scaling):
+//   output[rows, N] = bf16( (x_scale * w_scale) * X_e4m3[rows, K] . W_e4m3[N, K]^T ), fp32 accumulate.
+//
+// The problem is HBM-bound (rows <= 128 means <= 256 FLOP per weight byte), so the design is a
+// weight stream: the operands are swapped so that 128 output features form the UMMA M dimension
+// and the (zero-padded) activation rows the UMMA N dimension. One CTA owns one 128-feature tile
+// over one K range; a TMA producer warp keeps a multi-stage ring of 128-byte-swizzled
+// [128 x 128 B] weight tiles and [rows x 128 B] activation tiles in flight, a single thread issues
+// tcgen05.mma (kind::f8f6f4, K = 32) into a TMEM accumulator, and four epilogue warps read the
+// accumulator with tcgen05.ld. Weights are read exactly once with an evict-first policy; the
+// activation matrix is re-read from L2 by every tile with an evict-last policy.
+#include "fp8_linear.cuh"
+#include "ptx.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include <mutex>
+
+namespace carat_b200 {
+namespace {
+
+constexpr int tile_features = 128;  // UMMA M
+constexpr int tile_k_bytes = 128;   // one 128B swizzle atom of e4m3 per row
+constexpr int umma_k = 32;
+constexpr int linear_threads = 192; // warp 0 TMA, warp 1 MMA + TMEM, warps 2-5 epilogue
+constexpr int weight_tile_bytes = tile_features * tile_k_bytes;
+constexpr int shared_budget = 200 * 1024;
+
+__host__ __device__ constexpr int stages_for(int padded_rows) {
+  const int per_stage = weight_tile_bytes + padded_rows * tile_k_bytes;
+  const int fit = shared_budget / per_stage;
+  return fit > 8 ? 8 : fit;
+}
+
+struct KernelArguments {
+  const float *input_scale;
+  const float *weight_scale;
+  __nv_bfloat16 *output;
+  float *partial;
+  unsigned long long *best;
+  int *device_error;
+  int rows;
+  int output_width;
+  int k_blocks;
+  int k_blocks_per_split;
+};
+
+__device__ __forceinline__ unsigned int orderable_bf16(float rounded) {
+  // Monotonic map of a bf16-representable float to 16 bits; NaN sorts below everything, matching
+  // a comparison chain that never selects NaN.
+  if (rounded != rounded)
+    return 0U;
+  const unsigned int bits = __float_as_uint(rounded) >> 16;
+  return (bits & 0x8000U) ? (~bits & 0xFFFFU) : (bits | 0x8000U);
+}
+
+template <int padded_rows, int mode>
+__global__ void __launch_bounds__(linear_threads, 1)
+fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
+                  const __grid_constant__ CUtensorMap input_map, const KernelArguments args) {
+  constexpr int stages = stages_for(padded_rows);
+  constexpr int input_tile_bytes = padded_rows * tile_k_bytes;
+  constexpr uint32_t stage_bytes = weight_tile_bytes + input_tile_bytes;
+  constexpr uint32_t idesc = ptx::umma_idesc(0, 0, tile_features, padded_rows);
+
+  extern __shared__ unsigned char shared_raw[];
+  __shared__ __align__(8) unsigned long long barriers[2 * stages + 1];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ unsigned long long row_best[mode == 2 ? padded_rows : 1];
+
+  const uint32_t tiles_base = (ptx::smem_u32(shared_raw) + 1023U) & ~1023U;
+  const uint32_t weight_tiles = tiles_base;
+  const uint32_t input_tiles = tiles_base + stages * weight_tile_bytes;
+  const uint32_t full_bar = ptx::smem_u32(&barriers[0]);
+  const uint32_t empty_bar = ptx::smem_u32(&barriers[stages]);
+  const uint32_t accum_bar = ptx::smem_u32(&barriers[2 * stages]);
+
+  const int warp = static_cast<int>(threadIdx.x) / 32;
+  const int lane = static_cast<int>(threadIdx.x) & 31;
+  const int tile = static_cast<int>(blockIdx.x);
+  const int split = static_cast<int>(blockIdx.y);
+  const int k_begin = split * args.k_blocks_per_split;
+  const int k_end = min(args.k_blocks, k_begin + args.k_blocks_per_split);
+  const int k_count = k_end - k_begin;
+
+  if (threadIdx.x == 0) {
+    for (int stage = 0; stage < stages; ++stage) {
+      ptx::mbarrier_init(full_bar + 8U * stage, 1);
+      ptx::mbarrier_init(empty_bar + 8U * stage, 1);
+    }
+    ptx::mbarrier_init(accum_bar, 1);
+    ptx::fence_mbarrier_init();
+    ptx::prefetch_tensormap(&weight_map);
+    ptx::prefetch_tensormap(&input_map);
+  }
+  if constexpr (mode == 2) {
+    for (int row = static_cast<int>(threadIdx.x); row < padded_rows; row += linear_threads)
+      row_best[row] = 0ULL;
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&tmem_base_slot), padded_rows);
+    ptx::tmem_relinquish_alloc_permit();
+  }
+  ptx::tcgen05_fence_before_thread_sync();
+  __syncthreads();
+  ptx::tcgen05_fence_after_thread_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint64_t stream_policy = ptx::policy_evict_first();
+      const uint64_t reuse_policy = ptx::policy_evict_last();
+      int issued = 0;
+      bool healthy = true;
+      for (int block = 0; block < k_count; ++block) {
+        const int stage = block % stages;
+        const uint32_t phase = static_cast<uint32_t>(block / stages) & 1U;
+        if (!ptx::mbarrier_wait_bounded(empty_bar + 8U * stage, phase ^ 1U)) {
+          healthy = false;
+          atomicExch(args.device_error, 1);
+          break;
+        }
+        ptx::mbarrier_arrive_expect_tx(full_bar + 8U * stage, stage_bytes);
+        const int k_byte = (k_begin + block) * tile_k_bytes;
+        ptx::tma_load_2d(weight_tiles + stage * weight_tile_bytes, &weight_map, k_byte,
+                         tile * tile_features, full_bar + 8U * stage, stream_policy);
+        ptx::tma_load_2d(input_tiles + stage * input_tile_bytes, &input_map, k_byte, 0,
+                         full_bar + 8U * stage, reuse_policy);
+        ++issued;
+      }
+      if (!healthy) {
+        // Let copies already in flight land before the CTA gives its shared memory back.
+        const int first = issued > stages ? issued - stages : 0;
+        for (int block = first; block < issued; ++block) {
+          ptx::mbarrier_wait_bounded(full_bar + 8U * (block % stages),
+                                     static_cast<uint32_t>(block / stages) & 1U);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool healthy = true;
+      for (int block = 0; block < k_count; ++block) {
+        const int stage = block % stages;
+        const uint32_t phase = static_cast<uint32_t>(block / stages) & 1U;
+        if (!ptx::mbarrier_wait_bounded(full_bar + 8U * stage, phase)) {
+          healthy = false;
+          atomicExch(args.device_error, 2);
+          break;
+        }
+        ptx::tcgen05_fence_after_thread_sync();
+        const uint64_t weight_desc =
+            ptx::umma_desc_k_major_sw128(weight_tiles + stage * weight_tile_bytes);
+        const uint64_t input_desc =
+            ptx::umma_desc_k_major_sw128(input_tiles + stage * input_tile_bytes);
+#pragma unroll
+        for (int step = 0; step < tile_k_bytes / umma_k; ++step) {
+          // +32 bytes along K inside the swizzle atom = +2 in the 16-byte address field.
+          ptx::tcgen05_mma_f8f6f4(tmem_base, weight_desc + 2ULL * step, input_desc + 2ULL * step,
+                                  idesc, (block > 0 || step > 0) ? 1U : 0U);
+        }
+        ptx::tcgen05_commit(empty_bar + 8U * stage);
+      }
+      // Arrives once every MMA above has retired (also on the unhealthy path, so that the
+      // epilogue warps leave their wait promptly).
+      (void)healthy;
+      ptx::tcgen05_commit(accum_bar);
+    }
+  } else {
+    const int quarter = warp & 3;  // TMEM lane group this warp may read
+    const int feature = tile * tile_features + quarter * 32 + lane;
+    const bool accum_ready =
+        __all_sync(0xFFFFFFFFU, ptx::mbarrier_wait_bounded(accum_bar, 0) ? 1 : 0) != 0;
+    if (!accum_ready && lane == 0)
+      atomicExch(args.device_error, 3);
+    ptx::tcgen05_fence_after_thread_sync();
+    const uint32_t lane_address = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    float scale = 1.0F;
+    if constexpr (mode != 1)
+      scale = args.input_scale[0] * args.weight_scale[0];
+#pragma unroll
+    for (int chunk = 0; chunk < padded_rows / 32; ++chunk) {
+      if (chunk * 32 < args.rows && accum_ready) {  // warp-uniform
+        uint32_t values[32];
+        ptx::tmem_load_32x32b_x32(lane_address + chunk * 32, values);
+        ptx::tmem_load_wait();
+        if constexpr (mode == 0) {
+          if (feature < args.output_width) {
+#pragma unroll
+            for (int column = 0; column < 32; ++column) {
+              const int row = chunk * 32 + column;
+              if (row < args.rows) {
+                args.output[static_cast<size_t>(row) * args.output_width + feature] =
+                    __float2bfloat16_rn(__uint_as_float(values[column]) * scale);
+              }
+            }
+          }
+        } else if constexpr (mode == 1) {
+          if (feature < args.output_width) {
+            float *destination =
+                args.partial + static_cast<size_t>(split) * args.rows * args.output_width + feature;
+#pragma unroll
+            for (int column = 0; column < 32; ++column) {
+              const int row = chunk * 32 + column;
+              if (row < args.rows)
+                destination[static_cast<size_t>(row) * args.output_width] =
+                    __uint_as_float(values[column]);
+            }
+          }
+        } else {
+          unsigned long long chunk_best = 0ULL;
+#pragma unroll
+          for (int column = 0; column < 32; ++column) {
+            const float rounded = __bfloat162float(
+                __float2bfloat16_rn(__uint_as_float(values[column]) * scale));
+            // Out-of-range features lose to everything; ties inside the warp go to the lowest
+            // lane, which is the lowest feature index.
+            const unsigned int key =
+                feature < args.output_width
+                    ? ((orderable_bf16(rounded) + 1U) << 8) | static_cast<unsigned int>(31 - lane)
+                    : 0U;
+            const unsigned int winner = __reduce_max_sync(0xFFFFFFFFU, key);
+            if (lane == column && winner != 0U) {
+              const unsigned int winner_lane = 31U - (winner & 31U);
+              const unsigned int winner_feature =
+                  static_cast<unsigned int>(tile * tile_features + quarter * 32) + winner_lane;
+              chunk_best = (static_cast<unsigned long long>(winner >> 8) << 32) |
+                           static_cast<unsigned long long>(~winner_feature);
+            }
+          }
+          const int row = chunk * 32 + lane;
+          if (row < args.rows && chunk_best != 0ULL)
+            atomicMax(&row_best[row], chunk_best);
+        }
+      }
+    }
+    if constexpr (mode == 2) {
+      // Combine the four feature quarters in shared memory, then one global atomic per row.
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const int row = (warp - 2) * 32 + lane;
+      if (row < args.rows && row < padded_rows) {
+        const unsigned long long candidate = row_best[row];
+        if (candidate != 0ULL)
+          atomicMax(args.best + row, candidate);
+      }
+    }
+  }
+
+  ptx::tcgen05_fence_before_thread_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tcgen05_fence_after_thread_sync();
+    ptx::tmem_dealloc(tmem_base, padded_rows);
+  }
+}
+
+__global__ void finalize_split_k_kernel(const float *partial, const float *input_scale,
+                                        const float *weight_scale, __nv_bfloat16 *output,
+                                        int splits, size_t elements) {
+  const float scale = input_scale[0] * weight_scale[0];
+  for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+       index < elements; index += static_cast<size_t>(blockDim.x) * gridDim.x) {
+    float sum = 0.0F;
+    for (int split = 0; split < splits; ++split)
+      sum += partial[static_cast<size_t>(split) * elements + index];
+    output[index] = __float2bfloat16_rn(sum * scale);
+  }
+}
+
+__global__ void unpack_best_kernel(const unsigned long long *best, int *tokens, int rows) {
+  const int row = static_cast<int>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (row < rows)
+    tokens[row] = best_index(best[row]);
+}
+
+__global__ void linear_simt_check_kernel(const __nv_fp8_e4m3 *input, const float *input_scale,
+                                         const __nv_fp8_e4m3 *weight, const float *weight_scale,
+                                         __nv_bfloat16 *output, int rows, int input_width,
+                                         int output_width) {
+  const int feature = static_cast<int>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int row = static_cast<int>(blockIdx.y);
+  if (feature >= output_width || row >= rows)
+    return;
+  const __nv_fp8_e4m3 *x = input + static_cast<size_t>(row) * input_width;
+  const __nv_fp8_e4m3 *w = weight + static_cast<size_t>(feature) * input_width;
+  float sum = 0.0F;
+  for (int k = 0; k < input_width; ++k)
+    sum += static_cast<float>(x[k]) * static_cast<float>(w[k]);
+  output[static_cast<size_t>(row) * output_width + feature] =
+      __float2bfloat16_rn(sum * (input_scale[0] * weight_scale[0]));
+}
+
+using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                 const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                 const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled_entry() {
+  static EncodeTiled entry = [] {
+    void *function = nullptr;
+    cudaDriverEntryPointQueryResult status{};
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &function, cudaEnableDefault, &status) !=
+            cudaSuccess ||
+        status != cudaDriverEntryPointSuccess) {
+      return static_cast<EncodeTiled>(nullptr);
+    }
+    return reinterpret_cast<EncodeTiled>(function);
+  }();
+  return entry;
+}
+
+// [outer, inner] row-major bytes, box [box_outer, 128] with the 128-byte swizzle; out-of-range
+// rows and K tails read as zero.
+bool encode_byte_matrix(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer,
+                        uint32_t box_outer) {
+  const EncodeTiled encode = encode_tiled_entry();
+  if (encode == nullptr)
+    return false;
+  const cuuint64_t dimensions[2] = {inner, outer};
+  const cuuint64_t strides[1] = {inner};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(tile_k_bytes), box_outer};
+  const cuuint32_t element_strides[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dimensions,
+                strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int padded_rows, int mode>
+int launch_variant(const LinearPlan &plan, const KernelArguments &arguments, cudaStream_t stream) {
+  constexpr int stages = stages_for(padded_rows);
+  constexpr int dynamic_bytes = stages * (weight_tile_bytes + padded_rows * tile_k_bytes) + 1024;
+  static std::once_flag configured;
+  static cudaError_t configure_status = cudaSuccess;
+  std::call_once(configured, [] {
+    configure_status = cudaFuncSetAttribute(fp8_linear_kernel<padded_rows, mode>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            dynamic_bytes);
+  });
+  if (configure_status != cudaSuccess)
+    return -10;
+  const dim3 grid(static_cast<unsigned>(plan.tiles), static_cast<unsigned>(plan.splits));
+  fp8_linear_kernel<padded_rows, mode><<<grid, linear_threads, dynamic_bytes, stream>>>(
+      plan.weight_map, plan.input_map, arguments);
+  return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
+}
+
+template <int mode>
+int launch_mode(const LinearPlan &plan, const KernelArguments &arguments, cudaStream_t stream) {
+  switch (plan.padded_rows) {
+  case 32:
+    return launch_variant<32, mode>(plan, arguments, stream);
+  case 64:
+    return launch_variant<64, mode>(plan, arguments, stream);
+  case 128:
+    return launch_variant<128, mode>(plan, arguments, stream);
+  default:
+    return -12;
+  }
+}
+
+KernelArguments base_arguments(const LinearPlan &plan, int *device_error) {
+  KernelArguments arguments{};
+  arguments.device_error = device_error;
+  arguments.rows = plan.rows;
+  arguments.output_width = plan.output_width;
+  arguments.k_blocks = plan.k_blocks;
+  arguments.k_blocks_per_split = plan.k_blocks_per_split;
+  return arguments;
+}
+
+} // namespace
+
+int make_linear_plan(LinearPlan *plan, const void *fp8_input, const void *fp8_weight, int rows,
+                     int input_width, int output_width, int requested_splits, const char **error) {
+  const auto fail = [&](const char *message, int code) {
+    if (error != nullptr)
+      *error = message;
+    return code;
+  };
+  if (plan == nullptr || fp8_input == nullptr || fp8_weight == nullptr || rows <= 0 ||
+      input_width <= 0 || output_width <= 0) {
+    return fail("invalid FP8 linear shape", -1);
+  }
+  if (rows > 128)
+    return fail("FP8 linear supports at most 128 rows", -2);
+  if (input_width % 16 != 0)
+    return fail("FP8 linear input width must be a multiple of 16", -3);
+  if ((reinterpret_cast<uintptr_t>(fp8_input) & 15U) != 0 ||
+      (reinterpret_cast<uintptr_t>(fp8_weight) & 15U) != 0) {
+    return fail("FP8 linear operands must be 16-byte aligned", -4);
+  }
+  LinearPlan result{};
+  result.rows = rows;
+  result.input_width = input_width;
+  result.output_width = output_width;
+  result.padded_rows = rows <= 32 ? 32 : rows <= 64 ? 64 : 128;
+  result.tiles = (output_width + tile_features - 1) / tile_features;
+  result.k_blocks = (input_width + tile_k_bytes - 1) / tile_k_bytes;
+  int splits = requested_splits;
+  if (splits <= 0) {
+    // Fill the 148 SMs when there are few feature tiles; keep at least four K blocks per split.
+    splits = result.tiles >= 120 ? 1 : 148 / result.tiles;
+    splits = splits < 1 ? 1 : splits;
+    const int most = result.k_blocks / 4 < 1 ? 1 : result.k_blocks / 4;
+    splits = splits > most ? most : splits;
+  }
+  if (splits > result.k_blocks)
+    splits = result.k_blocks;
+  result.k_blocks_per_split = (result.k_blocks + splits - 1) / splits;
+  result.splits = (result.k_blocks + result.k_blocks_per_split - 1) / result.k_blocks_per_split;
+  if (!encode_byte_matrix(&result.weight_map, fp8_weight, static_cast<uint64_t>(input_width),
+                          static_cast<uint64_t>(output_width), tile_features) ||
+      !encode_byte_matrix(&result.input_map, fp8_input, static_cast<uint64_t>(input_width),
+                          static_cast<uint64_t>(rows), static_cast<uint32_t>(result.padded_rows))) {
+    return fail("cuTensorMapEncodeTiled failed", -5);
+  }
+  *plan = result;
+  return 0;
+}
+
+std::size_t linear_partial_bytes(const LinearPlan &plan) {
+  return plan.splits <= 1 ? 0
+                          : sizeof(float) * static_cast<std::size_t>(plan.splits) * plan.rows *
+                                plan.output_width;
+}
+
+int launch_linear_bf16(const LinearPlan &plan, const float *input_scale, const float *weight_scale,
+                       void *bf16_output, float *partial, int *device_error, cudaStream_t stream) {
+  KernelArguments arguments = base_arguments(plan, device_error);
+  arguments.input_scale = input_scale;
+  arguments.weight_scale = weight_scale;
+  arguments.output = static_cast<__nv_bfloat16 *>(bf16_output);
+  arguments.partial = partial;
+  if (plan.splits == 1)
+    return launch_mode<0>(plan, arguments, stream);
+  if (partial == nullptr)
+    return -13;
+  const int status = launch_mode<1>(plan, arguments, stream);
+  if (status != 0)
+    return status;
+  return launch_finalize_split_k(partial, input_scale, weight_scale, bf16_output, plan.splits,
+                                 plan.rows, plan.output_width, stream);
+}
+
+int launch_linear_partial(const LinearPlan &plan, float *partial, int *device_error,
+                          cudaStream_t stream) {
+  if (partial == nullptr)
+    return -13;
+  KernelArguments arguments = base_arguments(plan, device_error);
+  arguments.partial = partial;
+  return launch_mode<1>(plan, arguments, stream);
+}
+
+int launch_linear_argmax(const LinearPlan &plan, const float *input_scale,
+                         const float *weight_scale, unsigned long long *best, int *device_error,
+                         cudaStream_t stream) {
+  if (plan.splits != 1 || best == nullptr)
+    return -14;
+  KernelArguments arguments = base_arguments(plan, device_error);
+  arguments.input_scale = input_scale;
+  arguments.weight_scale = weight_scale;
+  arguments.best = best;
+  return launch_mode<2>(plan, arguments, stream);
+}
+
+int launch_finalize_split_k(const float *partial, const float *input_scale,
+                            const float *weight_scale, void *bf16_output, int splits, int rows,
+                            int output_width, cudaStream_t stream) {
+  const size_t elements = static_cast<size_t>(rows) * output_width;
+  const int blocks = static_cast<int>((elements + 255) / 256);
+  finalize_split_k_kernel<<<blocks < 1184 ? blocks : 1184, 256, 0, stream>>>(
+      partial, input_scale, weight_scale, static_cast<__nv_bfloat16 *>(bf16_output), splits,
+      elements);
+  return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
+}
+
+int launch_unpack_best(const unsigned long long *best, int *tokens, int rows,
+                       cudaStream_t stream) {
+  unpack_best_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(best, tokens, rows);
+  return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
+}
+
+int launch_linear_simt_check(const void *fp8_input, const float *input_scale,
+                             const void *fp8_weight, const float *weight_scale, void *bf16_output,
+                             int rows, int input_width, int output_width, cudaStream_t stream) {
+  const dim3 grid(static_cast<unsigned>((output_width + 127) / 128), static_cast<unsigned>(rows));
+  linear_simt_check_kernel<<<grid, 128, 0, stream>>>(
+      static_cast<const __nv_fp8_e4m3 *>(fp8_input), input_scale,
+      static_cast<const __nv_fp8_e4m3 *>(fp8_weight), weight_scale,
+      static_cast<__nv_bfloat16 *>(bf16_output), rows, input_width, output_width);
+  return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
+}
+
+} // namespace carat_b200

@@ -1,0 +1,77 @@
+// Host-side interface of the weight-streaming FP8 (e4m3) linear for up to 128 activation rows.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace carat_b200 {
+
+// How the accumulator tile leaves the kernel.
+enum class LinearEpilogue : int {
+  bf16 = 0,     // y[row, n] = bf16(acc * x_scale * w_scale)
+  partial = 1,  // split-K: fp32 partial sums, finished by finalize_split_k or a fused consumer
+  argmax = 2,   // per-row argmax of bf16(acc * scale); logits never reach memory
+};
+
+// One launch description. Tensor maps are encoded once (weights and activation buffers of the
+// runner never move) and captured by value into the kernel parameters.
+struct LinearPlan {
+  CUtensorMap weight_map;
+  CUtensorMap input_map;
+  int rows{0};
+  int input_width{0};
+  int output_width{0};
+  int padded_rows{0};       // UMMA N: 32, 64 or 128
+  int tiles{0};             // output-feature tiles of 128
+  int splits{1};            // split-K factor
+  int k_blocks{0};          // 128-byte K blocks
+  int k_blocks_per_split{0};
+};
+
+// Returns 0 or a negative error; `error` (may be null) receives a static message.
+int make_linear_plan(LinearPlan *plan, const void *fp8_input, const void *fp8_weight, int rows,
+                     int input_width, int output_width, int requested_splits, const char **error);
+
+// Bytes of fp32 scratch a plan needs when it runs as split-K (0 when splits == 1).
+std::size_t linear_partial_bytes(const LinearPlan &plan);
+
+// bf16 epilogue; when plan.splits > 1 the kernel writes fp32 partials into `partial` and a second
+// kernel sums, scales and rounds them into `output`.
+int launch_linear_bf16(const LinearPlan &plan, const float *input_scale, const float *weight_scale,
+                       void *bf16_output, float *partial, int *device_error, cudaStream_t stream);
+
+// Split-K only: leaves the unscaled fp32 partials [splits, rows, output_width] for a consumer that
+// sums them itself.
+int launch_linear_partial(const LinearPlan &plan, float *partial, int *device_error,
+                          cudaStream_t stream);
+
+// Argmax epilogue. `best` holds one packed 64-bit key per row and must be zero before the launch:
+// (orderable bf16 logit << 32) | ~index, combined with atomicMax, so equal logits keep the lowest
+// index. unpack with best_index().
+int launch_linear_argmax(const LinearPlan &plan, const float *input_scale,
+                         const float *weight_scale, unsigned long long *best, int *device_error,
+                         cudaStream_t stream);
+
+// tokens[row] = index stored in best[row].
+int launch_unpack_best(const unsigned long long *best, int *tokens, int rows, cudaStream_t stream);
+
+// Sums split-K partials, applies the scale product and rounds to bf16.
+int launch_finalize_split_k(const float *partial, const float *input_scale,
+                            const float *weight_scale, void *bf16_output, int splits, int rows,
+                            int output_width, cudaStream_t stream);
+
+// Plain one-thread-per-output kernel with the same contract as the bf16 epilogue. It exists so the
+// tensor-core kernel can be cross-checked on the device at full size; nothing on the step path
+// calls it.
+int launch_linear_simt_check(const void *fp8_input, const float *input_scale,
+                             const void *fp8_weight, const float *weight_scale, void *bf16_output,
+                             int rows, int input_width, int output_width, cudaStream_t stream);
+
+__host__ __device__ inline int best_index(unsigned long long key) {
+  return static_cast<int>(~static_cast<unsigned int>(key & 0xFFFFFFFFULL));
+}
+
+} // namespace carat_b200
