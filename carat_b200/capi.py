@@ -1,0 +1,136 @@
+"""ctypes binding of libcarat_b200.so (the C ABI declared in include/carat_b200.h).
+
+Loading fails loudly when the library has not been built: there is no fallback path.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_size_t, c_void_p
+
+_PACKAGE = os.path.dirname(os.path.abspath(__file__))
+LIBRARY_PATH = os.path.join(_PACKAGE, "libcarat_b200.so")
+
+
+class CaratError(RuntimeError):
+    """A C entry point returned a failure; the text is carat_b200_last_error()."""
+
+
+class LayerShape(Structure):
+    _fields_ = [("global_attention", c_int32), ("query_heads", c_int32), ("kv_heads", c_int32),
+                ("head_dim", c_int32), ("rope_theta", c_float), ("key_equals_value", c_int32)]
+
+
+class ModelConfig(Structure):
+    _fields_ = [("hidden_size", c_int32), ("intermediate_size", c_int32),
+                ("vocabulary_size", c_int32), ("sliding_window", c_int32),
+                ("rms_norm_epsilon", c_float), ("layer_count", c_int32),
+                ("layers", POINTER(LayerShape))]
+
+
+class LayerWeights(Structure):
+    _fields_ = [("input_norm", c_void_p), ("q_norm", c_void_p), ("k_norm", c_void_p),
+                ("qkv", c_void_p), ("qkv_scale", c_void_p), ("o", c_void_p), ("o_scale", c_void_p),
+                ("post_attention_norm", c_void_p), ("pre_mlp_norm", c_void_p),
+                ("gate_up", c_void_p), ("gate_up_scale", c_void_p), ("down", c_void_p),
+                ("down_scale", c_void_p), ("post_mlp_norm", c_void_p), ("scalar", c_void_p)]
+
+
+class ModelWeights(Structure):
+    _fields_ = [("token_embedding", c_void_p), ("token_embedding_fp8", c_void_p),
+                ("token_embedding_scale", c_void_p), ("final_norm", c_void_p),
+                ("layers", POINTER(LayerWeights))]
+
+
+class AssistantConfig(Structure):
+    _fields_ = [("hidden_size", c_int32), ("intermediate_size", c_int32), ("query_heads", c_int32),
+                ("layer_count", c_int32), ("layer_global", POINTER(c_int32)),
+                ("rms_norm_epsilon", c_float)]
+
+
+class AssistantWeights(Structure):
+    _fields_ = [("token_embedding", c_void_p), ("token_embedding_scale", c_void_p),
+                ("pre_projection", c_void_p), ("pre_projection_scale", c_void_p),
+                ("post_projection", c_void_p), ("post_projection_scale", c_void_p),
+                ("final_norm", c_void_p), ("layers", POINTER(LayerWeights))]
+
+
+# name -> (restype, argtypes); every symbol include/carat_b200.h declares.
+_P = c_void_p
+_I = c_int
+_F = c_float
+_IP = POINTER(c_int)
+SIGNATURES = {
+    "carat_b200_last_error": (c_char_p, []),
+    "carat_b200_abi_version": (_I, []),
+    "carat_b200_device_error": (_I, [_IP]),
+    "carat_b200_fp8_linear": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P, c_size_t, _P]),
+    "carat_b200_fp8_linear_workspace_bytes": (c_size_t, [_I, _I, _I]),
+    "carat_b200_fp8_linear_argmax": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
+    "carat_b200_fp8_linear_check": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
+    "carat_b200_quantize_bf16_to_fp8": (_I, [_P, _P, _P, _P, _I, _I, _P]),
+    "carat_b200_quantize_bf16_tensor_to_fp8": (_I, [_P, _P, _P, _P, c_size_t, _P]),
+    "carat_b200_rms_norm_quantize": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _P]),
+    "carat_b200_rms_norm_add_and_norm_quantize": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _F,
+                                                      _P]),
+    "carat_b200_gelu_gate_quantize": (_I, [_P, _P, _P, _P, _I, _I, _P]),
+    "carat_b200_rms_norm_add_scale_then_norm_quantize": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P,
+                                                             _P, _I, _I, _F, _P]),
+    "carat_b200_rope_tables": (_I, [_P, _P, _I, _I, _F, _I, _P]),
+    "carat_b200_qkv_postprocess": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
+                                       _I, _F, _P]),
+    "carat_b200_verify_attention": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
+                                        _I, _I, _P]),
+    "carat_b200_backup_kv_ring_spans": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "carat_b200_restore_kv_ring_suffixes": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "carat_b200_argmax_bf16_rows": (_I, [_P, _I, _I, _P, _P]),
+    "carat_b200_greedy_prefix_accept": (_I, [_P, _P, _P, _P, _I, _I, _P, _P, _P]),
+    "carat_b200_runner_create": (_I, [POINTER(ModelConfig), POINTER(ModelWeights), _I, _I,
+                                     POINTER(AssistantConfig), POINTER(AssistantWeights),
+                                     POINTER(c_void_p)]),
+    "carat_b200_runner_destroy": (None, [_P]),
+    "carat_b200_runner_verify_greedy_proposals": (_I, [_P, _IP, _I, _I, _IP, _IP, _IP, _I, _IP,
+                                                      _IP]),
+    "carat_b200_runner_draft": (_I, [_P, _IP, _IP, _IP, _I, _I, _IP]),
+    "carat_b200_runner_prefill_slot_fp8": (_I, [_P, _I, _IP, _I, _I, _IP]),
+    "carat_b200_runner_reset_slot": (_I, [_P, _I]),
+    "carat_b200_runner_seed_empty_cache_for_benchmark": (_I, [_P, _I]),
+    "carat_b200_runner_batch": (_I, [_P]),
+    "carat_b200_runner_slot_position": (_I, [_P, _I, _IP]),
+    "carat_b200_runner_has_assistant": (_I, [_P]),
+    "carat_b200_runner_last_predictions": (_I, [_P, _IP, _I]),
+    "carat_b200_runner_device_pointer": (_I, [_P, _I, _I, POINTER(c_void_p), POINTER(c_size_t)]),
+    "carat_b200_runner_read": (_I, [_P, _I, _I, c_size_t, _P, c_size_t]),
+    "carat_b200_runner_last_device_ms": (_I, [_P, POINTER(c_float), POINTER(c_float)]),
+    "carat_b200_runner_last_launches": (_I, [_P, _IP, _IP]),
+}
+
+_library = None
+
+
+def library() -> ctypes.CDLL:
+    """The loaded shared library with argument types set. Raises when it is missing."""
+    global _library
+    if _library is None:
+        if not os.path.exists(LIBRARY_PATH):
+            raise CaratError(
+                f"{LIBRARY_PATH} is missing: build it with `python -m carat_b200.build` "
+                "(there is no CPU or PyTorch fallback)")
+        loaded = ctypes.CDLL(LIBRARY_PATH)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            function = getattr(loaded, name)
+            function.restype = restype
+            function.argtypes = argtypes
+        _library = loaded
+    return _library
+
+
+def check(status: int) -> None:
+    if status != 0:
+        message = library().carat_b200_last_error()
+        raise CaratError(message.decode() if message else f"carat_b200 call failed ({status})")
+
+
+def int_array(values):
+    values = list(values)
+    return (c_int * len(values))(*values)

@@ -1,0 +1,64 @@
+// Attention of the verify step (depth proposal rows per request over that request's KV cache plus
+// the proposals themselves) and of the drafter (one row per request over the target's cache).
+//
+// Reference semantics (cuda/prefill_gemm_attention.cu:165-349,552-730, cuda/gemm_attention.cu:88-132):
+// scale 1.0; scores rounded to bf16; fp32 max / exp / sum over the visible keys; probabilities
+// rounded to bf16 (masked keys are exactly 0); P.V accumulated in fp32 and rounded to bf16 once.
+// The computation therefore runs in three phases over a bf16 score buffer, like the reference's
+// QK GEMM -> softmax -> PV GEMM, and each K and V row is streamed from HBM exactly once.
+//
+// Key columns of a request: [0, context) are cache rows 0 .. context-1 in physical order, where
+// context = min(position, capacity) for a sliding ring and = position for a global cache;
+// [context, context + depth) are the proposal rows. A sliding ring is read in place: physical row
+// r holds the newest logical position p <= position-1 with p % capacity == r, and query t (at
+// logical position position + t) sees it iff p >= position + t - (window - 1). Proposal u is
+// visible to query t iff u <= t.
+#pragma once
+
+#include <cuda_runtime.h>
+
+namespace carat_b200 {
+
+struct AttentionArguments {
+  const void *queries;       // [requests, query_heads, depth, head_dim] bf16
+  const void *key_cache;     // layer base; row r of (slot, head) at
+  const void *value_cache;   //   base + slot*slot_stride + head*head_stride + r*head_dim
+  long long slot_stride;     // elements
+  long long head_stride;     // elements
+  // Proposal rows. When null the proposals are already in the cache at rows position + t
+  // (global layers); otherwise row t of (request, head) is at
+  //   new_keys + request*new_request_stride + head*new_head_stride + t*head_dim.
+  const void *new_keys;
+  const void *new_values;
+  long long new_request_stride;
+  long long new_head_stride;
+  const int *positions;      // [requests] logical position of proposal 0
+  const int *slots;          // [requests]
+  void *scores;              // scratch [requests, query_heads, depth, score_stride] bf16
+  int score_stride;          // >= max context + depth, multiple of 8
+  void *output;              // [requests * depth, query_heads * head_dim] bf16 (single chunk)
+  float *chunk_partials;     // [chunks, requests * depth, query_heads * head_dim] fp32 (chunks > 1)
+  int chunks;                // key chunks the P.V phase is split into (1 = write bf16 output)
+  int chunk_keys;            // keys per chunk (multiple of 64)
+  int requests;
+  int depth;
+  int query_heads;
+  int kv_heads;
+  int head_dim;              // 64, 256 or 512
+  int capacity;              // rows per (slot, head) in the cache
+  int window;                // sliding window, 0 = causal over the whole cache
+  int max_context_rows;      // upper bound of `context` over the requests (sizes the grid)
+  int draft;                 // 1: drafter semantics (depth == 1, no proposal rows, the first
+                             //    min(position + 1, capacity) cache rows are visible)
+};
+
+// Plain CUDA-core implementation of the three phases. It is the bring-up path and the on-device
+// cross-check for the tensor-core kernels.
+int launch_attention_simt(const AttentionArguments &arguments, cudaStream_t stream);
+
+// Number of key chunks needed for `max_context_rows` (+ depth proposals) at `chunk_keys` per chunk.
+inline int attention_chunks(int max_context_rows, int depth, int chunk_keys) {
+  return (max_context_rows + depth + chunk_keys - 1) / chunk_keys;
+}
+
+} // namespace carat_b200

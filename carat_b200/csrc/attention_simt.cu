@@ -1,0 +1,297 @@
+#include "attention.cuh"
+
+#include <cuda_bf16.h>
+#include <math_constants.h>
+
+namespace carat_b200 {
+namespace {
+
+struct KeyGeometry {
+  int context;  // cache rows [0, context) take part
+  int keys;     // context + proposal rows
+};
+
+__device__ __forceinline__ KeyGeometry geometry(const AttentionArguments &a, int request) {
+  const int position = a.positions[request];
+  KeyGeometry g;
+  if (a.draft) {
+    g.context = min(position + 1, a.capacity);
+    g.keys = g.context;
+  } else {
+    g.context = a.window > 0 ? min(position, a.capacity) : position;
+    g.keys = g.context + a.depth;
+  }
+  return g;
+}
+
+// Pointer to key/value row `column` of (request, kv_head).
+__device__ __forceinline__ const __nv_bfloat16 *row_pointer(const AttentionArguments &a,
+                                                            const void *cache, const void *fresh,
+                                                            int request, int kv_head, int column,
+                                                            int context) {
+  const int slot = a.slots[request];
+  const auto *cache_rows = static_cast<const __nv_bfloat16 *>(cache) + slot * a.slot_stride +
+                           kv_head * a.head_stride;
+  if (column < context)
+    return cache_rows + static_cast<size_t>(column) * a.head_dim;
+  const int proposal = column - context;
+  if (fresh == nullptr) {
+    // Global layers: proposals were written straight into the cache at position + t.
+    return cache_rows + static_cast<size_t>(a.positions[request] + proposal) * a.head_dim;
+  }
+  return static_cast<const __nv_bfloat16 *>(fresh) + request * a.new_request_stride +
+         kv_head * a.new_head_stride + static_cast<size_t>(proposal) * a.head_dim;
+}
+
+// Phase 1: scores[row, key] = bf16(q_row . k_key). One thread per key, queries in shared memory.
+template <int dimension>
+__global__ void __launch_bounds__(128) scores_kernel(AttentionArguments a) {
+  extern __shared__ __align__(16) unsigned char shared_raw[];
+  auto *shared_queries = reinterpret_cast<__nv_bfloat16 *>(shared_raw);
+  const int request = static_cast<int>(blockIdx.z);
+  const int kv_head = static_cast<int>(blockIdx.y);
+  const int group = a.query_heads / a.kv_heads;
+  const int rows = group * a.depth;
+  const KeyGeometry g = geometry(a, request);
+  const int first_key = static_cast<int>(blockIdx.x) * 128;
+  if (first_key >= g.keys)
+    return;
+  const auto *query_rows = static_cast<const __nv_bfloat16 *>(a.queries) +
+                           (static_cast<size_t>(request) * a.query_heads + kv_head * group) *
+                               a.depth * dimension;
+  for (int index = static_cast<int>(threadIdx.x) * 8; index < rows * dimension; index += 128 * 8)
+    *reinterpret_cast<uint4 *>(shared_queries + index) =
+        *reinterpret_cast<const uint4 *>(query_rows + index);
+  __syncthreads();
+  const int key = first_key + static_cast<int>(threadIdx.x);
+  if (key >= g.keys)
+    return;
+  const __nv_bfloat16 *key_row =
+      row_pointer(a, a.key_cache, a.new_keys, request, kv_head, key, g.context);
+  auto *score_rows = static_cast<__nv_bfloat16 *>(a.scores) +
+                     (static_cast<size_t>(request) * a.query_heads + kv_head * group) * a.depth *
+                         a.score_stride;
+  for (int row_base = 0; row_base < rows; row_base += 8) {
+    float sums[8] = {0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F};
+    for (int component = 0; component < dimension; component += 8) {
+      const uint4 key_raw = *reinterpret_cast<const uint4 *>(key_row + component);
+      const auto *key_pairs = reinterpret_cast<const __nv_bfloat162 *>(&key_raw);
+      float key_values[8];
+#pragma unroll
+      for (int pair = 0; pair < 4; ++pair) {
+        const float2 both = __bfloat1622float2(key_pairs[pair]);
+        key_values[2 * pair] = both.x;
+        key_values[2 * pair + 1] = both.y;
+      }
+#pragma unroll
+      for (int row = 0; row < 8; ++row) {
+        if (row_base + row < rows) {
+          const uint4 query_raw = *reinterpret_cast<const uint4 *>(
+              shared_queries + (row_base + row) * dimension + component);
+          const auto *query_pairs = reinterpret_cast<const __nv_bfloat162 *>(&query_raw);
+#pragma unroll
+          for (int pair = 0; pair < 4; ++pair) {
+            const float2 both = __bfloat1622float2(query_pairs[pair]);
+            sums[row] = fmaf(both.x, key_values[2 * pair], sums[row]);
+            sums[row] = fmaf(both.y, key_values[2 * pair + 1], sums[row]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int row = 0; row < 8; ++row) {
+      if (row_base + row < rows)
+        score_rows[static_cast<size_t>(row_base + row) * a.score_stride + key] =
+            __float2bfloat16_rn(sums[row]);
+    }
+  }
+}
+
+__device__ __forceinline__ bool key_visible(const AttentionArguments &a, int position, int token,
+                                            int column, int context) {
+  if (a.draft)
+    return true;
+  if (column >= context)
+    return column - context <= token;
+  if (a.window <= 0)
+    return true;
+  // Physical ring row -> the logical position it currently holds.
+  const int newest = position - 1;
+  const int held = newest - ((newest - column) % a.capacity);
+  return held >= position + token - (a.window - 1);
+}
+
+// Phase 2: in-place softmax of one score row; masked and padding columns become exact zeros.
+__global__ void __launch_bounds__(128) softmax_kernel(AttentionArguments a) {
+  __shared__ float scratch[4];
+  const int row_index = static_cast<int>(blockIdx.x);
+  const int token = row_index % a.depth;
+  const int request = row_index / (a.depth * a.query_heads);
+  const KeyGeometry g = geometry(a, request);
+  const int position = a.positions[request];
+  auto *row = static_cast<__nv_bfloat16 *>(a.scores) + static_cast<size_t>(row_index) * a.score_stride;
+  const int lane = static_cast<int>(threadIdx.x) & 31;
+  const int warp = static_cast<int>(threadIdx.x) >> 5;
+
+  float maximum = -CUDART_INF_F;
+  for (int key = static_cast<int>(threadIdx.x); key < g.keys; key += 128) {
+    if (key_visible(a, position, token, key, g.context))
+      maximum = fmaxf(maximum, __bfloat162float(row[key]));
+  }
+  for (int offset = 16; offset > 0; offset >>= 1)
+    maximum = fmaxf(maximum, __shfl_xor_sync(0xFFFFFFFFU, maximum, offset));
+  if (lane == 0)
+    scratch[warp] = maximum;
+  __syncthreads();
+  maximum = fmaxf(fmaxf(scratch[0], scratch[1]), fmaxf(scratch[2], scratch[3]));
+  __syncthreads();
+
+  float sum = 0.0F;
+  for (int key = static_cast<int>(threadIdx.x); key < g.keys; key += 128) {
+    if (key_visible(a, position, token, key, g.context))
+      sum += expf(__bfloat162float(row[key]) - maximum);
+  }
+  for (int offset = 16; offset > 0; offset >>= 1)
+    sum += __shfl_xor_sync(0xFFFFFFFFU, sum, offset);
+  if (lane == 0)
+    scratch[warp] = sum;
+  __syncthreads();
+  const float inverse_sum = 1.0F / (scratch[0] + scratch[1] + scratch[2] + scratch[3]);
+
+  const int padded = min(a.score_stride, (g.keys + 63) / 64 * 64);
+  for (int key = static_cast<int>(threadIdx.x); key < padded; key += 128) {
+    const bool visible = key < g.keys && key_visible(a, position, token, key, g.context);
+    row[key] = visible
+                   ? __float2bfloat16_rn(expf(__bfloat162float(row[key]) - maximum) * inverse_sum)
+                   : __float2bfloat16_rn(0.0F);
+  }
+}
+
+// Phase 3: out[row, :] = sum_key P[row, key] * V[key, :] over one key chunk. Each thread owns two
+// adjacent components; probabilities are staged through shared memory 64 keys at a time.
+template <int dimension, int max_rows>
+__global__ void __launch_bounds__(dimension / 2) pv_kernel(AttentionArguments a) {
+  __shared__ __nv_bfloat16 probabilities[max_rows][64];
+  const int request = static_cast<int>(blockIdx.z);
+  const int kv_head = static_cast<int>(blockIdx.y);
+  const int chunk = static_cast<int>(blockIdx.x);
+  const int group = a.query_heads / a.kv_heads;
+  const int rows = group * a.depth;
+  const KeyGeometry g = geometry(a, request);
+  const int chunk_begin = chunk * a.chunk_keys;
+  const int chunk_end = min(g.keys, chunk_begin + a.chunk_keys);
+  const int component = static_cast<int>(threadIdx.x) * 2;
+  const auto *score_rows = static_cast<const __nv_bfloat16 *>(a.scores) +
+                           (static_cast<size_t>(request) * a.query_heads + kv_head * group) *
+                               a.depth * a.score_stride;
+  float sums[max_rows][2];
+#pragma unroll
+  for (int row = 0; row < max_rows; ++row) {
+    sums[row][0] = 0.0F;
+    sums[row][1] = 0.0F;
+  }
+  for (int tile = chunk_begin; tile < chunk_end; tile += 64) {
+    __syncthreads();
+    for (int index = static_cast<int>(threadIdx.x); index < rows * 64; index += dimension / 2) {
+      const int row = index / 64;
+      const int key = tile + index % 64;
+      probabilities[row][index % 64] =
+          key < chunk_end ? score_rows[static_cast<size_t>(row) * a.score_stride + key]
+                          : __float2bfloat16_rn(0.0F);
+    }
+    __syncthreads();
+    const int tile_keys = min(64, chunk_end - tile);
+    for (int offset = 0; offset < tile_keys; ++offset) {
+      const __nv_bfloat16 *value_row = row_pointer(a, a.value_cache, a.new_values, request,
+                                                   kv_head, tile + offset, g.context);
+      const float2 value =
+          __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(value_row + component));
+#pragma unroll
+      for (int row = 0; row < max_rows; ++row) {
+        if (row < rows) {
+          const float probability = __bfloat162float(probabilities[row][offset]);
+          sums[row][0] = fmaf(probability, value.x, sums[row][0]);
+          sums[row][1] = fmaf(probability, value.y, sums[row][1]);
+        }
+      }
+    }
+  }
+  const int width = a.query_heads * dimension;
+#pragma unroll
+  for (int row = 0; row < max_rows; ++row) {
+    if (row < rows) {
+      const int local_head = row / a.depth;
+      const int token = row % a.depth;
+      const size_t out_row = static_cast<size_t>(request) * a.depth + token;
+      const size_t column = static_cast<size_t>(kv_head * group + local_head) * dimension + component;
+      if (a.chunks > 1) {
+        float *destination = a.chunk_partials +
+                             (static_cast<size_t>(chunk) * a.requests * a.depth + out_row) * width +
+                             column;
+        *reinterpret_cast<float2 *>(destination) = make_float2(sums[row][0], sums[row][1]);
+      } else {
+        auto *destination = static_cast<__nv_bfloat16 *>(a.output) + out_row * width + column;
+        *reinterpret_cast<__nv_bfloat162 *>(destination) =
+            __halves2bfloat162(__float2bfloat16_rn(sums[row][0]), __float2bfloat16_rn(sums[row][1]));
+      }
+    }
+  }
+}
+
+template <int dimension> int launch_phases(const AttentionArguments &a, cudaStream_t stream) {
+  const int group = a.query_heads / a.kv_heads;
+  const int rows = group * a.depth;
+  const int max_keys = a.max_context_rows + (a.draft ? 0 : a.depth);
+  const size_t query_bytes = static_cast<size_t>(rows) * dimension * sizeof(__nv_bfloat16);
+  if (query_bytes > 96 * 1024 || rows > 80)
+    return -2;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(scores_kernel<dimension>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             96 * 1024) != cudaSuccess)
+      return -10;
+    configured = true;
+  }
+  const dim3 score_grid(static_cast<unsigned>((max_keys + 127) / 128),
+                        static_cast<unsigned>(a.kv_heads), static_cast<unsigned>(a.requests));
+  scores_kernel<dimension><<<score_grid, 128, query_bytes, stream>>>(a);
+  softmax_kernel<<<a.requests * a.query_heads * a.depth, 128, 0, stream>>>(a);
+  const dim3 pv_grid(static_cast<unsigned>(a.chunks), static_cast<unsigned>(a.kv_heads),
+                     static_cast<unsigned>(a.requests));
+  if (rows <= 16) {
+    pv_kernel<dimension, 16><<<pv_grid, dimension / 2, 0, stream>>>(a);
+  } else if (rows <= 40) {
+    pv_kernel<dimension, 40><<<pv_grid, dimension / 2, 0, stream>>>(a);
+  } else {
+    pv_kernel<dimension, 80><<<pv_grid, dimension / 2, 0, stream>>>(a);
+  }
+  return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
+}
+
+} // namespace
+
+int launch_attention_simt(const AttentionArguments &a, cudaStream_t stream) {
+  if (a.queries == nullptr || a.key_cache == nullptr || a.value_cache == nullptr ||
+      a.positions == nullptr || a.slots == nullptr || a.scores == nullptr || a.requests <= 0 ||
+      a.depth <= 0 || a.query_heads <= 0 || a.kv_heads <= 0 || a.query_heads % a.kv_heads != 0 ||
+      a.capacity <= 0 || a.chunks <= 0 || a.chunk_keys <= 0 || a.chunk_keys % 64 != 0 ||
+      a.score_stride % 8 != 0 || (a.chunks > 1 ? a.chunk_partials == nullptr : a.output == nullptr) ||
+      (a.draft && a.depth != 1)) {
+    return -1;
+  }
+  const int max_keys = a.max_context_rows + (a.draft ? 0 : a.depth);
+  if (max_keys > a.score_stride || a.chunks * a.chunk_keys < max_keys)
+    return -2;
+  switch (a.head_dim) {
+  case 64:
+    return launch_phases<64>(a, stream);
+  case 256:
+    return launch_phases<256>(a, stream);
+  case 512:
+    return launch_phases<512>(a, stream);
+  default:
+    return -3;
+  }
+}
+
+} // namespace carat_b200

@@ -1,0 +1,300 @@
+// C entry points for the row operators, attention-side operators and bookkeeping kernels
+// (declared in include/carat_b200.h).
+#include "../../include/carat_b200.h"
+#include "accept.cuh"
+#include "attention.cuh"
+#include "context.cuh"
+#include "qkv_post.cuh"
+#include "row_ops.cuh"
+
+#include <string>
+
+using namespace carat_b200;
+
+namespace {
+
+int finish(int status, const char *what) {
+  if (status == 0)
+    return 0;
+  const cudaError_t last = cudaGetLastError();
+  if (status == -1) {
+    set_last_error(std::string("invalid ") + what + " arguments");
+  } else if (status == -2) {
+    set_last_error(std::string(what) + " shape exceeds what one launch supports");
+  } else if (status == -3) {
+    set_last_error(std::string(what) + ": unsupported head dimension");
+  } else {
+    set_last_error(std::string(what) + " launch failed: " + cudaGetErrorString(last));
+  }
+  return status;
+}
+
+// Clears the caller's scratch word on the stream, then hands out the quantisation target.
+int prepare_target(QuantTarget *target, void *fp8_output, float *scale, void *scratch,
+                   cudaStream_t stream) {
+  if (fp8_output == nullptr || scale == nullptr || scratch == nullptr) {
+    set_last_error("invalid FP8 quantization shape");
+    return -1;
+  }
+  const int status =
+      check_cuda(cudaMemsetAsync(scratch, 0, sizeof(unsigned int), stream), "clear FP8 amax");
+  if (status != 0)
+    return status;
+  *target = QuantTarget{fp8_output, scale, static_cast<unsigned int *>(scratch)};
+  return 0;
+}
+
+} // namespace
+
+extern "C" int carat_b200_quantize_bf16_to_fp8(const void *bf16_input, void *fp8_output,
+                                               float *device_scale, void *device_scratch,
+                                               int rows, int width, void *stream) {
+  const auto cuda_stream = static_cast<cudaStream_t>(stream);
+  QuantTarget target{};
+  const int status = prepare_target(&target, fp8_output, device_scale, device_scratch, cuda_stream);
+  if (status != 0)
+    return status;
+  return finish(launch_quant(bf16_input, nullptr, 0, target, rows, width, cuda_stream),
+                "FP8 quantization");
+}
+
+extern "C" int carat_b200_quantize_bf16_tensor_to_fp8(const void *bf16_input, void *fp8_output,
+                                                      float *device_scale, void *device_scratch,
+                                                      size_t elements, void *stream) {
+  const auto cuda_stream = static_cast<cudaStream_t>(stream);
+  QuantTarget target{};
+  const int status = prepare_target(&target, fp8_output, device_scale, device_scratch, cuda_stream);
+  if (status != 0)
+    return status;
+  return finish(launch_quant_tensor(bf16_input, fp8_output, device_scale, target.amax_bits,
+                                    elements, cuda_stream),
+                "FP8 quantization");
+}
+
+extern "C" int carat_b200_rms_norm_quantize(const void *bf16_input, const void *bf16_weight,
+                                            void *bf16_normalized, void *fp8_output,
+                                            float *device_scale, void *device_scratch, int rows,
+                                            int width, float epsilon, void *stream) {
+  const auto cuda_stream = static_cast<cudaStream_t>(stream);
+  QuantTarget target{};
+  const int status = prepare_target(&target, fp8_output, device_scale, device_scratch, cuda_stream);
+  if (status != 0)
+    return status;
+  return finish(launch_norm_quant(bf16_input, bf16_weight, bf16_normalized, target, rows, width,
+                                  epsilon, cuda_stream),
+                "RMSNorm quantization");
+}
+
+extern "C" int carat_b200_rms_norm_add_and_norm_quantize(
+    const void *bf16_input, const void *bf16_weight, const void *bf16_residual,
+    const void *bf16_next_weight, void *bf16_first, void *fp8_output, float *device_scale,
+    void *device_scratch, int rows, int width, float epsilon, void *stream) {
+  const auto cuda_stream = static_cast<cudaStream_t>(stream);
+  QuantTarget target{};
+  const int status = prepare_target(&target, fp8_output, device_scale, device_scratch, cuda_stream);
+  if (status != 0)
+    return status;
+  return finish(launch_post_attention_norms_quant(bf16_input, PartialSource{}, bf16_weight,
+                                                  bf16_residual, bf16_next_weight, bf16_first,
+                                                  target, rows, width, epsilon, cuda_stream),
+                "RMSNorm add-and-norm quantization");
+}
+
+extern "C" int carat_b200_gelu_gate_quantize(const void *bf16_packed_gate_up, void *fp8_output,
+                                             float *device_scale, void *device_scratch, int rows,
+                                             int width, void *stream) {
+  const auto cuda_stream = static_cast<cudaStream_t>(stream);
+  QuantTarget target{};
+  const int status = prepare_target(&target, fp8_output, device_scale, device_scratch, cuda_stream);
+  if (status != 0)
+    return status;
+  return finish(launch_geglu_quant(bf16_packed_gate_up, target, rows, width, cuda_stream),
+                "GeGLU quantization");
+}
+
+extern "C" int carat_b200_rms_norm_add_scale_then_norm_quantize(
+    const void *bf16_input, const void *bf16_weight, const void *bf16_residual,
+    const void *bf16_scalar, void *bf16_output, const void *bf16_next_weight, void *bf16_next,
+    void *fp8_output, float *device_scale, void *device_scratch, int rows, int width,
+    float epsilon, void *stream) {
+  const auto cuda_stream = static_cast<cudaStream_t>(stream);
+  QuantTarget target{};
+  const int status = prepare_target(&target, fp8_output, device_scale, device_scratch, cuda_stream);
+  if (status != 0)
+    return status;
+  return finish(launch_layer_output_norm_quant(bf16_input, PartialSource{}, bf16_weight,
+                                               bf16_residual, bf16_scalar, bf16_output,
+                                               bf16_next_weight, bf16_next, target, rows, width,
+                                               epsilon, cuda_stream),
+                "layer output quantization");
+}
+
+extern "C" int carat_b200_rope_tables(void *bf16_cosine, void *bf16_sine, int positions,
+                                      int head_dim, float theta, int proportional, void *stream) {
+  return finish(launch_rope_tables(bf16_cosine, bf16_sine, positions, head_dim, theta,
+                                   proportional != 0, static_cast<cudaStream_t>(stream)),
+                "RoPE table");
+}
+
+extern "C" int carat_b200_qkv_postprocess(const void *bf16_packed, const void *bf16_query_norm,
+                                          const void *bf16_key_norm, const void *bf16_cosine,
+                                          const void *bf16_sine, void *bf16_queries,
+                                          void *bf16_keys, void *bf16_values,
+                                          const int *device_positions, int requests, int depth,
+                                          int query_heads, int kv_heads, int head_dim,
+                                          int key_equals_value, int table_positions, float epsilon,
+                                          void *stream) {
+  QkvPostArguments a{};
+  a.packed = bf16_packed;
+  a.query_norm = bf16_query_norm;
+  a.key_norm = bf16_key_norm;
+  a.cosine = bf16_cosine;
+  a.sine = bf16_sine;
+  a.queries = bf16_queries;
+  a.key_base = bf16_keys;
+  a.value_base = bf16_values;
+  a.head_stride = static_cast<long long>(depth) * head_dim;
+  a.slot_stride = a.head_stride * kv_heads;
+  a.positions = device_positions;
+  a.direct = 0;
+  a.capacity = depth > 0 ? depth : 1;
+  a.requests = requests;
+  a.depth = depth;
+  a.query_heads = query_heads;
+  a.kv_heads = kv_heads;
+  a.head_dim = head_dim;
+  a.key_equals_value = key_equals_value;
+  a.max_positions = table_positions;
+  a.epsilon = epsilon;
+  return finish(launch_qkv_post(a, static_cast<cudaStream_t>(stream)), "QKV post-processing");
+}
+
+namespace {
+__global__ void identity_slots_kernel(int *slots, int count) {
+  const int index = static_cast<int>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (index < count)
+    slots[index] = index;
+}
+} // namespace
+
+extern "C" int carat_b200_verify_attention(const void *bf16_queries, const void *bf16_key_caches,
+                                           const void *bf16_value_caches,
+                                           const void *bf16_new_keys, const void *bf16_new_values,
+                                           const int *device_positions, void *bf16_output,
+                                           void *bf16_scores, int score_stride, int requests,
+                                           int depth, int query_heads, int kv_heads, int head_dim,
+                                           int capacity, int window, int max_position,
+                                           void *stream) {
+  if (bf16_new_keys == nullptr || bf16_new_values == nullptr || requests <= 0 || requests > 1024) {
+    set_last_error("invalid verify attention arguments");
+    return -1;
+  }
+  const auto cuda_stream = static_cast<cudaStream_t>(stream);
+  // Request r owns cache r: an identity slot table kept in device memory for the library's life.
+  static int *identity_slots = nullptr;
+  if (identity_slots == nullptr) {
+    if (check_cuda(cudaMalloc(&identity_slots, sizeof(int) * 1024), "allocate slot table") != 0)
+      return -100;
+    identity_slots_kernel<<<4, 256, 0, cuda_stream>>>(identity_slots, 1024);
+  }
+  AttentionArguments a{};
+  a.queries = bf16_queries;
+  a.key_cache = bf16_key_caches;
+  a.value_cache = bf16_value_caches;
+  a.head_stride = static_cast<long long>(capacity) * head_dim;
+  a.slot_stride = a.head_stride * kv_heads;
+  a.new_keys = bf16_new_keys;
+  a.new_values = bf16_new_values;
+  a.new_head_stride = static_cast<long long>(depth) * head_dim;
+  a.new_request_stride = a.new_head_stride * kv_heads;
+  a.positions = device_positions;
+  a.slots = identity_slots;
+  a.scores = bf16_scores;
+  a.score_stride = score_stride;
+  a.output = bf16_output;
+  a.chunks = 1;
+  a.chunk_keys = (score_stride + 63) / 64 * 64;
+  a.requests = requests;
+  a.depth = depth;
+  a.query_heads = query_heads;
+  a.kv_heads = kv_heads;
+  a.head_dim = head_dim;
+  a.capacity = capacity;
+  a.window = window;
+  a.max_context_rows = window > 0 ? (max_position < capacity ? max_position : capacity)
+                                  : max_position;
+  return finish(launch_attention_simt(a, cuda_stream), "verify attention");
+}
+
+extern "C" int carat_b200_backup_kv_ring_spans(const void *const *device_key_sources,
+                                               const void *const *device_value_sources,
+                                               void *backup_keys, void *backup_values,
+                                               const int *device_position_starts, int requests,
+                                               int heads, int tokens, int head_dim,
+                                               int source_capacity, void *stream) {
+  return finish(launch_backup_kv_ring_spans(device_key_sources, device_value_sources, backup_keys,
+                                            backup_values, device_position_starts, requests, heads,
+                                            tokens, head_dim, source_capacity,
+                                            static_cast<cudaStream_t>(stream)),
+                "KV ring backup");
+}
+
+extern "C" int carat_b200_restore_kv_ring_suffixes(
+    const void *backup_keys, const void *backup_values, void *const *device_key_destinations,
+    void *const *device_value_destinations, const int *device_position_starts,
+    const int *device_accepted_tokens, int requests, int heads, int tokens, int head_dim,
+    int destination_capacity, void *stream) {
+  return finish(launch_restore_kv_ring_suffixes(
+                    backup_keys, backup_values, device_key_destinations, device_value_destinations,
+                    device_position_starts, device_accepted_tokens, requests, heads, tokens,
+                    head_dim, destination_capacity, static_cast<cudaStream_t>(stream)),
+                "KV ring restore");
+}
+
+extern "C" int carat_b200_argmax_bf16_rows(const void *bf16_values, int rows, int elements,
+                                           int *device_output, void *stream) {
+  return finish(launch_argmax_bf16_rows(bf16_values, rows, elements, device_output,
+                                        static_cast<cudaStream_t>(stream)),
+                "argmax");
+}
+
+namespace {
+__global__ void accept_only_kernel(const int *proposals, const int *target_first,
+                                   const int *predictions, const int *caps, int requests,
+                                   int depth, int *accepted_tokens, int *next_tokens) {
+  const int request = static_cast<int>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (request >= requests)
+    return;
+  int cap = depth;
+  if (caps != nullptr)
+    cap = min(max(caps[request], 0), depth);
+  const int start = request * depth;
+  int accepted = 0;
+  while (accepted < cap) {
+    const int expected = accepted == 0 ? target_first[request] : predictions[start + accepted - 1];
+    if (proposals[start + accepted] != expected)
+      break;
+    ++accepted;
+  }
+  accepted_tokens[request] = accepted;
+  next_tokens[request] = accepted == 0 ? target_first[request] : predictions[start + accepted - 1];
+}
+} // namespace
+
+extern "C" int carat_b200_greedy_prefix_accept(const int *device_proposals,
+                                               const int *device_target_first,
+                                               const int *device_predictions,
+                                               const int *device_caps, int requests, int depth,
+                                               int *device_accepted, int *device_next_tokens,
+                                               void *stream) {
+  if (device_proposals == nullptr || device_target_first == nullptr ||
+      device_predictions == nullptr || device_accepted == nullptr ||
+      device_next_tokens == nullptr || requests <= 0 || depth <= 0) {
+    set_last_error("invalid greedy verification batch");
+    return -1;
+  }
+  accept_only_kernel<<<(requests + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      device_proposals, device_target_first, device_predictions, device_caps, requests, depth,
+      device_accepted, device_next_tokens);
+  return finish(cudaPeekAtLastError() == cudaSuccess ? 0 : -11, "greedy prefix accept");
+}

@@ -1,0 +1,559 @@
+#include "row_ops.cuh"
+
+#include <cooperative_groups.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+namespace cg = cooperative_groups;
+
+namespace carat_b200 {
+namespace {
+
+constexpr int row_threads = 512;
+constexpr int row_warps = row_threads / 32;
+
+enum class RowMode : int { embed_norm, norm, plain, post_attention, geglu, layer_output, embed_concat };
+
+struct RowArguments {
+  // sources
+  const __nv_bfloat16 *input;        // bf16 [rows, width] (or [rows, 2*width] for geglu)
+  const float *partial;              // fp32 [splits, rows, width] when splits > 0
+  int splits;
+  const float *input_scale;
+  const float *weight_scale;
+  const __nv_bfloat16 *embedding;
+  const int *tokens;
+  const int *row_indices;
+  int vocabulary;
+  const __nv_bfloat16 *norm_weight;
+  const __nv_bfloat16 *residual;
+  const __nv_bfloat16 *next_norm_weight;
+  const __nv_bfloat16 *scalar;
+  // bf16 outputs (any may be null)
+  __nv_bfloat16 *first_out;
+  __nv_bfloat16 *second_out;
+  // quantised output
+  unsigned char *fp8_output;
+  float *scale;
+  unsigned int *amax_bits;
+  unsigned int *clear_base;
+  int clear_words;
+  int width;
+  float epsilon;
+};
+
+__device__ __forceinline__ float warp_sum(float value) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1)
+    value += __shfl_xor_sync(0xFFFFFFFFU, value, offset);
+  return value;
+}
+
+__device__ __forceinline__ float warp_max(float value) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1)
+    value = fmaxf(value, __shfl_xor_sync(0xFFFFFFFFU, value, offset));
+  return value;
+}
+
+// Every thread receives the block-wide result. `scratch` holds row_warps floats.
+__device__ float block_sum(float value, float *scratch) {
+  value = warp_sum(value);
+  __syncthreads();
+  if ((threadIdx.x & 31U) == 0U)
+    scratch[threadIdx.x >> 5U] = value;
+  __syncthreads();
+  float total = threadIdx.x < row_warps ? scratch[threadIdx.x] : 0.0F;
+  if (threadIdx.x < 32U)
+    total = warp_sum(total);
+  if (threadIdx.x == 0U)
+    scratch[0] = total;
+  __syncthreads();
+  return scratch[0];
+}
+
+__device__ float block_max(float value, float *scratch) {
+  value = warp_max(value);
+  __syncthreads();
+  if ((threadIdx.x & 31U) == 0U)
+    scratch[threadIdx.x >> 5U] = value;
+  __syncthreads();
+  float total = threadIdx.x < row_warps ? scratch[threadIdx.x] : 0.0F;
+  if (threadIdx.x < 32U)
+    total = warp_max(total);
+  if (threadIdx.x == 0U)
+    scratch[0] = total;
+  __syncthreads();
+  return scratch[0];
+}
+
+struct Pack8 {
+  float v[8];
+};
+
+__device__ __forceinline__ Pack8 load_bf16x8(const __nv_bfloat16 *pointer) {
+  const uint4 raw = *reinterpret_cast<const uint4 *>(pointer);
+  const __nv_bfloat162 *pairs = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+  Pack8 result;
+#pragma unroll
+  for (int pair = 0; pair < 4; ++pair) {
+    const float2 both = __bfloat1622float2(pairs[pair]);
+    result.v[2 * pair] = both.x;
+    result.v[2 * pair + 1] = both.y;
+  }
+  return result;
+}
+
+// Rounds to bf16, stores, and returns the rounded values as floats.
+__device__ __forceinline__ Pack8 round_bf16x8(const Pack8 &values, uint4 *packed) {
+  __nv_bfloat162 pairs[4];
+  Pack8 rounded;
+#pragma unroll
+  for (int pair = 0; pair < 4; ++pair) {
+    pairs[pair] = __halves2bfloat162(__float2bfloat16_rn(values.v[2 * pair]),
+                                     __float2bfloat16_rn(values.v[2 * pair + 1]));
+    const float2 both = __bfloat1622float2(pairs[pair]);
+    rounded.v[2 * pair] = both.x;
+    rounded.v[2 * pair + 1] = both.y;
+  }
+  *packed = *reinterpret_cast<const uint4 *>(pairs);
+  return rounded;
+}
+
+__device__ __forceinline__ float gelu_tanh(float value) {
+  constexpr float coefficient = 0.7978845608028654F;
+  return 0.5F * value * (1.0F + tanhf(coefficient * (value + 0.044715F * value * value * value)));
+}
+
+// Loads eight values of the row's primary source: a bf16 tensor, or split-K / key-chunk partials
+// summed in a fixed order, scaled and rounded to bf16 exactly like a separate finishing kernel.
+__device__ __forceinline__ Pack8 load_source(const RowArguments &a, size_t row, int column,
+                                             size_t rows, float partial_scale) {
+  if (a.splits <= 0)
+    return load_bf16x8(a.input + row * a.width + column);
+  Pack8 sum;
+#pragma unroll
+  for (int index = 0; index < 8; ++index)
+    sum.v[index] = 0.0F;
+  for (int split = 0; split < a.splits; ++split) {
+    const float *source = a.partial + (static_cast<size_t>(split) * rows + row) * a.width + column;
+    const float4 low = *reinterpret_cast<const float4 *>(source);
+    const float4 high = *reinterpret_cast<const float4 *>(source + 4);
+    sum.v[0] += low.x;
+    sum.v[1] += low.y;
+    sum.v[2] += low.z;
+    sum.v[3] += low.w;
+    sum.v[4] += high.x;
+    sum.v[5] += high.y;
+    sum.v[6] += high.z;
+    sum.v[7] += high.w;
+  }
+  Pack8 rounded;
+#pragma unroll
+  for (int index = 0; index < 8; ++index)
+    rounded.v[index] = __bfloat162float(__float2bfloat16_rn(sum.v[index] * partial_scale));
+  return rounded;
+}
+
+template <RowMode mode> __global__ void __launch_bounds__(row_threads) row_kernel(RowArguments a) {
+  cg::grid_group grid = cg::this_grid();
+  extern __shared__ __align__(16) unsigned char row_storage[];
+  auto *row_values = reinterpret_cast<__nv_bfloat16 *>(row_storage);
+  __shared__ float scratch[row_warps];
+
+  const size_t row = blockIdx.x;
+  const size_t rows = gridDim.x;
+  const int width = a.width;
+  const float width_value = static_cast<float>(width);
+  float row_amax = 0.0F;
+
+  if constexpr (mode == RowMode::embed_norm) {
+    // The per-step scratch words must be zero before the first atomic maximum of the step; the
+    // barrier below orders this against every later use, including this kernel's own.
+    for (int word = static_cast<int>(blockIdx.x) * row_threads + static_cast<int>(threadIdx.x);
+         word < a.clear_words; word += static_cast<int>(gridDim.x) * row_threads)
+      a.clear_base[word] = 0U;
+    grid.sync();
+  }
+
+  float partial_scale = 1.0F;
+  if (a.splits > 0 && a.input_scale != nullptr)
+    partial_scale = a.input_scale[0] * a.weight_scale[0];
+
+  if constexpr (mode == RowMode::plain) {
+    for (int column = static_cast<int>(threadIdx.x) * 8; column < width; column += row_threads * 8) {
+      const Pack8 values = load_source(a, row, column, rows, partial_scale);
+      uint4 packed;
+      const Pack8 rounded = round_bf16x8(values, &packed);
+      *reinterpret_cast<uint4 *>(row_values + column) = packed;
+      if (a.first_out != nullptr)
+        *reinterpret_cast<uint4 *>(a.first_out + row * width + column) = packed;
+#pragma unroll
+      for (int index = 0; index < 8; ++index)
+        row_amax = fmaxf(row_amax, fabsf(rounded.v[index]));
+    }
+  } else if constexpr (mode == RowMode::embed_concat) {
+    // `width` is the concatenated width; the left half is the scaled embedding row, the right
+    // half a bf16 copy of the carried hidden state.
+    const int half = width / 2;
+    const int token = a.tokens[row];
+    const size_t source_row = a.row_indices != nullptr ? static_cast<size_t>(a.row_indices[row]) : row;
+    const float embed_scale = __bfloat162float(__float2bfloat16_rn(sqrtf(static_cast<float>(half))));
+    for (int column = static_cast<int>(threadIdx.x) * 8; column < width; column += row_threads * 8) {
+      Pack8 values;
+      if (column < half) {
+        if (token >= 0 && token < a.vocabulary) {
+          values = load_bf16x8(a.embedding + static_cast<size_t>(token) * half + column);
+        } else {
+#pragma unroll
+          for (int index = 0; index < 8; ++index)
+            values.v[index] = 0.0F;
+        }
+#pragma unroll
+        for (int index = 0; index < 8; ++index)
+          values.v[index] *= embed_scale;
+      } else {
+        values = load_bf16x8(a.input + source_row * half + (column - half));
+      }
+      uint4 packed;
+      const Pack8 rounded = round_bf16x8(values, &packed);
+      *reinterpret_cast<uint4 *>(row_values + column) = packed;
+#pragma unroll
+      for (int index = 0; index < 8; ++index)
+        row_amax = fmaxf(row_amax, fabsf(rounded.v[index]));
+    }
+  } else if constexpr (mode == RowMode::geglu) {
+    const __nv_bfloat16 *packed_row = a.input + row * 2 * width;
+    for (int column = static_cast<int>(threadIdx.x) * 8; column < width; column += row_threads * 8) {
+      const Pack8 gate = load_bf16x8(packed_row + column);
+      const Pack8 up = load_bf16x8(packed_row + width + column);
+      Pack8 product;
+#pragma unroll
+      for (int index = 0; index < 8; ++index)
+        product.v[index] = gelu_tanh(gate.v[index]) * up.v[index];
+      uint4 packed;
+      const Pack8 rounded = round_bf16x8(product, &packed);
+      *reinterpret_cast<uint4 *>(row_values + column) = packed;
+#pragma unroll
+      for (int index = 0; index < 8; ++index)
+        row_amax = fmaxf(row_amax, fabsf(rounded.v[index]));
+    }
+  } else {
+    // Stage 1: the row that gets normalised first, kept in shared memory as bf16.
+    float square_sum = 0.0F;
+    for (int column = static_cast<int>(threadIdx.x) * 8; column < width; column += row_threads * 8) {
+      Pack8 values;
+      if constexpr (mode == RowMode::embed_norm) {
+        const int token = a.tokens[row];
+        const float scale = __bfloat162float(__float2bfloat16_rn(sqrtf(width_value)));
+        Pack8 raw;
+        if (token >= 0 && token < a.vocabulary) {
+          raw = load_bf16x8(a.embedding + static_cast<size_t>(token) * width + column);
+        } else {
+#pragma unroll
+          for (int index = 0; index < 8; ++index)
+            raw.v[index] = 0.0F;
+        }
+#pragma unroll
+        for (int index = 0; index < 8; ++index)
+          raw.v[index] *= scale;
+        uint4 packed;
+        values = round_bf16x8(raw, &packed);
+        *reinterpret_cast<uint4 *>(a.first_out + row * width + column) = packed;
+        *reinterpret_cast<uint4 *>(row_values + column) = packed;
+      } else {
+        values = load_source(a, row, column, rows, partial_scale);
+        uint4 packed;
+        (void)round_bf16x8(values, &packed);  // already bf16-exact; repack for shared memory
+        *reinterpret_cast<uint4 *>(row_values + column) = packed;
+      }
+#pragma unroll
+      for (int index = 0; index < 8; ++index)
+        square_sum += values.v[index] * values.v[index];
+    }
+    float inverse_rms = rsqrtf(block_sum(square_sum, scratch) / width_value + a.epsilon);
+
+    if constexpr (mode == RowMode::post_attention || mode == RowMode::layer_output) {
+      // first = bf16(norm(x) * w + residual) [* scalar, rounded again, for the layer output];
+      // it replaces the row in shared memory and is what the second norm reads.
+      float layer_scale = 1.0F;
+      if constexpr (mode == RowMode::layer_output)
+        layer_scale = __bfloat162float(*a.scalar);
+      square_sum = 0.0F;
+      for (int column = static_cast<int>(threadIdx.x) * 8; column < width;
+           column += row_threads * 8) {
+        const Pack8 values = load_bf16x8(row_values + column);
+        const Pack8 weights = load_bf16x8(a.norm_weight + column);
+        const Pack8 residual = load_bf16x8(a.residual + row * width + column);
+        Pack8 result;
+#pragma unroll
+        for (int index = 0; index < 8; ++index)
+          result.v[index] = values.v[index] * inverse_rms * weights.v[index] + residual.v[index];
+        uint4 packed;
+        Pack8 rounded = round_bf16x8(result, &packed);
+        if constexpr (mode == RowMode::layer_output) {
+#pragma unroll
+          for (int index = 0; index < 8; ++index)
+            result.v[index] = rounded.v[index] * layer_scale;
+          rounded = round_bf16x8(result, &packed);
+        }
+        *reinterpret_cast<uint4 *>(row_values + column) = packed;
+        *reinterpret_cast<uint4 *>(a.first_out + row * width + column) = packed;
+#pragma unroll
+        for (int index = 0; index < 8; ++index)
+          square_sum += rounded.v[index] * rounded.v[index];
+      }
+      inverse_rms = rsqrtf(block_sum(square_sum, scratch) / width_value + a.epsilon);
+    }
+
+    // Stage 2: the normalised row that is quantised.
+    const __nv_bfloat16 *weight =
+        (mode == RowMode::post_attention || mode == RowMode::layer_output) ? a.next_norm_weight
+                                                                           : a.norm_weight;
+    for (int column = static_cast<int>(threadIdx.x) * 8; column < width; column += row_threads * 8) {
+      const Pack8 values = load_bf16x8(row_values + column);
+      const Pack8 weights = load_bf16x8(weight + column);
+      Pack8 result;
+#pragma unroll
+      for (int index = 0; index < 8; ++index)
+        result.v[index] = values.v[index] * inverse_rms * weights.v[index];
+      uint4 packed;
+      const Pack8 rounded = round_bf16x8(result, &packed);
+      *reinterpret_cast<uint4 *>(row_values + column) = packed;
+      if (a.second_out != nullptr)
+        *reinterpret_cast<uint4 *>(a.second_out + row * width + column) = packed;
+#pragma unroll
+      for (int index = 0; index < 8; ++index)
+        row_amax = fmaxf(row_amax, fabsf(rounded.v[index]));
+    }
+  }
+
+  // Tensor-wide maximum, one barrier, then quantise this row from shared memory.
+  row_amax = block_max(row_amax, scratch);
+  if (threadIdx.x == 0U)
+    atomicMax(a.amax_bits, __float_as_uint(row_amax));
+  grid.sync();
+  const float tensor_amax = __uint_as_float(*reinterpret_cast<volatile unsigned int *>(a.amax_bits));
+  const float scale = tensor_amax > 0.0F ? tensor_amax / 448.0F : 1.0F;
+  const float inverse_scale = 1.0F / scale;
+  if (blockIdx.x == 0U && threadIdx.x == 0U)
+    *a.scale = scale;
+  for (int column = static_cast<int>(threadIdx.x) * 8; column < width; column += row_threads * 8) {
+    const Pack8 values = load_bf16x8(row_values + column);
+    __nv_fp8x4_e4m3 low(make_float4(values.v[0] * inverse_scale, values.v[1] * inverse_scale,
+                                    values.v[2] * inverse_scale, values.v[3] * inverse_scale));
+    __nv_fp8x4_e4m3 high(make_float4(values.v[4] * inverse_scale, values.v[5] * inverse_scale,
+                                     values.v[6] * inverse_scale, values.v[7] * inverse_scale));
+    uint2 packed;
+    packed.x = low.__x;
+    packed.y = high.__x;
+    *reinterpret_cast<uint2 *>(a.fp8_output + row * width + column) = packed;
+  }
+}
+
+template <RowMode mode> int launch_rows(RowArguments arguments, int rows, cudaStream_t stream) {
+  if (rows <= 0 || arguments.width <= 0 || arguments.width % 8 != 0 ||
+      arguments.fp8_output == nullptr || arguments.scale == nullptr ||
+      arguments.amax_bits == nullptr) {
+    return -1;
+  }
+  const size_t shared_bytes = static_cast<size_t>(arguments.width) * sizeof(__nv_bfloat16);
+  static int resident_limit = -1;
+  static cudaError_t configure_status = cudaSuccess;
+  if (resident_limit < 0) {
+    configure_status = cudaFuncSetAttribute(row_kernel<mode>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    int device = 0;
+    int multiprocessors = 0;
+    int per_multiprocessor = 0;
+    if (configure_status == cudaSuccess)
+      configure_status = cudaGetDevice(&device);
+    if (configure_status == cudaSuccess)
+      configure_status =
+          cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device);
+    if (configure_status == cudaSuccess)
+      configure_status = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+          &per_multiprocessor, row_kernel<mode>, row_threads, 64 * 1024);
+    resident_limit = configure_status == cudaSuccess ? multiprocessors * per_multiprocessor : 0;
+  }
+  if (configure_status != cudaSuccess)
+    return -10;
+  if (rows > resident_limit || shared_bytes > 64 * 1024)
+    return -2;
+  void *kernel_arguments[] = {&arguments};
+  const cudaError_t status = cudaLaunchCooperativeKernel(
+      reinterpret_cast<const void *>(row_kernel<mode>), dim3(static_cast<unsigned>(rows)),
+      dim3(row_threads), kernel_arguments, shared_bytes, stream);
+  return status == cudaSuccess ? 0 : -11;
+}
+
+// Large tensors (weights at load time): the reference's three-launch form, cuda/linear.cu:117-153.
+__global__ void tensor_amax_kernel(const __nv_bfloat16 *input, size_t elements,
+                                   unsigned int *maximum_bits) {
+  __shared__ float scratch[row_warps];
+  float maximum = 0.0F;
+  for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; index < elements;
+       index += static_cast<size_t>(blockDim.x) * gridDim.x)
+    maximum = fmaxf(maximum, fabsf(__bfloat162float(input[index])));
+  maximum = block_max(maximum, scratch);
+  if (threadIdx.x == 0U)
+    atomicMax(maximum_bits, __float_as_uint(maximum));
+}
+
+__global__ void tensor_scale_kernel(const unsigned int *maximum_bits, float *scale) {
+  const float maximum = __uint_as_float(*maximum_bits);
+  *scale = maximum > 0.0F ? maximum / 448.0F : 1.0F;
+}
+
+__global__ void tensor_quantize_kernel(const __nv_bfloat16 *input, __nv_fp8_e4m3 *output,
+                                       const float *scale, size_t elements) {
+  const float inverse_scale = 1.0F / *scale;
+  for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; index < elements;
+       index += static_cast<size_t>(blockDim.x) * gridDim.x)
+    output[index] = __nv_fp8_e4m3(__bfloat162float(input[index]) * inverse_scale);
+}
+
+RowArguments base_arguments(QuantTarget target, int width, float epsilon) {
+  RowArguments arguments{};
+  arguments.fp8_output = static_cast<unsigned char *>(target.fp8_output);
+  arguments.scale = target.scale;
+  arguments.amax_bits = target.amax_bits;
+  arguments.width = width;
+  arguments.epsilon = epsilon;
+  return arguments;
+}
+
+void set_source(RowArguments &arguments, const void *input, const PartialSource &source) {
+  arguments.input = static_cast<const __nv_bfloat16 *>(input);
+  if (source.partial != nullptr && source.splits > 0) {
+    arguments.partial = source.partial;
+    arguments.splits = source.splits;
+    arguments.input_scale = source.input_scale;
+    arguments.weight_scale = source.weight_scale;
+  }
+}
+
+} // namespace
+
+int launch_quant_tensor(const void *input, void *fp8_output, float *scale,
+                        unsigned int *amax_bits, size_t elements, cudaStream_t stream) {
+  if (input == nullptr || fp8_output == nullptr || scale == nullptr || amax_bits == nullptr ||
+      elements == 0) {
+    return -1;
+  }
+  const size_t wanted = (elements + row_threads - 1) / row_threads;
+  const int blocks = static_cast<int>(wanted < 4096 ? wanted : 4096);
+  tensor_amax_kernel<<<blocks, row_threads, 0, stream>>>(
+      static_cast<const __nv_bfloat16 *>(input), elements, amax_bits);
+  tensor_scale_kernel<<<1, 1, 0, stream>>>(amax_bits, scale);
+  tensor_quantize_kernel<<<blocks, row_threads, 0, stream>>>(
+      static_cast<const __nv_bfloat16 *>(input), static_cast<__nv_fp8_e4m3 *>(fp8_output), scale,
+      elements);
+  return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
+}
+
+int launch_embed_norm_quant(const void *embedding, const int *tokens, int vocabulary,
+                            const void *norm_weight, void *hidden_out, QuantTarget target,
+                            int rows, int width, float epsilon, unsigned int *clear_base,
+                            int clear_words, cudaStream_t stream) {
+  if (embedding == nullptr || tokens == nullptr || norm_weight == nullptr || hidden_out == nullptr)
+    return -1;
+  RowArguments arguments = base_arguments(target, width, epsilon);
+  arguments.embedding = static_cast<const __nv_bfloat16 *>(embedding);
+  arguments.tokens = tokens;
+  arguments.vocabulary = vocabulary;
+  arguments.norm_weight = static_cast<const __nv_bfloat16 *>(norm_weight);
+  arguments.first_out = static_cast<__nv_bfloat16 *>(hidden_out);
+  arguments.clear_base = clear_base;
+  arguments.clear_words = clear_base == nullptr ? 0 : clear_words;
+  return launch_rows<RowMode::embed_norm>(arguments, rows, stream);
+}
+
+int launch_embed_concat_quant(const void *embedding, const int *tokens, int vocabulary,
+                              const void *hidden, const int *row_indices, QuantTarget target,
+                              int rows, int width, cudaStream_t stream) {
+  if (embedding == nullptr || tokens == nullptr || hidden == nullptr)
+    return -1;
+  RowArguments arguments = base_arguments(target, 2 * width, 0.0F);
+  arguments.embedding = static_cast<const __nv_bfloat16 *>(embedding);
+  arguments.tokens = tokens;
+  arguments.vocabulary = vocabulary;
+  arguments.input = static_cast<const __nv_bfloat16 *>(hidden);
+  arguments.row_indices = row_indices;
+  return launch_rows<RowMode::embed_concat>(arguments, rows, stream);
+}
+
+int launch_norm_quant(const void *input, const void *norm_weight, void *normalized_out,
+                      QuantTarget target, int rows, int width, float epsilon,
+                      cudaStream_t stream) {
+  if (input == nullptr || norm_weight == nullptr)
+    return -1;
+  RowArguments arguments = base_arguments(target, width, epsilon);
+  arguments.input = static_cast<const __nv_bfloat16 *>(input);
+  arguments.norm_weight = static_cast<const __nv_bfloat16 *>(norm_weight);
+  arguments.second_out = static_cast<__nv_bfloat16 *>(normalized_out);
+  return launch_rows<RowMode::norm>(arguments, rows, stream);
+}
+
+int launch_quant(const void *input, const float *chunk_partials, int chunks, QuantTarget target,
+                 int rows, int width, cudaStream_t stream) {
+  if (input == nullptr && chunk_partials == nullptr)
+    return -1;
+  RowArguments arguments = base_arguments(target, width, 0.0F);
+  arguments.input = static_cast<const __nv_bfloat16 *>(input);
+  if (chunk_partials != nullptr && chunks > 0) {
+    arguments.partial = chunk_partials;
+    arguments.splits = chunks;
+  }
+  return launch_rows<RowMode::plain>(arguments, rows, stream);
+}
+
+int launch_post_attention_norms_quant(const void *projected, PartialSource source,
+                                      const void *norm_weight, const void *residual,
+                                      const void *next_norm_weight, void *first_out,
+                                      QuantTarget target, int rows, int width, float epsilon,
+                                      cudaStream_t stream) {
+  if ((projected == nullptr && source.partial == nullptr) || norm_weight == nullptr ||
+      residual == nullptr || next_norm_weight == nullptr || first_out == nullptr) {
+    return -1;
+  }
+  RowArguments arguments = base_arguments(target, width, epsilon);
+  set_source(arguments, projected, source);
+  arguments.norm_weight = static_cast<const __nv_bfloat16 *>(norm_weight);
+  arguments.residual = static_cast<const __nv_bfloat16 *>(residual);
+  arguments.next_norm_weight = static_cast<const __nv_bfloat16 *>(next_norm_weight);
+  arguments.first_out = static_cast<__nv_bfloat16 *>(first_out);
+  return launch_rows<RowMode::post_attention>(arguments, rows, stream);
+}
+
+int launch_geglu_quant(const void *packed_gate_up, QuantTarget target, int rows, int width,
+                       cudaStream_t stream) {
+  if (packed_gate_up == nullptr)
+    return -1;
+  RowArguments arguments = base_arguments(target, width, 0.0F);
+  arguments.input = static_cast<const __nv_bfloat16 *>(packed_gate_up);
+  return launch_rows<RowMode::geglu>(arguments, rows, stream);
+}
+
+int launch_layer_output_norm_quant(const void *down, PartialSource source, const void *norm_weight,
+                                   const void *residual, const void *scalar, void *output,
+                                   const void *next_norm_weight, void *next_out,
+                                   QuantTarget target, int rows, int width, float epsilon,
+                                   cudaStream_t stream) {
+  if ((down == nullptr && source.partial == nullptr) || norm_weight == nullptr ||
+      residual == nullptr || scalar == nullptr || output == nullptr ||
+      next_norm_weight == nullptr) {
+    return -1;
+  }
+  RowArguments arguments = base_arguments(target, width, epsilon);
+  set_source(arguments, down, source);
+  arguments.norm_weight = static_cast<const __nv_bfloat16 *>(norm_weight);
+  arguments.residual = static_cast<const __nv_bfloat16 *>(residual);
+  arguments.scalar = static_cast<const __nv_bfloat16 *>(scalar);
+  arguments.first_out = static_cast<__nv_bfloat16 *>(output);
+  arguments.next_norm_weight = static_cast<const __nv_bfloat16 *>(next_norm_weight);
+  arguments.second_out = static_cast<__nv_bfloat16 *>(next_out);
+  return launch_rows<RowMode::layer_output>(arguments, rows, stream);
+}
+
+} // namespace carat_b200

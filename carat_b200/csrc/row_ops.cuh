@@ -1,0 +1,87 @@
+// Row-wise fused operators of the verify / draft step. Each one produces a bf16 activation row the
+// way the reference does (same fp32 math, same bf16 rounding points) and, in the same launch,
+// quantises the whole [rows, width] tensor to e4m3 with the reference's tensor-wide scale rule
+// (amax / 448, cuda/linear.cu:76-115). The tensor-wide maximum couples all rows, so the kernels are
+// cooperative launches: one CTA per row, an atomic maximum, one grid barrier, then every CTA
+// quantises its row straight from shared memory. Nothing is re-read from HBM.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace carat_b200 {
+
+// Where a quantised activation goes, plus the running maximum that must be zero before the launch.
+struct QuantTarget {
+  void *fp8_output;        // [rows, width] e4m3
+  float *scale;            // one fp32: amax / 448 (1.0 when amax == 0)
+  unsigned int *amax_bits; // scratch word, zero on entry
+};
+
+// Sum of split-K partials: value = bf16((sum_s partial[s]) * input_scale * weight_scale).
+struct PartialSource {
+  const float *partial;      // [splits, rows, width] fp32
+  int splits;
+  const float *input_scale;  // device scalars of the linear that produced the partials
+  const float *weight_scale;
+};
+
+// Tensor-scale quantisation of a tensor of any size in three launches (amax, scale, convert), the
+// form the reference uses for weights at load time (cuda/linear.cu:117-153,261-271).
+// *amax_bits must be zero on entry.
+int launch_quant_tensor(const void *input, void *fp8_output, float *scale,
+                        unsigned int *amax_bits, size_t elements, cudaStream_t stream);
+
+// hidden = bf16(embedding[token] * bf16(sqrt(width))) (cuda/ops.cu:321-335); normalized =
+// bf16(rmsnorm(hidden) * norm_weight) (cuda/ops.cu:27-68) -> e4m3. Also zeroes `clear_words`
+// 32-bit words at `clear_base` (the per-step amax scratch) before anything uses them.
+int launch_embed_norm_quant(const void *embedding, const int *tokens, int vocabulary,
+                            const void *norm_weight, void *hidden_out, QuantTarget target,
+                            int rows, int width, float epsilon, unsigned int *clear_base,
+                            int clear_words, cudaStream_t stream);
+
+// Drafter input row: [ bf16(embedding[token] * bf16(sqrt(width))) | hidden[source_row] ] -> e4m3 over
+// 2 * width columns (cuda/assistant_runner.cu:279-285). source_row = row_indices[r] when
+// row_indices is given (first draft step: gather from the per-slot table), else r.
+int launch_embed_concat_quant(const void *embedding, const int *tokens, int vocabulary,
+                              const void *hidden, const int *row_indices, QuantTarget target,
+                              int rows, int width, cudaStream_t stream);
+
+// normalized = bf16(rmsnorm(input) * norm_weight) -> e4m3 (cuda/layer_runner.cu:241-262 without the
+// intermediate bf16 tensor). When normalized_out is not null the bf16 rows are stored too.
+int launch_norm_quant(const void *input, const void *norm_weight, void *normalized_out,
+                      QuantTarget target, int rows, int width, float epsilon,
+                      cudaStream_t stream);
+
+// Plain tensor-scale quantisation of a bf16 tensor (cuda/linear.cu:76-115). When `partials` is
+// given (attention split over key chunks) the bf16 input is first formed as
+// bf16(sum_c partials[c]) from [chunks, rows, width] fp32.
+int launch_quant(const void *input, const float *chunk_partials, int chunks, QuantTarget target,
+                 int rows, int width, cudaStream_t stream);
+
+// projected = source (bf16 tensor or split-K partials); first = bf16(rmsnorm(projected) * w1 +
+// residual); second = bf16(rmsnorm(first) * w2) -> e4m3 (cuda/ops.cu:87-179,
+// cuda/layer_runner.cu:306-330). `first_out` receives the new residual stream.
+int launch_post_attention_norms_quant(const void *projected, PartialSource source,
+                                      const void *norm_weight, const void *residual,
+                                      const void *next_norm_weight, void *first_out,
+                                      QuantTarget target, int rows, int width, float epsilon,
+                                      cudaStream_t stream);
+
+// activated = bf16(gelu_tanh(gate) * up) from rows packed [gate | up] -> e4m3
+// (cuda/ops.cu:228-284).
+int launch_geglu_quant(const void *packed_gate_up, QuantTarget target, int rows, int width,
+                       cudaStream_t stream);
+
+// down = source; output = bf16(bf16(rmsnorm(down) * w + residual) * scalar)
+// (cuda/ops.cu:181-217); then next = bf16(rmsnorm(output) * next_norm_weight) -> e4m3, which is
+// the following layer's input norm or the final norm. `next_out` (may be null) stores the bf16
+// rows of `next` (the final-normed hidden state the drafter receives).
+int launch_layer_output_norm_quant(const void *down, PartialSource source, const void *norm_weight,
+                                   const void *residual, const void *scalar, void *output,
+                                   const void *next_norm_weight, void *next_out,
+                                   QuantTarget target, int rows, int width, float epsilon,
+                                   cudaStream_t stream);
+
+} // namespace carat_b200

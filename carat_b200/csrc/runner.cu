@@ -1,0 +1,1146 @@
+// The batch runner: request slots, KV arenas and the verify / draft steps, i.e. the part of
+// carat::Gemma4BatchModelRunner and carat::Gemma4AssistantRunner that the speculative-decoding
+// loop calls (cuda/batch_model_runner.cu:1617-1836, cuda/assistant_runner.cu:218-338), exported as
+// C entry points. Every per-step decision that the reference takes on the host after a
+// device-to-host copy (accept lengths, hidden hand-off, rollback) runs on the device here; one
+// host-to-device copy starts a step and one device-to-host copy ends it.
+#include "../../include/carat_b200.h"
+#include "accept.cuh"
+#include "attention.cuh"
+#include "context.cuh"
+#include "fp8_linear.cuh"
+#include "qkv_post.cuh"
+#include "row_ops.cuh"
+
+#include <algorithm>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+using namespace carat_b200;
+
+namespace {
+
+constexpr int maximum_depth = 9;       // k = 8 drafts + the forced token
+constexpr int maximum_rows = 128;      // rows one FP8 linear launch accepts
+constexpr int global_chunk_keys = 1024;
+
+struct Failure {
+  std::string message;
+};
+
+void require_cuda(cudaError_t result, const char *operation) {
+  if (result != cudaSuccess)
+    throw Failure{std::string(operation) + ": " + cudaGetErrorString(result)};
+}
+
+void require_launch(int status, const char *operation) {
+  if (status != 0) {
+    const cudaError_t last = cudaGetLastError();
+    throw Failure{std::string(operation) + " failed (" + std::to_string(status) + "): " +
+                  cudaGetErrorString(last)};
+  }
+}
+
+class DeviceBuffer {
+public:
+  DeviceBuffer() = default;
+  explicit DeviceBuffer(size_t bytes, bool zero = false) { allocate(bytes, zero); }
+  DeviceBuffer(const DeviceBuffer &) = delete;
+  DeviceBuffer &operator=(const DeviceBuffer &) = delete;
+  DeviceBuffer(DeviceBuffer &&other) noexcept : pointer_(other.pointer_), bytes_(other.bytes_) {
+    other.pointer_ = nullptr;
+    other.bytes_ = 0;
+  }
+  ~DeviceBuffer() { cudaFree(pointer_); }
+  void allocate(size_t bytes, bool zero = false) {
+    bytes_ = bytes < 256 ? 256 : bytes;
+    require_cuda(cudaMalloc(&pointer_, bytes_), "allocate runner memory");
+    if (zero)
+      require_cuda(cudaMemset(pointer_, 0, bytes_), "clear runner memory");
+  }
+  template <typename T = void> T *get() const { return static_cast<T *>(pointer_); }
+  size_t bytes() const { return bytes_; }
+
+private:
+  void *pointer_{nullptr};
+  size_t bytes_{0};
+};
+
+class PinnedBuffer {
+public:
+  PinnedBuffer() = default;
+  PinnedBuffer(const PinnedBuffer &) = delete;
+  PinnedBuffer &operator=(const PinnedBuffer &) = delete;
+  ~PinnedBuffer() { cudaFreeHost(pointer_); }
+  void allocate(size_t bytes) {
+    require_cuda(cudaMallocHost(&pointer_, bytes), "allocate pinned mailbox");
+  }
+  template <typename T> T *get() const { return static_cast<T *>(pointer_); }
+
+private:
+  void *pointer_{nullptr};
+};
+
+struct LayerState {
+  carat_b200_layer_shape shape{};
+  carat_b200_layer_weights weights{};
+  int capacity{0};
+  int rope{0};  // index into Runner::rope_tables
+  DeviceBuffer kv;        // K region then V region
+  size_t value_offset{0}; // bytes
+  long long slot_stride{0};
+  long long head_stride{0};
+  DeviceBuffer staged;    // sliding layers: proposal K then V, [requests, kv_heads, depth, D]
+  size_t staged_value_offset{0};
+  int query_width() const { return shape.query_heads * shape.head_dim; }
+  int kv_width() const { return shape.kv_heads * shape.head_dim; }
+  int packed_width() const { return query_width() + kv_width() * (shape.key_equals_value ? 1 : 2); }
+  void *keys() const { return kv.get<unsigned char>(); }
+  void *values() const { return kv.get<unsigned char>() + value_offset; }
+  void *staged_keys() const { return staged.get<unsigned char>(); }
+  void *staged_values() const { return staged.get<unsigned char>() + staged_value_offset; }
+};
+
+struct RopeTable {
+  int head_dim;
+  float theta;
+  bool proportional;
+  DeviceBuffer cosine;
+  DeviceBuffer sine;
+};
+
+struct LayerPlans {
+  LinearPlan qkv, o, gate_up, down;
+};
+
+struct StepPlans {
+  std::vector<LayerPlans> layers;
+  LinearPlan head;        // LM head (argmax epilogue)
+  LinearPlan pre, post;   // drafter projections
+};
+
+} // namespace
+
+struct carat_b200_runner {
+  // ---- model
+  carat_b200_model_config config{};
+  std::vector<carat_b200_layer_shape> shapes;
+  carat_b200_model_weights weights{};
+  std::vector<LayerState> layers;
+  std::vector<std::unique_ptr<RopeTable>> rope_tables;
+  int batch{0};
+  int maximum_context{0};
+  int shared_sliding{-1};
+  int shared_global{-1};
+  // ---- assistant
+  bool has_assistant{false};
+  carat_b200_assistant_config assistant{};
+  std::vector<int32_t> assistant_kinds;
+  carat_b200_assistant_weights assistant_weights{};
+  std::vector<carat_b200_layer_weights> assistant_layers;
+  // ---- state
+  std::vector<int> slot_positions;
+  DeviceBuffer device_slot_positions;
+  DeviceBuffer hidden_by_slot;
+  cudaStream_t stream{nullptr};
+  cudaEvent_t start_event{nullptr};
+  cudaEvent_t stop_event{nullptr};
+  float last_verify_ms{0.0F};
+  float last_draft_ms{0.0F};
+  int last_verify_launches{0};
+  int last_draft_launches{0};
+  int launches{0};
+  int last_rows{0};
+  std::vector<int> last_predictions;
+  // ---- workspaces (target)
+  DeviceBuffer hidden_a, hidden_b, residual, final_hidden;
+  DeviceBuffer quantized;    // e4m3 activation feeding the next linear
+  DeviceBuffer packed;       // QKV projection output
+  DeviceBuffer queries;
+  DeviceBuffer attention_out;
+  DeviceBuffer attention_partials;
+  DeviceBuffer scores;
+  DeviceBuffer projected;    // bf16 output of a linear that did not split K
+  DeviceBuffer gate_up;
+  DeviceBuffer split_partials;
+  DeviceBuffer scratch_words;  // [amax words | argmax keys]
+  DeviceBuffer scales;
+  DeviceBuffer step_inputs;    // tokens, positions, slots, target_first, caps
+  DeviceBuffer step_results;   // accepted, next, predictions, error word
+  DeviceBuffer commit_layers;
+  int commit_layer_count{0};
+  PinnedBuffer host_inputs;
+  PinnedBuffer host_results;
+  int amax_words{0};
+  int score_stride_sliding{0};
+  int score_stride_global{0};
+  int *device_error{nullptr};
+  std::map<int, StepPlans> verify_plans;
+  // ---- workspaces (assistant)
+  DeviceBuffer a_hidden_a, a_hidden_b, a_residual, a_final_hidden, a_quantized, a_projected,
+      a_queries, a_attention_out, a_attention_partials, a_scores, a_linear_out, a_gate_up,
+      a_previous_hidden, a_scratch_words, a_scales, a_tokens, a_proposals;
+  int a_amax_words{0};
+  std::map<int, StepPlans> draft_plans;
+
+  ~carat_b200_runner() {
+    if (start_event != nullptr)
+      cudaEventDestroy(start_event);
+    if (stop_event != nullptr)
+      cudaEventDestroy(stop_event);
+    if (stream != nullptr)
+      cudaStreamDestroy(stream);
+  }
+};
+
+namespace {
+
+using Runner = carat_b200_runner;
+
+LinearPlan plan_linear(const void *input, const void *weight, int rows, int in, int out,
+                       int splits) {
+  LinearPlan plan;
+  const char *message = "invalid FP8 linear shape";
+  if (make_linear_plan(&plan, input, weight, rows, in, out, splits, &message) != 0)
+    throw Failure{message};
+  return plan;
+}
+
+int find_rope(Runner &runner, int head_dim, float theta, bool proportional) {
+  for (size_t index = 0; index < runner.rope_tables.size(); ++index) {
+    const RopeTable &table = *runner.rope_tables[index];
+    if (table.head_dim == head_dim && table.theta == theta && table.proportional == proportional)
+      return static_cast<int>(index);
+  }
+  auto table = std::make_unique<RopeTable>();
+  table->head_dim = head_dim;
+  table->theta = theta;
+  table->proportional = proportional;
+  const size_t bytes = static_cast<size_t>(runner.maximum_context) * head_dim * 2;
+  table->cosine.allocate(bytes);
+  table->sine.allocate(bytes);
+  require_launch(launch_rope_tables(table->cosine.get(), table->sine.get(), runner.maximum_context,
+                                    head_dim, theta, proportional, runner.stream),
+                 "build RoPE tables");
+  runner.rope_tables.push_back(std::move(table));
+  return static_cast<int>(runner.rope_tables.size()) - 1;
+}
+
+size_t align_up(size_t value, size_t alignment = 256) {
+  return (value + alignment - 1) / alignment * alignment;
+}
+
+void build_runner(Runner &runner, const carat_b200_model_config &config,
+                  const carat_b200_model_weights &weights, int batch, int maximum_context,
+                  const carat_b200_assistant_config *assistant,
+                  const carat_b200_assistant_weights *assistant_weights) {
+  if (batch <= 0 || maximum_context <= 0 || config.layer_count <= 0 || config.layers == nullptr ||
+      weights.layers == nullptr || config.hidden_size <= 0 || config.hidden_size % 16 != 0 ||
+      config.intermediate_size <= 0 || config.intermediate_size % 16 != 0 ||
+      config.vocabulary_size <= 0 || config.sliding_window <= 0 ||
+      weights.token_embedding == nullptr || weights.token_embedding_fp8 == nullptr ||
+      weights.token_embedding_scale == nullptr || weights.final_norm == nullptr) {
+    throw Failure{"invalid batch model runner shape"};
+  }
+  runner.config = config;
+  runner.shapes.assign(config.layers, config.layers + config.layer_count);
+  runner.config.layers = runner.shapes.data();
+  runner.weights = weights;
+  runner.batch = batch;
+  runner.maximum_context = maximum_context;
+  require_cuda(cudaStreamCreateWithFlags(&runner.stream, cudaStreamNonBlocking),
+               "create runner stream");
+  require_cuda(cudaEventCreate(&runner.start_event), "create timing event");
+  require_cuda(cudaEventCreate(&runner.stop_event), "create timing event");
+  runner.device_error = device_error_word();
+  if (runner.device_error == nullptr)
+    throw Failure{"device error word is unavailable"};
+
+  const int hidden = config.hidden_size;
+  const int rows = maximum_rows;
+  int widest_query = 0;
+  int widest_packed = 0;
+  std::vector<CommitLayer> commit;
+  runner.layers.resize(static_cast<size_t>(config.layer_count));
+  for (int index = 0; index < config.layer_count; ++index) {
+    LayerState &layer = runner.layers[static_cast<size_t>(index)];
+    layer.shape = config.layers[index];
+    layer.weights = weights.layers[index];
+    const auto &shape = layer.shape;
+    if (shape.query_heads <= 0 || shape.kv_heads <= 0 || shape.query_heads % shape.kv_heads != 0 ||
+        (shape.head_dim != 64 && shape.head_dim != 256 && shape.head_dim != 512)) {
+      throw Failure{"unsupported Gemma 4 attention shape"};
+    }
+    if (shape.global_attention) {
+      runner.shared_global = index;
+    } else {
+      runner.shared_sliding = index;
+    }
+    layer.capacity = shape.global_attention ? maximum_context
+                                            : std::min(maximum_context, config.sliding_window);
+    layer.head_stride = static_cast<long long>(layer.capacity) * shape.head_dim;
+    layer.slot_stride = layer.head_stride * shape.kv_heads;
+    const size_t payload = align_up(static_cast<size_t>(batch) * layer.slot_stride * 2);
+    layer.value_offset = payload;
+    layer.kv.allocate(2 * payload, true);
+    layer.rope = find_rope(runner, shape.head_dim, shape.rope_theta, shape.global_attention != 0);
+    if (!shape.global_attention) {
+      const size_t staged = align_up(static_cast<size_t>(batch) * shape.kv_heads * maximum_depth *
+                                     shape.head_dim * 2);
+      layer.staged_value_offset = staged;
+      layer.staged.allocate(2 * staged, true);
+      CommitLayer entry{};
+      entry.key_cache = layer.keys();
+      entry.value_cache = layer.values();
+      entry.staged_keys = layer.staged_keys();
+      entry.staged_values = layer.staged_values();
+      entry.slot_stride = layer.slot_stride;
+      entry.head_stride = layer.head_stride;
+      entry.kv_heads = shape.kv_heads;
+      entry.head_dim = shape.head_dim;
+      entry.capacity = layer.capacity;
+      commit.push_back(entry);
+    }
+    widest_query = std::max(widest_query, layer.query_width());
+    widest_packed = std::max(widest_packed, layer.packed_width());
+  }
+  runner.commit_layer_count = static_cast<int>(commit.size());
+  if (!commit.empty()) {
+    runner.commit_layers.allocate(commit.size() * sizeof(CommitLayer));
+    require_cuda(cudaMemcpy(runner.commit_layers.get(), commit.data(),
+                            commit.size() * sizeof(CommitLayer), cudaMemcpyHostToDevice),
+                 "copy commit table");
+  }
+
+  runner.slot_positions.assign(static_cast<size_t>(batch), 0);
+  runner.device_slot_positions.allocate(sizeof(int) * batch, true);
+  runner.hidden_by_slot.allocate(static_cast<size_t>(batch) * hidden * 2, true);
+  const size_t row_hidden = static_cast<size_t>(rows) * hidden * 2;
+  runner.hidden_a.allocate(row_hidden);
+  runner.hidden_b.allocate(row_hidden);
+  runner.residual.allocate(row_hidden);
+  runner.final_hidden.allocate(row_hidden, true);
+  const int widest_input = std::max({hidden, config.intermediate_size, widest_query});
+  runner.quantized.allocate(static_cast<size_t>(rows) * widest_input);
+  runner.packed.allocate(static_cast<size_t>(rows) * widest_packed * 2);
+  runner.queries.allocate(static_cast<size_t>(rows) * widest_query * 2);
+  runner.attention_out.allocate(static_cast<size_t>(rows) * widest_query * 2);
+  const int global_chunks = attention_chunks(maximum_context, 0, global_chunk_keys);
+  runner.attention_partials.allocate(static_cast<size_t>(global_chunks) * rows * widest_query * 4);
+  const int sliding_capacity = std::min(maximum_context, config.sliding_window);
+  runner.score_stride_sliding = (sliding_capacity + maximum_depth + 63) / 64 * 64;
+  runner.score_stride_global = (maximum_context + 63) / 64 * 64;
+  int most_heads = 0;
+  for (const LayerState &layer : runner.layers)
+    most_heads = std::max(most_heads, layer.shape.query_heads);
+  runner.scores.allocate(static_cast<size_t>(rows) * most_heads *
+                         std::max(runner.score_stride_sliding, runner.score_stride_global) * 2);
+  runner.projected.allocate(row_hidden);
+  runner.gate_up.allocate(static_cast<size_t>(rows) * 2 * config.intermediate_size * 2);
+  // Split-K partials [splits, rows, features] fp32; plans that would need more are rejected.
+  runner.split_partials.allocate(static_cast<size_t>(16) * rows * std::max(hidden, 4096) * 4);
+  runner.amax_words = (config.layer_count + 1) * 4;
+  runner.scratch_words.allocate(static_cast<size_t>(runner.amax_words + 2 * rows) * 4, true);
+  runner.scales.allocate(static_cast<size_t>(runner.amax_words) * 4, true);
+  runner.step_inputs.allocate(sizeof(int) * (rows + 4 * batch), true);
+  runner.step_results.allocate(sizeof(int) * (2 * batch + rows + 1), true);
+  runner.host_inputs.allocate(sizeof(int) * (rows + 4 * batch));
+  runner.host_results.allocate(sizeof(int) * (2 * batch + rows + 1 + batch * maximum_depth));
+
+  if (assistant != nullptr && assistant_weights != nullptr) {
+    if (assistant->hidden_size <= 0 || assistant->hidden_size % 16 != 0 ||
+        assistant->intermediate_size <= 0 || assistant->intermediate_size % 16 != 0 ||
+        assistant->query_heads <= 0 || assistant->layer_count <= 0 ||
+        assistant->layer_global == nullptr || assistant_weights->layers == nullptr ||
+        assistant_weights->token_embedding == nullptr ||
+        assistant_weights->pre_projection == nullptr ||
+        assistant_weights->post_projection == nullptr || assistant_weights->final_norm == nullptr) {
+      throw Failure{"invalid assistant shape"};
+    }
+    runner.has_assistant = true;
+    runner.assistant = *assistant;
+    runner.assistant_kinds.assign(assistant->layer_global,
+                                  assistant->layer_global + assistant->layer_count);
+    runner.assistant.layer_global = runner.assistant_kinds.data();
+    runner.assistant_weights = *assistant_weights;
+    runner.assistant_layers.assign(assistant_weights->layers,
+                                   assistant_weights->layers + assistant->layer_count);
+    runner.assistant_weights.layers = runner.assistant_layers.data();
+    int widest = 0;
+    for (int index = 0; index < assistant->layer_count; ++index) {
+      const int shared = assistant->layer_global[index] ? runner.shared_global : runner.shared_sliding;
+      if (shared < 0)
+        throw Failure{"assistant layer has no target KV layer to share"};
+      const auto &shape = runner.layers[static_cast<size_t>(shared)].shape;
+      if (assistant->query_heads % shape.kv_heads != 0)
+        throw Failure{"assistant query heads do not divide into the shared KV heads"};
+      widest = std::max(widest, assistant->query_heads * shape.head_dim);
+    }
+    const int a_hidden = assistant->hidden_size;
+    const size_t a_row_hidden = static_cast<size_t>(batch) * a_hidden * 2;
+    runner.a_hidden_a.allocate(a_row_hidden);
+    runner.a_hidden_b.allocate(a_row_hidden);
+    runner.a_residual.allocate(a_row_hidden);
+    runner.a_final_hidden.allocate(a_row_hidden);
+    runner.a_linear_out.allocate(std::max(a_row_hidden, static_cast<size_t>(batch) * hidden * 2));
+    const int a_widest_input =
+        std::max({2 * hidden, assistant->intermediate_size, widest, a_hidden});
+    runner.a_quantized.allocate(static_cast<size_t>(batch) * a_widest_input);
+    runner.a_projected.allocate(static_cast<size_t>(batch) * widest * 2);
+    runner.a_queries.allocate(static_cast<size_t>(batch) * widest * 2);
+    runner.a_attention_out.allocate(static_cast<size_t>(batch) * widest * 2);
+    runner.a_attention_partials.allocate(static_cast<size_t>(global_chunks) * batch * widest * 4);
+    runner.a_scores.allocate(static_cast<size_t>(batch) * assistant->query_heads *
+                             runner.score_stride_global * 2);
+    runner.a_gate_up.allocate(static_cast<size_t>(batch) * 2 * assistant->intermediate_size * 2);
+    runner.a_previous_hidden.allocate(static_cast<size_t>(batch) * hidden * 2);
+    runner.a_amax_words = 2 + 4 * assistant->layer_count;
+    runner.a_scratch_words.allocate(static_cast<size_t>(runner.a_amax_words + 2 * batch) * 4, true);
+    runner.a_scales.allocate(static_cast<size_t>(runner.a_amax_words) * 4, true);
+    runner.a_tokens.allocate(sizeof(int) * 4 * batch, true);
+    runner.a_proposals.allocate(sizeof(int) * batch * maximum_depth, true);
+  }
+  require_cuda(cudaStreamSynchronize(runner.stream), "finish runner construction");
+}
+
+StepPlans &verify_plans_for(Runner &runner, int rows) {
+  const auto found = runner.verify_plans.find(rows);
+  if (found != runner.verify_plans.end())
+    return found->second;
+  StepPlans plans;
+  const int hidden = runner.config.hidden_size;
+  const int intermediate = runner.config.intermediate_size;
+  for (const LayerState &layer : runner.layers) {
+    LayerPlans entry;
+    entry.qkv = plan_linear(runner.quantized.get(), layer.weights.qkv, rows, hidden,
+                            layer.packed_width(), 0);
+    entry.o = plan_linear(runner.quantized.get(), layer.weights.o, rows, layer.query_width(),
+                          hidden, 0);
+    entry.gate_up = plan_linear(runner.quantized.get(), layer.weights.gate_up, rows, hidden,
+                                2 * intermediate, 0);
+    entry.down = plan_linear(runner.quantized.get(), layer.weights.down, rows, intermediate,
+                             hidden, 0);
+    for (const LinearPlan *plan : {&entry.qkv, &entry.o, &entry.gate_up, &entry.down}) {
+      if (linear_partial_bytes(*plan) > runner.split_partials.bytes())
+        throw Failure{"split-K workspace is too small for this model shape"};
+    }
+    plans.layers.push_back(entry);
+  }
+  plans.head = plan_linear(runner.quantized.get(), runner.weights.token_embedding_fp8, rows, hidden,
+                           runner.config.vocabulary_size, 1);
+  return runner.verify_plans.emplace(rows, std::move(plans)).first->second;
+}
+
+const LayerState &shared_layer(const Runner &runner, int assistant_layer) {
+  const int index = runner.assistant_kinds[static_cast<size_t>(assistant_layer)]
+                        ? runner.shared_global
+                        : runner.shared_sliding;
+  return runner.layers[static_cast<size_t>(index)];
+}
+
+StepPlans &draft_plans_for(Runner &runner, int rows) {
+  const auto found = runner.draft_plans.find(rows);
+  if (found != runner.draft_plans.end())
+    return found->second;
+  StepPlans plans;
+  const int hidden = runner.config.hidden_size;
+  const int a_hidden = runner.assistant.hidden_size;
+  const int intermediate = runner.assistant.intermediate_size;
+  size_t most_partial = 0;
+  for (int index = 0; index < runner.assistant.layer_count; ++index) {
+    const auto &weights = runner.assistant_layers[static_cast<size_t>(index)];
+    const int query_width = runner.assistant.query_heads * shared_layer(runner, index).shape.head_dim;
+    LayerPlans entry;
+    entry.qkv = plan_linear(runner.a_quantized.get(), weights.qkv, rows, a_hidden, query_width, 0);
+    entry.o = plan_linear(runner.a_quantized.get(), weights.o, rows, query_width, a_hidden, 0);
+    entry.gate_up =
+        plan_linear(runner.a_quantized.get(), weights.gate_up, rows, a_hidden, 2 * intermediate, 0);
+    entry.down = plan_linear(runner.a_quantized.get(), weights.down, rows, intermediate, a_hidden, 0);
+    for (const LinearPlan *plan : {&entry.qkv, &entry.o, &entry.gate_up, &entry.down})
+      most_partial = std::max(most_partial, linear_partial_bytes(*plan));
+    plans.layers.push_back(entry);
+  }
+  plans.head = plan_linear(runner.a_quantized.get(), runner.assistant_weights.token_embedding, rows,
+                           a_hidden, runner.config.vocabulary_size, 1);
+  plans.pre = plan_linear(runner.a_quantized.get(), runner.assistant_weights.pre_projection, rows,
+                          2 * hidden, a_hidden, 0);
+  plans.post = plan_linear(runner.a_quantized.get(), runner.assistant_weights.post_projection, rows,
+                           a_hidden, hidden, 0);
+  most_partial = std::max({most_partial, linear_partial_bytes(plans.pre),
+                           linear_partial_bytes(plans.post)});
+  if (most_partial > runner.split_partials.bytes())
+    throw Failure{"split-K workspace is too small for this assistant shape"};
+  return runner.draft_plans.emplace(rows, std::move(plans)).first->second;
+}
+
+// Runs a linear into bf16 `output`, or leaves split-K partials for a fused consumer. Returns the
+// PartialSource the consumer should read (splits == 0 means "read `output`").
+PartialSource run_linear(Runner &runner, const LinearPlan &plan, const float *input_scale,
+                         const float *weight_scale, void *output, bool consumer_sums) {
+  auto *partials = runner.split_partials.get<float>();
+  if (plan.splits > 1 && consumer_sums) {
+    require_launch(launch_linear_partial(plan, partials, runner.device_error, runner.stream),
+                   "FP8 linear");
+    runner.launches += 1;
+    return PartialSource{partials, plan.splits, input_scale, weight_scale};
+  }
+  require_launch(launch_linear_bf16(plan, input_scale, weight_scale, output, partials,
+                                    runner.device_error, runner.stream),
+                 "FP8 linear");
+  runner.launches += plan.splits > 1 ? 2 : 1;
+  return PartialSource{nullptr, 0, nullptr, nullptr};
+}
+
+struct StepLayout {
+  int *tokens;
+  int *positions;
+  int *slots;
+  int *target_first;
+  int *caps;
+};
+
+StepLayout layout_inputs(int *base, int rows, int batch) {
+  return {base, base + rows, base + rows + batch, base + rows + 2 * batch, base + rows + 3 * batch};
+}
+
+void verify_step(Runner &runner, const int *proposals, int requests, int depth,
+                 const int *target_first, const int *slots, const int *caps, int flags,
+                 bool allow_empty_slot, int *accepted_out, int *next_out) {
+  const auto &config = runner.config;
+  if (proposals == nullptr || requests <= 0 || requests > runner.batch || depth <= 0 ||
+      depth > maximum_depth || requests * depth > maximum_rows || target_first == nullptr ||
+      slots == nullptr || accepted_out == nullptr || next_out == nullptr) {
+    throw Failure{"invalid greedy verification batch"};
+  }
+  std::vector<bool> seen(static_cast<size_t>(runner.batch), false);
+  const int rows = requests * depth;
+  const StepLayout host = layout_inputs(runner.host_inputs.get<int>(), maximum_rows, runner.batch);
+  int longest = 0;
+  for (int request = 0; request < requests; ++request) {
+    const int slot = slots[request];
+    if (slot < 0 || slot >= runner.batch || seen[static_cast<size_t>(slot)])
+      throw Failure{"invalid or repeated speculative slot"};
+    seen[static_cast<size_t>(slot)] = true;
+    const int position = runner.slot_positions[static_cast<size_t>(slot)];
+    if ((position <= 0 && !allow_empty_slot) || position + depth > runner.maximum_context)
+      throw Failure{"speculative slot is empty or lacks context capacity"};
+    for (int token = 0; token < depth; ++token) {
+      const int id = proposals[request * depth + token];
+      if (id < 0 || id >= config.vocabulary_size)
+        throw Failure{"speculative proposal contains an invalid token"};
+      host.tokens[request * depth + token] = id;
+    }
+    host.positions[request] = position;
+    host.slots[request] = slot;
+    host.target_first[request] = target_first[request];
+    host.caps[request] = caps != nullptr ? caps[request] : depth;
+    longest = std::max(longest, position);
+  }
+  StepPlans &plans = verify_plans_for(runner, rows);
+  const StepLayout device =
+      layout_inputs(runner.step_inputs.get<int>(), maximum_rows, runner.batch);
+  cudaStream_t stream = runner.stream;
+  require_cuda(cudaMemcpyAsync(runner.step_inputs.get(), runner.host_inputs.get<int>(),
+                               sizeof(int) * (maximum_rows + 4 * runner.batch),
+                               cudaMemcpyHostToDevice, stream),
+               "copy speculative step inputs");
+  require_cuda(cudaEventRecord(runner.start_event, stream), "record step start");
+  runner.launches = 0;
+
+  const int hidden = config.hidden_size;
+  const float epsilon = config.rms_norm_epsilon;
+  auto *amax = runner.scratch_words.get<unsigned int>();
+  auto *best = reinterpret_cast<unsigned long long *>(amax + runner.amax_words);
+  auto *scales = runner.scales.get<float>();
+  const auto target = [&](int word) {
+    return QuantTarget{runner.quantized.get(), scales + word, amax + word};
+  };
+
+  void *current = runner.hidden_a.get();
+  void *other = runner.hidden_b.get();
+  require_launch(launch_embed_norm_quant(runner.weights.token_embedding, device.tokens,
+                                         config.vocabulary_size, runner.layers[0].weights.input_norm,
+                                         current, target(0), rows, hidden, epsilon, amax,
+                                         runner.amax_words + 2 * maximum_rows, stream),
+                 "embedding and input norm");
+  runner.launches += 1;
+
+  for (int index = 0; index < config.layer_count; ++index) {
+    const LayerState &layer = runner.layers[static_cast<size_t>(index)];
+    const LayerPlans &plan = plans.layers[static_cast<size_t>(index)];
+    const auto &shape = layer.shape;
+    const auto &w = layer.weights;
+    const int word = index * 4;
+    const RopeTable &rope = *runner.rope_tables[static_cast<size_t>(layer.rope)];
+
+    run_linear(runner, plan.qkv, scales + word, w.qkv_scale, runner.packed.get(), false);
+
+    QkvPostArguments post{};
+    post.packed = runner.packed.get();
+    post.query_norm = w.q_norm;
+    post.key_norm = w.k_norm;
+    post.cosine = rope.cosine.get();
+    post.sine = rope.sine.get();
+    post.queries = runner.queries.get();
+    post.positions = device.positions;
+    post.slots = device.slots;
+    post.requests = requests;
+    post.depth = depth;
+    post.query_heads = shape.query_heads;
+    post.kv_heads = shape.kv_heads;
+    post.head_dim = shape.head_dim;
+    post.key_equals_value = shape.key_equals_value;
+    post.max_positions = runner.maximum_context;
+    post.epsilon = epsilon;
+    post.capacity = layer.capacity;
+    if (shape.global_attention) {
+      post.direct = 1;
+      post.key_base = layer.keys();
+      post.value_base = layer.values();
+      post.slot_stride = layer.slot_stride;
+      post.head_stride = layer.head_stride;
+    } else {
+      post.direct = 0;
+      post.key_base = layer.staged_keys();
+      post.value_base = layer.staged_values();
+      post.head_stride = static_cast<long long>(depth) * shape.head_dim;
+      post.slot_stride = post.head_stride * shape.kv_heads;
+    }
+    require_launch(launch_qkv_post(post, stream), "QKV post-processing");
+    runner.launches += 1;
+
+    AttentionArguments attention{};
+    attention.queries = runner.queries.get();
+    attention.key_cache = layer.keys();
+    attention.value_cache = layer.values();
+    attention.slot_stride = layer.slot_stride;
+    attention.head_stride = layer.head_stride;
+    attention.positions = device.positions;
+    attention.slots = device.slots;
+    attention.scores = runner.scores.get();
+    attention.output = runner.attention_out.get();
+    attention.chunk_partials = runner.attention_partials.get<float>();
+    attention.requests = requests;
+    attention.depth = depth;
+    attention.query_heads = shape.query_heads;
+    attention.kv_heads = shape.kv_heads;
+    attention.head_dim = shape.head_dim;
+    attention.capacity = layer.capacity;
+    if (shape.global_attention) {
+      attention.window = 0;
+      attention.max_context_rows = longest;
+      attention.score_stride = runner.score_stride_global;
+      attention.chunk_keys = global_chunk_keys;
+      attention.chunks = attention_chunks(longest, depth, global_chunk_keys);
+    } else {
+      attention.window = config.sliding_window;
+      attention.new_keys = layer.staged_keys();
+      attention.new_values = layer.staged_values();
+      attention.new_request_stride = post.slot_stride;
+      attention.new_head_stride = post.head_stride;
+      attention.max_context_rows = std::min(longest, layer.capacity);
+      attention.score_stride = runner.score_stride_sliding;
+      attention.chunk_keys = runner.score_stride_sliding;
+      attention.chunks = 1;
+    }
+    require_launch(launch_attention_simt(attention, stream), "verify attention");
+    runner.launches += 3;
+
+    require_launch(launch_quant(attention.chunks > 1 ? nullptr : runner.attention_out.get(),
+                                attention.chunks > 1 ? runner.attention_partials.get<float>()
+                                                     : nullptr,
+                                attention.chunks, target(word + 1), rows, layer.query_width(),
+                                stream),
+                   "attention output quantisation");
+    runner.launches += 1;
+
+    const PartialSource o_source = run_linear(runner, plan.o, scales + word + 1, w.o_scale,
+                                              runner.projected.get(), true);
+    require_launch(launch_post_attention_norms_quant(
+                       runner.projected.get(), o_source, w.post_attention_norm, current,
+                       w.pre_mlp_norm, runner.residual.get(), target(word + 2), rows, hidden,
+                       epsilon, stream),
+                   "post-attention norms");
+    runner.launches += 1;
+
+    run_linear(runner, plan.gate_up, scales + word + 2, w.gate_up_scale, runner.gate_up.get(),
+               false);
+    require_launch(launch_geglu_quant(runner.gate_up.get(), target(word + 3), rows,
+                                      config.intermediate_size, stream),
+                   "GeGLU");
+    runner.launches += 1;
+
+    const PartialSource down_source = run_linear(runner, plan.down, scales + word + 3,
+                                                 w.down_scale, runner.projected.get(), true);
+    const bool last = index + 1 == config.layer_count;
+    const void *next_norm = last ? runner.weights.final_norm
+                                 : runner.layers[static_cast<size_t>(index) + 1].weights.input_norm;
+    require_launch(launch_layer_output_norm_quant(
+                       runner.projected.get(), down_source, w.post_mlp_norm, runner.residual.get(),
+                       w.scalar, other, next_norm, last ? runner.final_hidden.get() : nullptr,
+                       target(word + 4), rows, hidden, epsilon, stream),
+                   "layer output");
+    runner.launches += 1;
+    std::swap(current, other);
+  }
+
+  const int head_word = config.layer_count * 4;
+  require_launch(launch_linear_argmax(plans.head, scales + head_word,
+                                      runner.weights.token_embedding_scale, best,
+                                      runner.device_error, stream),
+                 "LM head");
+  runner.launches += 1;
+
+  int *results = runner.step_results.get<int>();
+  AcceptArguments accept{};
+  accept.best = best;
+  accept.proposals = device.tokens;
+  accept.target_first = device.target_first;
+  accept.caps = device.caps;
+  accept.assume_match = (flags & CARAT_B200_VERIFY_ASSUME_MATCH) != 0 ? 1 : 0;
+  accept.accepted = results;
+  accept.next_tokens = results + runner.batch;
+  accept.predictions = results + 2 * runner.batch;
+  accept.final_hidden = runner.final_hidden.get();
+  accept.hidden_by_slot = runner.hidden_by_slot.get();
+  accept.slots = device.slots;
+  accept.slot_positions = runner.device_slot_positions.get<int>();
+  accept.requests = requests;
+  accept.depth = depth;
+  accept.hidden = hidden;
+  require_launch(launch_accept(accept, stream), "greedy prefix accept");
+  runner.launches += 1;
+  if (runner.commit_layer_count > 0) {
+    require_launch(launch_commit(runner.commit_layers.get<CommitLayer>(), runner.commit_layer_count,
+                                 device.positions, accept.accepted, device.slots, requests, depth, 0,
+                                 stream),
+                   "KV commit");
+    runner.launches += 1;
+  }
+  require_cuda(cudaEventRecord(runner.stop_event, stream), "record step end");
+  int *host_results = runner.host_results.get<int>();
+  const int result_words = 2 * runner.batch + maximum_rows;
+  require_cuda(cudaMemcpyAsync(host_results, results, sizeof(int) * result_words,
+                               cudaMemcpyDeviceToHost, stream),
+               "copy speculative results");
+  require_cuda(cudaMemcpyAsync(host_results + result_words, runner.device_error, sizeof(int),
+                               cudaMemcpyDeviceToHost, stream),
+               "copy device error word");
+  require_cuda(cudaStreamSynchronize(stream), "synchronize speculative verification");
+  require_cuda(cudaEventElapsedTime(&runner.last_verify_ms, runner.start_event, runner.stop_event),
+               "read step time");
+  runner.last_verify_launches = runner.launches;
+  runner.last_rows = rows;
+  if (host_results[result_words] != 0) {
+    const int code = host_results[result_words];
+    cudaMemsetAsync(runner.device_error, 0, sizeof(int), stream);
+    throw Failure{"a kernel wait ran out during speculative verification (code " +
+                  std::to_string(code) + ")"};
+  }
+  runner.last_predictions.assign(host_results + 2 * runner.batch,
+                                 host_results + 2 * runner.batch + rows);
+  for (int request = 0; request < requests; ++request) {
+    accepted_out[request] = host_results[request];
+    next_out[request] = host_results[runner.batch + request];
+    runner.slot_positions[static_cast<size_t>(slots[request])] += host_results[request];
+  }
+}
+
+void draft_step(Runner &runner, const int *last_tokens, const int *slots, const int *forced,
+                int requests, int depth, int *proposals_out) {
+  if (!runner.has_assistant || last_tokens == nullptr || slots == nullptr || requests <= 0 ||
+      proposals_out == nullptr) {
+    throw Failure{"assistant is not configured or draft batch is invalid"};
+  }
+  if (requests > runner.batch || depth <= 0 || depth > maximum_depth)
+    throw Failure{"invalid assistant draft batch"};
+  const auto &config = runner.config;
+  const auto &assistant = runner.assistant;
+  int *host = runner.host_inputs.get<int>();
+  int *host_tokens = host;
+  int *host_context = host + runner.batch;
+  int *host_slots = host + 2 * runner.batch;
+  int *host_forced = host + 3 * runner.batch;
+  int longest = 0;
+  for (int row = 0; row < requests; ++row) {
+    const int slot = slots[row];
+    if (slot < 0 || slot >= runner.batch || runner.slot_positions[static_cast<size_t>(slot)] <= 0)
+      throw Failure{"assistant slot is empty or invalid"};
+    if (last_tokens[row] < 0 || last_tokens[row] >= config.vocabulary_size)
+      throw Failure{"invalid assistant row metadata"};
+    host_tokens[row] = last_tokens[row];
+    host_context[row] = runner.slot_positions[static_cast<size_t>(slot)] - 1;
+    host_slots[row] = slot;
+    host_forced[row] = forced != nullptr ? forced[row] : 0;
+    longest = std::max(longest, host_context[row] + 1);
+  }
+  StepPlans &plans = draft_plans_for(runner, requests);
+  cudaStream_t stream = runner.stream;
+  int *device = runner.a_tokens.get<int>();
+  int *device_tokens = device;
+  int *device_context = device + runner.batch;
+  int *device_slots = device + 2 * runner.batch;
+  int *device_forced = device + 3 * runner.batch;
+  require_cuda(cudaMemcpyAsync(device, host, sizeof(int) * 4 * runner.batch,
+                               cudaMemcpyHostToDevice, stream),
+               "copy assistant inputs");
+  require_cuda(cudaEventRecord(runner.start_event, stream), "record draft start");
+  runner.launches = 0;
+
+  const int hidden = config.hidden_size;
+  const int a_hidden = assistant.hidden_size;
+  const float epsilon = assistant.rms_norm_epsilon;
+  auto *amax = runner.a_scratch_words.get<unsigned int>();
+  auto *best = reinterpret_cast<unsigned long long *>(amax + runner.a_amax_words);
+  auto *scales = runner.a_scales.get<float>();
+  const auto target = [&](int word) {
+    return QuantTarget{runner.a_quantized.get(), scales + word, amax + word};
+  };
+  int *draft_tokens = runner.a_proposals.get<int>();  // [depth][requests]
+
+  for (int draft_index = 0; draft_index < depth; ++draft_index) {
+    require_cuda(cudaMemsetAsync(amax, 0, sizeof(int) * (runner.a_amax_words + 2 * runner.batch),
+                                 stream),
+                 "clear assistant scratch");
+    const int *input_tokens =
+        draft_index == 0 ? device_tokens : draft_tokens + (draft_index - 1) * requests;
+    require_launch(launch_embed_concat_quant(
+                       runner.weights.token_embedding, input_tokens, config.vocabulary_size,
+                       draft_index == 0 ? runner.hidden_by_slot.get()
+                                        : runner.a_previous_hidden.get(),
+                       draft_index == 0 ? device_slots : nullptr, target(0), requests, hidden,
+                       stream),
+                   "assistant input");
+    runner.launches += 1;
+    void *current = runner.a_hidden_a.get();
+    void *other = runner.a_hidden_b.get();
+    run_linear(runner, plans.pre, scales + 0, runner.assistant_weights.pre_projection_scale,
+               current, false);
+    require_launch(launch_norm_quant(current, runner.assistant_layers[0].input_norm, nullptr,
+                                     target(1), requests, a_hidden, epsilon, stream),
+                   "assistant input norm");
+    runner.launches += 1;
+    int input_word = 1;
+    for (int index = 0; index < assistant.layer_count; ++index) {
+      const auto &w = runner.assistant_layers[static_cast<size_t>(index)];
+      const LayerPlans &plan = plans.layers[static_cast<size_t>(index)];
+      const LayerState &shared = shared_layer(runner, index);
+      const auto &shape = shared.shape;
+      const int query_width = assistant.query_heads * shape.head_dim;
+      const int word = 2 + 4 * index;
+      const RopeTable &rope = *runner.rope_tables[static_cast<size_t>(shared.rope)];
+      run_linear(runner, plan.qkv, scales + input_word, w.qkv_scale, runner.a_projected.get(),
+                 false);
+      require_launch(launch_query_post(runner.a_projected.get(), w.q_norm, rope.cosine.get(),
+                                       rope.sine.get(), runner.a_queries.get(), device_context,
+                                       draft_index, requests, assistant.query_heads,
+                                       shape.head_dim, runner.maximum_context, epsilon, stream),
+                     "assistant query post-processing");
+      runner.launches += 1;
+      AttentionArguments attention{};
+      attention.queries = runner.a_queries.get();
+      attention.key_cache = shared.keys();
+      attention.value_cache = shared.values();
+      attention.slot_stride = shared.slot_stride;
+      attention.head_stride = shared.head_stride;
+      attention.positions = device_context;
+      attention.slots = device_slots;
+      attention.scores = runner.a_scores.get();
+      attention.output = runner.a_attention_out.get();
+      attention.chunk_partials = runner.a_attention_partials.get<float>();
+      attention.requests = requests;
+      attention.depth = 1;
+      attention.query_heads = assistant.query_heads;
+      attention.kv_heads = shape.kv_heads;
+      attention.head_dim = shape.head_dim;
+      attention.capacity = shared.capacity;
+      attention.window = shape.global_attention ? 0 : config.sliding_window;
+      attention.draft = 1;
+      attention.max_context_rows = std::min(longest, shared.capacity);
+      attention.score_stride = runner.score_stride_global;
+      attention.chunk_keys = global_chunk_keys;
+      attention.chunks = attention_chunks(attention.max_context_rows, 0, global_chunk_keys);
+      require_launch(launch_attention_simt(attention, stream), "assistant attention");
+      runner.launches += 3;
+      require_launch(launch_quant(attention.chunks > 1 ? nullptr : runner.a_attention_out.get(),
+                                  attention.chunks > 1 ? runner.a_attention_partials.get<float>()
+                                                       : nullptr,
+                                  attention.chunks, target(word), requests, query_width, stream),
+                     "assistant attention quantisation");
+      runner.launches += 1;
+      const PartialSource o_source = run_linear(runner, plan.o, scales + word, w.o_scale,
+                                                runner.a_linear_out.get(), true);
+      require_launch(launch_post_attention_norms_quant(
+                         runner.a_linear_out.get(), o_source, w.post_attention_norm, current,
+                         w.pre_mlp_norm, runner.a_residual.get(), target(word + 1), requests,
+                         a_hidden, epsilon, stream),
+                     "assistant post-attention norms");
+      runner.launches += 1;
+      run_linear(runner, plan.gate_up, scales + word + 1, w.gate_up_scale, runner.a_gate_up.get(),
+                 false);
+      require_launch(launch_geglu_quant(runner.a_gate_up.get(), target(word + 2), requests,
+                                        assistant.intermediate_size, stream),
+                     "assistant GeGLU");
+      runner.launches += 1;
+      const PartialSource down_source = run_linear(runner, plan.down, scales + word + 2,
+                                                   w.down_scale, runner.a_linear_out.get(), true);
+      const bool last = index + 1 == assistant.layer_count;
+      const void *next_norm = last ? runner.assistant_weights.final_norm
+                                   : runner.assistant_layers[static_cast<size_t>(index) + 1].input_norm;
+      require_launch(launch_layer_output_norm_quant(
+                         runner.a_linear_out.get(), down_source, w.post_mlp_norm,
+                         runner.a_residual.get(), w.scalar, other, next_norm,
+                         last ? runner.a_final_hidden.get() : nullptr, target(word + 3), requests,
+                         a_hidden, epsilon, stream),
+                     "assistant layer output");
+      runner.launches += 1;
+      input_word = word + 3;
+      std::swap(current, other);
+    }
+    int *step_tokens = draft_tokens + draft_index * requests;
+    if (draft_index == 0 && forced != nullptr) {
+      // The target already produced this token; the drafter's LM head would be dead work
+      // (cuda/assistant_runner.cu:306-312).
+      require_cuda(cudaMemcpyAsync(step_tokens, device_forced, sizeof(int) * requests,
+                                   cudaMemcpyDeviceToDevice, stream),
+                   "select forced assistant first tokens");
+    } else {
+      require_launch(launch_linear_argmax(plans.head, scales + input_word,
+                                          runner.assistant_weights.token_embedding_scale, best,
+                                          runner.device_error, stream),
+                     "assistant LM head");
+      require_launch(launch_unpack_best(best, step_tokens, requests, stream), "assistant argmax");
+      runner.launches += 2;
+    }
+    run_linear(runner, plans.post, scales + input_word,
+               runner.assistant_weights.post_projection_scale, runner.a_previous_hidden.get(),
+               false);
+  }
+  require_cuda(cudaEventRecord(runner.stop_event, stream), "record draft end");
+  int *host_results = runner.host_results.get<int>();
+  require_cuda(cudaMemcpyAsync(host_results, draft_tokens, sizeof(int) * depth * requests,
+                               cudaMemcpyDeviceToHost, stream),
+               "copy assistant proposals");
+  require_cuda(cudaMemcpyAsync(host_results + depth * requests, runner.device_error, sizeof(int),
+                               cudaMemcpyDeviceToHost, stream),
+               "copy device error word");
+  require_cuda(cudaStreamSynchronize(stream), "synchronize assistant draft");
+  require_cuda(cudaEventElapsedTime(&runner.last_draft_ms, runner.start_event, runner.stop_event),
+               "read draft time");
+  runner.last_draft_launches = runner.launches;
+  if (host_results[depth * requests] != 0) {
+    const int code = host_results[depth * requests];
+    cudaMemsetAsync(runner.device_error, 0, sizeof(int), stream);
+    throw Failure{"a kernel wait ran out during assistant drafting (code " + std::to_string(code) +
+                  ")"};
+  }
+  for (int draft_index = 0; draft_index < depth; ++draft_index)
+    for (int row = 0; row < requests; ++row)
+      proposals_out[row * depth + draft_index] = host_results[draft_index * requests + row];
+}
+
+template <typename Body> int guarded(Body &&body) {
+  try {
+    body();
+    return 0;
+  } catch (const Failure &failure) {
+    set_last_error(failure.message);
+    return -1;
+  } catch (const std::exception &error) {
+    set_last_error(error.what());
+    return -2;
+  }
+}
+
+} // namespace
+
+extern "C" int carat_b200_runner_create(const carat_b200_model_config *config,
+                                        const carat_b200_model_weights *weights, int batch,
+                                        int maximum_context,
+                                        const carat_b200_assistant_config *assistant,
+                                        const carat_b200_assistant_weights *assistant_weights,
+                                        carat_b200_runner **runner) {
+  return guarded([&] {
+    if (config == nullptr || weights == nullptr || runner == nullptr)
+      throw Failure{"invalid batch model runner shape"};
+    auto built = std::make_unique<carat_b200_runner>();
+    build_runner(*built, *config, *weights, batch, maximum_context, assistant, assistant_weights);
+    *runner = built.release();
+  });
+}
+
+extern "C" void carat_b200_runner_destroy(carat_b200_runner *runner) { delete runner; }
+
+extern "C" int carat_b200_runner_verify_greedy_proposals(
+    carat_b200_runner *runner, const int *proposals, int requests, int depth,
+    const int *target_first_tokens, const int *slots, const int *maximum_accepted_tokens,
+    int flags, int *accepted_tokens, int *next_tokens) {
+  return guarded([&] {
+    if (runner == nullptr)
+      throw Failure{"invalid greedy verification batch"};
+    verify_step(*runner, proposals, requests, depth, target_first_tokens, slots,
+                maximum_accepted_tokens, flags, false, accepted_tokens, next_tokens);
+  });
+}
+
+extern "C" int carat_b200_runner_draft(carat_b200_runner *runner, const int *last_tokens,
+                                       const int *slots, const int *forced_first_tokens,
+                                       int requests, int depth, int *proposals_out) {
+  return guarded([&] {
+    if (runner == nullptr)
+      throw Failure{"assistant is not configured or draft batch is invalid"};
+    draft_step(*runner, last_tokens, slots, forced_first_tokens, requests, depth, proposals_out);
+  });
+}
+
+extern "C" int carat_b200_runner_prefill_slot_fp8(carat_b200_runner *runner, int slot,
+                                                  const int *tokens, int count, int chunk,
+                                                  int *next_token) {
+  return guarded([&] {
+    if (runner == nullptr || tokens == nullptr || count <= 0 || chunk <= 0 || chunk > 8 ||
+        next_token == nullptr || slot < 0 || slot >= runner->batch) {
+      throw Failure{"invalid slot prefill request"};
+    }
+    for (int start = 0; start < count; start += chunk) {
+      const int part = std::min(chunk, count - start);
+      int accepted = 0;
+      int next = 0;
+      verify_step(*runner, tokens + start, 1, part, tokens + start, &slot, nullptr,
+                  CARAT_B200_VERIFY_ASSUME_MATCH, true, &accepted, &next);
+      *next_token = next;
+    }
+  });
+}
+
+extern "C" int carat_b200_runner_reset_slot(carat_b200_runner *runner, int slot) {
+  return guarded([&] {
+    if (runner == nullptr || slot < 0 || slot >= runner->batch)
+      throw Failure{"invalid slot"};
+    runner->slot_positions[static_cast<size_t>(slot)] = 0;
+    require_cuda(cudaMemsetAsync(runner->device_slot_positions.get<int>() + slot, 0, sizeof(int),
+                                 runner->stream),
+                 "reset slot position");
+    require_cuda(cudaStreamSynchronize(runner->stream), "reset slot");
+  });
+}
+
+extern "C" int carat_b200_runner_seed_empty_cache_for_benchmark(carat_b200_runner *runner,
+                                                                int position) {
+  return guarded([&] {
+    if (runner == nullptr || position < 0 || position >= runner->maximum_context)
+      throw Failure{"invalid benchmark cache position"};
+    for (LayerState &layer : runner->layers)
+      require_cuda(cudaMemsetAsync(layer.kv.get(), 0, layer.kv.bytes(), runner->stream),
+                   "clear KV arena");
+    std::fill(runner->slot_positions.begin(), runner->slot_positions.end(), position);
+    require_cuda(cudaMemcpyAsync(runner->device_slot_positions.get(), runner->slot_positions.data(),
+                                 sizeof(int) * runner->batch, cudaMemcpyHostToDevice,
+                                 runner->stream),
+                 "seed slot positions");
+    require_cuda(cudaStreamSynchronize(runner->stream), "seed benchmark cache");
+  });
+}
+
+extern "C" int carat_b200_runner_batch(const carat_b200_runner *runner) {
+  return runner == nullptr ? 0 : runner->batch;
+}
+
+extern "C" int carat_b200_runner_slot_position(const carat_b200_runner *runner, int slot,
+                                               int *position) {
+  return guarded([&] {
+    if (runner == nullptr || position == nullptr || slot < 0 || slot >= runner->batch)
+      throw Failure{"invalid slot"};
+    *position = runner->slot_positions[static_cast<size_t>(slot)];
+  });
+}
+
+extern "C" int carat_b200_runner_has_assistant(const carat_b200_runner *runner) {
+  return runner != nullptr && runner->has_assistant ? 1 : 0;
+}
+
+extern "C" int carat_b200_runner_last_predictions(carat_b200_runner *runner, int *predictions,
+                                                  int count) {
+  return guarded([&] {
+    if (runner == nullptr || predictions == nullptr || count <= 0 || count > runner->last_rows)
+      throw Failure{"no predictions of that size are available"};
+    std::memcpy(predictions, runner->last_predictions.data(),
+                sizeof(int) * static_cast<size_t>(count));
+  });
+}
+
+extern "C" int carat_b200_runner_device_pointer(carat_b200_runner *runner, int which, int layer,
+                                                void **pointer, size_t *bytes) {
+  return guarded([&] {
+    if (runner == nullptr || pointer == nullptr || bytes == nullptr)
+      throw Failure{"invalid inspection request"};
+    if (which == 0 || which == 1) {
+      if (layer < 0 || layer >= runner->config.layer_count)
+        throw Failure{"invalid layer"};
+      const LayerState &state = runner->layers[static_cast<size_t>(layer)];
+      *pointer = which == 0 ? state.keys() : state.values();
+      *bytes = static_cast<size_t>(runner->batch) * state.slot_stride * 2;
+    } else if (which == 2) {
+      *pointer = runner->hidden_by_slot.get();
+      *bytes = static_cast<size_t>(runner->batch) * runner->config.hidden_size * 2;
+    } else if (which == 3) {
+      *pointer = runner->final_hidden.get();
+      *bytes = static_cast<size_t>(runner->last_rows) * runner->config.hidden_size * 2;
+    } else if (which >= 6 && which <= 12) {
+      const DeviceBuffer *buffers[] = {&runner->packed,   &runner->queries,   &runner->attention_out,
+                                       &runner->residual, &runner->gate_up,   &runner->quantized,
+                                       &runner->scales};
+      *pointer = buffers[which - 6]->get();
+      *bytes = buffers[which - 6]->bytes();
+    } else if (which == 4 && runner->has_assistant) {
+      *pointer = runner->a_final_hidden.get();
+      *bytes = runner->a_final_hidden.bytes();
+    } else if (which == 5 && runner->has_assistant) {
+      *pointer = runner->a_previous_hidden.get();
+      *bytes = runner->a_previous_hidden.bytes();
+    } else {
+      throw Failure{"invalid inspection request"};
+    }
+  });
+}
+
+extern "C" int carat_b200_runner_read(carat_b200_runner *runner, int which, int layer,
+                                      size_t offset, void *destination, size_t bytes) {
+  void *base = nullptr;
+  size_t available = 0;
+  const int status = carat_b200_runner_device_pointer(runner, which, layer, &base, &available);
+  if (status != 0)
+    return status;
+  return guarded([&] {
+    if (destination == nullptr || offset + bytes > available)
+      throw Failure{"inspection read exceeds the runner's buffer"};
+    require_cuda(cudaStreamSynchronize(runner->stream), "drain runner stream");
+    require_cuda(cudaMemcpy(destination, static_cast<unsigned char *>(base) + offset, bytes,
+                            cudaMemcpyDefault),
+                 "read runner buffer");
+  });
+}
+
+extern "C" int carat_b200_runner_last_device_ms(const carat_b200_runner *runner, float *verify_ms,
+                                                float *draft_ms) {
+  if (runner == nullptr)
+    return -1;
+  if (verify_ms != nullptr)
+    *verify_ms = runner->last_verify_ms;
+  if (draft_ms != nullptr)
+    *draft_ms = runner->last_draft_ms;
+  return 0;
+}
+
+extern "C" int carat_b200_runner_last_launches(const carat_b200_runner *runner,
+                                               int *verify_launches, int *draft_launches) {
+  if (runner == nullptr)
+    return -1;
+  if (verify_launches != nullptr)
+    *verify_launches = runner->last_verify_launches;
+  if (draft_launches != nullptr)
+    *draft_launches = runner->last_draft_launches;
+  return 0;
+}

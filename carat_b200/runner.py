@@ -1,0 +1,361 @@
+"""Host-side mirror of the reference's runner interface for the speculative-decoding path.
+
+Class and method names follow include/carat/batch_model_runner.h, include/carat/device_weights.h and
+include/carat/gemma4_config.h of the reference so that callers (and the parity tests) read like the
+reference's own code; every call goes through the C ABI in include/carat_b200.h. PyTorch is used
+here only to own device memory.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from . import capi
+from .capi import CaratError, check, int_array
+
+VERIFY_ASSUME_MATCH = 1
+
+
+# --------------------------------------------------------------------------- configuration
+@dataclass
+class Gemma4LayerConfig:
+    """include/carat/gemma4_config.h:14-26."""
+
+    attention: str  # "sliding" | "global"
+    query_heads: int
+    kv_heads: int
+    head_dimension: int
+    rope_theta: float
+    key_equals_value: bool
+
+    def query_width(self) -> int:
+        return self.query_heads * self.head_dimension
+
+    def kv_width(self) -> int:
+        return self.kv_heads * self.head_dimension
+
+    def packed_width(self) -> int:
+        return self.query_width() + self.kv_width() * (1 if self.key_equals_value else 2)
+
+
+@dataclass
+class Gemma4Config:
+    """include/carat/gemma4_config.h:28-43 (the fields the path reads)."""
+
+    hidden_size: int
+    intermediate_size: int
+    vocabulary_size: int
+    sliding_window: int
+    rms_norm_epsilon: float
+    layers: List[Gemma4LayerConfig] = field(default_factory=list)
+
+    @staticmethod
+    def gemma4_31b() -> "Gemma4Config":
+        """Gemma-4-31B text shapes (reference: src/fp8_linear_benchmark.cu:346-351,
+        cuda/layer_runner.cu:162-176). The layer order is assumed to repeat 5 sliding : 1 global."""
+        layers = []
+        for index in range(60):
+            if index % 6 == 5:
+                layers.append(Gemma4LayerConfig("global", 32, 4, 512, 1e6, True))
+            else:
+                layers.append(Gemma4LayerConfig("sliding", 32, 16, 256, 1e4, False))
+        return Gemma4Config(5376, 21504, 262144, 1024, 1e-6, layers)
+
+    @staticmethod
+    def tiny() -> "Gemma4Config":
+        """The CPU-runnable plumbing case: 3 sliding (window 128) + 1 global layer, hidden 256,
+        4 query / 2 KV heads, head_dim 64, FFN 1024, vocab 4096."""
+        layers = [Gemma4LayerConfig("sliding", 4, 2, 64, 1e4, False) for _ in range(3)]
+        layers.append(Gemma4LayerConfig("global", 4, 2, 64, 1e6, True))
+        return Gemma4Config(256, 1024, 4096, 128, 1e-6, layers)
+
+
+@dataclass
+class Gemma4AssistantConfig:
+    """Drafter shape (reference constants: cuda/assistant_runner.cu:22-27,166-170)."""
+
+    hidden_size: int = 1024
+    intermediate_size: int = 8192
+    query_heads: int = 32
+    layers: List[str] = field(default_factory=lambda: ["sliding", "sliding", "sliding", "global"])
+    rms_norm_epsilon: float = 1e-6
+
+
+# --------------------------------------------------------------------------- weights
+class DeviceWeightArena:
+    """BF16 segments by name (include/carat/device_weights.h DeviceWeightArena::at)."""
+
+    def __init__(self, tensors: Dict[str, torch.Tensor]):
+        self.tensors = {}
+        for name, tensor in tensors.items():
+            if not tensor.is_cuda or tensor.dtype != torch.bfloat16:
+                raise CaratError(f"weight segment {name} must be a CUDA bf16 tensor")
+            self.tensors[name] = tensor.contiguous()
+
+    @staticmethod
+    def from_host(tensors: Dict[str, torch.Tensor], device="cuda") -> "DeviceWeightArena":
+        return DeviceWeightArena({name: value.to(device=device, dtype=torch.bfloat16)
+                                  for name, value in tensors.items()})
+
+    def at(self, name: str) -> torch.Tensor:
+        return self.tensors[name]
+
+    def names(self):
+        return self.tensors.keys()
+
+
+def quantize_tensor_to_fp8(tensor: torch.Tensor):
+    """Tensor-scale e4m3 quantisation on the device through the C ABI; returns (bytes, scale)."""
+    library = capi.library()
+    tensor = tensor.contiguous()
+    output = torch.empty(tensor.shape, dtype=torch.uint8, device=tensor.device)
+    scale = torch.zeros(1, dtype=torch.float32, device=tensor.device)
+    scratch = torch.zeros(1, dtype=torch.int32, device=tensor.device)
+    stream = torch.cuda.current_stream(tensor.device).cuda_stream
+    check(library.carat_b200_quantize_bf16_tensor_to_fp8(
+        tensor.data_ptr(), output.data_ptr(), scale.data_ptr(), scratch.data_ptr(),
+        tensor.numel(), stream))
+    return output, scale
+
+
+class Fp8WeightArena:
+    """e4m3 bytes + one fp32 scale per 2-D segment (include/carat/device_weights.h Fp8WeightArena,
+    cuda/device_weights.cu:200-263)."""
+
+    def __init__(self):
+        self.bytes: Dict[str, torch.Tensor] = {}
+        self.scales: Dict[str, torch.Tensor] = {}
+
+    @staticmethod
+    def quantize(weights: DeviceWeightArena) -> "Fp8WeightArena":
+        arena = Fp8WeightArena()
+        for name in weights.names():
+            tensor = weights.at(name)
+            if tensor.dim() == 2:
+                arena.bytes[name], arena.scales[name] = quantize_tensor_to_fp8(tensor)
+        torch.cuda.synchronize()
+        return arena
+
+    def add(self, name: str, fp8_bytes: torch.Tensor, scale: torch.Tensor) -> None:
+        self.bytes[name] = fp8_bytes
+        self.scales[name] = scale
+
+    def at(self, name: str) -> torch.Tensor:
+        return self.bytes[name]
+
+    def scale(self, name: str) -> torch.Tensor:
+        return self.scales[name]
+
+
+@dataclass
+class GreedyVerificationResult:
+    """include/carat/batch_model_runner.h:10-15."""
+
+    accepted_tokens: List[int]
+    next_tokens: List[int]
+
+
+def _pointer(tensor: Optional[torch.Tensor]):
+    return None if tensor is None else ctypes.c_void_p(tensor.data_ptr())
+
+
+class Gemma4BatchModelRunner:
+    """include/carat/batch_model_runner.h:22-77, the methods on the speculative-decoding path."""
+
+    def __init__(self, config: Gemma4Config, weights: DeviceWeightArena, batch: int,
+                 maximum_context: int, fp8_weights: Optional[Fp8WeightArena] = None,
+                 assistant_weights: Optional[DeviceWeightArena] = None,
+                 assistant_fp8_weights: Optional[Fp8WeightArena] = None,
+                 assistant_config: Optional[Gemma4AssistantConfig] = None):
+        self._library = capi.library()
+        self._handle = ctypes.c_void_p()
+        if fp8_weights is None:
+            raise CaratError("invalid greedy verification batch")  # FP8 weights are required
+        self.config = config
+        self._keep = [weights, fp8_weights, assistant_weights, assistant_fp8_weights]
+        shapes = (capi.LayerShape * len(config.layers))()
+        layer_weights = (capi.LayerWeights * len(config.layers))()
+        for index, layer in enumerate(config.layers):
+            shapes[index] = capi.LayerShape(1 if layer.attention == "global" else 0,
+                                            layer.query_heads, layer.kv_heads,
+                                            layer.head_dimension, layer.rope_theta,
+                                            1 if layer.key_equals_value else 0)
+            layer_weights[index] = self._layer_weights(weights, fp8_weights, f"layer.{index}.",
+                                                       "qkv", True)
+        model_config = capi.ModelConfig(config.hidden_size, config.intermediate_size,
+                                        config.vocabulary_size, config.sliding_window,
+                                        config.rms_norm_epsilon, len(config.layers), shapes)
+        model_weights = capi.ModelWeights(
+            weights.at("token_embedding").data_ptr(), fp8_weights.at("token_embedding").data_ptr(),
+            fp8_weights.scale("token_embedding").data_ptr(), weights.at("final_norm").data_ptr(),
+            layer_weights)
+        assistant_struct = None
+        assistant_weight_struct = None
+        if assistant_weights is not None:
+            if assistant_fp8_weights is None:
+                raise CaratError("assistant FP8 mode requires quantized assistant weights")
+            assistant_config = assistant_config or Gemma4AssistantConfig()
+            kinds = (ctypes.c_int32 * len(assistant_config.layers))(
+                *[1 if kind == "global" else 0 for kind in assistant_config.layers])
+            a_layers = (capi.LayerWeights * len(assistant_config.layers))()
+            for index in range(len(assistant_config.layers)):
+                a_layers[index] = self._layer_weights(assistant_weights, assistant_fp8_weights,
+                                                      f"layer.{index}.", "q", False)
+            assistant_struct = capi.AssistantConfig(
+                assistant_config.hidden_size, assistant_config.intermediate_size,
+                assistant_config.query_heads, len(assistant_config.layers), kinds,
+                assistant_config.rms_norm_epsilon)
+            fp8 = assistant_fp8_weights
+            assistant_weight_struct = capi.AssistantWeights(
+                fp8.at("token_embedding").data_ptr(), fp8.scale("token_embedding").data_ptr(),
+                fp8.at("pre_projection").data_ptr(), fp8.scale("pre_projection").data_ptr(),
+                fp8.at("post_projection").data_ptr(), fp8.scale("post_projection").data_ptr(),
+                assistant_weights.at("final_norm").data_ptr(), a_layers)
+            self._keep += [kinds, a_layers]
+        self._keep += [shapes, layer_weights]
+        check(self._library.carat_b200_runner_create(
+            ctypes.byref(model_config), ctypes.byref(model_weights), batch, maximum_context,
+            ctypes.byref(assistant_struct) if assistant_struct is not None else None,
+            ctypes.byref(assistant_weight_struct) if assistant_weight_struct is not None else None,
+            ctypes.byref(self._handle)))
+
+    @staticmethod
+    def _layer_weights(weights, fp8, prefix, projection, has_key_norm) -> capi.LayerWeights:
+        def bf16(name):
+            return weights.at(prefix + name).data_ptr()
+
+        return capi.LayerWeights(
+            bf16("input_norm"), bf16("q_norm"), bf16("k_norm") if has_key_norm else None,
+            fp8.at(prefix + projection).data_ptr(), fp8.scale(prefix + projection).data_ptr(),
+            fp8.at(prefix + "o").data_ptr(), fp8.scale(prefix + "o").data_ptr(),
+            bf16("post_attention_norm"), bf16("pre_mlp_norm"),
+            fp8.at(prefix + "gate_up").data_ptr(), fp8.scale(prefix + "gate_up").data_ptr(),
+            fp8.at(prefix + "down").data_ptr(), fp8.scale(prefix + "down").data_ptr(),
+            bf16("post_mlp_norm"), bf16("scalar"))
+
+    def close(self) -> None:
+        if self._handle:
+            self._library.carat_b200_runner_destroy(self._handle)
+            self._handle = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # interpreter shutdown
+            pass
+
+    # ---- the speculative-decoding path
+    def verify_greedy_proposals(self, proposals: Sequence[Sequence[int]],
+                                target_first_tokens: Sequence[int], slots: Sequence[int],
+                                maximum_accepted_tokens: Sequence[int] = (),
+                                flags: int = 0) -> GreedyVerificationResult:
+        requests = len(proposals)
+        depth = len(proposals[0]) if requests else 0
+        if requests == 0 or len(target_first_tokens) != requests or len(slots) != requests:
+            raise CaratError("invalid greedy verification batch")
+        if maximum_accepted_tokens and len(maximum_accepted_tokens) != requests:
+            raise CaratError("speculative acceptance caps do not match request count")
+        if any(len(row) != depth for row in proposals):
+            raise CaratError("invalid or repeated speculative slot")
+        flat = int_array([token for row in proposals for token in row])
+        accepted = (ctypes.c_int * requests)()
+        next_tokens = (ctypes.c_int * requests)()
+        caps = int_array(maximum_accepted_tokens) if maximum_accepted_tokens else None
+        check(self._library.carat_b200_runner_verify_greedy_proposals(
+            self._handle, flat, requests, depth, int_array(target_first_tokens), int_array(slots),
+            caps, flags, accepted, next_tokens))
+        return GreedyVerificationResult(list(accepted), list(next_tokens))
+
+    def has_assistant(self) -> bool:
+        return bool(self._library.carat_b200_runner_has_assistant(self._handle))
+
+    def draft_four(self, last_tokens: Sequence[int], slots: Sequence[int],
+                   forced_first_tokens: Sequence[int] = (), depth: int = 4) -> List[List[int]]:
+        requests = len(last_tokens)
+        if requests == 0 or len(slots) != requests:
+            raise CaratError("assistant is not configured or draft batch is invalid")
+        if forced_first_tokens and len(forced_first_tokens) != requests:
+            raise CaratError("forced assistant first tokens do not match draft batch")
+        output = (ctypes.c_int * (requests * max(depth, 1)))()
+        forced = int_array(forced_first_tokens) if forced_first_tokens else None
+        check(self._library.carat_b200_runner_draft(self._handle, int_array(last_tokens),
+                                                    int_array(slots), forced, requests, depth,
+                                                    output))
+        return [list(output[row * depth:(row + 1) * depth]) for row in range(requests)]
+
+    def prefill_slot_fp8(self, slot: int, token_ids: Sequence[int], chunk_tokens: int = 8) -> int:
+        next_token = ctypes.c_int(0)
+        check(self._library.carat_b200_runner_prefill_slot_fp8(
+            self._handle, slot, int_array(token_ids), len(token_ids), chunk_tokens,
+            ctypes.byref(next_token)))
+        return next_token.value
+
+    def reset_slot(self, slot: int) -> None:
+        check(self._library.carat_b200_runner_reset_slot(self._handle, slot))
+
+    def seed_empty_cache_for_benchmark(self, position: int) -> None:
+        check(self._library.carat_b200_runner_seed_empty_cache_for_benchmark(self._handle,
+                                                                             position))
+
+    def batch(self) -> int:
+        return self._library.carat_b200_runner_batch(self._handle)
+
+    def slot_position(self, slot: int) -> int:
+        position = ctypes.c_int(0)
+        check(self._library.carat_b200_runner_slot_position(self._handle, slot,
+                                                            ctypes.byref(position)))
+        return position.value
+
+    # ---- inspection
+    def last_predictions(self, count: int) -> List[int]:
+        output = (ctypes.c_int * count)()
+        check(self._library.carat_b200_runner_last_predictions(self._handle, output, count))
+        return list(output)
+
+    def _device_view(self, which: int, layer: int, shape) -> torch.Tensor:
+        elements = 1
+        for extent in shape:
+            elements *= extent
+        holder = torch.empty(elements, dtype=torch.bfloat16, device="cuda")
+        check(self._library.carat_b200_runner_read(self._handle, which, layer, 0,
+                                                   holder.data_ptr(), elements * 2))
+        return holder.reshape(shape)
+
+    def key_cache(self, layer: int, capacity: int) -> torch.Tensor:
+        shape = self.config.layers[layer]
+        return self._device_view(0, layer, (self.batch(), shape.kv_heads, capacity,
+                                            shape.head_dimension))
+
+    def value_cache(self, layer: int, capacity: int) -> torch.Tensor:
+        shape = self.config.layers[layer]
+        return self._device_view(1, layer, (self.batch(), shape.kv_heads, capacity,
+                                            shape.head_dimension))
+
+    def target_hidden_slots(self) -> torch.Tensor:
+        return self._device_view(2, 0, (self.batch(), self.config.hidden_size))
+
+    def last_final_hidden(self, rows: int) -> torch.Tensor:
+        return self._device_view(3, 0, (rows, self.config.hidden_size))
+
+    def assistant_final_hidden(self, rows: int, width: int) -> torch.Tensor:
+        return self._device_view(4, 0, (rows, width))
+
+    def assistant_previous_hidden(self, rows: int) -> torch.Tensor:
+        return self._device_view(5, 0, (rows, self.config.hidden_size))
+
+    def last_device_ms(self):
+        verify = ctypes.c_float(0)
+        draft = ctypes.c_float(0)
+        check(self._library.carat_b200_runner_last_device_ms(self._handle, ctypes.byref(verify),
+                                                             ctypes.byref(draft)))
+        return verify.value, draft.value
+
+    def last_launches(self):
+        verify = ctypes.c_int(0)
+        draft = ctypes.c_int(0)
+        check(self._library.carat_b200_runner_last_launches(self._handle, ctypes.byref(verify),
+                                                            ctypes.byref(draft)))
+        return verify.value, draft.value

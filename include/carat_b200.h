@@ -17,6 +17,12 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#if defined(__GNUC__)
+#define CARAT_B200_API __attribute__((visibility("default")))
+#else
+#define CARAT_B200_API
+#endif
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -24,15 +30,15 @@ extern "C" {
 /* Library ------------------------------------------------------------------------------------ */
 
 /* Thread-local text of the most recent failure. */
-const char *carat_b200_last_error(void);
+CARAT_B200_API const char *carat_b200_last_error(void);
 
 /* ABI version of this header (bumped on incompatible changes). */
-int carat_b200_abi_version(void);
+CARAT_B200_API int carat_b200_abi_version(void);
 
 /* Kernels that wait on hardware barriers give up after a bounded time and record a code in a
  * per-device word instead of hanging. Synchronises the device, returns the code in *code
  * (0 = healthy) and clears it. */
-int carat_b200_device_error(int *code);
+CARAT_B200_API int carat_b200_device_error(int *code);
 
 /* FP8 linear ---------------------------------------------------------------------------------- */
 
@@ -43,28 +49,309 @@ int carat_b200_device_error(int *code);
  * carat_b200_fp8_linear_workspace_bytes() bytes (may be NULL when that is 0).
  * Replaces carat::Fp8Linear::run with Fp8Scaling::tensor (include/carat/linear.h:32-41,
  * cuda/linear.cu:645-803). */
-int carat_b200_fp8_linear(const void *fp8_input, const float *device_input_scale,
+CARAT_B200_API int carat_b200_fp8_linear(const void *fp8_input, const float *device_input_scale,
                           const void *fp8_weight, const float *device_weight_scale,
                           void *bf16_output, int rows, int input_width, int output_width,
                           void *workspace, size_t workspace_bytes, void *stream);
 
-size_t carat_b200_fp8_linear_workspace_bytes(int rows, int input_width, int output_width);
+CARAT_B200_API size_t carat_b200_fp8_linear_workspace_bytes(int rows, int input_width, int output_width);
 
 /* Fused LM head: device_tokens[row] = argmax_n bf16(scale * input[row] . weight[n]), ties to the
  * lowest n, without writing the logits. `device_keys` is rows * 8 bytes of scratch.
  * Replaces run_decode_lm_head + argmax_bf16_rows (cuda/batch_model_runner.cu:840-853,
  * cuda/ops.cu:935-981, 1566-1579). */
-int carat_b200_fp8_linear_argmax(const void *fp8_input, const float *device_input_scale,
+CARAT_B200_API int carat_b200_fp8_linear_argmax(const void *fp8_input, const float *device_input_scale,
                                  const void *fp8_weight, const float *device_weight_scale,
                                  int *device_tokens, void *device_keys, int rows, int input_width,
                                  int output_width, void *stream);
 
 /* Same contract as carat_b200_fp8_linear computed one output per thread without tensor cores.
  * A device-side cross-check for tests at sizes a CPU cannot finish; no step path calls it. */
-int carat_b200_fp8_linear_check(const void *fp8_input, const float *device_input_scale,
+CARAT_B200_API int carat_b200_fp8_linear_check(const void *fp8_input, const float *device_input_scale,
                                 const void *fp8_weight, const float *device_weight_scale,
                                 void *bf16_output, int rows, int input_width, int output_width,
                                 void *stream);
+
+/* Activation quantisation and fused row operators ----------------------------------------------- */
+
+/* All of these quantise a [rows, width] bf16 tensor to e4m3 with one tensor-wide scale:
+ * *device_scale = amax / 448 (1.0 when amax == 0), value = e4m3(x * (1 / scale)), saturating
+ * (carat::quantize_bf16_to_fp8_e4m3 and its _from_row_amax / _from_amax_values forms,
+ * include/carat/linear.h:93-110, cuda/linear.cu:76-296). rows <= 256, width a multiple of 8 and
+ * at most 32768. `device_scratch` is one 32-bit word the call clears and uses for the running
+ * maximum. Each call is one cooperative launch. */
+
+/* Plain quantisation. */
+CARAT_B200_API int carat_b200_quantize_bf16_to_fp8(const void *bf16_input, void *fp8_output, float *device_scale,
+                                    void *device_scratch, int rows, int width, void *stream);
+
+/* Same contract for a tensor of any size (weights at load time): three ordinary launches, the
+ * reference's non-cooperative branch (cuda/linear.cu:117-153,261-271; used by
+ * Fp8WeightArena::quantize, cuda/device_weights.cu:200-263). */
+CARAT_B200_API int carat_b200_quantize_bf16_tensor_to_fp8(const void *bf16_input, void *fp8_output,
+                                                          float *device_scale,
+                                                          void *device_scratch, size_t elements,
+                                                          void *stream);
+
+/* normalized = bf16(rmsnorm(input) * weight) [stored to bf16_normalized when not NULL], then
+ * quantised. Replaces rms_norm_bf16_with_row_amax + quantize_..._from_row_amax
+ * (include/carat/cuda_ops.h:10-16, cuda/layer_runner.cu:241-262). */
+CARAT_B200_API int carat_b200_rms_norm_quantize(const void *bf16_input, const void *bf16_weight,
+                                 void *bf16_normalized, void *fp8_output, float *device_scale,
+                                 void *device_scratch, int rows, int width, float epsilon,
+                                 void *stream);
+
+/* first = bf16(rmsnorm(input) * weight + residual) -> bf16_first; second = bf16(rmsnorm(first) *
+ * next_weight) -> quantised. Replaces rms_norm_add_and_norm_bf16_with_row_amax + quantiser
+ * (include/carat/cuda_ops.h:19-29, cuda/layer_runner.cu:306-330). */
+CARAT_B200_API int carat_b200_rms_norm_add_and_norm_quantize(const void *bf16_input, const void *bf16_weight,
+                                              const void *bf16_residual,
+                                              const void *bf16_next_weight, void *bf16_first,
+                                              void *fp8_output, float *device_scale,
+                                              void *device_scratch, int rows, int width,
+                                              float epsilon, void *stream);
+
+/* activated = bf16(gelu_tanh(gate) * up) from rows packed [gate | up] (2 * width columns), then
+ * quantised. Replaces gelu_tanh_gate_rows_bf16_with_block_amax + reduce_block_amax_to_rows +
+ * quantiser (include/carat/cuda_ops.h:36-44, cuda/layer_runner.cu:331-347). */
+CARAT_B200_API int carat_b200_gelu_gate_quantize(const void *bf16_packed_gate_up, void *fp8_output,
+                                  float *device_scale, void *device_scratch, int rows, int width,
+                                  void *stream);
+
+/* output = bf16(bf16(rmsnorm(input) * weight + residual) * scalar) -> bf16_output; then
+ * bf16(rmsnorm(output) * next_weight) [-> bf16_next when not NULL] -> quantised: the layer tail
+ * (rms_norm_add_scale_bf16, include/carat/cuda_ops.h:30-32) fused with the norm that follows it. */
+CARAT_B200_API int carat_b200_rms_norm_add_scale_then_norm_quantize(
+    const void *bf16_input, const void *bf16_weight, const void *bf16_residual,
+    const void *bf16_scalar, void *bf16_output, const void *bf16_next_weight, void *bf16_next,
+    void *fp8_output, float *device_scale, void *device_scratch, int rows, int width,
+    float epsilon, void *stream);
+
+/* Attention-side operators ---------------------------------------------------------------------- */
+
+/* bf16 cos/sin tables [positions, head_dim] (cuda/qkv.cu:44-64 rope_cache_kernel): sliding layers
+ * theta^(-2i/D) for every pair; proportional (global) layers only for i < D/8. */
+CARAT_B200_API int carat_b200_rope_tables(void *bf16_cosine, void *bf16_sine, int positions, int head_dim,
+                           float theta, int proportional, void *stream);
+
+/* Q: per-head rmsnorm * weight -> bf16 -> rotate-half RoPE -> bf16, stored
+ * [requests, query_heads, depth, head_dim]. K likewise, V = rmsnorm without weight (from the K
+ * slice when key_equals_value); both stored [requests, kv_heads, depth, head_dim].
+ * packed rows are [Q | K | V] (V absent when key_equals_value). head_dim is 64, 256 or 512.
+ * Replaces Gemma4QkvPostprocessor::run_prefill_uniform (include/carat/qkv.h:40-47,
+ * cuda/qkv.cu:387-475). */
+CARAT_B200_API int carat_b200_qkv_postprocess(const void *bf16_packed, const void *bf16_query_norm,
+                               const void *bf16_key_norm, const void *bf16_cosine,
+                               const void *bf16_sine, void *bf16_queries, void *bf16_keys,
+                               void *bf16_values, const int *device_positions, int requests,
+                               int depth, int query_heads, int kv_heads, int head_dim,
+                               int key_equals_value, int table_positions, float epsilon,
+                               void *stream);
+
+/* Verify attention of `depth` proposal rows per request over that request's cache plus the
+ * proposals. caches: [requests, kv_heads, capacity, head_dim] (logical position p in row
+ * p % capacity); proposals [requests, kv_heads, depth, head_dim]; queries
+ * [requests, query_heads, depth, head_dim]; output [requests * depth, query_heads * head_dim].
+ * window = 0 selects causal attention over a linear cache, otherwise the sliding window.
+ * scores is scratch of requests * query_heads * depth * score_stride bf16 with
+ * score_stride >= min(max position, capacity) + depth, a multiple of 8.
+ * Replaces GemmCausalPrefillAttention::run_uniform_batch / run_uniform_ring_batch
+ * (include/carat/prefill_gemm_attention.h:24-47). */
+CARAT_B200_API int carat_b200_verify_attention(const void *bf16_queries, const void *bf16_key_caches,
+                                const void *bf16_value_caches, const void *bf16_new_keys,
+                                const void *bf16_new_values, const int *device_positions,
+                                void *bf16_output, void *bf16_scores, int score_stride,
+                                int requests, int depth, int query_heads, int kv_heads,
+                                int head_dim, int capacity, int window, int max_position,
+                                void *stream);
+
+/* Rollback primitives with the reference's signatures
+ * (include/carat/cuda_ops.h:124-135, cuda/ops.cu:827-871,1485-1525). */
+CARAT_B200_API int carat_b200_backup_kv_ring_spans(const void *const *device_key_sources,
+                                    const void *const *device_value_sources, void *backup_keys,
+                                    void *backup_values, const int *device_position_starts,
+                                    int requests, int heads, int tokens, int head_dim,
+                                    int source_capacity, void *stream);
+CARAT_B200_API int carat_b200_restore_kv_ring_suffixes(const void *backup_keys, const void *backup_values,
+                                        void *const *device_key_destinations,
+                                        void *const *device_value_destinations,
+                                        const int *device_position_starts,
+                                        const int *device_accepted_tokens, int requests, int heads,
+                                        int tokens, int head_dim, int destination_capacity,
+                                        void *stream);
+
+/* Row argmax over bf16 values, ties to the lowest index
+ * (argmax_bf16_rows, include/carat/cuda_ops.h:149-151, cuda/ops.cu:935-981). */
+CARAT_B200_API int carat_b200_argmax_bf16_rows(const void *bf16_values, int rows, int elements,
+                                int *device_output, void *stream);
+
+/* Greedy prefix-accept on the device (the host loop of cuda/batch_model_runner.cu:1735-1759):
+ * accepted[r] = longest prefix with proposals[r][i] == (i == 0 ? target_first[r] :
+ * predictions[r][i-1]), capped by caps[r] (NULL = depth); next[r] = accepted == 0 ?
+ * target_first[r] : predictions[r][accepted-1]. */
+CARAT_B200_API int carat_b200_greedy_prefix_accept(const int *device_proposals, const int *device_target_first,
+                                    const int *device_predictions, const int *device_caps,
+                                    int requests, int depth, int *device_accepted,
+                                    int *device_next_tokens, void *stream);
+
+/* Runner ------------------------------------------------------------------------------------------ */
+
+/* One decoder layer's attention shape (carat::Gemma4LayerConfig, include/carat/gemma4_config.h:14-26). */
+typedef struct carat_b200_layer_shape {
+  int32_t global_attention; /* 0 = sliding window ring, 1 = global */
+  int32_t query_heads;
+  int32_t kv_heads;
+  int32_t head_dim;         /* 64, 256 or 512 */
+  float rope_theta;
+  int32_t key_equals_value;
+} carat_b200_layer_shape;
+
+/* carat::Gemma4Config (include/carat/gemma4_config.h:28-43), the fields the path reads. */
+typedef struct carat_b200_model_config {
+  int32_t hidden_size;
+  int32_t intermediate_size;
+  int32_t vocabulary_size;
+  int32_t sliding_window;
+  float rms_norm_epsilon;
+  int32_t layer_count;
+  const carat_b200_layer_shape *layers;
+} carat_b200_model_config;
+
+/* Device pointers of one layer's segments, named as in the reference's weight plan
+ * (src/weight_plan.cpp:37-82). Norm weights and the scalar are bf16 (DeviceWeightArena::at);
+ * matrices are e4m3 row-major [out, in] with one fp32 scale (Fp8WeightArena::at / ::scale,
+ * cuda/device_weights.cu:200-263). Every matrix pointer must be 16-byte aligned. */
+typedef struct carat_b200_layer_weights {
+  const void *input_norm;
+  const void *q_norm;
+  const void *k_norm;
+  const void *qkv;
+  const float *qkv_scale;
+  const void *o;
+  const float *o_scale;
+  const void *post_attention_norm;
+  const void *pre_mlp_norm;
+  const void *gate_up;
+  const float *gate_up_scale;
+  const void *down;
+  const float *down_scale;
+  const void *post_mlp_norm;
+  const void *scalar;
+} carat_b200_layer_weights;
+
+typedef struct carat_b200_model_weights {
+  const void *token_embedding;            /* bf16 [vocabulary, hidden] */
+  const void *token_embedding_fp8;        /* e4m3 copy used as the tied LM head */
+  const float *token_embedding_scale;
+  const void *final_norm;
+  const carat_b200_layer_weights *layers; /* layer_count entries */
+} carat_b200_model_weights;
+
+/* Drafter shape. The reference hard-codes hidden 1024, intermediate 8192, 32 query heads and four
+ * layers of which the last is global (cuda/assistant_runner.cu:22-27,166-170); here they are
+ * parameters. Layer i attends the target's last layer of the kind layer_global[i] selects. */
+typedef struct carat_b200_assistant_config {
+  int32_t hidden_size;
+  int32_t intermediate_size;
+  int32_t query_heads;
+  int32_t layer_count;
+  const int32_t *layer_global; /* layer_count entries, 0 = sliding, 1 = global */
+  float rms_norm_epsilon;
+} carat_b200_assistant_config;
+
+/* Drafter segments (src/weight_plan.cpp:84-128); all matrices e4m3 + scale (the reference's
+ * CARAT_ASSISTANT_FP8_MODE=all, cuda/assistant_runner.cu:147-160). `qkv` holds the `q` segment;
+ * k_norm is unused. */
+typedef struct carat_b200_assistant_weights {
+  const void *token_embedding;   /* e4m3 [vocabulary, hidden]: the drafter's LM head */
+  const float *token_embedding_scale;
+  const void *pre_projection;    /* e4m3 [hidden, 2 * target hidden] */
+  const float *pre_projection_scale;
+  const void *post_projection;   /* e4m3 [target hidden, hidden] */
+  const float *post_projection_scale;
+  const void *final_norm;
+  const carat_b200_layer_weights *layers;
+} carat_b200_assistant_weights;
+
+typedef struct carat_b200_runner carat_b200_runner;
+
+/* Builds a runner with `batch` request slots of `maximum_context` tokens on the current device:
+ * KV arenas (zero-filled, per layer K then V, each [slot][kv_head][capacity][head_dim] bf16 with
+ * capacity = min(maximum_context, sliding_window) for sliding layers), proposal staging,
+ * workspaces and RoPE tables. Weights are borrowed and must outlive the runner. assistant and
+ * assistant_weights may both be NULL. Replaces the Gemma4BatchModelRunner constructor
+ * (include/carat/batch_model_runner.h:24-28, cuda/batch_model_runner.cu:255-606). */
+CARAT_B200_API int carat_b200_runner_create(const carat_b200_model_config *config,
+                             const carat_b200_model_weights *weights, int batch,
+                             int maximum_context, const carat_b200_assistant_config *assistant,
+                             const carat_b200_assistant_weights *assistant_weights,
+                             carat_b200_runner **runner);
+CARAT_B200_API void carat_b200_runner_destroy(carat_b200_runner *runner);
+
+enum {
+  /* Throughput runs only: every proposal counts as matching, so maximum_accepted alone sets the
+   * accepted length (used to inject accept lengths with random-init weights). */
+  CARAT_B200_VERIFY_ASSUME_MATCH = 1
+};
+
+/* proposals is [requests][depth] row-major. Writes accepted_tokens[requests] and
+ * next_tokens[requests]; advances each slot by its accepted count; rejected sliding-ring rows are
+ * left exactly as they were; returns after the results are on the host. Error texts match the
+ * reference's exceptions. Replaces Gemma4BatchModelRunner::verify_greedy_proposals
+ * (include/carat/batch_model_runner.h:55-60, cuda/batch_model_runner.cu:1617-1810). */
+CARAT_B200_API int carat_b200_runner_verify_greedy_proposals(carat_b200_runner *runner, const int *proposals,
+                                              int requests, int depth,
+                                              const int *target_first_tokens, const int *slots,
+                                              const int *maximum_accepted_tokens, int flags,
+                                              int *accepted_tokens, int *next_tokens);
+
+/* proposals_out is [requests][depth]. forced_first_tokens may be NULL. Replaces
+ * Gemma4BatchModelRunner::draft_four and Gemma4AssistantRunner::draft_four
+ * (include/carat/batch_model_runner.h:62-65, include/carat/assistant_runner.h:20-26,
+ * cuda/assistant_runner.cu:218-338). */
+CARAT_B200_API int carat_b200_runner_draft(carat_b200_runner *runner, const int *last_tokens, const int *slots,
+                            const int *forced_first_tokens, int requests, int depth,
+                            int *proposals_out);
+
+/* Makes `count` tokens resident in an empty or partly filled slot by running them through the FP8
+ * verify forward `chunk` (<= 8) rows at a time with every row accepted, and returns the greedy
+ * next token. An interim stand-in for prefill_slot_chunk (include/carat/batch_model_runner.h:38-41):
+ * the reference prefills in BF16 (cuda/batch_model_runner.cu:1274-1275). */
+CARAT_B200_API int carat_b200_runner_prefill_slot_fp8(carat_b200_runner *runner, int slot, const int *tokens,
+                                       int count, int chunk, int *next_token);
+
+/* include/carat/batch_model_runner.h:66-72 */
+CARAT_B200_API int carat_b200_runner_reset_slot(carat_b200_runner *runner, int slot);
+CARAT_B200_API int carat_b200_runner_seed_empty_cache_for_benchmark(carat_b200_runner *runner, int position);
+CARAT_B200_API int carat_b200_runner_batch(const carat_b200_runner *runner);
+CARAT_B200_API int carat_b200_runner_slot_position(const carat_b200_runner *runner, int slot, int *position);
+CARAT_B200_API int carat_b200_runner_has_assistant(const carat_b200_runner *runner);
+
+/* Inspection (tests and tools). */
+
+/* Target argmax of every row of the last verify call, [requests * depth]. */
+CARAT_B200_API int carat_b200_runner_last_predictions(carat_b200_runner *runner, int *predictions, int count);
+/* Device pointers owned by the runner: which = 0 key cache of `layer`, 1 value cache of `layer`
+ * ([slot][kv_head][capacity][head_dim] bf16), 2 hidden-by-slot table [batch, hidden] bf16,
+ * 3 final-normed hidden rows of the last verify call [requests * depth, hidden] bf16,
+ * 4 the drafter's final-normed hidden rows of its last draft step [requests, drafter hidden],
+ * 5 the drafter's carried hidden rows after its last draft step [requests, hidden],
+ * 6-12 the last layer's workspaces as the last verify call left them: packed QKV projection,
+ * queries, attention output, post-attention residual, gate|up projection, the e4m3 activation
+ * buffer, and the fp32 activation scales (four per layer). */
+CARAT_B200_API int carat_b200_runner_device_pointer(carat_b200_runner *runner, int which, int layer,
+                                     void **pointer, size_t *bytes);
+/* Copies `bytes` bytes starting `offset` bytes into one of those buffers to `destination` (host or
+ * device memory) after the runner's stream has drained. */
+CARAT_B200_API int carat_b200_runner_read(carat_b200_runner *runner, int which, int layer,
+                                          size_t offset, void *destination, size_t bytes);
+/* Device time of the last verify / draft call in milliseconds (CUDA events on the runner's
+ * stream, kernels only). */
+CARAT_B200_API int carat_b200_runner_last_device_ms(const carat_b200_runner *runner, float *verify_ms,
+                                     float *draft_ms);
+/* Kernel launches issued by the last verify / draft call. */
+CARAT_B200_API int carat_b200_runner_last_launches(const carat_b200_runner *runner, int *verify_launches,
+                                    int *draft_launches);
 
 #ifdef __cplusplus
 }

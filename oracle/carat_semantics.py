@@ -524,7 +524,7 @@ class OracleRunner:
 
     # ---- drafter (cuda/assistant_runner.cu:162-338, cuda/batch_model_runner.cu:1812-1836)
     def draft(self, last_tokens: Sequence[int], slots: Sequence[int],
-              forced_first_tokens: Sequence[int] = (), depth: int = 4) -> List[List[int]]:
+              forced_first_tokens: Sequence[int] = (), depth: int = 4, trace: bool = False):
         if self.assistant is None or len(last_tokens) != len(slots) or not last_tokens:
             raise RuntimeError("assistant is not configured or draft batch is invalid")
         if forced_first_tokens and len(forced_first_tokens) != len(last_tokens):
@@ -539,6 +539,7 @@ class OracleRunner:
         previous_hidden = self.target_hidden[list(slots)].clone()
         tokens = torch.tensor(list(last_tokens), dtype=torch.int64)
         proposals = [[0] * depth for _ in range(active)]
+        traces = []
 
         def linear(x, name):
             return self._linear(x, name, w, self.assistant_fp8_weights, self.assistant_fp8)
@@ -577,13 +578,20 @@ class OracleRunner:
                                        self.assistant_fp8_weights, self.assistant_fp8,
                                        assistant.intermediate, assistant.eps)
             final_hidden = rms_norm(hidden, w["final_norm"], assistant.eps)
+            margin = None
             if draft_index == 0 and forced_first_tokens:
                 tokens = torch.tensor(list(forced_first_tokens), dtype=torch.int64)
             else:
-                tokens = argmax_lowest_index(linear(final_hidden, "token_embedding")).long()
+                logits = linear(final_hidden, "token_embedding")
+                tokens = argmax_lowest_index(logits).long()
+                top2 = torch.topk(logits, 2, dim=-1).values
+                margin = top2[:, 0] - top2[:, 1]
             previous_hidden = linear(final_hidden, "post_projection")
+            traces.append((final_hidden, previous_hidden, margin))
             for row in range(active):
                 proposals[row][draft_index] = int(tokens[row])
+        if trace:
+            return proposals, traces
         return proposals
 
     def prefill_slot_fp8(self, slot: int, tokens: Sequence[int], chunk: int = 8) -> int:
