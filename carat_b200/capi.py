@@ -95,6 +95,7 @@ SIGNATURES = {
     "carat_b200_runner_prefill_slot_fp8": (_I, [_P, _I, _IP, _I, _I, _IP]),
     "carat_b200_runner_reset_slot": (_I, [_P, _I]),
     "carat_b200_runner_seed_empty_cache_for_benchmark": (_I, [_P, _I]),
+    "carat_b200_runner_seed_slot_positions": (_I, [_P, _IP]),
     "carat_b200_runner_batch": (_I, [_P]),
     "carat_b200_runner_slot_position": (_I, [_P, _I, _IP]),
     "carat_b200_runner_has_assistant": (_I, [_P]),

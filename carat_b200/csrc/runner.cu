@@ -1044,6 +1044,27 @@ extern "C" int carat_b200_runner_seed_empty_cache_for_benchmark(carat_b200_runne
   });
 }
 
+extern "C" int carat_b200_runner_seed_slot_positions(carat_b200_runner *runner,
+                                                     const int *positions) {
+  return guarded([&] {
+    if (runner == nullptr || positions == nullptr)
+      throw Failure{"invalid benchmark cache position"};
+    for (int slot = 0; slot < runner->batch; ++slot) {
+      if (positions[slot] < 0 || positions[slot] >= runner->maximum_context)
+        throw Failure{"invalid benchmark cache position"};
+    }
+    for (LayerState &layer : runner->layers)
+      require_cuda(cudaMemsetAsync(layer.kv.get(), 0, layer.kv.bytes(), runner->stream),
+                   "clear KV arena");
+    runner->slot_positions.assign(positions, positions + runner->batch);
+    require_cuda(cudaMemcpyAsync(runner->device_slot_positions.get(), runner->slot_positions.data(),
+                                 sizeof(int) * runner->batch, cudaMemcpyHostToDevice,
+                                 runner->stream),
+                 "seed slot positions");
+    require_cuda(cudaStreamSynchronize(runner->stream), "seed benchmark cache");
+  });
+}
+
 extern "C" int carat_b200_runner_batch(const carat_b200_runner *runner) {
   return runner == nullptr ? 0 : runner->batch;
 }

@@ -300,6 +300,13 @@ class Gemma4BatchModelRunner:
         check(self._library.carat_b200_runner_seed_empty_cache_for_benchmark(self._handle,
                                                                              position))
 
+    def seed_slot_positions(self, positions: Sequence[int]) -> None:
+        """Benchmark helper: zero KV and one context length per slot."""
+        if len(positions) != self.batch():
+            raise CaratError("invalid benchmark cache position")
+        check(self._library.carat_b200_runner_seed_slot_positions(self._handle,
+                                                                  int_array(positions)))
+
     def batch(self) -> int:
         return self._library.carat_b200_runner_batch(self._handle)
 

@@ -323,6 +323,11 @@ CARAT_B200_API int carat_b200_runner_prefill_slot_fp8(carat_b200_runner *runner,
 /* include/carat/batch_model_runner.h:66-72 */
 CARAT_B200_API int carat_b200_runner_reset_slot(carat_b200_runner *runner, int slot);
 CARAT_B200_API int carat_b200_runner_seed_empty_cache_for_benchmark(carat_b200_runner *runner, int position);
+/* Benchmark helper with no counterpart in the reference: like
+ * seed_empty_cache_for_benchmark but with one position per slot (`positions` has batch entries),
+ * so a synthetic request mix with ragged context lengths can be timed without a prefill. */
+CARAT_B200_API int carat_b200_runner_seed_slot_positions(carat_b200_runner *runner,
+                                                         const int *positions);
 CARAT_B200_API int carat_b200_runner_batch(const carat_b200_runner *runner);
 CARAT_B200_API int carat_b200_runner_slot_position(const carat_b200_runner *runner, int slot, int *position);
 CARAT_B200_API int carat_b200_runner_has_assistant(const carat_b200_runner *runner);
