@@ -66,6 +66,7 @@ SIGNATURES = {
     "carat_b200_device_error": (_I, [_IP]),
     "carat_b200_fp8_linear": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P, c_size_t, _P]),
     "carat_b200_fp8_linear_workspace_bytes": (c_size_t, [_I, _I, _I]),
+    "carat_b200_fp8_linear_static": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "carat_b200_fp8_linear_argmax": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "carat_b200_fp8_linear_check": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "carat_b200_quantize_bf16_to_fp8": (_I, [_P, _P, _P, _P, _I, _I, _P]),
@@ -105,6 +106,8 @@ SIGNATURES = {
     "carat_b200_runner_last_device_ms": (_I, [_P, POINTER(c_float), POINTER(c_float)]),
     "carat_b200_runner_last_launches": (_I, [_P, _IP, _IP]),
 }
+
+STATIC_SCRATCH_BYTES = 8 * 1024 * 1024  # CARAT_B200_STATIC_SCRATCH_BYTES
 
 _library = None
 

@@ -56,6 +56,27 @@ CARAT_B200_API int carat_b200_fp8_linear(const void *fp8_input, const float *dev
 
 CARAT_B200_API size_t carat_b200_fp8_linear_workspace_bytes(int rows, int input_width, int output_width);
 
+/* The same linear for callers that cannot allocate device memory (inside a stream capture, in a
+ * serving loop whose allocator is frozen, or in a plugin with a fixed memory budget): the
+ * split-K partial sums live in an 8 MiB array built into the library image, so no workspace is
+ * passed and the call makes no cudaMalloc / cudaFree or other allocating call. This entry point
+ * has no counterpart in the reference.
+ *  - Shapes whose partial sums need more than CARAT_B200_STATIC_SCRATCH_BYTES
+ *    (splits * rows * output_width * 4, as carat_b200_fp8_linear_workspace_bytes reports) are
+ *    rejected with an error; use carat_b200_fp8_linear for those.
+ *  - The first call on each device looks the array's device address up; make that first call
+ *    outside any stream capture.
+ *  - All calls on a device share the one array: calls that overlap on the GPU (different streams,
+ *    no dependency) race on it. Nothing in it has to be zero between calls; every launch
+ *    overwrites the part it reads. Every GPU that loads the library holds the array until exit. */
+#define CARAT_B200_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u)
+CARAT_B200_API int carat_b200_fp8_linear_static(const void *fp8_input,
+                                                const float *device_input_scale,
+                                                const void *fp8_weight,
+                                                const float *device_weight_scale,
+                                                void *bf16_output, int rows, int input_width,
+                                                int output_width, void *stream);
+
 /* Fused LM head: device_tokens[row] = argmax_n bf16(scale * input[row] . weight[n]), ties to the
  * lowest n, without writing the logits. `device_keys` is rows * 8 bytes of scratch.
  * Replaces run_decode_lm_head + argmax_bf16_rows (cuda/batch_model_runner.cu:840-853,
