@@ -82,6 +82,8 @@ SIGNATURES = {
                                        _I, _F, _P]),
     "carat_b200_verify_attention": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
                                         _I, _I, _P]),
+    "carat_b200_verify_attention_check": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
+                                              _I, _I, _I, _I, _P]),
     "carat_b200_backup_kv_ring_spans": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "carat_b200_restore_kv_ring_suffixes": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "carat_b200_argmax_bf16_rows": (_I, [_P, _I, _I, _P, _P]),

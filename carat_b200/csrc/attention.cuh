@@ -7,12 +7,11 @@
 // The computation therefore runs in three phases over a bf16 score buffer, like the reference's
 // QK GEMM -> softmax -> PV GEMM, and each K and V row is streamed from HBM exactly once.
 //
-// Key columns of a request: [0, context) are cache rows 0 .. context-1 in physical order, where
-// context = min(position, capacity) for a sliding ring and = position for a global cache;
-// [context, context + depth) are the proposal rows. A sliding ring is read in place: physical row
-// r holds the newest logical position p <= position-1 with p % capacity == r, and query t (at
-// logical position position + t) sees it iff p >= position + t - (window - 1). Proposal u is
-// visible to query t iff u <= t.
+// The score buffer's column layout (proposals in columns 0..15, cache rows from column 16 on) is
+// described in attention_geometry.cuh. A sliding ring is read in place: physical row r holds the
+// newest logical position p <= position-1 with p % capacity == r, and query t (at logical
+// position position + t) sees it iff p >= position + t - (window - 1). Proposal u is visible to
+// query t iff u <= t.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -35,11 +34,12 @@ struct AttentionArguments {
   const int *positions;      // [requests] logical position of proposal 0
   const int *slots;          // [requests]
   void *scores;              // scratch [requests, query_heads, depth, score_stride] bf16
-  int score_stride;          // >= max context + depth, multiple of 8
+  int score_stride;          // >= score_columns(max_cache_rows), multiple of 8
   void *output;              // [requests * depth, query_heads * head_dim] bf16 (single chunk)
   float *chunk_partials;     // [chunks, requests * depth, query_heads * head_dim] fp32 (chunks > 1)
-  int chunks;                // key chunks the P.V phase is split into (1 = write bf16 output)
-  int chunk_keys;            // keys per chunk (multiple of 64)
+  int chunks;                // cache-row chunks the P.V phase is split into (1 = write bf16
+                             // output); the proposal columns belong to chunk 0
+  int chunk_keys;            // cache rows per chunk (multiple of 128)
   int requests;
   int depth;
   int query_heads;
@@ -47,7 +47,10 @@ struct AttentionArguments {
   int head_dim;              // 64, 256 or 512
   int capacity;              // rows per (slot, head) in the cache
   int window;                // sliding window, 0 = causal over the whole cache
-  int max_context_rows;      // upper bound of `context` over the requests (sizes the grid)
+  int max_cache_rows;        // upper bound over the requests of the cache rows that take part
+                             // (see attention_geometry.cuh); sizes the grids
+  // Tensor maps for the tensor-core kernels (null: the CUDA-core kernels run).
+  const struct AttentionMaps *maps;
   int draft;                 // 1: drafter semantics (depth == 1, no proposal rows, the first
                              //    min(position + 1, capacity) cache rows are visible)
 };
@@ -56,9 +59,20 @@ struct AttentionArguments {
 // cross-check for the tensor-core kernels.
 int launch_attention_simt(const AttentionArguments &arguments, cudaStream_t stream);
 
-// Number of key chunks needed for `max_context_rows` (+ depth proposals) at `chunk_keys` per chunk.
-inline int attention_chunks(int max_context_rows, int depth, int chunk_keys) {
-  return (max_context_rows + depth + chunk_keys - 1) / chunk_keys;
+// Tensor-core implementation (tcgen05 + TMA): head_dim 256 or 512, capacity a multiple of 128,
+// arguments.maps set. Same phases, same rounding points.
+int launch_attention_tc(const AttentionArguments &arguments, cudaStream_t stream);
+
+// Argument checks shared by both implementations (0 = fine).
+int validate_attention(const AttentionArguments &arguments);
+
+// Shared phase 2 (in-place softmax over the score buffer).
+int launch_attention_softmax(const AttentionArguments &arguments, cudaStream_t stream);
+
+// Number of cache-row chunks needed for `max_cache_rows` at `chunk_keys` rows per chunk.
+inline int attention_chunks(int max_cache_rows, int chunk_keys) {
+  const int chunks = (max_cache_rows + chunk_keys - 1) / chunk_keys;
+  return chunks < 1 ? 1 : chunks;
 }
 
 } // namespace carat_b200

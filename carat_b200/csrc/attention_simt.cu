@@ -1,4 +1,5 @@
 #include "attention.cuh"
+#include "attention_geometry.cuh"
 
 #include <cuda_bf16.h>
 #include <math_constants.h>
@@ -6,44 +7,25 @@
 namespace carat_b200 {
 namespace {
 
-struct KeyGeometry {
-  int context;  // cache rows [0, context) take part
-  int keys;     // context + proposal rows
-};
-
-__device__ __forceinline__ KeyGeometry geometry(const AttentionArguments &a, int request) {
-  const int position = a.positions[request];
-  KeyGeometry g;
-  if (a.draft) {
-    g.context = min(position + 1, a.capacity);
-    g.keys = g.context;
-  } else {
-    g.context = a.window > 0 ? min(position, a.capacity) : position;
-    g.keys = g.context + a.depth;
-  }
-  return g;
-}
-
-// Pointer to key/value row `column` of (request, kv_head).
+// Pointer to the key/value row behind score column `column` of (request, kv_head).
 __device__ __forceinline__ const __nv_bfloat16 *row_pointer(const AttentionArguments &a,
                                                             const void *cache, const void *fresh,
-                                                            int request, int kv_head, int column,
-                                                            int context) {
-  const int slot = a.slots[request];
-  const auto *cache_rows = static_cast<const __nv_bfloat16 *>(cache) + slot * a.slot_stride +
-                           kv_head * a.head_stride;
-  if (column < context)
-    return cache_rows + static_cast<size_t>(column) * a.head_dim;
-  const int proposal = column - context;
-  if (fresh == nullptr) {
-    // Global layers: proposals were written straight into the cache at position + t.
-    return cache_rows + static_cast<size_t>(a.positions[request] + proposal) * a.head_dim;
+                                                            int request, int kv_head, int column) {
+  if (column < proposal_columns) {
+    return static_cast<const __nv_bfloat16 *>(fresh) + request * a.new_request_stride +
+           kv_head * a.new_head_stride + static_cast<size_t>(column) * a.head_dim;
   }
-  return static_cast<const __nv_bfloat16 *>(fresh) + request * a.new_request_stride +
-         kv_head * a.new_head_stride + static_cast<size_t>(proposal) * a.head_dim;
+  const int slot = a.slots[request];
+  return static_cast<const __nv_bfloat16 *>(cache) + slot * a.slot_stride +
+         kv_head * a.head_stride + static_cast<size_t>(column - proposal_columns) * a.head_dim;
 }
 
-// Phase 1: scores[row, key] = bf16(q_row . k_key). One thread per key, queries in shared memory.
+__device__ __forceinline__ bool column_has_row(const KeyGeometry &g, int column) {
+  return column < proposal_columns ? column < g.proposals : column - proposal_columns < g.cache_rows;
+}
+
+// Phase 1: scores[row, column] = bf16(q_row . k_column). One thread per column, queries in
+// shared memory.
 template <int dimension>
 __global__ void __launch_bounds__(128) scores_kernel(AttentionArguments a) {
   extern __shared__ __align__(16) unsigned char shared_raw[];
@@ -52,9 +34,9 @@ __global__ void __launch_bounds__(128) scores_kernel(AttentionArguments a) {
   const int kv_head = static_cast<int>(blockIdx.y);
   const int group = a.query_heads / a.kv_heads;
   const int rows = group * a.depth;
-  const KeyGeometry g = geometry(a, request);
-  const int first_key = static_cast<int>(blockIdx.x) * 128;
-  if (first_key >= g.keys)
+  const KeyGeometry g = key_geometry(a, request);
+  const int first_column = static_cast<int>(blockIdx.x) * 128;
+  if (first_column >= g.columns())
     return;
   const auto *query_rows = static_cast<const __nv_bfloat16 *>(a.queries) +
                            (static_cast<size_t>(request) * a.query_heads + kv_head * group) *
@@ -63,11 +45,10 @@ __global__ void __launch_bounds__(128) scores_kernel(AttentionArguments a) {
     *reinterpret_cast<uint4 *>(shared_queries + index) =
         *reinterpret_cast<const uint4 *>(query_rows + index);
   __syncthreads();
-  const int key = first_key + static_cast<int>(threadIdx.x);
-  if (key >= g.keys)
+  const int column = first_column + static_cast<int>(threadIdx.x);
+  if (column >= g.columns() || !column_has_row(g, column))
     return;
-  const __nv_bfloat16 *key_row =
-      row_pointer(a, a.key_cache, a.new_keys, request, kv_head, key, g.context);
+  const __nv_bfloat16 *key_row = row_pointer(a, a.key_cache, a.new_keys, request, kv_head, column);
   auto *score_rows = static_cast<__nv_bfloat16 *>(a.scores) +
                      (static_cast<size_t>(request) * a.query_heads + kv_head * group) * a.depth *
                          a.score_stride;
@@ -101,24 +82,10 @@ __global__ void __launch_bounds__(128) scores_kernel(AttentionArguments a) {
 #pragma unroll
     for (int row = 0; row < 8; ++row) {
       if (row_base + row < rows)
-        score_rows[static_cast<size_t>(row_base + row) * a.score_stride + key] =
+        score_rows[static_cast<size_t>(row_base + row) * a.score_stride + column] =
             __float2bfloat16_rn(sums[row]);
     }
   }
-}
-
-__device__ __forceinline__ bool key_visible(const AttentionArguments &a, int position, int token,
-                                            int column, int context) {
-  if (a.draft)
-    return true;
-  if (column >= context)
-    return column - context <= token;
-  if (a.window <= 0)
-    return true;
-  // Physical ring row -> the logical position it currently holds.
-  const int newest = position - 1;
-  const int held = newest - ((newest - column) % a.capacity);
-  return held >= position + token - (a.window - 1);
 }
 
 // Phase 2: in-place softmax of one score row; masked and padding columns become exact zeros.
@@ -127,16 +94,17 @@ __global__ void __launch_bounds__(128) softmax_kernel(AttentionArguments a) {
   const int row_index = static_cast<int>(blockIdx.x);
   const int token = row_index % a.depth;
   const int request = row_index / (a.depth * a.query_heads);
-  const KeyGeometry g = geometry(a, request);
+  const KeyGeometry g = key_geometry(a, request);
   const int position = a.positions[request];
   auto *row = static_cast<__nv_bfloat16 *>(a.scores) + static_cast<size_t>(row_index) * a.score_stride;
   const int lane = static_cast<int>(threadIdx.x) & 31;
   const int warp = static_cast<int>(threadIdx.x) >> 5;
+  const int columns = g.columns();
 
   float maximum = -CUDART_INF_F;
-  for (int key = static_cast<int>(threadIdx.x); key < g.keys; key += 128) {
-    if (key_visible(a, position, token, key, g.context))
-      maximum = fmaxf(maximum, __bfloat162float(row[key]));
+  for (int column = static_cast<int>(threadIdx.x); column < columns; column += 128) {
+    if (column_visible(a, g, position, token, column))
+      maximum = fmaxf(maximum, __bfloat162float(row[column]));
   }
   for (int offset = 16; offset > 0; offset >>= 1)
     maximum = fmaxf(maximum, __shfl_xor_sync(0xFFFFFFFFU, maximum, offset));
@@ -147,9 +115,9 @@ __global__ void __launch_bounds__(128) softmax_kernel(AttentionArguments a) {
   __syncthreads();
 
   float sum = 0.0F;
-  for (int key = static_cast<int>(threadIdx.x); key < g.keys; key += 128) {
-    if (key_visible(a, position, token, key, g.context))
-      sum += expf(__bfloat162float(row[key]) - maximum);
+  for (int column = static_cast<int>(threadIdx.x); column < columns; column += 128) {
+    if (column_visible(a, g, position, token, column))
+      sum += expf(__bfloat162float(row[column]) - maximum);
   }
   for (int offset = 16; offset > 0; offset >>= 1)
     sum += __shfl_xor_sync(0xFFFFFFFFU, sum, offset);
@@ -158,17 +126,19 @@ __global__ void __launch_bounds__(128) softmax_kernel(AttentionArguments a) {
   __syncthreads();
   const float inverse_sum = 1.0F / (scratch[0] + scratch[1] + scratch[2] + scratch[3]);
 
-  const int padded = min(a.score_stride, (g.keys + 63) / 64 * 64);
-  for (int key = static_cast<int>(threadIdx.x); key < padded; key += 128) {
-    const bool visible = key < g.keys && key_visible(a, position, token, key, g.context);
-    row[key] = visible
-                   ? __float2bfloat16_rn(expf(__bfloat162float(row[key]) - maximum) * inverse_sum)
-                   : __float2bfloat16_rn(0.0F);
+  // Zero through the end of the last 128-row cache tile: the P.V phase multiplies whole tiles.
+  const int padded = min(a.score_stride, score_columns(g.cache_rows));
+  for (int column = static_cast<int>(threadIdx.x); column < padded; column += 128) {
+    const bool visible = column_visible(a, g, position, token, column);
+    row[column] = visible
+                      ? __float2bfloat16_rn(expf(__bfloat162float(row[column]) - maximum) * inverse_sum)
+                      : __float2bfloat16_rn(0.0F);
   }
 }
 
-// Phase 3: out[row, :] = sum_key P[row, key] * V[key, :] over one key chunk. Each thread owns two
-// adjacent components; probabilities are staged through shared memory 64 keys at a time.
+// Phase 3: out[row, :] = sum_column P[row, column] * V[column, :] over one chunk of cache rows
+// (chunk 0 also takes the proposal columns). Each thread owns two adjacent components;
+// probabilities are staged through shared memory 64 columns at a time.
 template <int dimension, int max_rows>
 __global__ void __launch_bounds__(dimension / 2) pv_kernel(AttentionArguments a) {
   __shared__ __nv_bfloat16 probabilities[max_rows][64];
@@ -177,9 +147,7 @@ __global__ void __launch_bounds__(dimension / 2) pv_kernel(AttentionArguments a)
   const int chunk = static_cast<int>(blockIdx.x);
   const int group = a.query_heads / a.kv_heads;
   const int rows = group * a.depth;
-  const KeyGeometry g = geometry(a, request);
-  const int chunk_begin = chunk * a.chunk_keys;
-  const int chunk_end = min(g.keys, chunk_begin + a.chunk_keys);
+  const KeyGeometry g = key_geometry(a, request);
   const int component = static_cast<int>(threadIdx.x) * 2;
   const auto *score_rows = static_cast<const __nv_bfloat16 *>(a.scores) +
                            (static_cast<size_t>(request) * a.query_heads + kv_head * group) *
@@ -190,28 +158,40 @@ __global__ void __launch_bounds__(dimension / 2) pv_kernel(AttentionArguments a)
     sums[row][0] = 0.0F;
     sums[row][1] = 0.0F;
   }
-  for (int tile = chunk_begin; tile < chunk_end; tile += 64) {
-    __syncthreads();
-    for (int index = static_cast<int>(threadIdx.x); index < rows * 64; index += dimension / 2) {
-      const int row = index / 64;
-      const int key = tile + index % 64;
-      probabilities[row][index % 64] =
-          key < chunk_end ? score_rows[static_cast<size_t>(row) * a.score_stride + key]
-                          : __float2bfloat16_rn(0.0F);
+  // Two column ranges: the proposals (chunk 0 only) and this chunk's cache rows.
+  for (int range = 0; range < 2; ++range) {
+    int begin;
+    int end;
+    if (range == 0) {
+      begin = 0;
+      end = chunk == 0 ? g.proposals : 0;
+    } else {
+      begin = proposal_columns + chunk * a.chunk_keys;
+      end = proposal_columns + min(g.cache_rows, (chunk + 1) * a.chunk_keys);
     }
-    __syncthreads();
-    const int tile_keys = min(64, chunk_end - tile);
-    for (int offset = 0; offset < tile_keys; ++offset) {
-      const __nv_bfloat16 *value_row = row_pointer(a, a.value_cache, a.new_values, request,
-                                                   kv_head, tile + offset, g.context);
-      const float2 value =
-          __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(value_row + component));
+    for (int tile = begin; tile < end; tile += 64) {
+      __syncthreads();
+      for (int index = static_cast<int>(threadIdx.x); index < rows * 64; index += dimension / 2) {
+        const int row = index / 64;
+        const int column = tile + index % 64;
+        probabilities[row][index % 64] =
+            column < end ? score_rows[static_cast<size_t>(row) * a.score_stride + column]
+                         : __float2bfloat16_rn(0.0F);
+      }
+      __syncthreads();
+      const int tile_columns = min(64, end - tile);
+      for (int offset = 0; offset < tile_columns; ++offset) {
+        const __nv_bfloat16 *value_row =
+            row_pointer(a, a.value_cache, a.new_values, request, kv_head, tile + offset);
+        const float2 value =
+            __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(value_row + component));
 #pragma unroll
-      for (int row = 0; row < max_rows; ++row) {
-        if (row < rows) {
-          const float probability = __bfloat162float(probabilities[row][offset]);
-          sums[row][0] = fmaf(probability, value.x, sums[row][0]);
-          sums[row][1] = fmaf(probability, value.y, sums[row][1]);
+        for (int row = 0; row < max_rows; ++row) {
+          if (row < rows) {
+            const float probability = __bfloat162float(probabilities[row][offset]);
+            sums[row][0] = fmaf(probability, value.x, sums[row][0]);
+            sums[row][1] = fmaf(probability, value.y, sums[row][1]);
+          }
         }
       }
     }
@@ -241,7 +221,7 @@ __global__ void __launch_bounds__(dimension / 2) pv_kernel(AttentionArguments a)
 template <int dimension> int launch_phases(const AttentionArguments &a, cudaStream_t stream) {
   const int group = a.query_heads / a.kv_heads;
   const int rows = group * a.depth;
-  const int max_keys = a.max_context_rows + (a.draft ? 0 : a.depth);
+  const int columns = proposal_columns + a.max_cache_rows;
   const size_t query_bytes = static_cast<size_t>(rows) * dimension * sizeof(__nv_bfloat16);
   if (query_bytes > 96 * 1024 || rows > 80)
     return -2;
@@ -252,7 +232,7 @@ template <int dimension> int launch_phases(const AttentionArguments &a, cudaStre
       return -10;
     configured = true;
   }
-  const dim3 score_grid(static_cast<unsigned>((max_keys + 127) / 128),
+  const dim3 score_grid(static_cast<unsigned>((columns + 127) / 128),
                         static_cast<unsigned>(a.kv_heads), static_cast<unsigned>(a.requests));
   scores_kernel<dimension><<<score_grid, 128, query_bytes, stream>>>(a);
   softmax_kernel<<<a.requests * a.query_heads * a.depth, 128, 0, stream>>>(a);
@@ -270,18 +250,33 @@ template <int dimension> int launch_phases(const AttentionArguments &a, cudaStre
 
 } // namespace
 
-int launch_attention_simt(const AttentionArguments &a, cudaStream_t stream) {
+int validate_attention(const AttentionArguments &a) {
   if (a.queries == nullptr || a.key_cache == nullptr || a.value_cache == nullptr ||
       a.positions == nullptr || a.slots == nullptr || a.scores == nullptr || a.requests <= 0 ||
-      a.depth <= 0 || a.query_heads <= 0 || a.kv_heads <= 0 || a.query_heads % a.kv_heads != 0 ||
-      a.capacity <= 0 || a.chunks <= 0 || a.chunk_keys <= 0 || a.chunk_keys % 64 != 0 ||
-      a.score_stride % 8 != 0 || (a.chunks > 1 ? a.chunk_partials == nullptr : a.output == nullptr) ||
-      (a.draft && a.depth != 1)) {
+      a.depth <= 0 || a.depth > proposal_columns || a.query_heads <= 0 || a.kv_heads <= 0 ||
+      a.query_heads % a.kv_heads != 0 || a.capacity <= 0 || a.chunks <= 0 || a.chunk_keys <= 0 ||
+      a.chunk_keys % 128 != 0 || a.score_stride % 8 != 0 || a.max_cache_rows < 0 ||
+      (a.chunks > 1 ? a.chunk_partials == nullptr : a.output == nullptr) ||
+      (a.draft && (a.depth != 1 || a.new_keys != nullptr)) ||
+      ((a.new_keys == nullptr) != (a.new_values == nullptr))) {
     return -1;
   }
-  const int max_keys = a.max_context_rows + (a.draft ? 0 : a.depth);
-  if (max_keys > a.score_stride || a.chunks * a.chunk_keys < max_keys)
+  if (score_columns(a.max_cache_rows) > a.score_stride ||
+      a.chunks * a.chunk_keys < a.max_cache_rows) {
     return -2;
+  }
+  return 0;
+}
+
+int launch_attention_softmax(const AttentionArguments &a, cudaStream_t stream) {
+  softmax_kernel<<<a.requests * a.query_heads * a.depth, 128, 0, stream>>>(a);
+  return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
+}
+
+int launch_attention_simt(const AttentionArguments &a, cudaStream_t stream) {
+  const int status = validate_attention(a);
+  if (status != 0)
+    return status;
   switch (a.head_dim) {
   case 64:
     return launch_phases<64>(a, stream);

@@ -1,0 +1,33 @@
+// Tensor maps of the tensor-core attention kernels. All tiles are bf16 with 128-byte rows
+// (64 elements) and the 128-byte swizzle, so one tile row is one swizzle-atom row.
+#pragma once
+
+#include <cuda.h>
+
+namespace carat_b200 {
+
+struct AttentionMaps {
+  CUtensorMap keys;        // cache K as [slots * kv_heads * capacity, head_dim], box 128 rows
+  CUtensorMap values;      // cache V, same view and box
+  CUtensorMap new_keys;    // staged proposals as [requests * kv_heads * depth, head_dim], box 16 rows
+  CUtensorMap new_values;
+  CUtensorMap queries;     // [query rows, head_dim], box padded_rows rows
+  CUtensorMap scores;      // [score rows, score_stride], box padded_rows rows x 64 columns
+  int padded_rows;         // UMMA N: 16, 48 or 80 (>= query_heads / kv_heads * depth)
+};
+
+// UMMA N for `rows` query rows per KV head, or 0 when there are too many.
+inline int attention_padded_rows(int rows) {
+  return rows <= 16 ? 16 : rows <= 48 ? 48 : rows <= 80 ? 80 : 0;
+}
+
+// Encodes the maps. `staged_*` may be null (global layers, drafter). row counts are the extents
+// of the underlying buffers (an upper bound is fine: rows beyond what a launch uses are never
+// stored). Returns 0 or a negative code.
+int make_attention_maps(AttentionMaps *maps, const void *key_cache, const void *value_cache,
+                        long long cache_rows, const void *staged_keys, const void *staged_values,
+                        long long staged_rows, const void *queries, long long query_rows,
+                        const void *scores, long long score_rows, int score_stride, int head_dim,
+                        int padded_rows);
+
+} // namespace carat_b200

@@ -3,6 +3,7 @@
 #include "../../include/carat_b200.h"
 #include "accept.cuh"
 #include "attention.cuh"
+#include "attention_tc.cuh"
 #include "context.cuh"
 #include "qkv_post.cuh"
 #include "row_ops.cuh"
@@ -177,15 +178,16 @@ __global__ void identity_slots_kernel(int *slots, int count) {
 }
 } // namespace
 
-extern "C" int carat_b200_verify_attention(const void *bf16_queries, const void *bf16_key_caches,
-                                           const void *bf16_value_caches,
-                                           const void *bf16_new_keys, const void *bf16_new_values,
-                                           const int *device_positions, void *bf16_output,
-                                           void *bf16_scores, int score_stride, int requests,
-                                           int depth, int query_heads, int kv_heads, int head_dim,
-                                           int capacity, int window, int max_position,
-                                           void *stream) {
-  if (bf16_new_keys == nullptr || bf16_new_values == nullptr || requests <= 0 || requests > 1024) {
+namespace {
+
+int run_verify_attention(bool tensor_cores, const void *bf16_queries, const void *bf16_key_caches,
+                         const void *bf16_value_caches, const void *bf16_new_keys,
+                         const void *bf16_new_values, const int *device_positions,
+                         void *bf16_output, void *bf16_scores, int score_stride, int requests,
+                         int depth, int query_heads, int kv_heads, int head_dim, int capacity,
+                         int window, int max_position, void *stream) {
+  if (requests <= 0 || requests > 1024 || kv_heads <= 0 || query_heads <= 0 || depth <= 0 ||
+      (window > 0 && (bf16_new_keys == nullptr || bf16_new_values == nullptr))) {
     set_last_error("invalid verify attention arguments");
     return -1;
   }
@@ -213,7 +215,6 @@ extern "C" int carat_b200_verify_attention(const void *bf16_queries, const void 
   a.score_stride = score_stride;
   a.output = bf16_output;
   a.chunks = 1;
-  a.chunk_keys = (score_stride + 63) / 64 * 64;
   a.requests = requests;
   a.depth = depth;
   a.query_heads = query_heads;
@@ -221,9 +222,57 @@ extern "C" int carat_b200_verify_attention(const void *bf16_queries, const void 
   a.head_dim = head_dim;
   a.capacity = capacity;
   a.window = window;
-  a.max_context_rows = window > 0 ? (max_position < capacity ? max_position : capacity)
-                                  : max_position;
+  const bool staged = bf16_new_keys != nullptr;
+  a.max_cache_rows = staged ? (max_position < capacity ? max_position : capacity)
+                            : max_position + depth;
+  a.chunk_keys = (a.max_cache_rows + 127) / 128 * 128;
+  if (a.chunk_keys == 0)
+    a.chunk_keys = 128;
+  AttentionMaps maps;
+  if (tensor_cores && (head_dim == 256 || head_dim == 512) && capacity % 128 == 0) {
+    const int padded = attention_padded_rows(query_heads / kv_heads * depth);
+    const long long score_rows = static_cast<long long>(requests) * query_heads * depth;
+    const int status = make_attention_maps(
+        &maps, bf16_key_caches, bf16_value_caches,
+        static_cast<long long>(requests) * kv_heads * capacity, bf16_new_keys, bf16_new_values,
+        static_cast<long long>(requests) * kv_heads * depth, bf16_queries, score_rows, bf16_scores,
+        score_rows, score_stride, head_dim, padded);
+    if (status != 0) {
+      set_last_error("verify attention: tensor map encoding failed");
+      return status;
+    }
+    a.maps = &maps;
+    return finish(launch_attention_tc(a, cuda_stream), "verify attention");
+  }
   return finish(launch_attention_simt(a, cuda_stream), "verify attention");
+}
+
+} // namespace
+
+extern "C" int carat_b200_verify_attention(const void *bf16_queries, const void *bf16_key_caches,
+                                           const void *bf16_value_caches,
+                                           const void *bf16_new_keys, const void *bf16_new_values,
+                                           const int *device_positions, void *bf16_output,
+                                           void *bf16_scores, int score_stride, int requests,
+                                           int depth, int query_heads, int kv_heads, int head_dim,
+                                           int capacity, int window, int max_position,
+                                           void *stream) {
+  return run_verify_attention(true, bf16_queries, bf16_key_caches, bf16_value_caches,
+                              bf16_new_keys, bf16_new_values, device_positions, bf16_output,
+                              bf16_scores, score_stride, requests, depth, query_heads, kv_heads,
+                              head_dim, capacity, window, max_position, stream);
+}
+
+extern "C" int carat_b200_verify_attention_check(
+    const void *bf16_queries, const void *bf16_key_caches, const void *bf16_value_caches,
+    const void *bf16_new_keys, const void *bf16_new_values, const int *device_positions,
+    void *bf16_output, void *bf16_scores, int score_stride, int requests, int depth,
+    int query_heads, int kv_heads, int head_dim, int capacity, int window, int max_position,
+    void *stream) {
+  return run_verify_attention(false, bf16_queries, bf16_key_caches, bf16_value_caches,
+                              bf16_new_keys, bf16_new_values, device_positions, bf16_output,
+                              bf16_scores, score_stride, requests, depth, query_heads, kv_heads,
+                              head_dim, capacity, window, max_position, stream);
 }
 
 extern "C" int carat_b200_backup_kv_ring_spans(const void *const *device_key_sources,

@@ -7,6 +7,8 @@
 #include "../../include/carat_b200.h"
 #include "accept.cuh"
 #include "attention.cuh"
+#include "attention_geometry.cuh"
+#include "attention_tc.cuh"
 #include "context.cuh"
 #include "fp8_linear.cuh"
 #include "qkv_post.cuh"
@@ -179,6 +181,8 @@ struct carat_b200_runner {
   int score_stride_global{0};
   int *device_error{nullptr};
   std::map<int, StepPlans> verify_plans;
+  std::map<std::pair<int, int>, AttentionMaps> verify_maps;  // (layer, depth)
+  std::map<int, AttentionMaps> draft_maps;                   // assistant layer
   // ---- workspaces (assistant)
   DeviceBuffer a_hidden_a, a_hidden_b, a_residual, a_final_hidden, a_quantized, a_projected,
       a_queries, a_attention_out, a_attention_partials, a_scores, a_linear_out, a_gate_up,
@@ -328,11 +332,11 @@ void build_runner(Runner &runner, const carat_b200_model_config &config,
   runner.packed.allocate(static_cast<size_t>(rows) * widest_packed * 2);
   runner.queries.allocate(static_cast<size_t>(rows) * widest_query * 2);
   runner.attention_out.allocate(static_cast<size_t>(rows) * widest_query * 2);
-  const int global_chunks = attention_chunks(maximum_context, 0, global_chunk_keys);
+  const int global_chunks = attention_chunks(maximum_context, global_chunk_keys);
   runner.attention_partials.allocate(static_cast<size_t>(global_chunks) * rows * widest_query * 4);
   const int sliding_capacity = std::min(maximum_context, config.sliding_window);
-  runner.score_stride_sliding = (sliding_capacity + maximum_depth + 63) / 64 * 64;
-  runner.score_stride_global = (maximum_context + 63) / 64 * 64;
+  runner.score_stride_sliding = score_columns(sliding_capacity);
+  runner.score_stride_global = score_columns(maximum_context);
   int most_heads = 0;
   for (const LayerState &layer : runner.layers)
     most_heads = std::max(most_heads, layer.shape.query_heads);
@@ -494,6 +498,56 @@ PartialSource run_linear(Runner &runner, const LinearPlan &plan, const float *in
   return PartialSource{nullptr, 0, nullptr, nullptr};
 }
 
+// Tensor maps of the tensor-core attention for one target layer at one depth (null when the layer
+// shape needs the CUDA-core kernels: head_dim 64 or a capacity that is not a multiple of 128).
+const AttentionMaps *verify_attention_maps(Runner &runner, int layer_index, int depth) {
+  const LayerState &layer = runner.layers[static_cast<size_t>(layer_index)];
+  const auto &shape = layer.shape;
+  const int padded = attention_padded_rows(shape.query_heads / shape.kv_heads * depth);
+  if ((shape.head_dim != 256 && shape.head_dim != 512) || layer.capacity % 128 != 0 || padded == 0)
+    return nullptr;
+  const auto key = std::make_pair(layer_index, depth);
+  const auto found = runner.verify_maps.find(key);
+  if (found != runner.verify_maps.end())
+    return &found->second;
+  const bool staged = !shape.global_attention;
+  const int stride = staged ? runner.score_stride_sliding : runner.score_stride_global;
+  AttentionMaps maps;
+  const int status = make_attention_maps(
+      &maps, layer.keys(), layer.values(),
+      static_cast<long long>(runner.batch) * shape.kv_heads * layer.capacity,
+      staged ? layer.staged_keys() : nullptr, staged ? layer.staged_values() : nullptr,
+      static_cast<long long>(runner.batch) * shape.kv_heads * depth, runner.queries.get(),
+      static_cast<long long>(runner.queries.bytes() / (2 * shape.head_dim)), runner.scores.get(),
+      static_cast<long long>(runner.scores.bytes() / (2 * stride)), stride, shape.head_dim, padded);
+  if (status != 0)
+    throw Failure{"attention tensor map encoding failed"};
+  return &runner.verify_maps.emplace(key, maps).first->second;
+}
+
+const AttentionMaps *draft_attention_maps(Runner &runner, int assistant_layer) {
+  const LayerState &shared = shared_layer(runner, assistant_layer);
+  const auto &shape = shared.shape;
+  const int padded = attention_padded_rows(runner.assistant.query_heads / shape.kv_heads);
+  if ((shape.head_dim != 256 && shape.head_dim != 512) || shared.capacity % 128 != 0 || padded == 0)
+    return nullptr;
+  const auto found = runner.draft_maps.find(assistant_layer);
+  if (found != runner.draft_maps.end())
+    return &found->second;
+  const int stride = runner.score_stride_global;
+  AttentionMaps maps;
+  const int status = make_attention_maps(
+      &maps, shared.keys(), shared.values(),
+      static_cast<long long>(runner.batch) * shape.kv_heads * shared.capacity, nullptr, nullptr, 0,
+      runner.a_queries.get(),
+      static_cast<long long>(runner.a_queries.bytes() / (2 * shape.head_dim)),
+      runner.a_scores.get(), static_cast<long long>(runner.a_scores.bytes() / (2 * stride)), stride,
+      shape.head_dim, padded);
+  if (status != 0)
+    throw Failure{"attention tensor map encoding failed"};
+  return &runner.draft_maps.emplace(assistant_layer, maps).first->second;
+}
+
 struct StepLayout {
   int *tokens;
   int *positions;
@@ -631,22 +685,25 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
     attention.capacity = layer.capacity;
     if (shape.global_attention) {
       attention.window = 0;
-      attention.max_context_rows = longest;
+      attention.max_cache_rows = longest + depth;
       attention.score_stride = runner.score_stride_global;
       attention.chunk_keys = global_chunk_keys;
-      attention.chunks = attention_chunks(longest, depth, global_chunk_keys);
+      attention.chunks = attention_chunks(longest + depth, global_chunk_keys);
     } else {
       attention.window = config.sliding_window;
       attention.new_keys = layer.staged_keys();
       attention.new_values = layer.staged_values();
       attention.new_request_stride = post.slot_stride;
       attention.new_head_stride = post.head_stride;
-      attention.max_context_rows = std::min(longest, layer.capacity);
+      attention.max_cache_rows = std::min(longest, layer.capacity);
       attention.score_stride = runner.score_stride_sliding;
-      attention.chunk_keys = runner.score_stride_sliding;
+      attention.chunk_keys = (layer.capacity + 127) / 128 * 128;
       attention.chunks = 1;
     }
-    require_launch(launch_attention_simt(attention, stream), "verify attention");
+    attention.maps = verify_attention_maps(runner, index, depth);
+    require_launch(attention.maps != nullptr ? launch_attention_tc(attention, stream)
+                                             : launch_attention_simt(attention, stream),
+                   "verify attention");
     runner.launches += 3;
 
     require_launch(launch_quant(attention.chunks > 1 ? nullptr : runner.attention_out.get(),
@@ -859,11 +916,14 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
       attention.capacity = shared.capacity;
       attention.window = shape.global_attention ? 0 : config.sliding_window;
       attention.draft = 1;
-      attention.max_context_rows = std::min(longest, shared.capacity);
+      attention.max_cache_rows = std::min(longest, shared.capacity);
       attention.score_stride = runner.score_stride_global;
       attention.chunk_keys = global_chunk_keys;
-      attention.chunks = attention_chunks(attention.max_context_rows, 0, global_chunk_keys);
-      require_launch(launch_attention_simt(attention, stream), "assistant attention");
+      attention.chunks = attention_chunks(attention.max_cache_rows, global_chunk_keys);
+      attention.maps = draft_attention_maps(runner, index);
+      require_launch(attention.maps != nullptr ? launch_attention_tc(attention, stream)
+                                               : launch_attention_simt(attention, stream),
+                     "assistant attention");
       runner.launches += 3;
       require_launch(launch_quant(attention.chunks > 1 ? nullptr : runner.a_attention_out.get(),
                                   attention.chunks > 1 ? runner.a_attention_partials.get<float>()

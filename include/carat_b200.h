@@ -169,14 +169,19 @@ CARAT_B200_API int carat_b200_qkv_postprocess(const void *bf16_packed, const voi
                                int key_equals_value, int table_positions, float epsilon,
                                void *stream);
 
-/* Verify attention of `depth` proposal rows per request over that request's cache plus the
+/* Verify attention of `depth` (<= 16) proposal rows per request over that request's cache plus the
  * proposals. caches: [requests, kv_heads, capacity, head_dim] (logical position p in row
- * p % capacity); proposals [requests, kv_heads, depth, head_dim]; queries
- * [requests, query_heads, depth, head_dim]; output [requests * depth, query_heads * head_dim].
- * window = 0 selects causal attention over a linear cache, otherwise the sliding window.
- * scores is scratch of requests * query_heads * depth * score_stride bf16 with
- * score_stride >= min(max position, capacity) + depth, a multiple of 8.
- * Replaces GemmCausalPrefillAttention::run_uniform_batch / run_uniform_ring_batch
+ * p % capacity); queries [requests, query_heads, depth, head_dim]; output
+ * [requests * depth, query_heads * head_dim].
+ *  - window > 0: sliding ring. The proposals' K/V are passed on the side as
+ *    [requests, kv_heads, depth, head_dim] and the ring is left untouched.
+ *  - window = 0 with new_keys/new_values NULL: causal attention over a linear cache that already
+ *    holds the proposals at rows position .. position + depth - 1.
+ * scores is scratch of requests * query_heads * depth * score_stride bf16, score_stride a multiple
+ * of 8 and >= 16 + the participating cache rows rounded up to 128 (cache rows = min(max_position,
+ * capacity) for a ring, max_position + depth for a linear cache).
+ * head_dim 256 / 512 with capacity % 128 == 0 runs on tensor cores (tcgen05 + TMA), head_dim 64 on
+ * CUDA cores. Replaces GemmCausalPrefillAttention::run_uniform_batch / run_uniform_ring_batch
  * (include/carat/prefill_gemm_attention.h:24-47). */
 CARAT_B200_API int carat_b200_verify_attention(const void *bf16_queries, const void *bf16_key_caches,
                                 const void *bf16_value_caches, const void *bf16_new_keys,
@@ -185,6 +190,15 @@ CARAT_B200_API int carat_b200_verify_attention(const void *bf16_queries, const v
                                 int requests, int depth, int query_heads, int kv_heads,
                                 int head_dim, int capacity, int window, int max_position,
                                 void *stream);
+
+/* Same contract on CUDA cores for every head_dim: the device-side cross-check of the tensor-core
+ * kernels; no step path calls it for head_dim 256 / 512. */
+CARAT_B200_API int carat_b200_verify_attention_check(
+    const void *bf16_queries, const void *bf16_key_caches, const void *bf16_value_caches,
+    const void *bf16_new_keys, const void *bf16_new_values, const int *device_positions,
+    void *bf16_output, void *bf16_scores, int score_stride, int requests, int depth,
+    int query_heads, int kv_heads, int head_dim, int capacity, int window, int max_position,
+    void *stream);
 
 /* Rollback primitives with the reference's signatures
  * (include/carat/cuda_ops.h:124-135, cuda/ops.cu:827-871,1485-1525). */

@@ -134,14 +134,23 @@ def test_layer_stage_by_stage(cuda_device, layer_index):
         queries.reshape(1, depth, heads, dim), [oracle.keys[layer_index][0]],
         [oracle.values[layer_index][0]], new_k.reshape(1, depth, kv_heads, dim),
         new_v.reshape(1, depth, kv_heads, dim), [position], window)
-    stride = (min(position, capacity) + depth + 63) // 64 * 64
+    cache_rows = min(position, capacity) if window > 0 else position + depth
+    stride = 16 + (cache_rows + 127) // 128 * 128
+    if window > 0:
+        cache_k, cache_v = dev(oracle.keys[layer_index][0:1]), dev(oracle.values[layer_index][0:1])
+        side_k = dev(new_k.reshape(1, depth, kv_heads, dim).permute(0, 2, 1, 3))
+        side_v = dev(new_v.reshape(1, depth, kv_heads, dim).permute(0, 2, 1, 3))
+    else:
+        filled_k = oracle.keys[layer_index][0:1].clone()
+        filled_v = oracle.values[layer_index][0:1].clone()
+        filled_k[0, :, position:position + depth] = new_k.reshape(depth, kv_heads, dim).permute(1, 0, 2)
+        filled_v[0, :, position:position + depth] = new_v.reshape(depth, kv_heads, dim).permute(1, 0, 2)
+        cache_k, cache_v, side_k, side_v = dev(filled_k), dev(filled_v), None, None
     d_out = torch.empty(depth, heads * dim, dtype=torch.bfloat16, device="cuda")
     d_scores = torch.zeros(heads * depth * stride, dtype=torch.bfloat16, device="cuda")
     check(lib.carat_b200_verify_attention(
         ptr(dev(queries.reshape(1, depth, heads, dim).permute(0, 2, 1, 3))),
-        ptr(dev(oracle.keys[layer_index][0:1])), ptr(dev(oracle.values[layer_index][0:1])),
-        ptr(dev(new_k.reshape(1, depth, kv_heads, dim).permute(0, 2, 1, 3))),
-        ptr(dev(new_v.reshape(1, depth, kv_heads, dim).permute(0, 2, 1, 3))),
+        ptr(cache_k), ptr(cache_v), ptr(side_k), ptr(side_v),
         ptr(dev(torch.tensor([position]), torch.int32)), ptr(d_out), ptr(d_scores), stride, 1, depth,
         heads, kv_heads, dim, capacity, window, position, None))
     torch.cuda.synchronize()

@@ -264,7 +264,7 @@ def test_ring_attention_reference_case(cuda_device, query_tokens):
         return torch.nn.functional.pad(tensor, (0, 48))
     requests, heads = 2, 2
     out = torch.empty(requests * query_tokens, heads * 64, dtype=torch.bfloat16, device="cuda")
-    stride = 64
+    stride = 16 + 128
     scores = torch.empty(requests * heads * query_tokens * stride, dtype=torch.bfloat16, device="cuda")
     check(lib.carat_b200_verify_attention(
         ptr(dev(pad(query))), ptr(dev(pad(old_k))), ptr(dev(pad(old_v))), ptr(dev(pad(new_k))),
@@ -281,6 +281,8 @@ def test_ring_attention_reference_case(cuda_device, query_tokens):
     (64, 4, 2, 0, 512, [1, 60, 200, 333, 500]),
     (256, 32, 16, 1024, 1024, [5, 1020, 1024, 3000]),
     (512, 32, 4, 0, 2048, [3, 700, 2040]),
+    (512, 8, 1, 0, 4096, [1, 2500, 4000]),
+    (256, 4, 2, 256, 256, [1, 128, 255, 256, 1000]),
 ])
 def test_verify_attention_matches_oracle(cuda_device, head_dim, heads, kv_heads, window, capacity,
                                          positions):
@@ -295,17 +297,38 @@ def test_verify_attention_matches_oracle(cuda_device, head_dim, heads, kv_heads,
     old_k = cs.bf16(torch.randn(requests, kv_heads, capacity, head_dim, generator=generator) * scale)
     old_v = cs.bf16(torch.randn(requests, kv_heads, capacity, head_dim, generator=generator))
     want = cs.verify_attention(queries, list(old_k), list(old_v), new_k, new_v, positions, window)
-    stride = (min(max(positions), capacity) + depth + 63) // 64 * 64
-    out = torch.empty(requests * depth, heads * head_dim, dtype=torch.bfloat16, device="cuda")
-    scores = torch.empty(requests * heads * depth * stride, dtype=torch.bfloat16, device="cuda")
-    check(lib.carat_b200_verify_attention(
-        ptr(dev(queries.permute(0, 2, 1, 3))), ptr(dev(old_k)), ptr(dev(old_v)),
-        ptr(dev(new_k.permute(0, 2, 1, 3))), ptr(dev(new_v.permute(0, 2, 1, 3))),
-        ptr(dev_int(positions)), ptr(out), ptr(scores),
-        stride, requests, depth, heads, kv_heads, head_dim, capacity, window, max(positions), None))
-    torch.cuda.synchronize()
-    got = out.float().cpu().reshape(requests, depth, heads, head_dim)
-    assert relative_error(got, want) < 2e-2
+    d_queries = dev(queries.permute(0, 2, 1, 3))
+    d_positions = dev_int(positions)
+    outputs = []
+    for entry in (lib.carat_b200_verify_attention, lib.carat_b200_verify_attention_check):
+        if window > 0:
+            rows = min(max(positions), capacity)
+            d_old_k, d_old_v = dev(old_k), dev(old_v)
+            d_new_k, d_new_v = dev(new_k.permute(0, 2, 1, 3)), dev(new_v.permute(0, 2, 1, 3))
+        else:
+            # Linear cache: the proposals are already in the cache at rows position + t.
+            rows = max(positions) + depth
+            filled_k, filled_v = old_k.clone(), old_v.clone()
+            for r, position in enumerate(positions):
+                filled_k[r, :, position:position + depth] = new_k[r].permute(1, 0, 2)
+                filled_v[r, :, position:position + depth] = new_v[r].permute(1, 0, 2)
+            d_old_k, d_old_v, d_new_k, d_new_v = dev(filled_k), dev(filled_v), None, None
+        stride = 16 + (rows + 127) // 128 * 128
+        out = torch.empty(requests * depth, heads * head_dim, dtype=torch.bfloat16, device="cuda")
+        scores = torch.empty(requests * heads * depth * stride, dtype=torch.bfloat16, device="cuda")
+        check(entry(ptr(d_queries), ptr(d_old_k), ptr(d_old_v), ptr(d_new_k), ptr(d_new_v),
+                    ptr(d_positions), ptr(out), ptr(scores), stride, requests, depth, heads,
+                    kv_heads, head_dim, capacity, window, max(positions), None))
+        torch.cuda.synchronize()
+        code = ctypes.c_int(0)
+        check(lib.carat_b200_device_error(ctypes.byref(code)))
+        assert code.value == 0
+        outputs.append(out.float().cpu().reshape(requests, depth, heads, head_dim))
+    for got in outputs:
+        assert relative_error(got, want) < 2e-2
+        assert (got != want).float().mean() < 0.02
+    # The tensor-core kernels and the CUDA-core cross-check agree to rare last-bit differences.
+    assert (outputs[0] != outputs[1]).float().mean() < 0.02
 
 
 def test_backup_restore_is_bit_exact(cuda_device):
