@@ -89,22 +89,68 @@ __global__ void __launch_bounds__(128) scores_kernel(AttentionArguments a) {
 }
 
 // Phase 2: in-place softmax of one score row; masked and padding columns become exact zeros.
-__global__ void __launch_bounds__(128) softmax_kernel(AttentionArguments a) {
-  __shared__ float scratch[4];
+// Visibility is evaluated without a division per element: for a ring row r the distance
+// m = (position - 1 - r) mod capacity back from the newest resident position is one compare and
+// add, and the row is inside query t's window iff m <= window - 2 - t.
+struct RowVisibility {
+  int proposals;
+  int cache_rows;
+  int token;
+  int mode;          // 0 everything, 1 causal over a linear cache, 2 ring window
+  int causal_last;   // mode 1: last visible cache row
+  int newest_row;    // mode 2: (position - 1) % capacity
+  int capacity;
+  int reach;         // mode 2: window - 2 - token
+  __device__ __forceinline__ bool operator()(int column) const {
+    if (column < proposal_columns)
+      return column < proposals && column <= token;
+    const int row = column - proposal_columns;
+    if (row >= cache_rows)
+      return false;
+    if (mode == 0)
+      return true;
+    if (mode == 1)
+      return row <= causal_last;
+    int distance = newest_row - row;
+    if (distance < 0)
+      distance += capacity;
+    return distance <= reach;
+  }
+};
+
+constexpr int softmax_threads = 128;
+
+__global__ void __launch_bounds__(softmax_threads) softmax_kernel(AttentionArguments a) {
+  __shared__ float scratch[softmax_threads / 32];
   const int row_index = static_cast<int>(blockIdx.x);
   const int token = row_index % a.depth;
   const int request = row_index / (a.depth * a.query_heads);
   const KeyGeometry g = key_geometry(a, request);
   const int position = a.positions[request];
+  RowVisibility visible;
+  visible.proposals = g.proposals;
+  visible.cache_rows = g.cache_rows;
+  visible.token = token;
+  visible.capacity = a.capacity;
+  visible.causal_last = position + token;
+  visible.newest_row = position > 0 ? (position - 1) % a.capacity : 0;
+  visible.reach = a.window - 2 - token;
+  visible.mode = a.draft ? 0 : a.new_keys == nullptr ? 1 : a.window > 0 ? 2 : 0;
   auto *row = static_cast<__nv_bfloat16 *>(a.scores) + static_cast<size_t>(row_index) * a.score_stride;
   const int lane = static_cast<int>(threadIdx.x) & 31;
   const int warp = static_cast<int>(threadIdx.x) >> 5;
-  const int columns = g.columns();
+  // Whole 128-row cache tiles: the P.V phase multiplies complete tiles, so padding must be zero.
+  const int padded = min(a.score_stride, score_columns(g.cache_rows));
 
   float maximum = -CUDART_INF_F;
-  for (int column = static_cast<int>(threadIdx.x); column < columns; column += 128) {
-    if (column_visible(a, g, position, token, column))
-      maximum = fmaxf(maximum, __bfloat162float(row[column]));
+  for (int base = static_cast<int>(threadIdx.x) * 8; base < padded; base += softmax_threads * 8) {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(row + base);
+    const auto *values = reinterpret_cast<const __nv_bfloat16 *>(&raw);
+#pragma unroll
+    for (int index = 0; index < 8; ++index) {
+      if (visible(base + index))
+        maximum = fmaxf(maximum, __bfloat162float(values[index]));
+    }
   }
   for (int offset = 16; offset > 0; offset >>= 1)
     maximum = fmaxf(maximum, __shfl_xor_sync(0xFFFFFFFFU, maximum, offset));
@@ -115,9 +161,14 @@ __global__ void __launch_bounds__(128) softmax_kernel(AttentionArguments a) {
   __syncthreads();
 
   float sum = 0.0F;
-  for (int column = static_cast<int>(threadIdx.x); column < columns; column += 128) {
-    if (column_visible(a, g, position, token, column))
-      sum += expf(__bfloat162float(row[column]) - maximum);
+  for (int base = static_cast<int>(threadIdx.x) * 8; base < padded; base += softmax_threads * 8) {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(row + base);
+    const auto *values = reinterpret_cast<const __nv_bfloat16 *>(&raw);
+#pragma unroll
+    for (int index = 0; index < 8; ++index) {
+      if (visible(base + index))
+        sum += expf(__bfloat162float(values[index]) - maximum);
+    }
   }
   for (int offset = 16; offset > 0; offset >>= 1)
     sum += __shfl_xor_sync(0xFFFFFFFFU, sum, offset);
@@ -126,13 +177,18 @@ __global__ void __launch_bounds__(128) softmax_kernel(AttentionArguments a) {
   __syncthreads();
   const float inverse_sum = 1.0F / (scratch[0] + scratch[1] + scratch[2] + scratch[3]);
 
-  // Zero through the end of the last 128-row cache tile: the P.V phase multiplies whole tiles.
-  const int padded = min(a.score_stride, score_columns(g.cache_rows));
-  for (int column = static_cast<int>(threadIdx.x); column < padded; column += 128) {
-    const bool visible = column_visible(a, g, position, token, column);
-    row[column] = visible
-                      ? __float2bfloat16_rn(expf(__bfloat162float(row[column]) - maximum) * inverse_sum)
-                      : __float2bfloat16_rn(0.0F);
+  for (int base = static_cast<int>(threadIdx.x) * 8; base < padded; base += softmax_threads * 8) {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(row + base);
+    const auto *values = reinterpret_cast<const __nv_bfloat16 *>(&raw);
+    __align__(16) __nv_bfloat16 result[8];
+#pragma unroll
+    for (int index = 0; index < 8; ++index) {
+      result[index] = visible(base + index)
+                          ? __float2bfloat16_rn(expf(__bfloat162float(values[index]) - maximum) *
+                                                inverse_sum)
+                          : __float2bfloat16_rn(0.0F);
+    }
+    *reinterpret_cast<uint4 *>(row + base) = *reinterpret_cast<const uint4 *>(result);
   }
 }
 
@@ -235,7 +291,7 @@ template <int dimension> int launch_phases(const AttentionArguments &a, cudaStre
   const dim3 score_grid(static_cast<unsigned>((columns + 127) / 128),
                         static_cast<unsigned>(a.kv_heads), static_cast<unsigned>(a.requests));
   scores_kernel<dimension><<<score_grid, 128, query_bytes, stream>>>(a);
-  softmax_kernel<<<a.requests * a.query_heads * a.depth, 128, 0, stream>>>(a);
+  softmax_kernel<<<a.requests * a.query_heads * a.depth, softmax_threads, 0, stream>>>(a);
   const dim3 pv_grid(static_cast<unsigned>(a.chunks), static_cast<unsigned>(a.kv_heads),
                      static_cast<unsigned>(a.requests));
   if (rows <= 16) {
@@ -269,7 +325,7 @@ int validate_attention(const AttentionArguments &a) {
 }
 
 int launch_attention_softmax(const AttentionArguments &a, cudaStream_t stream) {
-  softmax_kernel<<<a.requests * a.query_heads * a.depth, 128, 0, stream>>>(a);
+  softmax_kernel<<<a.requests * a.query_heads * a.depth, softmax_threads, 0, stream>>>(a);
   return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
 }
 

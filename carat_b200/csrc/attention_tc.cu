@@ -265,19 +265,39 @@ scores_tc_kernel(const __grid_constant__ CUtensorMap key_map,
 }
 
 // ------------------------------------------------------------------------------------ P.V
+// One CTA covers every output component of one (request, kv head) over one chunk of cache rows, so
+// whole V rows are fetched (a row is head_dim * 2 bytes of contiguous HBM) and the probability
+// tile is loaded once. A pipeline stage holds 64 KB of V: 128 keys at head_dim 256, 64 keys at 512.
+template <int dimension> struct PvShape {
+  static constexpr int slices = dimension / 128;               // UMMA M = 128 components each
+  static constexpr int stage_keys = 32768 / dimension;         // 128 or 64
+  static constexpr int boxes = dimension / 64;                 // V boxes per stage
+  static constexpr int box_bytes = stage_keys * 128;
+  static constexpr int value_bytes = boxes * box_bytes;        // 64 KB
+  static constexpr int score_boxes = stage_keys / 64;
+};
+
+template <int dimension, int padded_rows> __host__ __device__ constexpr int pv_stage_bytes() {
+  return PvShape<dimension>::value_bytes + PvShape<dimension>::score_boxes * padded_rows * 128;
+}
+
+template <int dimension, int padded_rows> __host__ __device__ constexpr int pv_stages() {
+  return (220 * 1024) / pv_stage_bytes<dimension, padded_rows>() >= 3 ? 3 : 2;
+}
+
 template <int dimension, int padded_rows>
 __global__ void __launch_bounds__(tc_threads, 1)
 pv_tc_kernel(const __grid_constant__ CUtensorMap value_map,
              const __grid_constant__ CUtensorMap new_value_map,
              const __grid_constant__ CUtensorMap score_map, const TcArguments args) {
-  constexpr int slices = dimension / 128;          // 128 output components per CTA (UMMA M)
-  constexpr int stages = 3;
-  constexpr uint32_t value_bytes = 2 * subtile_bytes;          // [128 keys x 128 components]
+  using Shape = PvShape<dimension>;
+  constexpr int stages = pv_stages<dimension, padded_rows>();
   constexpr uint32_t score_box_bytes = padded_rows * 128;      // [padded_rows x 64 keys]
-  constexpr uint32_t stage_bytes = value_bytes + 2 * score_box_bytes;
+  constexpr uint32_t stage_bytes = pv_stage_bytes<dimension, padded_rows>();
   // bf16 x bf16 -> fp32, A (V^T) MN-major: bit 15.
   constexpr uint32_t idesc = ptx::umma_idesc(1, 1, 128, padded_rows) | (1U << 15);
-  constexpr uint32_t tmem_columns = tmem_columns_for(padded_rows);
+  constexpr uint32_t tmem_columns =
+      Shape::slices * padded_rows <= 256 ? tmem_columns_for(Shape::slices * padded_rows) : 512U;
   const AttentionArguments &a = args.a;
 
   extern __shared__ unsigned char shared_raw[];
@@ -290,15 +310,14 @@ pv_tc_kernel(const __grid_constant__ CUtensorMap value_map,
 
   const int warp = static_cast<int>(threadIdx.x) / 32;
   const int lane = static_cast<int>(threadIdx.x) & 31;
-  const int chunk = static_cast<int>(blockIdx.x) / slices;
-  const int slice = static_cast<int>(blockIdx.x) % slices;
+  const int chunk = static_cast<int>(blockIdx.x);
   const int kv_head = static_cast<int>(blockIdx.y);
   const int request = static_cast<int>(blockIdx.z);
   const int group = a.query_heads / a.kv_heads;
   const int rows = group * a.depth;
   const KeyGeometry g = key_geometry(a, request);
-  const int total_tiles = (g.cache_rows + tile_rows - 1) / tile_rows;
-  const int tiles_per_chunk = a.chunk_keys / tile_rows;
+  const int total_tiles = (g.cache_rows + Shape::stage_keys - 1) / Shape::stage_keys;
+  const int tiles_per_chunk = a.chunk_keys / Shape::stage_keys;
   const int first_tile = chunk * tiles_per_chunk;
   const int last_tile = min(total_tiles, first_tile + tiles_per_chunk);
   const int cache_items = max(0, last_tile - first_tile);
@@ -343,26 +362,26 @@ pv_tc_kernel(const __grid_constant__ CUtensorMap value_map,
           break;
         }
         const uint32_t values = base + stage * stage_bytes;
-        const uint32_t scores = values + value_bytes;
+        const uint32_t scores = values + Shape::value_bytes;
         if (item < proposal_items) {
           ptx::mbarrier_arrive_expect_tx(full_bar + 8U * stage,
-                                         2 * proposal_columns * 128 + score_box_bytes);
-          for (int half = 0; half < 2; ++half)
-            ptx::tma_load_2d(values + half * subtile_bytes, &new_value_map,
-                             slice * 128 + half * 64, staged_row0, full_bar + 8U * stage,
-                             reuse_policy);
+                                         Shape::boxes * proposal_columns * 128 + score_box_bytes);
+          for (int box = 0; box < Shape::boxes; ++box)
+            ptx::tma_load_2d(values + box * Shape::box_bytes, &new_value_map, box * 64, staged_row0,
+                             full_bar + 8U * stage, reuse_policy);
           ptx::tma_load_2d(scores, &score_map, 0, query_row0, full_bar + 8U * stage, reuse_policy);
         } else {
           const int tile = first_tile + item - proposal_items;
           ptx::mbarrier_arrive_expect_tx(full_bar + 8U * stage, stage_bytes);
-          for (int half = 0; half < 2; ++half) {
-            ptx::tma_load_2d(values + half * subtile_bytes, &value_map, slice * 128 + half * 64,
-                             static_cast<int>(cache_row0 + static_cast<long long>(tile) * tile_rows),
-                             full_bar + 8U * stage, stream_policy);
-            ptx::tma_load_2d(scores + half * score_box_bytes, &score_map,
-                             proposal_columns + tile * tile_rows + half * 64, query_row0,
+          for (int box = 0; box < Shape::boxes; ++box)
+            ptx::tma_load_2d(
+                values + box * Shape::box_bytes, &value_map, box * 64,
+                static_cast<int>(cache_row0 + static_cast<long long>(tile) * Shape::stage_keys),
+                full_bar + 8U * stage, stream_policy);
+          for (int box = 0; box < Shape::score_boxes; ++box)
+            ptx::tma_load_2d(scores + box * score_box_bytes, &score_map,
+                             proposal_columns + tile * Shape::stage_keys + box * 64, query_row0,
                              full_bar + 8U * stage, reuse_policy);
-          }
         }
       }
       if (!healthy) {
@@ -374,38 +393,37 @@ pv_tc_kernel(const __grid_constant__ CUtensorMap value_map,
     }
   } else if (warp == 1) {
     if (lane == 0 && items > 0) {
-      bool healthy = true;
       for (int item = 0; item < items; ++item) {
         const int stage = item % stages;
         const uint32_t phase = static_cast<uint32_t>(item / stages) & 1U;
         if (!ptx::mbarrier_wait_bounded(full_bar + 8U * stage, phase)) {
-          healthy = false;
           atomicExch(args.device_error, 22);
           break;
         }
         ptx::tcgen05_fence_after_thread_sync();
         const uint32_t values = base + stage * stage_bytes;
-        const uint32_t scores = values + value_bytes;
-        const int steps = item < proposal_items ? 1 : tile_rows / 16;
+        const uint32_t scores = values + Shape::value_bytes;
+        const int steps = item < proposal_items ? 1 : Shape::stage_keys / 16;
         for (int step = 0; step < steps; ++step) {
-          // 16 keys per instruction: two 8-row swizzle atoms of the V tile (2048 bytes), and 32
+          // 16 keys per instruction: two 8-row swizzle atoms of a V box (2048 bytes), and 32
           // bytes along the key axis of the probability box that holds them.
-          const uint64_t value_desc =
-              umma_desc_mn_major_sw128(values + step * 2048, subtile_bytes);
           const uint64_t score_desc =
               ptx::umma_desc_k_major_sw128(scores + (step / 4) * score_box_bytes) +
               2ULL * (step % 4);
-          ptx::tcgen05_mma_f16(tmem_base, value_desc, score_desc, idesc,
-                               (item > 0 || step > 0) ? 1U : 0U);
+#pragma unroll
+          for (int slice = 0; slice < Shape::slices; ++slice) {
+            const uint64_t value_desc = umma_desc_mn_major_sw128(
+                values + 2 * slice * Shape::box_bytes + step * 2048, Shape::box_bytes);
+            ptx::tcgen05_mma_f16(tmem_base + slice * padded_rows, value_desc, score_desc, idesc,
+                                 (item > 0 || step > 0) ? 1U : 0U);
+          }
         }
         ptx::tcgen05_commit(empty_bar + 8U * stage);
       }
-      (void)healthy;
       ptx::tcgen05_commit(acc_bar);
     }
   } else {
     const int quarter = warp & 3;
-    const int component = slice * 128 + quarter * 32 + lane;
     bool ready = true;
     if (items > 0) {
       ready = __all_sync(0xFFFFFFFFU, ptx::mbarrier_wait_bounded(acc_bar, 0) ? 1 : 0) != 0;
@@ -416,33 +434,38 @@ pv_tc_kernel(const __grid_constant__ CUtensorMap value_map,
     const int width = a.query_heads * dimension;
     const uint32_t lane_address = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll
-    for (int part = 0; part < padded_rows / 16; ++part) {
-      if (part * 16 < rows && ready) {
-        uint32_t values[16];
-        if (items > 0) {
-          ptx::tmem_load_32x32b_x16(lane_address + part * 16, values);
-          ptx::tmem_load_wait();
-        } else {
+    for (int slice = 0; slice < Shape::slices; ++slice) {
+      const int component = slice * 128 + quarter * 32 + lane;
 #pragma unroll
-          for (int index = 0; index < 16; ++index)
-            values[index] = 0U;
-        }
+      for (int part = 0; part < padded_rows / 16; ++part) {
+        if (part * 16 < rows && ready) {
+          uint32_t values[16];
+          if (items > 0) {
+            ptx::tmem_load_32x32b_x16(lane_address + slice * padded_rows + part * 16, values);
+            ptx::tmem_load_wait();
+          } else {
 #pragma unroll
-        for (int index = 0; index < 16; ++index) {
-          const int row = part * 16 + index;
-          if (row < rows) {
-            const int local_head = row / a.depth;
-            const int token = row % a.depth;
-            const size_t out_row = static_cast<size_t>(request) * a.depth + token;
-            const size_t column =
-                static_cast<size_t>(kv_head * group + local_head) * dimension + component;
-            const float value = __uint_as_float(values[index]);
-            if (a.chunks > 1) {
-              a.chunk_partials[(static_cast<size_t>(chunk) * a.requests * a.depth + out_row) * width +
-                               column] = value;
-            } else {
-              static_cast<__nv_bfloat16 *>(a.output)[out_row * width + column] =
-                  __float2bfloat16_rn(value);
+            for (int index = 0; index < 16; ++index)
+              values[index] = 0U;
+          }
+#pragma unroll
+          for (int index = 0; index < 16; ++index) {
+            const int row = part * 16 + index;
+            if (row < rows) {
+              const int local_head = row / a.depth;
+              const int token = row % a.depth;
+              const size_t out_row = static_cast<size_t>(request) * a.depth + token;
+              const size_t column =
+                  static_cast<size_t>(kv_head * group + local_head) * dimension + component;
+              const float value = __uint_as_float(values[index]);
+              if (a.chunks > 1) {
+                a.chunk_partials[(static_cast<size_t>(chunk) * a.requests * a.depth + out_row) *
+                                     width +
+                                 column] = value;
+              } else {
+                static_cast<__nv_bfloat16 *>(a.output)[out_row * width + column] =
+                    __float2bfloat16_rn(value);
+              }
             }
           }
         }
@@ -497,7 +520,8 @@ template <int dimension, int padded_rows>
 int launch_tc(const AttentionArguments &a, int *device_error, cudaStream_t stream) {
   constexpr int score_shared =
       (dimension / 64) * padded_rows * 128 + 2 * 4 * subtile_bytes + 1024;
-  constexpr int pv_shared = 3 * (2 * subtile_bytes + 2 * padded_rows * 128) + 1024;
+  constexpr int pv_shared =
+      pv_stages<dimension, padded_rows>() * pv_stage_bytes<dimension, padded_rows>() + 1024;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(scores_tc_kernel<dimension, padded_rows>,
@@ -519,7 +543,7 @@ int launch_tc(const AttentionArguments &a, int *device_error, cudaStream_t strea
   const int status = launch_attention_softmax(a, stream);
   if (status != 0)
     return status;
-  const dim3 pv_grid(static_cast<unsigned>(a.chunks * (dimension / 128)),
+  const dim3 pv_grid(static_cast<unsigned>(a.chunks),
                      static_cast<unsigned>(a.kv_heads), static_cast<unsigned>(a.requests));
   pv_tc_kernel<dimension, padded_rows><<<pv_grid, tc_threads, pv_shared, stream>>>(
       maps.values, staged ? maps.new_values : maps.values, maps.scores, arguments);
@@ -554,7 +578,7 @@ int make_attention_maps(AttentionMaps *maps, const void *key_cache, const void *
   AttentionMaps result{};
   result.padded_rows = padded_rows;
   if (!encode_bf16_rows(&result.keys, key_cache, cache_rows, head_dim, tile_rows) ||
-      !encode_bf16_rows(&result.values, value_cache, cache_rows, head_dim, tile_rows) ||
+      !encode_bf16_rows(&result.values, value_cache, cache_rows, head_dim, 32768 / head_dim) ||
       !encode_bf16_rows(&result.queries, queries, query_rows, head_dim, padded_rows) ||
       !encode_bf16_rows(&result.scores, scores, score_rows, score_stride, padded_rows)) {
     return -5;

@@ -8,7 +8,7 @@ namespace carat_b200 {
 
 struct AttentionMaps {
   CUtensorMap keys;        // cache K as [slots * kv_heads * capacity, head_dim], box 128 rows
-  CUtensorMap values;      // cache V, same view and box
+  CUtensorMap values;      // cache V, same view, box 128 rows (head_dim 256) or 64 rows (512)
   CUtensorMap new_keys;    // staged proposals as [requests * kv_heads * depth, head_dim], box 16 rows
   CUtensorMap new_values;
   CUtensorMap queries;     // [query rows, head_dim], box padded_rows rows

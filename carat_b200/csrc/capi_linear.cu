@@ -35,18 +35,7 @@ extern "C" int carat_b200_device_error(int *code) { return read_and_clear_device
 
 extern "C" size_t carat_b200_fp8_linear_workspace_bytes(int rows, int input_width,
                                                         int output_width) {
-  if (rows <= 0 || rows > 128 || input_width <= 0 || output_width <= 0)
-    return 0;
-  // Same split choice as make_linear_plan, without touching tensor maps.
-  const int tiles = (output_width + 127) / 128;
-  const int k_blocks = (input_width + 127) / 128;
-  int splits = tiles >= 120 ? 1 : 148 / tiles;
-  splits = splits < 1 ? 1 : splits;
-  const int most = k_blocks / 4 < 1 ? 1 : k_blocks / 4;
-  splits = splits > most ? most : splits;
-  const int per_split = (k_blocks + splits - 1) / splits;
-  splits = (k_blocks + per_split - 1) / per_split;
-  return splits <= 1 ? 0 : sizeof(float) * static_cast<size_t>(splits) * rows * output_width;
+  return linear_partial_bytes_for(rows, input_width, output_width);
 }
 
 extern "C" int carat_b200_fp8_linear(const void *fp8_input, const float *device_input_scale,
@@ -89,6 +78,7 @@ extern "C" int carat_b200_fp8_linear_argmax(const void *fp8_input, const float *
     return -1;
   }
   LinearPlan plan;
+  // One piece per tile: the LM head has thousands of tiles, the tail round needs no cutting.
   int status = plan_or_fail(&plan, fp8_input, fp8_weight, rows, input_width, output_width, 1);
   if (status != 0)
     return status;

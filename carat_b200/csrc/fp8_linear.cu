@@ -39,14 +39,33 @@ struct KernelArguments {
   const float *input_scale;
   const float *weight_scale;
   __nv_bfloat16 *output;
-  float *partial;
-  unsigned long long *best;
+  float *partial;             // mode 1: [splits, rows, output_width]
+  unsigned long long *best;   // mode 2
   int *device_error;
   int rows;
   int output_width;
+  int tiles;
   int k_blocks;
+  int splits;                 // K pieces per tile (1 unless mode 1)
   int k_blocks_per_split;
 };
+
+struct WorkItem {
+  int tile;
+  int piece;
+  int k_begin;
+  int k_count;
+};
+
+// Items are numbered piece-major so that the pieces of one tile land on different CTAs.
+__device__ __forceinline__ WorkItem decode_item(const KernelArguments &args, int index) {
+  WorkItem item;
+  item.tile = index % args.tiles;
+  item.piece = index / args.tiles;
+  item.k_begin = item.piece * args.k_blocks_per_split;
+  item.k_count = min(args.k_blocks, item.k_begin + args.k_blocks_per_split) - item.k_begin;
+  return item;
+}
 
 __device__ __forceinline__ unsigned int orderable_bf16(float rounded) {
   // Monotonic map of a bf16-representable float to 16 bits; NaN sorts below everything, matching
@@ -57,6 +76,46 @@ __device__ __forceinline__ unsigned int orderable_bf16(float rounded) {
   return (bits & 0x8000U) ? (~bits & 0xFFFFU) : (bits | 0x8000U);
 }
 
+// Finishes 32 accumulator columns (activation rows chunk*32 ..) of one feature.
+template <int mode>
+__device__ __forceinline__ void finish_chunk(const KernelArguments &args, const float (&values)[32],
+                                             int chunk, int feature, int feature_base, int lane,
+                                             float scale, unsigned long long *row_best) {
+  if constexpr (mode == 0) {
+    if (feature < args.output_width) {
+#pragma unroll
+      for (int column = 0; column < 32; ++column) {
+        const int row = chunk * 32 + column;
+        if (row < args.rows)
+          args.output[static_cast<size_t>(row) * args.output_width + feature] =
+              __float2bfloat16_rn(values[column] * scale);
+      }
+    }
+  } else {
+    unsigned long long chunk_best = 0ULL;
+#pragma unroll
+    for (int column = 0; column < 32; ++column) {
+      const float rounded = __bfloat162float(__float2bfloat16_rn(values[column] * scale));
+      // Out-of-range features lose to everything; ties inside the warp go to the lowest lane,
+      // which is the lowest feature index.
+      const unsigned int key =
+          feature < args.output_width
+              ? ((orderable_bf16(rounded) + 1U) << 8) | static_cast<unsigned int>(31 - lane)
+              : 0U;
+      const unsigned int winner = __reduce_max_sync(0xFFFFFFFFU, key);
+      if (lane == column && winner != 0U) {
+        const unsigned int winner_feature =
+            static_cast<unsigned int>(feature_base) + (31U - (winner & 31U));
+        chunk_best = (static_cast<unsigned long long>(winner >> 8) << 32) |
+                     static_cast<unsigned long long>(~winner_feature);
+      }
+    }
+    const int row = chunk * 32 + lane;
+    if (row < args.rows && chunk_best != 0ULL)
+      atomicMax(&row_best[row], chunk_best);
+  }
+}
+
 template <int padded_rows, int mode>
 __global__ void __launch_bounds__(linear_threads, 1)
 fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
@@ -65,9 +124,10 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
   constexpr int input_tile_bytes = padded_rows * tile_k_bytes;
   constexpr uint32_t stage_bytes = weight_tile_bytes + input_tile_bytes;
   constexpr uint32_t idesc = ptx::umma_idesc(0, 0, tile_features, padded_rows);
+  constexpr uint32_t tmem_columns = 2 * padded_rows < 32 ? 32 : 2 * padded_rows;
 
   extern __shared__ unsigned char shared_raw[];
-  __shared__ __align__(8) unsigned long long barriers[2 * stages + 1];
+  __shared__ __align__(8) unsigned long long barriers[2 * stages + 4];
   __shared__ uint32_t tmem_base_slot;
   __shared__ unsigned long long row_best[mode == 2 ? padded_rows : 1];
 
@@ -76,22 +136,24 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
   const uint32_t input_tiles = tiles_base + stages * weight_tile_bytes;
   const uint32_t full_bar = ptx::smem_u32(&barriers[0]);
   const uint32_t empty_bar = ptx::smem_u32(&barriers[stages]);
-  const uint32_t accum_bar = ptx::smem_u32(&barriers[2 * stages]);
+  const uint32_t acc_full_bar = ptx::smem_u32(&barriers[2 * stages]);
+  const uint32_t acc_empty_bar = ptx::smem_u32(&barriers[2 * stages + 2]);
 
   const int warp = static_cast<int>(threadIdx.x) / 32;
   const int lane = static_cast<int>(threadIdx.x) & 31;
-  const int tile = static_cast<int>(blockIdx.x);
-  const int split = static_cast<int>(blockIdx.y);
-  const int k_begin = split * args.k_blocks_per_split;
-  const int k_end = min(args.k_blocks, k_begin + args.k_blocks_per_split);
-  const int k_count = k_end - k_begin;
+  const int items = args.tiles * args.splits;
+  const int first_item = static_cast<int>(blockIdx.x);
+  const int item_stride = static_cast<int>(gridDim.x);
 
   if (threadIdx.x == 0) {
     for (int stage = 0; stage < stages; ++stage) {
       ptx::mbarrier_init(full_bar + 8U * stage, 1);
       ptx::mbarrier_init(empty_bar + 8U * stage, 1);
     }
-    ptx::mbarrier_init(accum_bar, 1);
+    for (int buffer = 0; buffer < 2; ++buffer) {
+      ptx::mbarrier_init(acc_full_bar + 8U * buffer, 1);
+      ptx::mbarrier_init(acc_empty_bar + 8U * buffer, 4);
+    }
     ptx::fence_mbarrier_init();
     ptx::prefetch_tensormap(&weight_map);
     ptx::prefetch_tensormap(&input_map);
@@ -101,7 +163,7 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
       row_best[row] = 0ULL;
   }
   if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(&tmem_base_slot), padded_rows);
+    ptx::tmem_alloc(ptx::smem_u32(&tmem_base_slot), tmem_columns);
     ptx::tmem_relinquish_alloc_permit();
   }
   ptx::tcgen05_fence_before_thread_sync();
@@ -115,136 +177,142 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
       const uint64_t reuse_policy = ptx::policy_evict_last();
       int issued = 0;
       bool healthy = true;
-      for (int block = 0; block < k_count; ++block) {
-        const int stage = block % stages;
-        const uint32_t phase = static_cast<uint32_t>(block / stages) & 1U;
-        if (!ptx::mbarrier_wait_bounded(empty_bar + 8U * stage, phase ^ 1U)) {
-          healthy = false;
-          atomicExch(args.device_error, 1);
-          break;
+      for (int index = first_item; index < items && healthy; index += item_stride) {
+        const WorkItem item = decode_item(args, index);
+        for (int block = 0; block < item.k_count; ++block, ++issued) {
+          const int stage = issued % stages;
+          const uint32_t phase = static_cast<uint32_t>(issued / stages) & 1U;
+          if (!ptx::mbarrier_wait_bounded(empty_bar + 8U * stage, phase ^ 1U)) {
+            healthy = false;
+            atomicExch(args.device_error, 1);
+            break;
+          }
+          ptx::mbarrier_arrive_expect_tx(full_bar + 8U * stage, stage_bytes);
+          const int k_byte = (item.k_begin + block) * tile_k_bytes;
+          ptx::tma_load_2d(weight_tiles + stage * weight_tile_bytes, &weight_map, k_byte,
+                           item.tile * tile_features, full_bar + 8U * stage, stream_policy);
+          ptx::tma_load_2d(input_tiles + stage * input_tile_bytes, &input_map, k_byte, 0,
+                           full_bar + 8U * stage, reuse_policy);
         }
-        ptx::mbarrier_arrive_expect_tx(full_bar + 8U * stage, stage_bytes);
-        const int k_byte = (k_begin + block) * tile_k_bytes;
-        ptx::tma_load_2d(weight_tiles + stage * weight_tile_bytes, &weight_map, k_byte,
-                         tile * tile_features, full_bar + 8U * stage, stream_policy);
-        ptx::tma_load_2d(input_tiles + stage * input_tile_bytes, &input_map, k_byte, 0,
-                         full_bar + 8U * stage, reuse_policy);
-        ++issued;
       }
       if (!healthy) {
         // Let copies already in flight land before the CTA gives its shared memory back.
         const int first = issued > stages ? issued - stages : 0;
-        for (int block = first; block < issued; ++block) {
+        for (int block = first; block < issued; ++block)
           ptx::mbarrier_wait_bounded(full_bar + 8U * (block % stages),
                                      static_cast<uint32_t>(block / stages) & 1U);
-        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      int consumed = 0;
+      int local = 0;
       bool healthy = true;
-      for (int block = 0; block < k_count; ++block) {
-        const int stage = block % stages;
-        const uint32_t phase = static_cast<uint32_t>(block / stages) & 1U;
-        if (!ptx::mbarrier_wait_bounded(full_bar + 8U * stage, phase)) {
-          healthy = false;
-          atomicExch(args.device_error, 2);
+      for (int index = first_item; index < items && healthy; index += item_stride, ++local) {
+        const WorkItem item = decode_item(args, index);
+        const int buffer = local & 1;
+        const uint32_t use = static_cast<uint32_t>(local >> 1);
+        if (!ptx::mbarrier_wait_bounded(acc_empty_bar + 8U * buffer, (use & 1U) ^ 1U)) {
+          atomicExch(args.device_error, 4);
           break;
         }
         ptx::tcgen05_fence_after_thread_sync();
-        const uint64_t weight_desc =
-            ptx::umma_desc_k_major_sw128(weight_tiles + stage * weight_tile_bytes);
-        const uint64_t input_desc =
-            ptx::umma_desc_k_major_sw128(input_tiles + stage * input_tile_bytes);
+        for (int block = 0; block < item.k_count; ++block, ++consumed) {
+          const int stage = consumed % stages;
+          const uint32_t phase = static_cast<uint32_t>(consumed / stages) & 1U;
+          if (!ptx::mbarrier_wait_bounded(full_bar + 8U * stage, phase)) {
+            healthy = false;
+            atomicExch(args.device_error, 2);
+            break;
+          }
+          ptx::tcgen05_fence_after_thread_sync();
+          const uint64_t weight_desc =
+              ptx::umma_desc_k_major_sw128(weight_tiles + stage * weight_tile_bytes);
+          const uint64_t input_desc =
+              ptx::umma_desc_k_major_sw128(input_tiles + stage * input_tile_bytes);
 #pragma unroll
-        for (int step = 0; step < tile_k_bytes / umma_k; ++step) {
-          // +32 bytes along K inside the swizzle atom = +2 in the 16-byte address field.
-          ptx::tcgen05_mma_f8f6f4(tmem_base, weight_desc + 2ULL * step, input_desc + 2ULL * step,
-                                  idesc, (block > 0 || step > 0) ? 1U : 0U);
+          for (int step = 0; step < tile_k_bytes / umma_k; ++step) {
+            // +32 bytes along K inside the swizzle atom = +2 in the 16-byte address field.
+            ptx::tcgen05_mma_f8f6f4(tmem_base + buffer * padded_rows, weight_desc + 2ULL * step,
+                                    input_desc + 2ULL * step, idesc,
+                                    (block > 0 || step > 0) ? 1U : 0U);
+          }
+          ptx::tcgen05_commit(empty_bar + 8U * stage);
         }
-        ptx::tcgen05_commit(empty_bar + 8U * stage);
+        if (healthy)
+          ptx::tcgen05_commit(acc_full_bar + 8U * buffer);
       }
-      // Arrives once every MMA above has retired (also on the unhealthy path, so that the
-      // epilogue warps leave their wait promptly).
-      (void)healthy;
-      ptx::tcgen05_commit(accum_bar);
     }
   } else {
     const int quarter = warp & 3;  // TMEM lane group this warp may read
-    const int feature = tile * tile_features + quarter * 32 + lane;
-    const bool accum_ready =
-        __all_sync(0xFFFFFFFFU, ptx::mbarrier_wait_bounded(accum_bar, 0) ? 1 : 0) != 0;
-    if (!accum_ready && lane == 0)
-      atomicExch(args.device_error, 3);
-    ptx::tcgen05_fence_after_thread_sync();
-    const uint32_t lane_address = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    [[maybe_unused]] const int epilogue_thread = (warp - 2) * 32 + lane;
     float scale = 1.0F;
     if constexpr (mode != 1)
       scale = args.input_scale[0] * args.weight_scale[0];
+    int local = 0;
+    for (int index = first_item; index < items; index += item_stride, ++local) {
+      const WorkItem item = decode_item(args, index);
+      const int buffer = local & 1;
+      const uint32_t use = static_cast<uint32_t>(local >> 1);
+      const bool ready =
+          __all_sync(0xFFFFFFFFU,
+                     ptx::mbarrier_wait_bounded(acc_full_bar + 8U * buffer, use & 1U) ? 1 : 0) != 0;
+      if (!ready) {
+        if (lane == 0)
+          atomicExch(args.device_error, 3);
+        break;
+      }
+      ptx::tcgen05_fence_after_thread_sync();
+      const int feature = item.tile * tile_features + quarter * 32 + lane;
+      const int feature_base = item.tile * tile_features + quarter * 32;
+      const uint32_t lane_address =
+          tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buffer * padded_rows;
 #pragma unroll
-    for (int chunk = 0; chunk < padded_rows / 32; ++chunk) {
-      if (chunk * 32 < args.rows && accum_ready) {  // warp-uniform
-        uint32_t values[32];
-        ptx::tmem_load_32x32b_x32(lane_address + chunk * 32, values);
-        ptx::tmem_load_wait();
-        if constexpr (mode == 0) {
-          if (feature < args.output_width) {
+      for (int chunk = 0; chunk < padded_rows / 32; ++chunk) {
+        if (chunk * 32 < args.rows) {  // warp-uniform
+          uint32_t raw[32];
+          ptx::tmem_load_32x32b_x32(lane_address + chunk * 32, raw);
+          ptx::tmem_load_wait();
+          if constexpr (mode == 1) {
+            if (feature < args.output_width) {
+              float *destination = args.partial +
+                                   static_cast<size_t>(item.piece) * args.rows * args.output_width +
+                                   feature;
 #pragma unroll
-            for (int column = 0; column < 32; ++column) {
-              const int row = chunk * 32 + column;
-              if (row < args.rows) {
-                args.output[static_cast<size_t>(row) * args.output_width + feature] =
-                    __float2bfloat16_rn(__uint_as_float(values[column]) * scale);
+              for (int column = 0; column < 32; ++column) {
+                const int row = chunk * 32 + column;
+                if (row < args.rows)
+                  destination[static_cast<size_t>(row) * args.output_width] =
+                      __uint_as_float(raw[column]);
               }
             }
-          }
-        } else if constexpr (mode == 1) {
-          if (feature < args.output_width) {
-            float *destination =
-                args.partial + static_cast<size_t>(split) * args.rows * args.output_width + feature;
+          } else {
+            float values[32];
 #pragma unroll
-            for (int column = 0; column < 32; ++column) {
-              const int row = chunk * 32 + column;
-              if (row < args.rows)
-                destination[static_cast<size_t>(row) * args.output_width] =
-                    __uint_as_float(values[column]);
-            }
+            for (int column = 0; column < 32; ++column)
+              values[column] = __uint_as_float(raw[column]);
+            finish_chunk<mode>(args, values, chunk, feature, feature_base, lane, scale, row_best);
           }
-        } else {
-          unsigned long long chunk_best = 0ULL;
-#pragma unroll
-          for (int column = 0; column < 32; ++column) {
-            const float rounded = __bfloat162float(
-                __float2bfloat16_rn(__uint_as_float(values[column]) * scale));
-            // Out-of-range features lose to everything; ties inside the warp go to the lowest
-            // lane, which is the lowest feature index.
-            const unsigned int key =
-                feature < args.output_width
-                    ? ((orderable_bf16(rounded) + 1U) << 8) | static_cast<unsigned int>(31 - lane)
-                    : 0U;
-            const unsigned int winner = __reduce_max_sync(0xFFFFFFFFU, key);
-            if (lane == column && winner != 0U) {
-              const unsigned int winner_lane = 31U - (winner & 31U);
-              const unsigned int winner_feature =
-                  static_cast<unsigned int>(tile * tile_features + quarter * 32) + winner_lane;
-              chunk_best = (static_cast<unsigned long long>(winner >> 8) << 32) |
-                           static_cast<unsigned long long>(~winner_feature);
-            }
-          }
-          const int row = chunk * 32 + lane;
-          if (row < args.rows && chunk_best != 0ULL)
-            atomicMax(&row_best[row], chunk_best);
         }
       }
-    }
-    if constexpr (mode == 2) {
-      // Combine the four feature quarters in shared memory, then one global atomic per row.
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      const int row = (warp - 2) * 32 + lane;
-      if (row < args.rows && row < padded_rows) {
-        const unsigned long long candidate = row_best[row];
-        if (candidate != 0ULL)
-          atomicMax(args.best + row, candidate);
+      // The accumulator buffer is free again as soon as its values are in registers.
+      ptx::tcgen05_fence_before_thread_sync();
+      __syncwarp();
+      if (lane == 0)
+        ptx::mbarrier_arrive(acc_empty_bar + 8U * buffer);
+
+      if constexpr (mode == 2) {
+        {
+          // Combine the four feature quarters in shared memory, then one global atomic per row.
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (epilogue_thread < args.rows && epilogue_thread < padded_rows) {
+            const unsigned long long candidate = row_best[epilogue_thread];
+            if (candidate != 0ULL)
+              atomicMax(args.best + epilogue_thread, candidate);
+            row_best[epilogue_thread] = 0ULL;
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
       }
     }
   }
@@ -253,7 +321,7 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
   __syncthreads();
   if (warp == 1) {
     ptx::tcgen05_fence_after_thread_sync();
-    ptx::tmem_dealloc(tmem_base, padded_rows);
+    ptx::tmem_dealloc(tmem_base, tmem_columns);
   }
 }
 
@@ -342,8 +410,9 @@ int launch_variant(const LinearPlan &plan, const KernelArguments &arguments, cud
   });
   if (configure_status != cudaSuccess)
     return -10;
-  const dim3 grid(static_cast<unsigned>(plan.tiles), static_cast<unsigned>(plan.splits));
-  fp8_linear_kernel<padded_rows, mode><<<grid, linear_threads, dynamic_bytes, stream>>>(
+  const int items = plan.tiles * arguments.splits;
+  const int ctas = items < plan.ctas ? items : plan.ctas;
+  fp8_linear_kernel<padded_rows, mode><<<ctas, linear_threads, dynamic_bytes, stream>>>(
       plan.weight_map, plan.input_map, arguments);
   return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
 }
@@ -362,17 +431,65 @@ int launch_mode(const LinearPlan &plan, const KernelArguments &arguments, cudaSt
   }
 }
 
-KernelArguments base_arguments(const LinearPlan &plan, int *device_error) {
+// `split` false: one piece per tile whatever the plan says (bf16 store and argmax epilogues).
+KernelArguments base_arguments(const LinearPlan &plan, int *device_error, bool split) {
   KernelArguments arguments{};
   arguments.device_error = device_error;
   arguments.rows = plan.rows;
   arguments.output_width = plan.output_width;
+  arguments.tiles = plan.tiles;
   arguments.k_blocks = plan.k_blocks;
-  arguments.k_blocks_per_split = plan.k_blocks_per_split;
+  arguments.splits = split ? plan.splits : 1;
+  arguments.k_blocks_per_split = split ? plan.k_blocks_per_split : plan.k_blocks;
   return arguments;
 }
 
+int multiprocessor_count() {
+  static int count = [] {
+    int device = 0;
+    int value = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        value <= 0) {
+      return 148;
+    }
+    return value;
+  }();
+  return count;
+}
+
+void schedule_linear(LinearPlan *plan, int rows, int input_width, int output_width,
+                     int requested_splits) {
+  LinearPlan &result = *plan;
+  result.rows = rows;
+  result.input_width = input_width;
+  result.output_width = output_width;
+  result.padded_rows = rows <= 32 ? 32 : rows <= 64 ? 64 : 128;
+  result.tiles = (output_width + tile_features - 1) / tile_features;
+  result.k_blocks = (input_width + tile_k_bytes - 1) / tile_k_bytes;
+  result.ctas = multiprocessor_count();
+  int splits = requested_splits;
+  if (splits <= 0) {
+    // Fewer tiles than SMs: cut K so that most SMs stream; keep at least four K blocks a piece.
+    splits = result.tiles >= result.ctas ? 1 : result.ctas / result.tiles;
+    const int most = result.k_blocks / 4 < 1 ? 1 : result.k_blocks / 4;
+    splits = splits > most ? most : splits;
+  }
+  if (splits > result.k_blocks)
+    splits = result.k_blocks;
+  result.k_blocks_per_split = (result.k_blocks + splits - 1) / splits;
+  result.splits = (result.k_blocks + result.k_blocks_per_split - 1) / result.k_blocks_per_split;
+}
+
 } // namespace
+
+std::size_t linear_partial_bytes_for(int rows, int input_width, int output_width) {
+  if (rows <= 0 || rows > 128 || input_width <= 0 || output_width <= 0)
+    return 0;
+  LinearPlan plan{};
+  schedule_linear(&plan, rows, input_width, output_width, 0);
+  return linear_partial_bytes(plan);
+}
 
 int make_linear_plan(LinearPlan *plan, const void *fp8_input, const void *fp8_weight, int rows,
                      int input_width, int output_width, int requested_splits, const char **error) {
@@ -394,24 +511,7 @@ int make_linear_plan(LinearPlan *plan, const void *fp8_input, const void *fp8_we
     return fail("FP8 linear operands must be 16-byte aligned", -4);
   }
   LinearPlan result{};
-  result.rows = rows;
-  result.input_width = input_width;
-  result.output_width = output_width;
-  result.padded_rows = rows <= 32 ? 32 : rows <= 64 ? 64 : 128;
-  result.tiles = (output_width + tile_features - 1) / tile_features;
-  result.k_blocks = (input_width + tile_k_bytes - 1) / tile_k_bytes;
-  int splits = requested_splits;
-  if (splits <= 0) {
-    // Fill the 148 SMs when there are few feature tiles; keep at least four K blocks per split.
-    splits = result.tiles >= 120 ? 1 : 148 / result.tiles;
-    splits = splits < 1 ? 1 : splits;
-    const int most = result.k_blocks / 4 < 1 ? 1 : result.k_blocks / 4;
-    splits = splits > most ? most : splits;
-  }
-  if (splits > result.k_blocks)
-    splits = result.k_blocks;
-  result.k_blocks_per_split = (result.k_blocks + splits - 1) / splits;
-  result.splits = (result.k_blocks + result.k_blocks_per_split - 1) / result.k_blocks_per_split;
+  schedule_linear(&result, rows, input_width, output_width, requested_splits);
   if (!encode_byte_matrix(&result.weight_map, fp8_weight, static_cast<uint64_t>(input_width),
                           static_cast<uint64_t>(output_width), tile_features) ||
       !encode_byte_matrix(&result.input_map, fp8_input, static_cast<uint64_t>(input_width),
@@ -430,27 +530,29 @@ std::size_t linear_partial_bytes(const LinearPlan &plan) {
 
 int launch_linear_bf16(const LinearPlan &plan, const float *input_scale, const float *weight_scale,
                        void *bf16_output, float *partial, int *device_error, cudaStream_t stream) {
-  KernelArguments arguments = base_arguments(plan, device_error);
-  arguments.input_scale = input_scale;
-  arguments.weight_scale = weight_scale;
-  arguments.output = static_cast<__nv_bfloat16 *>(bf16_output);
-  arguments.partial = partial;
-  if (plan.splits == 1)
+  if (plan.splits == 1) {
+    KernelArguments arguments = base_arguments(plan, device_error, false);
+    arguments.input_scale = input_scale;
+    arguments.weight_scale = weight_scale;
+    arguments.output = static_cast<__nv_bfloat16 *>(bf16_output);
     return launch_mode<0>(plan, arguments, stream);
-  if (partial == nullptr)
-    return -13;
-  const int status = launch_mode<1>(plan, arguments, stream);
+  }
+  const int status = launch_linear_partial(plan, partial, device_error, stream);
   if (status != 0)
     return status;
-  return launch_finalize_split_k(partial, input_scale, weight_scale, bf16_output, plan.splits,
-                                 plan.rows, plan.output_width, stream);
+  const size_t elements = static_cast<size_t>(plan.rows) * plan.output_width;
+  const int blocks = static_cast<int>((elements + 255) / 256);
+  finalize_split_k_kernel<<<blocks < 1184 ? blocks : 1184, 256, 0, stream>>>(
+      partial, input_scale, weight_scale, static_cast<__nv_bfloat16 *>(bf16_output), plan.splits,
+      elements);
+  return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
 }
 
 int launch_linear_partial(const LinearPlan &plan, float *partial, int *device_error,
                           cudaStream_t stream) {
   if (partial == nullptr)
     return -13;
-  KernelArguments arguments = base_arguments(plan, device_error);
+  KernelArguments arguments = base_arguments(plan, device_error, true);
   arguments.partial = partial;
   return launch_mode<1>(plan, arguments, stream);
 }
@@ -458,24 +560,13 @@ int launch_linear_partial(const LinearPlan &plan, float *partial, int *device_er
 int launch_linear_argmax(const LinearPlan &plan, const float *input_scale,
                          const float *weight_scale, unsigned long long *best, int *device_error,
                          cudaStream_t stream) {
-  if (plan.splits != 1 || best == nullptr)
+  if (best == nullptr)
     return -14;
-  KernelArguments arguments = base_arguments(plan, device_error);
+  KernelArguments arguments = base_arguments(plan, device_error, false);
   arguments.input_scale = input_scale;
   arguments.weight_scale = weight_scale;
   arguments.best = best;
   return launch_mode<2>(plan, arguments, stream);
-}
-
-int launch_finalize_split_k(const float *partial, const float *input_scale,
-                            const float *weight_scale, void *bf16_output, int splits, int rows,
-                            int output_width, cudaStream_t stream) {
-  const size_t elements = static_cast<size_t>(rows) * output_width;
-  const int blocks = static_cast<int>((elements + 255) / 256);
-  finalize_split_k_kernel<<<blocks < 1184 ? blocks : 1184, 256, 0, stream>>>(
-      partial, input_scale, weight_scale, static_cast<__nv_bfloat16 *>(bf16_output), splits,
-      elements);
-  return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
 }
 
 int launch_unpack_best(const unsigned long long *best, int *tokens, int rows,

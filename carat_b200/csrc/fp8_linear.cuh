@@ -9,15 +9,12 @@
 
 namespace carat_b200 {
 
-// How the accumulator tile leaves the kernel.
-enum class LinearEpilogue : int {
-  bf16 = 0,     // y[row, n] = bf16(acc * x_scale * w_scale)
-  partial = 1,  // split-K: fp32 partial sums, finished by finalize_split_k or a fused consumer
-  argmax = 2,   // per-row argmax of bf16(acc * scale); logits never reach memory
-};
-
 // One launch description. Tensor maps are encoded once (weights and activation buffers of the
 // runner never move) and captured by value into the kernel parameters.
+//
+// The kernel is persistent: at most `ctas` CTAs (one per SM) walk the list of work items
+// (128-feature tile x K piece), so barrier set-up, TMEM allocation and pipeline fill are paid once
+// per CTA and a tile's epilogue overlaps the next tile's loads (two TMEM accumulators).
 struct LinearPlan {
   CUtensorMap weight_map;
   CUtensorMap input_map;
@@ -26,42 +23,42 @@ struct LinearPlan {
   int output_width{0};
   int padded_rows{0};       // UMMA N: 32, 64 or 128
   int tiles{0};             // output-feature tiles of 128
-  int splits{1};            // split-K factor
   int k_blocks{0};          // 128-byte K blocks
+  int ctas{0};              // persistent CTAs (multiprocessor count)
+  int splits{1};            // K pieces per tile when there are fewer tiles than SMs
   int k_blocks_per_split{0};
 };
 
 // Returns 0 or a negative error; `error` (may be null) receives a static message.
+// requested_splits <= 0 picks the split factor automatically.
 int make_linear_plan(LinearPlan *plan, const void *fp8_input, const void *fp8_weight, int rows,
                      int input_width, int output_width, int requested_splits, const char **error);
 
-// Bytes of fp32 scratch a plan needs when it runs as split-K (0 when splits == 1).
+// Bytes of fp32 scratch a plan needs when it splits K (0 when splits == 1):
+// [splits, rows, output_width].
 std::size_t linear_partial_bytes(const LinearPlan &plan);
 
-// bf16 epilogue; when plan.splits > 1 the kernel writes fp32 partials into `partial` and a second
-// kernel sums, scales and rounds them into `output`.
+// The same figure from the shape alone (no tensor maps, usable without a device).
+std::size_t linear_partial_bytes_for(int rows, int input_width, int output_width);
+
+// y[row, n] = bf16(acc * x_scale * w_scale). When plan.splits > 1 the kernel writes fp32 partial
+// sums into `partial` and a second kernel sums, scales and rounds them into `output`.
 int launch_linear_bf16(const LinearPlan &plan, const float *input_scale, const float *weight_scale,
                        void *bf16_output, float *partial, int *device_error, cudaStream_t stream);
 
-// Split-K only: leaves the unscaled fp32 partials [splits, rows, output_width] for a consumer that
-// sums them itself.
+// Leaves the unscaled fp32 partial sums [splits, rows, output_width] for a consumer that sums them.
 int launch_linear_partial(const LinearPlan &plan, float *partial, int *device_error,
                           cudaStream_t stream);
 
-// Argmax epilogue. `best` holds one packed 64-bit key per row and must be zero before the launch:
-// (orderable bf16 logit << 32) | ~index, combined with atomicMax, so equal logits keep the lowest
-// index. unpack with best_index().
+// Argmax epilogue (always one piece per tile). `best` holds one packed 64-bit key per row and must
+// be zero before the launch: (orderable bf16 logit << 32) | ~index, combined with atomicMax, so
+// equal logits keep the lowest index. Unpack with best_index().
 int launch_linear_argmax(const LinearPlan &plan, const float *input_scale,
                          const float *weight_scale, unsigned long long *best, int *device_error,
                          cudaStream_t stream);
 
 // tokens[row] = index stored in best[row].
 int launch_unpack_best(const unsigned long long *best, int *tokens, int rows, cudaStream_t stream);
-
-// Sums split-K partials, applies the scale product and rounds to bf16.
-int launch_finalize_split_k(const float *partial, const float *input_scale,
-                            const float *weight_scale, void *bf16_output, int splits, int rows,
-                            int output_width, cudaStream_t stream);
 
 // Plain one-thread-per-output kernel with the same contract as the bf16 epilogue. It exists so the
 // tensor-core kernel can be cross-checked on the device at full size; nothing on the step path

@@ -167,7 +167,7 @@ struct carat_b200_runner {
   DeviceBuffer scores;
   DeviceBuffer projected;    // bf16 output of a linear that did not split K
   DeviceBuffer gate_up;
-  DeviceBuffer split_partials;
+  DeviceBuffer split_partials;  // fp32 [splits, rows, width] left for a fused consumer
   DeviceBuffer scratch_words;  // [amax words | argmax keys]
   DeviceBuffer scales;
   DeviceBuffer step_inputs;    // tokens, positions, slots, target_first, caps

@@ -1,0 +1,90 @@
+"""Small, self-ending workloads for profiler captures (one kernel family each, a few launches,
+inputs larger than the 126 MB L2 but well under a few GB on the device).
+
+    python -m carat_b200.profile_cases linear      # FP8 linear 120 x 5376 -> 43008 (231 MB weights)
+    python -m carat_b200.profile_cases lm_head     # fused LM head 120 x 5376 -> 262144 (1.4 GB)
+    python -m carat_b200.profile_cases attention   # sliding verify attention, 24 slots, full ring
+    python -m carat_b200.profile_cases global      # global verify attention, 24 slots, 4096 context
+"""
+from __future__ import annotations
+
+import ctypes
+import sys
+
+import torch
+
+from . import capi
+from .capi import check
+
+
+def _ptr(tensor):
+    return ctypes.c_void_p(tensor.data_ptr()) if tensor is not None else None
+
+
+def _fp8(rows, cols, seed):
+    generator = torch.Generator(device="cuda").manual_seed(seed)
+    return torch.randint(0, 120, (rows, cols), dtype=torch.uint8, device="cuda", generator=generator)
+
+
+def linear(rows=120, k=5376, n=43008, launches=4):
+    library = capi.library()
+    x, w = _fp8(rows, k, 0), _fp8(n, k, 1)
+    scale = torch.full((1,), 0.01, dtype=torch.float32, device="cuda")
+    out = torch.empty(rows, n, dtype=torch.bfloat16, device="cuda")
+    need = library.carat_b200_fp8_linear_workspace_bytes(rows, k, n)
+    work = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    for _ in range(launches):
+        check(library.carat_b200_fp8_linear(_ptr(x), _ptr(scale), _ptr(w), _ptr(scale), _ptr(out),
+                                            rows, k, n, _ptr(work), need, None))
+    torch.cuda.synchronize()
+
+
+def lm_head(rows=120, k=5376, n=262144, launches=3):
+    library = capi.library()
+    x, w = _fp8(rows, k, 0), _fp8(n, k, 1)
+    scale = torch.full((1,), 0.01, dtype=torch.float32, device="cuda")
+    tokens = torch.empty(rows, dtype=torch.int32, device="cuda")
+    keys = torch.empty(rows, dtype=torch.int64, device="cuda")
+    for _ in range(launches):
+        check(library.carat_b200_fp8_linear_argmax(_ptr(x), _ptr(scale), _ptr(w), _ptr(scale),
+                                                   _ptr(tokens), _ptr(keys), rows, k, n, None))
+    torch.cuda.synchronize()
+
+
+def attention(head_dim=256, heads=32, kv_heads=16, window=1024, capacity=1024, position=3000,
+              requests=24, depth=5, launches=3):
+    library = capi.library()
+    generator = torch.Generator(device="cuda").manual_seed(0)
+
+    def normal(*shape):
+        return (torch.randn(*shape, device="cuda", generator=generator) * 0.3).to(torch.bfloat16)
+
+    queries = normal(requests, heads, depth, head_dim)
+    keys = normal(requests, kv_heads, capacity, head_dim)
+    values = normal(requests, kv_heads, capacity, head_dim)
+    staged = window > 0
+    new_keys = normal(requests, kv_heads, depth, head_dim) if staged else None
+    new_values = normal(requests, kv_heads, depth, head_dim) if staged else None
+    rows = min(position, capacity) if staged else position + depth
+    stride = 16 + (rows + 127) // 128 * 128
+    positions = torch.full((requests,), position, dtype=torch.int32, device="cuda")
+    out = torch.empty(requests * depth, heads * head_dim, dtype=torch.bfloat16, device="cuda")
+    scores = torch.empty(requests * heads * depth * stride, dtype=torch.bfloat16, device="cuda")
+    for _ in range(launches):
+        check(library.carat_b200_verify_attention(
+            _ptr(queries), _ptr(keys), _ptr(values), _ptr(new_keys), _ptr(new_values),
+            _ptr(positions), _ptr(out), _ptr(scores), stride, requests, depth, heads, kv_heads,
+            head_dim, capacity, window, position, None))
+    torch.cuda.synchronize()
+
+
+def global_attention():
+    attention(head_dim=512, heads=32, kv_heads=4, window=0, capacity=8192, position=4096)
+
+
+CASES = {"linear": linear, "lm_head": lm_head, "attention": attention, "global": global_attention}
+
+if __name__ == "__main__":
+    name = sys.argv[1] if len(sys.argv) > 1 else "linear"
+    CASES[name]()
+    print(f"profile case {name} done")

@@ -61,9 +61,9 @@ CARAT_B200_API size_t carat_b200_fp8_linear_workspace_bytes(int rows, int input_
  * split-K partial sums live in an 8 MiB array built into the library image, so no workspace is
  * passed and the call makes no cudaMalloc / cudaFree or other allocating call. This entry point
  * has no counterpart in the reference.
- *  - Shapes whose partial sums need more than CARAT_B200_STATIC_SCRATCH_BYTES
- *    (splits * rows * output_width * 4, as carat_b200_fp8_linear_workspace_bytes reports) are
- *    rejected with an error; use carat_b200_fp8_linear for those.
+ *  - Shapes whose split-K scratch (carat_b200_fp8_linear_workspace_bytes) exceeds
+ *    CARAT_B200_STATIC_SCRATCH_BYTES are rejected with an error; use carat_b200_fp8_linear for
+ *    those.
  *  - The first call on each device looks the array's device address up; make that first call
  *    outside any stream capture.
  *  - All calls on a device share the one array: calls that overlap on the GPU (different streams,

@@ -30,6 +30,7 @@ def test_library_reports_its_abi_version_and_errors():
     # An invalid shape is rejected on the host before any CUDA call.
     assert library.carat_b200_fp8_linear_workspace_bytes(0, 128, 128) == 0
     assert library.carat_b200_fp8_linear_workspace_bytes(120, 8192, 5376) == 3 * 120 * 5376 * 4
+    assert library.carat_b200_fp8_linear_workspace_bytes(120, 5376, 18944) == 0
     status = library.carat_b200_fp8_linear(None, None, None, None, None, 4, 128, 128, None, 0, None)
     assert status != 0
     assert b"invalid FP8 linear shape" in library.carat_b200_last_error()
