@@ -1,5 +1,6 @@
 #include "accept.cuh"
 #include "fp8_linear.cuh"
+#include "launch.cuh"
 
 #include <cuda_bf16.h>
 #include <math_constants.h>
@@ -9,6 +10,8 @@ namespace {
 
 __global__ void accept_kernel(AcceptArguments a) {
   __shared__ int shared_accepted;
+  grid_dependency_launch();
+  grid_dependency_wait();
   const int request = static_cast<int>(blockIdx.x);
   const int start = request * a.depth;
   if (threadIdx.x == 0) {
@@ -46,6 +49,8 @@ __global__ void accept_kernel(AcceptArguments a) {
 
 __global__ void commit_kernel(const CommitLayer *layers, const int *positions, const int *accepted,
                               const int *slots, int depth) {
+  grid_dependency_launch();
+  grid_dependency_wait();
   const CommitLayer layer = layers[blockIdx.y];
   const int request = static_cast<int>(blockIdx.x);
   const int limit = min(accepted[request], depth);
@@ -160,7 +165,7 @@ int launch_accept(const AcceptArguments &a, cudaStream_t stream) {
       a.slot_positions == nullptr || a.requests <= 0 || a.depth <= 0 || a.hidden % 8 != 0) {
     return -1;
   }
-  accept_kernel<<<a.requests, 256, 0, stream>>>(a);
+  launch_chained(accept_kernel, dim3(static_cast<unsigned>(a.requests)), dim3(256), 0, stream, false, a);
   return launched();
 }
 
@@ -173,8 +178,8 @@ int launch_commit(const CommitLayer *device_layers, int layers, const int *posit
   if (device_layers == nullptr || positions == nullptr || accepted == nullptr || slots == nullptr ||
       requests <= 0 || depth <= 0)
     return -1;
-  commit_kernel<<<dim3(static_cast<unsigned>(requests), static_cast<unsigned>(layers)), 256, 0,
-                  stream>>>(device_layers, positions, accepted, slots, depth);
+  launch_chained(commit_kernel, dim3(static_cast<unsigned>(requests), static_cast<unsigned>(layers)),
+                 dim3(256), 0, stream, false, device_layers, positions, accepted, slots, depth);
   return launched();
 }
 

@@ -1,5 +1,6 @@
 #include "attention.cuh"
 #include "attention_geometry.cuh"
+#include "launch.cuh"
 
 #include <cuda_bf16.h>
 #include <math_constants.h>
@@ -30,6 +31,8 @@ template <int dimension>
 __global__ void __launch_bounds__(128) scores_kernel(AttentionArguments a) {
   extern __shared__ __align__(16) unsigned char shared_raw[];
   auto *shared_queries = reinterpret_cast<__nv_bfloat16 *>(shared_raw);
+  grid_dependency_launch();
+  grid_dependency_wait();
   const int request = static_cast<int>(blockIdx.z);
   const int kv_head = static_cast<int>(blockIdx.y);
   const int group = a.query_heads / a.kv_heads;
@@ -122,6 +125,8 @@ constexpr int softmax_threads = 128;
 
 __global__ void __launch_bounds__(softmax_threads) softmax_kernel(AttentionArguments a) {
   __shared__ float scratch[softmax_threads / 32];
+  grid_dependency_launch();
+  grid_dependency_wait();
   const int row_index = static_cast<int>(blockIdx.x);
   const int token = row_index % a.depth;
   const int request = row_index / (a.depth * a.query_heads);
@@ -198,6 +203,8 @@ __global__ void __launch_bounds__(softmax_threads) softmax_kernel(AttentionArgum
 template <int dimension, int max_rows>
 __global__ void __launch_bounds__(dimension / 2) pv_kernel(AttentionArguments a) {
   __shared__ __nv_bfloat16 probabilities[max_rows][64];
+  grid_dependency_launch();
+  grid_dependency_wait();
   const int request = static_cast<int>(blockIdx.z);
   const int kv_head = static_cast<int>(blockIdx.y);
   const int chunk = static_cast<int>(blockIdx.x);
@@ -290,16 +297,17 @@ template <int dimension> int launch_phases(const AttentionArguments &a, cudaStre
   }
   const dim3 score_grid(static_cast<unsigned>((columns + 127) / 128),
                         static_cast<unsigned>(a.kv_heads), static_cast<unsigned>(a.requests));
-  scores_kernel<dimension><<<score_grid, 128, query_bytes, stream>>>(a);
-  softmax_kernel<<<a.requests * a.query_heads * a.depth, softmax_threads, 0, stream>>>(a);
+  launch_chained(scores_kernel<dimension>, score_grid, dim3(128), query_bytes, stream, false, a);
+  launch_chained(softmax_kernel, dim3(static_cast<unsigned>(a.requests * a.query_heads * a.depth)),
+                 dim3(softmax_threads), 0, stream, false, a);
   const dim3 pv_grid(static_cast<unsigned>(a.chunks), static_cast<unsigned>(a.kv_heads),
                      static_cast<unsigned>(a.requests));
   if (rows <= 16) {
-    pv_kernel<dimension, 16><<<pv_grid, dimension / 2, 0, stream>>>(a);
+    launch_chained(pv_kernel<dimension, 16>, pv_grid, dim3(dimension / 2), 0, stream, false, a);
   } else if (rows <= 40) {
-    pv_kernel<dimension, 40><<<pv_grid, dimension / 2, 0, stream>>>(a);
+    launch_chained(pv_kernel<dimension, 40>, pv_grid, dim3(dimension / 2), 0, stream, false, a);
   } else {
-    pv_kernel<dimension, 80><<<pv_grid, dimension / 2, 0, stream>>>(a);
+    launch_chained(pv_kernel<dimension, 80>, pv_grid, dim3(dimension / 2), 0, stream, false, a);
   }
   return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
 }
@@ -325,7 +333,8 @@ int validate_attention(const AttentionArguments &a) {
 }
 
 int launch_attention_softmax(const AttentionArguments &a, cudaStream_t stream) {
-  softmax_kernel<<<a.requests * a.query_heads * a.depth, softmax_threads, 0, stream>>>(a);
+  launch_chained(softmax_kernel, dim3(static_cast<unsigned>(a.requests * a.query_heads * a.depth)),
+                 dim3(softmax_threads), 0, stream, false, a);
   return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
 }
 

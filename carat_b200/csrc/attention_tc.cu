@@ -11,6 +11,7 @@
 #include "attention_geometry.cuh"
 #include "attention_tc.cuh"
 #include "context.cuh"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 #include <cuda_bf16.h>
@@ -88,6 +89,7 @@ scores_tc_kernel(const __grid_constant__ CUtensorMap key_map,
   const int cache_items = max(0, last_tile - first_tile);
   const int proposal_items = (chunk == 0 && g.proposals > 0) ? 1 : 0;
   const int items = proposal_items + cache_items;
+  grid_dependency_launch();
   if (items == 0)
     return;
   const int query_row0 = (request * a.query_heads + kv_head * group) * a.depth;
@@ -117,6 +119,7 @@ scores_tc_kernel(const __grid_constant__ CUtensorMap key_map,
   __syncthreads();
   ptx::tcgen05_fence_after_thread_sync();
   const uint32_t tmem_base = tmem_base_slot;
+  grid_dependency_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -328,6 +331,7 @@ pv_tc_kernel(const __grid_constant__ CUtensorMap value_map,
       (static_cast<long long>(a.slots[request]) * a.kv_heads + kv_head) * a.capacity;
   const int staged_row0 = (request * a.kv_heads + kv_head) * a.depth;
 
+  grid_dependency_launch();
   if (threadIdx.x == 0) {
     for (int stage = 0; stage < stages; ++stage) {
       ptx::mbarrier_init(full_bar + 8U * stage, 1);
@@ -346,6 +350,7 @@ pv_tc_kernel(const __grid_constant__ CUtensorMap value_map,
   __syncthreads();
   ptx::tcgen05_fence_after_thread_sync();
   const uint32_t tmem_base = tmem_base_slot;
+  grid_dependency_wait();
 
   if (warp == 0) {
     if (lane == 0 && items > 0) {
@@ -538,15 +543,17 @@ int launch_tc(const AttentionArguments &a, int *device_error, cudaStream_t strea
   const bool staged = a.new_keys != nullptr;
   const dim3 score_grid(static_cast<unsigned>(attention_chunks(a.max_cache_rows, score_chunk_rows)),
                         static_cast<unsigned>(a.kv_heads), static_cast<unsigned>(a.requests));
-  scores_tc_kernel<dimension, padded_rows><<<score_grid, tc_threads, score_shared, stream>>>(
-      maps.keys, staged ? maps.new_keys : maps.keys, maps.queries, arguments);
+  launch_chained(scores_tc_kernel<dimension, padded_rows>, score_grid, dim3(tc_threads),
+                 score_shared, stream, false, maps.keys, staged ? maps.new_keys : maps.keys,
+                 maps.queries, arguments);
   const int status = launch_attention_softmax(a, stream);
   if (status != 0)
     return status;
   const dim3 pv_grid(static_cast<unsigned>(a.chunks),
                      static_cast<unsigned>(a.kv_heads), static_cast<unsigned>(a.requests));
-  pv_tc_kernel<dimension, padded_rows><<<pv_grid, tc_threads, pv_shared, stream>>>(
-      maps.values, staged ? maps.new_values : maps.values, maps.scores, arguments);
+  launch_chained(pv_tc_kernel<dimension, padded_rows>, pv_grid, dim3(tc_threads), pv_shared, stream,
+                 false, maps.values, staged ? maps.new_values : maps.values, maps.scores,
+                 arguments);
   return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
 }
 

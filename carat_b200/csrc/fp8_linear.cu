@@ -12,6 +12,7 @@
 // accumulator with tcgen05.ld. Weights are read exactly once with an evict-first policy; the
 // activation matrix is re-read from L2 by every tile with an evict-last policy.
 #include "fp8_linear.cuh"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 #include <cuda_bf16.h>
@@ -145,6 +146,7 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
   const int first_item = static_cast<int>(blockIdx.x);
   const int item_stride = static_cast<int>(gridDim.x);
 
+  grid_dependency_launch();
   if (threadIdx.x == 0) {
     for (int stage = 0; stage < stages; ++stage) {
       ptx::mbarrier_init(full_bar + 8U * stage, 1);
@@ -177,20 +179,36 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
       const uint64_t reuse_policy = ptx::policy_evict_last();
       int issued = 0;
       bool healthy = true;
+      // The weights are static: the first ring of weight tiles is requested before the grid this
+      // launch depends on has finished. The activation tiles of those stages follow once it has.
+      int early = 0;
+      if (first_item < items) {
+        const WorkItem item = decode_item(args, first_item);
+        early = min(item.k_count, stages);
+        for (int block = 0; block < early; ++block) {
+          ptx::mbarrier_arrive_expect_tx(full_bar + 8U * block, stage_bytes);
+          ptx::tma_load_2d(weight_tiles + block * weight_tile_bytes, &weight_map,
+                           (item.k_begin + block) * tile_k_bytes, item.tile * tile_features,
+                           full_bar + 8U * block, stream_policy);
+        }
+      }
+      grid_dependency_wait();
       for (int index = first_item; index < items && healthy; index += item_stride) {
         const WorkItem item = decode_item(args, index);
         for (int block = 0; block < item.k_count; ++block, ++issued) {
           const int stage = issued % stages;
           const uint32_t phase = static_cast<uint32_t>(issued / stages) & 1U;
-          if (!ptx::mbarrier_wait_bounded(empty_bar + 8U * stage, phase ^ 1U)) {
-            healthy = false;
-            atomicExch(args.device_error, 1);
-            break;
-          }
-          ptx::mbarrier_arrive_expect_tx(full_bar + 8U * stage, stage_bytes);
           const int k_byte = (item.k_begin + block) * tile_k_bytes;
-          ptx::tma_load_2d(weight_tiles + stage * weight_tile_bytes, &weight_map, k_byte,
-                           item.tile * tile_features, full_bar + 8U * stage, stream_policy);
+          if (issued >= early) {
+            if (!ptx::mbarrier_wait_bounded(empty_bar + 8U * stage, phase ^ 1U)) {
+              healthy = false;
+              atomicExch(args.device_error, 1);
+              break;
+            }
+            ptx::mbarrier_arrive_expect_tx(full_bar + 8U * stage, stage_bytes);
+            ptx::tma_load_2d(weight_tiles + stage * weight_tile_bytes, &weight_map, k_byte,
+                             item.tile * tile_features, full_bar + 8U * stage, stream_policy);
+          }
           ptx::tma_load_2d(input_tiles + stage * input_tile_bytes, &input_map, k_byte, 0,
                            full_bar + 8U * stage, reuse_policy);
         }
@@ -246,6 +264,7 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
   } else {
     const int quarter = warp & 3;  // TMEM lane group this warp may read
     [[maybe_unused]] const int epilogue_thread = (warp - 2) * 32 + lane;
+    grid_dependency_wait();
     float scale = 1.0F;
     if constexpr (mode != 1)
       scale = args.input_scale[0] * args.weight_scale[0];
@@ -328,6 +347,8 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
 __global__ void finalize_split_k_kernel(const float *partial, const float *input_scale,
                                         const float *weight_scale, __nv_bfloat16 *output,
                                         int splits, size_t elements) {
+  grid_dependency_launch();
+  grid_dependency_wait();
   const float scale = input_scale[0] * weight_scale[0];
   for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
        index < elements; index += static_cast<size_t>(blockDim.x) * gridDim.x) {
@@ -412,9 +433,11 @@ int launch_variant(const LinearPlan &plan, const KernelArguments &arguments, cud
     return -10;
   const int items = plan.tiles * arguments.splits;
   const int ctas = items < plan.ctas ? items : plan.ctas;
-  fp8_linear_kernel<padded_rows, mode><<<ctas, linear_threads, dynamic_bytes, stream>>>(
-      plan.weight_map, plan.input_map, arguments);
-  return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
+  return launch_chained(fp8_linear_kernel<padded_rows, mode>, dim3(static_cast<unsigned>(ctas)),
+                        dim3(linear_threads), dynamic_bytes, stream, false, plan.weight_map,
+                        plan.input_map, arguments) == cudaSuccess
+             ? 0
+             : -11;
 }
 
 template <int mode>
@@ -542,10 +565,12 @@ int launch_linear_bf16(const LinearPlan &plan, const float *input_scale, const f
     return status;
   const size_t elements = static_cast<size_t>(plan.rows) * plan.output_width;
   const int blocks = static_cast<int>((elements + 255) / 256);
-  finalize_split_k_kernel<<<blocks < 1184 ? blocks : 1184, 256, 0, stream>>>(
-      partial, input_scale, weight_scale, static_cast<__nv_bfloat16 *>(bf16_output), plan.splits,
-      elements);
-  return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
+  return launch_chained(finalize_split_k_kernel, dim3(blocks < 1184 ? blocks : 1184), dim3(256), 0,
+                        stream, false, static_cast<const float *>(partial), input_scale,
+                        weight_scale, static_cast<__nv_bfloat16 *>(bf16_output), plan.splits,
+                        elements) == cudaSuccess
+             ? 0
+             : -11;
 }
 
 int launch_linear_partial(const LinearPlan &plan, float *partial, int *device_error,

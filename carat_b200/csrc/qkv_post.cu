@@ -1,5 +1,7 @@
 #include "qkv_post.cuh"
 
+#include "launch.cuh"
+
 #include <cuda_bf16.h>
 
 namespace carat_b200 {
@@ -67,6 +69,8 @@ __device__ __forceinline__ void norm_rope_store(const float (&low)[per], const f
 
 template <int per> __global__ void qkv_post_kernel(QkvPostArguments a) {
   constexpr int dimension = per * 64;
+  grid_dependency_launch();
+  grid_dependency_wait();
   const int warp = static_cast<int>(blockIdx.x) * (blockDim.x / 32) + (threadIdx.x / 32);
   const int lane = static_cast<int>(threadIdx.x) & 31;
   const int heads_per_row = a.query_heads + a.kv_heads;
@@ -143,6 +147,8 @@ __global__ void query_post_kernel(const __nv_bfloat16 *projected, const __nv_bfl
                                   const int *positions, int position_offset, int requests,
                                   int query_heads, int max_positions, float epsilon) {
   constexpr int dimension = per * 64;
+  grid_dependency_launch();
+  grid_dependency_wait();
   const int warp = static_cast<int>(blockIdx.x) * (blockDim.x / 32) + (threadIdx.x / 32);
   const int lane = static_cast<int>(threadIdx.x) & 31;
   if (warp >= requests * query_heads)
@@ -190,13 +196,13 @@ int launch_qkv_post(const QkvPostArguments &a, cudaStream_t stream) {
   const int blocks = (warps + 3) / 4;
   switch (a.head_dim) {
   case 64:
-    qkv_post_kernel<1><<<blocks, 128, 0, stream>>>(a);
+    launch_chained(qkv_post_kernel<1>, dim3(blocks), dim3(128), 0, stream, false, a);
     break;
   case 256:
-    qkv_post_kernel<4><<<blocks, 128, 0, stream>>>(a);
+    launch_chained(qkv_post_kernel<4>, dim3(blocks), dim3(128), 0, stream, false, a);
     break;
   case 512:
-    qkv_post_kernel<8><<<blocks, 128, 0, stream>>>(a);
+    launch_chained(qkv_post_kernel<8>, dim3(blocks), dim3(128), 0, stream, false, a);
     break;
   default:
     return -3;
@@ -221,16 +227,16 @@ int launch_query_post(const void *projected, const void *query_norm, const void 
   auto *q = static_cast<__nv_bfloat16 *>(queries);
   switch (head_dim) {
   case 64:
-    query_post_kernel<1><<<blocks, 128, 0, stream>>>(p, w, c, s, q, positions, position_offset,
-                                                     requests, query_heads, max_positions, epsilon);
+    launch_chained(query_post_kernel<1>, dim3(blocks), dim3(128), 0, stream, false, p, w, c, s, q,
+                   positions, position_offset, requests, query_heads, max_positions, epsilon);
     break;
   case 256:
-    query_post_kernel<4><<<blocks, 128, 0, stream>>>(p, w, c, s, q, positions, position_offset,
-                                                     requests, query_heads, max_positions, epsilon);
+    launch_chained(query_post_kernel<4>, dim3(blocks), dim3(128), 0, stream, false, p, w, c, s, q,
+                   positions, position_offset, requests, query_heads, max_positions, epsilon);
     break;
   case 512:
-    query_post_kernel<8><<<blocks, 128, 0, stream>>>(p, w, c, s, q, positions, position_offset,
-                                                     requests, query_heads, max_positions, epsilon);
+    launch_chained(query_post_kernel<8>, dim3(blocks), dim3(128), 0, stream, false, p, w, c, s, q,
+                   positions, position_offset, requests, query_heads, max_positions, epsilon);
     break;
   default:
     return -3;

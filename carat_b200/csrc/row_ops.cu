@@ -1,5 +1,7 @@
 #include "row_ops.cuh"
 
+#include "launch.cuh"
+
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -166,6 +168,8 @@ template <RowMode mode> __global__ void __launch_bounds__(row_threads) row_kerne
   const int width = a.width;
   const float width_value = static_cast<float>(width);
   float row_amax = 0.0F;
+  grid_dependency_launch();
+  grid_dependency_wait();
 
   if constexpr (mode == RowMode::embed_norm) {
     // The per-step scratch words must be zero before the first atomic maximum of the step; the
@@ -380,10 +384,9 @@ template <RowMode mode> int launch_rows(RowArguments arguments, int rows, cudaSt
     return -10;
   if (rows > resident_limit || shared_bytes > 64 * 1024)
     return -2;
-  void *kernel_arguments[] = {&arguments};
-  const cudaError_t status = cudaLaunchCooperativeKernel(
-      reinterpret_cast<const void *>(row_kernel<mode>), dim3(static_cast<unsigned>(rows)),
-      dim3(row_threads), kernel_arguments, shared_bytes, stream);
+  const cudaError_t status =
+      launch_chained(row_kernel<mode>, dim3(static_cast<unsigned>(rows)), dim3(row_threads),
+                     shared_bytes, stream, true, arguments);
   return status == cudaSuccess ? 0 : -11;
 }
 
