@@ -106,6 +106,18 @@ __device__ __forceinline__ Pack8 load_bf16x8(const __nv_bfloat16 *pointer) {
   return result;
 }
 
+__device__ __forceinline__ Pack8 unpack_bf16x8(const uint4 &raw) {
+  const __nv_bfloat162 *pairs = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+  Pack8 result;
+#pragma unroll
+  for (int pair = 0; pair < 4; ++pair) {
+    const float2 both = __bfloat1622float2(pairs[pair]);
+    result.v[2 * pair] = both.x;
+    result.v[2 * pair + 1] = both.y;
+  }
+  return result;
+}
+
 // Rounds to bf16, stores, and returns the rounded values as floats.
 __device__ __forceinline__ Pack8 round_bf16x8(const Pack8 &values, uint4 *packed) {
   __nv_bfloat162 pairs[4];
@@ -137,6 +149,7 @@ __device__ __forceinline__ Pack8 load_source(const RowArguments &a, size_t row, 
 #pragma unroll
   for (int index = 0; index < 8; ++index)
     sum.v[index] = 0.0F;
+#pragma unroll 4
   for (int split = 0; split < a.splits; ++split) {
     const float *source = a.partial + (static_cast<size_t>(split) * rows + row) * a.width + column;
     const float4 low = *reinterpret_cast<const float4 *>(source);
@@ -157,18 +170,38 @@ __device__ __forceinline__ Pack8 load_source(const RowArguments &a, size_t row, 
   return rounded;
 }
 
-template <RowMode mode> __global__ void __launch_bounds__(row_threads) row_kernel(RowArguments a) {
+// Every thread owns `chunks` groups of eight consecutive columns, group c at column
+// (c * row_threads + thread) * 8, and keeps them in registers from the first load to the e4m3
+// store: the row never goes through shared or global memory between the phases. Static operands
+// (norm weights) are loaded before the wait on the previous grid, everything else right after it,
+// so one global-memory round trip feeds the whole kernel.
+template <RowMode mode, int chunks>
+__global__ void __launch_bounds__(row_threads) row_kernel(RowArguments a) {
   cg::grid_group grid = cg::this_grid();
-  extern __shared__ __align__(16) unsigned char row_storage[];
-  auto *row_values = reinterpret_cast<__nv_bfloat16 *>(row_storage);
   __shared__ float scratch[row_warps];
 
   const size_t row = blockIdx.x;
   const size_t rows = gridDim.x;
   const int width = a.width;
   const float width_value = static_cast<float>(width);
-  float row_amax = 0.0F;
+  constexpr bool two_norms = mode == RowMode::post_attention || mode == RowMode::layer_output;
+  constexpr bool one_norm = mode == RowMode::embed_norm || mode == RowMode::norm;
+
   grid_dependency_launch();
+  uint4 weight_raw[chunks];
+  uint4 next_weight_raw[chunks];
+#pragma unroll
+  for (int chunk = 0; chunk < chunks; ++chunk) {
+    const int column = (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+    weight_raw[chunk] = make_uint4(0, 0, 0, 0);
+    next_weight_raw[chunk] = make_uint4(0, 0, 0, 0);
+    if (column < width) {
+      if constexpr (one_norm || two_norms)
+        weight_raw[chunk] = *reinterpret_cast<const uint4 *>(a.norm_weight + column);
+      if constexpr (two_norms)
+        next_weight_raw[chunk] = *reinterpret_cast<const uint4 *>(a.next_norm_weight + column);
+    }
+  }
   grid_dependency_wait();
 
   if constexpr (mode == RowMode::embed_norm) {
@@ -184,51 +217,52 @@ template <RowMode mode> __global__ void __launch_bounds__(row_threads) row_kerne
   if (a.splits > 0 && a.input_scale != nullptr)
     partial_scale = a.input_scale[0] * a.weight_scale[0];
 
-  if constexpr (mode == RowMode::plain) {
-    for (int column = static_cast<int>(threadIdx.x) * 8; column < width; column += row_threads * 8) {
-      const Pack8 values = load_source(a, row, column, rows, partial_scale);
-      uint4 packed;
-      const Pack8 rounded = round_bf16x8(values, &packed);
-      *reinterpret_cast<uint4 *>(row_values + column) = packed;
-      if (a.first_out != nullptr)
-        *reinterpret_cast<uint4 *>(a.first_out + row * width + column) = packed;
+  // ---- load: the bf16-exact starting row (and the residual) into registers
+  Pack8 values[chunks];
+  uint4 residual_raw[chunks];
+#pragma unroll
+  for (int chunk = 0; chunk < chunks; ++chunk) {
+    const int column = (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+    residual_raw[chunk] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int index = 0; index < 8; ++index)
+      values[chunk].v[index] = 0.0F;
+    if (column >= width)
+      continue;
+    if constexpr (mode == RowMode::embed_norm) {
+      const int token = a.tokens[row];
+      const float scale = __bfloat162float(__float2bfloat16_rn(sqrtf(width_value)));
+      Pack8 raw = values[chunk];
+      if (token >= 0 && token < a.vocabulary)
+        raw = load_bf16x8(a.embedding + static_cast<size_t>(token) * width + column);
 #pragma unroll
       for (int index = 0; index < 8; ++index)
-        row_amax = fmaxf(row_amax, fabsf(rounded.v[index]));
-    }
-  } else if constexpr (mode == RowMode::embed_concat) {
-    // `width` is the concatenated width; the left half is the scaled embedding row, the right
-    // half a bf16 copy of the carried hidden state.
-    const int half = width / 2;
-    const int token = a.tokens[row];
-    const size_t source_row = a.row_indices != nullptr ? static_cast<size_t>(a.row_indices[row]) : row;
-    const float embed_scale = __bfloat162float(__float2bfloat16_rn(sqrtf(static_cast<float>(half))));
-    for (int column = static_cast<int>(threadIdx.x) * 8; column < width; column += row_threads * 8) {
-      Pack8 values;
+        raw.v[index] *= scale;
+      uint4 packed;
+      values[chunk] = round_bf16x8(raw, &packed);
+      *reinterpret_cast<uint4 *>(a.first_out + row * width + column) = packed;
+    } else if constexpr (mode == RowMode::embed_concat) {
+      // `width` is the concatenated width: scaled embedding row, then the carried hidden state.
+      const int half = width / 2;
       if (column < half) {
-        if (token >= 0 && token < a.vocabulary) {
-          values = load_bf16x8(a.embedding + static_cast<size_t>(token) * half + column);
-        } else {
-#pragma unroll
-          for (int index = 0; index < 8; ++index)
-            values.v[index] = 0.0F;
-        }
+        const int token = a.tokens[row];
+        const float scale =
+            __bfloat162float(__float2bfloat16_rn(sqrtf(static_cast<float>(half))));
+        Pack8 raw = values[chunk];
+        if (token >= 0 && token < a.vocabulary)
+          raw = load_bf16x8(a.embedding + static_cast<size_t>(token) * half + column);
 #pragma unroll
         for (int index = 0; index < 8; ++index)
-          values.v[index] *= embed_scale;
+          raw.v[index] *= scale;
+        uint4 packed;
+        values[chunk] = round_bf16x8(raw, &packed);
       } else {
-        values = load_bf16x8(a.input + source_row * half + (column - half));
+        const size_t source_row =
+            a.row_indices != nullptr ? static_cast<size_t>(a.row_indices[row]) : row;
+        values[chunk] = load_bf16x8(a.input + source_row * half + (column - half));
       }
-      uint4 packed;
-      const Pack8 rounded = round_bf16x8(values, &packed);
-      *reinterpret_cast<uint4 *>(row_values + column) = packed;
-#pragma unroll
-      for (int index = 0; index < 8; ++index)
-        row_amax = fmaxf(row_amax, fabsf(rounded.v[index]));
-    }
-  } else if constexpr (mode == RowMode::geglu) {
-    const __nv_bfloat16 *packed_row = a.input + row * 2 * width;
-    for (int column = static_cast<int>(threadIdx.x) * 8; column < width; column += row_threads * 8) {
+    } else if constexpr (mode == RowMode::geglu) {
+      const __nv_bfloat16 *packed_row = a.input + row * 2 * width;
       const Pack8 gate = load_bf16x8(packed_row + column);
       const Pack8 up = load_bf16x8(packed_row + width + column);
       Pack8 product;
@@ -236,103 +270,101 @@ template <RowMode mode> __global__ void __launch_bounds__(row_threads) row_kerne
       for (int index = 0; index < 8; ++index)
         product.v[index] = gelu_tanh(gate.v[index]) * up.v[index];
       uint4 packed;
-      const Pack8 rounded = round_bf16x8(product, &packed);
-      *reinterpret_cast<uint4 *>(row_values + column) = packed;
-#pragma unroll
-      for (int index = 0; index < 8; ++index)
-        row_amax = fmaxf(row_amax, fabsf(rounded.v[index]));
-    }
-  } else {
-    // Stage 1: the row that gets normalised first, kept in shared memory as bf16.
-    float square_sum = 0.0F;
-    for (int column = static_cast<int>(threadIdx.x) * 8; column < width; column += row_threads * 8) {
-      Pack8 values;
-      if constexpr (mode == RowMode::embed_norm) {
-        const int token = a.tokens[row];
-        const float scale = __bfloat162float(__float2bfloat16_rn(sqrtf(width_value)));
-        Pack8 raw;
-        if (token >= 0 && token < a.vocabulary) {
-          raw = load_bf16x8(a.embedding + static_cast<size_t>(token) * width + column);
-        } else {
-#pragma unroll
-          for (int index = 0; index < 8; ++index)
-            raw.v[index] = 0.0F;
+      values[chunk] = round_bf16x8(product, &packed);
+    } else {
+      values[chunk] = load_source(a, row, column, rows, partial_scale);
+      if constexpr (mode == RowMode::plain) {
+        if (a.first_out != nullptr) {
+          uint4 packed;
+          (void)round_bf16x8(values[chunk], &packed);
+          *reinterpret_cast<uint4 *>(a.first_out + row * width + column) = packed;
         }
-#pragma unroll
-        for (int index = 0; index < 8; ++index)
-          raw.v[index] *= scale;
-        uint4 packed;
-        values = round_bf16x8(raw, &packed);
-        *reinterpret_cast<uint4 *>(a.first_out + row * width + column) = packed;
-        *reinterpret_cast<uint4 *>(row_values + column) = packed;
-      } else {
-        values = load_source(a, row, column, rows, partial_scale);
-        uint4 packed;
-        (void)round_bf16x8(values, &packed);  // already bf16-exact; repack for shared memory
-        *reinterpret_cast<uint4 *>(row_values + column) = packed;
       }
-#pragma unroll
-      for (int index = 0; index < 8; ++index)
-        square_sum += values.v[index] * values.v[index];
-    }
-    float inverse_rms = rsqrtf(block_sum(square_sum, scratch) / width_value + a.epsilon);
-
-    if constexpr (mode == RowMode::post_attention || mode == RowMode::layer_output) {
-      // first = bf16(norm(x) * w + residual) [* scalar, rounded again, for the layer output];
-      // it replaces the row in shared memory and is what the second norm reads.
-      float layer_scale = 1.0F;
-      if constexpr (mode == RowMode::layer_output)
-        layer_scale = __bfloat162float(*a.scalar);
-      square_sum = 0.0F;
-      for (int column = static_cast<int>(threadIdx.x) * 8; column < width;
-           column += row_threads * 8) {
-        const Pack8 values = load_bf16x8(row_values + column);
-        const Pack8 weights = load_bf16x8(a.norm_weight + column);
-        const Pack8 residual = load_bf16x8(a.residual + row * width + column);
-        Pack8 result;
-#pragma unroll
-        for (int index = 0; index < 8; ++index)
-          result.v[index] = values.v[index] * inverse_rms * weights.v[index] + residual.v[index];
-        uint4 packed;
-        Pack8 rounded = round_bf16x8(result, &packed);
-        if constexpr (mode == RowMode::layer_output) {
-#pragma unroll
-          for (int index = 0; index < 8; ++index)
-            result.v[index] = rounded.v[index] * layer_scale;
-          rounded = round_bf16x8(result, &packed);
-        }
-        *reinterpret_cast<uint4 *>(row_values + column) = packed;
-        *reinterpret_cast<uint4 *>(a.first_out + row * width + column) = packed;
-#pragma unroll
-        for (int index = 0; index < 8; ++index)
-          square_sum += rounded.v[index] * rounded.v[index];
-      }
-      inverse_rms = rsqrtf(block_sum(square_sum, scratch) / width_value + a.epsilon);
-    }
-
-    // Stage 2: the normalised row that is quantised.
-    const __nv_bfloat16 *weight =
-        (mode == RowMode::post_attention || mode == RowMode::layer_output) ? a.next_norm_weight
-                                                                           : a.norm_weight;
-    for (int column = static_cast<int>(threadIdx.x) * 8; column < width; column += row_threads * 8) {
-      const Pack8 values = load_bf16x8(row_values + column);
-      const Pack8 weights = load_bf16x8(weight + column);
-      Pack8 result;
-#pragma unroll
-      for (int index = 0; index < 8; ++index)
-        result.v[index] = values.v[index] * inverse_rms * weights.v[index];
-      uint4 packed;
-      const Pack8 rounded = round_bf16x8(result, &packed);
-      *reinterpret_cast<uint4 *>(row_values + column) = packed;
-      if (a.second_out != nullptr)
-        *reinterpret_cast<uint4 *>(a.second_out + row * width + column) = packed;
-#pragma unroll
-      for (int index = 0; index < 8; ++index)
-        row_amax = fmaxf(row_amax, fabsf(rounded.v[index]));
+      if constexpr (two_norms)
+        residual_raw[chunk] = *reinterpret_cast<const uint4 *>(a.residual + row * width + column);
     }
   }
 
-  // Tensor-wide maximum, one barrier, then quantise this row from shared memory.
+  // ---- first norm (+ residual, + layer scalar), rounded to bf16 exactly where the reference does
+  if constexpr (one_norm || two_norms) {
+    float square_sum = 0.0F;
+#pragma unroll
+    for (int chunk = 0; chunk < chunks; ++chunk)
+#pragma unroll
+      for (int index = 0; index < 8; ++index)
+        square_sum += values[chunk].v[index] * values[chunk].v[index];
+    const float inverse_rms = rsqrtf(block_sum(square_sum, scratch) / width_value + a.epsilon);
+    float layer_scale = 1.0F;
+    if constexpr (mode == RowMode::layer_output)
+      layer_scale = __bfloat162float(*a.scalar);
+#pragma unroll
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+      const int column = (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+      if (column >= width)
+        continue;
+      const Pack8 weights = unpack_bf16x8(weight_raw[chunk]);
+      Pack8 result;
+      if constexpr (two_norms) {
+        const Pack8 residual = unpack_bf16x8(residual_raw[chunk]);
+#pragma unroll
+        for (int index = 0; index < 8; ++index)
+          result.v[index] =
+              values[chunk].v[index] * inverse_rms * weights.v[index] + residual.v[index];
+      } else {
+#pragma unroll
+        for (int index = 0; index < 8; ++index)
+          result.v[index] = values[chunk].v[index] * inverse_rms * weights.v[index];
+      }
+      uint4 packed;
+      values[chunk] = round_bf16x8(result, &packed);
+      if constexpr (mode == RowMode::layer_output) {
+#pragma unroll
+        for (int index = 0; index < 8; ++index)
+          result.v[index] = values[chunk].v[index] * layer_scale;
+        values[chunk] = round_bf16x8(result, &packed);
+      }
+      if constexpr (two_norms)
+        *reinterpret_cast<uint4 *>(a.first_out + row * width + column) = packed;
+      if constexpr (one_norm) {
+        if (a.second_out != nullptr)
+          *reinterpret_cast<uint4 *>(a.second_out + row * width + column) = packed;
+      }
+    }
+  }
+
+  // ---- second norm of the row just formed
+  if constexpr (two_norms) {
+    float square_sum = 0.0F;
+#pragma unroll
+    for (int chunk = 0; chunk < chunks; ++chunk)
+#pragma unroll
+      for (int index = 0; index < 8; ++index)
+        square_sum += values[chunk].v[index] * values[chunk].v[index];
+    const float inverse_rms = rsqrtf(block_sum(square_sum, scratch) / width_value + a.epsilon);
+#pragma unroll
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+      const int column = (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+      if (column >= width)
+        continue;
+      const Pack8 weights = unpack_bf16x8(next_weight_raw[chunk]);
+      Pack8 result;
+#pragma unroll
+      for (int index = 0; index < 8; ++index)
+        result.v[index] = values[chunk].v[index] * inverse_rms * weights.v[index];
+      uint4 packed;
+      values[chunk] = round_bf16x8(result, &packed);
+      if (a.second_out != nullptr)
+        *reinterpret_cast<uint4 *>(a.second_out + row * width + column) = packed;
+    }
+  }
+
+  // ---- tensor-wide maximum, one barrier, e4m3 from registers
+  float row_amax = 0.0F;
+#pragma unroll
+  for (int chunk = 0; chunk < chunks; ++chunk)
+#pragma unroll
+    for (int index = 0; index < 8; ++index)
+      row_amax = fmaxf(row_amax, fabsf(values[chunk].v[index]));
   row_amax = block_max(row_amax, scratch);
   if (threadIdx.x == 0U)
     atomicMax(a.amax_bits, __float_as_uint(row_amax));
@@ -342,17 +374,48 @@ template <RowMode mode> __global__ void __launch_bounds__(row_threads) row_kerne
   const float inverse_scale = 1.0F / scale;
   if (blockIdx.x == 0U && threadIdx.x == 0U)
     *a.scale = scale;
-  for (int column = static_cast<int>(threadIdx.x) * 8; column < width; column += row_threads * 8) {
-    const Pack8 values = load_bf16x8(row_values + column);
-    __nv_fp8x4_e4m3 low(make_float4(values.v[0] * inverse_scale, values.v[1] * inverse_scale,
-                                    values.v[2] * inverse_scale, values.v[3] * inverse_scale));
-    __nv_fp8x4_e4m3 high(make_float4(values.v[4] * inverse_scale, values.v[5] * inverse_scale,
-                                     values.v[6] * inverse_scale, values.v[7] * inverse_scale));
+#pragma unroll
+  for (int chunk = 0; chunk < chunks; ++chunk) {
+    const int column = (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+    if (column >= width)
+      continue;
+    const Pack8 &v = values[chunk];
+    __nv_fp8x4_e4m3 low(make_float4(v.v[0] * inverse_scale, v.v[1] * inverse_scale,
+                                    v.v[2] * inverse_scale, v.v[3] * inverse_scale));
+    __nv_fp8x4_e4m3 high(make_float4(v.v[4] * inverse_scale, v.v[5] * inverse_scale,
+                                     v.v[6] * inverse_scale, v.v[7] * inverse_scale));
     uint2 packed;
     packed.x = low.__x;
     packed.y = high.__x;
     *reinterpret_cast<uint2 *>(a.fp8_output + row * width + column) = packed;
   }
+}
+
+template <RowMode mode, int chunks>
+int launch_rows_chunks(const RowArguments &arguments, int rows, cudaStream_t stream) {
+  static int resident_limit = -1;
+  static cudaError_t configure_status = cudaSuccess;
+  if (resident_limit < 0) {
+    int device = 0;
+    int multiprocessors = 0;
+    int per_multiprocessor = 0;
+    configure_status = cudaGetDevice(&device);
+    if (configure_status == cudaSuccess)
+      configure_status =
+          cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device);
+    if (configure_status == cudaSuccess)
+      configure_status = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+          &per_multiprocessor, row_kernel<mode, chunks>, row_threads, 0);
+    resident_limit = configure_status == cudaSuccess ? multiprocessors * per_multiprocessor : 0;
+  }
+  if (configure_status != cudaSuccess)
+    return -10;
+  if (rows > resident_limit)
+    return -2;
+  const cudaError_t status =
+      launch_chained(row_kernel<mode, chunks>, dim3(static_cast<unsigned>(rows)),
+                     dim3(row_threads), 0, stream, true, arguments);
+  return status == cudaSuccess ? 0 : -11;
 }
 
 template <RowMode mode> int launch_rows(RowArguments arguments, int rows, cudaStream_t stream) {
@@ -361,33 +424,14 @@ template <RowMode mode> int launch_rows(RowArguments arguments, int rows, cudaSt
       arguments.amax_bits == nullptr) {
     return -1;
   }
-  const size_t shared_bytes = static_cast<size_t>(arguments.width) * sizeof(__nv_bfloat16);
-  static int resident_limit = -1;
-  static cudaError_t configure_status = cudaSuccess;
-  if (resident_limit < 0) {
-    configure_status = cudaFuncSetAttribute(row_kernel<mode>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-    int device = 0;
-    int multiprocessors = 0;
-    int per_multiprocessor = 0;
-    if (configure_status == cudaSuccess)
-      configure_status = cudaGetDevice(&device);
-    if (configure_status == cudaSuccess)
-      configure_status =
-          cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device);
-    if (configure_status == cudaSuccess)
-      configure_status = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-          &per_multiprocessor, row_kernel<mode>, row_threads, 64 * 1024);
-    resident_limit = configure_status == cudaSuccess ? multiprocessors * per_multiprocessor : 0;
-  }
-  if (configure_status != cudaSuccess)
-    return -10;
-  if (rows > resident_limit || shared_bytes > 64 * 1024)
-    return -2;
-  const cudaError_t status =
-      launch_chained(row_kernel<mode>, dim3(static_cast<unsigned>(rows)), dim3(row_threads),
-                     shared_bytes, stream, true, arguments);
-  return status == cudaSuccess ? 0 : -11;
+  const int groups = (arguments.width / 8 + row_threads - 1) / row_threads;
+  if (groups <= 2)
+    return launch_rows_chunks<mode, 2>(arguments, rows, stream);
+  if (groups <= 4)
+    return launch_rows_chunks<mode, 4>(arguments, rows, stream);
+  if (groups <= 8)
+    return launch_rows_chunks<mode, 8>(arguments, rows, stream);
+  return -2;
 }
 
 // Large tensors (weights at load time): the reference's three-launch form, cuda/linear.cu:117-153.
