@@ -28,20 +28,6 @@ __host__ __device__ constexpr uint32_t tmem_columns_for(int columns) {
   return columns <= 32 ? 32U : columns <= 64 ? 64U : columns <= 128 ? 128U : 256U;
 }
 
-// MN-major operand written by TMA as [rows = K index][64 elements = MN index] with the 128-byte
-// swizzle: eight K rows form one 1024-byte atom (SBO), the next 64 MN elements live in the next
-// TMA box `mn_atom_bytes` further (LBO).
-__device__ __forceinline__ uint64_t umma_desc_mn_major_sw128(uint32_t smem_address,
-                                                             uint32_t mn_atom_bytes) {
-  uint64_t desc = 0;
-  desc |= static_cast<uint64_t>((smem_address & 0x3FFFFU) >> 4);
-  desc |= static_cast<uint64_t>(mn_atom_bytes >> 4) << 16;
-  desc |= static_cast<uint64_t>(1024 >> 4) << 32;
-  desc |= static_cast<uint64_t>(1) << 46;
-  desc |= static_cast<uint64_t>(2) << 61;
-  return desc;
-}
-
 struct TcArguments {
   AttentionArguments a;
   int *device_error;
@@ -417,7 +403,7 @@ pv_tc_kernel(const __grid_constant__ CUtensorMap value_map,
               2ULL * (step % 4);
 #pragma unroll
           for (int slice = 0; slice < Shape::slices; ++slice) {
-            const uint64_t value_desc = umma_desc_mn_major_sw128(
+            const uint64_t value_desc = ptx::umma_desc_mn_major_sw128(
                 values + 2 * slice * Shape::box_bytes + step * 2048, Shape::box_bytes);
             ptx::tcgen05_mma_f16(tmem_base + slice * padded_rows, value_desc, score_desc, idesc,
                                  (item > 0 || step > 0) ? 1U : 0U);
@@ -571,6 +557,15 @@ int launch_tc_rows(const AttentionArguments &a, int *device_error, cudaStream_t 
   }
 }
 
+// CARAT_B200_FUSED_ATTENTION=0 keeps the three-kernel path everywhere (for comparisons).
+bool fused_enabled() {
+  static const bool enabled = [] {
+    const char *configured = std::getenv("CARAT_B200_FUSED_ATTENTION");
+    return configured == nullptr || configured[0] != '0';
+  }();
+  return enabled;
+}
+
 } // namespace
 
 int make_attention_maps(AttentionMaps *maps, const void *key_cache, const void *value_cache,
@@ -589,6 +584,11 @@ int make_attention_maps(AttentionMaps *maps, const void *key_cache, const void *
       !encode_bf16_rows(&result.queries, queries, query_rows, head_dim, padded_rows) ||
       !encode_bf16_rows(&result.scores, scores, score_rows, score_stride, padded_rows)) {
     return -5;
+  }
+  if (head_dim == 256) {
+    if (!encode_bf16_rows(&result.values32, value_cache, cache_rows, head_dim, 32))
+      return -5;
+    result.has_fused = 1;
   }
   if (staged_keys != nullptr) {
     if (!encode_bf16_rows(&result.new_keys, staged_keys, staged_rows, head_dim, proposal_columns) ||
@@ -612,6 +612,8 @@ int launch_attention_tc(const AttentionArguments &a, cudaStream_t stream) {
   int *device_error = device_error_word();
   if (device_error == nullptr)
     return -101;
+  if (attention_fused_applies(a) && fused_enabled())
+    return launch_attention_fused(a, device_error, stream);
   switch (a.head_dim) {
   case 256:
     return launch_tc_rows<256>(a, device_error, stream);

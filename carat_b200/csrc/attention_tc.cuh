@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda.h>
+#include <cuda_runtime.h>
 
 namespace carat_b200 {
 
@@ -14,6 +15,8 @@ struct AttentionMaps {
   CUtensorMap queries;     // [query rows, head_dim], box padded_rows rows
   CUtensorMap scores;      // [score rows, score_stride], box padded_rows rows x 64 columns
   int padded_rows;         // UMMA N: 16, 48 or 80 (>= query_heads / kv_heads * depth)
+  CUtensorMap values32;    // cache V with 32-row boxes (head_dim 256 only), for the one-kernel path
+  int has_fused;           // values32 is encoded
 };
 
 // UMMA N for `rows` query rows per KV head, or 0 when there are too many.
@@ -29,5 +32,14 @@ int make_attention_maps(AttentionMaps *maps, const void *key_cache, const void *
                         long long staged_rows, const void *queries, long long query_rows,
                         const void *scores, long long score_rows, int score_stride, int head_dim,
                         int padded_rows);
+
+struct AttentionArguments;
+
+// The one-kernel path (scores, softmax and P.V inside one CTA per (request, kv head)): head_dim
+// 256, at most 16 query rows per KV head, at most 1024 cache rows, a single chunk, and either
+// staged proposals or drafter semantics.
+bool attention_fused_applies(const AttentionArguments &arguments);
+int launch_attention_fused(const AttentionArguments &arguments, int *device_error,
+                           cudaStream_t stream);
 
 } // namespace carat_b200

@@ -71,6 +71,14 @@ __device__ __forceinline__ bool mbarrier_wait_bounded(uint32_t bar, uint32_t par
   }
 }
 
+// The same wait for single-thread issue loops, where every instruction of the loop body is on the
+// critical path: the common case (the phase has already completed) costs one try_wait.
+__device__ __forceinline__ bool mbarrier_wait_fast(uint32_t bar, uint32_t parity) {
+  if (mbarrier_try_wait(bar, parity))
+    return true;
+  return mbarrier_wait_bounded(bar, parity);
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ uint64_t policy_evict_first() {
   uint64_t policy;
@@ -165,6 +173,42 @@ __device__ __forceinline__ void tcgen05_mma_f16(uint32_t tmem_d, uint64_t desc_a
                : "memory");
 }
 
+// Variants for issue loops. The descriptors travel as 32-bit halves so that stepping along K or to
+// the next pipeline stage is one 32-bit add on the low word (the start-address field; it cannot
+// carry into the neighbouring field while the tile stays inside shared memory), and the
+// accumulate flag is usually a constant the compiler folds.
+__device__ __forceinline__ void tcgen05_mma_f16_split(uint32_t tmem_d, uint32_t a_low,
+                                                      uint32_t a_high, uint32_t b_low,
+                                                      uint32_t b_high, uint32_t idesc,
+                                                      uint32_t accumulate) {
+  asm volatile("{\n\t"
+               ".reg .pred p;\n\t"
+               ".reg .b64 da, db;\n\t"
+               "setp.ne.b32 p, %6, 0;\n\t"
+               "mov.b64 da, {%1, %2};\n\t"
+               "mov.b64 db, {%3, %4};\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+               "}" ::"r"(tmem_d),
+               "r"(a_low), "r"(a_high), "r"(b_low), "r"(b_high), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_mma_f8f6f4_split(uint32_t tmem_d, uint32_t a_low,
+                                                         uint32_t a_high, uint32_t b_low,
+                                                         uint32_t b_high, uint32_t idesc,
+                                                         uint32_t accumulate) {
+  asm volatile("{\n\t"
+               ".reg .pred p;\n\t"
+               ".reg .b64 da, db;\n\t"
+               "setp.ne.b32 p, %6, 0;\n\t"
+               "mov.b64 da, {%1, %2};\n\t"
+               "mov.b64 db, {%3, %4};\n\t"
+               "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %5, p;\n\t"
+               "}" ::"r"(tmem_d),
+               "r"(a_low), "r"(a_high), "r"(b_low), "r"(b_high), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+
 // Each thread of the warp reads 32 consecutive fp32 columns of its own TMEM lane
 // (lane = 32 * (warp % 4) + laneid).
 __device__ __forceinline__ void tmem_load_32x32b_x32(uint32_t taddr, uint32_t (&v)[32]) {
@@ -205,6 +249,20 @@ __device__ __forceinline__ uint64_t umma_desc_k_major_sw128(uint32_t smem_addres
   uint64_t desc = 0;
   desc |= static_cast<uint64_t>((smem_address & 0x3FFFFU) >> 4);
   desc |= static_cast<uint64_t>(1) << 16;
+  desc |= static_cast<uint64_t>(1024 >> 4) << 32;
+  desc |= static_cast<uint64_t>(1) << 46;
+  desc |= static_cast<uint64_t>(2) << 61;
+  return desc;
+}
+
+// MN-major operand written by TMA as [rows = K index][64 elements = MN index] with the 128-byte
+// swizzle: eight K rows form one 1024-byte atom (SBO), the next 64 MN elements live in the next
+// TMA box `mn_atom_bytes` further (LBO).
+__device__ __forceinline__ uint64_t umma_desc_mn_major_sw128(uint32_t smem_address,
+                                                             uint32_t mn_atom_bytes) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((smem_address & 0x3FFFFU) >> 4);
+  desc |= static_cast<uint64_t>(mn_atom_bytes >> 4) << 16;
   desc |= static_cast<uint64_t>(1024 >> 4) << 32;
   desc |= static_cast<uint64_t>(1) << 46;
   desc |= static_cast<uint64_t>(2) << 61;

@@ -70,21 +70,33 @@ def attention(head_dim=256, heads=32, kv_heads=16, window=1024, capacity=1024, p
     positions = torch.full((requests,), position, dtype=torch.int32, device="cuda")
     out = torch.empty(requests * depth, heads * head_dim, dtype=torch.bfloat16, device="cuda")
     scores = torch.empty(requests * heads * depth * stride, dtype=torch.bfloat16, device="cuda")
-    for _ in range(launches):
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    for launch in range(launches):
+        if launch == 1:
+            start.record()
         check(library.carat_b200_verify_attention(
             _ptr(queries), _ptr(keys), _ptr(values), _ptr(new_keys), _ptr(new_values),
             _ptr(positions), _ptr(out), _ptr(scores), stride, requests, depth, heads, kv_heads,
             head_dim, capacity, window, position, None))
+    stop.record()
     torch.cuda.synchronize()
+    if launches > 1:
+        print(f"attention head_dim={head_dim}: {start.elapsed_time(stop) / (launches - 1) * 1e3:.1f} us "
+              f"per call over {launches - 1} calls")
 
 
-def global_attention():
-    attention(head_dim=512, heads=32, kv_heads=4, window=0, capacity=8192, position=4096)
+def global_attention(launches=3):
+    attention(head_dim=512, heads=32, kv_heads=4, window=0, capacity=8192, position=4096,
+              launches=launches)
 
 
 CASES = {"linear": linear, "lm_head": lm_head, "attention": attention, "global": global_attention}
 
 if __name__ == "__main__":
     name = sys.argv[1] if len(sys.argv) > 1 else "linear"
-    CASES[name]()
+    if len(sys.argv) > 2:
+        CASES[name](launches=int(sys.argv[2]))
+    else:
+        CASES[name]()
     print(f"profile case {name} done")
