@@ -173,11 +173,15 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
   ptx::tcgen05_fence_after_thread_sync();
   const uint32_t tmem_base = tmem_base_slot;
 
+  // The TMA and MMA roles are single threads whose loop bodies are the critical path (a dependent
+  // instruction costs several cycles and nothing hides it), so both keep a running ring cursor and
+  // precomputed descriptor words instead of dividing and rebuilding descriptors per K block.
   if (warp == 0) {
     if (lane == 0) {
       const uint64_t stream_policy = ptx::policy_evict_first();
       const uint64_t reuse_policy = ptx::policy_evict_last();
-      int issued = 0;
+      uint32_t stage = 0;
+      uint32_t phase = 0;
       bool healthy = true;
       // The weights are static: the first ring of weight tiles is requested before the grid this
       // launch depends on has finished. The activation tiles of those stages follow once it has.
@@ -195,70 +199,84 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
       grid_dependency_wait();
       for (int index = first_item; index < items && healthy; index += item_stride) {
         const WorkItem item = decode_item(args, index);
-        for (int block = 0; block < item.k_count; ++block, ++issued) {
-          const int stage = issued % stages;
-          const uint32_t phase = static_cast<uint32_t>(issued / stages) & 1U;
-          const int k_byte = (item.k_begin + block) * tile_k_bytes;
-          if (issued >= early) {
-            if (!ptx::mbarrier_wait_bounded(empty_bar + 8U * stage, phase ^ 1U)) {
+        const int feature0 = item.tile * tile_features;
+        int k_byte = item.k_begin * tile_k_bytes;
+        for (int block = 0; block < item.k_count; ++block, k_byte += tile_k_bytes) {
+          const uint32_t full = full_bar + 8U * stage;
+          if (early > 0) {
+            --early;     // this stage's weight tile is already on its way
+          } else {
+            if (!ptx::mbarrier_wait_fast(empty_bar + 8U * stage, phase ^ 1U)) {
               healthy = false;
               atomicExch(args.device_error, 1);
               break;
             }
-            ptx::mbarrier_arrive_expect_tx(full_bar + 8U * stage, stage_bytes);
+            ptx::mbarrier_arrive_expect_tx(full, stage_bytes);
             ptx::tma_load_2d(weight_tiles + stage * weight_tile_bytes, &weight_map, k_byte,
-                             item.tile * tile_features, full_bar + 8U * stage, stream_policy);
+                             feature0, full, stream_policy);
           }
-          ptx::tma_load_2d(input_tiles + stage * input_tile_bytes, &input_map, k_byte, 0,
-                           full_bar + 8U * stage, reuse_policy);
+          ptx::tma_load_2d(input_tiles + stage * input_tile_bytes, &input_map, k_byte, 0, full,
+                           reuse_policy);
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1U;
+          }
         }
       }
       if (!healthy) {
-        // Let copies already in flight land before the CTA gives its shared memory back.
-        const int first = issued > stages ? issued - stages : 0;
-        for (int block = first; block < issued; ++block)
-          ptx::mbarrier_wait_bounded(full_bar + 8U * (block % stages),
-                                     static_cast<uint32_t>(block / stages) & 1U);
+        // Let copies already in flight land before the CTA gives its shared memory back: wait
+        // for the phase each stage was last armed for.
+        for (uint32_t other = 0; other < static_cast<uint32_t>(stages); ++other)
+          ptx::mbarrier_wait_bounded(full_bar + 8U * other, other < stage ? phase : phase ^ 1U);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      int consumed = 0;
-      int local = 0;
+      const uint64_t weight_desc = ptx::umma_desc_k_major_sw128(weight_tiles);
+      const uint64_t input_desc = ptx::umma_desc_k_major_sw128(input_tiles);
+      const uint32_t desc_high = static_cast<uint32_t>(weight_desc >> 32);
+      const uint32_t weight_low = static_cast<uint32_t>(weight_desc);
+      const uint32_t input_low = static_cast<uint32_t>(input_desc);
+      uint32_t stage = 0;
+      uint32_t phase = 0;
+      uint32_t buffer = 0;
+      uint32_t buffer_phase = 0;
       bool healthy = true;
-      for (int index = first_item; index < items && healthy; index += item_stride, ++local) {
+      for (int index = first_item; index < items && healthy; index += item_stride) {
         const WorkItem item = decode_item(args, index);
-        const int buffer = local & 1;
-        const uint32_t use = static_cast<uint32_t>(local >> 1);
-        if (!ptx::mbarrier_wait_bounded(acc_empty_bar + 8U * buffer, (use & 1U) ^ 1U)) {
+        if (!ptx::mbarrier_wait_fast(acc_empty_bar + 8U * buffer, buffer_phase ^ 1U)) {
           atomicExch(args.device_error, 4);
           break;
         }
         ptx::tcgen05_fence_after_thread_sync();
-        for (int block = 0; block < item.k_count; ++block, ++consumed) {
-          const int stage = consumed % stages;
-          const uint32_t phase = static_cast<uint32_t>(consumed / stages) & 1U;
-          if (!ptx::mbarrier_wait_bounded(full_bar + 8U * stage, phase)) {
+        const uint32_t accumulator = tmem_base + buffer * padded_rows;
+        for (int block = 0; block < item.k_count; ++block) {
+          if (!ptx::mbarrier_wait_fast(full_bar + 8U * stage, phase)) {
             healthy = false;
             atomicExch(args.device_error, 2);
             break;
           }
           ptx::tcgen05_fence_after_thread_sync();
-          const uint64_t weight_desc =
-              ptx::umma_desc_k_major_sw128(weight_tiles + stage * weight_tile_bytes);
-          const uint64_t input_desc =
-              ptx::umma_desc_k_major_sw128(input_tiles + stage * input_tile_bytes);
+          const uint32_t a_low = weight_low + stage * (weight_tile_bytes >> 4);
+          const uint32_t b_low = input_low + stage * (input_tile_bytes >> 4);
+          // +32 bytes along K inside the swizzle atom = +2 in the 16-byte address field.
+          ptx::tcgen05_mma_f8f6f4_split(accumulator, a_low, desc_high, b_low, desc_high, idesc,
+                                        block > 0 ? 1U : 0U);
 #pragma unroll
-          for (int step = 0; step < tile_k_bytes / umma_k; ++step) {
-            // +32 bytes along K inside the swizzle atom = +2 in the 16-byte address field.
-            ptx::tcgen05_mma_f8f6f4(tmem_base + buffer * padded_rows, weight_desc + 2ULL * step,
-                                    input_desc + 2ULL * step, idesc,
-                                    (block > 0 || step > 0) ? 1U : 0U);
-          }
+          for (int step = 1; step < tile_k_bytes / umma_k; ++step)
+            ptx::tcgen05_mma_f8f6f4_split(accumulator, a_low + 2 * step, desc_high,
+                                          b_low + 2 * step, desc_high, idesc, 1U);
           ptx::tcgen05_commit(empty_bar + 8U * stage);
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1U;
+          }
         }
         if (healthy)
           ptx::tcgen05_commit(acc_full_bar + 8U * buffer);
+        buffer ^= 1U;
+        if (buffer == 0)
+          buffer_phase ^= 1U;
       }
     }
   } else {

@@ -33,10 +33,18 @@ def linear(rows=120, k=5376, n=43008, launches=4):
     out = torch.empty(rows, n, dtype=torch.bfloat16, device="cuda")
     need = library.carat_b200_fp8_linear_workspace_bytes(rows, k, n)
     work = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
-    for _ in range(launches):
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    for launch in range(launches):
+        if launch == 1:
+            start.record()
         check(library.carat_b200_fp8_linear(_ptr(x), _ptr(scale), _ptr(w), _ptr(scale), _ptr(out),
                                             rows, k, n, _ptr(work), need, None))
+    stop.record()
     torch.cuda.synchronize()
+    if launches > 1:
+        micro = start.elapsed_time(stop) / (launches - 1) * 1e3
+        print(f"linear {rows}x{k}x{n}: {micro:.1f} us per call, {k * n / micro / 1e6:.2f} TB/s of weights")
 
 
 def lm_head(rows=120, k=5376, n=262144, launches=3):
@@ -45,10 +53,18 @@ def lm_head(rows=120, k=5376, n=262144, launches=3):
     scale = torch.full((1,), 0.01, dtype=torch.float32, device="cuda")
     tokens = torch.empty(rows, dtype=torch.int32, device="cuda")
     keys = torch.empty(rows, dtype=torch.int64, device="cuda")
-    for _ in range(launches):
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    for launch in range(launches):
+        if launch == 1:
+            start.record()
         check(library.carat_b200_fp8_linear_argmax(_ptr(x), _ptr(scale), _ptr(w), _ptr(scale),
                                                    _ptr(tokens), _ptr(keys), rows, k, n, None))
+    stop.record()
     torch.cuda.synchronize()
+    if launches > 1:
+        micro = start.elapsed_time(stop) / (launches - 1) * 1e3
+        print(f"lm head {rows}x{k}x{n}: {micro:.1f} us per call, {k * n / micro / 1e6:.2f} TB/s of weights")
 
 
 def attention(head_dim=256, heads=32, kv_heads=16, window=1024, capacity=1024, position=3000,
@@ -95,7 +111,9 @@ CASES = {"linear": linear, "lm_head": lm_head, "attention": attention, "global":
 
 if __name__ == "__main__":
     name = sys.argv[1] if len(sys.argv) > 1 else "linear"
-    if len(sys.argv) > 2:
+    if len(sys.argv) > 4:
+        CASES[name](launches=int(sys.argv[2]), k=int(sys.argv[3]), n=int(sys.argv[4]))
+    elif len(sys.argv) > 2:
         CASES[name](launches=int(sys.argv[2]))
     else:
         CASES[name]()
