@@ -51,6 +51,12 @@ struct AttentionArguments {
                              // (see attention_geometry.cuh); sizes the grids
   // Tensor maps for the tensor-core kernels (null: the CUDA-core kernels run).
   const struct AttentionMaps *maps;
+  // Scratch of the two-kernel tensor-core path: one (maximum, sum of exp) pair per score row and
+  // chunk, [score rows, stats_stride] with stats_stride >= chunks.
+  float2 *stats;
+  int stats_stride;
+  int sum_chunks;            // chunks > 1 only: also sum the chunk partials into `output` (bf16);
+                             // otherwise the consumer of `chunk_partials` does the sum
   int draft;                 // 1: drafter semantics (depth == 1, no proposal rows, the first
                              //    min(position + 1, capacity) cache rows are visible)
 };
@@ -62,6 +68,9 @@ int launch_attention_simt(const AttentionArguments &arguments, cudaStream_t stre
 // Tensor-core implementation (tcgen05 + TMA): head_dim 256 or 512, capacity a multiple of 128,
 // arguments.maps set. Same phases, same rounding points.
 int launch_attention_tc(const AttentionArguments &arguments, cudaStream_t stream);
+
+// Kernels launch_attention_tc launches for these arguments (the CUDA-core path launches three).
+int attention_tc_launches(const AttentionArguments &arguments);
 
 // Argument checks shared by both implementations (0 = fine).
 int validate_attention(const AttentionArguments &arguments);

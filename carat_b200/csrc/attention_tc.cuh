@@ -9,14 +9,12 @@ namespace carat_b200 {
 
 struct AttentionMaps {
   CUtensorMap keys;        // cache K as [slots * kv_heads * capacity, head_dim], box 128 rows
-  CUtensorMap values;      // cache V, same view, box 128 rows (head_dim 256) or 64 rows (512)
   CUtensorMap new_keys;    // staged proposals as [requests * kv_heads * depth, head_dim], box 16 rows
   CUtensorMap new_values;
   CUtensorMap queries;     // [query rows, head_dim], box padded_rows rows
-  CUtensorMap scores;      // [score rows, score_stride], box padded_rows rows x 64 columns
   int padded_rows;         // UMMA N: 16, 48 or 80 (>= query_heads / kv_heads * depth)
-  CUtensorMap values32;    // cache V with 32-row boxes (head_dim 256 only), for the one-kernel path
-  int has_fused;           // values32 is encoded
+  CUtensorMap values32;    // cache V with 32-row boxes
+  int has_fused;           // head_dim 256: the one-kernel path may be used
 };
 
 // UMMA N for `rows` query rows per KV head, or 0 when there are too many.
@@ -41,5 +39,11 @@ struct AttentionArguments;
 bool attention_fused_applies(const AttentionArguments &arguments);
 int launch_attention_fused(const AttentionArguments &arguments, int *device_error,
                            cudaStream_t stream);
+
+// The two-kernel path for everything else the tensor cores cover (head_dim 256 or 512, any number
+// of chunks): persistent scores kernel with per-chunk softmax statistics, persistent P.V kernel
+// that builds the probabilities on the fly. Needs arguments.stats.
+int launch_attention_stream(const AttentionArguments &arguments, int *device_error,
+                            cudaStream_t stream);
 
 } // namespace carat_b200

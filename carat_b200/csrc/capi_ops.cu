@@ -241,6 +241,45 @@ int run_verify_attention(bool tensor_cores, const void *bf16_queries, const void
       set_last_error("verify attention: tensor map encoding failed");
       return status;
     }
+    // One (maximum, sum) pair per score row: scratch of the two-kernel path, kept for the
+    // library's life and grown when a call needs more (cudaFree waits for the device first).
+    static float2 *stats = nullptr;
+    static long long stats_rows = 0;
+    static float *partials = nullptr;
+    static size_t partial_bytes = 0;
+    constexpr int long_chunk_keys = 1024;
+    if (!staged && a.max_cache_rows > long_chunk_keys) {
+      // Long linear caches are cut into chunks like the runner does; the chunk partials live in
+      // library scratch and are summed into the caller's output.
+      a.chunk_keys = long_chunk_keys;
+      a.chunks = attention_chunks(a.max_cache_rows, long_chunk_keys);
+      a.sum_chunks = 1;
+      const size_t need = sizeof(float) * static_cast<size_t>(a.chunks) * requests * depth *
+                          query_heads * head_dim;
+      if (need > partial_bytes) {
+        if (partials != nullptr)
+          cudaFree(partials);
+        partials = nullptr;
+        partial_bytes = 0;
+        if (check_cuda(cudaMalloc(&partials, need), "allocate attention chunk partials") != 0)
+          return -100;
+        partial_bytes = need;
+      }
+      a.chunk_partials = partials;
+    }
+    const long long stats_need = score_rows * a.chunks;
+    if (stats_need > stats_rows) {
+      if (stats != nullptr)
+        cudaFree(stats);
+      stats = nullptr;
+      stats_rows = 0;
+      if (check_cuda(cudaMalloc(&stats, sizeof(float2) * static_cast<size_t>(stats_need)),
+                     "allocate attention statistics") != 0)
+        return -100;
+      stats_rows = stats_need;
+    }
+    a.stats = stats;
+    a.stats_stride = a.chunks;
     a.maps = &maps;
     return finish(launch_attention_tc(a, cuda_stream), "verify attention");
   }

@@ -165,6 +165,8 @@ struct carat_b200_runner {
   DeviceBuffer attention_out;
   DeviceBuffer attention_partials;
   DeviceBuffer scores;
+  DeviceBuffer attention_stats;   // float2 [score rows, global chunks]
+  int stats_stride{0};
   DeviceBuffer projected;    // bf16 output of a linear that did not split K
   DeviceBuffer gate_up;
   DeviceBuffer split_partials;  // fp32 [splits, rows, width] left for a fused consumer
@@ -342,6 +344,9 @@ void build_runner(Runner &runner, const carat_b200_model_config &config,
     most_heads = std::max(most_heads, layer.shape.query_heads);
   runner.scores.allocate(static_cast<size_t>(rows) * most_heads *
                          std::max(runner.score_stride_sliding, runner.score_stride_global) * 2);
+  runner.stats_stride = global_chunks;
+  runner.attention_stats.allocate(static_cast<size_t>(rows) * most_heads * global_chunks *
+                                  sizeof(float2));
   runner.projected.allocate(row_hidden);
   runner.gate_up.allocate(static_cast<size_t>(rows) * 2 * config.intermediate_size * 2);
   // Split-K partials [splits, rows, features] fp32; plans that would need more are rejected.
@@ -700,11 +705,13 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
       attention.chunk_keys = (layer.capacity + 127) / 128 * 128;
       attention.chunks = 1;
     }
+    attention.stats = runner.attention_stats.get<float2>();
+    attention.stats_stride = runner.stats_stride;
     attention.maps = verify_attention_maps(runner, index, depth);
     require_launch(attention.maps != nullptr ? launch_attention_tc(attention, stream)
                                              : launch_attention_simt(attention, stream),
                    "verify attention");
-    runner.launches += 3;
+    runner.launches += attention.maps != nullptr ? attention_tc_launches(attention) : 3;
 
     require_launch(launch_quant(attention.chunks > 1 ? nullptr : runner.attention_out.get(),
                                 attention.chunks > 1 ? runner.attention_partials.get<float>()
@@ -920,11 +927,13 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
       attention.score_stride = runner.score_stride_global;
       attention.chunk_keys = global_chunk_keys;
       attention.chunks = attention_chunks(attention.max_cache_rows, global_chunk_keys);
+      attention.stats = runner.attention_stats.get<float2>();
+      attention.stats_stride = runner.stats_stride;
       attention.maps = draft_attention_maps(runner, index);
       require_launch(attention.maps != nullptr ? launch_attention_tc(attention, stream)
                                                : launch_attention_simt(attention, stream),
                      "assistant attention");
-      runner.launches += 3;
+      runner.launches += attention.maps != nullptr ? attention_tc_launches(attention) : 3;
       require_launch(launch_quant(attention.chunks > 1 ? nullptr : runner.a_attention_out.get(),
                                   attention.chunks > 1 ? runner.a_attention_partials.get<float>()
                                                        : nullptr,
