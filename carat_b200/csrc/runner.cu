@@ -1055,6 +1055,33 @@ extern "C" int carat_b200_runner_verify_greedy_proposals(
   });
 }
 
+extern "C" int carat_b200_runner_append_ragged(carat_b200_runner *runner, const int *token_ids,
+                                               const int *slots, int count, int *next_tokens) {
+  return guarded([&] {
+    if (runner == nullptr || token_ids == nullptr || slots == nullptr || next_tokens == nullptr ||
+        count <= 0 || count > runner->batch) {
+      throw Failure{"invalid ragged token batch"};
+    }
+    std::vector<bool> seen(static_cast<size_t>(runner->batch), false);
+    for (int row = 0; row < count; ++row) {
+      const int slot = slots[row];
+      if (slot < 0 || slot >= runner->batch || seen[static_cast<size_t>(slot)] ||
+          token_ids[row] < 0 || token_ids[row] >= runner->config.vocabulary_size) {
+        throw Failure{"invalid or repeated ragged slot"};
+      }
+      seen[static_cast<size_t>(slot)] = true;
+      const int position = runner->slot_positions[static_cast<size_t>(slot)];
+      if (position <= 0 || position >= runner->maximum_context)
+        throw Failure{"ragged slot is empty or full"};
+    }
+    // One row per slot whose only proposal is the forced token: it is always accepted, its KV
+    // rows are committed, the position advances by one and the prediction is the next token.
+    std::vector<int> accepted(static_cast<size_t>(count));
+    verify_step(*runner, token_ids, count, 1, token_ids, slots, nullptr, 0, false,
+                accepted.data(), next_tokens);
+  });
+}
+
 extern "C" int carat_b200_runner_draft(carat_b200_runner *runner, const int *last_tokens,
                                        const int *slots, const int *forced_first_tokens,
                                        int requests, int depth, int *proposals_out) {

@@ -269,6 +269,17 @@ class Gemma4BatchModelRunner:
             caps, flags, accepted, next_tokens))
         return GreedyVerificationResult(list(accepted), list(next_tokens))
 
+    def append_ragged(self, token_ids: Sequence[int], slots: Sequence[int]) -> List[int]:
+        """Plain decode, one token per listed slot; returns the greedy next tokens
+        (Gemma4BatchModelRunner::append_ragged, cuda/batch_model_runner.cu:1544-1615)."""
+        active = len(token_ids)
+        if active == 0 or len(slots) != active:
+            raise CaratError("invalid ragged token batch")
+        next_tokens = (ctypes.c_int * active)()
+        check(self._library.carat_b200_runner_append_ragged(
+            self._handle, int_array(token_ids), int_array(slots), active, next_tokens))
+        return list(next_tokens)
+
     def has_assistant(self) -> bool:
         return bool(self._library.carat_b200_runner_has_assistant(self._handle))
 

@@ -340,6 +340,18 @@ CARAT_B200_API int carat_b200_runner_verify_greedy_proposals(carat_b200_runner *
                                               const int *maximum_accepted_tokens, int flags,
                                               int *accepted_tokens, int *next_tokens);
 
+/* Plain decode: token_ids[row] becomes resident in slots[row] (each slot at most once, none empty
+ * or full), every listed slot advances by one position, and next_tokens[row] receives the greedy
+ * next token. The forward is the verify forward with one row per slot, so the slot's final hidden
+ * state for the drafter is refreshed as well. Returns after the results are on the host. Error
+ * texts match the reference's exceptions ("invalid ragged token batch", "invalid or repeated
+ * ragged slot", "ragged slot is empty or full"). Replaces Gemma4BatchModelRunner::append_ragged
+ * (include/carat/batch_model_runner.h:55, cuda/batch_model_runner.cu:1544-1615); the reference's
+ * launch-graph cache for this call has no counterpart because the step is a short chain of
+ * dependent launches already overlapped by programmatic dependent launch. */
+CARAT_B200_API int carat_b200_runner_append_ragged(carat_b200_runner *runner, const int *token_ids,
+                                                   const int *slots, int count, int *next_tokens);
+
 /* proposals_out is [requests][depth]. forced_first_tokens may be NULL. Replaces
  * Gemma4BatchModelRunner::draft_four and Gemma4AssistantRunner::draft_four
  * (include/carat/batch_model_runner.h:62-65, include/carat/assistant_runner.h:20-26,

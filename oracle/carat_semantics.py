@@ -607,6 +607,28 @@ class OracleRunner:
             next_token = next_tokens[0]
         return next_token
 
+    def append_ragged(self, token_ids: Sequence[int], slots: Sequence[int]) -> List[int]:
+        """Plain decode, one token per listed slot (cuda/batch_model_runner.cu:1544-1615): the
+        token becomes resident at the slot's position, the position advances by one, and the
+        greedy next token comes back. The forward is the verify forward with one row per slot
+        (same norms, tensor-scale e4m3 linears, ring attention and tied LM head; the reference's
+        decode kernels differ from its verify kernels only in launch shape), so it is restated
+        as a depth-1 verification whose single proposal is the forced token itself."""
+        active = len(token_ids)
+        if active <= 0 or active > self.slots or len(slots) != active:
+            raise RuntimeError("invalid ragged token batch")
+        seen = set()
+        for token, slot in zip(token_ids, slots):
+            if (slot < 0 or slot >= self.slots or slot in seen or token < 0
+                    or token >= self.config.vocab):
+                raise RuntimeError("invalid or repeated ragged slot")
+            seen.add(slot)
+            if self.positions[slot] <= 0 or self.positions[slot] >= self.config.max_context:
+                raise RuntimeError("ragged slot is empty or full")
+        _, next_tokens = self.verify_greedy_proposals([[token] for token in token_ids],
+                                                      list(token_ids), list(slots))
+        return next_tokens
+
     def seed_empty_cache_for_benchmark(self, position: int):
         """cuda/batch_model_runner.cu seed_empty_cache_for_benchmark: zero KV, advance positions."""
         for index in range(len(self.config.layers)):

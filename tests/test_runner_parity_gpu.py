@@ -210,6 +210,41 @@ def test_injected_accept_lengths(pair):
         assert device.slot_position(slot) == starts[request] + caps[request]
 
 
+def test_append_ragged_plain_decode(pair):
+    """Plain decode (append_ragged) against the oracle, teacher-forced: both sides append the same
+    tokens to the same slots; next tokens must agree or be a near-tie in the oracle's logits, and
+    positions and the drafter's hidden hand-off must follow."""
+    config, oracle, device, _ = pair
+    import carat_b200
+    generator = torch.Generator().manual_seed(11)
+    flagged = 0
+    for step, slots in enumerate([[0, 1, 2, 3], [2, 0], [3], [1, 3, 0]]):
+        tokens = torch.randint(3, config.vocab, (len(slots),), generator=generator).tolist()
+        starts = [device.slot_position(slot) for slot in slots]
+        scout = copy.deepcopy(oracle)
+        _, _, trace = scout.verify_greedy_proposals([[t] for t in tokens], tokens, slots,
+                                                    trace=True)
+        want = oracle.append_ragged(tokens, slots)
+        got = device.append_ragged(tokens, slots)
+        hidden = device.last_final_hidden(len(slots))
+        assert rms_relative_error(hidden, trace.final_hidden) < TOLERANCE
+        for row, slot in enumerate(slots):
+            assert device.slot_position(slot) == starts[row] + 1 == oracle.positions[slot]
+            if got[row] != want[row]:
+                assert near_tie(trace, row, got[row]), (step, row, got[row], want[row])
+                flagged += 1
+        by_slot = device.target_hidden_slots()
+        for row, slot in enumerate(slots):
+            assert rms_relative_error(by_slot[slot], oracle.target_hidden[slot]) < TOLERANCE
+    print(f"append_ragged: {flagged} near-tie predictions flagged")
+    with pytest.raises(carat_b200.CaratError, match="invalid ragged token batch"):
+        device.append_ragged([5, 6, 7, 8, 9], [0, 1, 2, 3, 0])
+    with pytest.raises(carat_b200.CaratError, match="invalid or repeated ragged slot"):
+        device.append_ragged([5, 6], [1, 1])
+    with pytest.raises(carat_b200.CaratError, match="invalid or repeated ragged slot"):
+        device.append_ragged([config.vocab], [1])
+
+
 def test_argument_errors_match_the_reference(pair):
     config, oracle, device, _ = pair
     import carat_b200
@@ -224,3 +259,5 @@ def test_argument_errors_match_the_reference(pair):
         device.verify_greedy_proposals([[5, 6]], [5], [3])
     with pytest.raises(carat_b200.CaratError, match="assistant slot is empty or invalid"):
         device.draft_four([5], [3], (), 2)
+    with pytest.raises(carat_b200.CaratError, match="ragged slot is empty or full"):
+        device.append_ragged([5], [3])
