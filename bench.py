@@ -474,8 +474,10 @@ def barrier(world):
 def reduce_max_and_sum(world, maxima, sums):
     if world == 1:
         return maxima, sums
-    m = torch.tensor(maxima, dtype=torch.float64, device="cuda")
-    s = torch.tensor(sums, dtype=torch.float64, device="cuda")
+    # NCCL reduces device tensors; the CPU tests of this plumbing run it over gloo.
+    device = "cuda" if torch.distributed.get_backend() == "nccl" else "cpu"
+    m = torch.tensor(maxima, dtype=torch.float64, device=device)
+    s = torch.tensor(sums, dtype=torch.float64, device=device)
     torch.distributed.all_reduce(m, op=torch.distributed.ReduceOp.MAX)
     torch.distributed.all_reduce(s, op=torch.distributed.ReduceOp.SUM)
     return m.tolist(), s.tolist()

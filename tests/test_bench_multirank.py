@@ -1,0 +1,98 @@
+"""The N > 1 plumbing of bench.py on CPU: two gloo ranks on the loopback address.
+
+Replicas share nothing on the data path (one runner per GPU, slots never migrate), so what has to
+be right is the aggregation: the timed region's duration is the maximum over ranks, the token count
+the sum, every rank takes a different seeded workload, and only rank 0 prints.
+"""
+import json
+import os
+import socket
+import subprocess
+import sys
+import textwrap
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = textwrap.dedent("""
+    import json, os, sys
+    sys.path.insert(0, os.environ["CARAT_ROOT"])
+    import torch
+    import bench
+    rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+    torch.distributed.init_process_group("gloo")
+    bench.barrier(world)
+    maxima, sums = bench.reduce_max_and_sum(world, [10.0 + rank, 5.0 - rank], [100.0 * (rank + 1)])
+    lengths = bench.accept_lengths(4, seed=7 + rank)
+    contexts = bench.context_lengths(seed=3 + rank)
+    bench.barrier(world)
+    with open(os.path.join(os.environ["CARAT_OUT"], f"rank{rank}.json"), "w") as out:
+        json.dump({"rank": rank, "maxima": maxima, "sums": sums,
+                   "lengths": lengths.tolist(), "contexts": contexts}, out)
+    torch.distributed.destroy_process_group()
+""")
+
+
+def free_port():
+    with socket.socket() as probe:
+        probe.bind(("127.0.0.1", 0))
+        return probe.getsockname()[1]
+
+
+def launch(script_path, out_dir, extra_args=()):
+    environment = dict(os.environ, CARAT_ROOT=ROOT, CARAT_OUT=str(out_dir))
+    command = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+               "--master-addr", "127.0.0.1", "--master-port", str(free_port()), script_path,
+               *extra_args]
+    return subprocess.run(command, capture_output=True, text=True, timeout=600, env=environment,
+                          cwd=ROOT)
+
+
+def test_two_ranks_aggregate_max_time_and_sum_tokens(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    done = launch(str(script), tmp_path)
+    assert done.returncode == 0, done.stderr[-2000:]
+    records = [json.loads((tmp_path / f"rank{rank}.json").read_text()) for rank in (0, 1)]
+    assert [record["rank"] for record in records] == [0, 1]
+    for record in records:
+        assert record["maxima"] == [11.0, 5.0]      # slowest rank's time, per entry
+        assert record["sums"] == [300.0]            # tokens of all ranks
+    # Each replica draws its own workload from its own seed.
+    assert records[0]["lengths"] != records[1]["lengths"]
+    assert records[0]["contexts"] != records[1]["contexts"]
+    for record in records:
+        assert all(1 <= value <= 5 for row in record["lengths"] for value in row)
+        assert all(128 <= value <= 6144 for value in record["contexts"])
+
+
+def test_single_rank_needs_no_process_group():
+    sys.path.insert(0, ROOT)
+    import bench
+    bench.barrier(1)
+    assert bench.reduce_max_and_sum(1, [3.0], [4.0]) == ([3.0], [4.0])
+
+
+def test_accept_lengths_are_seeded_and_bounded():
+    sys.path.insert(0, ROOT)
+    import bench
+    first = bench.accept_lengths(64, seed=7)
+    again = bench.accept_lengths(64, seed=7)
+    assert torch.equal(first, again)
+    assert first.shape == (64, bench.SLOTS)
+    assert int(first.min()) >= 1 and int(first.max()) <= bench.DEPTH
+    assert 2.0 < float(first.float().mean()) < 3.0   # geometric, mean 2.5, cut at the depth
+
+
+def test_step_byte_accounting_matches_the_published_figures():
+    sys.path.insert(0, ROOT)
+    import bench
+    import carat_b200
+    config = carat_b200.Gemma4Config.gemma4_31b()
+    assert bench.step_weight_bytes(config) == 30_696_013_824
+    # Full sliding rings (16 KiB per row, 50 layers) plus 8 KiB per context row on 10 global layers.
+    positions = [4096] * bench.SLOTS
+    per_slot = 50 * 16384 * 1024 + 10 * 8192 * (4096 + bench.DEPTH)
+    assert bench.step_kv_bytes(config, positions) == bench.SLOTS * per_slot
