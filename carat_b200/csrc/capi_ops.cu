@@ -109,7 +109,7 @@ extern "C" int carat_b200_gelu_gate_quantize(const void *bf16_packed_gate_up, vo
   const int status = prepare_target(&target, fp8_output, device_scale, device_scratch, cuda_stream);
   if (status != 0)
     return status;
-  return finish(launch_geglu_quant(bf16_packed_gate_up, target, rows, width, cuda_stream),
+  return finish(launch_geglu_quant(bf16_packed_gate_up, TailSource{}, target, rows, width, cuda_stream),
                 "GeGLU quantization");
 }
 

@@ -49,6 +49,12 @@ struct KernelArguments {
   int k_blocks;
   int splits;                 // K pieces per tile (1 unless mode 1)
   int k_blocks_per_split;
+  // Mode 0 only: the last `tail_tiles` feature tiles are cut into `tail_splits` K pieces whose
+  // fp32 partial sums go to tail_partial [piece, rows, tail_tiles * 128] instead of `output`.
+  float *tail_partial;
+  int tail_tiles;
+  int tail_splits;
+  int tail_k_blocks_per_split;
 };
 
 struct WorkItem {
@@ -56,16 +62,34 @@ struct WorkItem {
   int piece;
   int k_begin;
   int k_count;
+  bool tail;
 };
 
-// Items are numbered piece-major so that the pieces of one tile land on different CTAs.
+// Items are numbered piece-major so that the pieces of one tile land on different CTAs; the whole
+// tiles come first and the pieces of the tail tiles last, so they fill the last partial round.
 __device__ __forceinline__ WorkItem decode_item(const KernelArguments &args, int index) {
   WorkItem item;
-  item.tile = index % args.tiles;
-  item.piece = index / args.tiles;
-  item.k_begin = item.piece * args.k_blocks_per_split;
-  item.k_count = min(args.k_blocks, item.k_begin + args.k_blocks_per_split) - item.k_begin;
+  const int whole_items = (args.tiles - args.tail_tiles) * args.splits;
+  if (index < whole_items) {
+    const int whole_tiles = args.tiles - args.tail_tiles;
+    item.tile = index % whole_tiles;
+    item.piece = index / whole_tiles;
+    item.k_begin = item.piece * args.k_blocks_per_split;
+    item.k_count = min(args.k_blocks, item.k_begin + args.k_blocks_per_split) - item.k_begin;
+    item.tail = false;
+  } else {
+    const int tail_index = index - whole_items;
+    item.tile = args.tiles - args.tail_tiles + tail_index % args.tail_tiles;
+    item.piece = tail_index / args.tail_tiles;
+    item.k_begin = item.piece * args.tail_k_blocks_per_split;
+    item.k_count = min(args.k_blocks, item.k_begin + args.tail_k_blocks_per_split) - item.k_begin;
+    item.tail = true;
+  }
   return item;
+}
+
+__device__ __forceinline__ int item_count(const KernelArguments &args) {
+  return (args.tiles - args.tail_tiles) * args.splits + args.tail_tiles * args.tail_splits;
 }
 
 __device__ __forceinline__ unsigned int orderable_bf16(float rounded) {
@@ -142,7 +166,7 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
 
   const int warp = static_cast<int>(threadIdx.x) / 32;
   const int lane = static_cast<int>(threadIdx.x) & 31;
-  const int items = args.tiles * args.splits;
+  const int items = item_count(args);
   const int first_item = static_cast<int>(blockIdx.x);
   const int item_stride = static_cast<int>(gridDim.x);
 
@@ -324,11 +348,32 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
               }
             }
           } else {
-            float values[32];
+            bool finished = false;
+            if constexpr (mode == 0) {
+              if (item.tail) {    // warp-uniform
+                const int tail_width = args.tail_tiles * tile_features;
+                const int tail_feature = feature - (args.tiles - args.tail_tiles) * tile_features;
+                float *destination = args.tail_partial +
+                                     static_cast<size_t>(item.piece) * args.rows * tail_width +
+                                     tail_feature;
 #pragma unroll
-            for (int column = 0; column < 32; ++column)
-              values[column] = __uint_as_float(raw[column]);
-            finish_chunk<mode>(args, values, chunk, feature, feature_base, lane, scale, row_best);
+                for (int column = 0; column < 32; ++column) {
+                  const int row = chunk * 32 + column;
+                  if (row < args.rows)
+                    destination[static_cast<size_t>(row) * tail_width] =
+                        __uint_as_float(raw[column]);
+                }
+                finished = true;
+              }
+            }
+            if (!finished) {
+              float values[32];
+#pragma unroll
+              for (int column = 0; column < 32; ++column)
+                values[column] = __uint_as_float(raw[column]);
+              finish_chunk<mode>(args, values, chunk, feature, feature_base, lane, scale,
+                                 row_best);
+            }
           }
         }
       }
@@ -374,6 +419,25 @@ __global__ void finalize_split_k_kernel(const float *partial, const float *input
     for (int split = 0; split < splits; ++split)
       sum += partial[static_cast<size_t>(split) * elements + index];
     output[index] = __float2bfloat16_rn(sum * scale);
+  }
+}
+
+// output[row, first_column + c] = bf16(scale * sum over pieces of partial[piece, row, c]).
+__global__ void finalize_tail_kernel(const float *partial, const float *input_scale,
+                                     const float *weight_scale, __nv_bfloat16 *output, int pieces,
+                                     int rows, int tail_width, int output_width, int first_column) {
+  grid_dependency_launch();
+  grid_dependency_wait();
+  const float scale = input_scale[0] * weight_scale[0];
+  const size_t elements = static_cast<size_t>(rows) * tail_width;
+  for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+       index < elements; index += static_cast<size_t>(blockDim.x) * gridDim.x) {
+    float sum = 0.0F;
+    for (int piece = 0; piece < pieces; ++piece)
+      sum += partial[static_cast<size_t>(piece) * elements + index];
+    const size_t row = index / tail_width;
+    const size_t column = index - row * tail_width;
+    output[row * output_width + first_column + column] = __float2bfloat16_rn(sum * scale);
   }
 }
 
@@ -449,7 +513,8 @@ int launch_variant(const LinearPlan &plan, const KernelArguments &arguments, cud
   });
   if (configure_status != cudaSuccess)
     return -10;
-  const int items = plan.tiles * arguments.splits;
+  const int items = (plan.tiles - arguments.tail_tiles) * arguments.splits +
+                    arguments.tail_tiles * arguments.tail_splits;
   const int ctas = items < plan.ctas ? items : plan.ctas;
   return launch_chained(fp8_linear_kernel<padded_rows, mode>, dim3(static_cast<unsigned>(ctas)),
                         dim3(linear_threads), dynamic_bytes, stream, false, plan.weight_map,
@@ -482,6 +547,9 @@ KernelArguments base_arguments(const LinearPlan &plan, int *device_error, bool s
   arguments.k_blocks = plan.k_blocks;
   arguments.splits = split ? plan.splits : 1;
   arguments.k_blocks_per_split = split ? plan.k_blocks_per_split : plan.k_blocks;
+  arguments.tail_tiles = 0;
+  arguments.tail_splits = 1;
+  arguments.tail_k_blocks_per_split = plan.k_blocks;
   return arguments;
 }
 
@@ -520,6 +588,24 @@ void schedule_linear(LinearPlan *plan, int rows, int input_width, int output_wid
     splits = result.k_blocks;
   result.k_blocks_per_split = (result.k_blocks + splits - 1) / splits;
   result.splits = (result.k_blocks + result.k_blocks_per_split - 1) / result.k_blocks_per_split;
+  // More tiles than SMs with a short last round: cutting the last round's tiles along K lets every
+  // SM take part in it (336 tiles on 148 SMs: 2 + 1/3 rounds instead of 3).
+  result.tail_tiles = 0;
+  result.tail_splits = 1;
+  result.tail_k_blocks_per_split = result.k_blocks;
+  const int remainder = result.tiles % result.ctas;
+  if (result.splits == 1 && result.tiles > result.ctas && remainder > 0 &&
+      remainder * 2 <= result.ctas && output_width % tile_features == 0) {
+    int pieces = result.ctas / remainder;
+    const int most = result.k_blocks / 4 < 1 ? 1 : result.k_blocks / 4;
+    pieces = pieces > most ? most : pieces;
+    if (pieces > 1) {
+      result.tail_tiles = remainder;
+      result.tail_k_blocks_per_split = (result.k_blocks + pieces - 1) / pieces;
+      result.tail_splits = (result.k_blocks + result.tail_k_blocks_per_split - 1) /
+                           result.tail_k_blocks_per_split;
+    }
+  }
 }
 
 } // namespace
@@ -564,13 +650,29 @@ int make_linear_plan(LinearPlan *plan, const void *fp8_input, const void *fp8_we
 }
 
 std::size_t linear_partial_bytes(const LinearPlan &plan) {
-  return plan.splits <= 1 ? 0
-                          : sizeof(float) * static_cast<std::size_t>(plan.splits) * plan.rows *
-                                plan.output_width;
+  if (plan.splits <= 1)
+    return linear_tail_bytes(plan);
+  return sizeof(float) * static_cast<std::size_t>(plan.splits) * plan.rows * plan.output_width;
 }
 
 int launch_linear_bf16(const LinearPlan &plan, const float *input_scale, const float *weight_scale,
                        void *bf16_output, float *partial, int *device_error, cudaStream_t stream) {
+  if (plan.splits == 1 && plan.tail_tiles > 0 && partial != nullptr) {
+    const int status = launch_linear_bf16_tail(plan, input_scale, weight_scale, bf16_output,
+                                               partial, device_error, stream);
+    if (status != 0)
+      return status;
+    const int tail_width = plan.tail_tiles * tile_features;
+    const size_t elements = static_cast<size_t>(plan.rows) * tail_width;
+    const int blocks = static_cast<int>((elements + 255) / 256);
+    return launch_chained(finalize_tail_kernel, dim3(blocks < 1184 ? blocks : 1184), dim3(256), 0,
+                          stream, false, static_cast<const float *>(partial), input_scale,
+                          weight_scale, static_cast<__nv_bfloat16 *>(bf16_output),
+                          plan.tail_splits, plan.rows, tail_width, plan.output_width,
+                          plan.output_width - tail_width) == cudaSuccess
+               ? 0
+               : -11;
+  }
   if (plan.splits == 1) {
     KernelArguments arguments = base_arguments(plan, device_error, false);
     arguments.input_scale = input_scale;
@@ -589,6 +691,28 @@ int launch_linear_bf16(const LinearPlan &plan, const float *input_scale, const f
                         elements) == cudaSuccess
              ? 0
              : -11;
+}
+
+int launch_linear_bf16_tail(const LinearPlan &plan, const float *input_scale,
+                            const float *weight_scale, void *bf16_output, float *tail_partial,
+                            int *device_error, cudaStream_t stream) {
+  if (plan.splits != 1 || plan.tail_tiles <= 0 || tail_partial == nullptr)
+    return -13;
+  KernelArguments arguments = base_arguments(plan, device_error, false);
+  arguments.input_scale = input_scale;
+  arguments.weight_scale = weight_scale;
+  arguments.output = static_cast<__nv_bfloat16 *>(bf16_output);
+  arguments.tail_partial = tail_partial;
+  arguments.tail_tiles = plan.tail_tiles;
+  arguments.tail_splits = plan.tail_splits;
+  arguments.tail_k_blocks_per_split = plan.tail_k_blocks_per_split;
+  return launch_mode<0>(plan, arguments, stream);
+}
+
+std::size_t linear_tail_bytes(const LinearPlan &plan) {
+  return plan.tail_tiles <= 0 ? 0
+                              : sizeof(float) * static_cast<std::size_t>(plan.tail_splits) *
+                                    plan.rows * plan.tail_tiles * tile_features;
 }
 
 int launch_linear_partial(const LinearPlan &plan, float *partial, int *device_error,

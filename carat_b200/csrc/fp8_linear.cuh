@@ -27,6 +27,11 @@ struct LinearPlan {
   int ctas{0};              // persistent CTAs (multiprocessor count)
   int splits{1};            // K pieces per tile when there are fewer tiles than SMs
   int k_blocks_per_split{0};
+  // When there are more tiles than SMs and the last round is short, the last `tail_tiles` tiles
+  // may be cut into `tail_splits` K pieces (launch_linear_bf16_tail); 0 = no such tail.
+  int tail_tiles{0};
+  int tail_splits{1};
+  int tail_k_blocks_per_split{0};
 };
 
 // Returns 0 or a negative error; `error` (may be null) receives a static message.
@@ -45,6 +50,14 @@ std::size_t linear_partial_bytes_for(int rows, int input_width, int output_width
 // sums into `partial` and a second kernel sums, scales and rounds them into `output`.
 int launch_linear_bf16(const LinearPlan &plan, const float *input_scale, const float *weight_scale,
                        void *bf16_output, float *partial, int *device_error, cudaStream_t stream);
+
+// bf16 epilogue for the whole tiles; the last plan.tail_tiles tiles leave unscaled fp32 partial sums
+// [tail_splits, rows, tail_tiles * 128] in `tail_partial` for a consumer that sums, scales and
+// rounds them (the values `bf16_output` would have held in those columns are not written).
+int launch_linear_bf16_tail(const LinearPlan &plan, const float *input_scale,
+                            const float *weight_scale, void *bf16_output, float *tail_partial,
+                            int *device_error, cudaStream_t stream);
+std::size_t linear_tail_bytes(const LinearPlan &plan);
 
 // Leaves the unscaled fp32 partial sums [splits, rows, output_width] for a consumer that sums them.
 int launch_linear_partial(const LinearPlan &plan, float *partial, int *device_error,

@@ -38,6 +38,12 @@ struct RowArguments {
   unsigned char *fp8_output;
   float *scale;
   unsigned int *amax_bits;
+  // geglu only: the up columns from packed column `tail_first_column` on come as fp32 partial
+  // sums [tail_splits, rows, tail_width] of the linear (scaled by input_scale * weight_scale).
+  const float *tail_partial;
+  int tail_splits;
+  int tail_first_column;
+  int tail_width;
   unsigned int *clear_base;
   int clear_words;
   int width;
@@ -264,7 +270,37 @@ __global__ void __launch_bounds__(row_threads) row_kernel(RowArguments a) {
     } else if constexpr (mode == RowMode::geglu) {
       const __nv_bfloat16 *packed_row = a.input + row * 2 * width;
       const Pack8 gate = load_bf16x8(packed_row + column);
-      const Pack8 up = load_bf16x8(packed_row + width + column);
+      Pack8 up;
+      if (a.tail_partial != nullptr && width + column >= a.tail_first_column) {
+        // Same finish as the linear's own epilogue: sum of the pieces, scaled, rounded to bf16.
+        const float tail_scale = a.input_scale[0] * a.weight_scale[0];
+        Pack8 sum;
+#pragma unroll
+        for (int index = 0; index < 8; ++index)
+          sum.v[index] = 0.0F;
+        for (int piece = 0; piece < a.tail_splits; ++piece) {
+          const float *source = a.tail_partial +
+                                (static_cast<size_t>(piece) * rows + row) * a.tail_width +
+                                (width + column - a.tail_first_column);
+          const float4 low = *reinterpret_cast<const float4 *>(source);
+          const float4 high = *reinterpret_cast<const float4 *>(source + 4);
+          sum.v[0] += low.x;
+          sum.v[1] += low.y;
+          sum.v[2] += low.z;
+          sum.v[3] += low.w;
+          sum.v[4] += high.x;
+          sum.v[5] += high.y;
+          sum.v[6] += high.z;
+          sum.v[7] += high.w;
+        }
+#pragma unroll
+        for (int index = 0; index < 8; ++index)
+          sum.v[index] *= tail_scale;
+        uint4 unused;
+        up = round_bf16x8(sum, &unused);
+      } else {
+        up = load_bf16x8(packed_row + width + column);
+      }
       Pack8 product;
 #pragma unroll
       for (int index = 0; index < 8; ++index)
@@ -573,12 +609,25 @@ int launch_post_attention_norms_quant(const void *projected, PartialSource sourc
   return launch_rows<RowMode::post_attention>(arguments, rows, stream);
 }
 
-int launch_geglu_quant(const void *packed_gate_up, QuantTarget target, int rows, int width,
-                       cudaStream_t stream) {
+int launch_geglu_quant(const void *packed_gate_up, TailSource tail, QuantTarget target, int rows,
+                       int width, cudaStream_t stream) {
   if (packed_gate_up == nullptr)
     return -1;
   RowArguments arguments = base_arguments(target, width, 0.0F);
   arguments.input = static_cast<const __nv_bfloat16 *>(packed_gate_up);
+  if (tail.partial != nullptr) {
+    if (tail.splits <= 0 || tail.width <= 0 || tail.width % 8 != 0 || tail.first_column < width ||
+        tail.first_column + tail.width != 2 * width || tail.input_scale == nullptr ||
+        tail.weight_scale == nullptr) {
+      return -1;
+    }
+    arguments.tail_partial = tail.partial;
+    arguments.tail_splits = tail.splits;
+    arguments.tail_first_column = tail.first_column;
+    arguments.tail_width = tail.width;
+    arguments.input_scale = tail.input_scale;
+    arguments.weight_scale = tail.weight_scale;
+  }
   return launch_rows<RowMode::geglu>(arguments, rows, stream);
 }
 

@@ -69,10 +69,22 @@ int launch_post_attention_norms_quant(const void *projected, PartialSource sourc
                                       QuantTarget target, int rows, int width, float epsilon,
                                       cudaStream_t stream);
 
+// The last columns of a packed [gate | up] row when the linear that produced it left them as fp32
+// K-piece partial sums (launch_linear_bf16_tail): [splits, rows, width] covering packed columns
+// first_column .. first_column + width, all inside the up half. partial == nullptr: no tail.
+struct TailSource {
+  const float *partial;
+  int splits;
+  int first_column;
+  int width;
+  const float *input_scale;
+  const float *weight_scale;
+};
+
 // activated = bf16(gelu_tanh(gate) * up) from rows packed [gate | up] -> e4m3
 // (cuda/ops.cu:228-284).
-int launch_geglu_quant(const void *packed_gate_up, QuantTarget target, int rows, int width,
-                       cudaStream_t stream);
+int launch_geglu_quant(const void *packed_gate_up, TailSource tail, QuantTarget target, int rows,
+                       int width, cudaStream_t stream);
 
 // down = source; output = bf16(bf16(rmsnorm(down) * w + residual) * scalar)
 // (cuda/ops.cu:181-217); then next = bf16(rmsnorm(output) * next_norm_weight) -> e4m3, which is

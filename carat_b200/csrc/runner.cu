@@ -499,7 +499,7 @@ PartialSource run_linear(Runner &runner, const LinearPlan &plan, const float *in
   require_launch(launch_linear_bf16(plan, input_scale, weight_scale, output, partials,
                                     runner.device_error, runner.stream),
                  "FP8 linear");
-  runner.launches += plan.splits > 1 ? 2 : 1;
+  runner.launches += (plan.splits > 1 || plan.tail_tiles > 0) ? 2 : 1;
   return PartialSource{nullptr, 0, nullptr, nullptr};
 }
 
@@ -730,9 +730,26 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
                    "post-attention norms");
     runner.launches += 1;
 
-    run_linear(runner, plan.gate_up, scales + word + 2, w.gate_up_scale, runner.gate_up.get(),
-               false);
-    require_launch(launch_geglu_quant(runner.gate_up.get(), target(word + 3), rows,
+    // 336 feature tiles on 148 SMs leave a short last round; its tiles are cut along K and the
+    // GeGLU kernel, which reads the up half anyway, sums the pieces.
+    TailSource tail{};
+    if (plan.gate_up.tail_tiles > 0 &&
+        linear_tail_bytes(plan.gate_up) <= runner.split_partials.bytes() &&
+        plan.gate_up.tail_tiles * 128 <= config.intermediate_size) {
+      require_launch(launch_linear_bf16_tail(plan.gate_up, scales + word + 2, w.gate_up_scale,
+                                             runner.gate_up.get(),
+                                             runner.split_partials.get<float>(),
+                                             runner.device_error, stream),
+                     "FP8 linear");
+      runner.launches += 1;
+      tail = TailSource{runner.split_partials.get<float>(), plan.gate_up.tail_splits,
+                        2 * config.intermediate_size - plan.gate_up.tail_tiles * 128,
+                        plan.gate_up.tail_tiles * 128, scales + word + 2, w.gate_up_scale};
+    } else {
+      run_linear(runner, plan.gate_up, scales + word + 2, w.gate_up_scale, runner.gate_up.get(),
+                 false);
+    }
+    require_launch(launch_geglu_quant(runner.gate_up.get(), tail, target(word + 3), rows,
                                       config.intermediate_size, stream),
                    "GeGLU");
     runner.launches += 1;
@@ -950,7 +967,7 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
       runner.launches += 1;
       run_linear(runner, plan.gate_up, scales + word + 1, w.gate_up_scale, runner.a_gate_up.get(),
                  false);
-      require_launch(launch_geglu_quant(runner.a_gate_up.get(), target(word + 2), requests,
+      require_launch(launch_geglu_quant(runner.a_gate_up.get(), TailSource{}, target(word + 2), requests,
                                         assistant.intermediate_size, stream),
                      "assistant GeGLU");
       runner.launches += 1;

@@ -1,0 +1,127 @@
+"""The FP8 linear (reference: Fp8Linear::run, cuda/linear.cu:645-803) through the C ABI, over every
+scheduling shape the plan can choose: one piece per tile, uniform split-K (fewer tiles than SMs),
+a K-cut tail round (more tiles than SMs with a short last round), ragged feature counts, and the
+fused argmax epilogue of the LM head.
+
+Products of e4m3 values are exact in fp32 and the sums here stay far below 2^24 ulps of trouble,
+but the accumulation order of a tensor-core K loop (and of split pieces) is not the oracle's, so
+the bar is: bit-exact for almost every element, the rest one bf16 ulp away (measured at a floor
+magnitude where sums cancel), against both the oracle and the plain one-thread-per-output
+cross-check kernel.
+"""
+import ctypes
+
+import pytest
+import torch
+
+import carat_b200
+from carat_b200.capi import check
+from oracle import carat_semantics as cs
+
+pytestmark = pytest.mark.gpu
+
+
+def ptr(tensor):
+    return ctypes.c_void_p(tensor.data_ptr())
+
+
+def quantised(rows, cols, std, seed):
+    generator = torch.Generator(device="cuda").manual_seed(seed)
+    values = (torch.randn(rows, cols, device="cuda", generator=generator) * std).to(torch.bfloat16)
+    return carat_b200.quantize_tensor_to_fp8(values)
+
+
+def one_ulp_apart(got, want):
+    """Every element within one bf16 ulp of the reference. Near a cancellation (|value| far below
+    the tensor's typical magnitude) an ulp of the value itself is meaningless, because the fp32
+    partial sums that cancelled were rounded at their own, larger magnitude; the ulp of 1/16 of
+    the tensor's rms is the floor there."""
+    got = got.float()
+    want = want.float()
+    floor = want.pow(2).mean().sqrt() / 16
+    allowed = torch.maximum(want.abs(), floor) * 2.0 ** -7
+    return bool(((got - want).abs() <= allowed).all())
+
+
+SHAPES = [
+    (120, 5376, 16384, "one piece per tile"),
+    (120, 8192, 5376, "uniform split-K"),
+    (120, 1024, 20480, "K-cut tail round"),          # 160 tiles on 148 SMs
+    (24, 1024, 8192 + 64, "ragged feature count"),
+    (5, 256, 384, "few rows"),
+    (64, 2048, 19072 + 128 * 20, "tail round, 64 padded rows"),
+]
+
+
+@pytest.mark.parametrize("rows,k,n,what", SHAPES)
+def test_linear_matches_oracle_and_cross_check(cuda_device, rows, k, n, what):
+    library = carat_b200.library()
+    weight, weight_scale = quantised(n, k, 0.02, 1)
+    activation, activation_scale = quantised(rows, k, 1.0, 2)
+    needed = library.carat_b200_fp8_linear_workspace_bytes(rows, k, n)
+    if what in ("uniform split-K", "K-cut tail round", "tail round, 64 padded rows"):
+        assert needed > 0, what
+    workspace = torch.empty(max(needed, 16), dtype=torch.uint8, device="cuda")
+    got = torch.full((rows, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    plain = torch.empty_like(got)
+    check(library.carat_b200_fp8_linear(ptr(activation), ptr(activation_scale), ptr(weight),
+                                        ptr(weight_scale), ptr(got), rows, k, n, ptr(workspace),
+                                        needed, None))
+    check(library.carat_b200_fp8_linear_check(ptr(activation), ptr(activation_scale), ptr(weight),
+                                              ptr(weight_scale), ptr(plain), rows, k, n, None))
+    torch.cuda.synchronize()
+    code = ctypes.c_int(0)
+    check(library.carat_b200_device_error(ctypes.byref(code)))
+    assert code.value == 0
+    want = cs.fp8_linear(activation.view(torch.float8_e4m3fn).float().cpu(),
+                         activation_scale.cpu(), weight.view(torch.float8_e4m3fn).float().cpu(),
+                         weight_scale.cpu())
+    got_host = got.cpu()
+    assert not torch.isnan(got_host.float()).any()
+    for reference in (want.to(torch.bfloat16), plain.cpu()):
+        assert float((got_host != reference).float().mean()) < 2e-3, what
+        assert one_ulp_apart(got_host, reference), what
+
+
+def test_lm_head_argmax_epilogue(cuda_device):
+    library = carat_b200.library()
+    rows, k, n = 120, 1024, 40000            # ragged last tile, several rounds of tiles
+    weight, weight_scale = quantised(n, k, 0.02, 3)
+    activation, activation_scale = quantised(rows, k, 1.0, 4)
+    tokens = torch.empty(rows, dtype=torch.int32, device="cuda")
+    keys = torch.empty(rows, dtype=torch.int64, device="cuda")
+    check(library.carat_b200_fp8_linear_argmax(ptr(activation), ptr(activation_scale), ptr(weight),
+                                               ptr(weight_scale), ptr(tokens), ptr(keys), rows, k,
+                                               n, None))
+    torch.cuda.synchronize()
+    logits = cs.fp8_linear(activation.view(torch.float8_e4m3fn).float().cpu(),
+                           activation_scale.cpu(), weight.view(torch.float8_e4m3fn).float().cpu(),
+                           weight_scale.cpu())
+    want = cs.argmax_lowest_index(logits)
+    got = tokens.cpu().long()
+    # A differing choice must be a tie or a one-ulp near-tie in the oracle's bf16 logits.
+    for row in range(rows):
+        if int(got[row]) != int(want[row]):
+            best = float(logits[row, want[row]])
+            chosen = float(logits[row, got[row]])
+            assert abs(best - chosen) <= abs(best) * 2 ** -7, (row, best, chosen)
+    assert float((got != want).float().mean()) < 0.05
+
+
+def test_argmax_ties_take_the_lowest_index(cuda_device):
+    """Equal logits: the reference's argmax keeps the lowest index (cuda/ops.cu:890-981)."""
+    library = carat_b200.library()
+    rows, k, n = 8, 128, 1024
+    weight = torch.zeros(n, k, dtype=torch.uint8, device="cuda")
+    one = torch.tensor([1.0]).to(torch.float8_e4m3fn).view(torch.uint8).item()
+    # Features 700 and 300 get identical weights: a tie between them in every row.
+    weight[700, :4] = one
+    weight[300, :4] = one
+    activation = torch.full((rows, k), one, dtype=torch.uint8, device="cuda")
+    scale = torch.ones(1, dtype=torch.float32, device="cuda")
+    tokens = torch.empty(rows, dtype=torch.int32, device="cuda")
+    keys = torch.empty(rows, dtype=torch.int64, device="cuda")
+    check(library.carat_b200_fp8_linear_argmax(ptr(activation), ptr(scale), ptr(weight), ptr(scale),
+                                               ptr(tokens), ptr(keys), rows, k, n, None))
+    torch.cuda.synchronize()
+    assert tokens.cpu().tolist() == [300] * rows
