@@ -44,6 +44,7 @@ struct RowArguments {
   int tail_splits;
   int tail_first_column;
   int tail_width;
+  int parts;                         // CTAs per row (GeGLU only; 0 or 1 = one)
   unsigned int *clear_base;
   int clear_words;
   int width;
@@ -64,35 +65,36 @@ __device__ __forceinline__ float warp_max(float value) {
   return value;
 }
 
-// Every thread receives the block-wide result. `scratch` holds row_warps floats.
-__device__ float block_sum(float value, float *scratch) {
+// Every thread receives the block-wide result after a single barrier: each warp leaves its
+// partial in shared memory and every thread adds up all of them (broadcast reads). `scratch`
+// holds 2 * row_warps floats; consecutive reductions alternate between the halves (`parity`), so
+// a warp that races ahead to the next reduction cannot overwrite partials others still read.
+__device__ __forceinline__ float block_sum(float value, float *scratch, int &parity) {
   value = warp_sum(value);
-  __syncthreads();
+  float *partials = scratch + parity * row_warps;
   if ((threadIdx.x & 31U) == 0U)
-    scratch[threadIdx.x >> 5U] = value;
+    partials[threadIdx.x >> 5U] = value;
   __syncthreads();
-  float total = threadIdx.x < row_warps ? scratch[threadIdx.x] : 0.0F;
-  if (threadIdx.x < 32U)
-    total = warp_sum(total);
-  if (threadIdx.x == 0U)
-    scratch[0] = total;
-  __syncthreads();
-  return scratch[0];
+  float total = 0.0F;
+#pragma unroll
+  for (int warp = 0; warp < row_warps; ++warp)
+    total += partials[warp];
+  parity ^= 1;
+  return total;
 }
 
-__device__ float block_max(float value, float *scratch) {
+__device__ __forceinline__ float block_max(float value, float *scratch, int &parity) {
   value = warp_max(value);
-  __syncthreads();
+  float *partials = scratch + parity * row_warps;
   if ((threadIdx.x & 31U) == 0U)
-    scratch[threadIdx.x >> 5U] = value;
+    partials[threadIdx.x >> 5U] = value;
   __syncthreads();
-  float total = threadIdx.x < row_warps ? scratch[threadIdx.x] : 0.0F;
-  if (threadIdx.x < 32U)
-    total = warp_max(total);
-  if (threadIdx.x == 0U)
-    scratch[0] = total;
-  __syncthreads();
-  return scratch[0];
+  float total = 0.0F;
+#pragma unroll
+  for (int warp = 0; warp < row_warps; ++warp)
+    total = fmaxf(total, partials[warp]);
+  parity ^= 1;
+  return total;
 }
 
 struct Pack8 {
@@ -155,19 +157,33 @@ __device__ __forceinline__ Pack8 load_source(const RowArguments &a, size_t row, 
 #pragma unroll
   for (int index = 0; index < 8; ++index)
     sum.v[index] = 0.0F;
-#pragma unroll 4
-  for (int split = 0; split < a.splits; ++split) {
-    const float *source = a.partial + (static_cast<size_t>(split) * rows + row) * a.width + column;
-    const float4 low = *reinterpret_cast<const float4 *>(source);
-    const float4 high = *reinterpret_cast<const float4 *>(source + 4);
-    sum.v[0] += low.x;
-    sum.v[1] += low.y;
-    sum.v[2] += low.z;
-    sum.v[3] += low.w;
-    sum.v[4] += high.x;
-    sum.v[5] += high.y;
-    sum.v[6] += high.z;
-    sum.v[7] += high.w;
+  // Four pieces at a time, all loads before the first add: a loop that loads and adds piece by
+  // piece pays one L2 round trip per piece.
+  for (int first = 0; first < a.splits; first += 4) {
+    float4 low[4];
+    float4 high[4];
+#pragma unroll
+    for (int offset = 0; offset < 4; ++offset) {
+      low[offset] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+      high[offset] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+      if (first + offset < a.splits) {
+        const float *source =
+            a.partial + (static_cast<size_t>(first + offset) * rows + row) * a.width + column;
+        low[offset] = *reinterpret_cast<const float4 *>(source);
+        high[offset] = *reinterpret_cast<const float4 *>(source + 4);
+      }
+    }
+#pragma unroll
+    for (int offset = 0; offset < 4; ++offset) {
+      sum.v[0] += low[offset].x;
+      sum.v[1] += low[offset].y;
+      sum.v[2] += low[offset].z;
+      sum.v[3] += low[offset].w;
+      sum.v[4] += high[offset].x;
+      sum.v[5] += high[offset].y;
+      sum.v[6] += high[offset].z;
+      sum.v[7] += high[offset].w;
+    }
   }
   Pack8 rounded;
 #pragma unroll
@@ -182,13 +198,21 @@ __device__ __forceinline__ Pack8 load_source(const RowArguments &a, size_t row, 
 // (norm weights) are loaded before the wait on the previous grid, everything else right after it,
 // so one global-memory round trip feeds the whole kernel.
 template <RowMode mode, int chunks>
-__global__ void __launch_bounds__(row_threads) row_kernel(RowArguments a) {
+__global__ void __launch_bounds__(row_threads, (mode == RowMode::geglu && chunks <= 4) ? 2 : 1)
+row_kernel(RowArguments a) {
   cg::grid_group grid = cg::this_grid();
-  __shared__ float scratch[row_warps];
+  __shared__ float scratch[2 * row_warps];
+  int parity = 0;
 
-  const size_t row = blockIdx.x;
-  const size_t rows = gridDim.x;
+  // Modes without a row-wide reduction (GeGLU) may cut a row into `parts` column ranges, one CTA
+  // each, so that a wide row does not sit in a single CTA.
+  const int parts = a.parts > 1 ? a.parts : 1;
+  const size_t row = blockIdx.x / parts;
+  const size_t rows = gridDim.x / parts;
   const int width = a.width;
+  const int part = static_cast<int>(blockIdx.x) - static_cast<int>(row) * parts;
+  const int column_base = part * (width / parts);
+  const int column_end = part + 1 == parts ? width : column_base + width / parts;
   const float width_value = static_cast<float>(width);
   constexpr bool two_norms = mode == RowMode::post_attention || mode == RowMode::layer_output;
   constexpr bool one_norm = mode == RowMode::embed_norm || mode == RowMode::norm;
@@ -198,10 +222,10 @@ __global__ void __launch_bounds__(row_threads) row_kernel(RowArguments a) {
   uint4 next_weight_raw[chunks];
 #pragma unroll
   for (int chunk = 0; chunk < chunks; ++chunk) {
-    const int column = (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+    const int column = column_base + (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
     weight_raw[chunk] = make_uint4(0, 0, 0, 0);
     next_weight_raw[chunk] = make_uint4(0, 0, 0, 0);
-    if (column < width) {
+    if (column < column_end) {
       if constexpr (one_norm || two_norms)
         weight_raw[chunk] = *reinterpret_cast<const uint4 *>(a.norm_weight + column);
       if constexpr (two_norms)
@@ -228,12 +252,12 @@ __global__ void __launch_bounds__(row_threads) row_kernel(RowArguments a) {
   uint4 residual_raw[chunks];
 #pragma unroll
   for (int chunk = 0; chunk < chunks; ++chunk) {
-    const int column = (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+    const int column = column_base + (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
     residual_raw[chunk] = make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int index = 0; index < 8; ++index)
       values[chunk].v[index] = 0.0F;
-    if (column >= width)
+    if (column >= column_end)
       continue;
     if constexpr (mode == RowMode::embed_norm) {
       const int token = a.tokens[row];
@@ -278,20 +302,33 @@ __global__ void __launch_bounds__(row_threads) row_kernel(RowArguments a) {
 #pragma unroll
         for (int index = 0; index < 8; ++index)
           sum.v[index] = 0.0F;
-        for (int piece = 0; piece < a.tail_splits; ++piece) {
-          const float *source = a.tail_partial +
-                                (static_cast<size_t>(piece) * rows + row) * a.tail_width +
-                                (width + column - a.tail_first_column);
-          const float4 low = *reinterpret_cast<const float4 *>(source);
-          const float4 high = *reinterpret_cast<const float4 *>(source + 4);
-          sum.v[0] += low.x;
-          sum.v[1] += low.y;
-          sum.v[2] += low.z;
-          sum.v[3] += low.w;
-          sum.v[4] += high.x;
-          sum.v[5] += high.y;
-          sum.v[6] += high.z;
-          sum.v[7] += high.w;
+        for (int first = 0; first < a.tail_splits; first += 4) {
+          float4 low[4];
+          float4 high[4];
+#pragma unroll
+          for (int offset = 0; offset < 4; ++offset) {
+            low[offset] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+            high[offset] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+            if (first + offset < a.tail_splits) {
+              const float *source =
+                  a.tail_partial +
+                  (static_cast<size_t>(first + offset) * rows + row) * a.tail_width +
+                  (width + column - a.tail_first_column);
+              low[offset] = *reinterpret_cast<const float4 *>(source);
+              high[offset] = *reinterpret_cast<const float4 *>(source + 4);
+            }
+          }
+#pragma unroll
+          for (int offset = 0; offset < 4; ++offset) {
+            sum.v[0] += low[offset].x;
+            sum.v[1] += low[offset].y;
+            sum.v[2] += low[offset].z;
+            sum.v[3] += low[offset].w;
+            sum.v[4] += high[offset].x;
+            sum.v[5] += high[offset].y;
+            sum.v[6] += high[offset].z;
+            sum.v[7] += high[offset].w;
+          }
         }
 #pragma unroll
         for (int index = 0; index < 8; ++index)
@@ -329,14 +366,14 @@ __global__ void __launch_bounds__(row_threads) row_kernel(RowArguments a) {
 #pragma unroll
       for (int index = 0; index < 8; ++index)
         square_sum += values[chunk].v[index] * values[chunk].v[index];
-    const float inverse_rms = rsqrtf(block_sum(square_sum, scratch) / width_value + a.epsilon);
+    const float inverse_rms = rsqrtf(block_sum(square_sum, scratch, parity) / width_value + a.epsilon);
     float layer_scale = 1.0F;
     if constexpr (mode == RowMode::layer_output)
       layer_scale = __bfloat162float(*a.scalar);
 #pragma unroll
     for (int chunk = 0; chunk < chunks; ++chunk) {
-      const int column = (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
-      if (column >= width)
+      const int column = column_base + (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+      if (column >= column_end)
         continue;
       const Pack8 weights = unpack_bf16x8(weight_raw[chunk]);
       Pack8 result;
@@ -376,11 +413,11 @@ __global__ void __launch_bounds__(row_threads) row_kernel(RowArguments a) {
 #pragma unroll
       for (int index = 0; index < 8; ++index)
         square_sum += values[chunk].v[index] * values[chunk].v[index];
-    const float inverse_rms = rsqrtf(block_sum(square_sum, scratch) / width_value + a.epsilon);
+    const float inverse_rms = rsqrtf(block_sum(square_sum, scratch, parity) / width_value + a.epsilon);
 #pragma unroll
     for (int chunk = 0; chunk < chunks; ++chunk) {
-      const int column = (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
-      if (column >= width)
+      const int column = column_base + (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+      if (column >= column_end)
         continue;
       const Pack8 weights = unpack_bf16x8(next_weight_raw[chunk]);
       Pack8 result;
@@ -401,7 +438,7 @@ __global__ void __launch_bounds__(row_threads) row_kernel(RowArguments a) {
 #pragma unroll
     for (int index = 0; index < 8; ++index)
       row_amax = fmaxf(row_amax, fabsf(values[chunk].v[index]));
-  row_amax = block_max(row_amax, scratch);
+  row_amax = block_max(row_amax, scratch, parity);
   if (threadIdx.x == 0U)
     atomicMax(a.amax_bits, __float_as_uint(row_amax));
   grid.sync();
@@ -412,8 +449,8 @@ __global__ void __launch_bounds__(row_threads) row_kernel(RowArguments a) {
     *a.scale = scale;
 #pragma unroll
   for (int chunk = 0; chunk < chunks; ++chunk) {
-    const int column = (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
-    if (column >= width)
+    const int column = column_base + (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+    if (column >= column_end)
       continue;
     const Pack8 &v = values[chunk];
     __nv_fp8x4_e4m3 low(make_float4(v.v[0] * inverse_scale, v.v[1] * inverse_scale,
@@ -460,25 +497,42 @@ template <RowMode mode> int launch_rows(RowArguments arguments, int rows, cudaSt
       arguments.amax_bits == nullptr) {
     return -1;
   }
-  const int groups = (arguments.width / 8 + row_threads - 1) / row_threads;
-  if (groups <= 2)
-    return launch_rows_chunks<mode, 2>(arguments, rows, stream);
-  if (groups <= 4)
-    return launch_rows_chunks<mode, 4>(arguments, rows, stream);
-  if (groups <= 8)
-    return launch_rows_chunks<mode, 8>(arguments, rows, stream);
+  int parts = 1;
+  if constexpr (mode == RowMode::geglu) {
+    // Wide rows: two CTAs a row when the halves stay multiples of eight columns and the grid
+    // still fits the device at once (checked by launch_rows_chunks).
+    if (arguments.width >= 8192 && arguments.width % 16 == 0 && rows <= 148)
+      parts = 2;
+  }
+  for (; parts >= 1; --parts) {
+    arguments.parts = parts;
+    const int span = arguments.width / parts;
+    const int groups = (span / 8 + row_threads - 1) / row_threads;
+    const int ctas = rows * parts;
+    int status = -2;
+    if (groups <= 2)
+      status = launch_rows_chunks<mode, 2>(arguments, ctas, stream);
+    else if (groups <= 4)
+      status = launch_rows_chunks<mode, 4>(arguments, ctas, stream);
+    else if (groups <= 8)
+      status = launch_rows_chunks<mode, 8>(arguments, ctas, stream);
+    // -2: the grid would not be resident at once; try again with one CTA a row.
+    if (status != -2 || parts == 1)
+      return status;
+  }
   return -2;
 }
 
 // Large tensors (weights at load time): the reference's three-launch form, cuda/linear.cu:117-153.
 __global__ void tensor_amax_kernel(const __nv_bfloat16 *input, size_t elements,
                                    unsigned int *maximum_bits) {
-  __shared__ float scratch[row_warps];
+  __shared__ float scratch[2 * row_warps];
+  int parity = 0;
   float maximum = 0.0F;
   for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; index < elements;
        index += static_cast<size_t>(blockDim.x) * gridDim.x)
     maximum = fmaxf(maximum, fabsf(__bfloat162float(input[index])));
-  maximum = block_max(maximum, scratch);
+  maximum = block_max(maximum, scratch, parity);
   if (threadIdx.x == 0U)
     atomicMax(maximum_bits, __float_as_uint(maximum));
 }
