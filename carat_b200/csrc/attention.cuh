@@ -55,6 +55,9 @@ struct AttentionArguments {
   // chunk, [score rows, stats_stride] with stats_stride >= chunks.
   float2 *stats;
   int stats_stride;
+  // chunks > 1 only: [requests] receives the number of chunks that hold any of the request's
+  // rows. Chunk partials beyond that count are NOT written; whoever sums them must stop there.
+  int *request_chunks;
   int sum_chunks;            // chunks > 1 only: also sum the chunk partials into `output` (bf16);
                              // otherwise the consumer of `chunk_partials` does the sum
   int draft;                 // 1: drafter semantics (depth == 1, no proposal rows, the first

@@ -610,8 +610,9 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_word;
   __shared__ StreamItem item_cache[cached_items];
-  __shared__ int row_head[padded_rows];       // query row -> head inside the group, token
-  __shared__ int row_token[padded_rows];
+  // Element offset of query row r inside a (request, kv head) block of the output:
+  // token(r) * width + head(r) * dimension.
+  __shared__ int row_offset[padded_rows];
   __shared__ float row_maximum[2][padded_rows];
   __shared__ float row_inverse_sum[2][padded_rows];
   volatile int *abort_flag = &abort_word;
@@ -650,8 +651,9 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
     ptx::prefetch_tensormap(&value_map);
   }
   if (static_cast<int>(threadIdx.x) < padded_rows) {
-    row_head[threadIdx.x] = static_cast<int>(threadIdx.x) / a.depth;
-    row_token[threadIdx.x] = static_cast<int>(threadIdx.x) % a.depth;
+    const int head = static_cast<int>(threadIdx.x) / a.depth;
+    const int token = static_cast<int>(threadIdx.x) - head * a.depth;
+    row_offset[threadIdx.x] = token * a.query_heads * dimension + head * dimension;
   }
   if (warp == 1) {
     ptx::tmem_alloc(ptx::smem_u32(&tmem_base_slot), tmem_columns);
@@ -809,77 +811,69 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
       }
     }
   } else if (warp < 2 + values_output_warps) {
-    // ---- output: O[component, row] -> fp32 chunk partials, or bf16 when there is one chunk
+    // ---- output: O[component, row] -> fp32 chunk partials, or bf16 when there is one chunk.
+    // Chunks that hold none of a request's rows are not written at all: the request's chunk
+    // count goes to a.request_chunks and the consumer of the partials stops there.
     const int quarter = warp & 3;
     const int width = a.query_heads * dimension;
-    const size_t total_rows = static_cast<size_t>(a.requests) * a.depth;
+    const size_t chunk_elements = static_cast<size_t>(a.requests) * a.depth * width;
     uint32_t local = 0;
     for (int index = static_cast<int>(blockIdx.x), ordinal = 0; index < args.items;
          index += static_cast<int>(gridDim.x), ++ordinal) {
       const StreamItem item = cached_item(a, index, ordinal, item_cache);
-      const bool empty = item.empty();
-      if (empty && a.chunks <= 1)
+      if (item.empty())
         continue;
-      uint32_t buffer = 0;
-      bool ready = true;
-      if (!empty) {
-        buffer = output_buffers == 2 ? (local & 1U) : 0U;
-        const uint32_t use = output_buffers == 2 ? (local >> 1) : local;
-        ++local;
-        ready = __all_sync(0xFFFFFFFFU, wait_checked(o_full_bar + 8U * buffer, use & 1U, abort_flag,
-                                                     args.device_error, 54)
-                                            ? 1
-                                            : 0) != 0;
-        ptx::tcgen05_fence_after_thread_sync();
+      if (a.chunks > 1 && item.chunk == 0 && item.kv_head == 0 && warp == 2 && lane == 0) {
+        const int by_rows = (item.cache_rows + a.chunk_keys - 1) / a.chunk_keys;
+        a.request_chunks[item.request] = by_rows > 0 ? by_rows : 1;
       }
+      const uint32_t buffer = output_buffers == 2 ? (local & 1U) : 0U;
+      const uint32_t use = output_buffers == 2 ? (local >> 1) : local;
+      ++local;
+      const bool ready =
+          __all_sync(0xFFFFFFFFU, wait_checked(o_full_bar + 8U * buffer, use & 1U, abort_flag,
+                                               args.device_error, 54)
+                                      ? 1
+                                      : 0) != 0;
+      ptx::tcgen05_fence_after_thread_sync();
       if (ready) {
         const uint32_t lane_address = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                       buffer * Shape::output_columns;
+        // First element of this (request, kv head) block, plus this thread's component.
+        const size_t block_base = static_cast<size_t>(item.request) * a.depth * width +
+                                  static_cast<size_t>(item.kv_head) * group * dimension +
+                                  quarter * 32 + lane;
+        float *partial_base =
+            a.chunks > 1 ? a.chunk_partials + item.chunk * chunk_elements + block_base : nullptr;
+        __nv_bfloat16 *output_base =
+            a.chunks > 1 ? nullptr : static_cast<__nv_bfloat16 *>(a.output) + block_base;
 #pragma unroll
         for (int slice = 0; slice < Shape::slices; ++slice) {
-          const int component = slice * 128 + quarter * 32 + lane;
 #pragma unroll
           for (int part = 0; part < padded_rows / 16; ++part) {
             if (part * 16 < rows) {           // warp-uniform
               uint32_t values[16];
-              if (!empty) {
-                ptx::tmem_load_32x32b_x16(lane_address + slice * padded_rows + part * 16, values);
-                ptx::tmem_load_wait();
-              } else {
-#pragma unroll
-                for (int entry = 0; entry < 16; ++entry)
-                  values[entry] = 0U;
-              }
+              ptx::tmem_load_32x32b_x16(lane_address + slice * padded_rows + part * 16, values);
+              ptx::tmem_load_wait();
 #pragma unroll
               for (int entry = 0; entry < 16; ++entry) {
                 const int row = part * 16 + entry;
                 if (row < rows) {
-                  const int local_head = row_head[row];
-                  const size_t out_row =
-                      static_cast<size_t>(item.request) * a.depth + row_token[row];
-                  const size_t column =
-                      static_cast<size_t>(item.kv_head * group + local_head) * dimension + component;
-                  const float value = __uint_as_float(values[entry]);
-                  if (a.chunks > 1) {
-                    a.chunk_partials[(static_cast<size_t>(item.chunk) * total_rows + out_row) *
-                                         width +
-                                     column] = value;
-                  } else {
-                    static_cast<__nv_bfloat16 *>(a.output)[out_row * width + column] =
-                        __float2bfloat16_rn(value);
-                  }
+                  const int offset = row_offset[row] + slice * 128;
+                  if (a.chunks > 1)
+                    partial_base[offset] = __uint_as_float(values[entry]);
+                  else
+                    output_base[offset] = __float2bfloat16_rn(__uint_as_float(values[entry]));
                 }
               }
             }
           }
         }
       }
-      if (!empty) {
-        ptx::tcgen05_fence_before_thread_sync();
-        __syncwarp();
-        if (lane == 0)
-          ptx::mbarrier_arrive(o_empty_bar + 8U * buffer);
-      }
+      ptx::tcgen05_fence_before_thread_sync();
+      __syncwarp();
+      if (lane == 0)
+        ptx::mbarrier_arrive(o_empty_bar + 8U * buffer);
     }
   } else {
     // ---- probability builders
@@ -992,14 +986,16 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
   }
 }
 
-// output[i] = bf16(sum over chunks of partials[chunk, i]), chunks summed in index order.
-__global__ void sum_chunks_kernel(const float *partials, int chunks, size_t elements,
+// output[i] = bf16(sum over the request's chunks of partials[chunk, i]), in index order.
+__global__ void sum_chunks_kernel(const float *partials, const int *request_chunks,
+                                  size_t request_elements, size_t elements,
                                   __nv_bfloat16 *output) {
   grid_dependency_launch();
   grid_dependency_wait();
   const size_t index = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
   if (index >= elements)
     return;
+  const int chunks = request_chunks[index / request_elements];
   float4 total = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
   for (int chunk = 0; chunk < chunks; ++chunk) {
     const float4 part = *reinterpret_cast<const float4 *>(partials + chunk * elements + index);
@@ -1058,9 +1054,11 @@ int launch_stream(const AttentionArguments &a, int *device_error, cudaStream_t s
     const size_t elements =
         static_cast<size_t>(a.requests) * a.depth * a.query_heads * dimension;
     const unsigned blocks = static_cast<unsigned>((elements / 4 + 255) / 256);
+    const size_t request_elements = static_cast<size_t>(a.depth) * a.query_heads * dimension;
     status = launch_chained(sum_chunks_kernel, dim3(blocks), dim3(256), 0, stream, false,
-                            static_cast<const float *>(a.chunk_partials), a.chunks, elements,
-                            static_cast<__nv_bfloat16 *>(a.output));
+                            static_cast<const float *>(a.chunk_partials),
+                            static_cast<const int *>(a.request_chunks), request_elements,
+                            elements, static_cast<__nv_bfloat16 *>(a.output));
   }
   return status == cudaSuccess ? 0 : -11;
 }
@@ -1084,7 +1082,7 @@ int launch_stream_rows(const AttentionArguments &a, int *device_error, cudaStrea
 
 int launch_attention_stream(const AttentionArguments &a, int *device_error, cudaStream_t stream) {
   if (a.maps == nullptr || a.stats == nullptr || a.stats_stride < a.chunks || a.chunks < 1 ||
-      (a.chunks > 1 && a.chunk_partials == nullptr) ||
+      (a.chunks > 1 && (a.chunk_partials == nullptr || a.request_chunks == nullptr)) ||
       a.chunk_keys <= 0 || a.chunk_keys % stream_tile_keys != 0 ||
       a.capacity % stream_tile_keys != 0) {
     return -1;

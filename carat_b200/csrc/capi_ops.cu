@@ -55,7 +55,7 @@ extern "C" int carat_b200_quantize_bf16_to_fp8(const void *bf16_input, void *fp8
   const int status = prepare_target(&target, fp8_output, device_scale, device_scratch, cuda_stream);
   if (status != 0)
     return status;
-  return finish(launch_quant(bf16_input, nullptr, 0, target, rows, width, cuda_stream),
+  return finish(launch_quant(bf16_input, nullptr, 0, nullptr, 1, target, rows, width, cuda_stream),
                 "FP8 quantization");
 }
 
@@ -247,6 +247,11 @@ int run_verify_attention(bool tensor_cores, const void *bf16_queries, const void
     static long long stats_rows = 0;
     static float *partials = nullptr;
     static size_t partial_bytes = 0;
+    static int *request_chunks = nullptr;       // [1024]: chunk counts of the last chunked call
+    if (request_chunks == nullptr &&
+        check_cuda(cudaMalloc(&request_chunks, sizeof(int) * 1024), "allocate chunk counts") != 0)
+      return -100;
+    a.request_chunks = request_chunks;
     constexpr int long_chunk_keys = 1024;
     if (!staged && a.max_cache_rows > long_chunk_keys) {
       // Long linear caches are cut into chunks like the runner does; the chunk partials live in

@@ -23,6 +23,8 @@ struct RowArguments {
   int splits;
   const float *input_scale;
   const float *weight_scale;
+  const int *valid_splits;           // optional per-row-group piece counts (see PartialSource)
+  int rows_per_group;
   const __nv_bfloat16 *embedding;
   const int *tokens;
   const int *row_indices;
@@ -159,14 +161,17 @@ __device__ __forceinline__ Pack8 load_source(const RowArguments &a, size_t row, 
     sum.v[index] = 0.0F;
   // Four pieces at a time, all loads before the first add: a loop that loads and adds piece by
   // piece pays one L2 round trip per piece.
-  for (int first = 0; first < a.splits; first += 4) {
+  int pieces = a.splits;
+  if (a.valid_splits != nullptr)
+    pieces = min(pieces, a.valid_splits[row / a.rows_per_group]);
+  for (int first = 0; first < pieces; first += 4) {
     float4 low[4];
     float4 high[4];
 #pragma unroll
     for (int offset = 0; offset < 4; ++offset) {
       low[offset] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
       high[offset] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-      if (first + offset < a.splits) {
+      if (first + offset < pieces) {
         const float *source =
             a.partial + (static_cast<size_t>(first + offset) * rows + row) * a.width + column;
         low[offset] = *reinterpret_cast<const float4 *>(source);
@@ -567,6 +572,8 @@ void set_source(RowArguments &arguments, const void *input, const PartialSource 
     arguments.splits = source.splits;
     arguments.input_scale = source.input_scale;
     arguments.weight_scale = source.weight_scale;
+    arguments.valid_splits = source.valid_splits;
+    arguments.rows_per_group = source.rows_per_group > 0 ? source.rows_per_group : 1;
   }
 }
 
@@ -632,8 +639,9 @@ int launch_norm_quant(const void *input, const void *norm_weight, void *normaliz
   return launch_rows<RowMode::norm>(arguments, rows, stream);
 }
 
-int launch_quant(const void *input, const float *chunk_partials, int chunks, QuantTarget target,
-                 int rows, int width, cudaStream_t stream) {
+int launch_quant(const void *input, const float *chunk_partials, int chunks,
+                 const int *request_chunks, int rows_per_request, QuantTarget target, int rows,
+                 int width, cudaStream_t stream) {
   if (input == nullptr && chunk_partials == nullptr)
     return -1;
   RowArguments arguments = base_arguments(target, width, 0.0F);
@@ -641,6 +649,8 @@ int launch_quant(const void *input, const float *chunk_partials, int chunks, Qua
   if (chunk_partials != nullptr && chunks > 0) {
     arguments.partial = chunk_partials;
     arguments.splits = chunks;
+    arguments.valid_splits = request_chunks;
+    arguments.rows_per_group = rows_per_request > 0 ? rows_per_request : 1;
   }
   return launch_rows<RowMode::plain>(arguments, rows, stream);
 }

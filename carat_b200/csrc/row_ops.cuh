@@ -25,6 +25,10 @@ struct PartialSource {
   int splits;
   const float *input_scale;  // device scalars of the linear that produced the partials
   const float *weight_scale;
+  // Optional: pieces beyond valid_splits[row / rows_per_group] were never written and are skipped
+  // (attention chunk partials: one count per request, rows_per_group = depth).
+  const int *valid_splits = nullptr;
+  int rows_per_group = 1;
 };
 
 // Tensor-scale quantisation of a tensor of any size in three launches (amax, scale, convert), the
@@ -56,9 +60,11 @@ int launch_norm_quant(const void *input, const void *norm_weight, void *normaliz
 
 // Plain tensor-scale quantisation of a bf16 tensor (cuda/linear.cu:76-115). When `partials` is
 // given (attention split over key chunks) the bf16 input is first formed as
-// bf16(sum_c partials[c]) from [chunks, rows, width] fp32.
-int launch_quant(const void *input, const float *chunk_partials, int chunks, QuantTarget target,
-                 int rows, int width, cudaStream_t stream);
+// bf16(sum_c partials[c]) from [chunks, rows, width] fp32. `request_chunks` (may be null: every
+// chunk counts) holds, per group of `rows_per_request` rows, how many chunks were written.
+int launch_quant(const void *input, const float *chunk_partials, int chunks,
+                 const int *request_chunks, int rows_per_request, QuantTarget target, int rows,
+                 int width, cudaStream_t stream);
 
 // projected = source (bf16 tensor or split-K partials); first = bf16(rmsnorm(projected) * w1 +
 // residual); second = bf16(rmsnorm(first) * w2) -> e4m3 (cuda/ops.cu:87-179,

@@ -166,6 +166,7 @@ struct carat_b200_runner {
   DeviceBuffer attention_partials;
   DeviceBuffer scores;
   DeviceBuffer attention_stats;   // float2 [score rows, global chunks]
+  DeviceBuffer request_chunks;    // int [batch]: chunks the last chunked attention wrote per request
   int stats_stride{0};
   DeviceBuffer projected;    // bf16 output of a linear that did not split K
   DeviceBuffer gate_up;
@@ -344,6 +345,7 @@ void build_runner(Runner &runner, const carat_b200_model_config &config,
     most_heads = std::max(most_heads, layer.shape.query_heads);
   runner.scores.allocate(static_cast<size_t>(rows) * most_heads *
                          std::max(runner.score_stride_sliding, runner.score_stride_global) * 2);
+  runner.request_chunks.allocate(static_cast<size_t>(batch) * sizeof(int), true);
   runner.stats_stride = global_chunks;
   runner.attention_stats.allocate(static_cast<size_t>(rows) * most_heads * global_chunks *
                                   sizeof(float2));
@@ -707,17 +709,21 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
     }
     attention.stats = runner.attention_stats.get<float2>();
     attention.stats_stride = runner.stats_stride;
+    attention.request_chunks = runner.request_chunks.get<int>();
     attention.maps = verify_attention_maps(runner, index, depth);
     require_launch(attention.maps != nullptr ? launch_attention_tc(attention, stream)
                                              : launch_attention_simt(attention, stream),
                    "verify attention");
     runner.launches += attention.maps != nullptr ? attention_tc_launches(attention) : 3;
 
+    // The tensor-core path writes only the chunks a request has rows in and says how many.
+    const bool counted = attention.chunks > 1 && attention.maps != nullptr;
     require_launch(launch_quant(attention.chunks > 1 ? nullptr : runner.attention_out.get(),
                                 attention.chunks > 1 ? runner.attention_partials.get<float>()
                                                      : nullptr,
-                                attention.chunks, target(word + 1), rows, layer.query_width(),
-                                stream),
+                                attention.chunks,
+                                counted ? runner.request_chunks.get<int>() : nullptr, depth,
+                                target(word + 1), rows, layer.query_width(), stream),
                    "attention output quantisation");
     runner.launches += 1;
 
@@ -946,15 +952,19 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
       attention.chunks = attention_chunks(attention.max_cache_rows, global_chunk_keys);
       attention.stats = runner.attention_stats.get<float2>();
       attention.stats_stride = runner.stats_stride;
+      attention.request_chunks = runner.request_chunks.get<int>();
       attention.maps = draft_attention_maps(runner, index);
       require_launch(attention.maps != nullptr ? launch_attention_tc(attention, stream)
                                                : launch_attention_simt(attention, stream),
                      "assistant attention");
       runner.launches += attention.maps != nullptr ? attention_tc_launches(attention) : 3;
+      const bool counted = attention.chunks > 1 && attention.maps != nullptr;
       require_launch(launch_quant(attention.chunks > 1 ? nullptr : runner.a_attention_out.get(),
                                   attention.chunks > 1 ? runner.a_attention_partials.get<float>()
                                                        : nullptr,
-                                  attention.chunks, target(word), requests, query_width, stream),
+                                  attention.chunks,
+                                  counted ? runner.request_chunks.get<int>() : nullptr, 1,
+                                  target(word), requests, query_width, stream),
                      "assistant attention quantisation");
       runner.launches += 1;
       const PartialSource o_source = run_linear(runner, plan.o, scales + word, w.o_scale,
