@@ -465,7 +465,9 @@ StepPlans &draft_plans_for(Runner &runner, int rows) {
     const auto &weights = runner.assistant_layers[static_cast<size_t>(index)];
     const int query_width = runner.assistant.query_heads * shared_layer(runner, index).shape.head_dim;
     LayerPlans entry;
-    entry.qkv = plan_linear(runner.a_quantized.get(), weights.qkv, rows, a_hidden, query_width, 0);
+    // Short K (a few K blocks) and a bf16 result: one piece per tile beats a split plus a
+    // finishing kernel even when the tiles do not fill the device.
+    entry.qkv = plan_linear(runner.a_quantized.get(), weights.qkv, rows, a_hidden, query_width, 1);
     entry.o = plan_linear(runner.a_quantized.get(), weights.o, rows, query_width, a_hidden, 0);
     entry.gate_up =
         plan_linear(runner.a_quantized.get(), weights.gate_up, rows, a_hidden, 2 * intermediate, 0);
@@ -479,7 +481,7 @@ StepPlans &draft_plans_for(Runner &runner, int rows) {
   plans.pre = plan_linear(runner.a_quantized.get(), runner.assistant_weights.pre_projection, rows,
                           2 * hidden, a_hidden, 0);
   plans.post = plan_linear(runner.a_quantized.get(), runner.assistant_weights.post_projection, rows,
-                           a_hidden, hidden, 0);
+                           a_hidden, hidden, 1);
   most_partial = std::max({most_partial, linear_partial_bytes(plans.pre),
                            linear_partial_bytes(plans.post)});
   if (most_partial > runner.split_partials.bytes())
