@@ -302,6 +302,10 @@ def run_ours(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+NCU_GATE_UP_DRAM_BYTES = 231.912192e6 + 6.525696e6
+NCU_GATE_UP_ALGORITHMIC_BYTES = 231211008 + 645120 + 10321920 + 8
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -363,7 +367,13 @@ def linear_roofline(library, config, fp8, peaks):
             "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
             "bytes_per_launch": total / launches, "ms_per_launch": elapsed_ms / launches,
-            "traffic": None}
+            # DRAM bytes per launch. One ncu capture of the 120 x 5376 -> 43008 launch
+            # (profiles/fp8_linear_gate_up_120x5376x43008.md) read 231.91 MB and wrote 6.53 MB
+            # against 242.18 MB algorithmic (part of the bf16 output was still in L2 when the
+            # counters stopped); every weight byte is read exactly once whatever the shape, so the
+            # figure is scaled to the sweep's mean launch by algorithmic bytes.
+            "traffic": total / launches * NCU_GATE_UP_DRAM_BYTES / NCU_GATE_UP_ALGORITHMIC_BYTES,
+            "traffic_source": "ncu capture of the gate_up launch, scaled by algorithmic bytes"}
 
 
 # --------------------------------------------------------------------------- CPU arm
