@@ -106,6 +106,7 @@ SIGNATURES = {
     "carat_b200_runner_last_predictions": (_I, [_P, _IP, _I]),
     "carat_b200_runner_device_pointer": (_I, [_P, _I, _I, POINTER(c_void_p), POINTER(c_size_t)]),
     "carat_b200_runner_read": (_I, [_P, _I, _I, c_size_t, _P, c_size_t]),
+    "carat_b200_runner_write": (_I, [_P, _I, _I, c_size_t, _P, c_size_t]),
     "carat_b200_runner_last_device_ms": (_I, [_P, POINTER(c_float), POINTER(c_float)]),
     "carat_b200_runner_last_launches": (_I, [_P, _IP, _IP]),
 }

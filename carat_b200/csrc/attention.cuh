@@ -4,8 +4,10 @@
 // Reference semantics (cuda/prefill_gemm_attention.cu:165-349,552-730, cuda/gemm_attention.cu:88-132):
 // scale 1.0; scores rounded to bf16; fp32 max / exp / sum over the visible keys; probabilities
 // rounded to bf16 (masked keys are exactly 0); P.V accumulated in fp32 and rounded to bf16 once.
-// The computation therefore runs in three phases over a bf16 score buffer, like the reference's
-// QK GEMM -> softmax -> PV GEMM, and each K and V row is streamed from HBM exactly once.
+// Every implementation keeps these rounding points and streams each K and V row from HBM exactly
+// once: the CUDA-core path in three kernels over a bf16 score buffer (like the reference's QK GEMM
+// -> softmax -> PV GEMM), the tensor-core paths in one kernel (sliding layers: scores stay in
+// shared memory) or two (scores + statistics, then P.V with the probabilities built on the fly).
 //
 // The score buffer's column layout (proposals in columns 0..15, cache rows from column 16 on) is
 // described in attention_geometry.cuh. A sliding ring is read in place: physical row r holds the
@@ -69,7 +71,8 @@ struct AttentionArguments {
 int launch_attention_simt(const AttentionArguments &arguments, cudaStream_t stream);
 
 // Tensor-core implementation (tcgen05 + TMA): head_dim 256 or 512, capacity a multiple of 128,
-// arguments.maps set. Same phases, same rounding points.
+// arguments.maps and arguments.stats set (and request_chunks when chunks > 1). Same rounding
+// points. Chooses the one-kernel path when it applies, else the two-kernel path.
 int launch_attention_tc(const AttentionArguments &arguments, cudaStream_t stream);
 
 // Kernels launch_attention_tc launches for these arguments (the CUDA-core path launches three).

@@ -46,25 +46,6 @@ __device__ __forceinline__ KeyGeometry key_geometry(const AttentionArguments &a,
                       a.draft != 0);
 }
 
-// Whether query `token` of a request at `position` may attend to score column `column`.
-__device__ __forceinline__ bool column_visible(const AttentionArguments &a, const KeyGeometry &g,
-                                               int position, int token, int column) {
-  if (column < proposal_columns)
-    return column < g.proposals && column <= token;
-  const int row = column - proposal_columns;
-  if (row >= g.cache_rows)
-    return false;
-  if (a.draft)
-    return true;
-  if (a.new_keys == nullptr)           // linear cache holding the proposals too: causal
-    return row <= position + token;
-  if (a.window <= 0)
-    return true;
-  // Physical ring row -> the newest logical position <= position - 1 it can hold.
-  const int newest = position - 1;
-  const int held = newest - ((newest - row) % a.capacity);
-  return held >= position + token - (a.window - 1);
-}
 #endif
 
 // Columns a launch has to cover for contexts up to `max_cache_rows`, rounded to whole 128-row

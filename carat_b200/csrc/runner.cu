@@ -1269,6 +1269,25 @@ extern "C" int carat_b200_runner_read(carat_b200_runner *runner, int which, int 
   });
 }
 
+extern "C" int carat_b200_runner_write(carat_b200_runner *runner, int which, int layer,
+                                       size_t offset, const void *source, size_t bytes) {
+  void *base = nullptr;
+  size_t available = 0;
+  const int status = carat_b200_runner_device_pointer(runner, which, layer, &base, &available);
+  if (status != 0)
+    return status;
+  return guarded([&] {
+    if (which < 0 || which > 2)
+      throw Failure{"only the KV caches and the hidden-by-slot table can be written"};
+    if (source == nullptr || offset + bytes > available)
+      throw Failure{"write exceeds the runner's buffer"};
+    require_cuda(cudaStreamSynchronize(runner->stream), "drain runner stream");
+    require_cuda(cudaMemcpy(static_cast<unsigned char *>(base) + offset, source, bytes,
+                            cudaMemcpyDefault),
+                 "write runner buffer");
+  });
+}
+
 extern "C" int carat_b200_runner_last_device_ms(const carat_b200_runner *runner, float *verify_ms,
                                                 float *draft_ms) {
   if (runner == nullptr)

@@ -342,6 +342,13 @@ class Gemma4BatchModelRunner:
                                                    holder.data_ptr(), elements * 2))
         return holder.reshape(shape)
 
+    def write_cache(self, which: int, layer: int, values: torch.Tensor) -> None:
+        """Overwrites a whole key (which = 0) or value (1) cache of `layer`, or the hidden-by-slot
+        table (2), with bf16 `values` laid out like the runner's buffer."""
+        data = values.to(dtype=torch.bfloat16).contiguous()
+        check(self._library.carat_b200_runner_write(self._handle, which, layer, 0, data.data_ptr(),
+                                                    data.numel() * 2))
+
     def key_cache(self, layer: int, capacity: int) -> torch.Tensor:
         shape = self.config.layers[layer]
         return self._device_view(0, layer, (self.batch(), shape.kv_heads, capacity,

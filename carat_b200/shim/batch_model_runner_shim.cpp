@@ -1,0 +1,245 @@
+// Drop-in implementation of carat::Gemma4BatchModelRunner (include/carat/batch_model_runner.h in
+// the Carat tree) over libcarat_b200's C ABI, for the speculative-decoding path:
+// verify_greedy_proposals, draft_four, append_ragged, reset_slot, seed_empty_cache_for_benchmark
+// and the accessors. Compile it inside the Carat build in place of cuda/batch_model_runner.cu and
+// link libcarat_b200.so; the scheduler (src/native_runtime_main.cpp) is unchanged.
+//
+// The methods outside that path (BF16 prefill, prefix reuse, clone_slot, the lock-step `append`)
+// throw: a build that needs them keeps the reference's runner for them. prefill_slot runs the
+// interim FP8 prefill of the library, which makes a prompt resident through the verify forward;
+// the reference prefills in BF16 (cuda/batch_model_runner.cu:1274-1275), so first tokens can
+// differ where logits nearly tie.
+#include "carat/batch_model_runner.h"
+#include "carat/device_weights.h"
+#include "carat/gemma4_config.h"
+
+#include "carat_b200.h"
+
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace carat {
+
+namespace {
+
+void check(int status) {
+  // The library reports the reference's own exception texts.
+  if (status != 0)
+    throw std::runtime_error(carat_b200_last_error());
+}
+
+[[noreturn]] void not_provided(const char *method) {
+  throw std::runtime_error(std::string(method) + " is not provided by carat-b200");
+}
+
+carat_b200_layer_weights layer_weights(const DeviceWeightArena &bf16, const Fp8WeightArena &fp8,
+                                       const std::string &prefix, bool assistant) {
+  const std::string projection = prefix + (assistant ? "q" : "qkv");
+  return carat_b200_layer_weights{
+      bf16.at(prefix + "input_norm"),
+      bf16.at(prefix + "q_norm"),
+      assistant ? nullptr : bf16.at(prefix + "k_norm"),
+      fp8.at(projection),
+      fp8.scale(projection),
+      fp8.at(prefix + "o"),
+      fp8.scale(prefix + "o"),
+      bf16.at(prefix + "post_attention_norm"),
+      bf16.at(prefix + "pre_mlp_norm"),
+      fp8.at(prefix + "gate_up"),
+      fp8.scale(prefix + "gate_up"),
+      fp8.at(prefix + "down"),
+      fp8.scale(prefix + "down"),
+      bf16.at(prefix + "post_mlp_norm"),
+      bf16.at(prefix + "scalar")};
+}
+
+} // namespace
+
+struct Gemma4BatchModelRunner::Implementation {
+  carat_b200_runner *handle{nullptr};
+  int batch{0};
+  int maximum_context{0};
+};
+
+Gemma4BatchModelRunner::Gemma4BatchModelRunner(const Gemma4Config &config,
+                                               const DeviceWeightArena &weights, int batch,
+                                               int maximum_context,
+                                               const Fp8WeightArena *fp8_weights,
+                                               const DeviceWeightArena *assistant_weights,
+                                               const Fp8WeightArena *assistant_fp8_weights)
+    : implementation_(std::make_unique<Implementation>()) {
+  if (fp8_weights == nullptr)
+    throw std::runtime_error("carat-b200 runs the FP8 path: an Fp8WeightArena is required");
+  std::vector<carat_b200_layer_shape> shapes;
+  std::vector<carat_b200_layer_weights> layers;
+  for (std::size_t index = 0; index < config.layers.size(); ++index) {
+    const Gemma4LayerConfig &layer = config.layers[index];
+    shapes.push_back({layer.attention == AttentionKind::global ? 1 : 0,
+                      static_cast<int32_t>(layer.query_heads), static_cast<int32_t>(layer.kv_heads),
+                      static_cast<int32_t>(layer.head_dimension),
+                      static_cast<float>(layer.rope_theta), layer.key_equals_value ? 1 : 0});
+    layers.push_back(layer_weights(weights, *fp8_weights,
+                                   "layer." + std::to_string(index) + ".", false));
+  }
+  const carat_b200_model_config model{
+      static_cast<int32_t>(config.hidden_size),     static_cast<int32_t>(config.intermediate_size),
+      static_cast<int32_t>(config.vocabulary_size), static_cast<int32_t>(config.sliding_window),
+      static_cast<float>(config.rms_norm_epsilon),  static_cast<int32_t>(shapes.size()),
+      shapes.data()};
+  const carat_b200_model_weights model_weights{
+      weights.at("token_embedding"), fp8_weights->at("token_embedding"),
+      fp8_weights->scale("token_embedding"), weights.at("final_norm"), layers.data()};
+
+  // The drafter's shape is fixed in the reference (cuda/assistant_runner.cu:22-27,166-170).
+  const int32_t assistant_layer_kinds[4] = {0, 0, 0, 1};
+  const carat_b200_assistant_config assistant_config{1024, 8192, 32, 4, assistant_layer_kinds,
+                                                     1.0e-6F};
+  std::vector<carat_b200_layer_weights> assistant_layers;
+  carat_b200_assistant_weights assistant{};
+  const bool with_assistant = assistant_weights != nullptr && assistant_fp8_weights != nullptr;
+  if (with_assistant) {
+    for (int index = 0; index < 4; ++index)
+      assistant_layers.push_back(layer_weights(*assistant_weights, *assistant_fp8_weights,
+                                               "layer." + std::to_string(index) + ".", true));
+    assistant = carat_b200_assistant_weights{
+        assistant_fp8_weights->at("token_embedding"),
+        assistant_fp8_weights->scale("token_embedding"),
+        assistant_fp8_weights->at("pre_projection"),
+        assistant_fp8_weights->scale("pre_projection"),
+        assistant_fp8_weights->at("post_projection"),
+        assistant_fp8_weights->scale("post_projection"),
+        assistant_weights->at("final_norm"),
+        assistant_layers.data()};
+  }
+  check(carat_b200_runner_create(&model, &model_weights, batch, maximum_context,
+                                 with_assistant ? &assistant_config : nullptr,
+                                 with_assistant ? &assistant : nullptr,
+                                 &implementation_->handle));
+  implementation_->batch = batch;
+  implementation_->maximum_context = maximum_context;
+}
+
+Gemma4BatchModelRunner::~Gemma4BatchModelRunner() {
+  if (implementation_ != nullptr && implementation_->handle != nullptr)
+    carat_b200_runner_destroy(implementation_->handle);
+}
+
+GreedyVerificationResult Gemma4BatchModelRunner::verify_greedy_proposals(
+    const std::vector<std::vector<int>> &proposals, const std::vector<int> &target_first_tokens,
+    const std::vector<int> &slots, const std::vector<int> &maximum_accepted_tokens) {
+  const int requests = static_cast<int>(proposals.size());
+  const int depth = requests > 0 ? static_cast<int>(proposals.front().size()) : 0;
+  if (requests == 0 || target_first_tokens.size() != proposals.size() ||
+      slots.size() != proposals.size()) {
+    throw std::runtime_error("invalid greedy verification batch");
+  }
+  if (!maximum_accepted_tokens.empty() && maximum_accepted_tokens.size() != proposals.size())
+    throw std::runtime_error("speculative acceptance caps do not match request count");
+  std::vector<int> flat;
+  flat.reserve(static_cast<std::size_t>(requests) * depth);
+  for (const std::vector<int> &row : proposals) {
+    if (static_cast<int>(row.size()) != depth)
+      throw std::runtime_error("invalid or repeated speculative slot");
+    flat.insert(flat.end(), row.begin(), row.end());
+  }
+  GreedyVerificationResult result;
+  result.accepted_tokens.resize(proposals.size());
+  result.next_tokens.resize(proposals.size());
+  check(carat_b200_runner_verify_greedy_proposals(
+      implementation_->handle, flat.data(), requests, depth, target_first_tokens.data(),
+      slots.data(), maximum_accepted_tokens.empty() ? nullptr : maximum_accepted_tokens.data(), 0,
+      result.accepted_tokens.data(), result.next_tokens.data()));
+  return result;
+}
+
+bool Gemma4BatchModelRunner::has_assistant() const {
+  return carat_b200_runner_has_assistant(implementation_->handle) != 0;
+}
+
+std::vector<std::vector<int>>
+Gemma4BatchModelRunner::draft_four(const std::vector<int> &last_tokens,
+                                   const std::vector<int> &slots,
+                                   const std::vector<int> &forced_first_tokens, int depth) {
+  if (last_tokens.empty() || slots.size() != last_tokens.size() || depth <= 0)
+    throw std::runtime_error("assistant is not configured or draft batch is invalid");
+  if (!forced_first_tokens.empty() && forced_first_tokens.size() != last_tokens.size())
+    throw std::runtime_error("forced assistant first tokens do not match draft batch");
+  std::vector<int> flat(last_tokens.size() * static_cast<std::size_t>(depth));
+  check(carat_b200_runner_draft(implementation_->handle, last_tokens.data(), slots.data(),
+                                forced_first_tokens.empty() ? nullptr : forced_first_tokens.data(),
+                                static_cast<int>(last_tokens.size()), depth, flat.data()));
+  std::vector<std::vector<int>> rows(last_tokens.size());
+  for (std::size_t row = 0; row < rows.size(); ++row)
+    rows[row].assign(flat.begin() + static_cast<std::ptrdiff_t>(row * depth),
+                     flat.begin() + static_cast<std::ptrdiff_t>((row + 1) * depth));
+  return rows;
+}
+
+std::vector<int> Gemma4BatchModelRunner::append_ragged(const std::vector<int> &token_ids,
+                                                       const std::vector<int> &slots) {
+  if (token_ids.empty() || slots.size() != token_ids.size())
+    throw std::runtime_error("invalid ragged token batch");
+  std::vector<int> next(token_ids.size());
+  check(carat_b200_runner_append_ragged(implementation_->handle, token_ids.data(), slots.data(),
+                                        static_cast<int>(token_ids.size()), next.data()));
+  return next;
+}
+
+int Gemma4BatchModelRunner::prefill_slot(int slot, const std::vector<int> &token_ids,
+                                         int chunk_tokens) {
+  int next = -1;
+  check(carat_b200_runner_prefill_slot_fp8(implementation_->handle, slot, token_ids.data(),
+                                           static_cast<int>(token_ids.size()),
+                                           chunk_tokens < 8 ? chunk_tokens : 8, &next));
+  return next;
+}
+
+void Gemma4BatchModelRunner::reset_slot(int slot) {
+  check(carat_b200_runner_reset_slot(implementation_->handle, slot));
+}
+
+void Gemma4BatchModelRunner::seed_empty_cache_for_benchmark(int position) {
+  check(carat_b200_runner_seed_empty_cache_for_benchmark(implementation_->handle, position));
+}
+
+int Gemma4BatchModelRunner::batch() const { return implementation_->batch; }
+
+int Gemma4BatchModelRunner::slot_position(int slot) const {
+  int position = 0;
+  check(carat_b200_runner_slot_position(implementation_->handle, slot, &position));
+  return position;
+}
+
+// ---- outside the path
+std::vector<int> Gemma4BatchModelRunner::append(const std::vector<int> &) {
+  not_provided("Gemma4BatchModelRunner::append");
+}
+int Gemma4BatchModelRunner::prefill_slot_from_prefix(int, const std::vector<int> &, int, int) {
+  not_provided("Gemma4BatchModelRunner::prefill_slot_from_prefix");
+}
+std::optional<int> Gemma4BatchModelRunner::prefill_slot_chunk(int, const std::vector<int> &, int) {
+  not_provided("Gemma4BatchModelRunner::prefill_slot_chunk");
+}
+std::vector<std::optional<int>>
+Gemma4BatchModelRunner::prefill_slots_chunks(const std::vector<int> &,
+                                             const std::vector<const std::vector<int> *> &, int) {
+  not_provided("Gemma4BatchModelRunner::prefill_slots_chunks");
+}
+std::vector<int>
+Gemma4BatchModelRunner::prefill_slots_suffix(const std::vector<int> &,
+                                             const std::vector<const std::vector<int> *> &) {
+  not_provided("Gemma4BatchModelRunner::prefill_slots_suffix");
+}
+LayerSlicedSuffixPrefillResult Gemma4BatchModelRunner::prefill_slots_suffix_layer_slice(
+    const std::vector<int> &, const std::vector<const std::vector<int> *> &, int) {
+  not_provided("Gemma4BatchModelRunner::prefill_slots_suffix_layer_slice");
+}
+void Gemma4BatchModelRunner::abort_suffix_layer_slices() {}
+bool Gemma4BatchModelRunner::has_suffix_layer_slices() const { return false; }
+std::uint64_t Gemma4BatchModelRunner::clone_slot(int, int) {
+  not_provided("Gemma4BatchModelRunner::clone_slot");
+}
+int Gemma4BatchModelRunner::position() const { not_provided("Gemma4BatchModelRunner::position"); }
+
+} // namespace carat

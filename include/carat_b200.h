@@ -397,6 +397,13 @@ CARAT_B200_API int carat_b200_runner_device_pointer(carat_b200_runner *runner, i
  * device memory) after the runner's stream has drained. */
 CARAT_B200_API int carat_b200_runner_read(carat_b200_runner *runner, int which, int layer,
                                           size_t offset, void *destination, size_t bytes);
+/* The opposite copy, for buffers 0-2 only (KV caches, hidden-by-slot table): restores state saved
+ * with carat_b200_runner_read, e.g. to move a slot's KV rows between runners or to start a test
+ * from a known cache. Positions are set separately (carat_b200_runner_seed_slot_positions, which
+ * zero-fills the caches, so call it first). No counterpart in the reference, whose clone_slot
+ * (cuda/batch_model_runner.cu:1499-1542) copies inside one runner. */
+CARAT_B200_API int carat_b200_runner_write(carat_b200_runner *runner, int which, int layer,
+                                           size_t offset, const void *source, size_t bytes);
 /* Device time of the last verify / draft call in milliseconds (CUDA events on the runner's
  * stream, kernels only). */
 CARAT_B200_API int carat_b200_runner_last_device_ms(const carat_b200_runner *runner, float *verify_ms,

@@ -1,0 +1,149 @@
+"""Device runner vs the CPU oracle with the head shapes of the 31B model (head_dim 256 sliding,
+head_dim 512 global with eight query heads per KV head), so that the runner drives the
+tensor-core attention kernels: the one-kernel sliding path, the two-kernel streaming path with a
+global context long enough for several 1024-row chunks (chunk partials summed by the next row
+kernel up to each request's own chunk count), and the drafter's attention over the shared caches.
+
+The caches start from seeded random rows written into both sides (a long prefill through a CPU
+oracle would take minutes), with ragged contexts: one slot inside the first chunk, one a few rows
+into the third, one with a ring that has not wrapped yet. The comparison is teacher-forced like
+tests/test_runner_parity_gpu.py and uses the same bar: bookkeeping bit-exact given the device's
+predictions, hidden states within the noise floor of the FP8 chain, differing predictions must be
+near-ties in the oracle's logits.
+"""
+import copy
+
+import pytest
+import torch
+
+import carat_b200
+from helpers import build_pair, rms_relative_error
+from oracle import carat_semantics as cs
+
+pytestmark = pytest.mark.gpu
+
+TOLERANCE = 0.12
+NEAR_TIE = 0.10
+MAX_CONTEXT = 2304          # 18 x 128 rows: three chunks of the global cache
+WINDOW = 256
+
+
+def small_real_config():
+    layers = [cs.LayerConfig("sliding", 4, 2, 256, 1e4, False),
+              cs.LayerConfig("global", 8, 1, 512, 1e6, True),
+              cs.LayerConfig("sliding", 4, 2, 256, 1e4, False)]
+    return cs.ModelConfig(256, 512, 2048, WINDOW, MAX_CONTEXT, 1e-6, layers)
+
+
+@pytest.fixture(scope="module")
+def pair(cuda_device):
+    config = small_real_config()
+    weights = cs.golden_tiny_weights(config)
+    assistant = cs.AssistantConfig(hidden=128, intermediate=256, query_heads=8,
+                                   layers=["sliding", "global"])
+    assistant_weights = cs.random_assistant_weights(config, assistant, 1)
+    oracle, device, _ = build_pair(config, weights, 3, assistant, assistant_weights)
+    positions = [700, 2100, 90]
+    device.seed_slot_positions(positions)
+    oracle.positions = list(positions)
+    generator = torch.Generator().manual_seed(5)
+    for index, layer in enumerate(config.layers):
+        capacity = config.capacity(index)
+        shape = (3, layer.kv_heads, capacity, layer.head_dim)
+        # Keys at the scale the model's own key norm produces, values at unit scale.
+        keys = cs.bf16(torch.randn(shape, generator=generator) * 0.35)
+        values = cs.bf16(torch.randn(shape, generator=generator))
+        for slot, position in enumerate(positions):
+            if position < capacity:       # rows the slot has not reached stay zero
+                keys[slot, :, position:, :] = 0
+                values[slot, :, position:, :] = 0
+        oracle.keys[index] = keys.clone()
+        oracle.values[index] = values.clone()
+        device.write_cache(0, index, keys)
+        device.write_cache(1, index, values)
+    hidden = cs.bf16(torch.randn(3, config.hidden, generator=generator))
+    oracle.target_hidden = hidden.clone()
+    device.write_cache(2, 0, hidden)
+    return config, oracle, device
+
+
+def near_tie(trace, row, chosen):
+    logits = trace.logits[row]
+    spread = float(logits.max() - logits.mean())
+    return float(logits.max() - logits[chosen]) < NEAR_TIE * spread
+
+
+def test_verify_steps_over_tensor_core_attention(pair):
+    config, oracle, device = pair
+    generator = torch.Generator().manual_seed(9)
+    slots = [0, 1, 2]
+    flagged = 0
+    for step, depth in enumerate([5, 5, 3]):
+        proposals = torch.randint(3, config.vocab, (3, depth), generator=generator).tolist()
+        firsts = [row[0] for row in proposals]
+        caps = [[5, 2, 4], [1, 5, 3], [3, 3, 3]][step]
+        scout = copy.deepcopy(oracle)
+        _, _, trace = scout.verify_greedy_proposals(proposals, firsts, slots, caps,
+                                                    assume_match=True, trace=True)
+        starts = [device.slot_position(slot) for slot in slots]
+        result = device.verify_greedy_proposals(proposals, firsts, slots, caps,
+                                                carat_b200.VERIFY_ASSUME_MATCH)
+        predictions = device.last_predictions(3 * depth)
+        want = cs.greedy_prefix_accept([list(p) for p in proposals], firsts, predictions, caps,
+                                       depth, True)
+        assert (result.accepted_tokens, result.next_tokens) == want
+        hidden = device.last_final_hidden(3 * depth)
+        assert rms_relative_error(hidden, trace.final_hidden) < TOLERANCE, step
+        for row, (got, expected) in enumerate(zip(predictions, trace.predictions.tolist())):
+            if got != expected:
+                assert near_tie(trace, row, got), (step, row, got, expected)
+                flagged += 1
+        oracle.verify_greedy_proposals(proposals, firsts, slots, result.accepted_tokens,
+                                       assume_match=True)
+        for request, slot in enumerate(slots):
+            assert device.slot_position(slot) == starts[request] + result.accepted_tokens[request]
+            assert device.slot_position(slot) == oracle.positions[slot]
+    for index in range(len(config.layers)):
+        capacity = config.capacity(index)
+        assert rms_relative_error(device.key_cache(index, capacity), oracle.keys[index]) < TOLERANCE
+        assert rms_relative_error(device.value_cache(index, capacity),
+                                  oracle.values[index]) < TOLERANCE
+    print(f"tensor-core runner parity: {flagged} near-tie predictions flagged")
+
+
+def test_rejected_rows_leave_the_sliding_ring_untouched(pair):
+    config, oracle, device = pair
+    before = device.key_cache(0, WINDOW).clone()
+    slots = [0, 1, 2]
+    starts = [device.slot_position(slot) for slot in slots]
+    proposals = [[7, 8, 9, 10, 11]] * 3
+    result = device.verify_greedy_proposals(proposals, [7, 7, 7], slots, [2, 0, 5],
+                                            carat_b200.VERIFY_ASSUME_MATCH)
+    assert result.accepted_tokens == [2, 0, 5]
+    oracle.verify_greedy_proposals(proposals, [7, 7, 7], slots, [2, 0, 5], assume_match=True)
+    after = device.key_cache(0, WINDOW)
+    for request, slot in enumerate(slots):
+        written = {(starts[request] + t) % WINDOW for t in range(result.accepted_tokens[request])}
+        untouched = [row for row in range(WINDOW) if row not in written]
+        assert torch.equal(after[slot][:, untouched, :].view(torch.int16),
+                           before[slot][:, untouched, :].view(torch.int16))
+
+
+def test_draft_over_shared_tensor_core_caches(pair):
+    """Two draft rows from the committed state: row 0 is the forced token, row 1 depends only on
+    forced inputs, so the drafter's hidden states are comparable with the oracle's."""
+    config, oracle, device = pair
+    slots = [0, 1, 2]
+    last_tokens = [11, 12, 13]
+    forced = [21, 22, 23]
+    want, traces = oracle.draft(last_tokens, slots, forced, 2, trace=True)
+    got = device.draft_four(last_tokens, slots, forced, 2)
+    assert [row[0] for row in got] == forced
+    hidden = device.assistant_final_hidden(3, oracle.assistant.hidden)
+    assert rms_relative_error(hidden, traces[1][0]) < TOLERANCE
+    assert rms_relative_error(device.assistant_previous_hidden(3), traces[1][1]) < TOLERANCE
+    mismatched = sum(1 for a, b in zip(got, want) if a[1] != b[1])
+    print(f"drafted second tokens that differ from the oracle: {mismatched} of 3")
+    longer = device.draft_four(last_tokens, slots, forced, 5)
+    assert [row[0] for row in longer] == forced
+    assert all(0 <= token < config.vocab for row in longer for token in row)
