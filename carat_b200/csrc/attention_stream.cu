@@ -30,7 +30,8 @@ namespace carat_b200 {
 namespace {
 
 constexpr int stream_tile_keys = 128;          // cache rows per score tile (UMMA M)
-constexpr int stream_stage_bytes = 16 * 1024;  // one [128 keys x 64 components] K sub-tile
+constexpr int stream_subtile_bytes = 16 * 1024; // one [128 keys x 64 components] K sub-tile
+constexpr int stream_stage_bytes = 2 * stream_subtile_bytes;   // two sub-tiles per ring stage
 constexpr int stream_value_keys = 32;          // cache rows per V stage
 constexpr float masked_score = -1.0e30F;       // stands in for -inf in the running statistics
 
@@ -188,7 +189,7 @@ template <int dimension, int padded_rows> struct ScoresShape {
   static constexpr int subtiles = dimension / 64;
   static constexpr int query_bytes = subtiles * padded_rows * 128;
   static constexpr int budget = 227 * 1024 - 1024 - 4096 - query_bytes;
-  static constexpr int stages = budget / stream_stage_bytes > 10 ? 10 : budget / stream_stage_bytes;
+  static constexpr int stages = budget / stream_stage_bytes > 5 ? 5 : budget / stream_stage_bytes;
   static constexpr int shared_bytes = query_bytes + stages * stream_stage_bytes + 1024;
 };
 
@@ -314,14 +315,19 @@ scores_stream_kernel(const __grid_constant__ CUtensorMap key_map,
           load_queries();
         if (item.proposals > 0) {
 #pragma unroll 1
-          for (int sub = 0; sub < subtiles && healthy; ++sub) {
+          for (int pair = 0; pair < subtiles / 2 && healthy; ++pair) {
             if (!wait_for_slot()) {
               healthy = false;
               break;
             }
-            ptx::mbarrier_arrive_expect_tx(full_bar + 8U * cursor.stage, proposal_columns * 128);
-            ptx::tma_load_2d(ring + cursor.stage * stream_stage_bytes, &new_key_map, sub * 64,
-                             item.staged_row0, full_bar + 8U * cursor.stage, reuse_policy);
+            ptx::mbarrier_arrive_expect_tx(full_bar + 8U * cursor.stage,
+                                           2 * proposal_columns * 128);
+#pragma unroll
+            for (int half = 0; half < 2; ++half)
+              ptx::tma_load_2d(ring + cursor.stage * stream_stage_bytes +
+                                   half * stream_subtile_bytes,
+                               &new_key_map, (pair * 2 + half) * 64, item.staged_row0,
+                               full_bar + 8U * cursor.stage, reuse_policy);
             cursor.advance();
           }
         }
@@ -329,14 +335,18 @@ scores_stream_kernel(const __grid_constant__ CUtensorMap key_map,
         for (int tile = 0; tile < tiles && healthy; ++tile) {
           const int row = item.cache_row0 + item.first_row + tile * stream_tile_keys;
 #pragma unroll
-          for (int sub = 0; sub < subtiles; ++sub) {
+          for (int pair = 0; pair < subtiles / 2; ++pair) {
             if (!wait_for_slot()) {
               healthy = false;
               break;
             }
             ptx::mbarrier_arrive_expect_tx(full_bar + 8U * cursor.stage, stream_stage_bytes);
-            ptx::tma_load_2d(ring + cursor.stage * stream_stage_bytes, &key_map, sub * 64, row,
-                             full_bar + 8U * cursor.stage, stream_policy);
+#pragma unroll
+            for (int half = 0; half < 2; ++half)
+              ptx::tma_load_2d(ring + cursor.stage * stream_stage_bytes +
+                                   half * stream_subtile_bytes,
+                               &key_map, (pair * 2 + half) * 64, row,
+                               full_bar + 8U * cursor.stage, stream_policy);
             cursor.advance();
           }
         }
@@ -387,20 +397,25 @@ scores_stream_kernel(const __grid_constant__ CUtensorMap key_map,
           ptx::tcgen05_fence_after_thread_sync();
           const uint32_t tmem_scores = tmem_base + accumulator * padded_rows;
 #pragma unroll
-          for (int sub = 0; sub < subtiles; ++sub) {
+          for (int pair = 0; pair < subtiles / 2; ++pair) {
             if (!wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
                               args.device_error, 44)) {
               healthy = false;
               break;
             }
             ptx::tcgen05_fence_after_thread_sync();
-            const uint32_t a_low = key_low + cursor.stage * (stream_stage_bytes >> 4);
-            const uint32_t b_low = query_low + sub * ((padded_rows * 128) >> 4);
 #pragma unroll
-            for (int step = 0; step < 4; ++step)
-              ptx::tcgen05_mma_f16_split(tmem_scores, a_low + 2 * step, desc_high,
-                                         b_low + 2 * step, desc_high, idesc,
-                                         (sub > 0 || step > 0) ? 1U : 0U);
+            for (int half = 0; half < 2; ++half) {
+              const int sub = pair * 2 + half;
+              const uint32_t a_low = key_low + cursor.stage * (stream_stage_bytes >> 4) +
+                                     half * (stream_subtile_bytes >> 4);
+              const uint32_t b_low = query_low + sub * ((padded_rows * 128) >> 4);
+#pragma unroll
+              for (int step = 0; step < 4; ++step)
+                ptx::tcgen05_mma_f16_split(tmem_scores, a_low + 2 * step, desc_high,
+                                           b_low + 2 * step, desc_high, idesc,
+                                           (sub > 0 || step > 0) ? 1U : 0U);
+            }
             ptx::tcgen05_commit(empty_bar + 8U * cursor.stage);
             cursor.advance();
           }

@@ -6,7 +6,8 @@ kernel up to each request's own chunk count), and the drafter's attention over t
 
 The caches start from seeded random rows written into both sides (a long prefill through a CPU
 oracle would take minutes), with ragged contexts: one slot inside the first chunk, one a few rows
-into the third, one with a ring that has not wrapped yet. The comparison is teacher-forced like
+into the third, one with a ring that has not wrapped yet. A one-layer model pins each attention
+kernel tightly; the two-layer model (one layer of each kind) is compared teacher-forced like
 tests/test_runner_parity_gpu.py and uses the same bar: bookkeeping bit-exact given the device's
 predictions, hidden states within the noise floor of the FP8 chain, differing predictions must be
 near-ties in the oracle's logits.
@@ -28,24 +29,22 @@ MAX_CONTEXT = 2304          # 18 x 128 rows: three chunks of the global cache
 WINDOW = 256
 
 
-def small_real_config():
-    layers = [cs.LayerConfig("sliding", 4, 2, 256, 1e4, False),
-              cs.LayerConfig("global", 8, 1, 512, 1e6, True),
-              cs.LayerConfig("sliding", 4, 2, 256, 1e4, False)]
-    return cs.ModelConfig(256, 512, 2048, WINDOW, MAX_CONTEXT, 1e-6, layers)
+SLIDING = cs.LayerConfig("sliding", 4, 2, 256, 1e4, False)
+GLOBAL = cs.LayerConfig("global", 8, 1, 512, 1e6, True)
+POSITIONS = [700, 2100, 90]
 
 
-@pytest.fixture(scope="module")
-def pair(cuda_device):
-    config = small_real_config()
+def small_real_config(layers=(SLIDING, GLOBAL)):
+    return cs.ModelConfig(256, 512, 2048, WINDOW, MAX_CONTEXT, 1e-6, list(layers))
+
+
+def build_seeded_pair(config, assistant=None, assistant_weights=None):
+    """Oracle and device runners over the same weights, with the same random rows in every cache
+    and the same ragged positions."""
     weights = cs.golden_tiny_weights(config)
-    assistant = cs.AssistantConfig(hidden=128, intermediate=256, query_heads=8,
-                                   layers=["sliding", "global"])
-    assistant_weights = cs.random_assistant_weights(config, assistant, 1)
     oracle, device, _ = build_pair(config, weights, 3, assistant, assistant_weights)
-    positions = [700, 2100, 90]
-    device.seed_slot_positions(positions)
-    oracle.positions = list(positions)
+    device.seed_slot_positions(POSITIONS)
+    oracle.positions = list(POSITIONS)
     generator = torch.Generator().manual_seed(5)
     for index, layer in enumerate(config.layers):
         capacity = config.capacity(index)
@@ -53,7 +52,7 @@ def pair(cuda_device):
         # Keys at the scale the model's own key norm produces, values at unit scale.
         keys = cs.bf16(torch.randn(shape, generator=generator) * 0.35)
         values = cs.bf16(torch.randn(shape, generator=generator))
-        for slot, position in enumerate(positions):
+        for slot, position in enumerate(POSITIONS):
             if position < capacity:       # rows the slot has not reached stay zero
                 keys[slot, :, position:, :] = 0
                 values[slot, :, position:, :] = 0
@@ -64,13 +63,71 @@ def pair(cuda_device):
     hidden = cs.bf16(torch.randn(3, config.hidden, generator=generator))
     oracle.target_hidden = hidden.clone()
     device.write_cache(2, 0, hidden)
+    return oracle, device
+
+
+@pytest.fixture(scope="module")
+def pair(cuda_device):
+    config = small_real_config()
+    assistant = cs.AssistantConfig(hidden=128, intermediate=256, query_heads=8,
+                                   layers=["sliding", "global"])
+    assistant_weights = cs.random_assistant_weights(config, assistant, 1)
+    oracle, device = build_seeded_pair(config, assistant, assistant_weights)
     return config, oracle, device
+
+
+@pytest.mark.parametrize("layer", [SLIDING, GLOBAL], ids=["sliding", "global"])
+def test_one_layer_first_step_is_tight(cuda_device, layer):
+    """One decoder layer from identical state: what separates the two sides is the summation order
+    inside the attention and the linears, before the FP8 chain has had a second layer to amplify
+    it (each further layer multiplies the norm-wise difference by two to five, measured)."""
+    config = small_real_config([layer])
+    oracle, device = build_seeded_pair(config)
+    generator = torch.Generator().manual_seed(9)
+    proposals = torch.randint(3, config.vocab, (3, 5), generator=generator).tolist()
+    firsts = [row[0] for row in proposals]
+    _, _, trace = oracle.verify_greedy_proposals(proposals, firsts, [0, 1, 2], [5, 5, 5],
+                                                 assume_match=True, trace=True)
+    device.verify_greedy_proposals(proposals, firsts, [0, 1, 2], [5, 5, 5],
+                                   carat_b200.VERIFY_ASSUME_MATCH)
+    assert rms_relative_error(device.last_final_hidden(15), trace.final_hidden) < 0.02
+    capacity = config.capacity(0)
+    assert rms_relative_error(device.key_cache(0, capacity), oracle.keys[0]) < 1e-3
+    assert rms_relative_error(device.value_cache(0, capacity), oracle.values[0]) < 1e-3
 
 
 def near_tie(trace, row, chosen):
     logits = trace.logits[row]
     spread = float(logits.max() - logits.mean())
     return float(logits.max() - logits[chosen]) < NEAR_TIE * spread
+
+
+def test_draft_over_shared_tensor_core_caches(pair):
+    """The drafter over the shared caches, from the seeded state both sides hold bit for bit: its
+    attention runs the same tensor-core kernels in draft mode (one query row per head, every
+    resident row visible), and here nothing upstream differs, so hidden states and tokens must
+    agree exactly. (After verify steps the two sides' caches differ in last bits, and this small
+    random-init drafter turns a one-ulp change of a single cached key row into a 20-50 % change of
+    its output, measured on the oracle alone, so a later comparison would say nothing.)"""
+    config, oracle, device = pair
+    slots = [0, 1, 2]
+    last_tokens = [11, 12, 13]
+    forced = [21, 22, 23]
+    scout = copy.deepcopy(oracle)
+    want, traces = scout.draft(last_tokens, slots, forced, 2, trace=True)
+    got = device.draft_four(last_tokens, slots, forced, 2)
+    assert got == want
+    hidden = device.assistant_final_hidden(3, oracle.assistant.hidden)
+    assert rms_relative_error(hidden, traces[1][0]) < 1e-3
+    assert rms_relative_error(device.assistant_previous_hidden(3), traces[1][1]) < 1e-3
+    longer = device.draft_four(last_tokens, slots, forced, 5)
+    assert [row[0] for row in longer] == forced
+    assert all(0 <= token < config.vocab for row in longer for token in row)
+    # Unforced drafts: the first token comes from one drafter forward; the later ones follow each
+    # side's own choices through the same chaotic chain and are not comparable.
+    want_free = copy.deepcopy(oracle).draft(last_tokens, slots, [], 3)
+    got_free = device.draft_four(last_tokens, slots, (), 3)
+    assert [row[0] for row in got_free] == [row[0] for row in want_free]
 
 
 def test_verify_steps_over_tensor_core_attention(pair):
@@ -129,21 +186,3 @@ def test_rejected_rows_leave_the_sliding_ring_untouched(pair):
                            before[slot][:, untouched, :].view(torch.int16))
 
 
-def test_draft_over_shared_tensor_core_caches(pair):
-    """Two draft rows from the committed state: row 0 is the forced token, row 1 depends only on
-    forced inputs, so the drafter's hidden states are comparable with the oracle's."""
-    config, oracle, device = pair
-    slots = [0, 1, 2]
-    last_tokens = [11, 12, 13]
-    forced = [21, 22, 23]
-    want, traces = oracle.draft(last_tokens, slots, forced, 2, trace=True)
-    got = device.draft_four(last_tokens, slots, forced, 2)
-    assert [row[0] for row in got] == forced
-    hidden = device.assistant_final_hidden(3, oracle.assistant.hidden)
-    assert rms_relative_error(hidden, traces[1][0]) < TOLERANCE
-    assert rms_relative_error(device.assistant_previous_hidden(3), traces[1][1]) < TOLERANCE
-    mismatched = sum(1 for a, b in zip(got, want) if a[1] != b[1])
-    print(f"drafted second tokens that differ from the oracle: {mismatched} of 3")
-    longer = device.draft_four(last_tokens, slots, forced, 5)
-    assert [row[0] for row in longer] == forced
-    assert all(0 <= token < config.vocab for row in longer for token in row)
