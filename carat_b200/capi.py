@@ -95,6 +95,7 @@ SIGNATURES = {
     "carat_b200_runner_verify_greedy_proposals": (_I, [_P, _IP, _I, _I, _IP, _IP, _IP, _I, _IP,
                                                       _IP]),
     "carat_b200_runner_append_ragged": (_I, [_P, _IP, _IP, _I, _IP]),
+    "carat_b200_runner_clone_slot": (_I, [_P, _I, _I, ctypes.POINTER(ctypes.c_uint64)]),
     "carat_b200_runner_draft": (_I, [_P, _IP, _IP, _IP, _I, _I, _IP]),
     "carat_b200_runner_prefill_slot_fp8": (_I, [_P, _I, _IP, _I, _I, _IP]),
     "carat_b200_runner_reset_slot": (_I, [_P, _I]),

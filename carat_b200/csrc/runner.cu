@@ -1152,6 +1152,51 @@ extern "C" int carat_b200_runner_reset_slot(carat_b200_runner *runner, int slot)
   });
 }
 
+extern "C" int carat_b200_runner_clone_slot(carat_b200_runner *runner, int source_slot,
+                                            int destination_slot, uint64_t *copied_bytes) {
+  return guarded([&] {
+    if (runner == nullptr || source_slot < 0 || source_slot >= runner->batch ||
+        destination_slot < 0 || destination_slot >= runner->batch ||
+        source_slot == destination_slot) {
+      throw Failure{"invalid cache slot clone"};
+    }
+    const int position = runner->slot_positions[static_cast<size_t>(source_slot)];
+    if (position <= 0 || position >= runner->maximum_context)
+      throw Failure{"source cache slot is empty or full"};
+    uint64_t copied = 0;
+    for (const LayerState &layer : runner->layers) {
+      // The first min(position, capacity) physical rows of every KV head, keys and values.
+      const int resident = std::min(position, layer.capacity);
+      const size_t row_bytes = static_cast<size_t>(resident) * layer.shape.head_dim * 2;
+      const size_t pitch = static_cast<size_t>(layer.head_stride) * 2;
+      for (unsigned char *base : {static_cast<unsigned char *>(layer.keys()),
+                                  static_cast<unsigned char *>(layer.values())}) {
+        require_cuda(cudaMemcpy2DAsync(
+                         base + static_cast<size_t>(destination_slot) * layer.slot_stride * 2,
+                         pitch, base + static_cast<size_t>(source_slot) * layer.slot_stride * 2,
+                         pitch, row_bytes, static_cast<size_t>(layer.shape.kv_heads),
+                         cudaMemcpyDeviceToDevice, runner->stream),
+                     "clone slot cache");
+        copied += row_bytes * static_cast<uint64_t>(layer.shape.kv_heads);
+      }
+    }
+    const size_t hidden_bytes = static_cast<size_t>(runner->config.hidden_size) * 2;
+    require_cuda(cudaMemcpyAsync(
+                     runner->hidden_by_slot.get<unsigned char>() + destination_slot * hidden_bytes,
+                     runner->hidden_by_slot.get<unsigned char>() + source_slot * hidden_bytes,
+                     hidden_bytes, cudaMemcpyDeviceToDevice, runner->stream),
+                 "clone slot target hidden state");
+    runner->slot_positions[static_cast<size_t>(destination_slot)] = position;
+    require_cuda(cudaMemcpyAsync(runner->device_slot_positions.get<int>() + destination_slot,
+                                 &runner->slot_positions[static_cast<size_t>(destination_slot)],
+                                 sizeof(int), cudaMemcpyHostToDevice, runner->stream),
+                 "clone slot position");
+    require_cuda(cudaStreamSynchronize(runner->stream), "synchronize slot cache clone");
+    if (copied_bytes != nullptr)
+      *copied_bytes = copied;
+  });
+}
+
 extern "C" int carat_b200_runner_seed_empty_cache_for_benchmark(carat_b200_runner *runner,
                                                                 int position) {
   return guarded([&] {

@@ -280,6 +280,15 @@ class Gemma4BatchModelRunner:
             self._handle, int_array(token_ids), int_array(slots), active, next_tokens))
         return list(next_tokens)
 
+    def clone_slot(self, source_slot: int, destination_slot: int) -> int:
+        """Copies a slot's resident KV rows, hand-off hidden row and position to another slot and
+        returns the KV bytes copied (Gemma4BatchModelRunner::clone_slot,
+        cuda/batch_model_runner.cu:1507-1542)."""
+        copied = ctypes.c_uint64(0)
+        check(self._library.carat_b200_runner_clone_slot(self._handle, source_slot,
+                                                         destination_slot, ctypes.byref(copied)))
+        return copied.value
+
     def has_assistant(self) -> bool:
         return bool(self._library.carat_b200_runner_has_assistant(self._handle))
 

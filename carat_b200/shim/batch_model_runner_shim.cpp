@@ -1,10 +1,10 @@
 // Drop-in implementation of carat::Gemma4BatchModelRunner (include/carat/batch_model_runner.h in
 // the Carat tree) over libcarat_b200's C ABI, for the speculative-decoding path:
-// verify_greedy_proposals, draft_four, append_ragged, reset_slot, seed_empty_cache_for_benchmark
-// and the accessors. Compile it inside the Carat build in place of cuda/batch_model_runner.cu and
+// verify_greedy_proposals, draft_four, append_ragged, clone_slot, reset_slot,
+// seed_empty_cache_for_benchmark and the accessors. Compile it inside the Carat build in place of cuda/batch_model_runner.cu and
 // link libcarat_b200.so; the scheduler (src/native_runtime_main.cpp) is unchanged.
 //
-// The methods outside that path (BF16 prefill, prefix reuse, clone_slot, the lock-step `append`)
+// The methods outside that path (BF16 prefill, prefix-reuse prefill, the lock-step `append`)
 // throw: a build that needs them keeps the reference's runner for them. prefill_slot runs the
 // interim FP8 prefill of the library, which makes a prompt resident through the verify forward;
 // the reference prefills in BF16 (cuda/batch_model_runner.cu:1274-1275), so first tokens can
@@ -195,6 +195,13 @@ int Gemma4BatchModelRunner::prefill_slot(int slot, const std::vector<int> &token
   return next;
 }
 
+std::uint64_t Gemma4BatchModelRunner::clone_slot(int source_slot, int destination_slot) {
+  std::uint64_t copied = 0;
+  check(carat_b200_runner_clone_slot(implementation_->handle, source_slot, destination_slot,
+                                     &copied));
+  return copied;
+}
+
 void Gemma4BatchModelRunner::reset_slot(int slot) {
   check(carat_b200_runner_reset_slot(implementation_->handle, slot));
 }
@@ -237,9 +244,6 @@ LayerSlicedSuffixPrefillResult Gemma4BatchModelRunner::prefill_slots_suffix_laye
 }
 void Gemma4BatchModelRunner::abort_suffix_layer_slices() {}
 bool Gemma4BatchModelRunner::has_suffix_layer_slices() const { return false; }
-std::uint64_t Gemma4BatchModelRunner::clone_slot(int, int) {
-  not_provided("Gemma4BatchModelRunner::clone_slot");
-}
 int Gemma4BatchModelRunner::position() const { not_provided("Gemma4BatchModelRunner::position"); }
 
 } // namespace carat

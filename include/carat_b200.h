@@ -367,6 +367,15 @@ CARAT_B200_API int carat_b200_runner_draft(carat_b200_runner *runner, const int 
 CARAT_B200_API int carat_b200_runner_prefill_slot_fp8(carat_b200_runner *runner, int slot, const int *tokens,
                                        int count, int chunk, int *next_token);
 
+/* Copies the resident KV rows (the first min(position, capacity) rows of every KV head of every
+ * layer), the slot's hidden-state hand-off row and the position of source_slot to
+ * destination_slot, so a request that shares a prompt prefix starts from it. copied_bytes (may be
+ * NULL) receives the KV bytes copied. Errors: "invalid cache slot clone", "source cache slot is
+ * empty or full". Replaces Gemma4BatchModelRunner::clone_slot
+ * (include/carat/batch_model_runner.h:54, cuda/batch_model_runner.cu:1507-1542). */
+CARAT_B200_API int carat_b200_runner_clone_slot(carat_b200_runner *runner, int source_slot,
+                                                int destination_slot, uint64_t *copied_bytes);
+
 /* include/carat/batch_model_runner.h:66-72 */
 CARAT_B200_API int carat_b200_runner_reset_slot(carat_b200_runner *runner, int slot);
 CARAT_B200_API int carat_b200_runner_seed_empty_cache_for_benchmark(carat_b200_runner *runner, int position);

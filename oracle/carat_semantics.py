@@ -629,6 +629,25 @@ class OracleRunner:
                                                       list(token_ids), list(slots))
         return next_tokens
 
+    def clone_slot(self, source_slot: int, destination_slot: int) -> int:
+        """cuda/batch_model_runner.cu:1507-1542: resident KV rows, hand-off hidden row and position
+        of one slot copied to another; returns the KV bytes copied."""
+        if (source_slot < 0 or source_slot >= self.slots or destination_slot < 0
+                or destination_slot >= self.slots or source_slot == destination_slot):
+            raise RuntimeError("invalid cache slot clone")
+        position = self.positions[source_slot]
+        if position <= 0 or position >= self.config.max_context:
+            raise RuntimeError("source cache slot is empty or full")
+        copied = 0
+        for index, layer in enumerate(self.config.layers):
+            resident = min(position, self.config.capacity(index))
+            for cache in (self.keys[index], self.values[index]):
+                cache[destination_slot][:, :resident, :] = cache[source_slot][:, :resident, :]
+                copied += 2 * resident * layer.kv_width
+        self.target_hidden[destination_slot] = self.target_hidden[source_slot]
+        self.positions[destination_slot] = position
+        return copied
+
     def seed_empty_cache_for_benchmark(self, position: int):
         """cuda/batch_model_runner.cu seed_empty_cache_for_benchmark: zero KV, advance positions."""
         for index in range(len(self.config.layers)):

@@ -245,6 +245,43 @@ def test_append_ragged_plain_decode(pair):
         device.append_ragged([config.vocab], [1])
 
 
+def test_clone_slot_copies_resident_state(pair):
+    """clone_slot: the destination holds the source's resident KV rows, hand-off hidden row and
+    position byte for byte, reports the reference's byte count, and continues exactly like the
+    source when each is stepped alone with the same tokens."""
+    config, oracle, device, _ = pair
+    import carat_b200
+    source, destination = 2, 1
+    position = device.slot_position(source)
+    assert position > 0
+    copied = device.clone_slot(source, destination)
+    assert copied == oracle.clone_slot(source, destination)
+    assert device.slot_position(destination) == position == oracle.positions[destination]
+    for index in range(len(config.layers)):
+        capacity = config.capacity(index)
+        resident = min(position, capacity)
+        for cache in (device.key_cache(index, capacity), device.value_cache(index, capacity)):
+            assert torch.equal(cache[destination][:, :resident].view(torch.int16),
+                               cache[source][:, :resident].view(torch.int16))
+    table = device.target_hidden_slots()
+    assert torch.equal(table[destination].view(torch.int16), table[source].view(torch.int16))
+    # Same state, same token, stepped alone (the activation scale depends on the cohort):
+    # identical next token and identical final hidden state, bit for bit.
+    first = device.append_ragged([17], [source])
+    hidden_source = device.last_final_hidden(1).clone()
+    second = device.append_ragged([17], [destination])
+    hidden_destination = device.last_final_hidden(1)
+    assert first == second
+    assert torch.equal(hidden_source.view(torch.int16), hidden_destination.view(torch.int16))
+    oracle.append_ragged([17], [source])
+    oracle.append_ragged([17], [destination])
+    with pytest.raises(carat_b200.CaratError, match="invalid cache slot clone"):
+        device.clone_slot(1, 1)
+    device.reset_slot(3)
+    with pytest.raises(carat_b200.CaratError, match="source cache slot is empty or full"):
+        device.clone_slot(3, 0)
+
+
 def test_argument_errors_match_the_reference(pair):
     config, oracle, device, _ = pair
     import carat_b200
