@@ -3,7 +3,7 @@
 // Contract (reference: cuda/linear.cu:645-803 Fp8Linear::run, tensor scaling):
 //   output[rows, N] = bf16( (x_scale * w_scale) * X_e4m3[rows, K] . W_e4m3[N, K]^T ), fp32 accumulate.
 //
-// The problem is HBM-bound (rows <= 128 means <= 256 FLOP per weight byte), so the design is a
+// The problem is HBM-bound (rows <= 256 means <= 512 FLOP per weight byte), so the design is a
 // weight stream: the operands are swapped so that 128 output features form the UMMA M dimension
 // and the (zero-padded) activation rows the UMMA N dimension. One CTA owns one 128-feature tile
 // over one K range; a TMA producer warp keeps a multi-stage ring of 128-byte-swizzled
@@ -387,11 +387,11 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
         {
           // Combine the four feature quarters in shared memory, then one global atomic per row.
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (epilogue_thread < args.rows && epilogue_thread < padded_rows) {
-            const unsigned long long candidate = row_best[epilogue_thread];
+          for (int row = epilogue_thread; row < args.rows && row < padded_rows; row += 128) {
+            const unsigned long long candidate = row_best[row];
             if (candidate != 0ULL)
-              atomicMax(args.best + epilogue_thread, candidate);
-            row_best[epilogue_thread] = 0ULL;
+              atomicMax(args.best + row, candidate);
+            row_best[row] = 0ULL;
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
         }
@@ -532,6 +532,8 @@ int launch_mode(const LinearPlan &plan, const KernelArguments &arguments, cudaSt
     return launch_variant<64, mode>(plan, arguments, stream);
   case 128:
     return launch_variant<128, mode>(plan, arguments, stream);
+  case 256:
+    return launch_variant<256, mode>(plan, arguments, stream);
   default:
     return -12;
   }
@@ -573,7 +575,7 @@ void schedule_linear(LinearPlan *plan, int rows, int input_width, int output_wid
   result.rows = rows;
   result.input_width = input_width;
   result.output_width = output_width;
-  result.padded_rows = rows <= 32 ? 32 : rows <= 64 ? 64 : 128;
+  result.padded_rows = rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
   result.tiles = (output_width + tile_features - 1) / tile_features;
   result.k_blocks = (input_width + tile_k_bytes - 1) / tile_k_bytes;
   result.ctas = multiprocessor_count();
@@ -611,7 +613,7 @@ void schedule_linear(LinearPlan *plan, int rows, int input_width, int output_wid
 } // namespace
 
 std::size_t linear_partial_bytes_for(int rows, int input_width, int output_width) {
-  if (rows <= 0 || rows > 128 || input_width <= 0 || output_width <= 0)
+  if (rows <= 0 || rows > 256 || input_width <= 0 || output_width <= 0)
     return 0;
   LinearPlan plan{};
   schedule_linear(&plan, rows, input_width, output_width, 0);
@@ -629,8 +631,8 @@ int make_linear_plan(LinearPlan *plan, const void *fp8_input, const void *fp8_we
       input_width <= 0 || output_width <= 0) {
     return fail("invalid FP8 linear shape", -1);
   }
-  if (rows > 128)
-    return fail("FP8 linear supports at most 128 rows", -2);
+  if (rows > 256)
+    return fail("FP8 linear supports at most 256 rows", -2);
   if (input_width % 16 != 0)
     return fail("FP8 linear input width must be a multiple of 16", -3);
   if ((reinterpret_cast<uintptr_t>(fp8_input) & 15U) != 0 ||

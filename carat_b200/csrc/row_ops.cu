@@ -47,6 +47,7 @@ struct RowArguments {
   int tail_first_column;
   int tail_width;
   int parts;                         // CTAs per row (GeGLU only; 0 or 1 = one)
+  __nv_bfloat16 *pass_rows;          // two-launch form: bf16 rows [rows, width] between the launches
   unsigned int *clear_base;
   int clear_words;
   int width;
@@ -202,10 +203,14 @@ __device__ __forceinline__ Pack8 load_source(const RowArguments &a, size_t row, 
 // store: the row never goes through shared or global memory between the phases. Static operands
 // (norm weights) are loaded before the wait on the previous grid, everything else right after it,
 // so one global-memory round trip feeds the whole kernel.
-template <RowMode mode, int chunks>
+//
+// `two_launches` = false: cooperative launch, one grid barrier between the maximum and the e4m3
+// store (needs every CTA resident at once). true: the kernel stops after the maximum, leaving the
+// bf16 rows in a.pass_rows, and quantize_rows_kernel finishes; used when there are more rows than
+// the device holds CTAs (the scratch words must then have been cleared by the caller).
+template <RowMode mode, int chunks, bool two_launches>
 __global__ void __launch_bounds__(row_threads, (mode == RowMode::geglu && chunks <= 4) ? 2 : 1)
 row_kernel(RowArguments a) {
-  cg::grid_group grid = cg::this_grid();
   __shared__ float scratch[2 * row_warps];
   int parity = 0;
 
@@ -239,13 +244,13 @@ row_kernel(RowArguments a) {
   }
   grid_dependency_wait();
 
-  if constexpr (mode == RowMode::embed_norm) {
+  if constexpr (mode == RowMode::embed_norm && !two_launches) {
     // The per-step scratch words must be zero before the first atomic maximum of the step; the
     // barrier below orders this against every later use, including this kernel's own.
     for (int word = static_cast<int>(blockIdx.x) * row_threads + static_cast<int>(threadIdx.x);
          word < a.clear_words; word += static_cast<int>(gridDim.x) * row_threads)
       a.clear_base[word] = 0U;
-    grid.sync();
+    cg::this_grid().sync();
   }
 
   float partial_scale = 1.0F;
@@ -446,7 +451,19 @@ row_kernel(RowArguments a) {
   row_amax = block_max(row_amax, scratch, parity);
   if (threadIdx.x == 0U)
     atomicMax(a.amax_bits, __float_as_uint(row_amax));
-  grid.sync();
+  if constexpr (two_launches) {
+#pragma unroll
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+      const int column = column_base + (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+      if (column >= column_end)
+        continue;
+      uint4 packed;
+      (void)round_bf16x8(values[chunk], &packed);   // already bf16-exact: repack
+      *reinterpret_cast<uint4 *>(a.pass_rows + row * width + column) = packed;
+    }
+    return;
+  }
+  cg::this_grid().sync();
   const float tensor_amax = __uint_as_float(*reinterpret_cast<volatile unsigned int *>(a.amax_bits));
   const float scale = tensor_amax > 0.0F ? tensor_amax / 448.0F : 1.0F;
   const float inverse_scale = 1.0F / scale;
@@ -469,8 +486,34 @@ row_kernel(RowArguments a) {
   }
 }
 
+// Second launch of the two-launch form: e4m3 = bf16 row / (maximum / 448), eight values a thread.
+__global__ void quantize_rows_kernel(const __nv_bfloat16 *rows, const unsigned int *amax_bits,
+                                     float *scale_out, unsigned char *fp8_output, size_t elements) {
+  grid_dependency_launch();
+  grid_dependency_wait();
+  const float tensor_amax = __uint_as_float(*amax_bits);
+  const float scale = tensor_amax > 0.0F ? tensor_amax / 448.0F : 1.0F;
+  const float inverse_scale = 1.0F / scale;
+  if (blockIdx.x == 0U && threadIdx.x == 0U)
+    *scale_out = scale;
+  const size_t index = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+  if (index >= elements)
+    return;
+  const Pack8 v = load_bf16x8(rows + index);
+  __nv_fp8x4_e4m3 low(make_float4(v.v[0] * inverse_scale, v.v[1] * inverse_scale,
+                                  v.v[2] * inverse_scale, v.v[3] * inverse_scale));
+  __nv_fp8x4_e4m3 high(make_float4(v.v[4] * inverse_scale, v.v[5] * inverse_scale,
+                                   v.v[6] * inverse_scale, v.v[7] * inverse_scale));
+  uint2 packed;
+  packed.x = low.__x;
+  packed.y = high.__x;
+  *reinterpret_cast<uint2 *>(fp8_output + index) = packed;
+}
+
+// `ctas` = rows * parts. Returns -2 when the grid cannot be resident at once and no two-launch
+// buffer was given.
 template <RowMode mode, int chunks>
-int launch_rows_chunks(const RowArguments &arguments, int rows, cudaStream_t stream) {
+int launch_rows_chunks(const RowArguments &arguments, int ctas, cudaStream_t stream) {
   static int resident_limit = -1;
   static cudaError_t configure_status = cudaSuccess;
   if (resident_limit < 0) {
@@ -483,16 +526,31 @@ int launch_rows_chunks(const RowArguments &arguments, int rows, cudaStream_t str
           cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device);
     if (configure_status == cudaSuccess)
       configure_status = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-          &per_multiprocessor, row_kernel<mode, chunks>, row_threads, 0);
+          &per_multiprocessor, row_kernel<mode, chunks, false>, row_threads, 0);
     resident_limit = configure_status == cudaSuccess ? multiprocessors * per_multiprocessor : 0;
   }
   if (configure_status != cudaSuccess)
     return -10;
-  if (rows > resident_limit)
+  if (ctas <= resident_limit) {
+    const cudaError_t status =
+        launch_chained(row_kernel<mode, chunks, false>, dim3(static_cast<unsigned>(ctas)),
+                       dim3(row_threads), 0, stream, true, arguments);
+    return status == cudaSuccess ? 0 : -11;
+  }
+  if (arguments.pass_rows == nullptr)
     return -2;
-  const cudaError_t status =
-      launch_chained(row_kernel<mode, chunks>, dim3(static_cast<unsigned>(rows)),
-                     dim3(row_threads), 0, stream, true, arguments);
+  cudaError_t status =
+      launch_chained(row_kernel<mode, chunks, true>, dim3(static_cast<unsigned>(ctas)),
+                     dim3(row_threads), 0, stream, false, arguments);
+  if (status != cudaSuccess)
+    return -11;
+  const int parts = arguments.parts > 1 ? arguments.parts : 1;
+  const size_t elements = static_cast<size_t>(ctas / parts) * arguments.width;
+  const unsigned blocks = static_cast<unsigned>((elements / 8 + 255) / 256);
+  status = launch_chained(quantize_rows_kernel, dim3(blocks), dim3(256), 0, stream, false,
+                          static_cast<const __nv_bfloat16 *>(arguments.pass_rows),
+                          static_cast<const unsigned int *>(arguments.amax_bits), arguments.scale,
+                          arguments.fp8_output, elements);
   return status == cudaSuccess ? 0 : -11;
 }
 
@@ -507,7 +565,7 @@ template <RowMode mode> int launch_rows(RowArguments arguments, int rows, cudaSt
     // Wide rows: two CTAs a row when the halves stay multiples of eight columns and the grid
     // still fits the device at once (checked by launch_rows_chunks).
     if (arguments.width >= 8192 && arguments.width % 16 == 0 && rows <= 148)
-      parts = 2;
+      parts = 2;   // 2 * 148 CTAs of the two-per-SM variant fit
   }
   for (; parts >= 1; --parts) {
     arguments.parts = parts;
@@ -560,6 +618,7 @@ RowArguments base_arguments(QuantTarget target, int width, float epsilon) {
   arguments.fp8_output = static_cast<unsigned char *>(target.fp8_output);
   arguments.scale = target.scale;
   arguments.amax_bits = target.amax_bits;
+  arguments.pass_rows = static_cast<__nv_bfloat16 *>(target.two_launch_rows);
   arguments.width = width;
   arguments.epsilon = epsilon;
   return arguments;

@@ -17,6 +17,10 @@ struct QuantTarget {
   void *fp8_output;        // [rows, width] e4m3
   float *scale;            // one fp32: amax / 448 (1.0 when amax == 0)
   unsigned int *amax_bits; // scratch word, zero on entry
+  // Optional bf16 scratch [rows, width]: lets the call run as two launches when there are more
+  // rows than the device holds CTAs at once (the one-launch form needs a grid barrier). Without
+  // it such calls fail. The embedding entry point then expects its scratch words pre-cleared.
+  void *two_launch_rows = nullptr;
 };
 
 // Sum of split-K partials: value = bf16((sum_s partial[s]) * input_scale * weight_scale).

@@ -26,8 +26,9 @@ using namespace carat_b200;
 namespace {
 
 constexpr int maximum_depth = 9;       // k = 8 drafts + the forced token
-constexpr int maximum_rows = 128;      // rows one FP8 linear launch accepts
+constexpr int maximum_rows = 256;      // rows one FP8 linear launch accepts (24 slots x depth 9 = 216)
 constexpr int global_chunk_keys = 1024;
+constexpr int resident_row_limit = 128;  // above this the step clears its scratch words up front
 
 struct Failure {
   std::string message;
@@ -167,6 +168,7 @@ struct carat_b200_runner {
   DeviceBuffer scores;
   DeviceBuffer attention_stats;   // float2 [score rows, global chunks]
   DeviceBuffer request_chunks;    // int [batch]: chunks the last chunked attention wrote per request
+  DeviceBuffer two_launch_rows;   // bf16 [maximum_rows, widest row]: row kernels with more rows than CTAs
   int stats_stride{0};
   DeviceBuffer projected;    // bf16 output of a linear that did not split K
   DeviceBuffer gate_up;
@@ -346,6 +348,7 @@ void build_runner(Runner &runner, const carat_b200_model_config &config,
   runner.scores.allocate(static_cast<size_t>(rows) * most_heads *
                          std::max(runner.score_stride_sliding, runner.score_stride_global) * 2);
   runner.request_chunks.allocate(static_cast<size_t>(batch) * sizeof(int), true);
+  runner.two_launch_rows.allocate(static_cast<size_t>(rows) * widest_input * 2);
   runner.stats_stride = global_chunks;
   runner.attention_stats.allocate(static_cast<size_t>(rows) * most_heads * global_chunks *
                                   sizeof(float2));
@@ -619,8 +622,15 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
   auto *best = reinterpret_cast<unsigned long long *>(amax + runner.amax_words);
   auto *scales = runner.scales.get<float>();
   const auto target = [&](int word) {
-    return QuantTarget{runner.quantized.get(), scales + word, amax + word};
+    return QuantTarget{runner.quantized.get(), scales + word, amax + word,
+                       runner.two_launch_rows.get()};
   };
+  // More rows than the device holds row-kernel CTAs: the row kernels run in their two-launch
+  // form, whose first kernel does not clear the scratch words itself.
+  if (rows > resident_row_limit)
+    require_cuda(cudaMemsetAsync(amax, 0, sizeof(int) * (runner.amax_words + 2 * maximum_rows),
+                                 stream),
+                 "clear step scratch");
 
   void *current = runner.hidden_a.get();
   void *other = runner.hidden_b.get();

@@ -44,7 +44,7 @@ CARAT_B200_API int carat_b200_device_error(int *code);
 
 /* output[rows, output_width] = bf16((input_scale * weight_scale) *
  *                                   input_e4m3[rows, input_width] . weight_e4m3[output_width, input_width]^T)
- * with fp32 accumulation. rows <= 128, input_width a multiple of 16, operands 16-byte aligned.
+ * with fp32 accumulation. rows <= 256, input_width a multiple of 16, operands 16-byte aligned.
  * `workspace` holds split-K partial sums and must be at least
  * carat_b200_fp8_linear_workspace_bytes() bytes (may be NULL when that is 0).
  * Replaces carat::Fp8Linear::run with Fp8Scaling::tensor (include/carat/linear.h:32-41,

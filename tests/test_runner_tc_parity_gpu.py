@@ -76,21 +76,26 @@ def pair(cuda_device):
     return config, oracle, device
 
 
+@pytest.mark.parametrize("depth", [5, 9])
 @pytest.mark.parametrize("layer", [SLIDING, GLOBAL], ids=["sliding", "global"])
-def test_one_layer_first_step_is_tight(cuda_device, layer):
+def test_one_layer_first_step_is_tight(cuda_device, layer, depth):
     """One decoder layer from identical state: what separates the two sides is the summation order
     inside the attention and the linears, before the FP8 chain has had a second layer to amplify
-    it (each further layer multiplies the norm-wise difference by two to five, measured)."""
+    it (each further layer multiplies the norm-wise difference by two to five, measured).
+    Depth 9 (k = 8 drafts) puts 18 query rows on a sliding KV head, more than the one-kernel path
+    takes, so the sliding layer then runs the two-kernel path with staged proposals."""
     config = small_real_config([layer])
     oracle, device = build_seeded_pair(config)
     generator = torch.Generator().manual_seed(9)
-    proposals = torch.randint(3, config.vocab, (3, 5), generator=generator).tolist()
+    proposals = torch.randint(3, config.vocab, (3, depth), generator=generator).tolist()
     firsts = [row[0] for row in proposals]
-    _, _, trace = oracle.verify_greedy_proposals(proposals, firsts, [0, 1, 2], [5, 5, 5],
+    caps = [depth, depth - 2, 1]
+    _, _, trace = oracle.verify_greedy_proposals(proposals, firsts, [0, 1, 2], caps,
                                                  assume_match=True, trace=True)
-    device.verify_greedy_proposals(proposals, firsts, [0, 1, 2], [5, 5, 5],
-                                   carat_b200.VERIFY_ASSUME_MATCH)
-    assert rms_relative_error(device.last_final_hidden(15), trace.final_hidden) < 0.02
+    result = device.verify_greedy_proposals(proposals, firsts, [0, 1, 2], caps,
+                                            carat_b200.VERIFY_ASSUME_MATCH)
+    assert result.accepted_tokens == caps
+    assert rms_relative_error(device.last_final_hidden(3 * depth), trace.final_hidden) < 0.02
     capacity = config.capacity(0)
     assert rms_relative_error(device.key_cache(0, capacity), oracle.keys[0]) < 1e-3
     assert rms_relative_error(device.value_cache(0, capacity), oracle.values[0]) < 1e-3
