@@ -7,4 +7,5 @@ mirror of the reference's runner interface.
 from .capi import CaratError, library  # noqa: F401
 from .runner import (DeviceWeightArena, Fp8WeightArena, Gemma4AssistantConfig,  # noqa: F401
                      Gemma4BatchModelRunner, Gemma4Config, Gemma4LayerConfig,
-                     GreedyVerificationResult, VERIFY_ASSUME_MATCH, quantize_tensor_to_fp8)
+                     GreedyVerificationResult, Int4Bf16Linear, VERIFY_ASSUME_MATCH,
+                     quantize_tensor_to_fp8)

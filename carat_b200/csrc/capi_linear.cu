@@ -1,7 +1,8 @@
-// C entry points for the FP8 linear kernels (declared in include/carat_b200.h).
+// C entry points for the FP8 and INT4 linear kernels (declared in include/carat_b200.h).
 #include "../../include/carat_b200.h"
 #include "context.cuh"
 #include "fp8_linear.cuh"
+#include "int4_linear.cuh"
 
 using namespace carat_b200;
 
@@ -117,4 +118,94 @@ extern "C" int carat_b200_fp8_linear_check(const void *fp8_input, const float *d
                                                 input_width, output_width,
                                                 static_cast<cudaStream_t>(stream)),
                        "FP8 linear check");
+}
+
+// INT4 weight-only linear ---------------------------------------------------------------------
+
+namespace {
+
+bool int4_shape_ok(int output_width, int input_width, int group_width) {
+  return output_width > 0 && input_width > 0 && (group_width == 128 || group_width == 256) &&
+         input_width % group_width == 0;
+}
+
+} // namespace
+
+extern "C" int carat_b200_int4_quantize_weight(const void *bf16_weight, void *packed_row_major,
+                                               void *bf16_scales, int output_width,
+                                               int input_width, int group_width, void *stream) {
+  if (bf16_weight == nullptr || packed_row_major == nullptr || bf16_scales == nullptr ||
+      !int4_shape_ok(output_width, input_width, group_width)) {
+    set_last_error("invalid BF16 INT4 linear weight shape");
+    return -1;
+  }
+  return launch_status(launch_int4_quantize(bf16_weight, packed_row_major, bf16_scales,
+                                            output_width, input_width, group_width,
+                                            static_cast<cudaStream_t>(stream)),
+                       "INT4 weight quantization");
+}
+
+extern "C" int carat_b200_int4_reorder_weight(const void *packed_row_major, void *reordered,
+                                              int output_width, int input_width, void *stream) {
+  if (packed_row_major == nullptr || reordered == nullptr || output_width <= 0 ||
+      input_width <= 0 || input_width % 8 != 0) {
+    set_last_error("invalid BF16 INT4 linear weight shape");
+    return -1;
+  }
+  const size_t bytes = static_cast<size_t>(output_width) * input_width / 2;
+  return launch_status(launch_int4_reorder(packed_row_major, reordered, bytes,
+                                           static_cast<cudaStream_t>(stream)),
+                       "INT4 weight reordering");
+}
+
+extern "C" size_t carat_b200_int4_linear_workspace_bytes(int rows, int input_width,
+                                                         int output_width) {
+  return int4_linear_partial_bytes_for(rows, input_width, output_width);
+}
+
+extern "C" int carat_b200_int4_linear(const void *bf16_input, const void *reordered_weight,
+                                      const void *bf16_scales, void *bf16_output, int rows,
+                                      int input_width, int output_width, int group_width,
+                                      void *workspace, size_t workspace_bytes, void *stream) {
+  if (bf16_output == nullptr) {
+    set_last_error("invalid BF16 INT4 linear activation shape");
+    return -1;
+  }
+  Int4LinearPlan plan;
+  const char *message = "invalid BF16 INT4 linear weight shape";
+  int status = make_int4_linear_plan(&plan, bf16_input, reordered_weight, bf16_scales, rows,
+                                     input_width, output_width, group_width, 0, &message);
+  if (status != 0) {
+    set_last_error(message);
+    return status;
+  }
+  const size_t needed = int4_linear_partial_bytes(plan);
+  if (needed > 0 && (workspace == nullptr || workspace_bytes < needed)) {
+    set_last_error("BF16 INT4 linear workspace is too small");
+    return -6;
+  }
+  int *error_word = device_error_word();
+  if (error_word == nullptr) {
+    set_last_error("device error word is unavailable");
+    return -101;
+  }
+  status = launch_int4_linear_bf16(plan, bf16_output, static_cast<float *>(workspace), error_word,
+                                   static_cast<cudaStream_t>(stream));
+  return launch_status(status, "BF16 INT4 linear");
+}
+
+extern "C" int carat_b200_int4_linear_check(const void *bf16_input, const void *packed_row_major,
+                                            const void *bf16_scales, void *bf16_output, int rows,
+                                            int input_width, int output_width, int group_width,
+                                            void *stream) {
+  if (bf16_input == nullptr || packed_row_major == nullptr || bf16_scales == nullptr ||
+      bf16_output == nullptr || rows <= 0 || !int4_shape_ok(output_width, input_width, group_width)) {
+    set_last_error("invalid BF16 INT4 linear weight shape");
+    return -1;
+  }
+  return launch_status(launch_int4_linear_simt_check(bf16_input, packed_row_major, bf16_scales,
+                                                     bf16_output, rows, input_width, output_width,
+                                                     group_width,
+                                                     static_cast<cudaStream_t>(stream)),
+                       "BF16 INT4 linear check");
 }

@@ -13,6 +13,7 @@
 // activation matrix is re-read from L2 by every tile with an evict-last policy.
 #include "fp8_linear.cuh"
 #include "launch.cuh"
+#include "linear_items.cuh"
 #include "ptx.cuh"
 
 #include <cuda_bf16.h>
@@ -23,7 +24,6 @@
 namespace carat_b200 {
 namespace {
 
-constexpr int tile_features = 128;  // UMMA M
 constexpr int tile_k_bytes = 128;   // one 128B swizzle atom of e4m3 per row
 constexpr int umma_k = 32;
 constexpr int linear_threads = 192; // warp 0 TMA, warp 1 MMA + TMEM, warps 2-5 epilogue
@@ -34,62 +34,6 @@ __host__ __device__ constexpr int stages_for(int padded_rows) {
   const int per_stage = weight_tile_bytes + padded_rows * tile_k_bytes;
   const int fit = shared_budget / per_stage;
   return fit > 8 ? 8 : fit;
-}
-
-struct KernelArguments {
-  const float *input_scale;
-  const float *weight_scale;
-  __nv_bfloat16 *output;
-  float *partial;             // mode 1: [splits, rows, output_width]
-  unsigned long long *best;   // mode 2
-  int *device_error;
-  int rows;
-  int output_width;
-  int tiles;
-  int k_blocks;
-  int splits;                 // K pieces per tile (1 unless mode 1)
-  int k_blocks_per_split;
-  // Mode 0 only: the last `tail_tiles` feature tiles are cut into `tail_splits` K pieces whose
-  // fp32 partial sums go to tail_partial [piece, rows, tail_tiles * 128] instead of `output`.
-  float *tail_partial;
-  int tail_tiles;
-  int tail_splits;
-  int tail_k_blocks_per_split;
-};
-
-struct WorkItem {
-  int tile;
-  int piece;
-  int k_begin;
-  int k_count;
-  bool tail;
-};
-
-// Items are numbered piece-major so that the pieces of one tile land on different CTAs; the whole
-// tiles come first and the pieces of the tail tiles last, so they fill the last partial round.
-__device__ __forceinline__ WorkItem decode_item(const KernelArguments &args, int index) {
-  WorkItem item;
-  const int whole_items = (args.tiles - args.tail_tiles) * args.splits;
-  if (index < whole_items) {
-    const int whole_tiles = args.tiles - args.tail_tiles;
-    item.tile = index % whole_tiles;
-    item.piece = index / whole_tiles;
-    item.k_begin = item.piece * args.k_blocks_per_split;
-    item.k_count = min(args.k_blocks, item.k_begin + args.k_blocks_per_split) - item.k_begin;
-    item.tail = false;
-  } else {
-    const int tail_index = index - whole_items;
-    item.tile = args.tiles - args.tail_tiles + tail_index % args.tail_tiles;
-    item.piece = tail_index / args.tail_tiles;
-    item.k_begin = item.piece * args.tail_k_blocks_per_split;
-    item.k_count = min(args.k_blocks, item.k_begin + args.tail_k_blocks_per_split) - item.k_begin;
-    item.tail = true;
-  }
-  return item;
-}
-
-__device__ __forceinline__ int item_count(const KernelArguments &args) {
-  return (args.tiles - args.tail_tiles) * args.splits + args.tail_tiles * args.tail_splits;
 }
 
 __device__ __forceinline__ unsigned int orderable_bf16(float rounded) {
@@ -464,25 +408,6 @@ __global__ void linear_simt_check_kernel(const __nv_fp8_e4m3 *input, const float
       __float2bfloat16_rn(sum * (input_scale[0] * weight_scale[0]));
 }
 
-using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
-                                 const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
-                                 const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_tiled_entry() {
-  static EncodeTiled entry = [] {
-    void *function = nullptr;
-    cudaDriverEntryPointQueryResult status{};
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &function, cudaEnableDefault, &status) !=
-            cudaSuccess ||
-        status != cudaDriverEntryPointSuccess) {
-      return static_cast<EncodeTiled>(nullptr);
-    }
-    return reinterpret_cast<EncodeTiled>(function);
-  }();
-  return entry;
-}
-
 // [outer, inner] row-major bytes, box [box_outer, 128] with the 128-byte swizzle; out-of-range
 // rows and K tails read as zero.
 bool encode_byte_matrix(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer,
@@ -553,61 +478,6 @@ KernelArguments base_arguments(const LinearPlan &plan, int *device_error, bool s
   arguments.tail_splits = 1;
   arguments.tail_k_blocks_per_split = plan.k_blocks;
   return arguments;
-}
-
-int multiprocessor_count() {
-  static int count = [] {
-    int device = 0;
-    int value = 0;
-    if (cudaGetDevice(&device) != cudaSuccess ||
-        cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
-        value <= 0) {
-      return 148;
-    }
-    return value;
-  }();
-  return count;
-}
-
-void schedule_linear(LinearPlan *plan, int rows, int input_width, int output_width,
-                     int requested_splits) {
-  LinearPlan &result = *plan;
-  result.rows = rows;
-  result.input_width = input_width;
-  result.output_width = output_width;
-  result.padded_rows = rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
-  result.tiles = (output_width + tile_features - 1) / tile_features;
-  result.k_blocks = (input_width + tile_k_bytes - 1) / tile_k_bytes;
-  result.ctas = multiprocessor_count();
-  int splits = requested_splits;
-  if (splits <= 0) {
-    // Fewer tiles than SMs: cut K so that most SMs stream; keep at least four K blocks a piece.
-    splits = result.tiles >= result.ctas ? 1 : result.ctas / result.tiles;
-    const int most = result.k_blocks / 4 < 1 ? 1 : result.k_blocks / 4;
-    splits = splits > most ? most : splits;
-  }
-  if (splits > result.k_blocks)
-    splits = result.k_blocks;
-  result.k_blocks_per_split = (result.k_blocks + splits - 1) / splits;
-  result.splits = (result.k_blocks + result.k_blocks_per_split - 1) / result.k_blocks_per_split;
-  // More tiles than SMs with a short last round: cutting the last round's tiles along K lets every
-  // SM take part in it (336 tiles on 148 SMs: 2 + 1/3 rounds instead of 3).
-  result.tail_tiles = 0;
-  result.tail_splits = 1;
-  result.tail_k_blocks_per_split = result.k_blocks;
-  const int remainder = result.tiles % result.ctas;
-  if (result.splits == 1 && result.tiles > result.ctas && remainder > 0 &&
-      remainder * 2 <= result.ctas && output_width % tile_features == 0) {
-    int pieces = result.ctas / remainder;
-    const int most = result.k_blocks / 4 < 1 ? 1 : result.k_blocks / 4;
-    pieces = pieces > most ? most : pieces;
-    if (pieces > 1) {
-      result.tail_tiles = remainder;
-      result.tail_k_blocks_per_split = (result.k_blocks + pieces - 1) / pieces;
-      result.tail_splits = (result.k_blocks + result.tail_k_blocks_per_split - 1) /
-                           result.tail_k_blocks_per_split;
-    }
-  }
 }
 
 } // namespace

@@ -209,6 +209,40 @@ __device__ __forceinline__ void tcgen05_mma_f8f6f4_split(uint32_t tmem_d, uint32
                : "memory");
 }
 
+// The same with the A operand in tensor memory: lane = A row (M = 128), each 32-bit column holds
+// two consecutive K elements, so one instruction (K = 16) consumes eight columns from `tmem_a`.
+__device__ __forceinline__ void tcgen05_mma_f16_tmem_a(uint32_t tmem_d, uint32_t tmem_a,
+                                                       uint32_t b_low, uint32_t b_high,
+                                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t"
+               ".reg .pred p;\n\t"
+               ".reg .b64 db;\n\t"
+               "setp.ne.b32 p, %5, 0;\n\t"
+               "mov.b64 db, {%2, %3};\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+               "}" ::"r"(tmem_d),
+               "r"(tmem_a), "r"(b_low), "r"(b_high), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+
+// Each thread of the warp writes 32 registers to 32 consecutive columns of its own TMEM lane.
+__device__ __forceinline__ void tmem_store_32x32b_x32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+      "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]),
+      "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]),
+      "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_store_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // Each thread of the warp reads 32 consecutive fp32 columns of its own TMEM lane
 // (lane = 32 * (warp % 4) + laneid).
 __device__ __forceinline__ void tmem_load_32x32b_x32(uint32_t taddr, uint32_t (&v)[32]) {

@@ -2,6 +2,7 @@
 inputs larger than the 126 MB L2 but well under a few GB on the device).
 
     python -m carat_b200.profile_cases linear      # FP8 linear 120 x 5376 -> 43008 (231 MB weights)
+    python -m carat_b200.profile_cases int4        # INT4 weight-only linear, same shape (116 MB of codes)
     python -m carat_b200.profile_cases lm_head     # fused LM head 120 x 5376 -> 262144 (1.4 GB)
     python -m carat_b200.profile_cases attention   # sliding verify attention, 24 slots, full ring
     python -m carat_b200.profile_cases global      # global verify attention, 24 slots, 4096 context
@@ -45,6 +46,32 @@ def linear(rows=120, k=5376, n=43008, launches=4):
     if launches > 1:
         micro = start.elapsed_time(stop) / (launches - 1) * 1e3
         print(f"linear {rows}x{k}x{n}: {micro:.1f} us per call, {k * n / micro / 1e6:.2f} TB/s of weights")
+
+
+def int4(rows=120, k=5376, n=43008, launches=4, group_width=128):
+    library = capi.library()
+    generator = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(rows, k, device="cuda", generator=generator).to(torch.bfloat16)
+    codes = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda", generator=generator)
+    scales = torch.full((k // group_width, n), 0.003, dtype=torch.bfloat16, device="cuda")
+    out = torch.empty(rows, n, dtype=torch.bfloat16, device="cuda")
+    need = library.carat_b200_int4_linear_workspace_bytes(rows, k, n)
+    work = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    for launch in range(launches):
+        if launch == 1:
+            start.record()
+        check(library.carat_b200_int4_linear(_ptr(x), _ptr(codes), _ptr(scales), _ptr(out), rows, k,
+                                             n, group_width, _ptr(work), need, None))
+    stop.record()
+    torch.cuda.synchronize()
+    if launches > 1:
+        micro = start.elapsed_time(stop) / (launches - 1) * 1e3
+        weight_bytes = k * n / 2 + (k // group_width) * n * 2
+        print(f"int4 linear {rows}x{k}x{n}: {micro:.1f} us per call, "
+              f"{weight_bytes / micro / 1e6:.2f} TB/s of codes and scales, "
+              f"{2 * rows * k * n / micro / 1e6:.0f} TFLOP/s")
 
 
 def lm_head(rows=120, k=5376, n=262144, launches=3):
@@ -107,11 +134,14 @@ def global_attention(launches=3):
               launches=launches)
 
 
-CASES = {"linear": linear, "lm_head": lm_head, "attention": attention, "global": global_attention}
+CASES = {"linear": linear, "int4": int4, "lm_head": lm_head, "attention": attention, "global": global_attention}
 
 if __name__ == "__main__":
     name = sys.argv[1] if len(sys.argv) > 1 else "linear"
-    if len(sys.argv) > 4:
+    if len(sys.argv) > 5:
+        CASES[name](launches=int(sys.argv[2]), k=int(sys.argv[3]), n=int(sys.argv[4]),
+                    rows=int(sys.argv[5]))
+    elif len(sys.argv) > 4:
         CASES[name](launches=int(sys.argv[2]), k=int(sys.argv[3]), n=int(sys.argv[4]))
     elif len(sys.argv) > 2:
         CASES[name](launches=int(sys.argv[2]))

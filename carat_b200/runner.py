@@ -121,6 +121,69 @@ def quantize_tensor_to_fp8(tensor: torch.Tensor):
     return output, scale
 
 
+class Int4Bf16Linear:
+    """Weight-only INT4 linear with bf16 activations (include/carat/linear.h:70-90 Int4Bf16Linear).
+
+    Like the reference's class, the constructor quantises a row-major bf16 [output_width,
+    input_width] weight in K-local groups (scale = bf16(max / 7), codes clamped to [-7, 7]) and
+    reorders the codes once for the kernel; `run` multiplies up to 128 bf16 rows with it."""
+
+    def __init__(self, row_major_weight: torch.Tensor, input_width: int, output_width: int,
+                 group_width: int = 256):
+        library = capi.library()
+        if (row_major_weight.dtype != torch.bfloat16 or input_width <= 0 or output_width <= 0
+                or row_major_weight.numel() != input_width * output_width
+                or group_width not in (128, 256) or input_width % group_width != 0
+                or output_width % 8 != 0):
+            raise CaratError("invalid BF16 INT4 linear weight shape")
+        device = row_major_weight.device
+        weight = row_major_weight.contiguous()
+        self.input_width = input_width
+        self.output_width = output_width
+        self.group_width = group_width
+        self.packed = torch.empty(output_width, input_width // 2, dtype=torch.uint8, device=device)
+        self.scales = torch.empty(input_width // group_width, output_width, dtype=torch.bfloat16,
+                                  device=device)
+        self.reordered = torch.empty_like(self.packed)
+        stream = torch.cuda.current_stream(device).cuda_stream
+        check(library.carat_b200_int4_quantize_weight(
+            weight.data_ptr(), self.packed.data_ptr(), self.scales.data_ptr(), output_width,
+            input_width, group_width, stream))
+        check(library.carat_b200_int4_reorder_weight(
+            self.packed.data_ptr(), self.reordered.data_ptr(), output_width, input_width, stream))
+        self._workspaces: Dict[int, torch.Tensor] = {}
+
+    @staticmethod
+    def supports_rows(rows: int) -> bool:
+        return 0 < rows <= 128
+
+    def run(self, bf16_input: torch.Tensor, bf16_output: Optional[torch.Tensor] = None):
+        library = capi.library()
+        rows = bf16_input.shape[0] if bf16_input.dim() == 2 else 0
+        if (bf16_input.dtype != torch.bfloat16 or not self.supports_rows(rows)
+                or bf16_input.shape[1] != self.input_width):
+            raise CaratError("invalid BF16 INT4 linear activation shape")
+        bf16_input = bf16_input.contiguous()
+        if bf16_output is None:
+            bf16_output = torch.empty(rows, self.output_width, dtype=torch.bfloat16,
+                                      device=bf16_input.device)
+        needed = library.carat_b200_int4_linear_workspace_bytes(rows, self.input_width,
+                                                                self.output_width)
+        workspace = self._workspaces.get(rows)
+        if workspace is None:
+            workspace = torch.empty(max(needed, 16), dtype=torch.uint8, device=bf16_input.device)
+            self._workspaces[rows] = workspace
+        stream = torch.cuda.current_stream(bf16_input.device).cuda_stream
+        check(library.carat_b200_int4_linear(
+            bf16_input.data_ptr(), self.reordered.data_ptr(), self.scales.data_ptr(),
+            bf16_output.data_ptr(), rows, self.input_width, self.output_width, self.group_width,
+            workspace.data_ptr(), needed, stream))
+        return bf16_output
+
+    def allocated_bytes(self) -> int:
+        return self.reordered.numel() + self.scales.numel() * 2
+
+
 class Fp8WeightArena:
     """e4m3 bytes + one fp32 scale per 2-D segment (include/carat/device_weights.h Fp8WeightArena,
     cuda/device_weights.cu:200-263)."""

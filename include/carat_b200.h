@@ -93,6 +93,44 @@ CARAT_B200_API int carat_b200_fp8_linear_check(const void *fp8_input, const floa
                                 void *bf16_output, int rows, int input_width, int output_width,
                                 void *stream);
 
+/* INT4 weight-only linear (W4A16) --------------------------------------------------------------- */
+
+/* Quantises a bf16 [output_width, input_width] weight in K-local groups of `group_width` (128 or
+ * 256) values: scale = bf16(max|w| / 7) (1.0 for an all-zero group), code = clamp(rint(w / scale),
+ * -7, 7). packed_row_major: output_width * input_width / 2 bytes, even K in the low nibble;
+ * bf16_scales: [input_width / group_width, output_width] (group-major).
+ * Replaces quantize_bf16_int4_kernel (cuda/int4_bf16_linear.cu:95-136), same layouts. */
+CARAT_B200_API int carat_b200_int4_quantize_weight(const void *bf16_weight, void *packed_row_major,
+                                                   void *bf16_scales, int output_width,
+                                                   int input_width, int group_width, void *stream);
+
+/* One-time reordering of the packed codes into the order the linear kernel streams (same size).
+ * Replaces the cutlass::reorder_tensor step of the reference's constructor
+ * (cuda/int4_bf16_linear.cu:268-276). */
+CARAT_B200_API int carat_b200_int4_reorder_weight(const void *packed_row_major, void *reordered,
+                                                  int output_width, int input_width, void *stream);
+
+/* output[rows, output_width] = bf16(input_bf16[rows, input_width] . W^T) with
+ * W[n, k] = bf16(code[n, k] * scale[k / group_width, n]) and fp32 accumulation. rows <= 128,
+ * output_width a multiple of 8, operands 16-byte aligned. `workspace` as for carat_b200_fp8_linear
+ * (size from carat_b200_int4_linear_workspace_bytes).
+ * Replaces carat::Int4Bf16Linear::run (include/carat/linear.h:70-90), whose constructor performs
+ * the two calls above. */
+CARAT_B200_API int carat_b200_int4_linear(const void *bf16_input, const void *reordered_weight,
+                                          const void *bf16_scales, void *bf16_output, int rows,
+                                          int input_width, int output_width, int group_width,
+                                          void *workspace, size_t workspace_bytes, void *stream);
+
+CARAT_B200_API size_t carat_b200_int4_linear_workspace_bytes(int rows, int input_width,
+                                                             int output_width);
+
+/* Same contract computed one output per thread from the row-major codes; a device-side
+ * cross-check for tests, no step path calls it. */
+CARAT_B200_API int carat_b200_int4_linear_check(const void *bf16_input, const void *packed_row_major,
+                                                const void *bf16_scales, void *bf16_output, int rows,
+                                                int input_width, int output_width, int group_width,
+                                                void *stream);
+
 /* Activation quantisation and fused row operators ----------------------------------------------- */
 
 /* All of these quantise a [rows, width] bf16 tensor to e4m3 with one tensor-wide scale:

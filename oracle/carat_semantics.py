@@ -181,6 +181,38 @@ def bf16_linear(x, w) -> torch.Tensor:
     return bf16(x @ w.t())
 
 
+def int4_quantize(weight: torch.Tensor, group_width: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cuda/int4_bf16_linear.cu:95-136: per output row and K-local group, scale = bf16(max|w| / 7)
+    (1 when the group is all zero), code = clamp(rint(w / float(scale)), -7, 7).
+    Returns (codes int8 [N, K], scales bf16-exact float [K / group, N], group-major)."""
+    rows, width = weight.shape
+    groups = width // group_width
+    grouped = weight.float().reshape(rows, groups, group_width)
+    maximum = grouped.abs().amax(dim=2)
+    scale = bf16(torch.where(maximum > 0, maximum / f32(7.0), torch.ones_like(maximum)))
+    codes = torch.clamp(torch.round(grouped / scale[:, :, None]), -7, 7)
+    return codes.reshape(rows, width).to(torch.int8), scale.t().contiguous()
+
+
+def int4_pack(codes: torch.Tensor) -> torch.Tensor:
+    """Two codes a byte, even K in the low nibble (cuda/int4_bf16_linear.cu:126-134)."""
+    nibbles = (codes.to(torch.int16) & 0xF).to(torch.uint8)
+    return nibbles[:, 0::2] | (nibbles[:, 1::2] << 4)
+
+
+def int4_dequantize(codes: torch.Tensor, scales: torch.Tensor, group_width: int) -> torch.Tensor:
+    """The weight the linear multiplies with: bf16(code * scale)
+    (tests/cuda_ops_tests.cu:824-843)."""
+    per_element = scales.t().repeat_interleave(group_width, dim=1)
+    return bf16(codes.float() * per_element)
+
+
+def int4_bf16_linear(x, codes, scales, group_width: int) -> torch.Tensor:
+    """Int4Bf16Linear::run (include/carat/linear.h:70-90): bf16(X . W^T) over the dequantised
+    weights, fp32 accumulation."""
+    return bf16_linear(x, int4_dequantize(codes, scales, group_width))
+
+
 def argmax_lowest_index(values: torch.Tensor) -> torch.Tensor:
     """cuda/ops.cu:890-981: maximum with ties to the lowest index (rows of bf16 logits)."""
     maximum = values.max(dim=-1, keepdim=True).values

@@ -52,3 +52,28 @@ def rms_relative_error(actual: torch.Tensor, expected: torch.Tensor) -> float:
     actual = actual.float().cpu().reshape(-1)
     expected = expected.float().cpu().reshape(-1)
     return float((actual - expected).norm() / expected.norm().clamp_min(1e-12))
+
+
+def one_ulp_apart(got: torch.Tensor, want: torch.Tensor) -> bool:
+    """Every element within one bf16 ulp of the reference. Near a cancellation (|value| far below
+    the tensor's typical magnitude) an ulp of the value itself is meaningless, because the fp32
+    partial sums that cancelled were rounded at their own, larger magnitude; the ulp of 1/16 of
+    the tensor's rms is the floor there."""
+    got = got.float()
+    want = want.float()
+    floor = want.pow(2).mean().sqrt() / 16
+    allowed = torch.maximum(want.abs(), floor) * 2.0 ** -7
+    return bool(((got - want).abs() <= allowed).all())
+
+
+def int4_reference_test_case():
+    """Weights and input of tests/cuda_ops_tests.cu:811-850, recomputed from their formulas."""
+    rows, input_width, output_width = 17, 512, 256
+    index = torch.arange(output_width * input_width, dtype=torch.float32)
+    amplitude = torch.where(index % input_width < 256, 1.0, 16.0)
+    weight = amplitude * (2.75 * torch.sin(index * 0.071) + 0.31 * torch.cos(index * 0.013))
+    cell = torch.arange(rows * input_width, dtype=torch.float32)
+    column = cell % input_width
+    value = 0.75 * torch.sin(cell * 0.037) - 0.21 * torch.cos(column * 0.019)
+    return (cs.bf16(weight).reshape(output_width, input_width),
+            cs.bf16(value).reshape(rows, input_width))

@@ -16,6 +16,7 @@ import torch
 
 import carat_b200
 from carat_b200.capi import check
+from helpers import one_ulp_apart
 from oracle import carat_semantics as cs
 
 pytestmark = pytest.mark.gpu
@@ -29,18 +30,6 @@ def quantised(rows, cols, std, seed):
     generator = torch.Generator(device="cuda").manual_seed(seed)
     values = (torch.randn(rows, cols, device="cuda", generator=generator) * std).to(torch.bfloat16)
     return carat_b200.quantize_tensor_to_fp8(values)
-
-
-def one_ulp_apart(got, want):
-    """Every element within one bf16 ulp of the reference. Near a cancellation (|value| far below
-    the tensor's typical magnitude) an ulp of the value itself is meaningless, because the fp32
-    partial sums that cancelled were rounded at their own, larger magnitude; the ulp of 1/16 of
-    the tensor's rms is the floor there."""
-    got = got.float()
-    want = want.float()
-    floor = want.pow(2).mean().sqrt() / 16
-    allowed = torch.maximum(want.abs(), floor) * 2.0 ** -7
-    return bool(((got - want).abs() <= allowed).all())
 
 
 SHAPES = [

@@ -210,3 +210,38 @@ def test_backup_restore_c_matches_python(c_oracle):
     for r in range(requests):
         assert np.array_equal(key_arrays[r], raw(keys[r]))
         assert np.array_equal(value_arrays[r], raw(values[r]))
+
+
+def test_int4_quantiser_follows_the_reference_test_oracle():
+    """tests/cuda_ops_tests.cu:824-843 spells the INT4 representation out element by element
+    (group maximum, bf16(max / 7), nearbyint, clamp to [-7, 7], bf16(code * scale)); the vectorised
+    restatement must agree with that loop on the test's own weights, whose second group of every
+    row is sixteen times larger than the first."""
+    import struct
+
+    from helpers import int4_reference_test_case
+
+    def to_bf16(value):
+        bits = struct.unpack("<I", struct.pack("<f", value))[0]
+        bits = (bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000
+        return struct.unpack("<f", struct.pack("<I", bits))[0]
+
+    def f32(value):
+        return struct.unpack("<f", struct.pack("<f", value))[0]
+
+    weight, _ = int4_reference_test_case()
+    codes, scales = cs.int4_quantize(weight, 256)
+    dequantised = cs.int4_dequantize(codes, scales, 256)
+    packed = cs.int4_pack(codes)
+    for row in (0, 1, 100, 255):
+        for begin in (0, 256):
+            values = [float(v) for v in weight[row, begin:begin + 256]]
+            maximum = max(abs(v) for v in values)
+            scale = to_bf16(f32(maximum / 7.0) if maximum > 0 else 1.0)
+            assert float(scales[begin // 256, row]) == scale
+            for offset, value in enumerate(values):
+                code = max(-7, min(7, round(f32(value / scale))))
+                assert int(codes[row, begin + offset]) == code
+                assert float(dequantised[row, begin + offset]) == to_bf16(f32(code * scale))
+                nibble = (int(packed[row, (begin + offset) // 2]) >> (4 * (offset & 1))) & 0xF
+                assert nibble == code & 0xF
