@@ -247,28 +247,33 @@ def run_ours(args, rank, world):
         next_tokens = result.next_tokens
         return sum(result.accepted_tokens), verify_ms, draft_ms, verify_launches + draft_launches
 
-    for step in range(args.warmup):
-        one_step(step)
-    barrier(world)
-    torch.cuda.synchronize()
-    sampler = ClockSampler(torch.cuda.current_device())
-    sampler.start()
-    positions_at_start = [runner.slot_position(slot) for slot in slots]
-    tokens = 0
-    device_ms = 0.0
-    verify_total_ms = 0.0
-    launches = 0
-    wall_start = time.perf_counter()
-    for step in range(args.warmup, args.warmup + args.steps):
-        accepted, verify_ms, draft_ms, step_launches = one_step(step)
-        tokens += accepted
-        device_ms += verify_ms + draft_ms
-        verify_total_ms += verify_ms
-        launches += step_launches
-    torch.cuda.synchronize()
-    wall_ms = (time.perf_counter() - wall_start) * 1e3
-    clocks = sampler.stop()
-    barrier(world)
+    def timed_run():
+        for step in range(args.warmup):
+            one_step(step)
+        barrier(world)
+        torch.cuda.synchronize()
+        sampler = ClockSampler(torch.cuda.current_device())
+        sampler.start()
+        positions = [runner.slot_position(slot) for slot in slots]
+        tokens = 0
+        device_ms = 0.0
+        verify_total_ms = 0.0
+        launches = 0
+        wall_start = time.perf_counter()
+        for step in range(args.warmup, args.warmup + args.steps):
+            accepted, verify_ms, draft_ms, step_launches = one_step(step)
+            tokens += accepted
+            device_ms += verify_ms + draft_ms
+            verify_total_ms += verify_ms
+            launches += step_launches
+        torch.cuda.synchronize()
+        wall_ms = (time.perf_counter() - wall_start) * 1e3
+        clocks = sampler.stop()
+        barrier(world)
+        return positions, tokens, device_ms, verify_total_ms, launches, wall_ms, clocks
+
+    (positions_at_start, tokens, device_ms, verify_total_ms, launches, wall_ms,
+     clocks) = timed_run()
 
     totals = reduce_max_and_sum(world, [device_ms, wall_ms], [float(tokens)])
     device_ms_max, wall_ms_max = totals[0]
@@ -297,9 +302,52 @@ def run_ours(args, rank, world):
         "mean_accepted": tokens / args.steps / SLOTS,
     }
     line["roofline"] = linear_roofline(library, config, fp8, peaks)
+    if world == 1 and args.int4_mlp:
+        line["int4_mlp"] = int4_variant(config, runner, timed_run, args, weight_bytes)
     if world == 1 and not args.skip_cpu:
         line["cpu_baseline"] = cpu_sample(config, lengths, kind_only=False)
     print(json.dumps(line), flush=True)
+
+
+def int4_variant(config, runner, timed_run, args, fp8_weight_bytes):
+    """The same timed loop with the target's gate_up / down as INT4 weight-only linears (groups of
+    128, bf16 activations): random codes and a constant scale stand in for quantised weights, the
+    work per step does not depend on the values."""
+    from carat_b200 import capi
+    try:
+        hidden, inter = config.hidden_size, config.intermediate_size
+        group = 128
+        generator = torch.Generator(device="cuda").manual_seed(5)
+        layers = (capi.Int4MlpLayer * len(config.layers))()
+        keep = []
+        up_scales = torch.full((hidden // group, 2 * inter), 0.006, dtype=torch.bfloat16,
+                               device="cuda")
+        down_scales = torch.full((inter // group, hidden), 0.006, dtype=torch.bfloat16,
+                                 device="cuda")
+        for index in range(len(config.layers)):
+            up = torch.randint(0, 256, (2 * inter, hidden // 2), dtype=torch.uint8, device="cuda",
+                               generator=generator)
+            down = torch.randint(0, 256, (hidden, inter // 2), dtype=torch.uint8, device="cuda",
+                                 generator=generator)
+            keep += [up, down]
+            layers[index].gate_up_codes = up.data_ptr()
+            layers[index].gate_up_scales = up_scales.data_ptr()
+            layers[index].down_codes = down.data_ptr()
+            layers[index].down_scales = down_scales.data_ptr()
+        torch.cuda.synchronize()
+        capi.check(capi.library().carat_b200_runner_use_int4_mlp(runner._handle, layers,
+                                                                 len(layers), group))
+        _, tokens, device_ms, verify_total_ms, launches, wall_ms, _ = timed_run()
+        capi.check(capi.library().carat_b200_runner_use_int4_mlp(runner._handle, None, 0, 0))
+        mlp_e4m3 = len(config.layers) * 3 * inter * hidden
+        mlp_int4 = len(config.layers) * (3 * inter * hidden // 2 + 3 * inter * hidden // group * 2)
+        return {"value": tokens / (device_ms / 1e3), "unit": UNIT,
+                "e2e": tokens / (wall_ms / 1e3), "ms_per_step": device_ms / args.steps,
+                "verify_ms": verify_total_ms / args.steps, "gpu_launches": launches,
+                "group_width": group,
+                "weight_bytes": fp8_weight_bytes - mlp_e4m3 + mlp_int4}
+    except Exception as error:  # the e4m3 numbers of the line stand on their own
+        return {"error": str(error)}
 
 
 NCU_GATE_UP_DRAM_BYTES = 231.912192e6 + 6.525696e6
@@ -499,6 +547,8 @@ def main():
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--int4-mlp", action="store_true",
+                        help="also time the step with INT4 weight-only MLP linears (N = 1 only)")
     parser.add_argument("--skip-cpu", action="store_true",
                         help="leave the cpu_baseline object out (profiling runs)")
     args = parser.parse_args()

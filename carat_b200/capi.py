@@ -36,6 +36,11 @@ class LayerWeights(Structure):
                 ("down_scale", c_void_p), ("post_mlp_norm", c_void_p), ("scalar", c_void_p)]
 
 
+class Int4MlpLayer(Structure):
+    _fields_ = [("gate_up_codes", c_void_p), ("gate_up_scales", c_void_p),
+                ("down_codes", c_void_p), ("down_scales", c_void_p)]
+
+
 class ModelWeights(Structure):
     _fields_ = [("token_embedding", c_void_p), ("token_embedding_fp8", c_void_p),
                 ("token_embedding_scale", c_void_p), ("final_norm", c_void_p),
@@ -97,6 +102,7 @@ SIGNATURES = {
                                      POINTER(AssistantConfig), POINTER(AssistantWeights),
                                      POINTER(c_void_p)]),
     "carat_b200_runner_destroy": (None, [_P]),
+    "carat_b200_runner_use_int4_mlp": (_I, [_P, POINTER(Int4MlpLayer), _I, _I]),
     "carat_b200_runner_verify_greedy_proposals": (_I, [_P, _IP, _I, _I, _IP, _IP, _IP, _I, _IP,
                                                       _IP]),
     "carat_b200_runner_append_ragged": (_I, [_P, _IP, _IP, _I, _IP]),

@@ -354,6 +354,8 @@ row_kernel(RowArguments a) {
         product.v[index] = gelu_tanh(gate.v[index]) * up.v[index];
       uint4 packed;
       values[chunk] = round_bf16x8(product, &packed);
+      if (a.second_out != nullptr)
+        *reinterpret_cast<uint4 *>(a.second_out + row * width + column) = packed;
     } else {
       values[chunk] = load_source(a, row, column, rows, partial_scale);
       if constexpr (mode == RowMode::plain) {
@@ -440,6 +442,9 @@ row_kernel(RowArguments a) {
         *reinterpret_cast<uint4 *>(a.second_out + row * width + column) = packed;
     }
   }
+
+  if (a.fp8_output == nullptr)
+    return;   // bf16 consumer: the row is already stored (uniform over the grid)
 
   // ---- tensor-wide maximum, one barrier, e4m3 from registers
   float row_amax = 0.0F;
@@ -531,6 +536,13 @@ int launch_rows_chunks(const RowArguments &arguments, int ctas, cudaStream_t str
   }
   if (configure_status != cudaSuccess)
     return -10;
+  if (arguments.fp8_output == nullptr) {
+    // No quantisation, so no grid barrier: any number of CTAs, plain launch.
+    const cudaError_t status =
+        launch_chained(row_kernel<mode, chunks, false>, dim3(static_cast<unsigned>(ctas)),
+                       dim3(row_threads), 0, stream, false, arguments);
+    return status == cudaSuccess ? 0 : -11;
+  }
   if (ctas <= resident_limit) {
     const cudaError_t status =
         launch_chained(row_kernel<mode, chunks, false>, dim3(static_cast<unsigned>(ctas)),
@@ -555,11 +567,12 @@ int launch_rows_chunks(const RowArguments &arguments, int ctas, cudaStream_t str
 }
 
 template <RowMode mode> int launch_rows(RowArguments arguments, int rows, cudaStream_t stream) {
-  if (rows <= 0 || arguments.width <= 0 || arguments.width % 8 != 0 ||
-      arguments.fp8_output == nullptr || arguments.scale == nullptr ||
-      arguments.amax_bits == nullptr) {
+  const bool quantised = arguments.fp8_output != nullptr && arguments.scale != nullptr &&
+                         arguments.amax_bits != nullptr;
+  const bool bf16_only = arguments.fp8_output == nullptr && arguments.second_out != nullptr &&
+                         (mode == RowMode::post_attention || mode == RowMode::geglu);
+  if (rows <= 0 || arguments.width <= 0 || arguments.width % 8 != 0 || !(quantised || bf16_only))
     return -1;
-  }
   int parts = 1;
   if constexpr (mode == RowMode::geglu) {
     // Wide rows: two CTAs a row when the halves stay multiples of eight columns and the grid
@@ -619,6 +632,7 @@ RowArguments base_arguments(QuantTarget target, int width, float epsilon) {
   arguments.scale = target.scale;
   arguments.amax_bits = target.amax_bits;
   arguments.pass_rows = static_cast<__nv_bfloat16 *>(target.two_launch_rows);
+  arguments.second_out = static_cast<__nv_bfloat16 *>(target.bf16_output);
   arguments.width = width;
   arguments.epsilon = epsilon;
   return arguments;

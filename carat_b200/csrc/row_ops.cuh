@@ -21,6 +21,9 @@ struct QuantTarget {
   // rows than the device holds CTAs at once (the one-launch form needs a grid barrier). Without
   // it such calls fail. The embedding entry point then expects its scratch words pre-cleared.
   void *two_launch_rows = nullptr;
+  // When fp8_output is null the call stops after the bf16 row: it is stored here and nothing is
+  // quantised (the consumer is a linear with bf16 activations; scale and amax_bits are unused).
+  void *bf16_output = nullptr;
 };
 
 // Sum of split-K partials: value = bf16((sum_s partial[s]) * input_scale * weight_scale).

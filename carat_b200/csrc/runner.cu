@@ -11,6 +11,7 @@
 #include "attention_tc.cuh"
 #include "context.cuh"
 #include "fp8_linear.cuh"
+#include "int4_linear.cuh"
 #include "qkv_post.cuh"
 #include "row_ops.cuh"
 
@@ -117,6 +118,7 @@ struct RopeTable {
 
 struct LayerPlans {
   LinearPlan qkv, o, gate_up, down;
+  Int4LinearPlan gate_up_int4, down_int4;   // used instead when the INT4 MLP variant is on
 };
 
 struct StepPlans {
@@ -186,6 +188,12 @@ struct carat_b200_runner {
   int score_stride_global{0};
   int *device_error{nullptr};
   std::map<int, StepPlans> verify_plans;
+  // ---- INT4 weight-only MLP variant (off unless carat_b200_runner_use_int4_mlp was called)
+  std::vector<carat_b200_int4_mlp_layer> int4_layers;
+  int int4_group{0};
+  DeviceBuffer pre_mlp;      // bf16 [rows, hidden]: input of the INT4 gate_up linear
+  DeviceBuffer activated;    // bf16 [rows, intermediate]: input of the INT4 down linear
+  DeviceBuffer unit_scale;   // one fp32 1.0: INT4 partial sums carry no tensor scales
   std::map<std::pair<int, int>, AttentionMaps> verify_maps;  // (layer, depth)
   std::map<int, AttentionMaps> draft_maps;                   // assistant layer
   // ---- workspaces (assistant)
@@ -441,6 +449,22 @@ StepPlans &verify_plans_for(Runner &runner, int rows) {
       if (linear_partial_bytes(*plan) > runner.split_partials.bytes())
         throw Failure{"split-K workspace is too small for this model shape"};
     }
+    if (!runner.int4_layers.empty()) {
+      const auto &int4 = runner.int4_layers[plans.layers.size()];
+      const char *message = "invalid BF16 INT4 linear weight shape";
+      if (make_int4_linear_plan(&entry.gate_up_int4, runner.pre_mlp.get(), int4.gate_up_codes,
+                                int4.gate_up_scales, rows, hidden, 2 * intermediate,
+                                runner.int4_group, 0, &message) != 0 ||
+          make_int4_linear_plan(&entry.down_int4, runner.activated.get(), int4.down_codes,
+                                int4.down_scales, rows, intermediate, hidden, runner.int4_group, 0,
+                                &message) != 0) {
+        throw Failure{message};
+      }
+      if (int4_linear_partial_bytes(entry.gate_up_int4) > runner.split_partials.bytes() ||
+          int4_linear_partial_bytes(entry.down_int4) > runner.split_partials.bytes()) {
+        throw Failure{"split-K workspace is too small for this model shape"};
+      }
+    }
     plans.layers.push_back(entry);
   }
   plans.head = plan_linear(runner.quantized.get(), runner.weights.token_embedding_fp8, rows, hidden,
@@ -581,6 +605,8 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
       slots == nullptr || accepted_out == nullptr || next_out == nullptr) {
     throw Failure{"invalid greedy verification batch"};
   }
+  if (!runner.int4_layers.empty() && requests * depth > 128)
+    throw Failure{"invalid BF16 INT4 linear activation shape"};
   std::vector<bool> seen(static_cast<size_t>(runner.batch), false);
   const int rows = requests * depth;
   const StepLayout host = layout_inputs(runner.host_inputs.get<int>(), maximum_rows, runner.batch);
@@ -624,6 +650,9 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
   const auto target = [&](int word) {
     return QuantTarget{runner.quantized.get(), scales + word, amax + word,
                        runner.two_launch_rows.get()};
+  };
+  const auto bf16_target = [](void *rows_out) {
+    return QuantTarget{nullptr, nullptr, nullptr, nullptr, rows_out};
   };
   // More rows than the device holds row-kernel CTAs: the row kernels run in their two-launch
   // form, whose first kernel does not clear the scratch words itself.
@@ -741,12 +770,68 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
 
     const PartialSource o_source = run_linear(runner, plan.o, scales + word + 1, w.o_scale,
                                               runner.projected.get(), true);
+    const bool int4_mlp = !runner.int4_layers.empty();
     require_launch(launch_post_attention_norms_quant(
                        runner.projected.get(), o_source, w.post_attention_norm, current,
-                       w.pre_mlp_norm, runner.residual.get(), target(word + 2), rows, hidden,
-                       epsilon, stream),
+                       w.pre_mlp_norm, runner.residual.get(),
+                       int4_mlp ? bf16_target(runner.pre_mlp.get()) : target(word + 2), rows,
+                       hidden, epsilon, stream),
                    "post-attention norms");
     runner.launches += 1;
+
+    if (int4_mlp) {
+      // Weight-only INT4 gate_up and down: bf16 activations in, no e4m3 quantisation between.
+      const float *unit = runner.unit_scale.get<float>();
+      auto *partials = runner.split_partials.get<float>();
+      const LinearPlan &up = plan.gate_up_int4.schedule;
+      TailSource tail{};
+      if (up.splits == 1 && up.tail_tiles > 0 && up.tail_tiles * 128 <= config.intermediate_size) {
+        require_launch(launch_int4_linear_bf16_tail(plan.gate_up_int4, runner.gate_up.get(),
+                                                    partials, runner.device_error, stream),
+                       "INT4 linear");
+        runner.launches += 1;
+        tail = TailSource{partials, up.tail_splits,
+                          2 * config.intermediate_size - up.tail_tiles * 128, up.tail_tiles * 128,
+                          unit, unit};
+      } else {
+        require_launch(launch_int4_linear_bf16(plan.gate_up_int4, runner.gate_up.get(), partials,
+                                               runner.device_error, stream),
+                       "INT4 linear");
+        runner.launches += (up.splits > 1 || up.tail_tiles > 0) ? 2 : 1;
+      }
+      require_launch(launch_geglu_quant(runner.gate_up.get(), tail,
+                                        bf16_target(runner.activated.get()), rows,
+                                        config.intermediate_size, stream),
+                     "GeGLU");
+      runner.launches += 1;
+      const LinearPlan &down = plan.down_int4.schedule;
+      PartialSource down_source{nullptr, 0, nullptr, nullptr};
+      if (down.splits > 1) {
+        require_launch(launch_int4_linear_partial(plan.down_int4, partials, runner.device_error,
+                                                  stream),
+                       "INT4 linear");
+        runner.launches += 1;
+        down_source = PartialSource{partials, down.splits, unit, unit};
+      } else {
+        require_launch(launch_int4_linear_bf16(plan.down_int4, runner.projected.get(), partials,
+                                               runner.device_error, stream),
+                       "INT4 linear");
+        runner.launches += down.tail_tiles > 0 ? 2 : 1;
+      }
+      const bool last = index + 1 == config.layer_count;
+      const void *next_norm =
+          last ? runner.weights.final_norm
+               : runner.layers[static_cast<size_t>(index) + 1].weights.input_norm;
+      require_launch(launch_layer_output_norm_quant(
+                         runner.projected.get(), down_source, w.post_mlp_norm,
+                         runner.residual.get(), w.scalar, other, next_norm,
+                         last ? runner.final_hidden.get() : nullptr, target(word + 4), rows, hidden,
+                         epsilon, stream),
+                     "layer output");
+      runner.launches += 1;
+      std::swap(current, other);
+      continue;
+    }
 
     // 336 feature tiles on 148 SMs leave a short last round; its tiles are cut along K and the
     // GeGLU kernel, which reads the up half anyway, sums the pieces.
@@ -1147,6 +1232,44 @@ extern "C" int carat_b200_runner_prefill_slot_fp8(carat_b200_runner *runner, int
                   CARAT_B200_VERIFY_ASSUME_MATCH, true, &accepted, &next);
       *next_token = next;
     }
+  });
+}
+
+extern "C" int carat_b200_runner_use_int4_mlp(carat_b200_runner *runner,
+                                              const carat_b200_int4_mlp_layer *layers,
+                                              int layer_count, int group_width) {
+  return guarded([&] {
+    if (runner == nullptr)
+      throw Failure{"invalid BF16 INT4 linear weight shape"};
+    runner->verify_plans.clear();
+    if (layers == nullptr) {
+      runner->int4_layers.clear();
+      return;
+    }
+    const int hidden = runner->config.hidden_size;
+    const int intermediate = runner->config.intermediate_size;
+    if (layer_count != runner->config.layer_count || (group_width != 128 && group_width != 256) ||
+        hidden % group_width != 0 || intermediate % group_width != 0) {
+      throw Failure{"invalid BF16 INT4 linear weight shape"};
+    }
+    for (int index = 0; index < layer_count; ++index) {
+      const carat_b200_int4_mlp_layer &layer = layers[index];
+      if (layer.gate_up_codes == nullptr || layer.gate_up_scales == nullptr ||
+          layer.down_codes == nullptr || layer.down_scales == nullptr) {
+        throw Failure{"invalid BF16 INT4 linear weight shape"};
+      }
+    }
+    if (runner->pre_mlp.get() == nullptr) {
+      runner->pre_mlp.allocate(static_cast<size_t>(128) * hidden * 2);
+      runner->activated.allocate(static_cast<size_t>(128) * intermediate * 2);
+      runner->unit_scale.allocate(sizeof(float));
+      const float one = 1.0F;
+      require_cuda(cudaMemcpy(runner->unit_scale.get(), &one, sizeof(float),
+                              cudaMemcpyHostToDevice),
+                   "store unit scale");
+    }
+    runner->int4_layers.assign(layers, layers + layer_count);
+    runner->int4_group = group_width;
   });
 }
 

@@ -414,6 +414,33 @@ class Gemma4BatchModelRunner:
                                                    holder.data_ptr(), elements * 2))
         return holder.reshape(shape)
 
+    def use_int4_mlp(self, weights: Optional[DeviceWeightArena], group_width: int = 128) -> None:
+        """Switches the target's gate_up and down projections to weight-only INT4 linears built
+        from the bf16 segments of `weights` (None switches back to the e4m3 linears). A step then
+        takes at most 128 rows."""
+        if weights is None:
+            check(self._library.carat_b200_runner_use_int4_mlp(self._handle, None, 0, 0))
+            self._int4 = None
+            return
+        hidden = self.config.hidden_size
+        intermediate = self.config.intermediate_size
+        layers = (capi.Int4MlpLayer * len(self.config.layers))()
+        linears = []
+        for index in range(len(self.config.layers)):
+            gate_up = Int4Bf16Linear(weights.at(f"layer.{index}.gate_up"), hidden,
+                                     2 * intermediate, group_width)
+            down = Int4Bf16Linear(weights.at(f"layer.{index}.down"), intermediate, hidden,
+                                  group_width)
+            linears += [gate_up, down]
+            layers[index].gate_up_codes = gate_up.reordered.data_ptr()
+            layers[index].gate_up_scales = gate_up.scales.data_ptr()
+            layers[index].down_codes = down.reordered.data_ptr()
+            layers[index].down_scales = down.scales.data_ptr()
+        torch.cuda.synchronize()
+        check(self._library.carat_b200_runner_use_int4_mlp(self._handle, layers, len(layers),
+                                                           group_width))
+        self._int4 = (layers, linears)
+
     def write_cache(self, which: int, layer: int, values: torch.Tensor) -> None:
         """Overwrites a whole key (which = 0) or value (1) cache of `layer`, or the hidden-by-slot
         table (2), with bf16 `values` laid out like the runner's buffer."""

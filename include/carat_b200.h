@@ -361,6 +361,23 @@ CARAT_B200_API int carat_b200_runner_create(const carat_b200_model_config *confi
                              carat_b200_runner **runner);
 CARAT_B200_API void carat_b200_runner_destroy(carat_b200_runner *runner);
 
+/* INT4 weight-only variant of the target's MLP linears (gate_up and down; group_width 128 or 256,
+ * bf16 activations, no e4m3 quantisation of their inputs). The codes are the reordered ones of
+ * carat_b200_int4_reorder_weight, the scales those of carat_b200_int4_quantize_weight; the caller
+ * keeps them alive. A step then takes at most 128 rows (carat::Int4Bf16Linear::supports_rows,
+ * cuda/int4_bf16_linear.cu:326-328). layers == NULL switches back to the e4m3 linears. The
+ * reference has this linear (include/carat/linear.h:70-90) but its runner never selects it for the
+ * MLP (include/carat/linear.h:47-51), so there is no reference method this replaces. */
+typedef struct carat_b200_int4_mlp_layer {
+  const void *gate_up_codes;   /* [2 * intermediate, hidden / 2] bytes, reordered */
+  const void *gate_up_scales;  /* bf16 [hidden / group_width, 2 * intermediate] */
+  const void *down_codes;      /* [hidden, intermediate / 2] bytes, reordered */
+  const void *down_scales;     /* bf16 [intermediate / group_width, hidden] */
+} carat_b200_int4_mlp_layer;
+CARAT_B200_API int carat_b200_runner_use_int4_mlp(carat_b200_runner *runner,
+                                                  const carat_b200_int4_mlp_layer *layers,
+                                                  int layer_count, int group_width);
+
 enum {
   /* Throughput runs only: every proposal counts as matching, so maximum_accepted alone sets the
    * accepted length (used to inject accept lengths with random-init weights). */

@@ -425,8 +425,22 @@ class OracleRunner:
         self.assistant_fp8_weights = (quantize_weights(assistant_weights)
                                       if assistant is not None and assistant_fp8 else None)
 
+    def use_int4_mlp(self, group_width: int = 128):
+        """The target's gate_up and down projections become weight-only INT4 linears over bf16
+        activations (quantiser rule of cuda/int4_bf16_linear.cu:95-136 at the given group width;
+        the reference itself has this linear but never selects it for the MLP, so this variant is
+        defined here: no e4m3 quantisation of pre_mlp / activated, everything else unchanged)."""
+        self.int4_group = group_width
+        self.int4_weights = {}
+        for index in range(len(self.config.layers)):
+            for name in (f"layer.{index}.gate_up", f"layer.{index}.down"):
+                self.int4_weights[name] = int4_quantize(self.weights[name], group_width)
+
     # ---- linears
     def _linear(self, x, name, weights=None, fp8_weights=None, use_fp8=None):
+        if (weights is None or weights is self.weights) and name in getattr(self, "int4_weights", {}):
+            codes, scales = self.int4_weights[name]
+            return int4_bf16_linear(x, codes, scales, self.int4_group)
         weights = self.weights if weights is None else weights
         fp8_weights = self.fp8_weights if fp8_weights is None else fp8_weights
         use_fp8 = self.fp8 if use_fp8 is None else use_fp8

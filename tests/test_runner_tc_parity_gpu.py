@@ -191,3 +191,31 @@ def test_rejected_rows_leave_the_sliding_ring_untouched(pair):
                            before[slot][:, untouched, :].view(torch.int16))
 
 
+
+
+@pytest.mark.parametrize("layer", [SLIDING, GLOBAL], ids=["sliding", "global"])
+def test_int4_mlp_variant_is_tight_over_one_layer(cuda_device, layer):
+    """The INT4 weight-only MLP variant (gate_up and down as W4A16 linears over bf16 activations,
+    groups of 128): device and oracle quantise the same bf16 weights with the same rule, so one
+    layer from identical state must agree as tightly as the e4m3 variant does."""
+    config = small_real_config([layer])
+    oracle, device = build_seeded_pair(config)
+    oracle.use_int4_mlp(128)
+    arena = carat_b200.DeviceWeightArena.from_host(cs.golden_tiny_weights(config))
+    device.use_int4_mlp(arena, 128)
+    generator = torch.Generator().manual_seed(9)
+    depth = 5
+    proposals = torch.randint(3, config.vocab, (3, depth), generator=generator).tolist()
+    firsts = [row[0] for row in proposals]
+    caps = [depth, depth - 2, 1]
+    _, _, trace = oracle.verify_greedy_proposals(proposals, firsts, [0, 1, 2], caps,
+                                                 assume_match=True, trace=True)
+    result = device.verify_greedy_proposals(proposals, firsts, [0, 1, 2], caps,
+                                            carat_b200.VERIFY_ASSUME_MATCH)
+    assert result.accepted_tokens == caps
+    assert rms_relative_error(device.last_final_hidden(3 * depth), trace.final_hidden) < 0.02
+    # Back to the e4m3 linears: the next step must differ from an INT4 step and still run.
+    device.use_int4_mlp(None)
+    again = device.verify_greedy_proposals(proposals, firsts, [0, 1, 2], caps,
+                                           carat_b200.VERIFY_ASSUME_MATCH)
+    assert again.accepted_tokens == caps
