@@ -35,7 +35,7 @@ constexpr int first_convert_warp = 7;    // 7-14 convert
 constexpr int convert_warps = 8;
 constexpr int code_tile_bytes = tile_features * 64;          // 128 features x 128 codes
 constexpr int scale_tile_bytes = tile_features * 2;
-constexpr int weight_buffers = 2;
+constexpr int weight_buffers = 4;
 constexpr int weight_columns = tile_k_elements / 2;          // TMEM columns of one converted K block
 
 template <int padded_rows> struct Layout {
@@ -136,14 +136,14 @@ int4_linear_kernel(const __grid_constant__ CUtensorMap code_map,
     abort_word = 0;
     for (int stage = 0; stage < L::code_stages; ++stage) {
       ptx::mbarrier_init(code_full + 8U * stage, 1);
-      ptx::mbarrier_init(code_empty + 8U * stage, convert_warps);
+      ptx::mbarrier_init(code_empty + 8U * stage, convert_warps / 2);
     }
     for (int stage = 0; stage < L::input_stages; ++stage) {
       ptx::mbarrier_init(input_full + 8U * stage, 1);
       ptx::mbarrier_init(input_empty + 8U * stage, 1);
     }
     for (int buffer = 0; buffer < weight_buffers; ++buffer) {
-      ptx::mbarrier_init(weight_full + 8U * buffer, convert_warps);
+      ptx::mbarrier_init(weight_full + 8U * buffer, convert_warps / 2);
       ptx::mbarrier_init(weight_empty + 8U * buffer, 1);
     }
     for (int buffer = 0; buffer < 2; ++buffer) {
@@ -227,35 +227,41 @@ int4_linear_kernel(const __grid_constant__ CUtensorMap code_map,
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint64_t input_desc = ptx::umma_desc_k_major_sw128(input_tiles);
-      const uint32_t desc_high = static_cast<uint32_t>(input_desc >> 32);
-      const uint32_t input_low = static_cast<uint32_t>(input_desc);
-      const uint32_t weight_base = tmem_base + L::weight_column0;
-      Cursor<L::input_stages> input_cursor;
-      Cursor<weight_buffers> weight_cursor;
-      uint32_t buffer = 0;
-      uint32_t buffer_phase = 0;
-      bool healthy = true;
-      for (int index = first_item; index < items && healthy; index += item_stride) {
-        const WorkItem item = decode_item(args, index);
-        if (!wait_checked(acc_empty + 8U * buffer, buffer_phase ^ 1U, abort_flag,
-                          args.device_error, 62)) {
+    // The whole warp walks the loop in lockstep and one elected lane issues: the loop state stays
+    // warp-uniform, so descriptor and ring arithmetic can run on the uniform datapath instead of
+    // competing with the converting warps for the integer pipe (with a single-lane loop the
+    // issue cost per MMA was 70-90 cycles beside them).
+    const uint64_t input_desc = ptx::umma_desc_k_major_sw128(input_tiles);
+    const uint32_t desc_high = static_cast<uint32_t>(input_desc >> 32);
+    const uint32_t input_low = static_cast<uint32_t>(input_desc);
+    const uint32_t weight_base = tmem_base + L::weight_column0;
+    Cursor<L::input_stages> input_cursor;
+    Cursor<weight_buffers> weight_cursor;
+    uint32_t buffer = 0;
+    uint32_t buffer_phase = 0;
+    bool healthy = true;
+    for (int index = first_item; index < items && healthy; index += item_stride) {
+      const WorkItem item = decode_item(args, index);
+      const bool free_accumulator = wait_checked(acc_empty + 8U * buffer, buffer_phase ^ 1U,
+                                                 abort_flag, args.device_error, 62);
+      if (__all_sync(0xFFFFFFFFU, free_accumulator ? 1 : 0) == 0)
+        break;
+      ptx::tcgen05_fence_after_thread_sync();
+      const uint32_t accumulator = tmem_base + buffer * padded_rows;
+      for (int block = 0; block < item.k_count; ++block) {
+        const bool ready =
+            wait_checked(weight_full + 8U * weight_cursor.stage, weight_cursor.phase, abort_flag,
+                         args.device_error, 63) &&
+            wait_checked(input_full + 8U * input_cursor.stage, input_cursor.phase, abort_flag,
+                         args.device_error, 64);
+        if (__all_sync(0xFFFFFFFFU, ready ? 1 : 0) == 0) {
+          healthy = false;
           break;
         }
         ptx::tcgen05_fence_after_thread_sync();
-        const uint32_t accumulator = tmem_base + buffer * padded_rows;
-        for (int block = 0; block < item.k_count; ++block) {
-          if (!wait_checked(weight_full + 8U * weight_cursor.stage, weight_cursor.phase,
-                            abort_flag, args.device_error, 63) ||
-              !wait_checked(input_full + 8U * input_cursor.stage, input_cursor.phase, abort_flag,
-                            args.device_error, 64)) {
-            healthy = false;
-            break;
-          }
-          ptx::tcgen05_fence_after_thread_sync();
-          const uint32_t a_columns = weight_base + weight_cursor.stage * weight_columns;
-          const uint32_t b_low = input_low + input_cursor.stage * (L::input_stage_bytes >> 4);
+        const uint32_t a_columns = weight_base + weight_cursor.stage * weight_columns;
+        const uint32_t b_low = input_low + input_cursor.stage * (L::input_stage_bytes >> 4);
+        if (ptx::elect_one()) {
 #pragma unroll
           for (int box = 0; box < 2; ++box) {
 #pragma unroll
@@ -270,35 +276,42 @@ int4_linear_kernel(const __grid_constant__ CUtensorMap code_map,
           }
           ptx::tcgen05_commit(weight_empty + 8U * weight_cursor.stage);
           ptx::tcgen05_commit(input_empty + 8U * input_cursor.stage);
-          weight_cursor.advance();
-          input_cursor.advance();
         }
-        if (healthy)
-          ptx::tcgen05_commit(acc_full + 8U * buffer);
-        buffer ^= 1U;
-        if (buffer == 0)
-          buffer_phase ^= 1U;
+        __syncwarp();
+        weight_cursor.advance();
+        input_cursor.advance();
       }
+      if (healthy && ptx::elect_one())
+        ptx::tcgen05_commit(acc_full + 8U * buffer);
+      __syncwarp();
+      buffer ^= 1U;
+      if (buffer == 0)
+        buffer_phase ^= 1U;
     }
   } else if (warp >= first_convert_warp) {
-    // Thread -> (feature row, half of the K block): a warp may touch only its own quarter of the
-    // TMEM lanes (warp index mod 4), lane = feature row, so two warps share a quarter and take 64
-    // K values (32 bytes of codes in, 32 TMEM columns out) each. Code tiles arrive with the
-    // 64-byte swizzle (16-byte chunk index xor bits 1-2 of the row), so the reads of a quarter
-    // warp touch eight different bank groups.
+    // Thread -> feature row: a warp may touch only its own quarter of the TMEM lanes (warp index
+    // mod 4), lane = feature row. The eight warps form two groups of four that take alternate K
+    // blocks, so that on every scheduler one warp is converting while the other waits, loads or
+    // stores (in lockstep all eight hit the integer and bf16 pipes at the same moment and leave
+    // them idle the rest of the time). Code tiles arrive with the 64-byte swizzle (16-byte chunk
+    // index xor bits 1-2 of the row), so the reads of a quarter warp touch eight bank groups.
     const int row = (warp & 3) * 32 + lane;
-    const int half = (warp - first_convert_warp) >> 2;
+    const int group = (warp - first_convert_warp) >> 2;
     const uint32_t code_swizzle = static_cast<uint32_t>(row >> 1) & 3U;
     const unsigned char *code_row = tiles_pointer + (code_tiles - tiles_base) + row * 64;
     const unsigned char *scale_row = tiles_pointer + (scale_tiles - tiles_base) + row * 2;
-    const uint32_t weight_lane = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
-                                 L::weight_column0 + half * (weight_columns / 2);
+    const uint32_t weight_lane =
+        tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + L::weight_column0;
     int total_blocks = 0;
     for (int index = first_item; index < items; index += item_stride)
       total_blocks += decode_item(args, index).k_count;
     Cursor<L::code_stages> code_cursor;
     Cursor<weight_buffers> weight_cursor;
-    for (int block = 0; block < total_blocks; ++block) {
+    if (group == 1) {
+      code_cursor.advance();
+      weight_cursor.advance();
+    }
+    for (int block = group; block < total_blocks; block += 2) {
       const bool ready =
           wait_checked(code_full + 8U * code_cursor.stage, code_cursor.phase, abort_flag,
                        args.device_error, 65) &&
@@ -307,20 +320,28 @@ int4_linear_kernel(const __grid_constant__ CUtensorMap code_map,
       if (__all_sync(0xFFFFFFFFU, ready ? 1 : 0) == 0)
         break;
       const unsigned char *codes = code_row + code_cursor.stage * code_tile_bytes;
-      const uint4 low = *reinterpret_cast<const uint4 *>(
-          codes + ((static_cast<uint32_t>(2 * half) ^ code_swizzle) << 4));
-      const uint4 high = *reinterpret_cast<const uint4 *>(
-          codes + ((static_cast<uint32_t>(2 * half + 1) ^ code_swizzle) << 4));
+      uint4 raw[4];
+#pragma unroll
+      for (int chunk = 0; chunk < 4; ++chunk)
+        raw[chunk] = *reinterpret_cast<const uint4 *>(
+            codes + ((static_cast<uint32_t>(chunk) ^ code_swizzle) << 4));
       const __nv_bfloat16 scale = *reinterpret_cast<const __nv_bfloat16 *>(
           scale_row + code_cursor.stage * scale_tile_bytes);
       const __nv_bfloat162 scale_pair = __halves2bfloat162(scale, scale);
-      const uint32_t words[8] = {low.x, low.y, low.z, low.w, high.x, high.y, high.z, high.w};
-      uint32_t converted[32];
-#pragma unroll
-      for (int chunk = 0; chunk < 8; ++chunk)
-        convert_word(words[chunk], scale_pair, converted + 4 * chunk);
       ptx::tcgen05_fence_after_thread_sync();
-      ptx::tmem_store_32x32b_x32(weight_lane + weight_cursor.stage * weight_columns, converted);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const uint32_t words[8] = {raw[2 * half].x,     raw[2 * half].y,     raw[2 * half].z,
+                                   raw[2 * half].w,     raw[2 * half + 1].x, raw[2 * half + 1].y,
+                                   raw[2 * half + 1].z, raw[2 * half + 1].w};
+        uint32_t converted[32];
+#pragma unroll
+        for (int word = 0; word < 8; ++word)
+          convert_word(words[word], scale_pair, converted + 4 * word);
+        ptx::tmem_store_32x32b_x32(
+            weight_lane + weight_cursor.stage * weight_columns + half * (weight_columns / 2),
+            converted);
+      }
       ptx::tmem_store_wait();
       ptx::tcgen05_fence_before_thread_sync();
       __syncwarp();
@@ -329,6 +350,8 @@ int4_linear_kernel(const __grid_constant__ CUtensorMap code_map,
         ptx::mbarrier_arrive(code_empty + 8U * code_cursor.stage);
       }
       code_cursor.advance();
+      code_cursor.advance();
+      weight_cursor.advance();
       weight_cursor.advance();
     }
   } else {

@@ -79,6 +79,18 @@ __device__ __forceinline__ bool mbarrier_wait_fast(uint32_t bar, uint32_t parity
   return mbarrier_wait_bounded(bar, parity);
 }
 
+// One lane of a converged warp (the same one every time) gets true.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t elected;
+  asm volatile("{\n\t"
+               ".reg .pred p;\n\t"
+               "elect.sync _|p, 0xFFFFFFFF;\n\t"
+               "selp.b32 %0, 1, 0, p;\n\t"
+               "}"
+               : "=r"(elected));
+  return elected != 0;
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ uint64_t policy_evict_first() {
   uint64_t policy;
