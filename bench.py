@@ -42,7 +42,7 @@ MEAN_ACCEPT = 2.5
 def workload_config(args):
     return {
         "workload": "configs[3] on one replica: 24 slots x 8192-token context, FP8 31B-shaped "
-                    "target + 4-layer 1024-wide FP8 drafter, k=4 (5 verify rows per slot), "
+                    f"target + 4-layer 1024-wide FP8 drafter, k={DRAFTS} ({DEPTH} verify rows per slot), "
                     "context lengths uniform in [128, 6144] (seeded), zero-filled KV, accept "
                     "lengths injected from a seeded geometric distribution with mean 2.5",
         "slots": SLOTS, "drafts": DRAFTS, "verify_rows": SLOTS * DEPTH,
@@ -291,8 +291,8 @@ def run_ours(args, rank, world):
         "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate, bf16 activations)",
         "data": "synthetic", "config": workload_config(args), "clocks": clocks,
         "e2e": {"value": tokens_all / (wall_ms_max / 1e3), "unit": UNIT,
-                "h2d_bytes_per_step": 4 * (128 + 4 * SLOTS) + 4 * 4 * SLOTS,
-                "d2h_bytes_per_step": 4 * (2 * SLOTS + 128 + 1) + 4 * (DEPTH * SLOTS + 1)},
+                "h2d_bytes_per_step": 4 * (256 + 4 * SLOTS) + 4 * 4 * SLOTS,
+                "d2h_bytes_per_step": 4 * (2 * SLOTS + 256 + 1) + 4 * (DEPTH * SLOTS + 1)},
         "gpu_launches": launches,
         "verify_step": {
             "ms": verify_ms_step, "weight_bytes": weight_bytes, "kv_bytes": kv_bytes,
@@ -347,6 +347,7 @@ def int4_variant(config, runner, timed_run, args, fp8_weight_bytes):
                 "group_width": group,
                 "weight_bytes": fp8_weight_bytes - mlp_e4m3 + mlp_int4}
     except Exception as error:  # the e4m3 numbers of the line stand on their own
+        capi.library().carat_b200_runner_use_int4_mlp(runner._handle, None, 0, 0)
         return {"error": str(error)}
 
 
@@ -547,11 +548,16 @@ def main():
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--drafts", type=int, default=4, choices=[2, 4, 8],
+                        help="k, drafted tokens per slot and step (the headline metric is k = 4)")
     parser.add_argument("--int4-mlp", action="store_true",
                         help="also time the step with INT4 weight-only MLP linears (N = 1 only)")
     parser.add_argument("--skip-cpu", action="store_true",
                         help="leave the cpu_baseline object out (profiling runs)")
     args = parser.parse_args()
+    global DRAFTS, DEPTH
+    DRAFTS = args.drafts
+    DEPTH = DRAFTS + 1
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
