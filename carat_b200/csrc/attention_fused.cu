@@ -92,21 +92,6 @@ __device__ __forceinline__ FusedItem fused_item(const AttentionArguments &a, int
   return item;
 }
 
-// Bounded wait that gives up at once when another role of the CTA has already given up. The common
-// case (the phase has completed) costs a single try_wait.
-__device__ __forceinline__ bool wait_checked(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                             int *device_error, int code) {
-  if (ptx::mbarrier_try_wait(bar, parity))
-    return true;
-  if (*abort_flag != 0)
-    return false;
-  if (ptx::mbarrier_wait_bounded(bar, parity))
-    return true;
-  *abort_flag = 1;
-  atomicExch(device_error, code);
-  return false;
-}
-
 // Position in the TMA ring; advancing is two instructions instead of a division.
 struct RingCursor {
   uint32_t stage{0};
@@ -233,7 +218,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
         const int proposal_items = item.proposals > 0 ? 1 : 0;
         const int buffer = local & 1;
         const uint32_t use = static_cast<uint32_t>(local >> 1);
-        if (!wait_checked(query_free_bar + 8U * buffer, (use & 1U) ^ 1U, abort_flag,
+        if (!ptx::mbarrier_wait_checked(query_free_bar + 8U * buffer, (use & 1U) ^ 1U, abort_flag,
                           args.device_error, 30)) {
           healthy = false;
           break;
@@ -249,7 +234,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
         if (proposal_items != 0) {
 #pragma unroll
           for (int sub = 0; sub < 4; ++sub) {
-            if (!wait_checked(empty_bar + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
+            if (!ptx::mbarrier_wait_checked(empty_bar + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
                               args.device_error, 31)) {
               healthy = false;
               break;
@@ -264,7 +249,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
           const int row = cache_row0 + tile * fused_tile_keys;
 #pragma unroll
           for (int sub = 0; sub < 4; ++sub) {
-            if (!wait_checked(empty_bar + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
+            if (!ptx::mbarrier_wait_checked(empty_bar + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
                               args.device_error, 31)) {
               healthy = false;
               break;
@@ -277,7 +262,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
         }
         // V: one stage per 32 keys, four [32 keys x 64 components] boxes.
         if (proposal_items != 0 && healthy) {
-          if (!wait_checked(empty_bar + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
+          if (!ptx::mbarrier_wait_checked(empty_bar + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
                             args.device_error, 32)) {
             healthy = false;
             break;
@@ -293,7 +278,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
         }
         const int value_groups = item.value_items - proposal_items;
         for (int key_group = 0; key_group < value_groups && healthy; ++key_group) {
-          if (!wait_checked(empty_bar + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
+          if (!ptx::mbarrier_wait_checked(empty_bar + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
                             args.device_error, 32)) {
             healthy = false;
             break;
@@ -342,14 +327,14 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
         const int query_buffer = local & 1;
         const uint32_t item_parity = static_cast<uint32_t>(local) & 1U;
         const uint32_t item_query_low = query_low + query_buffer * (fused_query_bytes >> 4);
-        if (!wait_checked(query_full_bar + 8U * query_buffer,
+        if (!ptx::mbarrier_wait_checked(query_full_bar + 8U * query_buffer,
                           static_cast<uint32_t>(local >> 1) & 1U, abort_flag, args.device_error,
                           33)) {
           healthy = false;
           break;
         }
         for (int tile_item = 0; tile_item < item.score_items && healthy; ++tile_item) {
-          if (!wait_checked(acc_empty_bar + 8U * accumulator, accumulator_phase ^ 1U, abort_flag,
+          if (!ptx::mbarrier_wait_checked(acc_empty_bar + 8U * accumulator, accumulator_phase ^ 1U, abort_flag,
                             args.device_error, 34)) {
             healthy = false;
             break;
@@ -358,7 +343,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
           const uint32_t tmem_scores = tmem_base + accumulator * fused_rows;
 #pragma unroll
           for (int sub = 0; sub < 4; ++sub) {
-            if (!wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
+            if (!ptx::mbarrier_wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
                               args.device_error, 35)) {
               healthy = false;
               break;
@@ -384,14 +369,14 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
           break;
         // The query tiles may be overwritten once every score instruction has completed.
         ptx::tcgen05_commit(query_free_bar + 8U * query_buffer);
-        if (!wait_checked(probability_bar, item_parity, abort_flag, args.device_error, 36)) {
+        if (!ptx::mbarrier_wait_checked(probability_bar, item_parity, abort_flag, args.device_error, 36)) {
           healthy = false;
           break;
         }
         ptx::tcgen05_fence_after_thread_sync();
         uint32_t accumulate = 0;
         if (proposal_items != 0) {
-          if (!wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
+          if (!ptx::mbarrier_wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
                             args.device_error, 37)) {
             healthy = false;
             break;
@@ -409,7 +394,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
         }
         const int value_groups = item.value_items - proposal_items;
         for (int key_group = 0; key_group < value_groups; ++key_group) {
-          if (!wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
+          if (!ptx::mbarrier_wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
                             args.device_error, 37)) {
             healthy = false;
             break;
@@ -477,7 +462,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
         const int buffer = tiles_done & 1;
         const uint32_t use = static_cast<uint32_t>(tiles_done >> 1);
         const bool ready =
-            __all_sync(0xFFFFFFFFU, wait_checked(acc_full_bar + 8U * buffer, use & 1U, abort_flag,
+            __all_sync(0xFFFFFFFFU, ptx::mbarrier_wait_checked(acc_full_bar + 8U * buffer, use & 1U, abort_flag,
                                                  args.device_error, 38)
                                         ? 1
                                         : 0) != 0;
@@ -626,7 +611,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
 
       // ---- phase 3: O -> bf16 output
       const bool finished =
-          __all_sync(0xFFFFFFFFU, wait_checked(output_bar, item_parity, abort_flag,
+          __all_sync(0xFFFFFFFFU, ptx::mbarrier_wait_checked(output_bar, item_parity, abort_flag,
                                                args.device_error, 39)
                                       ? 1
                                       : 0) != 0;

@@ -98,21 +98,6 @@ __device__ __forceinline__ StreamItem cached_item(const AttentionArguments &a, i
   return ordinal < cached_items ? cache[ordinal] : stream_item(a, index);
 }
 
-// Bounded wait that gives up at once when another role of the CTA has already given up. The common
-// case (the phase has completed) costs a single try_wait.
-__device__ __forceinline__ bool wait_checked(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                             int *device_error, int code) {
-  if (ptx::mbarrier_try_wait(bar, parity))
-    return true;
-  if (*abort_flag != 0)
-    return false;
-  if (ptx::mbarrier_wait_bounded(bar, parity))
-    return true;
-  *abort_flag = 1;
-  atomicExch(device_error, code);
-  return false;
-}
-
 template <int stages> struct Cursor {
   uint32_t stage{0};
   uint32_t phase{0};
@@ -351,7 +336,7 @@ scores_stream_kernel(const __grid_constant__ CUtensorMap key_map,
           }
         }
         if (healthy && query_pending) {
-          if (!wait_checked(query_free_bar, query_parity, abort_flag, args.device_error, 40)) {
+          if (!ptx::mbarrier_wait_checked(query_free_bar, query_parity, abort_flag, args.device_error, 40)) {
             healthy = false;
             break;
           }
@@ -381,7 +366,7 @@ scores_stream_kernel(const __grid_constant__ CUtensorMap key_map,
         const StreamItem item = cached_item(a, index, ordinal, item_cache);
         if (item.empty())
           continue;
-        if (!wait_checked(query_full_bar, local & 1U, abort_flag, args.device_error, 42)) {
+        if (!ptx::mbarrier_wait_checked(query_full_bar, local & 1U, abort_flag, args.device_error, 42)) {
           healthy = false;
           break;
         }
@@ -389,7 +374,7 @@ scores_stream_kernel(const __grid_constant__ CUtensorMap key_map,
         const int tiles = (item.proposals > 0 ? 1 : 0) +
                           (item.rows_here + stream_tile_keys - 1) / stream_tile_keys;
         for (int tile = 0; tile < tiles && healthy; ++tile) {
-          if (!wait_checked(acc_empty_bar + 8U * accumulator, accumulator_phase ^ 1U, abort_flag,
+          if (!ptx::mbarrier_wait_checked(acc_empty_bar + 8U * accumulator, accumulator_phase ^ 1U, abort_flag,
                             args.device_error, 43)) {
             healthy = false;
             break;
@@ -398,7 +383,7 @@ scores_stream_kernel(const __grid_constant__ CUtensorMap key_map,
           const uint32_t tmem_scores = tmem_base + accumulator * padded_rows;
 #pragma unroll
           for (int pair = 0; pair < subtiles / 2; ++pair) {
-            if (!wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
+            if (!ptx::mbarrier_wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
                               args.device_error, 44)) {
               healthy = false;
               break;
@@ -476,7 +461,7 @@ scores_stream_kernel(const __grid_constant__ CUtensorMap key_map,
       for (int tile = 0; tile < tiles; ++tile, ++tiles_done) {
         const uint32_t buffer = tiles_done & 1U;
         const bool ready =
-            __all_sync(0xFFFFFFFFU, wait_checked(acc_full_bar + 8U * buffer, (tiles_done >> 1) & 1U,
+            __all_sync(0xFFFFFFFFU, ptx::mbarrier_wait_checked(acc_full_bar + 8U * buffer, (tiles_done >> 1) & 1U,
                                                  abort_flag, args.device_error, 45)
                                         ? 1
                                         : 0) != 0;
@@ -694,7 +679,7 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
         if (item.empty())
           continue;
         if (item.proposals > 0) {
-          if (!wait_checked(empty_bar + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
+          if (!ptx::mbarrier_wait_checked(empty_bar + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
                             args.device_error, 50)) {
             healthy = false;
             break;
@@ -711,7 +696,7 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
         const int key_groups = (item.rows_here + stream_value_keys - 1) / stream_value_keys;
         int row = item.cache_row0 + item.first_row;
         for (int key_group = 0; key_group < key_groups; ++key_group, row += stream_value_keys) {
-          if (!wait_checked(empty_bar + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
+          if (!ptx::mbarrier_wait_checked(empty_bar + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
                             args.device_error, 50)) {
             healthy = false;
             break;
@@ -750,7 +735,7 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
         const uint32_t buffer = output_buffers == 2 ? (local & 1U) : 0U;
         const uint32_t use = output_buffers == 2 ? (local >> 1) : local;
         ++local;
-        if (!wait_checked(o_empty_bar + 8U * buffer, (use & 1U) ^ 1U, abort_flag,
+        if (!ptx::mbarrier_wait_checked(o_empty_bar + 8U * buffer, (use & 1U) ^ 1U, abort_flag,
                           args.device_error, 51)) {
           healthy = false;
           break;
@@ -759,9 +744,9 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
         const uint32_t tmem_output = tmem_base + buffer * Shape::output_columns;
         uint32_t accumulate = 0;
         if (item.proposals > 0) {
-          if (!wait_checked(p_full_bar + 8U * probability_cursor.stage, probability_cursor.phase,
+          if (!ptx::mbarrier_wait_checked(p_full_bar + 8U * probability_cursor.stage, probability_cursor.phase,
                             abort_flag, args.device_error, 52) ||
-              !wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
+              !ptx::mbarrier_wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
                             args.device_error, 53)) {
             healthy = false;
             break;
@@ -785,12 +770,12 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
         for (int key_group = 0; key_group < key_groups; ++key_group) {
           const int half = key_group & 1;
           if (half == 0 &&
-              !wait_checked(p_full_bar + 8U * probability_cursor.stage, probability_cursor.phase,
+              !ptx::mbarrier_wait_checked(p_full_bar + 8U * probability_cursor.stage, probability_cursor.phase,
                             abort_flag, args.device_error, 52)) {
             healthy = false;
             break;
           }
-          if (!wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
+          if (!ptx::mbarrier_wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
                             args.device_error, 53)) {
             healthy = false;
             break;
@@ -846,7 +831,7 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
       const uint32_t use = output_buffers == 2 ? (local >> 1) : local;
       ++local;
       const bool ready =
-          __all_sync(0xFFFFFFFFU, wait_checked(o_full_bar + 8U * buffer, use & 1U, abort_flag,
+          __all_sync(0xFFFFFFFFU, ptx::mbarrier_wait_checked(o_full_bar + 8U * buffer, use & 1U, abort_flag,
                                                args.device_error, 54)
                                       ? 1
                                       : 0) != 0;
@@ -958,7 +943,7 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
         if (box + 1 < boxes)
           load_box(box + 1, ahead);
         const bool free_slot =
-            __all_sync(0xFFFFFFFFU, wait_checked(p_empty_bar + 8U * cursor.stage,
+            __all_sync(0xFFFFFFFFU, ptx::mbarrier_wait_checked(p_empty_bar + 8U * cursor.stage,
                                                  cursor.phase ^ 1U, abort_flag, args.device_error,
                                                  55)
                                         ? 1

@@ -51,20 +51,6 @@ template <int padded_rows> struct Layout {
                                        code_stages * (code_tile_bytes + scale_tile_bytes) + 1024;
 };
 
-// Bounded wait that gives up at once when another role of the CTA already has.
-__device__ __forceinline__ bool wait_checked(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                             int *device_error, int code) {
-  if (ptx::mbarrier_try_wait(bar, parity))
-    return true;
-  if (*abort_flag != 0)
-    return false;
-  if (ptx::mbarrier_wait_bounded(bar, parity))
-    return true;
-  *abort_flag = 1;
-  atomicExch(device_error, code);
-  return false;
-}
-
 template <int stages> struct Cursor {
   uint32_t stage{0};
   uint32_t phase{0};
@@ -175,7 +161,7 @@ int4_linear_kernel(const __grid_constant__ CUtensorMap code_map,
         const WorkItem item = decode_item(args, index);
         const int feature0 = item.tile * tile_features;
         for (int block = item.k_begin; block < item.k_begin + item.k_count; ++block) {
-          if (!wait_checked(code_empty + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
+          if (!ptx::mbarrier_wait_checked(code_empty + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
                             args.device_error, 60)) {
             healthy = false;
             break;
@@ -205,7 +191,7 @@ int4_linear_kernel(const __grid_constant__ CUtensorMap code_map,
       for (int index = first_item; index < items && healthy; index += item_stride) {
         const WorkItem item = decode_item(args, index);
         for (int block = item.k_begin; block < item.k_begin + item.k_count; ++block) {
-          if (!wait_checked(input_empty + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
+          if (!ptx::mbarrier_wait_checked(input_empty + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
                             args.device_error, 61)) {
             healthy = false;
             break;
@@ -242,7 +228,7 @@ int4_linear_kernel(const __grid_constant__ CUtensorMap code_map,
     bool healthy = true;
     for (int index = first_item; index < items && healthy; index += item_stride) {
       const WorkItem item = decode_item(args, index);
-      const bool free_accumulator = wait_checked(acc_empty + 8U * buffer, buffer_phase ^ 1U,
+      const bool free_accumulator = ptx::mbarrier_wait_checked(acc_empty + 8U * buffer, buffer_phase ^ 1U,
                                                  abort_flag, args.device_error, 62);
       if (__all_sync(0xFFFFFFFFU, free_accumulator ? 1 : 0) == 0)
         break;
@@ -250,9 +236,9 @@ int4_linear_kernel(const __grid_constant__ CUtensorMap code_map,
       const uint32_t accumulator = tmem_base + buffer * padded_rows;
       for (int block = 0; block < item.k_count; ++block) {
         const bool ready =
-            wait_checked(weight_full + 8U * weight_cursor.stage, weight_cursor.phase, abort_flag,
+            ptx::mbarrier_wait_checked(weight_full + 8U * weight_cursor.stage, weight_cursor.phase, abort_flag,
                          args.device_error, 63) &&
-            wait_checked(input_full + 8U * input_cursor.stage, input_cursor.phase, abort_flag,
+            ptx::mbarrier_wait_checked(input_full + 8U * input_cursor.stage, input_cursor.phase, abort_flag,
                          args.device_error, 64);
         if (__all_sync(0xFFFFFFFFU, ready ? 1 : 0) == 0) {
           healthy = false;
@@ -313,9 +299,9 @@ int4_linear_kernel(const __grid_constant__ CUtensorMap code_map,
     }
     for (int block = group; block < total_blocks; block += 2) {
       const bool ready =
-          wait_checked(code_full + 8U * code_cursor.stage, code_cursor.phase, abort_flag,
+          ptx::mbarrier_wait_checked(code_full + 8U * code_cursor.stage, code_cursor.phase, abort_flag,
                        args.device_error, 65) &&
-          wait_checked(weight_empty + 8U * weight_cursor.stage, weight_cursor.phase ^ 1U,
+          ptx::mbarrier_wait_checked(weight_empty + 8U * weight_cursor.stage, weight_cursor.phase ^ 1U,
                        abort_flag, args.device_error, 66);
       if (__all_sync(0xFFFFFFFFU, ready ? 1 : 0) == 0)
         break;
@@ -362,7 +348,7 @@ int4_linear_kernel(const __grid_constant__ CUtensorMap code_map,
       const WorkItem item = decode_item(args, index);
       const int buffer = local & 1;
       const uint32_t use = static_cast<uint32_t>(local >> 1);
-      const bool ready = wait_checked(acc_full + 8U * buffer, use & 1U, abort_flag,
+      const bool ready = ptx::mbarrier_wait_checked(acc_full + 8U * buffer, use & 1U, abort_flag,
                                       args.device_error, 67);
       if (__all_sync(0xFFFFFFFFU, ready ? 1 : 0) == 0)
         break;

@@ -79,6 +79,24 @@ __device__ __forceinline__ bool mbarrier_wait_fast(uint32_t bar, uint32_t parity
   return mbarrier_wait_bounded(bar, parity);
 }
 
+// Bounded wait for kernels with several roles: gives up at once when another role of the CTA has
+// already given up (`abort_flag`, in shared memory), otherwise waits, and on running out records
+// `code` in the per-device error word and raises the flag. The common case (the phase has
+// completed) costs a single try_wait.
+__device__ __forceinline__ bool mbarrier_wait_checked(uint32_t bar, uint32_t parity,
+                                                      volatile int *abort_flag, int *device_error,
+                                                      int code) {
+  if (mbarrier_try_wait(bar, parity))
+    return true;
+  if (*abort_flag != 0)
+    return false;
+  if (mbarrier_wait_bounded(bar, parity))
+    return true;
+  *abort_flag = 1;
+  atomicExch(device_error, code);
+  return false;
+}
+
 // One lane of a converged warp (the same one every time) gets true.
 __device__ __forceinline__ bool elect_one() {
   uint32_t elected;
