@@ -8,16 +8,18 @@
 // activation rows = UMMA N, persistent CTAs walking tile x K-piece items), with one more stage
 // between TMA and the tensor core: the 4-bit codes cannot feed tcgen05.mma together with bf16
 // activations, so eight warps turn every [128 features x 128 K] tile of codes (8 KB, plus its 128
-// group scales) into bf16 and store it into tensor memory (tcgen05.st), where the MMA thread takes
+// group scales) into bf16 and store it into tensor memory (tcgen05.st), where the MMA warp takes
 // it as the A operand (kind::f16, A in TMEM) against the bf16 activation boxes in shared memory.
 // Keeping the converted weights out of shared memory matters: written there and read back by the
 // tensor core they cost 64 KB of shared-memory traffic per K block on top of the 72 KB of TMA
 // writes and B-operand reads, and the kernel was bound by shared-memory bandwidth (measured: no
 // change when either TMA stream was switched off). Rings: codes + scales (TMA, deep, small),
-// activations (TMA from L2), converted weights (two TMEM buffers of 64 columns). The codes are
-// read from HBM exactly once; that is half the bytes of the e4m3 weights, but the bf16 MMA needs
-// twice the tensor-core time per weight (about 65 cycles per 128 x 128 x 16 MMA, eight per K
-// block) and the activation boxes are twice as large.
+// activations (TMA from L2), converted weights (four TMEM buffers of 64 columns, filled by two
+// groups of four warps on alternate K blocks). The codes are read from HBM exactly once; that is
+// half the bytes of the e4m3 weights, but the kernel is bound on the SM: at 128 padded rows the
+// eight bf16 MMAs of a K block keep the tensor pipe busy about 700 cycles (an e4m3 MMA consumes 32
+// bytes of a weight row, a bf16 MMA over 4-bit codes 8), and below 64 rows the conversion (shift,
+// mask-or, bf16 subtract, bf16 multiply per pair of codes) is the limit.
 #include "int4_linear.cuh"
 #include "launch.cuh"
 #include "linear_items.cuh"
