@@ -219,3 +219,40 @@ def test_int4_mlp_variant_is_tight_over_one_layer(cuda_device, layer):
     again = device.verify_greedy_proposals(proposals, firsts, [0, 1, 2], caps,
                                            carat_b200.VERIFY_ASSUME_MATCH)
     assert again.accepted_tokens == caps
+
+
+def test_int4_mlp_variant_over_two_layers_teacher_forced(cuda_device):
+    """The same teacher-forced comparison as the e4m3 runner, with both sides in the INT4 MLP
+    variant: bookkeeping bit-exact given the device's predictions, hidden states within the noise
+    floor of the remaining e4m3 chain (attention projections), differing predictions near-ties."""
+    config = small_real_config()
+    oracle, device = build_seeded_pair(config)
+    oracle.use_int4_mlp(128)
+    arena = carat_b200.DeviceWeightArena.from_host(cs.golden_tiny_weights(config))
+    device.use_int4_mlp(arena, 128)
+    generator = torch.Generator().manual_seed(21)
+    slots = [0, 1, 2]
+    for step, depth in enumerate([5, 3]):
+        proposals = torch.randint(3, config.vocab, (3, depth), generator=generator).tolist()
+        firsts = [row[0] for row in proposals]
+        caps = [[4, 1, 5], [3, 2, 1]][step]
+        scout = copy.deepcopy(oracle)
+        _, _, trace = scout.verify_greedy_proposals(proposals, firsts, slots, caps,
+                                                    assume_match=True, trace=True)
+        starts = [device.slot_position(slot) for slot in slots]
+        result = device.verify_greedy_proposals(proposals, firsts, slots, caps,
+                                                carat_b200.VERIFY_ASSUME_MATCH)
+        predictions = device.last_predictions(3 * depth)
+        want = cs.greedy_prefix_accept([list(p) for p in proposals], firsts, predictions, caps,
+                                       depth, True)
+        assert (result.accepted_tokens, result.next_tokens) == want
+        assert rms_relative_error(device.last_final_hidden(3 * depth),
+                                  trace.final_hidden) < TOLERANCE, step
+        for row, (got, expected) in enumerate(zip(predictions, trace.predictions.tolist())):
+            if got != expected:
+                assert near_tie(trace, row, got), (step, row, got, expected)
+        oracle.verify_greedy_proposals(proposals, firsts, slots, result.accepted_tokens,
+                                       assume_match=True)
+        for request, slot in enumerate(slots):
+            assert device.slot_position(slot) == starts[request] + result.accepted_tokens[request]
+            assert device.slot_position(slot) == oracle.positions[slot]
