@@ -199,34 +199,41 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint64_t weight_desc = ptx::umma_desc_k_major_sw128(weight_tiles);
-      const uint64_t input_desc = ptx::umma_desc_k_major_sw128(input_tiles);
-      const uint32_t desc_high = static_cast<uint32_t>(weight_desc >> 32);
-      const uint32_t weight_low = static_cast<uint32_t>(weight_desc);
-      const uint32_t input_low = static_cast<uint32_t>(input_desc);
-      uint32_t stage = 0;
-      uint32_t phase = 0;
-      uint32_t buffer = 0;
-      uint32_t buffer_phase = 0;
-      bool healthy = true;
-      for (int index = first_item; index < items && healthy; index += item_stride) {
-        const WorkItem item = decode_item(args, index);
-        if (!ptx::mbarrier_wait_fast(acc_empty_bar + 8U * buffer, buffer_phase ^ 1U)) {
+    // The whole warp walks the loop in lockstep and one elected lane issues, so the loop state
+    // stays warp-uniform (descriptor and ring arithmetic on the uniform datapath).
+    const uint64_t weight_desc = ptx::umma_desc_k_major_sw128(weight_tiles);
+    const uint64_t input_desc = ptx::umma_desc_k_major_sw128(input_tiles);
+    const uint32_t desc_high = static_cast<uint32_t>(weight_desc >> 32);
+    const uint32_t weight_low = static_cast<uint32_t>(weight_desc);
+    const uint32_t input_low = static_cast<uint32_t>(input_desc);
+    uint32_t stage = 0;
+    uint32_t phase = 0;
+    uint32_t buffer = 0;
+    uint32_t buffer_phase = 0;
+    bool healthy = true;
+    for (int index = first_item; index < items && healthy; index += item_stride) {
+      const WorkItem item = decode_item(args, index);
+      const bool free_accumulator =
+          ptx::mbarrier_wait_fast(acc_empty_bar + 8U * buffer, buffer_phase ^ 1U);
+      if (__all_sync(0xFFFFFFFFU, free_accumulator ? 1 : 0) == 0) {
+        if (lane == 0)
           atomicExch(args.device_error, 4);
+        break;
+      }
+      ptx::tcgen05_fence_after_thread_sync();
+      const uint32_t accumulator = tmem_base + buffer * padded_rows;
+      for (int block = 0; block < item.k_count; ++block) {
+        const bool ready = ptx::mbarrier_wait_fast(full_bar + 8U * stage, phase);
+        if (__all_sync(0xFFFFFFFFU, ready ? 1 : 0) == 0) {
+          healthy = false;
+          if (lane == 0)
+            atomicExch(args.device_error, 2);
           break;
         }
         ptx::tcgen05_fence_after_thread_sync();
-        const uint32_t accumulator = tmem_base + buffer * padded_rows;
-        for (int block = 0; block < item.k_count; ++block) {
-          if (!ptx::mbarrier_wait_fast(full_bar + 8U * stage, phase)) {
-            healthy = false;
-            atomicExch(args.device_error, 2);
-            break;
-          }
-          ptx::tcgen05_fence_after_thread_sync();
-          const uint32_t a_low = weight_low + stage * (weight_tile_bytes >> 4);
-          const uint32_t b_low = input_low + stage * (input_tile_bytes >> 4);
+        const uint32_t a_low = weight_low + stage * (weight_tile_bytes >> 4);
+        const uint32_t b_low = input_low + stage * (input_tile_bytes >> 4);
+        if (ptx::elect_one()) {
           // +32 bytes along K inside the swizzle atom = +2 in the 16-byte address field.
           ptx::tcgen05_mma_f8f6f4_split(accumulator, a_low, desc_high, b_low, desc_high, idesc,
                                         block > 0 ? 1U : 0U);
@@ -235,17 +242,19 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
             ptx::tcgen05_mma_f8f6f4_split(accumulator, a_low + 2 * step, desc_high,
                                           b_low + 2 * step, desc_high, idesc, 1U);
           ptx::tcgen05_commit(empty_bar + 8U * stage);
-          if (++stage == stages) {
-            stage = 0;
-            phase ^= 1U;
-          }
         }
-        if (healthy)
-          ptx::tcgen05_commit(acc_full_bar + 8U * buffer);
-        buffer ^= 1U;
-        if (buffer == 0)
-          buffer_phase ^= 1U;
+        __syncwarp();
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1U;
+        }
       }
+      if (healthy && ptx::elect_one())
+        ptx::tcgen05_commit(acc_full_bar + 8U * buffer);
+      __syncwarp();
+      buffer ^= 1U;
+      if (buffer == 0)
+        buffer_phase ^= 1U;
     }
   } else {
     const int quarter = warp & 3;  // TMEM lane group this warp may read
