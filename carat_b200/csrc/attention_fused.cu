@@ -303,7 +303,9 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
+      // The whole warp walks this role in lockstep and one elected lane issues, so the loop state
+      // stays warp-uniform.
       // Descriptor words. High words carry SBO (1024 bytes), version and swizzle mode and are the
       // same for both layouts; the low words hold the start address (16-byte units) and, for the
       // MN-major V tiles, the byte distance between 64-component boxes.
@@ -327,15 +329,15 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
         const int query_buffer = local & 1;
         const uint32_t item_parity = static_cast<uint32_t>(local) & 1U;
         const uint32_t item_query_low = query_low + query_buffer * (fused_query_bytes >> 4);
-        if (!ptx::mbarrier_wait_checked(query_full_bar + 8U * query_buffer,
+        if (__all_sync(0xFFFFFFFFU, ptx::mbarrier_wait_checked(query_full_bar + 8U * query_buffer,
                           static_cast<uint32_t>(local >> 1) & 1U, abort_flag, args.device_error,
-                          33)) {
+                          33) ? 1 : 0) == 0) {
           healthy = false;
           break;
         }
         for (int tile_item = 0; tile_item < item.score_items && healthy; ++tile_item) {
-          if (!ptx::mbarrier_wait_checked(acc_empty_bar + 8U * accumulator, accumulator_phase ^ 1U, abort_flag,
-                            args.device_error, 34)) {
+          if (__all_sync(0xFFFFFFFFU, ptx::mbarrier_wait_checked(acc_empty_bar + 8U * accumulator, accumulator_phase ^ 1U, abort_flag,
+                            args.device_error, 34) ? 1 : 0) == 0) {
             healthy = false;
             break;
           }
@@ -343,24 +345,28 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
           const uint32_t tmem_scores = tmem_base + accumulator * fused_rows;
 #pragma unroll
           for (int sub = 0; sub < 4; ++sub) {
-            if (!ptx::mbarrier_wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
-                              args.device_error, 35)) {
+            if (__all_sync(0xFFFFFFFFU, ptx::mbarrier_wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
+                              args.device_error, 35) ? 1 : 0) == 0) {
               healthy = false;
               break;
             }
             ptx::tcgen05_fence_after_thread_sync();
             const uint32_t a_low = key_low + cursor.stage * stage_step;
             const uint32_t b_low = item_query_low + sub * ((fused_rows * 128) >> 4);
+            if (ptx::elect_one()) {
 #pragma unroll
-            for (int step = 0; step < 4; ++step)
-              ptx::tcgen05_mma_f16_split(tmem_scores, a_low + 2 * step, desc_high,
-                                         b_low + 2 * step, desc_high, score_idesc,
-                                         (sub > 0 || step > 0) ? 1U : 0U);
-            ptx::tcgen05_commit(empty_bar + 8U * cursor.stage);
+              for (int step = 0; step < 4; ++step)
+                ptx::tcgen05_mma_f16_split(tmem_scores, a_low + 2 * step, desc_high,
+                                           b_low + 2 * step, desc_high, score_idesc,
+                                           (sub > 0 || step > 0) ? 1U : 0U);
+              ptx::tcgen05_commit(empty_bar + 8U * cursor.stage);
+            }
+            __syncwarp();
             cursor.advance();
           }
-          if (healthy)
+          if (healthy && ptx::elect_one())
             ptx::tcgen05_commit(acc_full_bar + 8U * accumulator);
+          __syncwarp();
           accumulator ^= 1U;
           if (accumulator == 0)
             accumulator_phase ^= 1U;
@@ -368,34 +374,39 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
         if (!healthy)
           break;
         // The query tiles may be overwritten once every score instruction has completed.
-        ptx::tcgen05_commit(query_free_bar + 8U * query_buffer);
-        if (!ptx::mbarrier_wait_checked(probability_bar, item_parity, abort_flag, args.device_error, 36)) {
+        if (ptx::elect_one())
+          ptx::tcgen05_commit(query_free_bar + 8U * query_buffer);
+        __syncwarp();
+        if (__all_sync(0xFFFFFFFFU, ptx::mbarrier_wait_checked(probability_bar, item_parity, abort_flag, args.device_error, 36) ? 1 : 0) == 0) {
           healthy = false;
           break;
         }
         ptx::tcgen05_fence_after_thread_sync();
         uint32_t accumulate = 0;
         if (proposal_items != 0) {
-          if (!ptx::mbarrier_wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
-                            args.device_error, 37)) {
+          if (__all_sync(0xFFFFFFFFU, ptx::mbarrier_wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
+                            args.device_error, 37) ? 1 : 0) == 0) {
             healthy = false;
             break;
           }
           ptx::tcgen05_fence_after_thread_sync();
           const uint32_t a_low = value_low + cursor.stage * stage_step;
+          if (ptx::elect_one()) {
 #pragma unroll
-          for (int slice = 0; slice < 2; ++slice)
-            ptx::tcgen05_mma_f16_split(tmem_output + slice * fused_rows,
-                                       a_low + slice * ((2 * value_box_bytes) >> 4), desc_high,
-                                       box_low, desc_high, value_idesc, 0U);
+            for (int slice = 0; slice < 2; ++slice)
+              ptx::tcgen05_mma_f16_split(tmem_output + slice * fused_rows,
+                                         a_low + slice * ((2 * value_box_bytes) >> 4), desc_high,
+                                         box_low, desc_high, value_idesc, 0U);
+            ptx::tcgen05_commit(empty_bar + 8U * cursor.stage);
+          }
+          __syncwarp();
           accumulate = 1;
-          ptx::tcgen05_commit(empty_bar + 8U * cursor.stage);
           cursor.advance();
         }
         const int value_groups = item.value_items - proposal_items;
         for (int key_group = 0; key_group < value_groups; ++key_group) {
-          if (!ptx::mbarrier_wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
-                            args.device_error, 37)) {
+          if (__all_sync(0xFFFFFFFFU, ptx::mbarrier_wait_checked(full_bar + 8U * cursor.stage, cursor.phase, abort_flag,
+                            args.device_error, 37) ? 1 : 0) == 0) {
             healthy = false;
             break;
           }
@@ -404,6 +415,7 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
           // Probability box (64 keys) and the 32-byte step inside its 128-byte rows.
           const uint32_t b_low = box_low + (1 + (key_group >> 1)) * (fused_box_bytes >> 4) +
                                  (key_group & 1) * 4;
+          if (ptx::elect_one()) {
 #pragma unroll
           for (int step = 0; step < 2; ++step) {
 #pragma unroll
@@ -416,12 +428,15 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
                   b_low + 2 * step, desc_high, value_idesc, step > 0 ? 1U : accumulate);
             }
           }
-          accumulate = 1;
           ptx::tcgen05_commit(empty_bar + 8U * cursor.stage);
+          }
+          __syncwarp();
+          accumulate = 1;
           cursor.advance();
         }
-        if (healthy)
+        if (healthy && ptx::elect_one())
           ptx::tcgen05_commit(output_bar);
+        __syncwarp();
       }
     }
   } else {
