@@ -43,6 +43,18 @@ def test_full_batch_depth_nine(cuda_device):
     _, _, trace = scout.verify_greedy_proposals(proposals, firsts, slots, caps, assume_match=True,
                                                 trace=True)
     starts = [device.slot_position(slot) for slot in slots]
+    # The INT4 MLP variant takes at most 128 rows a step (the reference's Int4Bf16Linear::
+    # supports_rows): 216 rows are refused before any launch, with the reference's text, and the
+    # state is untouched; wrong shapes are refused when the variant is switched on.
+    arena = carat_b200.DeviceWeightArena.from_host(weights)
+    with pytest.raises(carat_b200.CaratError, match="invalid BF16 INT4 linear weight shape"):
+        device.use_int4_mlp(arena, 64)
+    device.use_int4_mlp(arena, 128)
+    with pytest.raises(carat_b200.CaratError, match="invalid BF16 INT4 linear activation shape"):
+        device.verify_greedy_proposals(proposals, firsts, slots, caps,
+                                       carat_b200.VERIFY_ASSUME_MATCH)
+    assert [device.slot_position(slot) for slot in slots] == starts
+    device.use_int4_mlp(None)
     result = device.verify_greedy_proposals(proposals, firsts, slots, caps,
                                             carat_b200.VERIFY_ASSUME_MATCH)
     assert result.accepted_tokens == caps
