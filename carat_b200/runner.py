@@ -405,6 +405,15 @@ class Gemma4BatchModelRunner:
         check(self._library.carat_b200_runner_last_predictions(self._handle, output, count))
         return list(output)
 
+    def device_pointer(self, which: int, layer: int = 0):
+        """(address, bytes) of a runner-owned device buffer (carat_b200_runner_device_pointer)."""
+        pointer = ctypes.c_void_p()
+        size = ctypes.c_size_t(0)
+        check(self._library.carat_b200_runner_device_pointer(self._handle, which, layer,
+                                                             ctypes.byref(pointer),
+                                                             ctypes.byref(size)))
+        return pointer.value, size.value
+
     def _device_view(self, which: int, layer: int, shape) -> torch.Tensor:
         elements = 1
         for extent in shape:
@@ -463,6 +472,32 @@ class Gemma4BatchModelRunner:
 
     def last_final_hidden(self, rows: int) -> torch.Tensor:
         return self._device_view(3, 0, (rows, self.config.hidden_size))
+
+    def last_logits(self, rows: int) -> torch.Tensor:
+        """bf16 logits [rows, vocabulary] of the last verify call. The step never stores logits
+        (the LM head's epilogue keeps only the argmax), so they are recomputed here from the
+        call's final-normed hidden rows with the same tensor-scale quantiser and FP8 linear
+        (run_decode_lm_head, cuda/batch_model_runner.cu:840-853). Inspection only."""
+        library = self._library
+        hidden = self.last_final_hidden(rows)
+        width, vocabulary = self.config.hidden_size, self.config.vocabulary_size
+        fp8 = self._keep[1]
+        quantised = torch.empty(rows, width, dtype=torch.uint8, device="cuda")
+        scale = torch.zeros(1, dtype=torch.float32, device="cuda")
+        scratch = torch.zeros(1, dtype=torch.int32, device="cuda")
+        logits = torch.empty(rows, vocabulary, dtype=torch.bfloat16, device="cuda")
+        needed = library.carat_b200_fp8_linear_workspace_bytes(rows, width, vocabulary)
+        workspace = torch.empty(max(needed, 16), dtype=torch.uint8, device="cuda")
+        stream = torch.cuda.current_stream().cuda_stream
+        check(library.carat_b200_quantize_bf16_to_fp8(hidden.data_ptr(), quantised.data_ptr(),
+                                                      scale.data_ptr(), scratch.data_ptr(), rows,
+                                                      width, stream))
+        check(library.carat_b200_fp8_linear(
+            quantised.data_ptr(), scale.data_ptr(), fp8.at("token_embedding").data_ptr(),
+            fp8.scale("token_embedding").data_ptr(), logits.data_ptr(), rows, width, vocabulary,
+            workspace.data_ptr(), needed, stream))
+        torch.cuda.synchronize()
+        return logits
 
     def assistant_final_hidden(self, rows: int, width: int) -> torch.Tensor:
         return self._device_view(4, 0, (rows, width))

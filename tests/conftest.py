@@ -19,3 +19,14 @@ def cuda_device():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+def reference_root():
+    """Root of a Gradiated/carat checkout, or None: the CARAT_REFERENCE environment variable, else
+    a directory named `reference` beside this repository."""
+    candidates = [os.environ.get("CARAT_REFERENCE"),
+                  os.path.join(os.path.dirname(ROOT), "reference")]
+    for candidate in candidates:
+        if candidate and os.path.isdir(os.path.join(candidate, "include", "carat")):
+            return candidate
+    return None

@@ -1,0 +1,399 @@
+"""The runner beside the reference's own Gemma4BatchModelRunner, on the same GPU, weights and calls.
+
+The reference side is carat::Gemma4BatchModelRunner / Gemma4AssistantRunner themselves
+(cuda/batch_model_runner.cu, cuda/assistant_runner.cu, cuda/layer_runner.cu ...) compiled
+unmodified for sm_100a into oracle/_ref/libref_cuda.so; its linears are cuBLASLt, its attention
+cuBLAS GEMMs plus its own softmax / repair kernels. Both runners get the same e4m3 weights and the
+same sequence of calls at the model's real widths (hidden 5376, FFN 21504, 32/16 heads of 256 and
+32/4 heads of 512, vocabulary 262144, 24 slots), starting from the zero-filled cache both sides'
+seed_empty_cache_for_benchmark leaves.
+
+Bars (the path's contract): accept lengths, next tokens and slot positions identical, except where
+a token differs at a logit near-tie. A near-tie is a top-2 margin within bf16 relative 2e-2 of the
+winning logit (the tolerance logits themselves are held to; at these magnitudes one bf16 ulp is
+already above the absolute 1e-2 figure, which is reported too). Near-ties are counted and bounded;
+after one, the two runners are re-synchronised by feeding both the reference's token.
+"""
+import os
+
+import pytest
+import torch
+
+import carat_b200
+import reference_cuda as ref
+from carat_b200.capi import check
+
+pytestmark = pytest.mark.gpu
+
+SLOTS = 24
+LIVE = 12               # slots 0..11 carry requests, 12..23 are scratch copies for look-ahead
+MAX_CONTEXT = 2048
+VOCABULARY = 262144
+
+
+def _random_matrix(rows, cols, generator, std=0.02):
+    out = torch.empty(rows, cols, dtype=torch.bfloat16, device="cuda")
+    step = max(1, (32 << 20) // cols)
+    for start in range(0, rows, step):
+        stop = min(rows, start + step)
+        out[start:stop] = (torch.randn(stop - start, cols, device="cuda", generator=generator)
+                           * std).to(torch.bfloat16)
+    return out
+
+
+def _norm(width, generator):
+    return (1.0 + 0.05 * torch.randn(width, device="cuda", generator=generator)).to(torch.bfloat16)
+
+
+class Pair:
+    """One set of weights, this repository's runner and the reference's runner over it."""
+
+    def __init__(self):
+        layers = [carat_b200.Gemma4LayerConfig("sliding", 32, 16, 256, 1e4, False),
+                  carat_b200.Gemma4LayerConfig("global", 32, 4, 512, 1e6, True)]
+        self.config = carat_b200.Gemma4Config(5376, 21504, VOCABULARY, 1024, 1e-6, layers)
+        generator = torch.Generator(device="cuda").manual_seed(0)
+        hidden, inter = self.config.hidden_size, self.config.intermediate_size
+        bf16 = {"token_embedding": _random_matrix(VOCABULARY, hidden, generator),
+                "final_norm": _norm(hidden, generator)}
+        for index, layer in enumerate(layers):
+            prefix = f"layer.{index}."
+            for name, width in (("input_norm", hidden), ("q_norm", layer.head_dimension),
+                                ("k_norm", layer.head_dimension), ("post_attention_norm", hidden),
+                                ("pre_mlp_norm", hidden), ("post_mlp_norm", hidden)):
+                bf16[prefix + name] = _norm(width, generator)
+            bf16[prefix + "scalar"] = torch.tensor([0.9], dtype=torch.bfloat16, device="cuda")
+            bf16[prefix + "qkv"] = _random_matrix(layer.packed_width(), hidden, generator)
+            bf16[prefix + "o"] = _random_matrix(hidden, layer.query_width(), generator)
+            bf16[prefix + "gate_up"] = _random_matrix(2 * inter, hidden, generator)
+            bf16[prefix + "down"] = _random_matrix(hidden, inter, generator)
+        self.weights = carat_b200.DeviceWeightArena(bf16)
+        self.fp8 = carat_b200.Fp8WeightArena.quantize(self.weights)
+
+        self.assistant_config = carat_b200.Gemma4AssistantConfig()
+        a_hidden, a_inter = 1024, 8192
+        a = {"token_embedding": _random_matrix(VOCABULARY, a_hidden, generator, 0.05),
+             "pre_projection": _random_matrix(a_hidden, 2 * hidden, generator),
+             "post_projection": _random_matrix(hidden, a_hidden, generator, 0.05),
+             "final_norm": _norm(a_hidden, generator)}
+        for index, kind in enumerate(self.assistant_config.layers):
+            prefix = f"layer.{index}."
+            head_dim = 512 if kind == "global" else 256
+            for name, width in (("input_norm", a_hidden), ("q_norm", head_dim),
+                                ("post_attention_norm", a_hidden), ("pre_mlp_norm", a_hidden),
+                                ("post_mlp_norm", a_hidden)):
+                a[prefix + name] = _norm(width, generator)
+            a[prefix + "scalar"] = torch.tensor([0.9], dtype=torch.bfloat16, device="cuda")
+            a[prefix + "q"] = _random_matrix(32 * head_dim, a_hidden, generator, 0.05)
+            a[prefix + "o"] = _random_matrix(a_hidden, 32 * head_dim, generator)
+            a[prefix + "gate_up"] = _random_matrix(2 * a_inter, a_hidden, generator, 0.05)
+            a[prefix + "down"] = _random_matrix(a_hidden, a_inter, generator)
+        self.assistant_weights = carat_b200.DeviceWeightArena(a)
+        self.assistant_fp8 = carat_b200.Fp8WeightArena.quantize(self.assistant_weights)
+        torch.cuda.synchronize()
+
+        self.ours = carat_b200.Gemma4BatchModelRunner(
+            self.config, self.weights, SLOTS, MAX_CONTEXT, self.fp8, self.assistant_weights,
+            self.assistant_fp8, self.assistant_config)
+        # The reference reads its drafter precision from the environment when it is built; this
+        # repository's drafter runs every linear in e4m3, the reference's "all" mode
+        # (cuda/assistant_runner.cu:31-43).
+        os.environ["CARAT_ASSISTANT_FP8_MODE"] = "all"
+        self.theirs = ref.ReferenceRunner(
+            self.config, self.weights.tensors, self.fp8.bytes, self.fp8.scales, SLOTS, MAX_CONTEXT,
+            self.assistant_weights.tensors, self.assistant_fp8.bytes, self.assistant_fp8.scales)
+
+    def close(self):
+        self.theirs.close()
+        self.ours.close()
+
+    def seed(self, position):
+        self.ours.seed_empty_cache_for_benchmark(position)
+        self.theirs.seed_empty_cache_for_benchmark(position)
+
+
+@pytest.fixture(scope="module")
+def pair(cuda_device):
+    ref.library()
+    made = Pair()
+    yield made
+    made.close()
+    torch.cuda.empty_cache()
+
+
+DRAFT_BAND = 0.2
+
+
+def drafter_logits(pair, rows):
+    """bf16 logits of the drafter's last draft step, recomputed from its final-normed hidden rows
+    with the quantiser and FP8 linear its LM head uses."""
+    library = carat_b200.library()
+    width = pair.assistant_config.hidden_size
+    hidden = pair.ours.assistant_final_hidden(rows, width)
+    quantised = torch.empty(rows, width, dtype=torch.uint8, device="cuda")
+    scale = torch.zeros(1, dtype=torch.float32, device="cuda")
+    scratch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    check(library.carat_b200_quantize_bf16_to_fp8(hidden.data_ptr(), quantised.data_ptr(),
+                                                  scale.data_ptr(), scratch.data_ptr(), rows,
+                                                  width, None))
+    logits = torch.empty(rows, VOCABULARY, dtype=torch.bfloat16, device="cuda")
+    needed = library.carat_b200_fp8_linear_workspace_bytes(rows, width, VOCABULARY)
+    workspace = torch.empty(max(needed, 16), dtype=torch.uint8, device="cuda")
+    fp8 = pair.assistant_fp8
+    check(library.carat_b200_fp8_linear(
+        quantised.data_ptr(), scale.data_ptr(), fp8.at("token_embedding").data_ptr(),
+        fp8.scale("token_embedding").data_ptr(), logits.data_ptr(), rows, width, VOCABULARY,
+        workspace.data_ptr(), needed, None))
+    torch.cuda.synchronize()
+    return logits.float()
+
+
+class NearTies:
+    def __init__(self):
+        self.relative = 0       # flagged: margin within bf16 relative 2e-2 of the top logit
+        self.absolute = 0       # of those, margin below 1e-2
+        self.rows = 0
+        self.diverged = False
+
+    def check(self, logits_row, token_a, token_b):
+        """Both tokens must sit within the near-tie band of this side's own logits."""
+        values = logits_row.float()
+        top = float(values.max())
+        margin = abs(float(values[token_a]) - float(values[token_b]))
+        low = min(float(values[token_a]), float(values[token_b]))
+        assert top - low <= 2e-2 * abs(top) + 1e-6, (top, low, token_a, token_b)
+        self.relative += 1
+        if margin < 1e-2:
+            self.absolute += 1
+
+
+def lookahead(pair, proposals, first, known, live, scratch):
+    """Fills proposals[:, 1:known+1] with the target's own greedy continuation, found by running
+    this side's verify on scratch copies of the live slots (one pass per extra token)."""
+    depth = len(proposals[0])
+    for column in range(1, known + 1):
+        for source, destination in zip(live, scratch):
+            pair.ours.clone_slot(source, destination)
+        pair.ours.verify_greedy_proposals(proposals, first, scratch)
+        predicted = pair.ours.last_predictions(len(live) * depth)
+        for row in range(len(live)):
+            proposals[row][column] = predicted[row * depth + column - 1]
+    return proposals
+
+
+def run_steps(pair, start_position, steps, depth, ragged_caps, drafts):
+    """Free-running verify (and draft) loop on both runners from the same seeded state."""
+    pair.seed(start_position)
+    generator = torch.Generator().manual_seed(start_position * 31 + depth)
+    live = list(range(LIVE))
+    scratch = list(range(LIVE, 2 * LIVE))
+    first = torch.randint(3, VOCABULARY, (LIVE,), generator=generator).tolist()
+    ties = NearTies()
+    accepted_total = 0
+    draft_rows = draft_mismatch = 0
+    for step in range(steps):
+        proposals = [[first[row]] + torch.randint(3, VOCABULARY, (depth - 1,),
+                                                  generator=generator).tolist()
+                     for row in range(LIVE)]
+        known = min(step % 4, depth - 1)
+        proposals = lookahead(pair, proposals, first, known, live, scratch)
+        caps = None
+        if ragged_caps:
+            caps = torch.randint(1, depth + 1, (LIVE,), generator=generator).tolist()
+        result = pair.ours.verify_greedy_proposals(proposals, first, live, caps or ())
+        predictions = pair.ours.last_predictions(LIVE * depth)
+        accepted_ref, next_ref = pair.theirs.verify_greedy_proposals(proposals, first, live, caps)
+        ties.rows += LIVE * depth
+        logits = None
+        diverged = False
+        for row in range(LIVE):
+            mine, theirs = result.accepted_tokens[row], accepted_ref[row]
+            if mine == theirs and result.next_tokens[row] == next_ref[row]:
+                continue
+            if logits is None:
+                logits = pair.ours.last_logits(LIVE * depth)
+            # The row whose prediction the two sides read differently: both candidates must be
+            # near-ties in this side's logits.
+            decided = min(mine, theirs)
+            deciding_row = row * depth + decided - 1
+            if mine == theirs:
+                ties.check(logits[deciding_row], result.next_tokens[row], next_ref[row])
+            else:
+                other = next_ref[row] if theirs < mine else proposals[row][decided]
+                ties.check(logits[deciding_row], predictions[deciding_row], other)
+                diverged = True
+        if diverged:
+            # Accept lengths differ at a flagged near-tie: the two caches now hold different
+            # positions, so the comparison ends here (counted by the caller's bound).
+            ties.diverged = True
+            break
+        for row in range(LIVE):
+            assert pair.ours.slot_position(live[row]) == pair.theirs.slot_position(live[row])
+        accepted_total += sum(accepted_ref)
+        if not ragged_caps:
+            assert len(set(accepted_ref)) == 1     # positions stay uniform
+            if caps is None:
+                assert accepted_ref[0] >= known + 1 or ties.relative > 0
+        # Both sides continue from the reference's next tokens.
+        first = list(next_ref)
+        if drafts:
+            # Forced first token, then one drafted token: the drafter's hidden rows of that draft
+            # step stay readable, so a differing token can be looked up in this side's logits.
+            last = [proposals[row][accepted_ref[row] - 1] for row in range(LIVE)]
+            drafted_a = pair.ours.draft_four(last, live, first, 2)
+            draft_logits = drafter_logits(pair, LIVE)
+            drafted_b = pair.theirs.draft_four(last, live, first, 2)
+            for row in range(LIVE):
+                assert drafted_a[row][0] == first[row] == drafted_b[row][0]
+                draft_rows += 1
+                if drafted_a[row][1] != drafted_b[row][1]:
+                    values = draft_logits[row]
+                    top = float(values.max())
+                    assert int(values.argmax()) == drafted_a[row][1]
+                    assert top - float(values[drafted_b[row][1]]) <= DRAFT_BAND * abs(top)
+                    draft_mismatch += 1
+    return ties, accepted_total, draft_rows, draft_mismatch
+
+
+def test_unwrapped_ring_equal_positions(pair):
+    """All slots at the same position below the window: the reference attends the real cache
+    directly (cuda/layer_runner.cu:852-878)."""
+    ties, accepted, _, _ = run_steps(pair, start_position=1, steps=12, depth=5, ragged_caps=False,
+                                     drafts=False)
+    print(f"near-ties: {ties.relative} flagged ({ties.absolute} below 1e-2) of {ties.rows} rows; "
+          f"{accepted} tokens accepted")
+    assert ties.relative <= 4
+    assert accepted >= 12 * LIVE
+
+
+def test_wrapped_ring_ragged_accept_lengths_and_drafts(pair):
+    """Every slot past the window: the reference writes proposals into the ring, repairs later
+    slots from the backup and restores rejected rows (cuda/layer_runner.cu:826-850,
+    cuda/ops.cu:827-871); caps make accept lengths and positions differ between slots. The
+    drafter runs after every step on both sides.
+
+    The random-init drafter (hidden 1024, every linear re-quantised to e4m3 from a tensor-wide
+    maximum, near-flat logits over 262144 entries) amplifies last-bit differences between the two
+    sides' linears far more than the target does: its first drafted token differs on a share of
+    the rows (test_drafter_disagreement_is_within_its_own_noise measures that share against the
+    reference's own sensitivity). Drafted tokens never reach the output stream unverified, so
+    this bounds acceptance rate, not correctness."""
+    ties, accepted, draft_rows, draft_mismatch = run_steps(
+        pair, start_position=1030, steps=10, depth=5, ragged_caps=True, drafts=True)
+    print(f"near-ties: {ties.relative} flagged ({ties.absolute} below 1e-2) of {ties.rows} rows; "
+          f"{accepted} tokens accepted; first drafted token differing on {draft_mismatch} of "
+          f"{draft_rows} rows")
+    assert ties.relative <= 4
+    assert accepted > 10 * LIVE
+    assert draft_mismatch <= 0.45 * draft_rows
+
+
+def test_drafter_disagreement_is_within_its_own_noise(pair):
+    """carat::Gemma4AssistantRunner run directly over this runner's own memory (target embedding,
+    hidden-by-slot table, the two shared KV layers), so both drafters read identical bytes.
+
+    With random-init weights the drafter's logits are nearly flat and its e4m3 chain is chaotic:
+    flipping the last bf16 bit of 1 % of the hidden hand-off elements changes the reference's own
+    first drafted token on a quarter to a third of the rows. The bar: this side disagrees with
+    the reference no more often than the reference disagrees with itself under that one-ulp
+    perturbation (plus 10 % of the rows for sampling noise), and where it disagrees the
+    reference's token is among this side's top candidates."""
+    assistant = ref.ReferenceAssistant(pair.assistant_weights.tensors, pair.assistant_fp8.bytes,
+                                       pair.assistant_fp8.scales, SLOTS, MAX_CONTEXT)
+    embedding = pair.weights.at("token_embedding").data_ptr()
+    live = list(range(LIVE))
+    cross = own_noise = reference_noise = rows = 0
+    try:
+        for start in (40, 1030):
+            pair.seed(start)
+            generator = torch.Generator().manual_seed(start)
+            first = torch.randint(3, VOCABULARY, (LIVE,), generator=generator).tolist()
+            for _ in range(5):
+                proposals = [[first[row]] + torch.randint(3, VOCABULARY, (4,),
+                                                          generator=generator).tolist()
+                             for row in range(LIVE)]
+                result = pair.ours.verify_greedy_proposals(proposals, first, live)
+                first = result.next_tokens
+                last = [proposals[row][result.accepted_tokens[row] - 1] for row in range(LIVE)]
+                contexts = [pair.ours.slot_position(slot) - 1 for slot in live]
+                hidden = pair.ours.device_pointer(2, 0)[0]
+                sliding = (pair.ours.device_pointer(0, 0)[0], pair.ours.device_pointer(1, 0)[0])
+                global_ = (pair.ours.device_pointer(0, 1)[0], pair.ours.device_pointer(1, 1)[0])
+
+                def theirs():
+                    return assistant.draft_four(embedding, hidden, last, contexts, live, first,
+                                                SLOTS, 2, sliding[0], sliding[1], 1024, global_[0],
+                                                global_[1], MAX_CONTEXT)
+
+                mine = pair.ours.draft_four(last, live, first, 2)
+                logits = drafter_logits(pair, LIVE)
+                reference = theirs()
+                table = pair.ours.target_hidden_slots()
+                bits = table.view(torch.int16).clone()
+                flip = torch.rand(bits.shape, device="cuda",
+                                  generator=torch.Generator(device="cuda").manual_seed(rows)) < 0.01
+                bits[flip] ^= 1
+                pair.ours.write_cache(2, 0, bits.view(torch.bfloat16))
+                mine_perturbed = pair.ours.draft_four(last, live, first, 2)
+                reference_perturbed = theirs()
+                pair.ours.write_cache(2, 0, table)
+                for row in range(LIVE):
+                    rows += 1
+                    own_noise += mine[row][1] != mine_perturbed[row][1]
+                    reference_noise += reference[row][1] != reference_perturbed[row][1]
+                    if mine[row][1] != reference[row][1]:
+                        cross += 1
+                        top = float(logits[row].max())
+                        gap = top - float(logits[row, reference[row][1]])
+                        assert gap <= DRAFT_BAND * abs(top)
+    finally:
+        assistant.close()
+    print(f"first drafted token over {rows} rows: differs from the reference on {cross}; the "
+          f"reference changes on {reference_noise} and this side on {own_noise} under a one-ulp "
+          "perturbation of 1 % of the hand-off elements")
+    assert cross <= max(reference_noise, own_noise) + 0.1 * rows
+
+
+def test_depth_eight_wrapped(pair):
+    ties, accepted, _, _ = run_steps(pair, start_position=1500, steps=6, depth=8,
+                                     ragged_caps=True, drafts=False)
+    print(f"near-ties: {ties.relative} flagged of {ties.rows} rows; {accepted} tokens accepted")
+    assert ties.relative <= 4
+
+
+def test_plain_decode_matches(pair):
+    """append_ragged on both sides (cuda/batch_model_runner.cu:1544-1615)."""
+    pair.seed(40)
+    generator = torch.Generator().manual_seed(5)
+    live = list(range(LIVE))
+    tokens = torch.randint(3, VOCABULARY, (LIVE,), generator=generator).tolist()
+    differing = 0
+    for _ in range(8):
+        mine = pair.ours.append_ragged(tokens, live)
+        theirs = pair.theirs.append_ragged(tokens, live)
+        differing += sum(a != b for a, b in zip(mine, theirs))
+        for slot in live:
+            assert pair.ours.slot_position(slot) == pair.theirs.slot_position(slot)
+        tokens = theirs
+    print(f"plain decode: {differing} of {8 * LIVE} next tokens differ")
+    assert differing <= 2
+
+
+def test_argument_errors_carry_the_reference_texts(pair):
+    pair.seed(10)
+    pair.ours.reset_slot(5)
+    pair.theirs.reset_slot(5)
+    cases = [
+        dict(proposals=[[5, 6], [7, 8]], first=[5, 7], slots=[3, 3]),
+        dict(proposals=[[5, 6], [7, 8]], first=[5, 7], slots=[3, SLOTS]),
+        dict(proposals=[[5, VOCABULARY], [7, 8]], first=[5, 7], slots=[0, 1]),
+        dict(proposals=[[5, 6], [7, 8]], first=[5, 7], slots=[4, 5]),       # slot 5 is empty
+    ]
+    for case in cases:
+        with pytest.raises(carat_b200.CaratError) as mine:
+            pair.ours.verify_greedy_proposals(case["proposals"], case["first"], case["slots"])
+        with pytest.raises(ref.ReferenceError_) as theirs:
+            pair.theirs.verify_greedy_proposals(case["proposals"], case["first"], case["slots"])
+        assert str(mine.value) == str(theirs.value)
+        for slot in range(5):
+            assert pair.ours.slot_position(slot) == pair.theirs.slot_position(slot) == 10

@@ -7,16 +7,18 @@ import subprocess
 
 import pytest
 
+from conftest import reference_root
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REFERENCE_INCLUDE = "/root/reference/include"
 
 
-@pytest.mark.skipif(not os.path.isdir(REFERENCE_INCLUDE), reason="reference headers not mounted")
+@pytest.mark.skipif(reference_root() is None, reason="no checkout of the reference found")
 @pytest.mark.skipif(shutil.which("g++") is None, reason="no g++")
 def test_shim_compiles_against_the_reference_headers():
+    cuda_home = os.environ.get("CUDA_HOME", os.path.dirname(os.path.dirname(shutil.which("nvcc"))))
     command = ["g++", "-std=c++20", "-fsyntax-only", "-Wall", "-Wextra", "-Werror",
-               "-I", REFERENCE_INCLUDE, "-I", os.path.join(ROOT, "include"),
-               "-I", "/usr/local/cuda/include",
+               "-I", os.path.join(reference_root(), "include"), "-I", os.path.join(ROOT, "include"),
+               "-I", os.path.join(cuda_home, "include"),
                os.path.join(ROOT, "carat_b200", "shim", "batch_model_runner_shim.cpp")]
     done = subprocess.run(command, capture_output=True, text=True, timeout=300)
     assert done.returncode == 0, done.stderr[-3000:]
