@@ -69,6 +69,7 @@ SIGNATURES = {
     "carat_b200_last_error": (c_char_p, []),
     "carat_b200_abi_version": (_I, []),
     "carat_b200_device_error": (_I, [_IP]),
+    "carat_b200_selftest_bounded_wait": (_I, [_P, _P]),
     "carat_b200_fp8_linear": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P, c_size_t, _P]),
     "carat_b200_fp8_linear_workspace_bytes": (c_size_t, [_I, _I, _I]),
     "carat_b200_fp8_linear_static": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),

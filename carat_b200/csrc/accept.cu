@@ -3,7 +3,6 @@
 #include "launch.cuh"
 
 #include <cuda_bf16.h>
-#include <math_constants.h>
 
 namespace carat_b200 {
 namespace {
@@ -29,7 +28,6 @@ __global__ void accept_kernel(AcceptArguments a) {
     a.accepted[request] = accepted;
     a.next_tokens[request] =
         accepted == 0 ? a.target_first[request] : best_index(a.best[start + accepted - 1]);
-    a.slot_positions[a.slots[request]] += accepted;
     shared_accepted = accepted;
   }
   for (int token = static_cast<int>(threadIdx.x); token < a.depth; token += blockDim.x)
@@ -75,74 +73,77 @@ __global__ void commit_kernel(const CommitLayer *layers, const int *positions, c
   }
 }
 
-__global__ void backup_kernel(const __nv_bfloat16 *const *key_sources,
-                              const __nv_bfloat16 *const *value_sources, __nv_bfloat16 *backup_keys,
-                              __nv_bfloat16 *backup_values, const int *positions, int requests,
-                              int heads, int tokens, int dimension, int capacity) {
-  const long long index = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const long long request_elements = static_cast<long long>(heads) * tokens * dimension;
-  if (index >= requests * request_elements)
-    return;
-  const int request = static_cast<int>(index / request_elements);
-  const long long local = index % request_elements;
-  const int component = static_cast<int>(local % dimension);
-  const int token = static_cast<int>((local / dimension) % tokens);
-  const int head = static_cast<int>(local / (static_cast<long long>(dimension) * tokens));
-  const size_t source =
-      (static_cast<size_t>(head) * capacity + (positions[request] + token) % capacity) * dimension +
-      component;
-  backup_keys[index] = key_sources[request][source];
-  backup_values[index] = value_sources[request][source];
+// Rollback primitive, both directions in one kernel: CTA (head, request) moves whole rows of
+// `dimension` bf16 as 16-byte vectors between the ring rows (position + token) % capacity of that
+// request's cache [heads, capacity, dimension] and the packed span [request][head][token]
+// [dimension]. restore = false saves the span; restore = true writes back the tokens from
+// accepted[request] on (the rejected suffix) and leaves accepted rows alone.
+template <bool restore>
+__global__ void ring_span_kernel(__nv_bfloat16 *const *key_caches,
+                                 __nv_bfloat16 *const *value_caches, __nv_bfloat16 *span_keys,
+                                 __nv_bfloat16 *span_values, const int *positions,
+                                 const int *accepted, int heads, int tokens, int dimension,
+                                 int capacity) {
+  const int head = static_cast<int>(blockIdx.x);
+  const int request = static_cast<int>(blockIdx.y);
+  const int first_token = restore ? min(max(accepted[request], 0), tokens) : 0;
+  const int vectors_per_row = dimension / 8;
+  const int position = positions[request];
+  const size_t span_base = (static_cast<size_t>(request) * heads + head) * tokens * dimension;
+  const size_t cache_base = static_cast<size_t>(head) * capacity * dimension;
+  uint4 *const span[2] = {reinterpret_cast<uint4 *>(span_keys + span_base),
+                          reinterpret_cast<uint4 *>(span_values + span_base)};
+  __nv_bfloat16 *const cache[2] = {key_caches[request] + cache_base,
+                                   value_caches[request] + cache_base};
+  const int vectors = (tokens - first_token) * vectors_per_row;
+  for (int index = static_cast<int>(threadIdx.x); index < vectors; index += blockDim.x) {
+    const int token = first_token + index / vectors_per_row;
+    const int vector = index % vectors_per_row;
+    const size_t ring_row = static_cast<size_t>((position + token) % capacity);
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      uint4 *ring = reinterpret_cast<uint4 *>(cache[which] + ring_row * dimension) + vector;
+      uint4 *saved = span[which] + static_cast<size_t>(token) * vectors_per_row + vector;
+      if constexpr (restore)
+        *ring = *saved;
+      else
+        *saved = *ring;
+    }
+  }
 }
 
-__global__ void restore_kernel(const __nv_bfloat16 *backup_keys, const __nv_bfloat16 *backup_values,
-                               __nv_bfloat16 *const *key_destinations,
-                               __nv_bfloat16 *const *value_destinations, const int *positions,
-                               const int *accepted, int requests, int heads, int tokens,
-                               int dimension, int capacity) {
-  const long long index = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const long long request_elements = static_cast<long long>(heads) * tokens * dimension;
-  if (index >= requests * request_elements)
-    return;
-  const int request = static_cast<int>(index / request_elements);
-  const long long local = index % request_elements;
-  const int component = static_cast<int>(local % dimension);
-  const int token = static_cast<int>((local / dimension) % tokens);
-  if (token < accepted[request])
-    return;
-  const int head = static_cast<int>(local / (static_cast<long long>(dimension) * tokens));
-  const size_t destination =
-      (static_cast<size_t>(head) * capacity + (positions[request] + token) % capacity) * dimension +
-      component;
-  key_destinations[request][destination] = backup_keys[index];
-  value_destinations[request][destination] = backup_values[index];
-}
-
-struct Best {
-  float value;
-  int index;
-};
-
-__device__ __forceinline__ Best better(Best left, Best right) {
-  return right.value > left.value || (right.value == left.value && right.index < left.index) ? right
-                                                                                             : left;
+// Row argmax with the LM head's packed keys: (orderable bf16 value << 32) | ~index, so one
+// unsigned maximum picks the largest value and, among equals, the lowest index; NaN orders below
+// every number and an all-NaN row yields index 0.
+__device__ __forceinline__ unsigned long long argmax_key(__nv_bfloat16 value, int index) {
+  const unsigned int bits = __bfloat16_as_ushort(value);
+  unsigned int orderable = (bits & 0x8000U) ? (~bits & 0xFFFFU) : (bits | 0x8000U);
+  if ((bits & 0x7FFFU) > 0x7F80U)
+    orderable = 0U;
+  return (static_cast<unsigned long long>(orderable) << 32) |
+         static_cast<unsigned long long>(~static_cast<unsigned int>(index));
 }
 
 __global__ void argmax_rows_kernel(const __nv_bfloat16 *values, int elements, int *output) {
-  __shared__ Best reduction[256];
+  __shared__ unsigned long long warp_best[32];
   const __nv_bfloat16 *row = values + static_cast<size_t>(blockIdx.x) * elements;
-  Best current{-CUDART_INF_F, 0};
-  for (int index = static_cast<int>(threadIdx.x); index < elements; index += 256)
-    current = better(current, {__bfloat162float(row[index]), index});
-  reduction[threadIdx.x] = current;
+  unsigned long long best = 0ULL;
+  for (int index = static_cast<int>(threadIdx.x); index < elements; index += blockDim.x)
+    best = max(best, argmax_key(row[index], index));
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1)
+    best = max(best, __shfl_xor_sync(0xFFFFFFFFU, best, offset));
+  if ((threadIdx.x & 31U) == 0U)
+    warp_best[threadIdx.x >> 5U] = best;
   __syncthreads();
-  for (int stride = 128; stride > 0; stride >>= 1) {
-    if (static_cast<int>(threadIdx.x) < stride)
-      reduction[threadIdx.x] = better(reduction[threadIdx.x], reduction[threadIdx.x + stride]);
-    __syncthreads();
+  if (threadIdx.x < 32U) {
+    best = threadIdx.x < (blockDim.x + 31U) / 32U ? warp_best[threadIdx.x] : 0ULL;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1)
+      best = max(best, __shfl_xor_sync(0xFFFFFFFFU, best, offset));
+    if (threadIdx.x == 0U)
+      output[blockIdx.x] = best_index(best);
   }
-  if (threadIdx.x == 0)
-    output[blockIdx.x] = reduction[0].index;
 }
 
 __global__ void move_rows_kernel(const __nv_bfloat16 *input, const int *indices,
@@ -162,7 +163,7 @@ int launch_accept(const AcceptArguments &a, cudaStream_t stream) {
   if (a.best == nullptr || a.proposals == nullptr || a.target_first == nullptr ||
       a.accepted == nullptr || a.next_tokens == nullptr || a.predictions == nullptr ||
       a.final_hidden == nullptr || a.hidden_by_slot == nullptr || a.slots == nullptr ||
-      a.slot_positions == nullptr || a.requests <= 0 || a.depth <= 0 || a.hidden % 8 != 0) {
+      a.requests <= 0 || a.depth <= 0 || a.hidden % 8 != 0) {
     return -1;
   }
   launch_chained(accept_kernel, dim3(static_cast<unsigned>(a.requests)), dim3(256), 0, stream, false, a);
@@ -192,12 +193,14 @@ int launch_backup_kv_ring_spans(const void *const *key_sources, const void *cons
       tokens <= 0 || head_dim <= 0 || capacity <= 0) {
     return -1;
   }
-  const long long elements = static_cast<long long>(requests) * heads * tokens * head_dim;
-  backup_kernel<<<static_cast<unsigned>((elements + 255) / 256), 256, 0, stream>>>(
-      reinterpret_cast<const __nv_bfloat16 *const *>(key_sources),
-      reinterpret_cast<const __nv_bfloat16 *const *>(value_sources),
+  if (head_dim % 8 != 0)
+    return -1;
+  ring_span_kernel<false><<<dim3(static_cast<unsigned>(heads), static_cast<unsigned>(requests)),
+                            128, 0, stream>>>(
+      reinterpret_cast<__nv_bfloat16 *const *>(const_cast<void *const *>(key_sources)),
+      reinterpret_cast<__nv_bfloat16 *const *>(const_cast<void *const *>(value_sources)),
       static_cast<__nv_bfloat16 *>(backup_keys), static_cast<__nv_bfloat16 *>(backup_values),
-      positions, requests, heads, tokens, head_dim, capacity);
+      positions, nullptr, heads, tokens, head_dim, capacity);
   return launched();
 }
 
@@ -211,13 +214,15 @@ int launch_restore_kv_ring_suffixes(const void *backup_keys, const void *backup_
       requests <= 0 || heads <= 0 || tokens <= 0 || head_dim <= 0 || capacity <= 0) {
     return -1;
   }
-  const long long elements = static_cast<long long>(requests) * heads * tokens * head_dim;
-  restore_kernel<<<static_cast<unsigned>((elements + 255) / 256), 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16 *>(backup_keys),
-      static_cast<const __nv_bfloat16 *>(backup_values),
+  if (head_dim % 8 != 0)
+    return -1;
+  ring_span_kernel<true><<<dim3(static_cast<unsigned>(heads), static_cast<unsigned>(requests)),
+                           128, 0, stream>>>(
       reinterpret_cast<__nv_bfloat16 *const *>(key_destinations),
-      reinterpret_cast<__nv_bfloat16 *const *>(value_destinations), positions, accepted, requests,
-      heads, tokens, head_dim, capacity);
+      reinterpret_cast<__nv_bfloat16 *const *>(value_destinations),
+      static_cast<__nv_bfloat16 *>(const_cast<void *>(backup_keys)),
+      static_cast<__nv_bfloat16 *>(const_cast<void *>(backup_values)), positions, accepted, heads,
+      tokens, head_dim, capacity);
   return launched();
 }
 

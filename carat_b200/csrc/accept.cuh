@@ -19,7 +19,6 @@ struct AcceptArguments {
   const void *final_hidden;        // [requests * depth, hidden] bf16, final-normed rows
   void *hidden_by_slot;            // [slots, hidden] bf16; row (accepted - 1) lands in slots[r]
   const int *slots;                // [requests]
-  int *slot_positions;             // device copy of the per-slot positions, += accepted
   int requests;
   int depth;
   int hidden;
@@ -27,8 +26,8 @@ struct AcceptArguments {
 
 // accepted = longest prefix with proposal[i] == (i == 0 ? target_first : prediction[i-1]), capped;
 // next = accepted == 0 ? target_first : prediction[accepted-1]
-// (cuda/batch_model_runner.cu:1735-1759); then the hand-off of :1761-1783 and the position update
-// of :1805-1807.
+// (cuda/batch_model_runner.cu:1735-1759); then the hand-off of :1761-1783. The position update
+// of :1805-1807 stays on the host, which owns the slot positions.
 int launch_accept(const AcceptArguments &arguments, cudaStream_t stream);
 
 // One sliding layer's share of the commit: proposal rows t < accepted[r] move from the staging

@@ -676,26 +676,16 @@ bool attention_fused_applies(const AttentionArguments &a) {
 }
 
 int launch_attention_fused(const AttentionArguments &a, int *device_error, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attention_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             fused_shared_bytes) != cudaSuccess) {
-      return -10;
-    }
-    configured = true;
+  static PerDeviceOnce configured;
+  if (configured.run([] {
+        return cudaFuncSetAttribute(attention_fused_kernel,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    fused_shared_bytes);
+      }) != cudaSuccess) {
+    return -10;
   }
   const AttentionMaps &maps = *a.maps;
-  static int multiprocessors = 0;
-  if (multiprocessors == 0) {
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess ||
-        cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device) !=
-            cudaSuccess ||
-        multiprocessors <= 0) {
-      multiprocessors = 0;
-      return -10;
-    }
-  }
+  const int multiprocessors = device_multiprocessors();
   const int items = a.requests * a.kv_heads;
   const FusedArguments arguments{a, device_error, items};
   const bool staged = a.new_keys != nullptr;

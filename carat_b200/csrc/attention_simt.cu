@@ -1,5 +1,6 @@
 #include "attention.cuh"
 #include "attention_geometry.cuh"
+#include "context.cuh"
 #include "launch.cuh"
 
 #include <cuda_bf16.h>
@@ -288,12 +289,12 @@ template <int dimension> int launch_phases(const AttentionArguments &a, cudaStre
   const size_t query_bytes = static_cast<size_t>(rows) * dimension * sizeof(__nv_bfloat16);
   if (query_bytes > 96 * 1024 || rows > 80)
     return -2;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(scores_kernel<dimension>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             96 * 1024) != cudaSuccess)
-      return -10;
-    configured = true;
+  static PerDeviceOnce configured;
+  if (configured.run([] {
+        return cudaFuncSetAttribute(scores_kernel<dimension>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      }) != cudaSuccess) {
+    return -10;
   }
   const dim3 score_grid(static_cast<unsigned>((columns + 127) / 128),
                         static_cast<unsigned>(a.kv_heads), static_cast<unsigned>(a.requests));

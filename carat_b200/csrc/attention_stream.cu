@@ -1017,23 +1017,20 @@ template <int dimension, int padded_rows>
 int launch_stream(const AttentionArguments &a, int *device_error, cudaStream_t stream) {
   using Scores = ScoresShape<dimension, padded_rows>;
   using Values = ValuesShape<dimension, padded_rows>;
-  static int multiprocessors = 0;
-  if (multiprocessors == 0) {
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess ||
-        cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device) !=
-            cudaSuccess ||
-        multiprocessors <= 0 ||
-        cudaFuncSetAttribute(scores_stream_kernel<dimension, padded_rows>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Scores::shared_bytes) != cudaSuccess ||
-        cudaFuncSetAttribute(values_stream_kernel<dimension, padded_rows>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Values::shared_bytes) != cudaSuccess) {
-      multiprocessors = 0;
-      return -10;
-    }
+  static PerDeviceOnce configured;
+  if (configured.run([] {
+        const cudaError_t first = cudaFuncSetAttribute(
+            scores_stream_kernel<dimension, padded_rows>,
+            cudaFuncAttributeMaxDynamicSharedMemorySize, Scores::shared_bytes);
+        if (first != cudaSuccess)
+          return first;
+        return cudaFuncSetAttribute(values_stream_kernel<dimension, padded_rows>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Values::shared_bytes);
+      }) != cudaSuccess) {
+    return -10;
   }
+  const int multiprocessors = device_multiprocessors();
   const AttentionMaps &maps = *a.maps;
   const int items = a.chunks * a.requests * a.kv_heads;
   const StreamArguments arguments{a, device_error, items};

@@ -180,6 +180,17 @@ __global__ void identity_slots_kernel(int *slots, int count) {
 
 namespace {
 
+// Scratch the op-level attention entry points keep for the library's life, one set per device.
+struct AttentionScratch {
+  int *identity_slots = nullptr;     // [1024]: request r owns cache r
+  float2 *stats = nullptr;           // one (maximum, sum) pair per score row and chunk
+  long long stats_rows = 0;
+  float *partials = nullptr;         // chunk partial outputs of long linear caches
+  size_t partial_bytes = 0;
+  int *request_chunks = nullptr;     // [1024]: chunk counts of the last chunked call
+};
+PerDevice<AttentionScratch> attention_scratch;
+
 int run_verify_attention(bool tensor_cores, const void *bf16_queries, const void *bf16_key_caches,
                          const void *bf16_value_caches, const void *bf16_new_keys,
                          const void *bf16_new_values, const int *device_positions,
@@ -192,8 +203,13 @@ int run_verify_attention(bool tensor_cores, const void *bf16_queries, const void
     return -1;
   }
   const auto cuda_stream = static_cast<cudaStream_t>(stream);
-  // Request r owns cache r: an identity slot table kept in device memory for the library's life.
-  static int *identity_slots = nullptr;
+  AttentionScratch *scratch_slot = attention_scratch.slot();
+  if (scratch_slot == nullptr) {
+    set_last_error("verify attention: no current device");
+    return -100;
+  }
+  std::lock_guard<std::mutex> scratch_lock(attention_scratch.lock());
+  int *&identity_slots = scratch_slot->identity_slots;
   if (identity_slots == nullptr) {
     if (check_cuda(cudaMalloc(&identity_slots, sizeof(int) * 1024), "allocate slot table") != 0)
       return -100;
@@ -243,11 +259,11 @@ int run_verify_attention(bool tensor_cores, const void *bf16_queries, const void
     }
     // One (maximum, sum) pair per score row: scratch of the two-kernel path, kept for the
     // library's life and grown when a call needs more (cudaFree waits for the device first).
-    static float2 *stats = nullptr;
-    static long long stats_rows = 0;
-    static float *partials = nullptr;
-    static size_t partial_bytes = 0;
-    static int *request_chunks = nullptr;       // [1024]: chunk counts of the last chunked call
+    float2 *&stats = scratch_slot->stats;
+    long long &stats_rows = scratch_slot->stats_rows;
+    float *&partials = scratch_slot->partials;
+    size_t &partial_bytes = scratch_slot->partial_bytes;
+    int *&request_chunks = scratch_slot->request_chunks;
     if (request_chunks == nullptr &&
         check_cuda(cudaMalloc(&request_chunks, sizeof(int) * 1024), "allocate chunk counts") != 0)
       return -100;

@@ -12,14 +12,13 @@
 // accumulator with tcgen05.ld. Weights are read exactly once with an evict-first policy; the
 // activation matrix is re-read from L2 by every tile with an evict-last policy.
 #include "fp8_linear.cuh"
+#include "context.cuh"
 #include "launch.cuh"
 #include "linear_items.cuh"
 #include "ptx.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
-
-#include <mutex>
 
 namespace carat_b200 {
 namespace {
@@ -99,6 +98,7 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
   __shared__ __align__(8) unsigned long long barriers[2 * stages + 4];
   __shared__ uint32_t tmem_base_slot;
   __shared__ unsigned long long row_best[mode == 2 ? padded_rows : 1];
+  __shared__ int epilogue_gave_up;   // mode 2: set by an epilogue warp whose wait ran out
 
   const uint32_t tiles_base = (ptx::smem_u32(shared_raw) + 1023U) & ~1023U;
   const uint32_t weight_tiles = tiles_base;
@@ -132,6 +132,8 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
     for (int row = static_cast<int>(threadIdx.x); row < padded_rows; row += linear_threads)
       row_best[row] = 0ULL;
   }
+  if (threadIdx.x == 0)
+    epilogue_gave_up = 0;
   if (warp == 1) {
     ptx::tmem_alloc(ptx::smem_u32(&tmem_base_slot), tmem_columns);
     ptx::tmem_relinquish_alloc_permit();
@@ -271,10 +273,20 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
       const bool ready =
           __all_sync(0xFFFFFFFFU,
                      ptx::mbarrier_wait_bounded(acc_full_bar + 8U * buffer, use & 1U) ? 1 : 0) != 0;
-      if (!ready) {
-        if (lane == 0)
-          atomicExch(args.device_error, 3);
-        break;
+      if (!ready && lane == 0) {
+        atomicExch(args.device_error, 3);
+        epilogue_gave_up = 1;
+      }
+      if constexpr (mode == 2) {
+        // The four epilogue warps meet at a named barrier further down, so they must leave the
+        // loop together: each one's wait is bounded, all reach this barrier, and all read the
+        // same flag after it.
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*reinterpret_cast<volatile int *>(&epilogue_gave_up) != 0)
+          break;
+      } else {
+        if (!ready)
+          break;
       }
       ptx::tcgen05_fence_after_thread_sync();
       const int feature = item.tile * tile_features + quarter * 32 + lane;
@@ -438,15 +450,13 @@ template <int padded_rows, int mode>
 int launch_variant(const LinearPlan &plan, const KernelArguments &arguments, cudaStream_t stream) {
   constexpr int stages = stages_for(padded_rows);
   constexpr int dynamic_bytes = stages * (weight_tile_bytes + padded_rows * tile_k_bytes) + 1024;
-  static std::once_flag configured;
-  static cudaError_t configure_status = cudaSuccess;
-  std::call_once(configured, [] {
-    configure_status = cudaFuncSetAttribute(fp8_linear_kernel<padded_rows, mode>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            dynamic_bytes);
-  });
-  if (configure_status != cudaSuccess)
+  static PerDeviceOnce configured;
+  if (configured.run([] {
+        return cudaFuncSetAttribute(fp8_linear_kernel<padded_rows, mode>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, dynamic_bytes);
+      }) != cudaSuccess) {
     return -10;
+  }
   const int items = (plan.tiles - arguments.tail_tiles) * arguments.splits +
                     arguments.tail_tiles * arguments.tail_splits;
   const int ctas = items < plan.ctas ? items : plan.ctas;

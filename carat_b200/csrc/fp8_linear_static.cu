@@ -1,11 +1,11 @@
 // FP8 linear for callers that must not allocate device memory.
 //
-// Some hosts of this library cannot call cudaMalloc at the point where they need a linear: code
-// running inside a CUDA-graph capture or a latency-critical serving loop whose allocator is
-// frozen, and plugins that are handed a fixed memory budget by their framework and are forbidden
-// to grow it. carat_b200_fp8_linear needs a caller-provided workspace for its split-K partial
-// sums; this variant keeps that workspace in a fixed array inside the library image instead, so
-// the caller passes inputs and outputs only and the call performs no allocation of any kind.
+// Some hosts of this library cannot call cudaMalloc at the point where they need a linear: a
+// latency-critical serving loop whose allocator is frozen once the model is loaded, and plugins
+// that are handed a fixed memory budget by their framework and are forbidden to grow it.
+// carat_b200_fp8_linear needs a caller-provided workspace for its split-K partial sums; this
+// variant keeps that workspace in a fixed array inside the library image instead, so the caller
+// passes inputs and outputs only and the call performs no allocation of any kind.
 #include "../../include/carat_b200.h"
 #include "context.cuh"
 #include "fp8_linear.cuh"
@@ -22,11 +22,10 @@ constexpr size_t static_partial_floats = 2U * 1024U * 1024U;
 
 static __device__ __align__(256) float static_partials[static_partial_floats];
 // The kernels record here when one of their bounded waits runs out (0 = healthy). Kept inside the
-// image for the same reason as the partial sums; this entry point does not read it back, because
-// doing so would synchronise the device.
+// image for the same reason as the partial sums. The launch path never reads it back (that would
+// synchronise the device); carat_b200_device_error() reads and clears it together with the
+// library's other error word.
 static __device__ __align__(256) int static_error_word[64];
-
-constexpr int maximum_devices = 64;
 
 struct DeviceScratch {
   float *partials{nullptr};
@@ -65,6 +64,7 @@ int scratch_for_current_device(DeviceScratch *result) {
     entry.partials = static_cast<float *>(partials);
     entry.error_word = static_cast<int *>(error_word);
     entry.ready = true;
+    register_extra_error_word(entry.error_word);
   }
   *result = entry;
   return 0;

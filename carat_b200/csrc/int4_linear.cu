@@ -524,15 +524,13 @@ int launch_variant(const Int4LinearPlan &plan, const KernelArguments &arguments,
                    cudaStream_t stream) {
   constexpr int dynamic_bytes = Layout<padded_rows>::dynamic_bytes;
   static_assert(dynamic_bytes <= 227 * 1024, "shared memory budget");
-  static std::once_flag configured;
-  static cudaError_t configure_status = cudaSuccess;
-  std::call_once(configured, [] {
-    configure_status = cudaFuncSetAttribute(int4_linear_kernel<padded_rows, mode>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            dynamic_bytes);
-  });
-  if (configure_status != cudaSuccess)
+  static PerDeviceOnce configured;
+  if (configured.run([] {
+        return cudaFuncSetAttribute(int4_linear_kernel<padded_rows, mode>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, dynamic_bytes);
+      }) != cudaSuccess) {
     return -10;
+  }
   const LinearPlan &schedule = plan.schedule;
   const int items = (schedule.tiles - arguments.tail_tiles) * arguments.splits +
                     arguments.tail_tiles * arguments.tail_splits;

@@ -3,6 +3,7 @@
 // schedule that picks split-K factors and the K-cut tail round.
 #pragma once
 
+#include "context.cuh"
 #include "fp8_linear.cuh"
 
 #include <cuda.h>
@@ -89,20 +90,6 @@ inline EncodeTiled encode_tiled_entry() {
   return entry;
 }
 
-inline int multiprocessor_count() {
-  static int count = [] {
-    int device = 0;
-    int value = 0;
-    if (cudaGetDevice(&device) != cudaSuccess ||
-        cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
-        value <= 0) {
-      return 148;
-    }
-    return value;
-  }();
-  return count;
-}
-
 inline void schedule_linear(LinearPlan *plan, int rows, int input_width, int output_width,
                      int requested_splits) {
   LinearPlan &result = *plan;
@@ -112,7 +99,7 @@ inline void schedule_linear(LinearPlan *plan, int rows, int input_width, int out
   result.padded_rows = rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
   result.tiles = (output_width + tile_features - 1) / tile_features;
   result.k_blocks = (input_width + tile_k_elements - 1) / tile_k_elements;
-  result.ctas = multiprocessor_count();
+  result.ctas = device_multiprocessors();
   int splits = requested_splits;
   if (splits <= 0) {
     // Fewer tiles than SMs: cut K so that most SMs stream; keep at least four K blocks a piece.

@@ -56,7 +56,8 @@ __device__ __forceinline__ bool mbarrier_try_wait(uint32_t bar, uint32_t parity)
 // returns control to the host with an error word instead of hanging the device.
 constexpr long long wait_cycle_limit = 4000000000LL;
 
-__device__ __forceinline__ bool mbarrier_wait_bounded(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbarrier_wait_bounded(uint32_t bar, uint32_t parity,
+                                                      long long cycle_limit = wait_cycle_limit) {
   if (mbarrier_try_wait(bar, parity))
     return true;
   const long long start = clock64();
@@ -66,7 +67,7 @@ __device__ __forceinline__ bool mbarrier_wait_bounded(uint32_t bar, uint32_t par
       if (mbarrier_try_wait(bar, parity))
         return true;
     }
-    if (clock64() - start > wait_cycle_limit)
+    if (clock64() - start > cycle_limit)
       return false;
   }
 }
@@ -85,12 +86,13 @@ __device__ __forceinline__ bool mbarrier_wait_fast(uint32_t bar, uint32_t parity
 // completed) costs a single try_wait.
 __device__ __forceinline__ bool mbarrier_wait_checked(uint32_t bar, uint32_t parity,
                                                       volatile int *abort_flag, int *device_error,
-                                                      int code) {
+                                                      int code,
+                                                      long long cycle_limit = wait_cycle_limit) {
   if (mbarrier_try_wait(bar, parity))
     return true;
   if (*abort_flag != 0)
     return false;
-  if (mbarrier_wait_bounded(bar, parity))
+  if (mbarrier_wait_bounded(bar, parity, cycle_limit))
     return true;
   *abort_flag = 1;
   atomicExch(device_error, code);

@@ -1,5 +1,6 @@
 #include "row_ops.cuh"
 
+#include "context.cuh"
 #include "launch.cuh"
 
 #include <cooperative_groups.h>
@@ -245,12 +246,14 @@ row_kernel(RowArguments a) {
   grid_dependency_wait();
 
   if constexpr (mode == RowMode::embed_norm && !two_launches) {
-    // The per-step scratch words must be zero before the first atomic maximum of the step; the
-    // barrier below orders this against every later use, including this kernel's own.
-    for (int word = static_cast<int>(blockIdx.x) * row_threads + static_cast<int>(threadIdx.x);
-         word < a.clear_words; word += static_cast<int>(gridDim.x) * row_threads)
-      a.clear_base[word] = 0U;
-    cg::this_grid().sync();
+    // When asked to, clear the per-step scratch words before the first atomic maximum of the
+    // step; the barrier orders this against every later use, including this kernel's own.
+    if (a.clear_words > 0) {
+      for (int word = static_cast<int>(blockIdx.x) * row_threads + static_cast<int>(threadIdx.x);
+           word < a.clear_words; word += static_cast<int>(gridDim.x) * row_threads)
+        a.clear_base[word] = 0U;
+      cg::this_grid().sync();
+    }
   }
 
   float partial_scale = 1.0F;
@@ -519,22 +522,26 @@ __global__ void quantize_rows_kernel(const __nv_bfloat16 *rows, const unsigned i
 // buffer was given.
 template <RowMode mode, int chunks>
 int launch_rows_chunks(const RowArguments &arguments, int ctas, cudaStream_t stream) {
-  static int resident_limit = -1;
-  static cudaError_t configure_status = cudaSuccess;
-  if (resident_limit < 0) {
-    int device = 0;
-    int multiprocessors = 0;
-    int per_multiprocessor = 0;
-    configure_status = cudaGetDevice(&device);
-    if (configure_status == cudaSuccess)
-      configure_status =
-          cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device);
-    if (configure_status == cudaSuccess)
-      configure_status = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-          &per_multiprocessor, row_kernel<mode, chunks, false>, row_threads, 0);
-    resident_limit = configure_status == cudaSuccess ? multiprocessors * per_multiprocessor : 0;
+  // CTAs of this variant the current device holds at once (the grid barrier needs them all).
+  static PerDevice<int> resident_limits;
+  int resident_limit = 0;
+  {
+    int *slot = resident_limits.slot();
+    if (slot == nullptr)
+      return -10;
+    std::lock_guard<std::mutex> lock(resident_limits.lock());
+    if (*slot <= 0) {
+      int per_multiprocessor = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+              &per_multiprocessor, row_kernel<mode, chunks, false>, row_threads, 0) !=
+          cudaSuccess) {
+        return -10;
+      }
+      *slot = device_multiprocessors() * per_multiprocessor;
+    }
+    resident_limit = *slot;
   }
-  if (configure_status != cudaSuccess)
+  if (resident_limit <= 0)
     return -10;
   if (arguments.fp8_output == nullptr) {
     // No quantisation, so no grid barrier: any number of CTAs, plain launch.

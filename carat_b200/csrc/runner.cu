@@ -29,7 +29,6 @@ namespace {
 constexpr int maximum_depth = 9;       // k = 8 drafts + the forced token
 constexpr int maximum_rows = 256;      // rows one FP8 linear launch accepts (24 slots x depth 9 = 216)
 constexpr int global_chunk_keys = 1024;
-constexpr int resident_row_limit = 128;  // above this the step clears its scratch words up front
 
 struct Failure {
   std::string message;
@@ -148,7 +147,6 @@ struct carat_b200_runner {
   std::vector<carat_b200_layer_weights> assistant_layers;
   // ---- state
   std::vector<int> slot_positions;
-  DeviceBuffer device_slot_positions;
   DeviceBuffer hidden_by_slot;
   cudaStream_t stream{nullptr};
   cudaEvent_t start_event{nullptr};
@@ -333,7 +331,6 @@ void build_runner(Runner &runner, const carat_b200_model_config &config,
   }
 
   runner.slot_positions.assign(static_cast<size_t>(batch), 0);
-  runner.device_slot_positions.allocate(sizeof(int) * batch, true);
   runner.hidden_by_slot.allocate(static_cast<size_t>(batch) * hidden * 2, true);
   const size_t row_hidden = static_cast<size_t>(rows) * hidden * 2;
   runner.hidden_a.allocate(row_hidden);
@@ -654,19 +651,17 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
   const auto bf16_target = [](void *rows_out) {
     return QuantTarget{nullptr, nullptr, nullptr, nullptr, rows_out};
   };
-  // More rows than the device holds row-kernel CTAs: the row kernels run in their two-launch
-  // form, whose first kernel does not clear the scratch words itself.
-  if (rows > resident_row_limit)
-    require_cuda(cudaMemsetAsync(amax, 0, sizeof(int) * (runner.amax_words + 2 * maximum_rows),
-                                 stream),
-                 "clear step scratch");
+  // The running maxima and the packed argmax keys must be zero before the step's first atomic.
+  require_cuda(cudaMemsetAsync(amax, 0, sizeof(int) * (runner.amax_words + 2 * maximum_rows),
+                               stream),
+               "clear step scratch");
 
   void *current = runner.hidden_a.get();
   void *other = runner.hidden_b.get();
   require_launch(launch_embed_norm_quant(runner.weights.token_embedding, device.tokens,
                                          config.vocabulary_size, runner.layers[0].weights.input_norm,
-                                         current, target(0), rows, hidden, epsilon, amax,
-                                         runner.amax_words + 2 * maximum_rows, stream),
+                                         current, target(0), rows, hidden, epsilon, nullptr, 0,
+                                         stream),
                  "embedding and input norm");
   runner.launches += 1;
 
@@ -891,7 +886,6 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
   accept.final_hidden = runner.final_hidden.get();
   accept.hidden_by_slot = runner.hidden_by_slot.get();
   accept.slots = device.slots;
-  accept.slot_positions = runner.device_slot_positions.get<int>();
   accept.requests = requests;
   accept.depth = depth;
   accept.hidden = hidden;
@@ -1278,10 +1272,6 @@ extern "C" int carat_b200_runner_reset_slot(carat_b200_runner *runner, int slot)
     if (runner == nullptr || slot < 0 || slot >= runner->batch)
       throw Failure{"invalid slot"};
     runner->slot_positions[static_cast<size_t>(slot)] = 0;
-    require_cuda(cudaMemsetAsync(runner->device_slot_positions.get<int>() + slot, 0, sizeof(int),
-                                 runner->stream),
-                 "reset slot position");
-    require_cuda(cudaStreamSynchronize(runner->stream), "reset slot");
   });
 }
 
@@ -1320,10 +1310,6 @@ extern "C" int carat_b200_runner_clone_slot(carat_b200_runner *runner, int sourc
                      hidden_bytes, cudaMemcpyDeviceToDevice, runner->stream),
                  "clone slot target hidden state");
     runner->slot_positions[static_cast<size_t>(destination_slot)] = position;
-    require_cuda(cudaMemcpyAsync(runner->device_slot_positions.get<int>() + destination_slot,
-                                 &runner->slot_positions[static_cast<size_t>(destination_slot)],
-                                 sizeof(int), cudaMemcpyHostToDevice, runner->stream),
-                 "clone slot position");
     require_cuda(cudaStreamSynchronize(runner->stream), "synchronize slot cache clone");
     if (copied_bytes != nullptr)
       *copied_bytes = copied;
@@ -1339,10 +1325,6 @@ extern "C" int carat_b200_runner_seed_empty_cache_for_benchmark(carat_b200_runne
       require_cuda(cudaMemsetAsync(layer.kv.get(), 0, layer.kv.bytes(), runner->stream),
                    "clear KV arena");
     std::fill(runner->slot_positions.begin(), runner->slot_positions.end(), position);
-    require_cuda(cudaMemcpyAsync(runner->device_slot_positions.get(), runner->slot_positions.data(),
-                                 sizeof(int) * runner->batch, cudaMemcpyHostToDevice,
-                                 runner->stream),
-                 "seed slot positions");
     require_cuda(cudaStreamSynchronize(runner->stream), "seed benchmark cache");
   });
 }
@@ -1360,10 +1342,6 @@ extern "C" int carat_b200_runner_seed_slot_positions(carat_b200_runner *runner,
       require_cuda(cudaMemsetAsync(layer.kv.get(), 0, layer.kv.bytes(), runner->stream),
                    "clear KV arena");
     runner->slot_positions.assign(positions, positions + runner->batch);
-    require_cuda(cudaMemcpyAsync(runner->device_slot_positions.get(), runner->slot_positions.data(),
-                                 sizeof(int) * runner->batch, cudaMemcpyHostToDevice,
-                                 runner->stream),
-                 "seed slot positions");
     require_cuda(cudaStreamSynchronize(runner->stream), "seed benchmark cache");
   });
 }

@@ -40,6 +40,14 @@ CARAT_B200_API int carat_b200_abi_version(void);
  * (0 = healthy) and clears it. */
 CARAT_B200_API int carat_b200_device_error(int *code);
 
+/* Runs the bounded-wait error path once, harmlessly: one CTA waits about a millisecond on a
+ * barrier that nothing arrives on, gives up, records code 90 in the error word and ends normally.
+ * device_report receives three ints: 1 if the wait gave up, 1 if a second wait in the same CTA
+ * then returned at once (the CTA-wide give-up flag), and the cycles that second wait took.
+ * carat_b200_device_error() afterwards returns 90 once and 0 from then on. No counterpart in the
+ * reference (its kernels have no device-side waits to bound). */
+CARAT_B200_API int carat_b200_selftest_bounded_wait(int *device_report, void *stream);
+
 /* FP8 linear ---------------------------------------------------------------------------------- */
 
 /* output[rows, output_width] = bf16((input_scale * weight_scale) *
@@ -56,19 +64,24 @@ CARAT_B200_API int carat_b200_fp8_linear(const void *fp8_input, const float *dev
 
 CARAT_B200_API size_t carat_b200_fp8_linear_workspace_bytes(int rows, int input_width, int output_width);
 
-/* The same linear for callers that cannot allocate device memory (inside a stream capture, in a
- * serving loop whose allocator is frozen, or in a plugin with a fixed memory budget): the
- * split-K partial sums live in an 8 MiB array built into the library image, so no workspace is
- * passed and the call makes no cudaMalloc / cudaFree or other allocating call. This entry point
- * has no counterpart in the reference.
+/* The same linear for callers that cannot allocate device memory where they need it (a serving
+ * loop whose allocator is frozen once the model is loaded, a plugin with a fixed memory budget
+ * its host framework will not let it grow): the split-K partial sums live in an 8 MiB array built
+ * into the library image, so no workspace is passed and the call makes no cudaMalloc / cudaFree
+ * or other allocating call. This entry point has no counterpart in the reference.
  *  - Shapes whose split-K scratch (carat_b200_fp8_linear_workspace_bytes) exceeds
  *    CARAT_B200_STATIC_SCRATCH_BYTES are rejected with an error; use carat_b200_fp8_linear for
  *    those.
- *  - The first call on each device looks the array's device address up; make that first call
- *    outside any stream capture.
+ *  - The first call on each device looks the array's device address up, and the first call of
+ *    each shape class (row bucket 32 / 64 / 128 / 256, with or without split-K) configures its
+ *    kernel; under lazy module loading the very first call also makes the driver load the module
+ *    that holds the 8 MiB. Make those first calls during set-up, before any stream capture.
  *  - All calls on a device share the one array: calls that overlap on the GPU (different streams,
  *    no dependency) race on it. Nothing in it has to be zero between calls; every launch
- *    overwrites the part it reads. Every GPU that loads the library holds the array until exit. */
+ *    overwrites the part it reads. Every GPU that loads the library holds the array until exit.
+ *  - A bounded wait that runs out inside this entry point records its code in a word that lives
+ *    in the library image too; carat_b200_device_error() reports and clears it like the codes of
+ *    every other entry point. */
 #define CARAT_B200_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u)
 CARAT_B200_API int carat_b200_fp8_linear_static(const void *fp8_input,
                                                 const float *device_input_scale,

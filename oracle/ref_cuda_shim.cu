@@ -38,76 +38,7 @@
 
 namespace carat {
 
-// ---------------------------------------------------------------------------- pointer-table arenas
-// The reference only forward-declares these two classes in device_weights.h; defining them here
-// lets the factory functions below receive the test's tables through their declared signatures.
-class WeightPlan {
-public:
-  std::map<std::string, const void *, std::less<>> pointers;
-  std::map<std::string, const float *, std::less<>> scales;
-};
-class ShardedSafetensors {};
-
-struct DeviceWeightArena::Implementation {
-  std::map<std::string, const void *, std::less<>> pointers;
-};
-
-DeviceWeightArena::DeviceWeightArena(std::unique_ptr<Implementation> implementation)
-    : implementation_(std::move(implementation)) {}
-DeviceWeightArena::~DeviceWeightArena() = default;
-
-std::unique_ptr<DeviceWeightArena> DeviceWeightArena::load(const WeightPlan &plan,
-                                                           const ShardedSafetensors &,
-                                                           const std::vector<std::string> &) {
-  auto implementation = std::make_unique<Implementation>();
-  implementation->pointers = plan.pointers;
-  return std::unique_ptr<DeviceWeightArena>(new DeviceWeightArena(std::move(implementation)));
-}
-
-const void *DeviceWeightArena::at(std::string_view name) const {
-  const auto found = implementation_->pointers.find(name);
-  if (found == implementation_->pointers.end())
-    throw std::runtime_error("test arena has no BF16 segment " + std::string(name));
-  return found->second;
-}
-std::uint64_t DeviceWeightArena::allocated_bytes() const { return 0; }
-std::uint64_t DeviceWeightArena::payload_bytes() const { return 0; }
-
-struct Fp8WeightArena::Implementation {
-  std::map<std::string, const void *, std::less<>> pointers;
-  std::map<std::string, const float *, std::less<>> scales;
-};
-
-Fp8WeightArena::Fp8WeightArena(std::unique_ptr<Implementation> implementation)
-    : implementation_(std::move(implementation)) {}
-Fp8WeightArena::~Fp8WeightArena() = default;
-
-std::unique_ptr<Fp8WeightArena> Fp8WeightArena::quantize(const WeightPlan &plan,
-                                                         const DeviceWeightArena &, Fp8Scaling,
-                                                         float) {
-  auto implementation = std::make_unique<Implementation>();
-  implementation->pointers = plan.pointers;
-  implementation->scales = plan.scales;
-  return std::unique_ptr<Fp8WeightArena>(new Fp8WeightArena(std::move(implementation)));
-}
-
-const void *Fp8WeightArena::at(std::string_view name) const {
-  const auto found = implementation_->pointers.find(name);
-  if (found == implementation_->pointers.end())
-    throw std::runtime_error("test arena has no FP8 segment " + std::string(name));
-  return found->second;
-}
-const float *Fp8WeightArena::scale(std::string_view name) const {
-  const auto found = implementation_->scales.find(name);
-  if (found == implementation_->scales.end())
-    throw std::runtime_error("test arena has no FP8 scale " + std::string(name));
-  return found->second;
-}
-void Fp8WeightArena::roundtrip_int4(std::string_view, int, int, int, int) {
-  throw std::runtime_error("INT4 round trip is not part of the test oracle build");
-}
-Fp8Scaling Fp8WeightArena::scaling() const { return Fp8Scaling::tensor; }
-std::uint64_t Fp8WeightArena::allocated_bytes() const { return 0; }
+#include "ref_arenas.inc"
 
 // ---------------------------------------------------------------------------- placeholders
 struct CudnnPrefillAttention::Implementation {};
@@ -181,24 +112,11 @@ void quantize_grouped_global_decode_values_wgmma_int8(const void *, void *, floa
 } // namespace carat
 
 // ---------------------------------------------------------------------------- C face
+// Every call returns with the device drained, so a fault shows up at the call that caused it.
+#define REF_FACE_AFTER_CALL() cudaDeviceSynchronize()
+#include "ref_face_helpers.inc"
+
 namespace {
-
-thread_local std::string last_error;
-
-template <typename Body> int guarded(Body &&body) {
-  try {
-    body();
-    const cudaError_t status = cudaDeviceSynchronize();
-    if (status != cudaSuccess) {
-      last_error = std::string("CUDA: ") + cudaGetErrorString(status);
-      return -2;
-    }
-    return 0;
-  } catch (const std::exception &error) {
-    last_error = error.what();
-    return -1;
-  }
-}
 
 carat::Fp8Linear &fp8_linear() {
   static carat::Fp8Linear linear(carat::Fp8Scaling::tensor);
@@ -503,163 +421,7 @@ int ref_decode_attention_run_ragged(int maximum_batch, int maximum_kv_heads, int
   });
 }
 
-// ---------------------------------------------------------------------------- whole runner
-struct ref_segment {
-  const char *name;
-  const void *pointer;
-  const float *scale;  // FP8 tables only
-};
-
-struct ref_layer {
-  int global_attention;
-  int query_heads;
-  int kv_heads;
-  int head_dimension;
-  int rotary_dimension;
-  double rope_theta;
-  int key_equals_value;
-};
-
-struct ref_runner {
-  carat::Gemma4Config config;
-  std::unique_ptr<carat::DeviceWeightArena> weights;
-  std::unique_ptr<carat::Fp8WeightArena> fp8;
-  std::unique_ptr<carat::DeviceWeightArena> assistant_weights;
-  std::unique_ptr<carat::Fp8WeightArena> assistant_fp8;
-  std::unique_ptr<carat::Gemma4BatchModelRunner> runner;
-};
-
-static carat::WeightPlan table_of(const ref_segment *segments, int count) {
-  carat::WeightPlan plan;
-  for (int index = 0; index < count; ++index) {
-    plan.pointers[segments[index].name] = segments[index].pointer;
-    if (segments[index].scale != nullptr)
-      plan.scales[segments[index].name] = segments[index].scale;
-  }
-  return plan;
-}
-
-// carat::Gemma4BatchModelRunner constructor (include/carat/batch_model_runner.h:24-28).
-ref_runner *ref_runner_create(int hidden, int intermediate, int vocabulary, int sliding_window,
-                              int maximum_positions, double epsilon, const ref_layer *layers,
-                              int layer_count, const ref_segment *bf16, int bf16_count,
-                              const ref_segment *fp8, int fp8_count, int batch,
-                              int maximum_context, const ref_segment *assistant_bf16,
-                              int assistant_bf16_count, const ref_segment *assistant_fp8,
-                              int assistant_fp8_count) {
-  try {
-    auto made = std::make_unique<ref_runner>();
-    made->config.hidden_size = static_cast<std::uint32_t>(hidden);
-    made->config.intermediate_size = static_cast<std::uint32_t>(intermediate);
-    made->config.vocabulary_size = static_cast<std::uint32_t>(vocabulary);
-    made->config.sliding_window = static_cast<std::uint32_t>(sliding_window);
-    made->config.maximum_positions = static_cast<std::uint32_t>(maximum_positions);
-    made->config.rms_norm_epsilon = epsilon;
-    made->config.final_logit_softcap = 30.0;
-    for (int index = 0; index < layer_count; ++index) {
-      carat::Gemma4LayerConfig layer{};
-      layer.attention = layers[index].global_attention ? carat::AttentionKind::global
-                                                        : carat::AttentionKind::sliding;
-      layer.query_heads = static_cast<std::uint32_t>(layers[index].query_heads);
-      layer.kv_heads = static_cast<std::uint32_t>(layers[index].kv_heads);
-      layer.head_dimension = static_cast<std::uint32_t>(layers[index].head_dimension);
-      layer.rotary_dimension = static_cast<std::uint32_t>(layers[index].rotary_dimension);
-      layer.rope_theta = layers[index].rope_theta;
-      layer.key_equals_value = layers[index].key_equals_value != 0;
-      made->config.layers.push_back(layer);
-    }
-    const carat::ShardedSafetensors none;
-    const carat::WeightPlan bf16_table = table_of(bf16, bf16_count);
-    made->weights = carat::DeviceWeightArena::load(bf16_table, none);
-    if (fp8 != nullptr && fp8_count > 0) {
-      made->fp8 = carat::Fp8WeightArena::quantize(table_of(fp8, fp8_count), *made->weights,
-                                                  carat::Fp8Scaling::tensor);
-    }
-    if (assistant_bf16 != nullptr && assistant_bf16_count > 0) {
-      made->assistant_weights =
-          carat::DeviceWeightArena::load(table_of(assistant_bf16, assistant_bf16_count), none);
-      if (assistant_fp8 != nullptr && assistant_fp8_count > 0) {
-        made->assistant_fp8 = carat::Fp8WeightArena::quantize(
-            table_of(assistant_fp8, assistant_fp8_count), *made->assistant_weights,
-            carat::Fp8Scaling::tensor);
-      }
-    }
-    made->runner = std::make_unique<carat::Gemma4BatchModelRunner>(
-        made->config, *made->weights, batch, maximum_context, made->fp8.get(),
-        made->assistant_weights.get(), made->assistant_fp8.get());
-    return made.release();
-  } catch (const std::exception &error) {
-    last_error = error.what();
-    return nullptr;
-  }
-}
-
-void ref_runner_destroy(ref_runner *runner) { delete runner; }
-
-int ref_runner_verify_greedy_proposals(ref_runner *runner, const int *proposals, int requests,
-                                       int depth, const int *target_first, const int *slots,
-                                       const int *caps, int *accepted, int *next_tokens) {
-  return guarded([&] {
-    std::vector<std::vector<int>> rows(static_cast<size_t>(requests));
-    for (int request = 0; request < requests; ++request)
-      rows[static_cast<size_t>(request)].assign(proposals + request * depth,
-                                                proposals + (request + 1) * depth);
-    const std::vector<int> first(target_first, target_first + requests);
-    const std::vector<int> slot_list(slots, slots + requests);
-    const std::vector<int> cap_list =
-        caps == nullptr ? std::vector<int>{} : std::vector<int>(caps, caps + requests);
-    const carat::GreedyVerificationResult result =
-        runner->runner->verify_greedy_proposals(rows, first, slot_list, cap_list);
-    std::memcpy(accepted, result.accepted_tokens.data(), sizeof(int) * requests);
-    std::memcpy(next_tokens, result.next_tokens.data(), sizeof(int) * requests);
-  });
-}
-
-int ref_runner_draft_four(ref_runner *runner, const int *last_tokens, const int *slots,
-                          const int *forced_first, int requests, int depth, int *proposals) {
-  return guarded([&] {
-    const std::vector<int> last(last_tokens, last_tokens + requests);
-    const std::vector<int> slot_list(slots, slots + requests);
-    const std::vector<int> forced = forced_first == nullptr
-                                        ? std::vector<int>{}
-                                        : std::vector<int>(forced_first, forced_first + requests);
-    const auto drafted = runner->runner->draft_four(last, slot_list, forced, depth);
-    for (int request = 0; request < requests; ++request)
-      std::memcpy(proposals + request * depth, drafted[static_cast<size_t>(request)].data(),
-                  sizeof(int) * depth);
-  });
-}
-
-int ref_runner_append_ragged(ref_runner *runner, const int *tokens, const int *slots, int count,
-                             int *next_tokens) {
-  return guarded([&] {
-    const std::vector<int> token_list(tokens, tokens + count);
-    const std::vector<int> slot_list(slots, slots + count);
-    const std::vector<int> result = runner->runner->append_ragged(token_list, slot_list);
-    std::memcpy(next_tokens, result.data(), sizeof(int) * count);
-  });
-}
-
-int ref_runner_clone_slot(ref_runner *runner, int source, int destination,
-                          unsigned long long *bytes) {
-  return guarded([&] {
-    const std::uint64_t copied = runner->runner->clone_slot(source, destination);
-    if (bytes != nullptr)
-      *bytes = copied;
-  });
-}
-
-int ref_runner_reset_slot(ref_runner *runner, int slot) {
-  return guarded([&] { runner->runner->reset_slot(slot); });
-}
-
-int ref_runner_seed_empty_cache_for_benchmark(ref_runner *runner, int position) {
-  return guarded([&] { runner->runner->seed_empty_cache_for_benchmark(position); });
-}
-
-int ref_runner_slot_position(ref_runner *runner, int slot, int *position) {
-  return guarded([&] { *position = runner->runner->slot_position(slot); });
-}
+#include "ref_runner_face.inc"
 
 // ---- carat::Gemma4AssistantRunner on its own (include/carat/assistant_runner.h:11-32): the
 // caller supplies the target embedding, the hidden-by-slot table and the two shared KV layers as

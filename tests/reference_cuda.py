@@ -12,6 +12,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIBRARY_PATH = os.path.join(ROOT, "oracle", "_ref", "libref_cuda.so")
+SHIM_LIBRARY_PATH = os.path.join(ROOT, "oracle", "_ref", "libshim_runner.so")
 
 _P, _I, _F = c_void_p, c_int, c_float
 
@@ -84,7 +85,29 @@ SIGNATURES = {
                                       POINTER(c_int)]),
 }
 
+RUNNER_FACE = ("ref_last_error", "ref_runner_create", "ref_runner_destroy",
+               "ref_runner_verify_greedy_proposals", "ref_runner_draft_four",
+               "ref_runner_append_ragged", "ref_runner_clone_slot", "ref_runner_reset_slot",
+               "ref_runner_seed_empty_cache_for_benchmark", "ref_runner_slot_position")
+
 _library = None
+_shim_library = None
+
+
+def shim_library() -> ctypes.CDLL:
+    """oracle/_ref/libshim_runner.so: this repository's drop-in C++ Gemma4BatchModelRunner
+    (carat_b200/shim/) compiled against the reference's headers, behind the same C face."""
+    global _shim_library
+    if _shim_library is None:
+        if not os.path.exists(SHIM_LIBRARY_PATH):
+            pytest.skip("oracle/_ref/libshim_runner.so is not built (make -C oracle shim "
+                        "REFERENCE=<carat checkout>)")
+        loaded = ctypes.CDLL(SHIM_LIBRARY_PATH, mode=os.RTLD_NOW)
+        for name in RUNNER_FACE:
+            function = getattr(loaded, name)
+            function.restype, function.argtypes = SIGNATURES[name]
+        _shim_library = loaded
+    return _shim_library
 
 
 def available() -> bool:
@@ -111,9 +134,9 @@ class ReferenceError_(RuntimeError):
     """The reference threw; the text is its exception message."""
 
 
-def check(status: int) -> None:
+def check(status: int, loaded=None) -> None:
     if status != 0:
-        message = library().ref_last_error()
+        message = (loaded or library()).ref_last_error()
         raise ReferenceError_(message.decode() if message else f"reference call failed ({status})")
 
 
@@ -138,8 +161,10 @@ class ReferenceRunner:
     test owns through the reference's own arena interface."""
 
     def __init__(self, config, bf16, fp8, fp8_scales, batch, maximum_context, assistant_bf16=None,
-                 assistant_fp8=None, assistant_fp8_scales=None):
-        self._library = library()
+                 assistant_fp8=None, assistant_fp8_scales=None, loaded=None):
+        # `loaded` selects the implementation of the class behind the face: the reference's own
+        # (default) or this repository's C++ shim (shim_library()).
+        self._library = loaded or library()
         self._keep = (bf16, fp8, fp8_scales, assistant_bf16, assistant_fp8, assistant_fp8_scales)
         layers = (Layer * len(config.layers))()
         for index, layer in enumerate(config.layers):
@@ -169,6 +194,9 @@ class ReferenceRunner:
         if not self._handle:
             raise ReferenceError_(self._library.ref_last_error().decode())
 
+    def _check(self, status):
+        check(status, self._library)
+
     def close(self):
         if self._handle:
             self._library.ref_runner_destroy(self._handle)
@@ -182,7 +210,7 @@ class ReferenceRunner:
         flat = ints(token for row in proposals for token in row)
         accepted = (c_int * requests)()
         following = (c_int * requests)()
-        check(self._library.ref_runner_verify_greedy_proposals(
+        self._check(self._library.ref_runner_verify_greedy_proposals(
             self._handle, flat, requests, depth, ints(target_first), ints(slots),
             ints(caps) if caps is not None else None, accepted, following))
         return list(accepted), list(following)
@@ -190,32 +218,32 @@ class ReferenceRunner:
     def draft_four(self, last_tokens, slots, forced=None, depth=4):
         requests = len(last_tokens)
         out = (c_int * (requests * depth))()
-        check(self._library.ref_runner_draft_four(
+        self._check(self._library.ref_runner_draft_four(
             self._handle, ints(last_tokens), ints(slots),
             ints(forced) if forced is not None else None, requests, depth, out))
         return [list(out[row * depth:(row + 1) * depth]) for row in range(requests)]
 
     def append_ragged(self, tokens, slots):
         out = (c_int * len(tokens))()
-        check(self._library.ref_runner_append_ragged(self._handle, ints(tokens), ints(slots),
+        self._check(self._library.ref_runner_append_ragged(self._handle, ints(tokens), ints(slots),
                                                      len(tokens), out))
         return list(out)
 
     def clone_slot(self, source, destination):
         copied = ctypes.c_ulonglong(0)
-        check(self._library.ref_runner_clone_slot(self._handle, source, destination,
+        self._check(self._library.ref_runner_clone_slot(self._handle, source, destination,
                                                   ctypes.byref(copied)))
         return copied.value
 
     def reset_slot(self, slot):
-        check(self._library.ref_runner_reset_slot(self._handle, slot))
+        self._check(self._library.ref_runner_reset_slot(self._handle, slot))
 
     def seed_empty_cache_for_benchmark(self, position):
-        check(self._library.ref_runner_seed_empty_cache_for_benchmark(self._handle, position))
+        self._check(self._library.ref_runner_seed_empty_cache_for_benchmark(self._handle, position))
 
     def slot_position(self, slot):
         value = c_int(0)
-        check(self._library.ref_runner_slot_position(self._handle, slot, ctypes.byref(value)))
+        self._check(self._library.ref_runner_slot_position(self._handle, slot, ctypes.byref(value)))
         return value.value
 
 

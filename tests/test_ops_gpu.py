@@ -410,3 +410,27 @@ def test_greedy_prefix_accept_matches_oracle(cuda_device):
     torch.cuda.synchronize()
     assert accepted.cpu().tolist() == want[0]
     assert nxt.cpu().tolist() == want[1]
+
+
+def test_a_wait_that_runs_out_reports_a_code_and_leaves_the_device_usable(cuda_device):
+    """The bounded-wait path of the pipelined kernels, exercised without breaking any of them: a
+    test-only kernel waits about a millisecond on a barrier nothing arrives on."""
+    lib = carat_b200.library()
+    code = ctypes.c_int(-1)
+    check(lib.carat_b200_device_error(ctypes.byref(code)))          # start from a clean word
+    report = torch.full((3,), -1, dtype=torch.int32, device="cuda")
+    check(lib.carat_b200_selftest_bounded_wait(ptr(report), None))
+    torch.cuda.synchronize()
+    gave_up, second_returned_at_once, cycles = report.cpu().tolist()
+    assert gave_up == 1 and second_returned_at_once == 1, (gave_up, second_returned_at_once, cycles)
+    check(lib.carat_b200_device_error(ctypes.byref(code)))
+    assert code.value == 90
+    check(lib.carat_b200_device_error(ctypes.byref(code)))
+    assert code.value == 0                                           # cleared by the read
+    # The context is intact: an ordinary operator still runs and is still exact.
+    x = cs.bf16(torch.randn(5, 256, generator=torch.Generator().manual_seed(1)))
+    out, scale, scratch = quant_buffers(5, 256)
+    check(lib.carat_b200_quantize_bf16_to_fp8(ptr(dev(x)), ptr(out), ptr(scale), ptr(scratch), 5,
+                                              256, None))
+    torch.cuda.synchronize()
+    assert_quantised(out, scale, x)

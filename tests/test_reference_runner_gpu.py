@@ -361,6 +361,45 @@ def test_depth_eight_wrapped(pair):
     assert ties.relative <= 4
 
 
+def test_drop_in_cpp_shim_runs_the_same_step(pair):
+    """carat_b200/shim/batch_model_runner_shim.cpp, compiled against the reference's own headers
+    and linked to libcarat_b200.so, driven through the reference's class interface: it must give
+    exactly what the Python mirror of the same C ABI gives (same kernels, same calls) and what the
+    reference's runner gives."""
+    shim = ref.ReferenceRunner(
+        pair.config, pair.weights.tensors, pair.fp8.bytes, pair.fp8.scales, SLOTS, MAX_CONTEXT,
+        pair.assistant_weights.tensors, pair.assistant_fp8.bytes, pair.assistant_fp8.scales,
+        loaded=ref.shim_library())
+    try:
+        pair.seed(1100)
+        shim.seed_empty_cache_for_benchmark(1100)
+        generator = torch.Generator().manual_seed(77)
+        live = list(range(LIVE))
+        first = torch.randint(3, VOCABULARY, (LIVE,), generator=generator).tolist()
+        for step in range(4):
+            proposals = [[first[row]] + torch.randint(3, VOCABULARY, (4,),
+                                                      generator=generator).tolist()
+                         for row in range(LIVE)]
+            caps = torch.randint(1, 6, (LIVE,), generator=generator).tolist()
+            mine = pair.ours.verify_greedy_proposals(proposals, first, live, caps)
+            through_shim = shim.verify_greedy_proposals(proposals, first, live, caps)
+            reference = pair.theirs.verify_greedy_proposals(proposals, first, live, caps)
+            assert through_shim == (mine.accepted_tokens, mine.next_tokens) == reference
+            first = list(reference[1])
+            last = [proposals[row][reference[0][row] - 1] for row in range(LIVE)]
+            assert shim.draft_four(last, live, first, 5) == pair.ours.draft_four(last, live, first, 5)
+            for slot in live:
+                assert shim.slot_position(slot) == pair.ours.slot_position(slot)
+        assert shim.clone_slot(0, LIVE) == pair.ours.clone_slot(0, LIVE) == \
+            pair.theirs.clone_slot(0, LIVE)
+        assert shim.append_ragged(first[:2], [0, LIVE]) == \
+            pair.ours.append_ragged(first[:2], [0, LIVE])
+        with pytest.raises(ref.ReferenceError_, match="invalid or repeated speculative slot"):
+            shim.verify_greedy_proposals([[5, 6], [7, 8]], [5, 7], [3, 3])
+    finally:
+        shim.close()
+
+
 def test_plain_decode_matches(pair):
     """append_ragged on both sides (cuda/batch_model_runner.cu:1544-1615)."""
     pair.seed(40)

@@ -1,7 +1,8 @@
 """carat_b200_fp8_linear_static: the FP8 linear for hosts that may not allocate device memory
-(stream captures, frozen-allocator serving loops, fixed-budget plugins). Its split-K scratch is an
-array inside the library, so it must give exactly what carat_b200_fp8_linear gives with a
-caller-provided workspace, call after call, and must refuse shapes the array cannot hold.
+(frozen-allocator serving loops, fixed-budget plugins). Its split-K scratch is an array inside the
+library, so it must give exactly what carat_b200_fp8_linear gives with a caller-provided
+workspace, call after call, agree with the CPU oracle, allocate nothing, and refuse shapes the
+array cannot hold.
 
 This file is collected last on purpose: a run that stops at the first failure has then already run
 every other test.
@@ -14,6 +15,8 @@ import torch
 import carat_b200
 from carat_b200 import capi
 from carat_b200.capi import check
+from helpers import one_ulp_apart
+from oracle import carat_semantics as cs
 
 pytestmark = pytest.mark.gpu
 
@@ -42,12 +45,25 @@ def test_static_scratch_linear_matches_workspace_linear_twice(cuda_device):
         check(library.carat_b200_fp8_linear(ptr(activation), ptr(activation_scale), ptr(weight),
                                             ptr(weight_scale), ptr(want), rows, k, n,
                                             ptr(workspace), needed, None))
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         check(library.carat_b200_fp8_linear_static(ptr(activation), ptr(activation_scale),
                                                    ptr(weight), ptr(weight_scale), ptr(got), rows,
                                                    k, n, None))
         torch.cuda.synchronize()
+        if call == 1:
+            # Once warmed up the call leaves the device's free memory exactly where it was.
+            assert torch.cuda.mem_get_info()[0] == free_before
         assert torch.equal(got.view(torch.int16), want.view(torch.int16))   # bit-exact
         assert float(want.float().abs().max()) > 0.0
+        # And both agree with the CPU oracle's FP8 linear to one bf16 ulp.
+        oracle = cs.fp8_linear(activation.view(torch.float8_e4m3fn).float().cpu(),
+                               activation_scale.cpu(), weight.view(torch.float8_e4m3fn).float().cpu(),
+                               weight_scale.cpu())
+        assert one_ulp_apart(got.float().cpu(), oracle)
+        code = ctypes.c_int(-1)
+        check(library.carat_b200_device_error(ctypes.byref(code)))
+        assert code.value == 0                # no bounded wait ran out, in either error word
 
 
 def test_static_scratch_linear_without_split_and_oversize_rejection(cuda_device):
