@@ -554,7 +554,15 @@ def main():
                         help="also time the step with INT4 weight-only MLP linears (N = 1 only)")
     parser.add_argument("--skip-cpu", action="store_true",
                         help="leave the cpu_baseline object out (profiling runs)")
+    parser.add_argument("--case", nargs="+", metavar="WORD",
+                        help="run one small single-kernel workload instead (bench_cases.py): "
+                             "NAME [launches [K N [rows]]]")
     args = parser.parse_args()
+    if args.case:
+        import bench_cases
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        bench_cases.run_case(args.case)
+        return
     global DRAFTS, DEPTH
     DRAFTS = args.drafts
     DEPTH = DRAFTS + 1

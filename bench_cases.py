@@ -1,21 +1,23 @@
-"""Small, self-ending workloads for profiler captures (one kernel family each, a few launches,
-inputs larger than the 126 MB L2 but well under a few GB on the device).
+"""Small, self-ending single-kernel workloads of bench.py (`python bench.py --case NAME ...`): one
+kernel family each, a few launches, inputs larger than the 126 MB L2 but well under a few GB on
+the device, so a profiler capture of them ends by itself.
 
-    python -m carat_b200.profile_cases linear      # FP8 linear 120 x 5376 -> 43008 (231 MB weights)
-    python -m carat_b200.profile_cases int4        # INT4 weight-only linear, same shape (116 MB of codes)
-    python -m carat_b200.profile_cases lm_head     # fused LM head 120 x 5376 -> 262144 (1.4 GB)
-    python -m carat_b200.profile_cases attention   # sliding verify attention, 24 slots, full ring
-    python -m carat_b200.profile_cases global      # global verify attention, 24 slots, 4096 context
+    python bench.py --case linear      # FP8 linear 120 x 5376 -> 43008 (231 MB weights)
+    python bench.py --case int4        # INT4 weight-only linear, same shape (116 MB of codes)
+    python bench.py --case lm_head     # fused LM head 120 x 5376 -> 262144 (1.4 GB)
+    python bench.py --case attention   # sliding verify attention, 24 slots, full ring
+    python bench.py --case global      # global verify attention, 24 slots, 4096 context
+
+Optional numbers after the name: launches [K N [rows]].
 """
 from __future__ import annotations
 
 import ctypes
-import sys
 
 import torch
 
-from . import capi
-from .capi import check
+from carat_b200 import capi
+from carat_b200.capi import check
 
 
 def _ptr(tensor):
@@ -136,15 +138,18 @@ def global_attention(launches=3):
 
 CASES = {"linear": linear, "int4": int4, "lm_head": lm_head, "attention": attention, "global": global_attention}
 
-if __name__ == "__main__":
-    name = sys.argv[1] if len(sys.argv) > 1 else "linear"
-    if len(sys.argv) > 5:
-        CASES[name](launches=int(sys.argv[2]), k=int(sys.argv[3]), n=int(sys.argv[4]),
-                    rows=int(sys.argv[5]))
-    elif len(sys.argv) > 4:
-        CASES[name](launches=int(sys.argv[2]), k=int(sys.argv[3]), n=int(sys.argv[4]))
-    elif len(sys.argv) > 2:
-        CASES[name](launches=int(sys.argv[2]))
+
+
+def run_case(words):
+    """words = [name, launches, K, N, rows] (all but the name optional)."""
+    name = words[0] if words else "linear"
+    numbers = [int(word) for word in words[1:]]
+    if len(numbers) > 3:
+        CASES[name](launches=numbers[0], k=numbers[1], n=numbers[2], rows=numbers[3])
+    elif len(numbers) > 2:
+        CASES[name](launches=numbers[0], k=numbers[1], n=numbers[2])
+    elif len(numbers) > 0:
+        CASES[name](launches=numbers[0])
     else:
         CASES[name]()
-    print(f"profile case {name} done")
+    print(f"case {name} done")
