@@ -43,8 +43,10 @@ def workload_config(args):
     return {
         "workload": "configs[3] on one replica: 24 slots x 8192-token context, FP8 31B-shaped "
                     f"target + 4-layer 1024-wide FP8 drafter, k={DRAFTS} ({DEPTH} verify rows per slot), "
-                    "context lengths uniform in [128, 6144] (seeded), zero-filled KV, accept "
-                    "lengths injected from a seeded geometric distribution with mean 2.5",
+                    "context lengths uniform in [128, 6144] (seeded), KV caches filled with seeded "
+                    "random bf16 rows, accept lengths injected from a seeded geometric distribution "
+                    "with mean 2.5; a static snapshot of the request mix (no arrivals, prefill or "
+                    "slot turnover inside the timed region)",
         "slots": SLOTS, "drafts": DRAFTS, "verify_rows": SLOTS * DEPTH,
         "max_context": MAX_CONTEXT, "parallelism": f"replicas x{args.gpus}",
         "l2": "inputs (30.7 GB of weights + KV per step) exceed the 126 MB L2",
@@ -192,6 +194,21 @@ def build_model(seed):
     return config, runner, fp8
 
 
+def fill_kv(runner, config, seed):
+    """Seeded random bf16 rows in every K and V cache (unit variance, like normalised keys and
+    values): the step's work does not depend on the values, but power and clocks under real data
+    are not those of a zero-filled cache."""
+    generator = torch.Generator(device="cuda").manual_seed(seed)
+    for index, layer in enumerate(config.layers):
+        capacity = config.sliding_window if layer.attention == "sliding" else MAX_CONTEXT
+        shape = (SLOTS, layer.kv_heads, capacity, layer.head_dimension)
+        for which in (0, 1):
+            values = torch.randn(shape, device="cuda", generator=generator, dtype=torch.bfloat16)
+            runner.write_cache(which, index, values)
+            del values
+    torch.cuda.synchronize()
+
+
 # --------------------------------------------------------------------------- byte accounting
 def linear_bytes(rows, k, n, fused_argmax=False):
     """Algorithmic bytes of one FP8 linear call: e4m3 weights + e4m3 activations in + bf16 out
@@ -225,18 +242,24 @@ def run_ours(args, rank, world):
     import carat_b200
     library = carat_b200.library()
     config, runner, fp8 = build_model(seed=0)
-    lengths = accept_lengths(args.steps + args.warmup, seed=7 + rank)
-    generator = torch.Generator().manual_seed(11 + rank)
+    seed_shift = 0 if args.same_seeds else rank
+    lengths = accept_lengths(args.steps + args.warmup, seed=7 + seed_shift)
+    generator = torch.Generator().manual_seed(11 + seed_shift)
     slots = list(range(SLOTS))
-    start_positions = context_lengths(seed=3 + rank)
-    runner.seed_slot_positions(start_positions)
+    start_positions = context_lengths(seed=3 + seed_shift)
+
+    def reseed():
+        runner.seed_slot_positions(start_positions)
+        fill_kv(runner, config, seed=5 + seed_shift)
+
+    reseed()
     last_tokens = torch.randint(3, config.vocabulary_size, (SLOTS,), generator=generator).tolist()
     next_tokens = torch.randint(3, config.vocabulary_size, (SLOTS,), generator=generator).tolist()
 
     def one_step(step):
         nonlocal last_tokens, next_tokens
         if any(runner.slot_position(slot) + DEPTH > MAX_CONTEXT for slot in slots):
-            runner.seed_slot_positions(start_positions)
+            reseed()
         proposals = runner.draft_four(last_tokens, slots, next_tokens, DEPTH)
         caps = lengths[step].tolist()
         result = runner.verify_greedy_proposals(proposals, next_tokens, slots, caps,
@@ -245,7 +268,7 @@ def run_ours(args, rank, world):
         verify_launches, draft_launches = runner.last_launches()
         last_tokens = [proposals[r][result.accepted_tokens[r] - 1] for r in range(SLOTS)]
         next_tokens = result.next_tokens
-        return sum(result.accepted_tokens), verify_ms, draft_ms, verify_launches + draft_launches
+        return result.accepted_tokens, verify_ms, draft_ms, verify_launches + draft_launches
 
     def timed_run():
         for step in range(args.warmup):
@@ -259,31 +282,37 @@ def run_ours(args, rank, world):
         device_ms = 0.0
         verify_total_ms = 0.0
         launches = 0
+        token_gaps = []      # per slot and step: step time / tokens the slot emitted in it
         wall_start = time.perf_counter()
         for step in range(args.warmup, args.warmup + args.steps):
             accepted, verify_ms, draft_ms, step_launches = one_step(step)
-            tokens += accepted
+            tokens += sum(accepted)
             device_ms += verify_ms + draft_ms
             verify_total_ms += verify_ms
             launches += step_launches
+            token_gaps += [(verify_ms + draft_ms) / count for count in accepted if count > 0]
         torch.cuda.synchronize()
         wall_ms = (time.perf_counter() - wall_start) * 1e3
         clocks = sampler.stop()
         barrier(world)
-        return positions, tokens, device_ms, verify_total_ms, launches, wall_ms, clocks
+        return positions, tokens, device_ms, verify_total_ms, launches, wall_ms, clocks, token_gaps
 
-    (positions_at_start, tokens, device_ms, verify_total_ms, launches, wall_ms,
-     clocks) = timed_run()
+    (positions_at_start, tokens, device_ms, verify_total_ms, launches, wall_ms, clocks,
+     token_gaps) = timed_run()
 
     totals = reduce_max_and_sum(world, [device_ms, wall_ms], [float(tokens)])
     device_ms_max, wall_ms_max = totals[0]
     tokens_all = totals[1][0]
+    weight_bytes = step_weight_bytes(config)
+    kv_bytes = step_kv_bytes(config, positions_at_start)
+    per_rank = gather_rows(world, [float(rank), device_ms / args.steps,
+                                   verify_total_ms / args.steps, float(kv_bytes), float(tokens),
+                                   (wall_ms - device_ms) / args.steps])
     if rank != 0:
         return
     peaks = measured_peaks()
-    weight_bytes = step_weight_bytes(config)
-    kv_bytes = step_kv_bytes(config, positions_at_start)
     verify_ms_step = verify_total_ms / args.steps
+    token_gaps.sort()
     line = {
         "metric": METRIC, "value": tokens_all / (device_ms_max / 1e3), "unit": UNIT,
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -300,13 +329,57 @@ def run_ours(args, rank, world):
             "frac_of_measured_peak": (weight_bytes + kv_bytes) / verify_ms_step / 1e6 / peaks["hbm_gbs"],
             "frac_of_nominal_8000": (weight_bytes + kv_bytes) / verify_ms_step / 1e6 / 8000.0},
         "mean_accepted": tokens / args.steps / SLOTS,
+        "inter_token_ms_p50": token_gaps[len(token_gaps) // 2] if token_gaps else None,
+        # Replicas never wait for one another, so the box's throughput is also the plain sum of
+        # what each replica does in its own time; `value` divides by the slowest replica's time.
+        "value_independent": sum(row[4] / (row[1] * args.steps / 1e3) for row in per_rank),
+        "per_rank": [{"rank": int(row[0]), "ms_per_step": row[1], "verify_ms": row[2],
+                      "kv_bytes": int(row[3]), "tokens": int(row[4]),
+                      "host_ms_per_step_beyond_device": row[5]} for row in per_rank],
+        "same_seeds_on_every_rank": bool(args.same_seeds),
     }
+    line["near_ties"] = near_tie_count(runner)
+    line["plain_decode"] = plain_decode(runner, config, slots, args)
     line["roofline"] = linear_roofline(library, config, fp8, peaks)
-    if world == 1 and args.int4_mlp:
+    if world == 1 and not args.skip_int4:
         line["int4_mlp"] = int4_variant(config, runner, timed_run, args, weight_bytes)
     if world == 1 and not args.skip_cpu:
+        line["library_baseline"] = library_baseline(config, fp8, peaks)
         line["cpu_baseline"] = cpu_sample(config, lengths, kind_only=False)
     print(json.dumps(line), flush=True)
+
+
+def near_tie_count(runner):
+    """Top-2 margins of the last verify call's logits (recomputed outside the timed region; the
+    step itself never stores logits): rows whose argmax a logit change within the path's
+    tolerance could flip."""
+    rows = SLOTS * DEPTH
+    logits = runner.last_logits(rows).float()
+    top2 = logits.topk(2, dim=1).values
+    margin = top2[:, 0] - top2[:, 1]
+    return {"rows": rows, "margin_below_1e-2": int((margin < 1e-2).sum()),
+            "margin_within_relative_2e-2": int((margin <= 2e-2 * top2[:, 0].abs()).sum())}
+
+
+def plain_decode(runner, config, slots, args):
+    """append_ragged, one token per slot over all 24 slots: the step the scheduler falls back to
+    below its speculation threshold (the same kernels at 24 rows)."""
+    generator = torch.Generator().manual_seed(23)
+    tokens = torch.randint(3, config.vocabulary_size, (SLOTS,), generator=generator).tolist()
+    for _ in range(args.warmup):
+        tokens = runner.append_ragged(tokens, slots)
+    device_ms = 0.0
+    launches = 0
+    steps = max(3, args.steps // 2)
+    begin = time.perf_counter()
+    for _ in range(steps):
+        tokens = runner.append_ragged(tokens, slots)
+        device_ms += runner.last_device_ms()[0]
+        launches = runner.last_launches()[0]
+    wall_ms = (time.perf_counter() - begin) * 1e3
+    return {"rows": SLOTS, "steps": steps, "ms_per_step": device_ms / steps,
+            "tokens_per_s": SLOTS * steps / (device_ms / 1e3),
+            "e2e_tokens_per_s": SLOTS * steps / (wall_ms / 1e3), "launches_per_step": launches}
 
 
 def int4_variant(config, runner, timed_run, args, fp8_weight_bytes):
@@ -337,7 +410,7 @@ def int4_variant(config, runner, timed_run, args, fp8_weight_bytes):
         torch.cuda.synchronize()
         capi.check(capi.library().carat_b200_runner_use_int4_mlp(runner._handle, layers,
                                                                  len(layers), group))
-        _, tokens, device_ms, verify_total_ms, launches, wall_ms, _ = timed_run()
+        _, tokens, device_ms, verify_total_ms, launches, wall_ms, _, _ = timed_run()
         capi.check(capi.library().carat_b200_runner_use_int4_mlp(runner._handle, None, 0, 0))
         mlp_e4m3 = len(config.layers) * 3 * inter * hidden
         mlp_int4 = len(config.layers) * (3 * inter * hidden // 2 + 3 * inter * hidden // group * 2)
@@ -425,7 +498,149 @@ def linear_roofline(library, config, fp8, peaks):
             "traffic_source": "ncu capture of the gate_up launch, scaled by algorithmic bytes"}
 
 
+# --------------------------------------------------------------------------- library baseline
+def library_baseline(config, fp8, peaks):
+    """The reference's own algorithm on the same GPU: its Fp8Linear (cuBLASLt) on the seven linear
+    shapes of the model at 120 rows, and its unfused LM-head chain (quantise -> FP8 GEMM ->
+    row argmax, cuda/batch_model_runner.cu:840-853,938-940), next to this repository's kernels on
+    the same weights. Each shape rotates over the weights of several layers so that every call
+    starts with a cold L2. The reference side is oracle/_ref/libref_cuda.so (the reference's
+    sources compiled unmodified for sm_100a); without it the object says so."""
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_cuda.so")
+    if not os.path.exists(path):
+        return {"unavailable": "oracle/_ref/libref_cuda.so is not built"}
+    import carat_b200
+    from carat_b200.capi import check
+    ours = carat_b200.library()
+    theirs = ctypes.CDLL(path, mode=os.RTLD_NOW)
+    P, I = ctypes.c_void_p, ctypes.c_int
+    theirs.ref_fp8_linear_launch.argtypes = [P, P, P, P, P, I, I, I]
+    theirs.ref_quantize_argmax_launch.argtypes = [P, P, P, P, P, P, P, P, I, I, I]
+    theirs.ref_argmax_bf16_workspace_bytes.restype = ctypes.c_size_t
+    theirs.ref_argmax_bf16_workspace_bytes.argtypes = [I]
+    theirs.ref_last_error.restype = ctypes.c_char_p
+    rows = SLOTS * DEPTH
+    hidden, inter = config.hidden_size, config.intermediate_size
+    sliding = [i for i, layer in enumerate(config.layers) if layer.attention == "sliding"]
+    global_ = [i for i, layer in enumerate(config.layers) if layer.attention == "global"]
+    first_sliding, first_global = config.layers[sliding[0]], config.layers[global_[0]]
+    shapes = [("sliding_qkv", "qkv", sliding, hidden, first_sliding.packed_width()),
+              ("sliding_o", "o", sliding, first_sliding.query_width(), hidden),
+              ("global_qkv", "qkv", global_, hidden, first_global.packed_width()),
+              ("global_o", "o", global_, first_global.query_width(), hidden),
+              ("gate_up", "gate_up", sliding, hidden, 2 * inter),
+              ("down", "down", sliding, inter, hidden)]
+    widest = max(inter, first_global.query_width())
+    x = torch.randint(0, 120, (rows, widest), dtype=torch.uint8, device="cuda")
+    scale = torch.ones(1, dtype=torch.float32, device="cuda")
+    out = torch.empty(rows, max(2 * inter, 4096), dtype=torch.bfloat16, device="cuda")
+    work = torch.empty(64 << 20, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def timed(call, count):
+        call(0)
+        call(1)
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for index in range(count):
+            call(index)
+        end.record()
+        torch.cuda.synchronize()
+        return begin.elapsed_time(end) / count * 1e3
+
+    result = {"rows": rows, "unit": "us per call", "shapes": {}}
+    for label, segment, layers, k, n in shapes:
+        names = [f"layer.{index}.{segment}" for index in layers[:10]]
+
+        def reference_call(index, names=names, k=k, n=n):
+            name = names[index % len(names)]
+            if theirs.ref_fp8_linear_launch(x.data_ptr(), scale.data_ptr(),
+                                            fp8.at(name).data_ptr(), fp8.scale(name).data_ptr(),
+                                            out.data_ptr(), rows, k, n) != 0:
+                raise RuntimeError(theirs.ref_last_error().decode())
+
+        def our_call(index, names=names, k=k, n=n):
+            name = names[index % len(names)]
+            check(ours.carat_b200_fp8_linear(
+                x.data_ptr(), scale.data_ptr(), fp8.at(name).data_ptr(),
+                fp8.scale(name).data_ptr(), out.data_ptr(), rows, k, n, work.data_ptr(),
+                work.numel(), stream))
+
+        count = 2 * len(names)
+        try:
+            reference_us = timed(reference_call, count)
+        except RuntimeError as error:
+            result["shapes"][label] = {"k": k, "n": n, "reference_error": str(error)}
+            continue
+        ours_us = timed(our_call, count)
+        result["shapes"][label] = {"k": k, "n": n, "cublaslt_us": reference_us, "ours_us": ours_us,
+                                   "cublaslt_weight_gbs": k * n / reference_us / 1e3,
+                                   "ours_weight_gbs": k * n / ours_us / 1e3}
+    # LM head: the reference's three launches (and 63 MB of logits) against the fused epilogue.
+    vocabulary = config.vocabulary_size
+    final_hidden = torch.randn(rows, hidden, device="cuda").to(torch.bfloat16)
+    quantised = torch.empty(rows, hidden, dtype=torch.uint8, device="cuda")
+    quantised_scale = torch.zeros(1, dtype=torch.float32, device="cuda")
+    scratch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    logits = torch.empty(rows, vocabulary, dtype=torch.bfloat16, device="cuda")
+    tokens = torch.empty(rows, dtype=torch.int32, device="cuda")
+    keys = torch.empty(rows, dtype=torch.int64, device="cuda")
+    argmax_work = torch.empty(theirs.ref_argmax_bf16_workspace_bytes(vocabulary) * rows,
+                              dtype=torch.uint8, device="cuda")
+    head, head_scale = fp8.at("token_embedding"), fp8.scale("token_embedding")
+
+    def reference_head(_):
+        if theirs.ref_quantize_argmax_launch(
+                final_hidden.data_ptr(), quantised.data_ptr(), quantised_scale.data_ptr(),
+                head.data_ptr(), head_scale.data_ptr(), logits.data_ptr(), tokens.data_ptr(),
+                argmax_work.data_ptr(), rows, hidden, vocabulary) != 0:
+            raise RuntimeError(theirs.ref_last_error().decode())
+
+    def our_head(_):
+        check(ours.carat_b200_quantize_bf16_to_fp8(
+            final_hidden.data_ptr(), quantised.data_ptr(), quantised_scale.data_ptr(),
+            scratch.data_ptr(), rows, hidden, stream))
+        check(ours.carat_b200_fp8_linear_argmax(
+            quantised.data_ptr(), quantised_scale.data_ptr(), head.data_ptr(),
+            head_scale.data_ptr(), tokens.data_ptr(), keys.data_ptr(), rows, hidden, vocabulary,
+            stream))
+
+    try:
+        result["lm_head_chain"] = {"k": hidden, "n": vocabulary,
+                                   "reference_unfused_us": timed(reference_head, 4),
+                                   "ours_fused_us": timed(our_head, 4)}
+    except RuntimeError as error:
+        result["lm_head_chain"] = {"reference_error": str(error)}
+    return result
+
+
 # --------------------------------------------------------------------------- CPU arm
+def bookkeeping_sample():
+    """Seconds one step's host bookkeeping takes (acceptance_cap + commit_speculation for 24
+    slots), with the reference's own compiled speculation.cpp when oracle/_ref holds it."""
+    from oracle import carat_semantics as cs
+    reference = os.path.join(ROOT, "oracle", "_ref", "libref_speculation.so")
+    begin = time.perf_counter()
+    if os.path.exists(reference):
+        library = ctypes.CDLL(reference)
+        proposals = (ctypes.c_int * DEPTH)(*range(10, 10 + DEPTH))
+        stops = (ctypes.c_int * 1)(1)
+        resident = (ctypes.c_int * (DEPTH + 1))()
+        emitted = (ctypes.c_int * (DEPTH + 1))()
+        counts = [ctypes.c_int(), ctypes.c_int(), ctypes.c_int()]
+        for _ in range(SLOTS):
+            cap = library.ref_acceptance_cap(DEPTH, 100, proposals, DEPTH, stops, 1)
+            library.ref_commit_speculation(10, proposals, max(cap - 1, 0), 20, stops, 1, resident,
+                                           ctypes.byref(counts[0]), emitted,
+                                           ctypes.byref(counts[1]), ctypes.byref(counts[2]))
+        return time.perf_counter() - begin, "reference speculation.cpp (oracle/_ref)"
+    for _ in range(SLOTS):
+        cap = cs.acceptance_cap(DEPTH, 100, list(range(10, 10 + DEPTH)), {1})
+        cs.commit_speculation(10, list(range(11, 10 + cap)), 20, {1})
+    return time.perf_counter() - begin, "oracle port of speculation.cpp"
+
+
 def cpu_sample(config, lengths, kind_only):
     """The reference's CPU path on a bounded sample: the oracle's restatement of one sliding layer,
     one global layer and the LM head of the verify forward at the benchmark's 120 rows and context
@@ -470,28 +685,7 @@ def cpu_sample(config, lengths, kind_only):
     logits = cs.fp8_linear(xq, xs, head[0], head[1])
     cs.argmax_lowest_index(logits)
     timings["lm_head"] = (time.perf_counter() - begin) * 8
-    # Host bookkeeping with the reference's own compiled logic when available.
-    bookkeeping = "oracle port"
-    reference = os.path.join(ROOT, "oracle", "_ref", "libref_speculation.so")
-    begin = time.perf_counter()
-    if os.path.exists(reference):
-        library = ctypes.CDLL(reference)
-        proposals = (ctypes.c_int * DEPTH)(*range(10, 10 + DEPTH))
-        stops = (ctypes.c_int * 1)(1)
-        resident = (ctypes.c_int * (DEPTH + 1))()
-        emitted = (ctypes.c_int * (DEPTH + 1))()
-        counts = [ctypes.c_int(), ctypes.c_int(), ctypes.c_int()]
-        for _ in range(SLOTS):
-            cap = library.ref_acceptance_cap(DEPTH, 100, proposals, DEPTH, stops, 1)
-            library.ref_commit_speculation(10, proposals, max(cap - 1, 0), 20, stops, 1, resident,
-                                           ctypes.byref(counts[0]), emitted,
-                                           ctypes.byref(counts[1]), ctypes.byref(counts[2]))
-        bookkeeping = "reference speculation.cpp (oracle/_ref)"
-    else:
-        for _ in range(SLOTS):
-            cap = cs.acceptance_cap(DEPTH, 100, list(range(10, 10 + DEPTH)), {1})
-            cs.commit_speculation(10, list(range(11, 10 + cap)), 20, {1})
-    timings["bookkeeping"] = time.perf_counter() - begin
+    timings["bookkeeping"], bookkeeping = bookkeeping_sample()
     step_seconds = 50 * timings["sliding"] + 10 * timings["global"] + timings["lm_head"] + \
         timings["bookkeeping"]
     mean_tokens = float(lengths.float().mean()) * SLOTS
@@ -500,8 +694,101 @@ def cpu_sample(config, lengths, kind_only):
                       "120 rows, 24 slots, the benchmark's context lengths (PyTorch CPU restatement "
                       f"of the reference's CUDA numerics), extrapolated x50 / x10 / x8; {bookkeeping}; "
                       "the drafter is not included",
+            "extrapolated": True,
             "seconds_per_step_extrapolated": step_seconds,
             "seconds_sampled": {k: round(v, 3) for k, v in timings.items()}}
+
+
+def hf_bf16_sample(lengths):
+    """The PyTorch CPU forward the reference's fixture tools run (Hugging Face Gemma4 text model,
+    BF16, eager attention; tools/generate_layer_fixture.py:57-86, tools/compare_gemma4_assistant.py)
+    on a bounded sample of the verify step: one sliding + one global decoder layer at the 31B
+    widths over 24 slots x (k+1) rows, attending a seeded random KV cache (1023 ring rows; the
+    benchmark's mean context length for the global layer, uniform because the model wants a
+    rectangular batch), and one eighth of the LM head. Extrapolated x50 / x10 / x8."""
+    from transformers import DynamicCache
+    from transformers.models.gemma4.configuration_gemma4 import Gemma4TextConfig
+    from transformers.models.gemma4.modeling_gemma4 import Gemma4TextModel
+
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    positions = context_lengths(seed=3)
+    context = sum(positions) // len(positions)
+    hidden, vocabulary = 5376, 262144
+    generator = torch.Generator().manual_seed(0)
+
+    def model_of(kinds):
+        config = Gemma4TextConfig(
+            vocab_size=4096, hidden_size=hidden, intermediate_size=21504,
+            num_hidden_layers=len(kinds), num_attention_heads=32, num_key_value_heads=16,
+            head_dim=256, global_head_dim=512, num_global_key_value_heads=4, attention_k_eq_v=True,
+            sliding_window=1024, layer_types=kinds, rms_norm_eps=1e-6,
+            hidden_size_per_layer_input=0, num_kv_shared_layers=0,
+            max_position_embeddings=MAX_CONTEXT, final_logit_softcapping=None,
+            tie_word_embeddings=True, attention_bias=False,
+            rope_parameters={
+                "sliding_attention": {"rope_type": "default", "rope_theta": 10000.0},
+                "full_attention": {"rope_type": "proportional", "partial_rotary_factor": 0.25,
+                                   "rope_theta": 1000000.0}})
+        config._attn_implementation = "eager"
+        return config, Gemma4TextModel(config).to(torch.bfloat16).eval()
+
+    def causal(keys):
+        mask = torch.zeros(SLOTS, 1, DEPTH, keys, dtype=torch.bfloat16)
+        for row in range(DEPTH):
+            mask[:, :, row, keys - DEPTH + row + 1:] = float("-inf")
+        return mask
+
+    # One forward through a [sliding, global] pair; each decoder layer is timed by hooks.
+    kinds = ["sliding_attention", "full_attention"]
+    config, model = model_of(kinds)
+    started, spent = {}, {0: [], 1: []}
+    for index, layer in enumerate(model.layers):
+        layer.register_forward_pre_hook(
+            lambda module, inputs, index=index: started.__setitem__(index, time.perf_counter()))
+        layer.register_forward_hook(
+            lambda module, inputs, output, index=index:
+            spent[index].append(time.perf_counter() - started[index]))
+    with torch.inference_mode():
+        for _ in range(2):
+            cache = DynamicCache(config=config)
+            for index, kind in enumerate(kinds):
+                heads, dim, rows = (16, 256, 1023) if kind == "sliding_attention" else \
+                    (4, 512, context)
+                cache.update(torch.randn(SLOTS, heads, rows, dim, generator=generator)
+                             .to(torch.bfloat16),
+                             torch.randn(SLOTS, heads, rows, dim, generator=generator)
+                             .to(torch.bfloat16), index)
+            ids = torch.randint(3, 4096, (SLOTS, DEPTH), generator=generator)
+            position_ids = (context + torch.arange(DEPTH))[None, :].expand(SLOTS, DEPTH)
+            model(input_ids=ids, past_key_values=cache, position_ids=position_ids, use_cache=True,
+                  attention_mask={"full_attention": causal(context + DEPTH),
+                                  "sliding_attention": causal(1023 + DEPTH)})
+    del model
+    sliding_seconds, global_seconds = min(spent[0]), min(spent[1])
+    head = torch.randn(vocabulary // 8, hidden, generator=generator).to(torch.bfloat16)
+    rows = torch.randn(SLOTS * DEPTH, hidden, generator=generator).to(torch.bfloat16)
+    begin = time.perf_counter()
+    (rows @ head.t()).argmax(dim=1)
+    head_seconds = (time.perf_counter() - begin) * 8
+    bookkeeping_seconds, bookkeeping = bookkeeping_sample()
+    step_seconds = 50 * sliding_seconds + 10 * global_seconds + head_seconds + bookkeeping_seconds
+    mean_tokens = float(lengths.float().mean()) * SLOTS
+    import transformers
+    return {"value": mean_tokens / step_seconds, "unit": UNIT, "cores": cores, "kind": "reference",
+            "sample": "Hugging Face Gemma4TextModel BF16 eager forward (transformers "
+                      f"{transformers.__version__}; the reference's fixture tools pin 5.19.0) of "
+                      "one sliding and one global 31B-width decoder layer (each timed by hooks) over "
+                      "24 slots x "
+                      f"{DEPTH} rows with a random KV cache (1023 ring rows / {context} global "
+                      "rows, the benchmark's mean context) and 1/8 of the BF16 LM head, best of 2, "
+                      f"extrapolated x50 / x10 / x8; {bookkeeping}; the drafter is not included",
+            "extrapolated": True,
+            "seconds_per_step_extrapolated": step_seconds,
+            "seconds_sampled": {"sliding": round(sliding_seconds, 3),
+                                "global": round(global_seconds, 3),
+                                "lm_head": round(head_seconds, 3),
+                                "bookkeeping": round(bookkeeping_seconds, 6)}}
 
 
 def run_reference(args, rank, world):
@@ -510,14 +797,23 @@ def run_reference(args, rank, world):
     lengths = accept_lengths(args.steps + args.warmup, seed=7)
     import carat_b200
     config = carat_b200.Gemma4Config.gemma4_31b()
-    samples = []
-    for _ in range(max(1, min(args.steps, 2))):
-        samples.append(cpu_sample(config, lengths, kind_only=True))
-    best = max(samples, key=lambda sample: sample["value"])
+    # One extrapolated sample stands for every step: a full 60-layer CPU step takes tens of
+    # seconds, so `steps` of them would not end in minutes. steps_run says what was executed.
+    port = cpu_sample(config, lengths, kind_only=True)
+    try:
+        best = hf_bf16_sample(lengths)
+        best["fp8_restatement"] = {key: port[key] for key in ("value", "kind", "sample",
+                                                             "seconds_per_step_extrapolated")}
+    except Exception as error:   # transformers without Gemma4, or too little host memory
+        best = port
+        best["hf_bf16_forward"] = f"skipped: {type(error).__name__}: {error}"
     line = {"impl": "reference", "metric": METRIC, "value": best["value"], "unit": UNIT,
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "steps_run": 0,
+            "extrapolated": True,
             "ms_per_step": best["seconds_per_step_extrapolated"] * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 values in fp32 arithmetic",
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 (Hugging Face CPU forward)" if best["kind"] == "reference"
+            else "fp8_e4m3 values in fp32 arithmetic",
             "data": "synthetic", "config": workload_config(args), "cpu_baseline": best,
             "e2e": {"value": best["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
                     "d2h_bytes_per_step": 0}}
@@ -542,6 +838,17 @@ def reduce_max_and_sum(world, maxima, sums):
     return m.tolist(), s.tolist()
 
 
+def gather_rows(world, row):
+    """Every rank's row of floats, in rank order, on every rank."""
+    if world == 1:
+        return [row]
+    device = "cuda" if torch.distributed.get_backend() == "nccl" else "cpu"
+    mine = torch.tensor(row, dtype=torch.float64, device=device)
+    rows = [torch.empty_like(mine) for _ in range(world)]
+    torch.distributed.all_gather(rows, mine)
+    return [entry.tolist() for entry in rows]
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -550,8 +857,12 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--drafts", type=int, default=4, choices=[2, 4, 8],
                         help="k, drafted tokens per slot and step (the headline metric is k = 4)")
-    parser.add_argument("--int4-mlp", action="store_true",
-                        help="also time the step with INT4 weight-only MLP linears (N = 1 only)")
+    parser.add_argument("--skip-int4", action="store_true",
+                        help="leave the int4_mlp object (the step with INT4 weight-only MLP "
+                             "linears, N = 1 only) out")
+    parser.add_argument("--same-seeds", action="store_true",
+                        help="N > 1: every rank draws the same contexts and accept lengths "
+                             "(separates workload skew from machine effects)")
     parser.add_argument("--skip-cpu", action="store_true",
                         help="leave the cpu_baseline object out (profiling runs)")
     parser.add_argument("--case", nargs="+", metavar="WORD",
