@@ -77,3 +77,19 @@ def int4_reference_test_case():
     value = 0.75 * torch.sin(cell * 0.037) - 0.21 * torch.cos(column * 0.019)
     return (cs.bf16(weight).reshape(output_width, input_width),
             cs.bf16(value).reshape(rows, input_width))
+
+
+# A differing greedy token is tolerated only at a logit near-tie. The path holds logits to bf16
+# relative 2e-2, so that is the band where the comparison is against the reference's own code on
+# the GPU at the model's real widths (tests/test_reference_runner_gpu.py: no row has needed it).
+# The tiny plumbing model compared with the CPU oracle gets a wider, stated band: its logits peak
+# near 1.1, where ONE bf16 ulp is already 0.7 % of the winning logit, its hidden width of 256
+# averages little, and its four-layer e4m3 chain answers a last-bit flip upstream with changes
+# of several ulps in a logit. Eight ulps there are 6e-2. Differing rows are counted and bounded.
+NEAR_TIE_RELATIVE = 2e-2
+NEAR_TIE_RELATIVE_TINY = 6e-2
+
+
+def near_tie(logits_row, chosen, band=NEAR_TIE_RELATIVE) -> bool:
+    top = float(logits_row.max())
+    return top - float(logits_row[chosen]) <= band * abs(top) + 1e-6

@@ -48,9 +48,10 @@ def _norm(width, generator):
 class Pair:
     """One set of weights, this repository's runner and the reference's runner over it."""
 
-    def __init__(self):
-        layers = [carat_b200.Gemma4LayerConfig("sliding", 32, 16, 256, 1e4, False),
-                  carat_b200.Gemma4LayerConfig("global", 32, 4, 512, 1e6, True)]
+    def __init__(self, sliding_layers=1):
+        layers = [carat_b200.Gemma4LayerConfig("sliding", 32, 16, 256, 1e4, False)
+                  for _ in range(sliding_layers)]
+        layers.append(carat_b200.Gemma4LayerConfig("global", 32, 4, 512, 1e6, True))
         self.config = carat_b200.Gemma4Config(5376, 21504, VOCABULARY, 1024, 1e-6, layers)
         generator = torch.Generator(device="cuda").manual_seed(0)
         hidden, inter = self.config.hidden_size, self.config.intermediate_size
@@ -359,6 +360,28 @@ def test_depth_eight_wrapped(pair):
                                      ragged_caps=True, drafts=False)
     print(f"near-ties: {ties.relative} flagged of {ties.rows} rows; {accepted} tokens accepted")
     assert ties.relative <= 4
+
+
+def test_six_layer_stack_free_running(cuda_device):
+    """One full period of the model's layer pattern (five sliding layers and a global one) at the
+    real widths: twelve more e4m3 requantisations between the embedding and the logits than the
+    two-layer pair above, same bar."""
+    ref.library()
+    deep = Pair(sliding_layers=5)
+    try:
+        ties, accepted, draft_rows, draft_mismatch = run_steps(
+            deep, start_position=1040, steps=8, depth=5, ragged_caps=True, drafts=False)
+        print(f"six layers: near-ties {ties.relative} flagged ({ties.absolute} below 1e-2) of "
+              f"{ties.rows} rows; {accepted} tokens accepted")
+        assert ties.relative <= 4
+        ties, accepted, _, _ = run_steps(deep, start_position=3, steps=8, depth=5,
+                                         ragged_caps=False, drafts=False)
+        print(f"six layers, unwrapped: near-ties {ties.relative} flagged of {ties.rows} rows; "
+              f"{accepted} tokens accepted")
+        assert ties.relative <= 4
+    finally:
+        deep.close()
+        torch.cuda.empty_cache()
 
 
 def test_drop_in_cpp_shim_runs_the_same_step(pair):

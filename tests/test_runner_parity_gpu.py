@@ -13,21 +13,23 @@ three parts:
   * the first step of an empty slot (no accumulated state) must match to the last bit;
   * bookkeeping (accept lengths, next tokens, positions, rollback) must be bit-exact given the
     device's own predictions;
-  * hidden states and KV rows must agree norm-wise within NOISE_FLOOR, and a prediction that
-    differs from the oracle's must be a near-tie in the oracle's logits; such rows are counted.
+  * hidden states and KV rows must agree norm-wise within TOLERANCE, and a prediction that
+    differs from the oracle's must be a near-tie in the oracle's logits (helpers.near_tie with
+    the band stated there for this tiny model); such rows are counted and bounded.
 """
 import copy
 
 import pytest
 import torch
 
+import carat_b200
+import helpers
 from helpers import build_pair, cosine, rms_relative_error
 from oracle import carat_semantics as cs
 
 pytestmark = pytest.mark.gpu
 
 TOLERANCE = 0.12   # norm-wise relative error, about twice the oracle's own one-ulp sensitivity
-NEAR_TIE = 0.10    # logit gap relative to the row's (max - mean) logit spread
 
 
 @pytest.fixture(scope="module")
@@ -47,10 +49,8 @@ def prompts(config, count, length, seed=0):
 
 
 def near_tie(trace, row, chosen):
-    """The device's choice must score within NEAR_TIE of the oracle's best in the oracle's logits."""
-    logits = trace.logits[row]
-    spread = float(logits.max() - logits.mean())
-    return float(logits.max() - logits[chosen]) < NEAR_TIE * spread
+    """The device's choice must be a near-tie with the oracle's best in the oracle's logits."""
+    return helpers.near_tie(trace.logits[row], chosen, helpers.NEAR_TIE_RELATIVE_TINY)
 
 
 def forced_step(oracle, device, proposals, firsts, slots, caps=(), flags=0):
@@ -237,6 +237,7 @@ def test_append_ragged_plain_decode(pair):
         for row, slot in enumerate(slots):
             assert rms_relative_error(by_slot[slot], oracle.target_hidden[slot]) < TOLERANCE
     print(f"append_ragged: {flagged} near-tie predictions flagged")
+    assert flagged <= 4
     with pytest.raises(carat_b200.CaratError, match="invalid ragged token batch"):
         device.append_ragged([5, 6, 7, 8, 9], [0, 1, 2, 3, 0])
     with pytest.raises(carat_b200.CaratError, match="invalid or repeated ragged slot"):
@@ -298,3 +299,34 @@ def test_argument_errors_match_the_reference(pair):
         device.draft_four([5], [3], (), 2)
     with pytest.raises(carat_b200.CaratError, match="ragged slot is empty or full"):
         device.append_ragged([5], [3])
+
+
+def test_hand_off_is_a_byte_copy_of_the_devices_own_row(pair):
+    """cuda/batch_model_runner.cu:1761-1783: row (accepted - 1) of the call's final-normed hidden
+    rows lands in the slot's entry of the hidden-by-slot table, byte for byte, and a request that
+    accepted nothing leaves its entry untouched."""
+    config, oracle, device, _ = pair
+    depth = 5
+    slots = [0, 1, 2, 3]
+    for slot in slots:
+        if device.slot_position(slot) == 0:
+            device.prefill_slot_fp8(slot, prompts(config, 1, 16, seed=40 + slot)[0], 8)
+    generator = torch.Generator().manual_seed(9)
+    proposals = [torch.randint(3, config.vocab, (depth,), generator=generator).tolist()
+                 for _ in slots]
+    firsts = [row[0] for row in proposals]
+    caps = [0, 1, 3, 5]
+    before = device.target_hidden_slots().clone()
+    result = device.verify_greedy_proposals(proposals, firsts, slots, caps,
+                                            carat_b200.VERIFY_ASSUME_MATCH)
+    assert result.accepted_tokens == caps
+    rows = device.last_final_hidden(len(slots) * depth)
+    table = device.target_hidden_slots()
+    for request, slot in enumerate(slots):
+        accepted = result.accepted_tokens[request]
+        if accepted == 0:
+            assert torch.equal(table[slot].view(torch.int16), before[slot].view(torch.int16))
+            assert result.next_tokens[request] == firsts[request]
+        else:
+            source = rows[request * depth + accepted - 1]
+            assert torch.equal(table[slot].view(torch.int16), source.view(torch.int16))

@@ -18,13 +18,13 @@ import pytest
 import torch
 
 import carat_b200
+import helpers
 from helpers import build_pair, rms_relative_error
 from oracle import carat_semantics as cs
 
 pytestmark = pytest.mark.gpu
 
 TOLERANCE = 0.12
-NEAR_TIE = 0.10
 MAX_CONTEXT = 2304          # 18 x 128 rows: three chunks of the global cache
 WINDOW = 256
 
@@ -102,9 +102,7 @@ def test_one_layer_first_step_is_tight(cuda_device, layer, depth):
 
 
 def near_tie(trace, row, chosen):
-    logits = trace.logits[row]
-    spread = float(logits.max() - logits.mean())
-    return float(logits.max() - logits[chosen]) < NEAR_TIE * spread
+    return helpers.near_tie(trace.logits[row], chosen, helpers.NEAR_TIE_RELATIVE_TINY)
 
 
 def test_draft_over_shared_tensor_core_caches(pair):
@@ -171,6 +169,7 @@ def test_verify_steps_over_tensor_core_attention(pair):
         assert rms_relative_error(device.value_cache(index, capacity),
                                   oracle.values[index]) < TOLERANCE
     print(f"tensor-core runner parity: {flagged} near-tie predictions flagged")
+    assert flagged <= 6
 
 
 def test_rejected_rows_leave_the_sliding_ring_untouched(pair):
