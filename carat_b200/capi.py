@@ -75,6 +75,9 @@ SIGNATURES = {
     "carat_b200_fp8_linear_static": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "carat_b200_fp8_linear_argmax": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "carat_b200_fp8_linear_check": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
+    "carat_b200_bf16_linear": (_I, [_P, _P, _P, _I, _I, _I, _P, c_size_t, _P]),
+    "carat_b200_bf16_linear_workspace_bytes": (c_size_t, [_I, _I, _I]),
+    "carat_b200_bf16_linear_argmax": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
     "carat_b200_int4_quantize_weight": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "carat_b200_int4_reorder_weight": (_I, [_P, _P, _I, _I, _P]),
     "carat_b200_int4_linear": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P, c_size_t, _P]),

@@ -9,10 +9,10 @@ using namespace carat_b200;
 namespace {
 
 int plan_or_fail(LinearPlan *plan, const void *input, const void *weight, int rows, int input_width,
-                 int output_width, int splits) {
+                 int output_width, int splits, int element_bytes = 1) {
   const char *message = "invalid FP8 linear shape";
-  const int status =
-      make_linear_plan(plan, input, weight, rows, input_width, output_width, splits, &message);
+  const int status = make_linear_plan(plan, input, weight, rows, input_width, output_width,
+                                      splits, &message, element_bytes);
   if (status != 0)
     set_last_error(message);
   return status;
@@ -118,6 +118,73 @@ extern "C" int carat_b200_fp8_linear_check(const void *fp8_input, const float *d
                                                 input_width, output_width,
                                                 static_cast<cudaStream_t>(stream)),
                        "FP8 linear check");
+}
+
+// BF16 linear (the same weight-streaming kernel with 16-bit operands) ----------------------------
+
+extern "C" size_t carat_b200_bf16_linear_workspace_bytes(int rows, int input_width,
+                                                         int output_width) {
+  return linear_partial_bytes_for(rows, input_width, output_width, 2);
+}
+
+extern "C" int carat_b200_bf16_linear(const void *bf16_input, const void *bf16_weight,
+                                      void *bf16_output, int rows, int input_width,
+                                      int output_width, void *workspace, size_t workspace_bytes,
+                                      void *stream) {
+  if (bf16_output == nullptr) {
+    set_last_error("invalid BF16 linear shape");
+    return -1;
+  }
+  LinearPlan plan;
+  int status = plan_or_fail(&plan, bf16_input, bf16_weight, rows, input_width, output_width, 0, 2);
+  if (status != 0) {
+    set_last_error("invalid BF16 linear shape");
+    return status;
+  }
+  const size_t needed = linear_partial_bytes(plan);
+  if (needed > 0 && (workspace == nullptr || workspace_bytes < needed)) {
+    set_last_error("BF16 linear workspace is too small");
+    return -6;
+  }
+  int *error_word = device_error_word();
+  if (error_word == nullptr) {
+    set_last_error("device error word is unavailable");
+    return -101;
+  }
+  status = launch_linear_bf16(plan, nullptr, nullptr, bf16_output, static_cast<float *>(workspace),
+                              error_word, static_cast<cudaStream_t>(stream));
+  return launch_status(status, "BF16 linear");
+}
+
+extern "C" int carat_b200_bf16_linear_argmax(const void *bf16_input, const void *bf16_weight,
+                                             int *device_tokens, void *device_keys, int rows,
+                                             int input_width, int output_width, void *stream) {
+  if (device_tokens == nullptr || device_keys == nullptr) {
+    set_last_error("invalid BF16 linear shape");
+    return -1;
+  }
+  LinearPlan plan;
+  int status = plan_or_fail(&plan, bf16_input, bf16_weight, rows, input_width, output_width, 1, 2);
+  if (status != 0) {
+    set_last_error("invalid BF16 linear shape");
+    return status;
+  }
+  int *error_word = device_error_word();
+  if (error_word == nullptr) {
+    set_last_error("device error word is unavailable");
+    return -101;
+  }
+  auto *keys = static_cast<unsigned long long *>(device_keys);
+  const auto cuda_stream = static_cast<cudaStream_t>(stream);
+  status = check_cuda(cudaMemsetAsync(keys, 0, sizeof(unsigned long long) * rows, cuda_stream),
+                      "clear argmax keys");
+  if (status != 0)
+    return status;
+  status = launch_linear_argmax(plan, nullptr, nullptr, keys, error_word, cuda_stream);
+  if (status != 0)
+    return launch_status(status, "BF16 LM head");
+  return launch_status(launch_unpack_best(keys, device_tokens, rows, cuda_stream),
+                       "argmax unpack");
 }
 
 // INT4 weight-only linear ---------------------------------------------------------------------

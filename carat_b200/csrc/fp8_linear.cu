@@ -84,14 +84,18 @@ __device__ __forceinline__ void finish_chunk(const KernelArguments &args, const 
   }
 }
 
-template <int padded_rows, int mode>
+// `wide` = bf16 operands (kind::f16, 64 K elements per 128-byte block) instead of e4m3
+// (kind::f8f6f4, 128 per block). Everything else is shared: both consume one 128-byte swizzle atom
+// per row and block in four MMAs of 32 bytes of K.
+template <int padded_rows, int mode, bool wide>
 __global__ void __launch_bounds__(linear_threads, 1)
 fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
                   const __grid_constant__ CUtensorMap input_map, const KernelArguments args) {
   constexpr int stages = stages_for(padded_rows);
   constexpr int input_tile_bytes = padded_rows * tile_k_bytes;
   constexpr uint32_t stage_bytes = weight_tile_bytes + input_tile_bytes;
-  constexpr uint32_t idesc = ptx::umma_idesc(0, 0, tile_features, padded_rows);
+  constexpr uint32_t idesc = wide ? ptx::umma_idesc(1, 1, tile_features, padded_rows)
+                                  : ptx::umma_idesc(0, 0, tile_features, padded_rows);
   constexpr uint32_t tmem_columns = 2 * padded_rows < 32 ? 32 : 2 * padded_rows;
 
   extern __shared__ unsigned char shared_raw[];
@@ -237,12 +241,21 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
         const uint32_t b_low = input_low + stage * (input_tile_bytes >> 4);
         if (ptx::elect_one()) {
           // +32 bytes along K inside the swizzle atom = +2 in the 16-byte address field.
-          ptx::tcgen05_mma_f8f6f4_split(accumulator, a_low, desc_high, b_low, desc_high, idesc,
-                                        block > 0 ? 1U : 0U);
+          if constexpr (wide) {
+            ptx::tcgen05_mma_f16_split(accumulator, a_low, desc_high, b_low, desc_high, idesc,
+                                       block > 0 ? 1U : 0U);
 #pragma unroll
-          for (int step = 1; step < tile_k_bytes / umma_k; ++step)
-            ptx::tcgen05_mma_f8f6f4_split(accumulator, a_low + 2 * step, desc_high,
-                                          b_low + 2 * step, desc_high, idesc, 1U);
+            for (int step = 1; step < tile_k_bytes / umma_k; ++step)
+              ptx::tcgen05_mma_f16_split(accumulator, a_low + 2 * step, desc_high,
+                                         b_low + 2 * step, desc_high, idesc, 1U);
+          } else {
+            ptx::tcgen05_mma_f8f6f4_split(accumulator, a_low, desc_high, b_low, desc_high, idesc,
+                                          block > 0 ? 1U : 0U);
+#pragma unroll
+            for (int step = 1; step < tile_k_bytes / umma_k; ++step)
+              ptx::tcgen05_mma_f8f6f4_split(accumulator, a_low + 2 * step, desc_high,
+                                            b_low + 2 * step, desc_high, idesc, 1U);
+          }
           ptx::tcgen05_commit(empty_bar + 8U * stage);
         }
         __syncwarp();
@@ -263,7 +276,7 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
     [[maybe_unused]] const int epilogue_thread = (warp - 2) * 32 + lane;
     grid_dependency_wait();
     float scale = 1.0F;
-    if constexpr (mode != 1)
+    if constexpr (mode != 1 && !wide)
       scale = args.input_scale[0] * args.weight_scale[0];
     int local = 0;
     for (int index = first_item; index < items; index += item_stride, ++local) {
@@ -377,7 +390,7 @@ __global__ void finalize_split_k_kernel(const float *partial, const float *input
                                         int splits, size_t elements) {
   grid_dependency_launch();
   grid_dependency_wait();
-  const float scale = input_scale[0] * weight_scale[0];
+  const float scale = input_scale != nullptr ? input_scale[0] * weight_scale[0] : 1.0F;
   for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
        index < elements; index += static_cast<size_t>(blockDim.x) * gridDim.x) {
     float sum = 0.0F;
@@ -393,7 +406,7 @@ __global__ void finalize_tail_kernel(const float *partial, const float *input_sc
                                      int rows, int tail_width, int output_width, int first_column) {
   grid_dependency_launch();
   grid_dependency_wait();
-  const float scale = input_scale[0] * weight_scale[0];
+  const float scale = input_scale != nullptr ? input_scale[0] * weight_scale[0] : 1.0F;
   const size_t elements = static_cast<size_t>(rows) * tail_width;
   for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
        index < elements; index += static_cast<size_t>(blockDim.x) * gridDim.x) {
@@ -446,13 +459,13 @@ bool encode_byte_matrix(CUtensorMap *map, const void *base, uint64_t inner, uint
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int padded_rows, int mode>
+template <int padded_rows, int mode, bool wide>
 int launch_variant(const LinearPlan &plan, const KernelArguments &arguments, cudaStream_t stream) {
   constexpr int stages = stages_for(padded_rows);
   constexpr int dynamic_bytes = stages * (weight_tile_bytes + padded_rows * tile_k_bytes) + 1024;
   static PerDeviceOnce configured;
   if (configured.run([] {
-        return cudaFuncSetAttribute(fp8_linear_kernel<padded_rows, mode>,
+        return cudaFuncSetAttribute(fp8_linear_kernel<padded_rows, mode, wide>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, dynamic_bytes);
       }) != cudaSuccess) {
     return -10;
@@ -460,27 +473,35 @@ int launch_variant(const LinearPlan &plan, const KernelArguments &arguments, cud
   const int items = (plan.tiles - arguments.tail_tiles) * arguments.splits +
                     arguments.tail_tiles * arguments.tail_splits;
   const int ctas = items < plan.ctas ? items : plan.ctas;
-  return launch_chained(fp8_linear_kernel<padded_rows, mode>, dim3(static_cast<unsigned>(ctas)),
+  return launch_chained(fp8_linear_kernel<padded_rows, mode, wide>,
+                        dim3(static_cast<unsigned>(ctas)),
                         dim3(linear_threads), dynamic_bytes, stream, false, plan.weight_map,
                         plan.input_map, arguments) == cudaSuccess
              ? 0
              : -11;
 }
 
-template <int mode>
-int launch_mode(const LinearPlan &plan, const KernelArguments &arguments, cudaStream_t stream) {
+template <int mode, bool wide>
+int launch_rows_bucket(const LinearPlan &plan, const KernelArguments &arguments,
+                       cudaStream_t stream) {
   switch (plan.padded_rows) {
   case 32:
-    return launch_variant<32, mode>(plan, arguments, stream);
+    return launch_variant<32, mode, wide>(plan, arguments, stream);
   case 64:
-    return launch_variant<64, mode>(plan, arguments, stream);
+    return launch_variant<64, mode, wide>(plan, arguments, stream);
   case 128:
-    return launch_variant<128, mode>(plan, arguments, stream);
+    return launch_variant<128, mode, wide>(plan, arguments, stream);
   case 256:
-    return launch_variant<256, mode>(plan, arguments, stream);
+    return launch_variant<256, mode, wide>(plan, arguments, stream);
   default:
     return -12;
   }
+}
+
+template <int mode>
+int launch_mode(const LinearPlan &plan, const KernelArguments &arguments, cudaStream_t stream) {
+  return plan.element_bytes == 2 ? launch_rows_bucket<mode, true>(plan, arguments, stream)
+                                 : launch_rows_bucket<mode, false>(plan, arguments, stream);
 }
 
 // `split` false: one piece per tile whatever the plan says (bf16 store and argmax epilogues).
@@ -501,16 +522,18 @@ KernelArguments base_arguments(const LinearPlan &plan, int *device_error, bool s
 
 } // namespace
 
-std::size_t linear_partial_bytes_for(int rows, int input_width, int output_width) {
+std::size_t linear_partial_bytes_for(int rows, int input_width, int output_width,
+                                     int element_bytes) {
   if (rows <= 0 || rows > 256 || input_width <= 0 || output_width <= 0)
     return 0;
   LinearPlan plan{};
-  schedule_linear(&plan, rows, input_width, output_width, 0);
+  schedule_linear(&plan, rows, input_width, output_width, 0, element_bytes);
   return linear_partial_bytes(plan);
 }
 
 int make_linear_plan(LinearPlan *plan, const void *fp8_input, const void *fp8_weight, int rows,
-                     int input_width, int output_width, int requested_splits, const char **error) {
+                     int input_width, int output_width, int requested_splits, const char **error,
+                     int element_bytes) {
   const auto fail = [&](const char *message, int code) {
     if (error != nullptr)
       *error = message;
@@ -520,20 +543,23 @@ int make_linear_plan(LinearPlan *plan, const void *fp8_input, const void *fp8_we
       input_width <= 0 || output_width <= 0) {
     return fail("invalid FP8 linear shape", -1);
   }
+  if (element_bytes != 1 && element_bytes != 2)
+    return fail("invalid FP8 linear shape", -1);
   if (rows > 256)
     return fail("FP8 linear supports at most 256 rows", -2);
-  if (input_width % 16 != 0)
+  if (input_width * element_bytes % 16 != 0)
     return fail("FP8 linear input width must be a multiple of 16", -3);
   if ((reinterpret_cast<uintptr_t>(fp8_input) & 15U) != 0 ||
       (reinterpret_cast<uintptr_t>(fp8_weight) & 15U) != 0) {
     return fail("FP8 linear operands must be 16-byte aligned", -4);
   }
   LinearPlan result{};
-  schedule_linear(&result, rows, input_width, output_width, requested_splits);
-  if (!encode_byte_matrix(&result.weight_map, fp8_weight, static_cast<uint64_t>(input_width),
+  schedule_linear(&result, rows, input_width, output_width, requested_splits, element_bytes);
+  const uint64_t row_bytes = static_cast<uint64_t>(input_width) * element_bytes;
+  if (!encode_byte_matrix(&result.weight_map, fp8_weight, row_bytes,
                           static_cast<uint64_t>(output_width), tile_features) ||
-      !encode_byte_matrix(&result.input_map, fp8_input, static_cast<uint64_t>(input_width),
-                          static_cast<uint64_t>(rows), static_cast<uint32_t>(result.padded_rows))) {
+      !encode_byte_matrix(&result.input_map, fp8_input, row_bytes, static_cast<uint64_t>(rows),
+                          static_cast<uint32_t>(result.padded_rows))) {
     return fail("cuTensorMapEncodeTiled failed", -5);
   }
   *plan = result;

@@ -1,4 +1,6 @@
-// Host-side interface of the weight-streaming FP8 (e4m3) linear for up to 128 activation rows.
+// Host-side interface of the weight-streaming linear for up to 256 activation rows: e4m3 operands
+// with tensor scales (the decode / verify path) or bf16 operands without scales (the drafter's
+// default precision and BF16 prefill), one kernel template for both.
 #pragma once
 
 #include <cuda.h>
@@ -32,19 +34,24 @@ struct LinearPlan {
   int tail_tiles{0};
   int tail_splits{1};
   int tail_k_blocks_per_split{0};
+  int element_bytes{1};     // 1: e4m3 operands; 2: bf16 operands (scales are then ignored)
 };
 
 // Returns 0 or a negative error; `error` (may be null) receives a static message.
 // requested_splits <= 0 picks the split factor automatically.
+// element_bytes = 2 plans the same linear for bf16 input and weight (input_width a multiple of 8);
+// the launch functions then take null scales and multiply by one.
 int make_linear_plan(LinearPlan *plan, const void *fp8_input, const void *fp8_weight, int rows,
-                     int input_width, int output_width, int requested_splits, const char **error);
+                     int input_width, int output_width, int requested_splits, const char **error,
+                     int element_bytes = 1);
 
 // Bytes of fp32 scratch a plan needs when it splits K (0 when splits == 1):
 // [splits, rows, output_width].
 std::size_t linear_partial_bytes(const LinearPlan &plan);
 
 // The same figure from the shape alone (no tensor maps, usable without a device).
-std::size_t linear_partial_bytes_for(int rows, int input_width, int output_width);
+std::size_t linear_partial_bytes_for(int rows, int input_width, int output_width,
+                                     int element_bytes = 1);
 
 // y[row, n] = bf16(acc * x_scale * w_scale). When plan.splits > 1 the kernel writes fp32 partial
 // sums into `partial` and a second kernel sums, scales and rounds them into `output`.

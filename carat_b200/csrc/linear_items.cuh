@@ -13,7 +13,7 @@
 namespace carat_b200 {
 
 constexpr int tile_features = 128;    // UMMA M: output features per tile
-constexpr int tile_k_elements = 128;  // K elements per block of the item list
+constexpr int tile_k_elements = 128;  // K bytes per block of the item list (one swizzle atom)
 
 struct KernelArguments {
   const float *input_scale;
@@ -91,14 +91,15 @@ inline EncodeTiled encode_tiled_entry() {
 }
 
 inline void schedule_linear(LinearPlan *plan, int rows, int input_width, int output_width,
-                     int requested_splits) {
+                     int requested_splits, int element_bytes = 1) {
   LinearPlan &result = *plan;
   result.rows = rows;
   result.input_width = input_width;
   result.output_width = output_width;
+  result.element_bytes = element_bytes;
   result.padded_rows = rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
   result.tiles = (output_width + tile_features - 1) / tile_features;
-  result.k_blocks = (input_width + tile_k_elements - 1) / tile_k_elements;
+  result.k_blocks = (input_width * element_bytes + tile_k_elements - 1) / tile_k_elements;
   result.ctas = device_multiprocessors();
   int splits = requested_splits;
   if (splits <= 0) {

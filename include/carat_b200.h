@@ -106,6 +106,31 @@ CARAT_B200_API int carat_b200_fp8_linear_check(const void *fp8_input, const floa
                                 void *bf16_output, int rows, int input_width, int output_width,
                                 void *stream);
 
+/* BF16 linear ----------------------------------------------------------------------------------- */
+
+/* output[rows, output_width] = bf16(input_bf16[rows, input_width] . weight_bf16[output_width,
+ * input_width]^T) with fp32 accumulation: the weight-streaming kernel of carat_b200_fp8_linear
+ * with 16-bit operands (tcgen05 kind::f16) and no scales. rows <= 256, input_width a multiple of
+ * 8, operands 16-byte aligned; callers with more rows (prefill chunks) call it per 256 rows.
+ * `workspace` as for carat_b200_fp8_linear, sized by carat_b200_bf16_linear_workspace_bytes().
+ * Replaces carat::Bf16Linear::run (include/carat/linear.h:13-26, cuda/linear.cu:534-643: cuBLAS),
+ * the linear of the drafter's default precision (cuda/assistant_runner.cu:147-160) and of BF16
+ * prefill (cuda/layer_runner.cu:611-728). */
+CARAT_B200_API int carat_b200_bf16_linear(const void *bf16_input, const void *bf16_weight,
+                                          void *bf16_output, int rows, int input_width,
+                                          int output_width, void *workspace,
+                                          size_t workspace_bytes, void *stream);
+
+CARAT_B200_API size_t carat_b200_bf16_linear_workspace_bytes(int rows, int input_width,
+                                                             int output_width);
+
+/* Fused BF16 LM head: device_tokens[row] = argmax_n bf16(input[row] . weight[n]), ties to the
+ * lowest n, logits never stored. Replaces Bf16Linear::run + argmax_bf16_rows as the drafter's
+ * default LM head does them (cuda/assistant_runner.cu:313-318). */
+CARAT_B200_API int carat_b200_bf16_linear_argmax(const void *bf16_input, const void *bf16_weight,
+                                                 int *device_tokens, void *device_keys, int rows,
+                                                 int input_width, int output_width, void *stream);
+
 /* INT4 weight-only linear (W4A16) --------------------------------------------------------------- */
 
 /* Quantises a bf16 [output_width, input_width] weight in K-local groups of `group_width` (128 or
