@@ -190,7 +190,7 @@ def build_model(seed):
     a_weights = carat_b200.DeviceWeightArena(a_bf16)
     torch.cuda.synchronize()
     runner = carat_b200.Gemma4BatchModelRunner(config, weights, SLOTS, MAX_CONTEXT, fp8, a_weights,
-                                               a_fp8, assistant_config)
+                                               a_fp8, assistant_config, assistant_fp8_mode="all")
     return config, runner, fp8
 
 

@@ -41,6 +41,15 @@ class Int4MlpLayer(Structure):
                 ("down_codes", c_void_p), ("down_scales", c_void_p)]
 
 
+class AssistantBf16Layer(Structure):
+    _fields_ = [("q", c_void_p), ("o", c_void_p), ("gate_up", c_void_p), ("down", c_void_p)]
+
+
+class AssistantBf16Weights(Structure):
+    _fields_ = [("token_embedding", c_void_p), ("pre_projection", c_void_p),
+                ("post_projection", c_void_p), ("layers", POINTER(AssistantBf16Layer))]
+
+
 class ModelWeights(Structure):
     _fields_ = [("token_embedding", c_void_p), ("token_embedding_fp8", c_void_p),
                 ("token_embedding_scale", c_void_p), ("final_norm", c_void_p),
@@ -106,6 +115,7 @@ SIGNATURES = {
                                      POINTER(AssistantConfig), POINTER(AssistantWeights),
                                      POINTER(c_void_p)]),
     "carat_b200_runner_destroy": (None, [_P]),
+    "carat_b200_runner_set_assistant_precision": (_I, [_P, _I, POINTER(AssistantBf16Weights)]),
     "carat_b200_runner_use_int4_mlp": (_I, [_P, POINTER(Int4MlpLayer), _I, _I]),
     "carat_b200_runner_verify_greedy_proposals": (_I, [_P, _IP, _I, _I, _IP, _IP, _IP, _I, _IP,
                                                       _IP]),

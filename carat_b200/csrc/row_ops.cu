@@ -304,6 +304,11 @@ row_kernel(RowArguments a) {
             a.row_indices != nullptr ? static_cast<size_t>(a.row_indices[row]) : row;
         values[chunk] = load_bf16x8(a.input + source_row * half + (column - half));
       }
+      if (a.second_out != nullptr) {   // bf16 consumer: keep the concatenated row
+        uint4 packed;
+        (void)round_bf16x8(values[chunk], &packed);
+        *reinterpret_cast<uint4 *>(a.second_out + row * width + column) = packed;
+      }
     } else if constexpr (mode == RowMode::geglu) {
       const __nv_bfloat16 *packed_row = a.input + row * 2 * width;
       const Pack8 gate = load_bf16x8(packed_row + column);
@@ -362,10 +367,11 @@ row_kernel(RowArguments a) {
     } else {
       values[chunk] = load_source(a, row, column, rows, partial_scale);
       if constexpr (mode == RowMode::plain) {
-        if (a.first_out != nullptr) {
+        __nv_bfloat16 *rows_out = a.first_out != nullptr ? a.first_out : a.second_out;
+        if (rows_out != nullptr) {
           uint4 packed;
           (void)round_bf16x8(values[chunk], &packed);
-          *reinterpret_cast<uint4 *>(a.first_out + row * width + column) = packed;
+          *reinterpret_cast<uint4 *>(rows_out + row * width + column) = packed;
         }
       }
       if constexpr (two_norms)
@@ -576,8 +582,9 @@ int launch_rows_chunks(const RowArguments &arguments, int ctas, cudaStream_t str
 template <RowMode mode> int launch_rows(RowArguments arguments, int rows, cudaStream_t stream) {
   const bool quantised = arguments.fp8_output != nullptr && arguments.scale != nullptr &&
                          arguments.amax_bits != nullptr;
-  const bool bf16_only = arguments.fp8_output == nullptr && arguments.second_out != nullptr &&
-                         (mode == RowMode::post_attention || mode == RowMode::geglu);
+  // Without an e4m3 target the call stops after the bf16 rows, which must then go somewhere.
+  const bool bf16_only = arguments.fp8_output == nullptr &&
+                         (arguments.second_out != nullptr || arguments.first_out != nullptr);
   if (rows <= 0 || arguments.width <= 0 || arguments.width % 8 != 0 || !(quantised || bf16_only))
     return -1;
   int parts = 1;

@@ -200,6 +200,13 @@ struct carat_b200_runner {
       a_previous_hidden, a_scratch_words, a_scales, a_tokens, a_proposals;
   int a_amax_words{0};
   std::map<int, StepPlans> draft_plans;
+  // ---- drafter precision (CARAT_B200_ASSISTANT_FP8_*): bf16 matrices and their plans
+  int assistant_mode{CARAT_B200_ASSISTANT_FP8_ALL};
+  bool assistant_has_fp8{false};
+  carat_b200_assistant_bf16_weights assistant_bf16{};
+  std::vector<carat_b200_assistant_bf16_layer> assistant_bf16_layers;
+  DeviceBuffer a_concat, a_normed, a_pre_mlp, a_activated;   // bf16 inputs of the bf16 linears
+  std::map<int, StepPlans> draft_plans_bf16;
 
   ~carat_b200_runner() {
     if (start_event != nullptr)
@@ -374,11 +381,14 @@ void build_runner(Runner &runner, const carat_b200_model_config &config,
         assistant->intermediate_size <= 0 || assistant->intermediate_size % 16 != 0 ||
         assistant->query_heads <= 0 || assistant->layer_count <= 0 ||
         assistant->layer_global == nullptr || assistant_weights->layers == nullptr ||
-        assistant_weights->token_embedding == nullptr ||
-        assistant_weights->pre_projection == nullptr ||
-        assistant_weights->post_projection == nullptr || assistant_weights->final_norm == nullptr) {
+        assistant_weights->final_norm == nullptr) {
       throw Failure{"invalid assistant shape"};
     }
+    // e4m3 matrices are optional: without them only the bf16 precision can be selected.
+    runner.assistant_has_fp8 = assistant_weights->token_embedding != nullptr &&
+                               assistant_weights->pre_projection != nullptr &&
+                               assistant_weights->post_projection != nullptr;
+    runner.assistant_mode = runner.assistant_has_fp8 ? CARAT_B200_ASSISTANT_FP8_ALL : -1;
     runner.has_assistant = true;
     runner.assistant = *assistant;
     runner.assistant_kinds.assign(assistant->layer_global,
@@ -419,6 +429,10 @@ void build_runner(Runner &runner, const carat_b200_model_config &config,
     runner.a_amax_words = 2 + 4 * assistant->layer_count;
     runner.a_scratch_words.allocate(static_cast<size_t>(runner.a_amax_words + 2 * batch) * 4, true);
     runner.a_scales.allocate(static_cast<size_t>(runner.a_amax_words) * 4, true);
+    runner.a_concat.allocate(static_cast<size_t>(batch) * 2 * hidden * 2);
+    runner.a_normed.allocate(a_row_hidden);
+    runner.a_pre_mlp.allocate(a_row_hidden);
+    runner.a_activated.allocate(static_cast<size_t>(batch) * assistant->intermediate_size * 2);
     runner.a_tokens.allocate(sizeof(int) * 4 * batch, true);
     runner.a_proposals.allocate(sizeof(int) * batch * maximum_depth, true);
   }
@@ -511,6 +525,55 @@ StepPlans &draft_plans_for(Runner &runner, int rows) {
   if (most_partial > runner.split_partials.bytes())
     throw Failure{"split-K workspace is too small for this assistant shape"};
   return runner.draft_plans.emplace(rows, std::move(plans)).first->second;
+}
+
+LinearPlan plan_bf16_linear(const void *input, const void *weight, int rows, int in, int out,
+                            int splits) {
+  LinearPlan plan;
+  const char *message = "invalid BF16 linear shape";
+  if (make_linear_plan(&plan, input, weight, rows, in, out, splits, &message, 2) != 0)
+    throw Failure{"invalid BF16 linear shape"};
+  return plan;
+}
+
+// The drafter's linears over bf16 weights and activations; the LM head stays the e4m3 plan of
+// draft_plans_for() in the lm_head mode.
+StepPlans &draft_plans_bf16_for(Runner &runner, int rows) {
+  const auto found = runner.draft_plans_bf16.find(rows);
+  if (found != runner.draft_plans_bf16.end())
+    return found->second;
+  StepPlans plans;
+  const int hidden = runner.config.hidden_size;
+  const int a_hidden = runner.assistant.hidden_size;
+  const int intermediate = runner.assistant.intermediate_size;
+  const auto &bf16 = runner.assistant_bf16;
+  size_t most_partial = 0;
+  for (int index = 0; index < runner.assistant.layer_count; ++index) {
+    const auto &weights = runner.assistant_bf16_layers[static_cast<size_t>(index)];
+    const int query_width = runner.assistant.query_heads * shared_layer(runner, index).shape.head_dim;
+    LayerPlans entry;
+    entry.qkv = plan_bf16_linear(runner.a_normed.get(), weights.q, rows, a_hidden, query_width, 1);
+    entry.o = plan_bf16_linear(runner.a_attention_out.get(), weights.o, rows, query_width,
+                               a_hidden, 0);
+    entry.gate_up = plan_bf16_linear(runner.a_pre_mlp.get(), weights.gate_up, rows, a_hidden,
+                                     2 * intermediate, 0);
+    entry.down = plan_bf16_linear(runner.a_activated.get(), weights.down, rows, intermediate,
+                                  a_hidden, 0);
+    for (const LinearPlan *plan : {&entry.qkv, &entry.o, &entry.gate_up, &entry.down})
+      most_partial = std::max(most_partial, linear_partial_bytes(*plan));
+    plans.layers.push_back(entry);
+  }
+  plans.head = plan_bf16_linear(runner.a_final_hidden.get(), bf16.token_embedding, rows, a_hidden,
+                                runner.config.vocabulary_size, 1);
+  plans.pre = plan_bf16_linear(runner.a_concat.get(), bf16.pre_projection, rows, 2 * hidden,
+                               a_hidden, 0);
+  plans.post = plan_bf16_linear(runner.a_final_hidden.get(), bf16.post_projection, rows, a_hidden,
+                                hidden, 1);
+  most_partial = std::max({most_partial, linear_partial_bytes(plans.pre),
+                           linear_partial_bytes(plans.post)});
+  if (most_partial > runner.split_partials.bytes())
+    throw Failure{"split-K workspace is too small for this assistant shape"};
+  return runner.draft_plans_bf16.emplace(rows, std::move(plans)).first->second;
 }
 
 // Runs a linear into bf16 `output`, or leaves split-K partials for a fused consumer. Returns the
@@ -955,7 +1018,12 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
     host_forced[row] = forced != nullptr ? forced[row] : 0;
     longest = std::max(longest, host_context[row] + 1);
   }
-  StepPlans &plans = draft_plans_for(runner, requests);
+  if (runner.assistant_mode < 0)
+    throw Failure{"assistant FP8 mode requires quantized assistant weights"};
+  // The e4m3 plans also serve the lm_head mode (its LM head); without e4m3 matrices only the
+  // bf16 plans exist.
+  StepPlans no_fp8_plans;
+  StepPlans &plans = runner.assistant_has_fp8 ? draft_plans_for(runner, requests) : no_fp8_plans;
   cudaStream_t stream = runner.stream;
   int *device = runner.a_tokens.get<int>();
   int *device_tokens = device;
@@ -979,6 +1047,7 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
   };
   int *draft_tokens = runner.a_proposals.get<int>();  // [depth][requests]
 
+  if (runner.assistant_mode == CARAT_B200_ASSISTANT_FP8_ALL) {
   for (int draft_index = 0; draft_index < depth; ++draft_index) {
     require_cuda(cudaMemsetAsync(amax, 0, sizeof(int) * (runner.a_amax_words + 2 * runner.batch),
                                  stream),
@@ -1106,6 +1175,147 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
                runner.assistant_weights.post_projection_scale, runner.a_previous_hidden.get(),
                false);
   }
+  } else {
+  // bf16 precision (the reference's default, and its lm_head mode): activations stay bf16 from
+  // one linear to the next, so the row kernels stop after their bf16 rows and nothing is
+  // quantised, except the final-normed hidden rows when the LM head alone runs in e4m3.
+  const bool head_fp8 = runner.assistant_mode == CARAT_B200_ASSISTANT_FP8_LM_HEAD;
+  StepPlans &wide = draft_plans_bf16_for(runner, requests);
+  const auto rows_only = [](void *rows_out) {
+    return QuantTarget{nullptr, nullptr, nullptr, nullptr, rows_out};
+  };
+  const int head_word = 0;
+  for (int draft_index = 0; draft_index < depth; ++draft_index) {
+    require_cuda(cudaMemsetAsync(amax, 0, sizeof(int) * (runner.a_amax_words + 2 * runner.batch),
+                                 stream),
+                 "clear assistant scratch");
+    const int *input_tokens =
+        draft_index == 0 ? device_tokens : draft_tokens + (draft_index - 1) * requests;
+    require_launch(launch_embed_concat_quant(
+                       runner.weights.token_embedding, input_tokens, config.vocabulary_size,
+                       draft_index == 0 ? runner.hidden_by_slot.get()
+                                        : runner.a_previous_hidden.get(),
+                       draft_index == 0 ? device_slots : nullptr, rows_only(runner.a_concat.get()),
+                       requests, hidden, stream),
+                   "assistant input");
+    runner.launches += 1;
+    void *current = runner.a_hidden_a.get();
+    void *other = runner.a_hidden_b.get();
+    run_linear(runner, wide.pre, nullptr, nullptr, current, false);
+    require_launch(launch_norm_quant(current, runner.assistant_layers[0].input_norm,
+                                     runner.a_normed.get(), QuantTarget{}, requests, a_hidden,
+                                     epsilon, stream),
+                   "assistant input norm");
+    runner.launches += 1;
+    for (int index = 0; index < assistant.layer_count; ++index) {
+      const auto &w = runner.assistant_layers[static_cast<size_t>(index)];
+      const LayerPlans &plan = wide.layers[static_cast<size_t>(index)];
+      const LayerState &shared = shared_layer(runner, index);
+      const auto &shape = shared.shape;
+      const int query_width = assistant.query_heads * shape.head_dim;
+      const RopeTable &rope = *runner.rope_tables[static_cast<size_t>(shared.rope)];
+      run_linear(runner, plan.qkv, nullptr, nullptr, runner.a_projected.get(), false);
+      require_launch(launch_query_post(runner.a_projected.get(), w.q_norm, rope.cosine.get(),
+                                       rope.sine.get(), runner.a_queries.get(), device_context,
+                                       draft_index, requests, assistant.query_heads,
+                                       shape.head_dim, runner.maximum_context, epsilon, stream),
+                     "assistant query post-processing");
+      runner.launches += 1;
+      AttentionArguments attention{};
+      attention.queries = runner.a_queries.get();
+      attention.key_cache = shared.keys();
+      attention.value_cache = shared.values();
+      attention.slot_stride = shared.slot_stride;
+      attention.head_stride = shared.head_stride;
+      attention.positions = device_context;
+      attention.slots = device_slots;
+      attention.scores = runner.a_scores.get();
+      attention.output = runner.a_attention_out.get();
+      attention.chunk_partials = runner.a_attention_partials.get<float>();
+      attention.requests = requests;
+      attention.depth = 1;
+      attention.query_heads = assistant.query_heads;
+      attention.kv_heads = shape.kv_heads;
+      attention.head_dim = shape.head_dim;
+      attention.capacity = shared.capacity;
+      attention.window = shape.global_attention ? 0 : config.sliding_window;
+      attention.draft = 1;
+      attention.max_cache_rows = std::min(longest, shared.capacity);
+      attention.score_stride = runner.score_stride_global;
+      attention.chunk_keys = global_chunk_keys;
+      attention.chunks = attention_chunks(attention.max_cache_rows, global_chunk_keys);
+      attention.stats = runner.attention_stats.get<float2>();
+      attention.stats_stride = runner.stats_stride;
+      attention.request_chunks = runner.request_chunks.get<int>();
+      attention.maps = draft_attention_maps(runner, index);
+      require_launch(attention.maps != nullptr ? launch_attention_tc(attention, stream)
+                                               : launch_attention_simt(attention, stream),
+                     "assistant attention");
+      runner.launches += attention.maps != nullptr ? attention_tc_launches(attention) : 3;
+      if (attention.chunks > 1) {
+        // Key-chunk partial outputs: summed and rounded into the bf16 rows the O linear reads.
+        const bool counted = attention.maps != nullptr;
+        require_launch(launch_quant(nullptr, runner.a_attention_partials.get<float>(),
+                                    attention.chunks,
+                                    counted ? runner.request_chunks.get<int>() : nullptr, 1,
+                                    rows_only(runner.a_attention_out.get()), requests,
+                                    query_width, stream),
+                       "assistant attention rows");
+        runner.launches += 1;
+      }
+      const PartialSource o_source =
+          run_linear(runner, plan.o, nullptr, nullptr, runner.a_linear_out.get(), true);
+      require_launch(launch_post_attention_norms_quant(
+                         runner.a_linear_out.get(), o_source, w.post_attention_norm, current,
+                         w.pre_mlp_norm, runner.a_residual.get(),
+                         rows_only(runner.a_pre_mlp.get()), requests, a_hidden, epsilon, stream),
+                     "assistant post-attention norms");
+      runner.launches += 1;
+      run_linear(runner, plan.gate_up, nullptr, nullptr, runner.a_gate_up.get(), false);
+      require_launch(launch_geglu_quant(runner.a_gate_up.get(), TailSource{},
+                                        rows_only(runner.a_activated.get()), requests,
+                                        assistant.intermediate_size, stream),
+                     "assistant GeGLU");
+      runner.launches += 1;
+      const PartialSource down_source =
+          run_linear(runner, plan.down, nullptr, nullptr, runner.a_linear_out.get(), true);
+      const bool last = index + 1 == assistant.layer_count;
+      const void *next_norm = last ? runner.assistant_weights.final_norm
+                                   : runner.assistant_layers[static_cast<size_t>(index) + 1].input_norm;
+      // The normed rows feed the next layer's Q linear, or (last layer) are the final hidden
+      // rows; those are also quantised when the LM head runs in e4m3.
+      const QuantTarget next_target = (last && head_fp8) ? target(head_word) : QuantTarget{};
+      require_launch(launch_layer_output_norm_quant(
+                         runner.a_linear_out.get(), down_source, w.post_mlp_norm,
+                         runner.a_residual.get(), w.scalar, other, next_norm,
+                         last ? runner.a_final_hidden.get() : runner.a_normed.get(), next_target,
+                         requests, a_hidden, epsilon, stream),
+                     "assistant layer output");
+      runner.launches += 1;
+      std::swap(current, other);
+    }
+    int *step_tokens = draft_tokens + draft_index * requests;
+    if (draft_index == 0 && forced != nullptr) {
+      require_cuda(cudaMemcpyAsync(step_tokens, device_forced, sizeof(int) * requests,
+                                   cudaMemcpyDeviceToDevice, stream),
+                   "select forced assistant first tokens");
+    } else {
+      if (head_fp8) {
+        require_launch(launch_linear_argmax(plans.head, scales + head_word,
+                                            runner.assistant_weights.token_embedding_scale, best,
+                                            runner.device_error, stream),
+                       "assistant LM head");
+      } else {
+        require_launch(launch_linear_argmax(wide.head, nullptr, nullptr, best,
+                                            runner.device_error, stream),
+                       "assistant LM head");
+      }
+      require_launch(launch_unpack_best(best, step_tokens, requests, stream), "assistant argmax");
+      runner.launches += 2;
+    }
+    run_linear(runner, wide.post, nullptr, nullptr, runner.a_previous_hidden.get(), false);
+  }
+  }
   require_cuda(cudaEventRecord(runner.stop_event, stream), "record draft end");
   int *host_results = runner.host_results.get<int>();
   require_cuda(cudaMemcpyAsync(host_results, draft_tokens, sizeof(int) * depth * requests,
@@ -1226,6 +1436,39 @@ extern "C" int carat_b200_runner_prefill_slot_fp8(carat_b200_runner *runner, int
                   CARAT_B200_VERIFY_ASSUME_MATCH, true, &accepted, &next);
       *next_token = next;
     }
+  });
+}
+
+extern "C" int carat_b200_runner_set_assistant_precision(
+    carat_b200_runner *runner, int mode, const carat_b200_assistant_bf16_weights *bf16) {
+  return guarded([&] {
+    if (runner == nullptr || !runner->has_assistant)
+      throw Failure{"assistant is not configured or draft batch is invalid"};
+    if (mode != CARAT_B200_ASSISTANT_FP8_OFF && mode != CARAT_B200_ASSISTANT_FP8_LM_HEAD &&
+        mode != CARAT_B200_ASSISTANT_FP8_ALL) {
+      throw Failure{"CARAT_ASSISTANT_FP8_MODE must be off, lm_head or all"};
+    }
+    if (mode != CARAT_B200_ASSISTANT_FP8_OFF && !runner->assistant_has_fp8)
+      throw Failure{"assistant FP8 mode requires quantized assistant weights"};
+    if (mode != CARAT_B200_ASSISTANT_FP8_ALL) {
+      if (bf16 == nullptr || bf16->layers == nullptr || bf16->token_embedding == nullptr ||
+          bf16->pre_projection == nullptr || bf16->post_projection == nullptr) {
+        throw Failure{"invalid assistant shape"};
+      }
+      for (int index = 0; index < runner->assistant.layer_count; ++index) {
+        const carat_b200_assistant_bf16_layer &layer = bf16->layers[index];
+        if (layer.q == nullptr || layer.o == nullptr || layer.gate_up == nullptr ||
+            layer.down == nullptr) {
+          throw Failure{"invalid assistant shape"};
+        }
+      }
+      runner->assistant_bf16 = *bf16;
+      runner->assistant_bf16_layers.assign(bf16->layers,
+                                           bf16->layers + runner->assistant.layer_count);
+      runner->assistant_bf16.layers = runner->assistant_bf16_layers.data();
+      runner->draft_plans_bf16.clear();
+    }
+    runner->assistant_mode = mode;
   });
 }
 

@@ -8,6 +8,7 @@ here only to own device memory.
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -17,6 +18,7 @@ from . import capi
 from .capi import CaratError, check, int_array
 
 VERIFY_ASSUME_MATCH = 1
+ASSISTANT_FP8_MODES = {"off": 0, "lm_head": 1, "all": 2}   # CARAT_ASSISTANT_FP8_MODE values
 
 
 # --------------------------------------------------------------------------- configuration
@@ -232,7 +234,11 @@ class Gemma4BatchModelRunner:
                  maximum_context: int, fp8_weights: Optional[Fp8WeightArena] = None,
                  assistant_weights: Optional[DeviceWeightArena] = None,
                  assistant_fp8_weights: Optional[Fp8WeightArena] = None,
-                 assistant_config: Optional[Gemma4AssistantConfig] = None):
+                 assistant_config: Optional[Gemma4AssistantConfig] = None,
+                 assistant_fp8_mode: Optional[str] = None):
+        """assistant_fp8_mode: "off" (every drafter linear in bf16), "lm_head" or "all"; None reads
+        CARAT_ASSISTANT_FP8_MODE like the reference does and falls back to its default, "off"
+        (cuda/assistant_runner.cu:29-43)."""
         self._library = capi.library()
         self._handle = ctypes.c_void_p()
         if fp8_weights is None:
@@ -257,8 +263,12 @@ class Gemma4BatchModelRunner:
             layer_weights)
         assistant_struct = None
         assistant_weight_struct = None
+        if assistant_fp8_mode is None:
+            assistant_fp8_mode = os.environ.get("CARAT_ASSISTANT_FP8_MODE", "off")
+        if assistant_fp8_mode not in ASSISTANT_FP8_MODES:
+            raise CaratError("CARAT_ASSISTANT_FP8_MODE must be off, lm_head or all")
         if assistant_weights is not None:
-            if assistant_fp8_weights is None:
+            if assistant_fp8_mode != "off" and assistant_fp8_weights is None:
                 raise CaratError("assistant FP8 mode requires quantized assistant weights")
             assistant_config = assistant_config or Gemma4AssistantConfig()
             kinds = (ctypes.c_int32 * len(assistant_config.layers))(
@@ -272,11 +282,16 @@ class Gemma4BatchModelRunner:
                 assistant_config.query_heads, len(assistant_config.layers), kinds,
                 assistant_config.rms_norm_epsilon)
             fp8 = assistant_fp8_weights
-            assistant_weight_struct = capi.AssistantWeights(
-                fp8.at("token_embedding").data_ptr(), fp8.scale("token_embedding").data_ptr(),
-                fp8.at("pre_projection").data_ptr(), fp8.scale("pre_projection").data_ptr(),
-                fp8.at("post_projection").data_ptr(), fp8.scale("post_projection").data_ptr(),
-                assistant_weights.at("final_norm").data_ptr(), a_layers)
+            if fp8 is not None:
+                assistant_weight_struct = capi.AssistantWeights(
+                    fp8.at("token_embedding").data_ptr(), fp8.scale("token_embedding").data_ptr(),
+                    fp8.at("pre_projection").data_ptr(), fp8.scale("pre_projection").data_ptr(),
+                    fp8.at("post_projection").data_ptr(), fp8.scale("post_projection").data_ptr(),
+                    assistant_weights.at("final_norm").data_ptr(), a_layers)
+            else:
+                assistant_weight_struct = capi.AssistantWeights(
+                    None, None, None, None, None, None,
+                    assistant_weights.at("final_norm").data_ptr(), a_layers)
             self._keep += [kinds, a_layers]
         self._keep += [shapes, layer_weights]
         check(self._library.carat_b200_runner_create(
@@ -284,12 +299,44 @@ class Gemma4BatchModelRunner:
             ctypes.byref(assistant_struct) if assistant_struct is not None else None,
             ctypes.byref(assistant_weight_struct) if assistant_weight_struct is not None else None,
             ctypes.byref(self._handle)))
+        self._assistant_weights = assistant_weights
+        self._assistant_layer_count = len(assistant_config.layers) if assistant_config else 0
+        if assistant_weights is not None:
+            self.set_assistant_fp8_mode(assistant_fp8_mode)
+
+    def set_assistant_fp8_mode(self, mode: str) -> None:
+        """Drafter precision, the reference's CARAT_ASSISTANT_FP8_MODE: "off" and "lm_head" run the
+        drafter's linears on the bf16 matrices of the assistant's DeviceWeightArena."""
+        if mode not in ASSISTANT_FP8_MODES:
+            raise CaratError("CARAT_ASSISTANT_FP8_MODE must be off, lm_head or all")
+        bf16 = None
+        if mode != "all":
+            arena = self._assistant_weights
+            layers = (capi.AssistantBf16Layer * self._assistant_layer_count)()
+            for index in range(self._assistant_layer_count):
+                prefix = f"layer.{index}."
+                layers[index] = capi.AssistantBf16Layer(
+                    arena.at(prefix + "q").data_ptr(), arena.at(prefix + "o").data_ptr(),
+                    arena.at(prefix + "gate_up").data_ptr(), arena.at(prefix + "down").data_ptr())
+            bf16 = capi.AssistantBf16Weights(arena.at("token_embedding").data_ptr(),
+                                             arena.at("pre_projection").data_ptr(),
+                                             arena.at("post_projection").data_ptr(), layers)
+            self._keep.append(layers)
+        check(self._library.carat_b200_runner_set_assistant_precision(
+            self._handle, ASSISTANT_FP8_MODES[mode],
+            ctypes.byref(bf16) if bf16 is not None else None))
+        self.assistant_fp8_mode = mode
 
     @staticmethod
     def _layer_weights(weights, fp8, prefix, projection, has_key_norm) -> capi.LayerWeights:
         def bf16(name):
             return weights.at(prefix + name).data_ptr()
 
+        if fp8 is None:     # a drafter without e4m3 matrices: norms only
+            return capi.LayerWeights(
+                bf16("input_norm"), bf16("q_norm"), bf16("k_norm") if has_key_norm else None,
+                None, None, None, None, bf16("post_attention_norm"), bf16("pre_mlp_norm"),
+                None, None, None, None, bf16("post_mlp_norm"), bf16("scalar"))
         return capi.LayerWeights(
             bf16("input_norm"), bf16("q_norm"), bf16("k_norm") if has_key_norm else None,
             fp8.at(prefix + projection).data_ptr(), fp8.scale(prefix + projection).data_ptr(),

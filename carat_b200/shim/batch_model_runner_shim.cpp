@@ -15,6 +15,7 @@
 
 #include "carat_b200.h"
 
+#include <cstdlib>
 #include <stdexcept>
 #include <string>
 #include <vector>
@@ -31,6 +32,33 @@ void check(int status) {
 
 [[noreturn]] void not_provided(const char *method) {
   throw std::runtime_error(std::string(method) + " is not provided by carat-b200");
+}
+
+// Norm vectors only: a drafter that runs in bf16 may come without an Fp8WeightArena.
+carat_b200_layer_weights norm_weights(const DeviceWeightArena &bf16, const std::string &prefix) {
+  carat_b200_layer_weights weights{};
+  weights.input_norm = bf16.at(prefix + "input_norm");
+  weights.q_norm = bf16.at(prefix + "q_norm");
+  weights.post_attention_norm = bf16.at(prefix + "post_attention_norm");
+  weights.pre_mlp_norm = bf16.at(prefix + "pre_mlp_norm");
+  weights.post_mlp_norm = bf16.at(prefix + "post_mlp_norm");
+  weights.scalar = bf16.at(prefix + "scalar");
+  return weights;
+}
+
+// CARAT_ASSISTANT_FP8_MODE, read where the reference reads it (cuda/assistant_runner.cu:31-43).
+int assistant_fp8_mode(const Fp8WeightArena *weights) {
+  const char *configured = std::getenv("CARAT_ASSISTANT_FP8_MODE");
+  const std::string mode = configured == nullptr ? "off" : configured;
+  if (mode == "off")
+    return CARAT_B200_ASSISTANT_FP8_OFF;
+  if (weights == nullptr)
+    throw std::runtime_error("assistant FP8 mode requires quantized assistant weights");
+  if (mode == "lm_head")
+    return CARAT_B200_ASSISTANT_FP8_LM_HEAD;
+  if (mode == "all")
+    return CARAT_B200_ASSISTANT_FP8_ALL;
+  throw std::runtime_error("CARAT_ASSISTANT_FP8_MODE must be off, lm_head or all");
 }
 
 carat_b200_layer_weights layer_weights(const DeviceWeightArena &bf16, const Fp8WeightArena &fp8,
@@ -97,20 +125,27 @@ Gemma4BatchModelRunner::Gemma4BatchModelRunner(const Gemma4Config &config,
                                                      1.0e-6F};
   std::vector<carat_b200_layer_weights> assistant_layers;
   carat_b200_assistant_weights assistant{};
-  const bool with_assistant = assistant_weights != nullptr && assistant_fp8_weights != nullptr;
+  const bool with_assistant = assistant_weights != nullptr;
+  int assistant_mode = CARAT_B200_ASSISTANT_FP8_OFF;
   if (with_assistant) {
-    for (int index = 0; index < 4; ++index)
-      assistant_layers.push_back(layer_weights(*assistant_weights, *assistant_fp8_weights,
-                                               "layer." + std::to_string(index) + ".", true));
-    assistant = carat_b200_assistant_weights{
-        assistant_fp8_weights->at("token_embedding"),
-        assistant_fp8_weights->scale("token_embedding"),
-        assistant_fp8_weights->at("pre_projection"),
-        assistant_fp8_weights->scale("pre_projection"),
-        assistant_fp8_weights->at("post_projection"),
-        assistant_fp8_weights->scale("post_projection"),
-        assistant_weights->at("final_norm"),
-        assistant_layers.data()};
+    assistant_mode = assistant_fp8_mode(assistant_fp8_weights);
+    for (int index = 0; index < 4; ++index) {
+      const std::string prefix = "layer." + std::to_string(index) + ".";
+      assistant_layers.push_back(
+          assistant_fp8_weights != nullptr
+              ? layer_weights(*assistant_weights, *assistant_fp8_weights, prefix, true)
+              : norm_weights(*assistant_weights, prefix));
+    }
+    assistant.final_norm = assistant_weights->at("final_norm");
+    assistant.layers = assistant_layers.data();
+    if (assistant_fp8_weights != nullptr) {
+      assistant.token_embedding = assistant_fp8_weights->at("token_embedding");
+      assistant.token_embedding_scale = assistant_fp8_weights->scale("token_embedding");
+      assistant.pre_projection = assistant_fp8_weights->at("pre_projection");
+      assistant.pre_projection_scale = assistant_fp8_weights->scale("pre_projection");
+      assistant.post_projection = assistant_fp8_weights->at("post_projection");
+      assistant.post_projection_scale = assistant_fp8_weights->scale("post_projection");
+    }
   }
   check(carat_b200_runner_create(&model, &model_weights, batch, maximum_context,
                                  with_assistant ? &assistant_config : nullptr,
@@ -118,6 +153,28 @@ Gemma4BatchModelRunner::Gemma4BatchModelRunner(const Gemma4Config &config,
                                  &implementation_->handle));
   implementation_->batch = batch;
   implementation_->maximum_context = maximum_context;
+  if (with_assistant) {
+    // The drafter's precision follows the reference's switch; its default runs every drafter
+    // linear on the bf16 matrices of the assistant's DeviceWeightArena.
+    std::vector<carat_b200_assistant_bf16_layer> bf16_layers;
+    carat_b200_assistant_bf16_weights bf16{};
+    if (assistant_mode != CARAT_B200_ASSISTANT_FP8_ALL) {
+      for (int index = 0; index < 4; ++index) {
+        const std::string prefix = "layer." + std::to_string(index) + ".";
+        bf16_layers.push_back({assistant_weights->at(prefix + "q"),
+                               assistant_weights->at(prefix + "o"),
+                               assistant_weights->at(prefix + "gate_up"),
+                               assistant_weights->at(prefix + "down")});
+      }
+      bf16.token_embedding = assistant_weights->at("token_embedding");
+      bf16.pre_projection = assistant_weights->at("pre_projection");
+      bf16.post_projection = assistant_weights->at("post_projection");
+      bf16.layers = bf16_layers.data();
+    }
+    check(carat_b200_runner_set_assistant_precision(
+        implementation_->handle, assistant_mode,
+        assistant_mode != CARAT_B200_ASSISTANT_FP8_ALL ? &bf16 : nullptr));
+  }
 }
 
 Gemma4BatchModelRunner::~Gemma4BatchModelRunner() {

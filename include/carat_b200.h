@@ -384,6 +384,27 @@ typedef struct carat_b200_assistant_weights {
   const carat_b200_layer_weights *layers;
 } carat_b200_assistant_weights;
 
+/* The drafter's matrices in bf16 (carat::DeviceWeightArena::at of the assistant plan,
+ * src/weight_plan.cpp:84-128), needed for the reference's default drafter precision. */
+typedef struct carat_b200_assistant_bf16_layer {
+  const void *q;
+  const void *o;
+  const void *gate_up;
+  const void *down;
+} carat_b200_assistant_bf16_layer;
+
+typedef struct carat_b200_assistant_bf16_weights {
+  const void *token_embedding;   /* bf16 [vocabulary, hidden] */
+  const void *pre_projection;    /* bf16 [hidden, 2 * target hidden] */
+  const void *post_projection;   /* bf16 [target hidden, hidden] */
+  const carat_b200_assistant_bf16_layer *layers;
+} carat_b200_assistant_bf16_weights;
+
+/* Values of CARAT_ASSISTANT_FP8_MODE in the reference (cuda/assistant_runner.cu:29-43). */
+#define CARAT_B200_ASSISTANT_FP8_OFF 0      /* every drafter linear in bf16: the reference's default */
+#define CARAT_B200_ASSISTANT_FP8_LM_HEAD 1  /* bf16, except the drafter's LM head in e4m3 */
+#define CARAT_B200_ASSISTANT_FP8_ALL 2      /* every drafter linear in e4m3 */
+
 typedef struct carat_b200_runner carat_b200_runner;
 
 /* Builds a runner with `batch` request slots of `maximum_context` tokens on the current device:
@@ -513,6 +534,15 @@ CARAT_B200_API int carat_b200_runner_last_device_ms(const carat_b200_runner *run
 /* Kernel launches issued by the last verify / draft call. */
 CARAT_B200_API int carat_b200_runner_last_launches(const carat_b200_runner *runner, int *verify_launches,
                                     int *draft_launches);
+/* Selects the drafter's precision like the reference's CARAT_ASSISTANT_FP8_MODE
+ * (cuda/assistant_runner.cu:29-43,147-160). A runner starts in CARAT_B200_ASSISTANT_FP8_ALL when
+ * it was created with e4m3 drafter matrices; OFF and LM_HEAD need the bf16 matrices (`bf16`, kept
+ * by reference like every weight), LM_HEAD and ALL need the e4m3 ones given at creation
+ * ("assistant FP8 mode requires quantized assistant weights" otherwise, the reference's text).
+ * A drafter created without e4m3 matrices (every matrix pointer of carat_b200_assistant_weights
+ * NULL, norms still given) must be put in OFF mode before its first draft. */
+CARAT_B200_API int carat_b200_runner_set_assistant_precision(
+    carat_b200_runner *runner, int mode, const carat_b200_assistant_bf16_weights *bf16);
 
 #ifdef __cplusplus
 }

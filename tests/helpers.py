@@ -30,7 +30,8 @@ def build_pair(config, weights, slots, assistant=None, assistant_weights=None):
         a_fp8 = carat_b200.Fp8WeightArena.quantize(a_arena)
         a_config = assistant_config(assistant)
     device = carat_b200.Gemma4BatchModelRunner(runner_config(config), arena, slots,
-                                               config.max_context, fp8, a_arena, a_fp8, a_config)
+                                               config.max_context, fp8, a_arena, a_fp8, a_config,
+                                               assistant_fp8_mode="all")
     return oracle, device, fp8
 
 

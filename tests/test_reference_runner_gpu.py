@@ -95,7 +95,7 @@ class Pair:
 
         self.ours = carat_b200.Gemma4BatchModelRunner(
             self.config, self.weights, SLOTS, MAX_CONTEXT, self.fp8, self.assistant_weights,
-            self.assistant_fp8, self.assistant_config)
+            self.assistant_fp8, self.assistant_config, assistant_fp8_mode="all")
         # The reference reads its drafter precision from the environment when it is built; this
         # repository's drafter runs every linear in e4m3, the reference's "all" mode
         # (cuda/assistant_runner.cu:31-43).
@@ -125,12 +125,15 @@ def pair(cuda_device):
 DRAFT_BAND = 0.2
 
 
-def drafter_logits(pair, rows):
+def drafter_logits(pair, rows, mode="all"):
     """bf16 logits of the drafter's last draft step, recomputed from its final-normed hidden rows
-    with the quantiser and FP8 linear its LM head uses."""
+    with the linear its LM head uses in `mode` (bf16 when "off", else quantiser + FP8 linear)."""
     library = carat_b200.library()
     width = pair.assistant_config.hidden_size
     hidden = pair.ours.assistant_final_hidden(rows, width)
+    if mode == "off":
+        table = pair.assistant_weights.at("token_embedding")
+        return (hidden.float() @ table.float().t()).to(torch.bfloat16).float()
     quantised = torch.empty(rows, width, dtype=torch.uint8, device="cuda")
     scale = torch.zeros(1, dtype=torch.float32, device="cuda")
     scratch = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -289,18 +292,15 @@ def test_wrapped_ring_ragged_accept_lengths_and_drafts(pair):
     assert draft_mismatch <= 0.45 * draft_rows
 
 
-def test_drafter_disagreement_is_within_its_own_noise(pair):
-    """carat::Gemma4AssistantRunner run directly over this runner's own memory (target embedding,
-    hidden-by-slot table, the two shared KV layers), so both drafters read identical bytes.
-
-    With random-init weights the drafter's logits are nearly flat and its e4m3 chain is chaotic:
-    flipping the last bf16 bit of 1 % of the hidden hand-off elements changes the reference's own
-    first drafted token on a quarter to a third of the rows. The bar: this side disagrees with
-    the reference no more often than the reference disagrees with itself under that one-ulp
-    perturbation (plus 10 % of the rows for sampling noise), and where it disagrees the
-    reference's token is among this side's top candidates."""
+def drafter_agreement(pair, mode):
+    """First drafted token of this side's drafter and of carat::Gemma4AssistantRunner run directly
+    over this runner's own memory (target embedding, hidden-by-slot table, the two shared KV
+    layers), in drafter precision `mode`; both also re-run with the last bf16 bit of 1 % of the
+    hand-off elements flipped. Returns (rows, cross, reference_noise, own_noise)."""
+    os.environ["CARAT_ASSISTANT_FP8_MODE"] = mode
     assistant = ref.ReferenceAssistant(pair.assistant_weights.tensors, pair.assistant_fp8.bytes,
                                        pair.assistant_fp8.scales, SLOTS, MAX_CONTEXT)
+    pair.ours.set_assistant_fp8_mode(mode)
     embedding = pair.weights.at("token_embedding").data_ptr()
     live = list(range(LIVE))
     cross = own_noise = reference_noise = rows = 0
@@ -327,7 +327,7 @@ def test_drafter_disagreement_is_within_its_own_noise(pair):
                                                 global_[1], MAX_CONTEXT)
 
                 mine = pair.ours.draft_four(last, live, first, 2)
-                logits = drafter_logits(pair, LIVE)
+                logits = drafter_logits(pair, LIVE, mode)
                 reference = theirs()
                 table = pair.ours.target_hidden_slots()
                 bits = table.view(torch.int16).clone()
@@ -349,9 +349,37 @@ def test_drafter_disagreement_is_within_its_own_noise(pair):
                         assert gap <= DRAFT_BAND * abs(top)
     finally:
         assistant.close()
-    print(f"first drafted token over {rows} rows: differs from the reference on {cross}; the "
-          f"reference changes on {reference_noise} and this side on {own_noise} under a one-ulp "
-          "perturbation of 1 % of the hand-off elements")
+        pair.ours.set_assistant_fp8_mode("all")
+        os.environ["CARAT_ASSISTANT_FP8_MODE"] = "all"
+    return rows, cross, reference_noise, own_noise
+
+
+def test_drafter_disagreement_is_within_its_own_noise(pair):
+    """Every drafter linear in e4m3 (the reference's CARAT_ASSISTANT_FP8_MODE=all).
+
+    With random-init weights the drafter's logits are nearly flat and its e4m3 chain is chaotic:
+    flipping the last bf16 bit of 1 % of the hidden hand-off elements changes the reference's own
+    first drafted token on a quarter to a third of the rows. The bar: this side disagrees with
+    the reference no more often than the reference disagrees with itself under that one-ulp
+    perturbation (plus 10 % of the rows for sampling noise), and where it disagrees the
+    reference's token is among this side's top candidates."""
+    rows, cross, reference_noise, own_noise = drafter_agreement(pair, "all")
+    print(f"e4m3 drafter, first drafted token over {rows} rows: differs from the reference on "
+          f"{cross}; the reference changes on {reference_noise} and this side on {own_noise} under "
+          "a one-ulp perturbation of 1 % of the hand-off elements")
+    assert cross <= max(reference_noise, own_noise) + 0.1 * rows
+
+
+@pytest.mark.parametrize("mode", ["off", "lm_head"])
+def test_drafter_default_precisions_against_the_reference(pair, mode):
+    """The reference's default drafter precision (every linear bf16 through cuBLAS,
+    cuda/assistant_runner.cu:147-160) and its lm_head mode (bf16, LM head alone in e4m3), with
+    this side on the bf16 weight-streaming linear. Same bar as the e4m3 drafter: no more
+    disagreement than the reference shows with itself under a one-ulp input perturbation."""
+    rows, cross, reference_noise, own_noise = drafter_agreement(pair, mode)
+    print(f"drafter mode {mode}, first drafted token over {rows} rows: differs from the reference "
+          f"on {cross}; the reference changes on {reference_noise} and this side on {own_noise} "
+          "under a one-ulp perturbation of 1 % of the hand-off elements")
     assert cross <= max(reference_noise, own_noise) + 0.1 * rows
 
 
