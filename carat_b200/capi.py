@@ -41,6 +41,10 @@ class Int4MlpLayer(Structure):
                 ("down_codes", c_void_p), ("down_scales", c_void_p)]
 
 
+class LayerBf16Weights(Structure):
+    _fields_ = [("qkv", c_void_p), ("o", c_void_p), ("gate_up", c_void_p), ("down", c_void_p)]
+
+
 class AssistantBf16Layer(Structure):
     _fields_ = [("q", c_void_p), ("o", c_void_p), ("gate_up", c_void_p), ("down", c_void_p)]
 
@@ -115,6 +119,8 @@ SIGNATURES = {
                                      POINTER(AssistantConfig), POINTER(AssistantWeights),
                                      POINTER(c_void_p)]),
     "carat_b200_runner_destroy": (None, [_P]),
+    "carat_b200_runner_set_bf16_weights": (_I, [_P, POINTER(LayerBf16Weights), _I]),
+    "carat_b200_runner_prefill_slots_chunks": (_I, [_P, _IP, POINTER(_IP), _IP, _I, _I, _IP, _IP]),
     "carat_b200_runner_set_assistant_precision": (_I, [_P, _I, POINTER(AssistantBf16Weights)]),
     "carat_b200_runner_use_int4_mlp": (_I, [_P, POINTER(Int4MlpLayer), _I, _I]),
     "carat_b200_runner_verify_greedy_proposals": (_I, [_P, _IP, _I, _I, _IP, _IP, _IP, _I, _IP,

@@ -200,6 +200,10 @@ struct carat_b200_runner {
       a_previous_hidden, a_scratch_words, a_scales, a_tokens, a_proposals;
   int a_amax_words{0};
   std::map<int, StepPlans> draft_plans;
+  // ---- BF16 prefill: the target's bf16 matrices, bf16 inputs of its linears, plans per row count
+  std::vector<carat_b200_layer_bf16_weights> bf16_layers;
+  DeviceBuffer p_normed, p_pre_mlp, p_activated;
+  std::map<int, StepPlans> prefill_plans;
   // ---- drafter precision (CARAT_B200_ASSISTANT_FP8_*): bf16 matrices and their plans
   int assistant_mode{CARAT_B200_ASSISTANT_FP8_ALL};
   bool assistant_has_fp8{false};
@@ -574,6 +578,36 @@ StepPlans &draft_plans_bf16_for(Runner &runner, int rows) {
   if (most_partial > runner.split_partials.bytes())
     throw Failure{"split-K workspace is too small for this assistant shape"};
   return runner.draft_plans_bf16.emplace(rows, std::move(plans)).first->second;
+}
+
+StepPlans &prefill_plans_for(Runner &runner, int rows) {
+  const auto found = runner.prefill_plans.find(rows);
+  if (found != runner.prefill_plans.end())
+    return found->second;
+  StepPlans plans;
+  const int hidden = runner.config.hidden_size;
+  const int intermediate = runner.config.intermediate_size;
+  for (size_t index = 0; index < runner.layers.size(); ++index) {
+    const LayerState &layer = runner.layers[index];
+    const carat_b200_layer_bf16_weights &weights = runner.bf16_layers[index];
+    LayerPlans entry;
+    entry.qkv = plan_bf16_linear(runner.p_normed.get(), weights.qkv, rows, hidden,
+                                 layer.packed_width(), 0);
+    entry.o = plan_bf16_linear(runner.attention_out.get(), weights.o, rows, layer.query_width(),
+                               hidden, 0);
+    entry.gate_up = plan_bf16_linear(runner.p_pre_mlp.get(), weights.gate_up, rows, hidden,
+                                     2 * intermediate, 0);
+    entry.down = plan_bf16_linear(runner.p_activated.get(), weights.down, rows, intermediate,
+                                  hidden, 0);
+    for (const LinearPlan *plan : {&entry.qkv, &entry.o, &entry.gate_up, &entry.down}) {
+      if (linear_partial_bytes(*plan) > runner.split_partials.bytes())
+        throw Failure{"split-K workspace is too small for this model shape"};
+    }
+    plans.layers.push_back(entry);
+  }
+  plans.head = plan_bf16_linear(runner.final_hidden.get(), runner.weights.token_embedding, rows,
+                                hidden, runner.config.vocabulary_size, 1);
+  return runner.prefill_plans.emplace(rows, std::move(plans)).first->second;
 }
 
 // Runs a linear into bf16 `output`, or leaves split-K partials for a fused consumer. Returns the
@@ -988,6 +1022,211 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
     next_out[request] = host_results[runner.batch + request];
     runner.slot_positions[static_cast<size_t>(slots[request])] += host_results[request];
   }
+}
+
+// One BF16 forward over `depth` prompt tokens of each listed slot, all of them made resident:
+// the verify step's layer loop with bf16 linears and no quantisation, every row committed.
+// When `predict` is set the bf16 LM head runs over the step's final-normed rows and
+// predictions_out receives the argmax of every row (requests * depth).
+void prefill_step(Runner &runner, const int *tokens, int requests, int depth, const int *slots,
+                  bool predict, int *predictions_out) {
+  const auto &config = runner.config;
+  const int rows = requests * depth;
+  const StepLayout host = layout_inputs(runner.host_inputs.get<int>(), maximum_rows, runner.batch);
+  int longest = 0;
+  for (int request = 0; request < requests; ++request) {
+    const int position = runner.slot_positions[static_cast<size_t>(slots[request])];
+    for (int token = 0; token < depth; ++token)
+      host.tokens[request * depth + token] = tokens[request * depth + token];
+    host.positions[request] = position;
+    host.slots[request] = slots[request];
+    host.target_first[request] = tokens[request * depth];
+    host.caps[request] = depth;    // doubles as the accept length of the commit: every row stays
+    longest = std::max(longest, position);
+  }
+  StepPlans &plans = prefill_plans_for(runner, rows);
+  const StepLayout device =
+      layout_inputs(runner.step_inputs.get<int>(), maximum_rows, runner.batch);
+  cudaStream_t stream = runner.stream;
+  require_cuda(cudaMemcpyAsync(runner.step_inputs.get(), runner.host_inputs.get<int>(),
+                               sizeof(int) * (maximum_rows + 4 * runner.batch),
+                               cudaMemcpyHostToDevice, stream),
+               "copy prefill step inputs");
+  runner.launches = 0;
+  const int hidden = config.hidden_size;
+  const float epsilon = config.rms_norm_epsilon;
+  const auto rows_only = [](void *rows_out) {
+    return QuantTarget{nullptr, nullptr, nullptr, nullptr, rows_out};
+  };
+  auto *best = reinterpret_cast<unsigned long long *>(runner.scratch_words.get<unsigned int>() +
+                                                      runner.amax_words);
+  if (predict)
+    require_cuda(cudaMemsetAsync(best, 0, sizeof(unsigned long long) * maximum_rows, stream),
+                 "clear argmax keys");
+
+  void *current = runner.hidden_a.get();
+  void *other = runner.hidden_b.get();
+  require_launch(launch_embed_norm_quant(runner.weights.token_embedding, device.tokens,
+                                         config.vocabulary_size, runner.layers[0].weights.input_norm,
+                                         current, rows_only(runner.p_normed.get()), rows, hidden,
+                                         epsilon, nullptr, 0, stream),
+                 "embedding and input norm");
+  runner.launches += 1;
+  for (int index = 0; index < config.layer_count; ++index) {
+    const LayerState &layer = runner.layers[static_cast<size_t>(index)];
+    const LayerPlans &plan = plans.layers[static_cast<size_t>(index)];
+    const auto &shape = layer.shape;
+    const auto &w = layer.weights;
+    const RopeTable &rope = *runner.rope_tables[static_cast<size_t>(layer.rope)];
+    run_linear(runner, plan.qkv, nullptr, nullptr, runner.packed.get(), false);
+
+    QkvPostArguments post{};
+    post.packed = runner.packed.get();
+    post.query_norm = w.q_norm;
+    post.key_norm = w.k_norm;
+    post.cosine = rope.cosine.get();
+    post.sine = rope.sine.get();
+    post.queries = runner.queries.get();
+    post.positions = device.positions;
+    post.slots = device.slots;
+    post.requests = requests;
+    post.depth = depth;
+    post.query_heads = shape.query_heads;
+    post.kv_heads = shape.kv_heads;
+    post.head_dim = shape.head_dim;
+    post.key_equals_value = shape.key_equals_value;
+    post.max_positions = runner.maximum_context;
+    post.epsilon = epsilon;
+    post.capacity = layer.capacity;
+    if (shape.global_attention) {
+      post.direct = 1;
+      post.key_base = layer.keys();
+      post.value_base = layer.values();
+      post.slot_stride = layer.slot_stride;
+      post.head_stride = layer.head_stride;
+    } else {
+      post.direct = 0;
+      post.key_base = layer.staged_keys();
+      post.value_base = layer.staged_values();
+      post.head_stride = static_cast<long long>(depth) * shape.head_dim;
+      post.slot_stride = post.head_stride * shape.kv_heads;
+    }
+    require_launch(launch_qkv_post(post, stream), "QKV post-processing");
+    runner.launches += 1;
+
+    AttentionArguments attention{};
+    attention.queries = runner.queries.get();
+    attention.key_cache = layer.keys();
+    attention.value_cache = layer.values();
+    attention.slot_stride = layer.slot_stride;
+    attention.head_stride = layer.head_stride;
+    attention.positions = device.positions;
+    attention.slots = device.slots;
+    attention.scores = runner.scores.get();
+    attention.output = runner.attention_out.get();
+    attention.chunk_partials = runner.attention_partials.get<float>();
+    attention.requests = requests;
+    attention.depth = depth;
+    attention.query_heads = shape.query_heads;
+    attention.kv_heads = shape.kv_heads;
+    attention.head_dim = shape.head_dim;
+    attention.capacity = layer.capacity;
+    if (shape.global_attention) {
+      attention.window = 0;
+      attention.max_cache_rows = longest + depth;
+      attention.score_stride = runner.score_stride_global;
+      attention.chunk_keys = global_chunk_keys;
+      attention.chunks = attention_chunks(longest + depth, global_chunk_keys);
+    } else {
+      attention.window = config.sliding_window;
+      attention.new_keys = layer.staged_keys();
+      attention.new_values = layer.staged_values();
+      attention.new_request_stride = post.slot_stride;
+      attention.new_head_stride = post.head_stride;
+      attention.max_cache_rows = std::min(longest, layer.capacity);
+      attention.score_stride = runner.score_stride_sliding;
+      attention.chunk_keys = (layer.capacity + 127) / 128 * 128;
+      attention.chunks = 1;
+    }
+    attention.stats = runner.attention_stats.get<float2>();
+    attention.stats_stride = runner.stats_stride;
+    attention.request_chunks = runner.request_chunks.get<int>();
+    attention.maps = verify_attention_maps(runner, index, depth);
+    require_launch(attention.maps != nullptr ? launch_attention_tc(attention, stream)
+                                             : launch_attention_simt(attention, stream),
+                   "prefill attention");
+    runner.launches += attention.maps != nullptr ? attention_tc_launches(attention) : 3;
+    if (attention.chunks > 1) {
+      const bool counted = attention.maps != nullptr;
+      require_launch(launch_quant(nullptr, runner.attention_partials.get<float>(),
+                                  attention.chunks,
+                                  counted ? runner.request_chunks.get<int>() : nullptr, depth,
+                                  rows_only(runner.attention_out.get()), rows,
+                                  layer.query_width(), stream),
+                     "prefill attention rows");
+      runner.launches += 1;
+    }
+    const PartialSource o_source =
+        run_linear(runner, plan.o, nullptr, nullptr, runner.projected.get(), true);
+    require_launch(launch_post_attention_norms_quant(
+                       runner.projected.get(), o_source, w.post_attention_norm, current,
+                       w.pre_mlp_norm, runner.residual.get(), rows_only(runner.p_pre_mlp.get()),
+                       rows, hidden, epsilon, stream),
+                   "post-attention norms");
+    runner.launches += 1;
+    run_linear(runner, plan.gate_up, nullptr, nullptr, runner.gate_up.get(), false);
+    require_launch(launch_geglu_quant(runner.gate_up.get(), TailSource{},
+                                      rows_only(runner.p_activated.get()), rows,
+                                      config.intermediate_size, stream),
+                   "GeGLU");
+    runner.launches += 1;
+    const PartialSource down_source =
+        run_linear(runner, plan.down, nullptr, nullptr, runner.projected.get(), true);
+    const bool last = index + 1 == config.layer_count;
+    const void *next_norm = last ? runner.weights.final_norm
+                                 : runner.layers[static_cast<size_t>(index) + 1].weights.input_norm;
+    require_launch(launch_layer_output_norm_quant(
+                       runner.projected.get(), down_source, w.post_mlp_norm, runner.residual.get(),
+                       w.scalar, other, next_norm,
+                       last ? runner.final_hidden.get() : runner.p_normed.get(), QuantTarget{},
+                       rows, hidden, epsilon, stream),
+                   "layer output");
+    runner.launches += 1;
+    std::swap(current, other);
+  }
+  if (runner.commit_layer_count > 0) {
+    require_launch(launch_commit(runner.commit_layers.get<CommitLayer>(), runner.commit_layer_count,
+                                 device.positions, device.caps, device.slots, requests, depth, 0,
+                                 stream),
+                   "KV commit");
+    runner.launches += 1;
+  }
+  int *host_results = runner.host_results.get<int>();
+  if (predict) {
+    require_launch(launch_linear_argmax(plans.head, nullptr, nullptr, best, runner.device_error,
+                                        stream),
+                   "BF16 LM head");
+    int *predictions = runner.step_results.get<int>() + 2 * runner.batch;
+    require_launch(launch_unpack_best(best, predictions, rows, stream), "prefill argmax");
+    runner.launches += 2;
+    require_cuda(cudaMemcpyAsync(host_results, predictions, sizeof(int) * rows,
+                                 cudaMemcpyDeviceToHost, stream),
+                 "copy prefill predictions");
+  }
+  require_cuda(cudaMemcpyAsync(host_results + maximum_rows, runner.device_error, sizeof(int),
+                               cudaMemcpyDeviceToHost, stream),
+               "copy device error word");
+  require_cuda(cudaStreamSynchronize(stream), "synchronize prefill step");
+  if (host_results[maximum_rows] != 0) {
+    const int code = host_results[maximum_rows];
+    cudaMemsetAsync(runner.device_error, 0, sizeof(int), stream);
+    throw Failure{"a kernel wait ran out during prefill (code " + std::to_string(code) + ")"};
+  }
+  if (predict)
+    std::copy(host_results, host_results + rows, predictions_out);
+  for (int request = 0; request < requests; ++request)
+    runner.slot_positions[static_cast<size_t>(slots[request])] += depth;
+  runner.last_rows = rows;
 }
 
 void draft_step(Runner &runner, const int *last_tokens, const int *slots, const int *forced,
@@ -1435,6 +1674,118 @@ extern "C" int carat_b200_runner_prefill_slot_fp8(carat_b200_runner *runner, int
       verify_step(*runner, tokens + start, 1, part, tokens + start, &slot, nullptr,
                   CARAT_B200_VERIFY_ASSUME_MATCH, true, &accepted, &next);
       *next_token = next;
+    }
+  });
+}
+
+extern "C" int carat_b200_runner_set_bf16_weights(carat_b200_runner *runner,
+                                                  const carat_b200_layer_bf16_weights *layers,
+                                                  int layer_count) {
+  return guarded([&] {
+    if (runner == nullptr || layers == nullptr || layer_count != runner->config.layer_count)
+      throw Failure{"invalid batch model runner shape"};
+    for (int index = 0; index < layer_count; ++index) {
+      if (layers[index].qkv == nullptr || layers[index].o == nullptr ||
+          layers[index].gate_up == nullptr || layers[index].down == nullptr) {
+        throw Failure{"invalid batch model runner shape"};
+      }
+    }
+    runner->bf16_layers.assign(layers, layers + layer_count);
+    runner->prefill_plans.clear();
+    if (runner->p_normed.get() == nullptr) {
+      const size_t rows = maximum_rows;
+      runner->p_normed.allocate(rows * runner->config.hidden_size * 2);
+      runner->p_pre_mlp.allocate(rows * runner->config.hidden_size * 2);
+      runner->p_activated.allocate(rows * runner->config.intermediate_size * 2);
+    }
+  });
+}
+
+extern "C" int carat_b200_runner_prefill_slots_chunks(
+    carat_b200_runner *runner, const int *slots, const int *const *token_ids,
+    const int *token_counts, int requests, int chunk_tokens, int *predictions,
+    int *has_prediction) {
+  return guarded([&] {
+    if (runner == nullptr || slots == nullptr || token_ids == nullptr || token_counts == nullptr ||
+        predictions == nullptr || has_prediction == nullptr || requests <= 0 ||
+        requests > runner->batch || chunk_tokens <= 0) {
+      throw Failure{"invalid batched chunk prefill shape"};
+    }
+    if (runner->bf16_layers.empty())
+      throw Failure{"BF16 prefill needs the target's bf16 weights"};
+    std::vector<bool> seen(static_cast<size_t>(runner->batch), false);
+    std::vector<int> begin(static_cast<size_t>(requests));
+    std::vector<int> end(static_cast<size_t>(requests));
+    for (int request = 0; request < requests; ++request) {
+      const int slot = slots[request];
+      if (slot < 0 || slot >= runner->batch || seen[static_cast<size_t>(slot)] ||
+          token_ids[request] == nullptr || token_counts[request] <= 0 ||
+          token_counts[request] > runner->maximum_context) {
+        throw Failure{"invalid batched chunk prefill request"};
+      }
+      seen[static_cast<size_t>(slot)] = true;
+      const int position = runner->slot_positions[static_cast<size_t>(slot)];
+      const int remaining = token_counts[request] - position;
+      if (position < 0 || remaining <= 0)
+        throw Failure{"batched chunk does not extend resident context"};
+      begin[static_cast<size_t>(request)] = position;
+      end[static_cast<size_t>(request)] = position + std::min(remaining, chunk_tokens);
+      for (int index = position; index < end[static_cast<size_t>(request)]; ++index) {
+        if (token_ids[request][index] < 0 ||
+            token_ids[request][index] >= runner->config.vocabulary_size) {
+          throw Failure{"batched chunk contains an invalid token id"};
+        }
+      }
+      has_prediction[request] = 0;
+      predictions[request] = -1;
+    }
+    // Walk the chunks in steps of at most eight tokens; a step takes every request that still
+    // has tokens left and as many tokens as the shortest of them has (rows of different requests
+    // never mix in bf16, so the grouping does not change any row).
+    constexpr int step_tokens = 8;
+    std::vector<int> cursor = begin;
+    const size_t hidden_bytes = static_cast<size_t>(runner->config.hidden_size) * 2;
+    for (;;) {
+      std::vector<int> active;
+      int depth = step_tokens;
+      for (int request = 0; request < requests; ++request) {
+        const int left = end[static_cast<size_t>(request)] - cursor[static_cast<size_t>(request)];
+        if (left > 0) {
+          active.push_back(request);
+          depth = std::min(depth, left);
+        }
+      }
+      if (active.empty())
+        break;
+      std::vector<int> step_slots;
+      std::vector<int> step_ids;
+      bool predict = false;
+      for (const int request : active) {
+        step_slots.push_back(slots[request]);
+        const int from = cursor[static_cast<size_t>(request)];
+        step_ids.insert(step_ids.end(), token_ids[request] + from, token_ids[request] + from + depth);
+        predict = predict || from + depth == token_counts[request];
+      }
+      std::vector<int> step_predictions(active.size() * static_cast<size_t>(depth), -1);
+      prefill_step(*runner, step_ids.data(), static_cast<int>(active.size()), depth,
+                   step_slots.data(), predict, step_predictions.data());
+      for (size_t index = 0; index < active.size(); ++index) {
+        const int request = active[index];
+        cursor[static_cast<size_t>(request)] += depth;
+        if (cursor[static_cast<size_t>(request)] != token_counts[request])
+          continue;
+        // The whole prompt is resident: its last row predicts the first generated token and its
+        // final-normed hidden row goes to the drafter's table (cuda/batch_model_runner.cu:1106-1124).
+        const size_t row = index * static_cast<size_t>(depth) + static_cast<size_t>(depth) - 1;
+        has_prediction[request] = 1;
+        predictions[request] = step_predictions[row];
+        require_cuda(cudaMemcpyAsync(
+                         runner->hidden_by_slot.get<unsigned char>() + slots[request] * hidden_bytes,
+                         runner->final_hidden.get<unsigned char>() + row * hidden_bytes,
+                         hidden_bytes, cudaMemcpyDeviceToDevice, runner->stream),
+                     "hand the prefill hidden row to the drafter");
+      }
+      require_cuda(cudaStreamSynchronize(runner->stream), "synchronize prefill hand-off");
     }
   });
 }

@@ -416,6 +416,75 @@ class Gemma4BatchModelRunner:
                                                     output))
         return [list(output[row * depth:(row + 1) * depth]) for row in range(requests)]
 
+    # ---- BF16 prefill (cuda/batch_model_runner.cu:1048-1355)
+    def set_bf16_weights(self, weights: Optional[DeviceWeightArena] = None) -> None:
+        """Hands the target's bf16 matrices (layer.N.qkv / o / gate_up / down of the
+        DeviceWeightArena the runner was built with, unless another arena is given) to the runner;
+        BF16 prefill runs on them."""
+        arena = weights or self._keep[0]
+        layers = (capi.LayerBf16Weights * len(self.config.layers))()
+        for index in range(len(self.config.layers)):
+            prefix = f"layer.{index}."
+            layers[index] = capi.LayerBf16Weights(
+                arena.at(prefix + "qkv").data_ptr(), arena.at(prefix + "o").data_ptr(),
+                arena.at(prefix + "gate_up").data_ptr(), arena.at(prefix + "down").data_ptr())
+        check(self._library.carat_b200_runner_set_bf16_weights(self._handle, layers, len(layers)))
+        self._keep.append(layers)
+        self._has_bf16 = True
+
+    def prefill_slots_chunks(self, slots: Sequence[int], token_ids: Sequence[Sequence[int]],
+                             chunk_tokens: int) -> List[Optional[int]]:
+        """One BF16 prefill chunk per listed slot; an entry holds the greedy next token only when
+        that request's whole prompt became resident (Gemma4BatchModelRunner::prefill_slots_chunks)."""
+        requests = len(slots)
+        if requests == 0 or len(token_ids) != requests:
+            raise CaratError("invalid batched chunk prefill shape")
+        if not getattr(self, "_has_bf16", False):
+            self.set_bf16_weights()
+        arrays = [int_array(tokens) for tokens in token_ids]
+        pointers = (ctypes.POINTER(ctypes.c_int) * requests)(*[
+            ctypes.cast(array, ctypes.POINTER(ctypes.c_int)) for array in arrays])
+        counts = int_array([len(tokens) for tokens in token_ids])
+        predictions = (ctypes.c_int * requests)()
+        has_prediction = (ctypes.c_int * requests)()
+        check(self._library.carat_b200_runner_prefill_slots_chunks(
+            self._handle, int_array(slots), pointers, counts, requests, chunk_tokens, predictions,
+            has_prediction))
+        return [predictions[r] if has_prediction[r] else None for r in range(requests)]
+
+    def prefill_slot_chunk(self, slot: int, token_ids: Sequence[int],
+                           chunk_tokens: int) -> Optional[int]:
+        """Gemma4BatchModelRunner::prefill_slot_chunk (cuda/batch_model_runner.cu:1066-1125)."""
+        if not token_ids or chunk_tokens <= 0:
+            raise CaratError("invalid slot prefill chunk shape")
+        return self.prefill_slots_chunks([slot], [token_ids], chunk_tokens)[0]
+
+    def prefill_slot(self, slot: int, token_ids: Sequence[int], chunk_tokens: int = 1024) -> int:
+        """Gemma4BatchModelRunner::prefill_slot (:1048-1052): reset the slot, prefill in BF16."""
+        self.reset_slot(slot)
+        return self.prefill_slot_from_prefix(slot, token_ids, 0, chunk_tokens)
+
+    def prefill_slot_from_prefix(self, slot: int, token_ids: Sequence[int],
+                                 cached_prefix_tokens: int, chunk_tokens: int = 1024) -> int:
+        """:1054-1064: the first cached_prefix_tokens of token_ids are already resident."""
+        if (not token_ids or chunk_tokens <= 0 or cached_prefix_tokens < 0
+                or cached_prefix_tokens >= len(token_ids)
+                or self.slot_position(slot) != cached_prefix_tokens):
+            raise CaratError("invalid slot prefill shape")
+        prediction = None
+        while prediction is None:
+            prediction = self.prefill_slot_chunk(slot, token_ids, chunk_tokens)
+        return prediction
+
+    def prefill_slots_suffix(self, slots: Sequence[int],
+                             token_ids: Sequence[Sequence[int]]) -> List[int]:
+        """Gemma4BatchModelRunner::prefill_slots_suffix (:1127-1228) for BF16 suffixes: whatever of
+        each prompt is not resident yet, in one call."""
+        if not slots or len(token_ids) != len(slots):
+            raise CaratError("invalid batched suffix prefill shape")
+        longest = max(len(tokens) for tokens in token_ids)
+        return self.prefill_slots_chunks(slots, token_ids, max(longest, 1))
+
     def prefill_slot_fp8(self, slot: int, token_ids: Sequence[int], chunk_tokens: int = 8) -> int:
         next_token = ctypes.c_int(0)
         check(self._library.carat_b200_runner_prefill_slot_fp8(

@@ -534,6 +534,38 @@ CARAT_B200_API int carat_b200_runner_last_device_ms(const carat_b200_runner *run
 /* Kernel launches issued by the last verify / draft call. */
 CARAT_B200_API int carat_b200_runner_last_launches(const carat_b200_runner *runner, int *verify_launches,
                                     int *draft_launches);
+/* The target's matrices in bf16 (carat::DeviceWeightArena::at: layer.N.qkv / o / gate_up / down,
+ * row-major [out, in]); the tied LM head is the bf16 token embedding the runner already holds.
+ * Needed only for BF16 prefill. */
+typedef struct carat_b200_layer_bf16_weights {
+  const void *qkv;
+  const void *o;
+  const void *gate_up;
+  const void *down;
+} carat_b200_layer_bf16_weights;
+
+CARAT_B200_API int carat_b200_runner_set_bf16_weights(carat_b200_runner *runner,
+                                                      const carat_b200_layer_bf16_weights *layers,
+                                                      int layer_count);
+
+/* BF16 prompt prefill, one chunk per listed slot: for request r the tokens
+ * token_ids[r][position .. position + min(chunk_tokens, remaining)) are made resident, where
+ * position is the slot's current position (0 for a reset slot, the cached prefix length after
+ * clone_slot) and token_counts[r] the prompt's length. has_prediction[r] = 1 and predictions[r] =
+ * the greedy next token only when that request's whole prompt is now resident; its final-normed
+ * last hidden row is then handed to the drafter's table. Every linear runs in bf16 even when
+ * decode runs in e4m3, as in the reference (cuda/batch_model_runner.cu:1274-1275).
+ * Replaces Gemma4BatchModelRunner::prefill_slots_chunks (and, with one slot, prefill_slot_chunk;
+ * with chunk_tokens >= every remainder, prefill_slots_suffix's result for a cold cache):
+ * include/carat/batch_model_runner.h:37-47, cuda/batch_model_runner.cu:1066-1125,1230-1355.
+ * Inside, a chunk is walked in steps of at most eight tokens per request through the same
+ * attention kernels the verify step uses; rows of different requests never mix in bf16, so the
+ * walk does not change results. Needs carat_b200_runner_set_bf16_weights. */
+CARAT_B200_API int carat_b200_runner_prefill_slots_chunks(
+    carat_b200_runner *runner, const int *slots, const int *const *token_ids,
+    const int *token_counts, int requests, int chunk_tokens, int *predictions,
+    int *has_prediction);
+
 /* Selects the drafter's precision like the reference's CARAT_ASSISTANT_FP8_MODE
  * (cuda/assistant_runner.cu:29-43,147-160). A runner starts in CARAT_B200_ASSISTANT_FP8_ALL when
  * it was created with e4m3 drafter matrices; OFF and LM_HEAD need the bf16 matrices (`bf16`, kept
