@@ -4,11 +4,11 @@
 // seed_empty_cache_for_benchmark and the accessors. Compile it inside the Carat build in place of cuda/batch_model_runner.cu and
 // link libcarat_b200.so; the scheduler (src/native_runtime_main.cpp) is unchanged.
 //
-// The methods outside that path (BF16 prefill, prefix-reuse prefill, the lock-step `append`)
-// throw: a build that needs them keeps the reference's runner for them. prefill_slot runs the
-// interim FP8 prefill of the library, which makes a prompt resident through the verify forward;
-// the reference prefills in BF16 (cuda/batch_model_runner.cu:1274-1275), so first tokens can
-// differ where logits nearly tie.
+// Prompt prefill (prefill_slot, prefill_slot_from_prefix, prefill_slot_chunk,
+// prefill_slots_chunks, prefill_slots_suffix) runs in BF16 on the bf16 matrices of the
+// DeviceWeightArena, as in the reference (cuda/batch_model_runner.cu:1274-1275).
+// prefill_slots_suffix_layer_slice finishes the whole suffix in its first call (it never leaves
+// layer slices pending), and the lock-step `append` is append_ragged over every slot.
 #include "carat/batch_model_runner.h"
 #include "carat/device_weights.h"
 #include "carat/gemma4_config.h"
@@ -16,6 +16,7 @@
 #include "carat_b200.h"
 
 #include <cstdlib>
+#include <optional>
 #include <stdexcept>
 #include <string>
 #include <vector>
@@ -28,10 +29,6 @@ void check(int status) {
   // The library reports the reference's own exception texts.
   if (status != 0)
     throw std::runtime_error(carat_b200_last_error());
-}
-
-[[noreturn]] void not_provided(const char *method) {
-  throw std::runtime_error(std::string(method) + " is not provided by carat-b200");
 }
 
 // Norm vectors only: a drafter that runs in bf16 may come without an Fp8WeightArena.
@@ -88,6 +85,31 @@ struct Gemma4BatchModelRunner::Implementation {
   carat_b200_runner *handle{nullptr};
   int batch{0};
   int maximum_context{0};
+  int current_position{0};   // the lock-step position `append` and the benchmark seed keep
+
+  // One prefill chunk per listed slot through the C ABI; an entry is set when the prompt is whole.
+  std::vector<std::optional<int>> chunks(const std::vector<int> &slots,
+                                         const std::vector<const std::vector<int> *> &token_ids,
+                                         int chunk_tokens) {
+    std::vector<const int *> pointers;
+    std::vector<int> counts;
+    for (const std::vector<int> *prompt : token_ids) {
+      pointers.push_back(prompt != nullptr ? prompt->data() : nullptr);
+      counts.push_back(prompt != nullptr ? static_cast<int>(prompt->size()) : 0);
+    }
+    std::vector<int> predictions(slots.size(), -1);
+    std::vector<int> has_prediction(slots.size(), 0);
+    check(carat_b200_runner_prefill_slots_chunks(handle, slots.data(), pointers.data(),
+                                                 counts.data(), static_cast<int>(slots.size()),
+                                                 chunk_tokens, predictions.data(),
+                                                 has_prediction.data()));
+    std::vector<std::optional<int>> result(slots.size());
+    for (std::size_t request = 0; request < slots.size(); ++request) {
+      if (has_prediction[request] != 0)
+        result[request] = predictions[request];
+    }
+    return result;
+  }
 };
 
 Gemma4BatchModelRunner::Gemma4BatchModelRunner(const Gemma4Config &config,
@@ -153,6 +175,17 @@ Gemma4BatchModelRunner::Gemma4BatchModelRunner(const Gemma4Config &config,
                                  &implementation_->handle));
   implementation_->batch = batch;
   implementation_->maximum_context = maximum_context;
+  {
+    // BF16 prefill reads the target's bf16 matrices straight from the DeviceWeightArena.
+    std::vector<carat_b200_layer_bf16_weights> bf16;
+    for (std::size_t index = 0; index < config.layers.size(); ++index) {
+      const std::string prefix = "layer." + std::to_string(index) + ".";
+      bf16.push_back({weights.at(prefix + "qkv"), weights.at(prefix + "o"),
+                      weights.at(prefix + "gate_up"), weights.at(prefix + "down")});
+    }
+    check(carat_b200_runner_set_bf16_weights(implementation_->handle, bf16.data(),
+                                             static_cast<int>(bf16.size())));
+  }
   if (with_assistant) {
     // The drafter's precision follows the reference's switch; its default runs every drafter
     // linear on the bf16 matrices of the assistant's DeviceWeightArena.
@@ -245,10 +278,82 @@ std::vector<int> Gemma4BatchModelRunner::append_ragged(const std::vector<int> &t
 
 int Gemma4BatchModelRunner::prefill_slot(int slot, const std::vector<int> &token_ids,
                                          int chunk_tokens) {
-  int next = -1;
-  check(carat_b200_runner_prefill_slot_fp8(implementation_->handle, slot, token_ids.data(),
-                                           static_cast<int>(token_ids.size()),
-                                           chunk_tokens < 8 ? chunk_tokens : 8, &next));
+  reset_slot(slot);
+  return prefill_slot_from_prefix(slot, token_ids, 0, chunk_tokens);
+}
+
+int Gemma4BatchModelRunner::prefill_slot_from_prefix(int slot, const std::vector<int> &token_ids,
+                                                     int cached_prefix_tokens, int chunk_tokens) {
+  if (slot < 0 || slot >= implementation_->batch || token_ids.empty() ||
+      token_ids.size() > static_cast<std::size_t>(implementation_->maximum_context) ||
+      chunk_tokens <= 0 || chunk_tokens > implementation_->maximum_context ||
+      cached_prefix_tokens < 0 || cached_prefix_tokens >= static_cast<int>(token_ids.size()) ||
+      slot_position(slot) != cached_prefix_tokens) {
+    throw std::runtime_error("invalid slot prefill shape");
+  }
+  std::optional<int> prediction;
+  while (!prediction)
+    prediction = prefill_slot_chunk(slot, token_ids, chunk_tokens);
+  return *prediction;
+}
+
+std::optional<int> Gemma4BatchModelRunner::prefill_slot_chunk(int slot,
+                                                              const std::vector<int> &token_ids,
+                                                              int chunk_tokens) {
+  if (slot < 0 || slot >= implementation_->batch || token_ids.empty() ||
+      token_ids.size() > static_cast<std::size_t>(implementation_->maximum_context) ||
+      chunk_tokens <= 0 || chunk_tokens > implementation_->maximum_context) {
+    throw std::runtime_error("invalid slot prefill chunk shape");
+  }
+  if (slot_position(slot) >= static_cast<int>(token_ids.size()))
+    throw std::runtime_error("slot prefill chunk does not extend resident context");
+  return implementation_->chunks({slot}, {&token_ids}, chunk_tokens).front();
+}
+
+std::vector<std::optional<int>>
+Gemma4BatchModelRunner::prefill_slots_chunks(const std::vector<int> &slots,
+                                             const std::vector<const std::vector<int> *> &token_ids,
+                                             int chunk_tokens) {
+  if (slots.empty() || token_ids.size() != slots.size() || chunk_tokens <= 0)
+    throw std::runtime_error("invalid batched chunk prefill shape");
+  return implementation_->chunks(slots, token_ids, chunk_tokens);
+}
+
+std::vector<int>
+Gemma4BatchModelRunner::prefill_slots_suffix(const std::vector<int> &slots,
+                                             const std::vector<const std::vector<int> *> &token_ids) {
+  if (slots.empty() || token_ids.size() != slots.size())
+    throw std::runtime_error("invalid batched suffix prefill shape");
+  std::vector<int> result;
+  for (const std::optional<int> &entry :
+       implementation_->chunks(slots, token_ids, implementation_->maximum_context)) {
+    result.push_back(entry.value());   // one chunk as long as the context holds any suffix
+  }
+  return result;
+}
+
+LayerSlicedSuffixPrefillResult Gemma4BatchModelRunner::prefill_slots_suffix_layer_slice(
+    const std::vector<int> &slots, const std::vector<const std::vector<int> *> &token_ids, int) {
+  // All layers in this call: the result is complete at once and nothing stays pending.
+  LayerSlicedSuffixPrefillResult result;
+  result.predictions = prefill_slots_suffix(slots, token_ids);
+  result.complete = true;
+  return result;
+}
+
+void Gemma4BatchModelRunner::abort_suffix_layer_slices() {}
+bool Gemma4BatchModelRunner::has_suffix_layer_slices() const { return false; }
+
+std::vector<int> Gemma4BatchModelRunner::append(const std::vector<int> &token_ids) {
+  if (token_ids.size() != static_cast<std::size_t>(implementation_->batch))
+    throw std::runtime_error("token batch has the wrong size");
+  if (implementation_->current_position >= implementation_->maximum_context)
+    throw std::runtime_error("batch context is full");
+  std::vector<int> slots(token_ids.size());
+  for (std::size_t slot = 0; slot < slots.size(); ++slot)
+    slots[slot] = static_cast<int>(slot);
+  std::vector<int> next = append_ragged(token_ids, slots);
+  ++implementation_->current_position;
   return next;
 }
 
@@ -265,6 +370,7 @@ void Gemma4BatchModelRunner::reset_slot(int slot) {
 
 void Gemma4BatchModelRunner::seed_empty_cache_for_benchmark(int position) {
   check(carat_b200_runner_seed_empty_cache_for_benchmark(implementation_->handle, position));
+  implementation_->current_position = position;
 }
 
 int Gemma4BatchModelRunner::batch() const { return implementation_->batch; }
@@ -275,32 +381,6 @@ int Gemma4BatchModelRunner::slot_position(int slot) const {
   return position;
 }
 
-// ---- outside the path
-std::vector<int> Gemma4BatchModelRunner::append(const std::vector<int> &) {
-  not_provided("Gemma4BatchModelRunner::append");
-}
-int Gemma4BatchModelRunner::prefill_slot_from_prefix(int, const std::vector<int> &, int, int) {
-  not_provided("Gemma4BatchModelRunner::prefill_slot_from_prefix");
-}
-std::optional<int> Gemma4BatchModelRunner::prefill_slot_chunk(int, const std::vector<int> &, int) {
-  not_provided("Gemma4BatchModelRunner::prefill_slot_chunk");
-}
-std::vector<std::optional<int>>
-Gemma4BatchModelRunner::prefill_slots_chunks(const std::vector<int> &,
-                                             const std::vector<const std::vector<int> *> &, int) {
-  not_provided("Gemma4BatchModelRunner::prefill_slots_chunks");
-}
-std::vector<int>
-Gemma4BatchModelRunner::prefill_slots_suffix(const std::vector<int> &,
-                                             const std::vector<const std::vector<int> *> &) {
-  not_provided("Gemma4BatchModelRunner::prefill_slots_suffix");
-}
-LayerSlicedSuffixPrefillResult Gemma4BatchModelRunner::prefill_slots_suffix_layer_slice(
-    const std::vector<int> &, const std::vector<const std::vector<int> *> &, int) {
-  not_provided("Gemma4BatchModelRunner::prefill_slots_suffix_layer_slice");
-}
-void Gemma4BatchModelRunner::abort_suffix_layer_slices() {}
-bool Gemma4BatchModelRunner::has_suffix_layer_slices() const { return false; }
-int Gemma4BatchModelRunner::position() const { not_provided("Gemma4BatchModelRunner::position"); }
+int Gemma4BatchModelRunner::position() const { return implementation_->current_position; }
 
 } // namespace carat

@@ -75,6 +75,10 @@ SIGNATURES = {
                                    POINTER(c_int)]),
     "ref_runner_append_ragged": (_I, [_P, POINTER(c_int), POINTER(c_int), _I, POINTER(c_int)]),
     "ref_runner_clone_slot": (_I, [_P, _I, _I, POINTER(ctypes.c_ulonglong)]),
+    "ref_runner_prefill_slot": (_I, [_P, _I, POINTER(c_int), _I, _I, POINTER(c_int)]),
+    "ref_runner_prefill_slots_chunks": (_I, [_P, POINTER(c_int), POINTER(POINTER(c_int)),
+                                            POINTER(c_int), _I, _I, POINTER(c_int),
+                                            POINTER(c_int)]),
     "ref_runner_reset_slot": (_I, [_P, _I]),
     "ref_runner_seed_empty_cache_for_benchmark": (_I, [_P, _I]),
     "ref_runner_slot_position": (_I, [_P, _I, POINTER(c_int)]),
@@ -88,6 +92,7 @@ SIGNATURES = {
 RUNNER_FACE = ("ref_last_error", "ref_runner_create", "ref_runner_destroy",
                "ref_runner_verify_greedy_proposals", "ref_runner_draft_four",
                "ref_runner_append_ragged", "ref_runner_clone_slot", "ref_runner_reset_slot",
+               "ref_runner_prefill_slot", "ref_runner_prefill_slots_chunks",
                "ref_runner_seed_empty_cache_for_benchmark", "ref_runner_slot_position")
 
 _library = None
@@ -228,6 +233,24 @@ class ReferenceRunner:
         self._check(self._library.ref_runner_append_ragged(self._handle, ints(tokens), ints(slots),
                                                      len(tokens), out))
         return list(out)
+
+    def prefill_slot(self, slot, tokens, chunk_tokens=1024):
+        out = c_int(0)
+        self._check(self._library.ref_runner_prefill_slot(self._handle, slot, ints(tokens),
+                                                          len(tokens), chunk_tokens,
+                                                          ctypes.byref(out)))
+        return out.value
+
+    def prefill_slots_chunks(self, slots, token_ids, chunk_tokens):
+        requests = len(slots)
+        arrays = [ints(tokens) for tokens in token_ids]
+        pointers = (POINTER(c_int) * requests)(*[ctypes.cast(a, POINTER(c_int)) for a in arrays])
+        predictions = (c_int * requests)()
+        has = (c_int * requests)()
+        self._check(self._library.ref_runner_prefill_slots_chunks(
+            self._handle, ints(slots), pointers, ints([len(t) for t in token_ids]), requests,
+            chunk_tokens, predictions, has))
+        return [predictions[r] if has[r] else None for r in range(requests)]
 
     def clone_slot(self, source, destination):
         copied = ctypes.c_ulonglong(0)

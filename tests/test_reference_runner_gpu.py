@@ -447,6 +447,15 @@ def test_drop_in_cpp_shim_runs_the_same_step(pair):
             pair.ours.append_ragged(first[:2], [0, LIVE])
         with pytest.raises(ref.ReferenceError_, match="invalid or repeated speculative slot"):
             shim.verify_greedy_proposals([[5, 6], [7, 8]], [5, 7], [3, 3])
+        # BF16 prefill through the shim's prefill_slot / prefill_slots_chunks: same as the mirror.
+        prompt = torch.randint(3, VOCABULARY, (45,), generator=generator).tolist()
+        assert shim.prefill_slot(20, prompt, 16) == pair.ours.prefill_slot(20, prompt, 16)
+        other = torch.randint(3, VOCABULARY, (30,), generator=generator).tolist()
+        for runner in (shim, pair.ours):
+            runner.reset_slot(21)
+            runner.reset_slot(22)
+        assert shim.prefill_slots_chunks([21, 22], [prompt, other], 64) == \
+            pair.ours.prefill_slots_chunks([21, 22], [prompt, other], 64)
     finally:
         shim.close()
 
