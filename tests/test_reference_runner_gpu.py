@@ -48,10 +48,11 @@ def _norm(width, generator):
 class Pair:
     """One set of weights, this repository's runner and the reference's runner over it."""
 
-    def __init__(self, sliding_layers=1):
+    def __init__(self, sliding_layers=1, global_layers=1, with_assistant=True):
         layers = [carat_b200.Gemma4LayerConfig("sliding", 32, 16, 256, 1e4, False)
                   for _ in range(sliding_layers)]
-        layers.append(carat_b200.Gemma4LayerConfig("global", 32, 4, 512, 1e6, True))
+        layers += [carat_b200.Gemma4LayerConfig("global", 32, 4, 512, 1e6, True)
+                   for _ in range(global_layers)]
         self.config = carat_b200.Gemma4Config(5376, 21504, VOCABULARY, 1024, 1e-6, layers)
         generator = torch.Generator(device="cuda").manual_seed(0)
         hidden, inter = self.config.hidden_size, self.config.intermediate_size
@@ -71,6 +72,13 @@ class Pair:
         self.weights = carat_b200.DeviceWeightArena(bf16)
         self.fp8 = carat_b200.Fp8WeightArena.quantize(self.weights)
 
+        if not with_assistant:
+            torch.cuda.synchronize()
+            self.ours = carat_b200.Gemma4BatchModelRunner(self.config, self.weights, SLOTS,
+                                                          MAX_CONTEXT, self.fp8)
+            self.theirs = ref.ReferenceRunner(self.config, self.weights.tensors, self.fp8.bytes,
+                                              self.fp8.scales, SLOTS, MAX_CONTEXT)
+            return
         self.assistant_config = carat_b200.Gemma4AssistantConfig()
         a_hidden, a_inter = 1024, 8192
         a = {"token_embedding": _random_matrix(VOCABULARY, a_hidden, generator, 0.05),
@@ -409,6 +417,51 @@ def test_six_layer_stack_free_running(cuda_device):
         assert ties.relative <= 4
     finally:
         deep.close()
+        torch.cuda.empty_cache()
+
+
+def test_bf16_prefill_against_the_reference_on_global_layers(cuda_device):
+    """Gemma4BatchModelRunner::prefill_slot of the reference itself (BF16 cuBLAS linears, its
+    tensor-core causal attention; cuda/batch_model_runner.cu:1048-1125) against this side's BF16
+    prefill, on a model of global layers only: the reference's sliding-layer prefill goes through
+    cuDNN's graph API, which the test build of the reference leaves out. Then both continue with
+    FP8 verify steps from the state each side built for itself."""
+    ref.library()
+    pair = Pair(sliding_layers=0, global_layers=2, with_assistant=False)
+    try:
+        generator = torch.Generator().manual_seed(21)
+        lengths = [200, 64, 333, 17]
+        prompts = [torch.randint(3, VOCABULARY, (n,), generator=generator).tolist() for n in lengths]
+        first_mine, first_theirs = [], []
+        for slot, prompt in enumerate(prompts):
+            first_theirs.append(pair.theirs.prefill_slot(slot, prompt, 128))
+            first_mine.append(pair.ours.prefill_slot(slot, prompt, 128))
+            assert pair.ours.slot_position(slot) == pair.theirs.slot_position(slot) == len(prompt)
+        differing = 0
+        for slot, (mine, theirs) in enumerate(zip(first_mine, first_theirs)):
+            if mine != theirs:
+                differing += 1
+        print(f"BF16 prefill first tokens differing from the reference: {differing} of "
+              f"{len(prompts)}")
+        assert differing <= 1
+        # Verify steps from the prefilled state (each side's own KV rows, equal up to bf16 noise).
+        live = list(range(len(prompts)))
+        first = list(first_theirs)
+        mismatches = 0
+        for _ in range(6):
+            proposals = [[first[row]] + torch.randint(3, VOCABULARY, (4,),
+                                                      generator=generator).tolist()
+                         for row in range(len(live))]
+            mine = pair.ours.verify_greedy_proposals(proposals, first, live)
+            theirs = pair.theirs.verify_greedy_proposals(proposals, first, live)
+            assert mine.accepted_tokens == theirs[0]
+            mismatches += sum(a != b for a, b in zip(mine.next_tokens, theirs[1]))
+            first = list(theirs[1])
+        print(f"next tokens differing over 6 verify steps after prefill: {mismatches} of "
+              f"{6 * len(live)}")
+        assert mismatches <= 2
+    finally:
+        pair.close()
         torch.cuda.empty_cache()
 
 
