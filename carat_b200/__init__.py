@@ -5,7 +5,8 @@ include/carat_b200.h); this package holds its sources, its build recipe and a th
 mirror of the reference's runner interface.
 """
 from .capi import CaratError, library  # noqa: F401
+from . import dispatcher, runner  # noqa: F401
 from .runner import (DeviceWeightArena, Fp8WeightArena, Gemma4AssistantConfig,  # noqa: F401
                      Gemma4BatchModelRunner, Gemma4Config, Gemma4LayerConfig,
-                     GreedyVerificationResult, Int4Bf16Linear, VERIFY_ASSUME_MATCH,
+                     GreedyVerificationResult, Int4Bf16Linear, LoadedWeights, VERIFY_ASSUME_MATCH,
                      quantize_tensor_to_fp8)

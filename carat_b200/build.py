@@ -12,7 +12,7 @@ import sys
 PACKAGE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = ["fp8_linear.cu", "fp8_linear_static.cu", "int4_linear.cu", "row_ops.cu", "qkv_post.cu", "attention_simt.cu", "attention_tc.cu",
     "attention_fused.cu", "attention_stream.cu", "accept.cu",
-           "context.cu", "selftest.cu", "runner.cu", "capi_linear.cu", "capi_ops.cu"]
+           "context.cu", "selftest.cu", "weights.cu", "placement.cu", "runner.cu", "capi_linear.cu", "capi_ops.cu"]
 LIBRARY = os.path.join(PACKAGE, "libcarat_b200.so")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC,-fvisibility=hidden", "-Xptxas", "-v"]

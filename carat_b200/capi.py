@@ -41,6 +41,28 @@ class Int4MlpLayer(Structure):
                 ("down_codes", c_void_p), ("down_scales", c_void_p)]
 
 
+class SlotView(Structure):
+    _fields_ = [("cached_tokens", POINTER(c_int)), ("cached_count", c_int32),
+                ("occupied", c_int32), ("age", ctypes.c_uint64), ("prefilling", c_int32)]
+
+
+class ReplicaView(Structure):
+    _fields_ = [("slots", POINTER(SlotView)), ("slot_count", c_int32),
+                ("queued_requests", c_int32), ("alive", c_int32)]
+
+
+class Placement(Structure):
+    _fields_ = [("decision", c_int32), ("replica", c_int32), ("destination", c_int32),
+                ("source", c_int32), ("prefix_tokens", ctypes.c_uint64)]
+
+
+class WeightSegment(Structure):
+    _fields_ = [("name", ctypes.c_char * 96), ("rank", c_int32),
+                ("shape", ctypes.c_uint64 * 2), ("arena_offset", ctypes.c_uint64),
+                ("byte_size", ctypes.c_uint64), ("bf16", c_void_p), ("fp8", c_void_p),
+                ("fp8_scale", c_void_p)]
+
+
 class LayerBf16Weights(Structure):
     _fields_ = [("qkv", c_void_p), ("o", c_void_p), ("gate_up", c_void_p), ("down", c_void_p)]
 
@@ -119,6 +141,16 @@ SIGNATURES = {
                                      POINTER(AssistantConfig), POINTER(AssistantWeights),
                                      POINTER(c_void_p)]),
     "carat_b200_runner_destroy": (None, [_P]),
+    "carat_b200_select_placement": (_I, [_IP, _I, POINTER(SlotView), _I, _I, POINTER(Placement)]),
+    "carat_b200_route_request": (_I, [_IP, _I, POINTER(ReplicaView), _I, _I, POINTER(Placement)]),
+    "carat_b200_weights_load": (_I, [c_char_p, POINTER(ModelConfig), POINTER(AssistantConfig), _I,
+                                    POINTER(c_void_p)]),
+    "carat_b200_weights_destroy": (None, [_P]),
+    "carat_b200_weights_segment_count": (_I, [_P]),
+    "carat_b200_weights_segment": (_I, [_P, _I, POINTER(WeightSegment)]),
+    "carat_b200_weights_find": (_I, [_P, c_char_p, POINTER(WeightSegment)]),
+    "carat_b200_weights_plan_text": (_I, [c_char_p, POINTER(ModelConfig), POINTER(AssistantConfig),
+                                         c_char_p, c_size_t, POINTER(c_size_t)]),
     "carat_b200_runner_set_bf16_weights": (_I, [_P, POINTER(LayerBf16Weights), _I]),
     "carat_b200_runner_prefill_slots_chunks": (_I, [_P, _IP, POINTER(_IP), _IP, _I, _I, _IP, _IP]),
     "carat_b200_runner_set_assistant_precision": (_I, [_P, _I, POINTER(AssistantBf16Weights)]),

@@ -86,6 +86,25 @@ class Gemma4AssistantConfig:
     rms_norm_epsilon: float = 1e-6
 
 
+def model_config_struct(config: "Gemma4Config"):
+    """capi.ModelConfig for `config`, plus the layer array it points into (keep both alive)."""
+    shapes = (capi.LayerShape * len(config.layers))()
+    for index, layer in enumerate(config.layers):
+        shapes[index] = capi.LayerShape(1 if layer.attention == "global" else 0, layer.query_heads,
+                                        layer.kv_heads, layer.head_dimension, layer.rope_theta,
+                                        1 if layer.key_equals_value else 0)
+    return capi.ModelConfig(config.hidden_size, config.intermediate_size, config.vocabulary_size,
+                            config.sliding_window, config.rms_norm_epsilon, len(config.layers),
+                            shapes), shapes
+
+
+def assistant_config_struct(config: "Gemma4AssistantConfig"):
+    kinds = (ctypes.c_int32 * len(config.layers))(
+        *[1 if kind == "global" else 0 for kind in config.layers])
+    return capi.AssistantConfig(config.hidden_size, config.intermediate_size, config.query_heads,
+                                len(config.layers), kinds, config.rms_norm_epsilon), kinds
+
+
 # --------------------------------------------------------------------------- weights
 class DeviceWeightArena:
     """BF16 segments by name (include/carat/device_weights.h DeviceWeightArena::at)."""
@@ -213,6 +232,70 @@ class Fp8WeightArena:
 
     def scale(self, name: str) -> torch.Tensor:
         return self.scales[name]
+
+
+class _DeviceView:
+    """Lets torch wrap device memory the C library owns (no copy)."""
+
+    def __init__(self, pointer: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr,
+                                         "data": (pointer, False), "version": 2}
+
+
+class LoadedWeights:
+    """A model directory loaded through the weight pipeline of the library
+    (carat_b200_weights_load: safetensors shards -> execution plan -> bf16 arena -> e4m3 arena;
+    ShardedSafetensors::open + WeightPlan::gemma4 + DeviceWeightArena::load +
+    Fp8WeightArena::quantize in the reference). `.bf16` and `.fp8` are the two arenas as the
+    runner's constructor takes them; their tensors view the library's device memory."""
+
+    def __init__(self, model_directory: str, config: Gemma4Config,
+                 assistant_config: Optional[Gemma4AssistantConfig] = None,
+                 quantize_fp8: bool = True):
+        self._library = capi.library()
+        self._handle = ctypes.c_void_p()
+        model_config, self._shapes = model_config_struct(config)
+        assistant = None
+        if assistant_config is not None:
+            assistant, self._kinds = assistant_config_struct(assistant_config)
+        check(self._library.carat_b200_weights_load(
+            model_directory.encode(), ctypes.byref(model_config),
+            ctypes.byref(assistant) if assistant is not None else None,
+            1 if quantize_fp8 else 0, ctypes.byref(self._handle)))
+        tensors, self.fp8 = {}, Fp8WeightArena()
+        for index in range(self._library.carat_b200_weights_segment_count(self._handle)):
+            segment = capi.WeightSegment()
+            check(self._library.carat_b200_weights_segment(self._handle, index,
+                                                           ctypes.byref(segment)))
+            name = segment.name.decode()
+            shape = [int(segment.shape[axis]) for axis in range(segment.rank)]
+            tensors[name] = torch.as_tensor(_DeviceView(segment.bf16, shape, "<u2"),
+                                            device="cuda").view(torch.bfloat16)
+            if segment.fp8:
+                self.fp8.add(name,
+                             torch.as_tensor(_DeviceView(segment.fp8, shape, "|u1"), device="cuda"),
+                             torch.as_tensor(_DeviceView(segment.fp8_scale, [1], "<f4"),
+                                             device="cuda"))
+        self.bf16 = DeviceWeightArena(tensors)
+
+    def find(self, name: str) -> capi.WeightSegment:
+        segment = capi.WeightSegment()
+        check(self._library.carat_b200_weights_find(self._handle, name.encode(),
+                                                    ctypes.byref(segment)))
+        return segment
+
+    def close(self) -> None:
+        if self._handle:
+            self.bf16 = None
+            self.fp8 = None
+            self._library.carat_b200_weights_destroy(self._handle)
+            self._handle = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # interpreter shutdown
+            pass
 
 
 @dataclass

@@ -534,6 +534,104 @@ CARAT_B200_API int carat_b200_runner_last_device_ms(const carat_b200_runner *run
 /* Kernel launches issued by the last verify / draft call. */
 CARAT_B200_API int carat_b200_runner_last_launches(const carat_b200_runner *runner, int *verify_launches,
                                     int *draft_launches);
+/* Request placement ------------------------------------------------------------------------------- */
+
+/* carat::SlotView (src/runtime/slot_policy.h:13-19): what the scheduler knows about one slot. */
+typedef struct carat_b200_slot_view {
+  const int *cached_tokens;   /* token ids resident in the slot's KV, host memory */
+  int32_t cached_count;
+  int32_t occupied;           /* a request is decoding or prefilling in it */
+  uint64_t age;               /* smaller = touched longer ago (eviction order) */
+  int32_t prefilling;
+} carat_b200_slot_view;
+
+/* One replica (one GPU, one runner) as the box-level router sees it. */
+typedef struct carat_b200_replica_view {
+  const carat_b200_slot_view *slots;
+  int32_t slot_count;
+  int32_t queued_requests;    /* admitted to this replica but not in a slot yet */
+  int32_t alive;              /* 0: the replica left; never chosen */
+} carat_b200_replica_view;
+
+#define CARAT_B200_PLACED 0
+#define CARAT_B200_NO_FREE_SLOT 1
+#define CARAT_B200_RESERVE_BLOCKED 2
+
+/* carat::PlacementDecision (src/runtime/slot_policy.h:27-37) plus the chosen replica. */
+typedef struct carat_b200_placement {
+  int32_t decision;           /* CARAT_B200_PLACED / NO_FREE_SLOT / RESERVE_BLOCKED */
+  int32_t replica;
+  int32_t destination;        /* slot the request goes to */
+  int32_t source;             /* slot whose cached prefix it reuses, -1 = none */
+  uint64_t prefix_tokens;     /* length of that prefix */
+} carat_b200_placement;
+
+/* The reference's slot choice inside one replica: carat::select_placement
+ * (src/runtime/slot_policy.cpp:22-84), same decisions on the same views. Host only. */
+CARAT_B200_API int carat_b200_select_placement(const int *input_ids, int input_count,
+                                               const carat_b200_slot_view *slots, int slot_count,
+                                               int idle_cache_reserve_slots,
+                                               carat_b200_placement *placement);
+
+/* Box-level routing over independent full-model replicas, which the single-GPU reference does
+ * not have: the replica whose placement reuses the longest cached prefix, then the least loaded
+ * (occupied slots + queued requests), then the lowest index; replicas that left are skipped.
+ * RESERVE_BLOCKED when no replica can place the request and at least one was held back by its
+ * idle-cache reserve. Host only; no data moves between replicas. */
+CARAT_B200_API int carat_b200_route_request(const int *input_ids, int input_count,
+                                            const carat_b200_replica_view *replicas,
+                                            int replica_count, int idle_cache_reserve_slots,
+                                            carat_b200_placement *placement);
+
+/* Weight pipeline ---------------------------------------------------------------------------------- */
+
+/* One execution segment of a loaded model (carat::WeightSegment, include/carat/weight_plan.h:18-24,
+ * plus where it lives on the device). Names are the reference's: token_embedding,
+ * layer.N.{input_norm,q_norm,k_norm,qkv,o,post_attention_norm,pre_mlp_norm,gate_up,down,
+ * post_mlp_norm,scalar}, final_norm; the drafter adds pre_projection, post_projection and
+ * layer.N.q (src/weight_plan.cpp:37-128). */
+typedef struct carat_b200_weight_segment {
+  char name[96];
+  int32_t rank;             /* 1 or 2 */
+  uint64_t shape[2];        /* [out, in] for matrices */
+  uint64_t arena_offset;    /* bytes from the start of the bf16 arena, 256-byte aligned */
+  uint64_t byte_size;       /* bf16 bytes */
+  const void *bf16;         /* device pointer (DeviceWeightArena::at) */
+  const void *fp8;          /* e4m3 bytes, NULL for vectors or when not quantised (Fp8WeightArena::at) */
+  const float *fp8_scale;   /* one fp32 on the device (Fp8WeightArena::scale) */
+} carat_b200_weight_segment;
+
+typedef struct carat_b200_weights carat_b200_weights;
+
+/* Reads a Hugging Face model directory (model.safetensors.index.json + shards, or a single
+ * model.safetensors), builds the execution plan with the reference's checks and messages, uploads
+ * every BF16 segment into one device arena (fused qkv and gate_up segments are stacked from their
+ * source tensors) and, when quantize_fp8 is non-zero, quantises every matrix to e4m3 with one
+ * tensor scale on the device as it arrives. `assistant` NULL loads the target described by
+ * `config`; otherwise the drafter, whose pre/post projections take the target's hidden size and
+ * vocabulary from `config`. Replaces ShardedSafetensors::open + WeightPlan::gemma4 /
+ * gemma4_assistant + DeviceWeightArena::load + Fp8WeightArena::quantize (src/safetensors.cpp,
+ * src/weight_plan.cpp:198-222, cuda/device_weights.cu:100-263). */
+CARAT_B200_API int carat_b200_weights_load(const char *model_directory,
+                                           const carat_b200_model_config *config,
+                                           const carat_b200_assistant_config *assistant,
+                                           int quantize_fp8, carat_b200_weights **weights);
+CARAT_B200_API void carat_b200_weights_destroy(carat_b200_weights *weights);
+CARAT_B200_API int carat_b200_weights_segment_count(const carat_b200_weights *weights);
+CARAT_B200_API int carat_b200_weights_segment(const carat_b200_weights *weights, int index,
+                                              carat_b200_weight_segment *segment);
+/* "missing execution weight NAME" when there is no such segment (WeightPlan::at). */
+CARAT_B200_API int carat_b200_weights_find(const carat_b200_weights *weights, const char *name,
+                                           carat_b200_weight_segment *segment);
+/* The plan alone, as text, without touching a device (validate_gemma4_weights and the inspect
+ * tool's view): "arena_bytes N" then one line per segment, "NAME shape .. offset N bytes N
+ * sources TENSOR@OFFSET ..". *needed receives the size including the terminator; the text is
+ * written when buffer_bytes suffices. */
+CARAT_B200_API int carat_b200_weights_plan_text(const char *model_directory,
+                                                const carat_b200_model_config *config,
+                                                const carat_b200_assistant_config *assistant,
+                                                char *buffer, size_t buffer_bytes, size_t *needed);
+
 /* The target's matrices in bf16 (carat::DeviceWeightArena::at: layer.N.qkv / o / gate_up / down,
  * row-major [out, in]); the tied LM head is the bf16 token embedding the runner already holds.
  * Needed only for BF16 prefill. */

@@ -34,3 +34,33 @@ extern "C" int ref_commit_speculation(int forced_token, const int *accepted_draf
   *next_out = commit.next_token;
   return commit.stopped ? 1 : 0;
 }
+
+// carat::select_placement over flat arrays: slot i's cached tokens are
+// cached[offsets[i] .. offsets[i + 1]). Returns 0 placed, 1 no free slot, 2 reserve blocked.
+#include "runtime/slot_policy.h"
+
+extern "C" int ref_select_placement(const int *input_ids, int input_count, const int *cached,
+                                    const int *offsets, const int *occupied,
+                                    const unsigned long long *ages, const int *prefilling,
+                                    int slot_count, int reserve, int *destination, int *source,
+                                    unsigned long long *prefix_tokens) {
+  std::vector<carat::SlotView> slots(static_cast<std::size_t>(slot_count));
+  for (int index = 0; index < slot_count; ++index) {
+    slots[static_cast<std::size_t>(index)] = carat::SlotView{
+        .cached_tokens = std::span<const int>(
+            cached + offsets[index], static_cast<std::size_t>(offsets[index + 1] - offsets[index])),
+        .occupied = occupied[index] != 0,
+        .age = ages[index],
+        .prefilling = prefilling[index] != 0};
+  }
+  const auto decision = carat::select_placement(
+      std::span<const int>(input_ids, static_cast<std::size_t>(input_count)), slots,
+      static_cast<std::size_t>(reserve));
+  if (const auto *placement = std::get_if<carat::Placement>(&decision)) {
+    *destination = placement->destination;
+    *source = placement->source.value_or(-1);
+    *prefix_tokens = placement->prefix_tokens;
+    return 0;
+  }
+  return std::holds_alternative<carat::NoFreeSlot>(decision) ? 1 : 2;
+}
