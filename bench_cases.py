@@ -50,6 +50,34 @@ def linear(rows=120, k=5376, n=43008, launches=4):
         print(f"linear {rows}x{k}x{n}: {micro:.1f} us per call, {k * n / micro / 1e6:.2f} TB/s of weights")
 
 
+def gated(rows=120, k=5376, n=21504, launches=4):
+    """gate_up with GeGLU in the epilogue; n is the gated (intermediate) width."""
+    library = capi.library()
+    weight, activation = _fp8(2 * n, k, 1), _fp8(rows, k, 2)
+    weight_scale = activation_scale = torch.full((1,), 0.01, dtype=torch.float32, device="cuda")
+    needed = library.carat_b200_fp8_linear_geglu_workspace_bytes(rows, k, n)
+    workspace = torch.empty(needed, dtype=torch.uint8, device="cuda")
+    activated = torch.empty(rows, n, dtype=torch.bfloat16, device="cuda")
+    amax = torch.zeros(1, dtype=torch.int32, device="cuda")
+    quantised = torch.empty(rows, n, dtype=torch.uint8, device="cuda")
+    out_scale = torch.zeros(1, dtype=torch.float32, device="cuda")
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    for launch in range(launches):
+        if launch == 1:
+            start.record()
+        check(library.carat_b200_fp8_linear_geglu(
+            _ptr(activation), _ptr(activation_scale), _ptr(weight), _ptr(weight_scale),
+            _ptr(activated), _ptr(amax), _ptr(quantised), _ptr(out_scale), rows, k, n,
+            _ptr(workspace), needed, None))
+    stop.record()
+    torch.cuda.synchronize()
+    if launches > 1:
+        micro = start.elapsed_time(stop) / (launches - 1) * 1e3
+        print(f"gated linear {rows}x{k}x2*{n}: {micro:.1f} us per call (with two small memsets), "
+              f"{2 * k * n / micro / 1e6:.2f} TB/s of weights")
+
+
 def int4(rows=120, k=5376, n=43008, launches=4, group_width=128):
     library = capi.library()
     generator = torch.Generator(device="cuda").manual_seed(0)
@@ -97,7 +125,7 @@ def lm_head(rows=120, k=5376, n=262144, launches=3):
 
 
 def attention(head_dim=256, heads=32, kv_heads=16, window=1024, capacity=1024, position=3000,
-              requests=24, depth=5, launches=3):
+              requests=24, depth=5, launches=3, contexts=None):
     library = capi.library()
     generator = torch.Generator(device="cuda").manual_seed(0)
 
@@ -110,9 +138,13 @@ def attention(head_dim=256, heads=32, kv_heads=16, window=1024, capacity=1024, p
     staged = window > 0
     new_keys = normal(requests, kv_heads, depth, head_dim) if staged else None
     new_values = normal(requests, kv_heads, depth, head_dim) if staged else None
+    if contexts is not None:
+        position = max(contexts)
     rows = min(position, capacity) if staged else position + depth
     stride = 16 + (rows + 127) // 128 * 128
     positions = torch.full((requests,), position, dtype=torch.int32, device="cuda")
+    if contexts is not None:
+        positions = torch.tensor(list(contexts), dtype=torch.int32, device="cuda")
     out = torch.empty(requests * depth, heads * head_dim, dtype=torch.bfloat16, device="cuda")
     scores = torch.empty(requests * heads * depth * stride, dtype=torch.bfloat16, device="cuda")
     start = torch.cuda.Event(enable_timing=True)
@@ -127,8 +159,11 @@ def attention(head_dim=256, heads=32, kv_heads=16, window=1024, capacity=1024, p
     stop.record()
     torch.cuda.synchronize()
     if launches > 1:
-        print(f"attention head_dim={head_dim}: {start.elapsed_time(stop) / (launches - 1) * 1e3:.1f} us "
-              f"per call over {launches - 1} calls")
+        micro = start.elapsed_time(stop) / (launches - 1) * 1e3
+        each = positions.clamp(max=capacity) if staged else positions + depth
+        moved = int(each.sum()) * kv_heads * head_dim * 2 * 2
+        print(f"attention head_dim={head_dim}: {micro:.1f} us per call over {launches - 1} calls, "
+              f"{moved / 1e6:.0f} MB of K and V, {moved / micro / 1e6:.2f} TB/s")
 
 
 def global_attention(launches=3):
@@ -136,7 +171,15 @@ def global_attention(launches=3):
               launches=launches)
 
 
-CASES = {"linear": linear, "int4": int4, "lm_head": lm_head, "attention": attention, "global": global_attention}
+def global_ragged(launches=3):
+    """Global layer at the benchmark's ragged contexts (128..6144 tokens, seed of rank 0)."""
+    import bench
+    attention(head_dim=512, heads=32, kv_heads=4, window=0, capacity=8192,
+              contexts=bench.context_lengths(seed=3), launches=launches)
+
+
+CASES = {"linear": linear, "gated": gated, "int4": int4, "lm_head": lm_head, "attention": attention, "global": global_attention,
+         "global_ragged": global_ragged}
 
 
 

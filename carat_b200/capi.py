@@ -107,6 +107,8 @@ SIGNATURES = {
     "carat_b200_selftest_bounded_wait": (_I, [_P, _P]),
     "carat_b200_fp8_linear": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P, c_size_t, _P]),
     "carat_b200_fp8_linear_workspace_bytes": (c_size_t, [_I, _I, _I]),
+    "carat_b200_fp8_linear_geglu": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, c_size_t, _P]),
+    "carat_b200_fp8_linear_geglu_workspace_bytes": (c_size_t, [_I, _I, _I]),
     "carat_b200_fp8_linear_static": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "carat_b200_fp8_linear_argmax": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "carat_b200_fp8_linear_check": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
@@ -119,6 +121,7 @@ SIGNATURES = {
     "carat_b200_int4_linear_workspace_bytes": (c_size_t, [_I, _I, _I]),
     "carat_b200_int4_linear_check": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "carat_b200_quantize_bf16_to_fp8": (_I, [_P, _P, _P, _P, _I, _I, _P]),
+    "carat_b200_quantize_bf16_to_fp8_from_amax": (_I, [_P, _P, _P, _P, c_size_t, _P]),
     "carat_b200_quantize_bf16_tensor_to_fp8": (_I, [_P, _P, _P, _P, c_size_t, _P]),
     "carat_b200_rms_norm_quantize": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _P]),
     "carat_b200_rms_norm_add_and_norm_quantize": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _F,

@@ -56,13 +56,12 @@ struct StreamItem {
   __device__ __forceinline__ bool empty() const { return rows_here <= 0 && proposals <= 0; }
 };
 
-__device__ __forceinline__ StreamItem stream_item(const AttentionArguments &a, int index) {
+__device__ __forceinline__ StreamItem stream_item(const AttentionArguments &a, int request,
+                                                  int kv_head, int chunk) {
   StreamItem item;
-  const int per_chunk = a.requests * a.kv_heads;
-  item.chunk = index / per_chunk;
-  const int remainder = index - item.chunk * per_chunk;
-  item.request = remainder / a.kv_heads;
-  item.kv_head = remainder - item.request * a.kv_heads;
+  item.chunk = chunk;
+  item.request = request;
+  item.kv_head = kv_head;
   const KeyGeometry g = key_geometry(a, item.request);
   const int group = a.query_heads / a.kv_heads;
   item.position = a.positions[item.request];
@@ -78,24 +77,108 @@ __device__ __forceinline__ StreamItem stream_item(const AttentionArguments &a, i
   return item;
 }
 
-// Every role of a CTA walks the same items (index = blockIdx.x + n * gridDim.x). Decoding one costs
-// two divisions and dependent global loads, which a single-thread issue loop cannot hide, so the
-// CTA decodes its first items once, in parallel, into shared memory.
+// Which items a CTA walks. Contexts are ragged, so dealing (chunk, request, head) triples out by
+// index leaves some CTAs with three full chunks and others with one short one, and the kernel
+// takes as long as its busiest CTA. Instead the items that exist are put in descending order of
+// their cache rows (all full chunks first, then every request's last, partial chunk, longest
+// first) and dealt out boustrophedon: round 0 to CTAs 0..G-1, round 1 to G-1..0, and so on, so
+// the CTA that got the larger item of one round gets the smaller of the next. Every CTA computes
+// the same order from the positions; every role of a CTA then walks the CTA's own short list.
 constexpr int cached_items = 32;
+constexpr int schedule_requests = 64;
 
-__device__ __forceinline__ void fill_item_cache(const AttentionArguments &a, int items,
-                                                StreamItem *cache) {
-  const int slot = static_cast<int>(threadIdx.x);
-  if (slot < cached_items) {
-    const int index = static_cast<int>(blockIdx.x) + slot * static_cast<int>(gridDim.x);
-    if (index < items)
-      cache[slot] = stream_item(a, index);
+struct StreamSchedule {
+  int count;                              // items of this CTA
+  int full_chunks[schedule_requests];     // whole chunks of each request
+  int full_before[schedule_requests];     // whole chunks of the requests before it
+  int by_rank[schedule_requests];         // requests that have a last partial chunk, longest first
+  int partial_rows[schedule_requests];    // rows of that chunk, -1 = the request has none
+  int total_full;
+  int total_partial;
+  StreamItem items[cached_items];
+};
+
+// Position `ordinal` of this CTA's list in the global order, or -1 past the end.
+__device__ __forceinline__ int dealt_index(int ordinal, int total) {
+  const int grid = static_cast<int>(gridDim.x);
+  const int block = static_cast<int>(blockIdx.x);
+  const int index = ordinal * grid + ((ordinal & 1) != 0 ? grid - 1 - block : block);
+  return index < total ? index : -1;
+}
+
+__device__ __forceinline__ StreamItem scheduled_item(const AttentionArguments &a,
+                                                     const StreamSchedule &schedule, int index) {
+  const int whole = schedule.total_full * a.kv_heads;
+  if (index < whole) {
+    const int chunk_index = index / a.kv_heads;
+    int request = 0;
+    while (request + 1 < a.requests && schedule.full_before[request + 1] <= chunk_index)
+      ++request;
+    return stream_item(a, request, index - chunk_index * a.kv_heads,
+                       chunk_index - schedule.full_before[request]);
+  }
+  const int rank = (index - whole) / a.kv_heads;
+  const int request = schedule.by_rank[rank];
+  return stream_item(a, request, index - whole - rank * a.kv_heads, schedule.full_chunks[request]);
+}
+
+// Called by the whole CTA, followed by __syncthreads().
+__device__ __forceinline__ void build_schedule(const AttentionArguments &a,
+                                               StreamSchedule &schedule) {
+  const int thread = static_cast<int>(threadIdx.x);
+  if (thread < a.requests) {
+    const KeyGeometry g = key_geometry(a, thread);
+    const int whole = g.cache_rows / a.chunk_keys;
+    const int rest = g.cache_rows - whole * a.chunk_keys;
+    schedule.full_chunks[thread] = whole;
+    // Proposals ride with chunk 0, which therefore exists even when the cache is still empty.
+    schedule.partial_rows[thread] = rest > 0 || (whole == 0 && g.proposals > 0) ? rest : -1;
+  }
+  __syncthreads();
+  if (thread < a.requests) {
+    int before = 0;
+    int rank = 0;
+    const int mine = schedule.partial_rows[thread];
+    for (int other = 0; other < a.requests; ++other) {
+      if (other < thread)
+        before += schedule.full_chunks[other];
+      const int theirs = schedule.partial_rows[other];
+      if (theirs >= 0 && (theirs > mine || (theirs == mine && other < thread)))
+        ++rank;
+    }
+    schedule.full_before[thread] = before;
+    if (mine >= 0)
+      schedule.by_rank[rank] = thread;
+    if (thread == a.requests - 1)
+      schedule.total_full = before + schedule.full_chunks[thread];
+  }
+  if (thread == 0) {
+    int partial = 0;
+    for (int request = 0; request < a.requests; ++request)
+      partial += schedule.partial_rows[request] >= 0 ? 1 : 0;
+    schedule.total_partial = partial;
+  }
+  __syncthreads();
+  const int total = (schedule.total_full + schedule.total_partial) * a.kv_heads;
+  if (thread < cached_items) {
+    const int index = dealt_index(thread, total);
+    if (index >= 0)
+      schedule.items[thread] = scheduled_item(a, schedule, index);
+  }
+  if (thread == 0) {
+    int count = 0;
+    while (dealt_index(count, total) >= 0)
+      ++count;
+    schedule.count = count;
   }
 }
 
-__device__ __forceinline__ StreamItem cached_item(const AttentionArguments &a, int index,
-                                                  int ordinal, const StreamItem *cache) {
-  return ordinal < cached_items ? cache[ordinal] : stream_item(a, index);
+__device__ __forceinline__ StreamItem cached_item(const AttentionArguments &a,
+                                                  const StreamSchedule &schedule, int ordinal) {
+  if (ordinal < cached_items)
+    return schedule.items[ordinal];
+  const int total = (schedule.total_full + schedule.total_partial) * a.kv_heads;
+  return scheduled_item(a, schedule, dealt_index(ordinal, total));
 }
 
 template <int stages> struct Cursor {
@@ -173,7 +256,7 @@ constexpr int scores_threads = 64 + scores_epilogue_threads;   // warp 0 TMA, wa
 template <int dimension, int padded_rows> struct ScoresShape {
   static constexpr int subtiles = dimension / 64;
   static constexpr int query_bytes = subtiles * padded_rows * 128;
-  static constexpr int budget = 227 * 1024 - 1024 - 4096 - query_bytes;
+  static constexpr int budget = 227 * 1024 - 1024 - 8192 - query_bytes;
   static constexpr int stages = budget / stream_stage_bytes > 5 ? 5 : budget / stream_stage_bytes;
   static constexpr int shared_bytes = query_bytes + stages * stream_stage_bytes + 1024;
 };
@@ -202,7 +285,7 @@ scores_stream_kernel(const __grid_constant__ CUtensorMap key_map,
   __shared__ float warp_maxima[scores_epilogue_warps][slots];
   __shared__ float warp_sums[scores_epilogue_warps][slots];
   __shared__ uint32_t token_slots[scores_row_groups][proposal_columns];
-  __shared__ StreamItem item_cache[cached_items];
+  __shared__ StreamSchedule schedule;
   volatile int *abort_flag = &abort_word;
   const uint32_t base = (ptx::smem_u32(shared_raw) + 1023U) & ~1023U;
   const uint32_t query_tiles = base;
@@ -245,7 +328,7 @@ scores_stream_kernel(const __grid_constant__ CUtensorMap key_map,
   ptx::tcgen05_fence_after_thread_sync();
   const uint32_t tmem_base = tmem_base_slot;
   grid_dependency_wait();
-  fill_item_cache(a, args.items, item_cache);
+  build_schedule(a, schedule);
   __syncthreads();
 
   if (warp == 0) {
@@ -255,9 +338,8 @@ scores_stream_kernel(const __grid_constant__ CUtensorMap key_map,
       Cursor<stages> cursor;
       bool healthy = true;
       uint32_t local = 0;
-      for (int index = static_cast<int>(blockIdx.x), ordinal = 0; index < args.items && healthy;
-           index += static_cast<int>(gridDim.x), ++ordinal) {
-        const StreamItem item = cached_item(a, index, ordinal, item_cache);
+      for (int ordinal = 0; ordinal < schedule.count && healthy; ++ordinal) {
+        const StreamItem item = cached_item(a, schedule, ordinal);
         if (item.empty())
           continue;
         // One query buffer: it is free once every score instruction of the previous item is done.
@@ -361,9 +443,8 @@ scores_stream_kernel(const __grid_constant__ CUtensorMap key_map,
       uint32_t accumulator_phase = 0;
       bool healthy = true;
       uint32_t local = 0;
-      for (int index = static_cast<int>(blockIdx.x), ordinal = 0; index < args.items && healthy;
-           index += static_cast<int>(gridDim.x), ++ordinal) {
-        const StreamItem item = cached_item(a, index, ordinal, item_cache);
+      for (int ordinal = 0; ordinal < schedule.count && healthy; ++ordinal) {
+        const StreamItem item = cached_item(a, schedule, ordinal);
         if (item.empty())
           continue;
         if (!ptx::mbarrier_wait_checked(query_full_bar, local & 1U, abort_flag, args.device_error, 42)) {
@@ -441,9 +522,8 @@ scores_stream_kernel(const __grid_constant__ CUtensorMap key_map,
     asm volatile("bar.sync 1, %0;" ::"n"(scores_epilogue_threads) : "memory");
     auto *scores = static_cast<__nv_bfloat16 *>(a.scores);
     uint32_t tiles_done = 0;
-    for (int index = static_cast<int>(blockIdx.x), ordinal = 0; index < args.items;
-         index += static_cast<int>(gridDim.x), ++ordinal) {
-      const StreamItem item = cached_item(a, index, ordinal, item_cache);
+    for (int ordinal = 0; ordinal < schedule.count; ++ordinal) {
+      const StreamItem item = cached_item(a, schedule, ordinal);
       if (item.empty())
         continue;
       const int newest_row = item.position > 0 ? (item.position - 1) % a.capacity : 0;
@@ -578,7 +658,7 @@ template <int dimension, int padded_rows> struct ValuesShape {
   static constexpr int stage_bytes = boxes * value_box_bytes;     // 32 KB at 512, 16 KB at 256
   static constexpr int probability_box_bytes = padded_rows * 128; // [rows x 64 keys]
   static constexpr int probability_boxes = 6;
-  static constexpr int budget = 227 * 1024 - 1024 - 3072 - probability_boxes * probability_box_bytes;
+  static constexpr int budget = 227 * 1024 - 1024 - 6144 - probability_boxes * probability_box_bytes;
   static constexpr int fit = budget / stage_bytes;
   static constexpr int stages = fit > 10 ? 10 : fit;
   static constexpr int output_columns = slices * padded_rows;
@@ -609,7 +689,7 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
   __shared__ __align__(8) unsigned long long barriers[2 * stages + 2 * probability_boxes + 4];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_word;
-  __shared__ StreamItem item_cache[cached_items];
+  __shared__ StreamSchedule schedule;
   // Element offset of query row r inside a (request, kv head) block of the output:
   // token(r) * width + head(r) * dimension.
   __shared__ int row_offset[padded_rows];
@@ -664,7 +744,7 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
   ptx::tcgen05_fence_after_thread_sync();
   const uint32_t tmem_base = tmem_base_slot;
   grid_dependency_wait();
-  fill_item_cache(a, args.items, item_cache);
+  build_schedule(a, schedule);
   __syncthreads();
 
   if (warp == 0) {
@@ -673,9 +753,8 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
       const uint64_t reuse_policy = ptx::policy_evict_last();
       Cursor<stages> cursor;
       bool healthy = true;
-      for (int index = static_cast<int>(blockIdx.x), ordinal = 0; index < args.items && healthy;
-           index += static_cast<int>(gridDim.x), ++ordinal) {
-        const StreamItem item = cached_item(a, index, ordinal, item_cache);
+      for (int ordinal = 0; ordinal < schedule.count && healthy; ++ordinal) {
+        const StreamItem item = cached_item(a, schedule, ordinal);
         if (item.empty())
           continue;
         if (item.proposals > 0) {
@@ -727,9 +806,8 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
       Cursor<probability_boxes> probability_cursor;
       bool healthy = true;
       uint32_t local = 0;
-      for (int index = static_cast<int>(blockIdx.x), ordinal = 0; index < args.items && healthy;
-           index += static_cast<int>(gridDim.x), ++ordinal) {
-        const StreamItem item = cached_item(a, index, ordinal, item_cache);
+      for (int ordinal = 0; ordinal < schedule.count && healthy; ++ordinal) {
+        const StreamItem item = cached_item(a, schedule, ordinal);
         if (item.empty())
           continue;
         const uint32_t buffer = output_buffers == 2 ? (local & 1U) : 0U;
@@ -818,9 +896,8 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
     const int width = a.query_heads * dimension;
     const size_t chunk_elements = static_cast<size_t>(a.requests) * a.depth * width;
     uint32_t local = 0;
-    for (int index = static_cast<int>(blockIdx.x), ordinal = 0; index < args.items;
-         index += static_cast<int>(gridDim.x), ++ordinal) {
-      const StreamItem item = cached_item(a, index, ordinal, item_cache);
+    for (int ordinal = 0; ordinal < schedule.count; ++ordinal) {
+      const StreamItem item = cached_item(a, schedule, ordinal);
       if (item.empty())
         continue;
       if (a.chunks > 1 && item.chunk == 0 && item.kv_head == 0 && warp == 2 && lane == 0) {
@@ -881,9 +958,8 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
     const auto *scores = static_cast<const __nv_bfloat16 *>(a.scores);
     Cursor<probability_boxes> cursor;
     uint32_t local = 0;
-    for (int index = static_cast<int>(blockIdx.x), ordinal = 0; index < args.items;
-         index += static_cast<int>(gridDim.x), ++ordinal) {
-      const StreamItem item = cached_item(a, index, ordinal, item_cache);
+    for (int ordinal = 0; ordinal < schedule.count; ++ordinal) {
+      const StreamItem item = cached_item(a, schedule, ordinal);
       if (item.empty())
         continue;
       const uint32_t parity = local & 1U;
@@ -1080,7 +1156,8 @@ int launch_stream_rows(const AttentionArguments &a, int *device_error, cudaStrea
 int launch_attention_stream(const AttentionArguments &a, int *device_error, cudaStream_t stream) {
   if (a.maps == nullptr || a.stats == nullptr || a.stats_stride < a.chunks || a.chunks < 1 ||
       (a.chunks > 1 && (a.chunk_partials == nullptr || a.request_chunks == nullptr)) ||
-      a.chunk_keys <= 0 || a.chunk_keys % stream_tile_keys != 0 ||
+      a.requests > schedule_requests || a.chunk_keys <= 0 ||
+      a.chunk_keys % stream_tile_keys != 0 ||
       a.capacity % stream_tile_keys != 0) {
     return -1;
   }

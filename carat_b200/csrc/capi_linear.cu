@@ -102,6 +102,72 @@ extern "C" int carat_b200_fp8_linear_argmax(const void *fp8_input, const float *
                        "argmax unpack");
 }
 
+// gate_up linear with GeGLU in the epilogue -----------------------------------------------------
+
+namespace {
+constexpr size_t gated_counter_bytes = 256;   // the grid barrier's word, on a line of its own
+
+size_t gated_tail_bytes(int rows, int input_width, int gated_width, int element_bytes) {
+  if (rows <= 0 || rows > 256 || input_width <= 0 || gated_width <= 0)
+    return 0;
+  LinearPlan plan{};
+  schedule_linear_shape(&plan, rows, input_width, 2 * gated_width, 1, element_bytes);
+  return (linear_tail_bytes(plan) + 255) / 256 * 256;
+}
+} // namespace
+
+extern "C" size_t carat_b200_fp8_linear_geglu_workspace_bytes(int rows, int input_width,
+                                                              int gated_width) {
+  return gated_tail_bytes(rows, input_width, gated_width, 1) + gated_counter_bytes;
+}
+
+extern "C" int carat_b200_fp8_linear_geglu(const void *fp8_input, const float *device_input_scale,
+                                           const void *fp8_weight,
+                                           const float *device_weight_scale, void *bf16_activated,
+                                           unsigned int *device_amax_bits, void *fp8_output,
+                                           float *device_output_scale, int rows, int input_width,
+                                           int gated_width, void *workspace,
+                                           size_t workspace_bytes, void *stream) {
+  if (device_input_scale == nullptr || device_weight_scale == nullptr ||
+      bf16_activated == nullptr || device_amax_bits == nullptr ||
+      (fp8_output != nullptr && device_output_scale == nullptr)) {
+    set_last_error("invalid FP8 linear shape");
+    return -1;
+  }
+  LinearPlan plan;
+  const char *message = "invalid FP8 linear shape";
+  int status = make_gated_linear_plan(&plan, fp8_input, fp8_weight, rows, input_width, gated_width,
+                                      &message, 1);
+  if (status != 0) {
+    set_last_error(message);
+    return status;
+  }
+  const size_t tail_bytes = gated_tail_bytes(rows, input_width, gated_width, 1);
+  if (workspace == nullptr || workspace_bytes < tail_bytes + gated_counter_bytes) {
+    set_last_error("FP8 linear workspace is too small");
+    return -6;
+  }
+  int *error_word = device_error_word();
+  if (error_word == nullptr) {
+    set_last_error("device error word is unavailable");
+    return -101;
+  }
+  const auto cuda_stream = static_cast<cudaStream_t>(stream);
+  auto *counter =
+      reinterpret_cast<unsigned int *>(static_cast<unsigned char *>(workspace) + tail_bytes);
+  status = check_cuda(cudaMemsetAsync(counter, 0, gated_counter_bytes, cuda_stream),
+                      "clear grid counter");
+  if (status == 0)
+    status = check_cuda(cudaMemsetAsync(device_amax_bits, 0, sizeof(unsigned int), cuda_stream),
+                        "clear activation maximum");
+  if (status != 0)
+    return status;
+  status = launch_linear_gated(plan, device_input_scale, device_weight_scale, bf16_activated,
+                               device_amax_bits, fp8_output, device_output_scale,
+                               static_cast<float *>(workspace), counter, error_word, cuda_stream);
+  return launch_status(status, "FP8 gated linear");
+}
+
 extern "C" int carat_b200_fp8_linear_check(const void *fp8_input, const float *device_input_scale,
                                            const void *fp8_weight,
                                            const float *device_weight_scale, void *bf16_output,

@@ -59,6 +59,24 @@ extern "C" int carat_b200_quantize_bf16_to_fp8(const void *bf16_input, void *fp8
                 "FP8 quantization");
 }
 
+extern "C" int carat_b200_quantize_bf16_to_fp8_from_amax(const void *bf16_input,
+                                                         const unsigned int *device_amax_bits,
+                                                         void *fp8_output, float *device_scale,
+                                                         size_t elements, void *stream) {
+  if (bf16_input == nullptr || device_amax_bits == nullptr || fp8_output == nullptr ||
+      device_scale == nullptr || elements == 0 || elements % 8 != 0) {
+    set_last_error("invalid FP8 quantization shape");
+    return -1;
+  }
+  QuantTarget target{};
+  target.fp8_output = fp8_output;
+  target.scale = device_scale;
+  target.amax_bits = const_cast<unsigned int *>(device_amax_bits);
+  return finish(launch_quantize_rows(bf16_input, target, elements,
+                                     static_cast<cudaStream_t>(stream)),
+                "FP8 quantization");
+}
+
 extern "C" int carat_b200_quantize_bf16_tensor_to_fp8(const void *bf16_input, void *fp8_output,
                                                       float *device_scale, void *device_scratch,
                                                       size_t elements, void *stream) {

@@ -16,6 +16,7 @@
 #include "launch.cuh"
 #include "linear_items.cuh"
 #include "ptx.cuh"
+#include "row_ops.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -84,6 +85,51 @@ __device__ __forceinline__ void finish_chunk(const KernelArguments &args, const 
   }
 }
 
+// Gated epilogue for 32 accumulator columns (activation rows chunk*32 ..). Thread t of the 128
+// epilogue threads holds gate feature t (t < 64) or up feature t - 64 of the tile; the pair
+// (t, t ^ 64) belongs to one activated column. Both round their sums to bf16 like the plain
+// epilogue, hand each other half of the rows through shared memory, and each finishes sixteen
+// rows: bf16(gelu(gate) * up), the arithmetic of the stand-alone GeGLU kernel.
+__device__ __forceinline__ void gated_chunk(const KernelArguments &args, const float (&values)[32],
+                                            int chunk, int tile, int quarter, int lane, float scale,
+                                            __nv_bfloat16 *exchange, float &amax) {
+  const bool gate_side = quarter < 2;
+  const int thread = quarter * 32 + lane;
+  // The gate side finishes rows 0..15 of the chunk and hands over its rows 16..31; the up side
+  // the other way round. Static indices throughout, so everything stays in registers.
+  __nv_bfloat16 kept[16];
+  __align__(16) __nv_bfloat16 given[16];
+#pragma unroll
+  for (int column = 0; column < 16; ++column) {
+    const __nv_bfloat16 low = __float2bfloat16_rn(values[column] * scale);
+    const __nv_bfloat16 high = __float2bfloat16_rn(values[16 + column] * scale);
+    kept[column] = gate_side ? low : high;
+    given[column] = gate_side ? high : low;
+  }
+  uint4 *mine = reinterpret_cast<uint4 *>(exchange + thread * 16);
+  mine[0] = *reinterpret_cast<const uint4 *>(&given[0]);
+  mine[1] = *reinterpret_cast<const uint4 *>(&given[8]);
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  __align__(16) __nv_bfloat16 other[16];
+  const uint4 *theirs = reinterpret_cast<const uint4 *>(exchange + (thread ^ 64) * 16);
+  *reinterpret_cast<uint4 *>(&other[0]) = theirs[0];
+  *reinterpret_cast<uint4 *>(&other[8]) = theirs[1];
+  __nv_bfloat16 *destination =
+      args.output + static_cast<size_t>(tile) * 64 + (quarter & 1) * 32 + lane;
+  const int first_row = chunk * 32 + (gate_side ? 0 : 16);
+#pragma unroll
+  for (int column = 0; column < 16; ++column) {
+    const float gate = __bfloat162float(gate_side ? kept[column] : other[column]);
+    const float up = __bfloat162float(gate_side ? other[column] : kept[column]);
+    const __nv_bfloat16 activated = __float2bfloat16_rn(gelu_tanh(gate) * up);
+    const int row = first_row + column;
+    if (row < args.rows) {
+      destination[static_cast<size_t>(row) * args.gated_width] = activated;
+      amax = fmaxf(amax, fabsf(__bfloat162float(activated)));
+    }
+  }
+}
+
 // `wide` = bf16 operands (kind::f16, 64 K elements per 128-byte block) instead of e4m3
 // (kind::f8f6f4, 128 per block). Everything else is shared: both consume one 128-byte swizzle atom
 // per row and block in four MMAs of 32 bytes of K.
@@ -102,7 +148,9 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
   __shared__ __align__(8) unsigned long long barriers[2 * stages + 4];
   __shared__ uint32_t tmem_base_slot;
   __shared__ unsigned long long row_best[mode == 2 ? padded_rows : 1];
-  __shared__ int epilogue_gave_up;   // mode 2: set by an epilogue warp whose wait ran out
+  __shared__ int epilogue_gave_up;   // modes 2, 3: set by an epilogue warp whose wait ran out
+  __shared__ int tail_is_last;       // mode 3: this CTA finished the last K piece of a tail tile
+  __shared__ __align__(16) __nv_bfloat16 exchange[mode == 3 ? 2 * 128 * 16 : 8];
 
   const uint32_t tiles_base = (ptx::smem_u32(shared_raw) + 1023U) & ~1023U;
   const uint32_t weight_tiles = tiles_base;
@@ -159,21 +207,32 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
       bool healthy = true;
       // The weights are static: the first ring of weight tiles is requested before the grid this
       // launch depends on has finished. The activation tiles of those stages follow once it has.
+      // Plain tiles are one [128 x 128 B] box; a gated tile is two [64 x 128 B] boxes, its gate
+      // rows and the up rows gated_width further down, stacked in the same stage.
+      const auto load_weights = [&](uint32_t destination, int k_byte, int tile, uint32_t bar) {
+        if constexpr (mode == 3) {
+          ptx::tma_load_2d(destination, &weight_map, k_byte, tile * (tile_features / 2), bar,
+                           stream_policy);
+          ptx::tma_load_2d(destination + weight_tile_bytes / 2, &weight_map, k_byte,
+                           args.gated_width + tile * (tile_features / 2), bar, stream_policy);
+        } else {
+          ptx::tma_load_2d(destination, &weight_map, k_byte, tile * tile_features, bar,
+                           stream_policy);
+        }
+      };
       int early = 0;
       if (first_item < items) {
         const WorkItem item = decode_item(args, first_item);
         early = min(item.k_count, stages);
         for (int block = 0; block < early; ++block) {
           ptx::mbarrier_arrive_expect_tx(full_bar + 8U * block, stage_bytes);
-          ptx::tma_load_2d(weight_tiles + block * weight_tile_bytes, &weight_map,
-                           (item.k_begin + block) * tile_k_bytes, item.tile * tile_features,
-                           full_bar + 8U * block, stream_policy);
+          load_weights(weight_tiles + block * weight_tile_bytes,
+                       (item.k_begin + block) * tile_k_bytes, item.tile, full_bar + 8U * block);
         }
       }
       grid_dependency_wait();
       for (int index = first_item; index < items && healthy; index += item_stride) {
         const WorkItem item = decode_item(args, index);
-        const int feature0 = item.tile * tile_features;
         int k_byte = item.k_begin * tile_k_bytes;
         for (int block = 0; block < item.k_count; ++block, k_byte += tile_k_bytes) {
           const uint32_t full = full_bar + 8U * stage;
@@ -186,8 +245,7 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
               break;
             }
             ptx::mbarrier_arrive_expect_tx(full, stage_bytes);
-            ptx::tma_load_2d(weight_tiles + stage * weight_tile_bytes, &weight_map, k_byte,
-                             feature0, full, stream_policy);
+            load_weights(weight_tiles + stage * weight_tile_bytes, k_byte, item.tile, full);
           }
           ptx::tma_load_2d(input_tiles + stage * input_tile_bytes, &input_map, k_byte, 0, full,
                            reuse_policy);
@@ -279,6 +337,8 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
     if constexpr (mode != 1 && !wide)
       scale = args.input_scale[0] * args.weight_scale[0];
     int local = 0;
+    [[maybe_unused]] int exchange_parity = 0;
+    [[maybe_unused]] float gated_amax = 0.0F;
     for (int index = first_item; index < items; index += item_stride, ++local) {
       const WorkItem item = decode_item(args, index);
       const int buffer = local & 1;
@@ -290,7 +350,7 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
         atomicExch(args.device_error, 3);
         epilogue_gave_up = 1;
       }
-      if constexpr (mode == 2) {
+      if constexpr (mode == 2 || mode == 3) {
         // The four epilogue warps meet at a named barrier further down, so they must leave the
         // loop together: each one's wait is bounded, all reach this barrier, and all read the
         // same flag after it.
@@ -306,6 +366,53 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
       const int feature_base = item.tile * tile_features + quarter * 32;
       const uint32_t lane_address =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buffer * padded_rows;
+      if constexpr (mode == 3) {
+        const int tail_width = args.tail_tiles * tile_features;
+        const int tail_tile = item.tile - (args.tiles - args.tail_tiles);
+        const int tail_feature = tail_tile * tile_features + quarter * 32 + lane;
+        if (item.tail) {    // uniform over the four warps
+          // Park this piece's sums; every CTA takes a share of finishing them after the loop.
+          float *destination = args.tail_partial +
+                               static_cast<size_t>(item.piece) * args.rows * tail_width +
+                               tail_feature;
+#pragma unroll 1
+          for (int chunk = 0; chunk < padded_rows / 32; ++chunk) {
+            if (chunk * 32 < args.rows) {
+              uint32_t raw[32];
+              ptx::tmem_load_32x32b_x32(lane_address + chunk * 32, raw);
+              ptx::tmem_load_wait();
+#pragma unroll
+              for (int column = 0; column < 32; ++column) {
+                const int row = chunk * 32 + column;
+                if (row < args.rows)
+                  destination[static_cast<size_t>(row) * tail_width] = __uint_as_float(raw[column]);
+              }
+            }
+          }
+        } else {
+#pragma unroll 1
+          for (int chunk = 0; chunk < padded_rows / 32; ++chunk) {
+            if (chunk * 32 < args.rows) {
+              uint32_t raw[32];
+              ptx::tmem_load_32x32b_x32(lane_address + chunk * 32, raw);
+              ptx::tmem_load_wait();
+              float values[32];
+#pragma unroll
+              for (int column = 0; column < 32; ++column)
+                values[column] = __uint_as_float(raw[column]);
+              gated_chunk(args, values, chunk, item.tile, quarter, lane, scale,
+                          exchange + exchange_parity * (128 * 16), gated_amax);
+              exchange_parity ^= 1;
+            }
+          }
+        }
+        {
+          ptx::tcgen05_fence_before_thread_sync();
+          __syncwarp();
+          if (lane == 0)
+            ptx::mbarrier_arrive(acc_empty_bar + 8U * buffer);
+        }
+      } else {
 #pragma unroll
       for (int chunk = 0; chunk < padded_rows / 32; ++chunk) {
         if (chunk * 32 < args.rows) {  // warp-uniform
@@ -360,6 +467,7 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
       __syncwarp();
       if (lane == 0)
         ptx::mbarrier_arrive(acc_empty_bar + 8U * buffer);
+      }
 
       if constexpr (mode == 2) {
         {
@@ -374,6 +482,147 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
           asm volatile("bar.sync 1, 128;" ::: "memory");
         }
       }
+    }
+    if constexpr (mode == 3) {
+      // Grid-wide phases after the item loop. Every CTA of the launch is resident (cooperative
+      // launch, one CTA per SM) and comes here, so a counter barrier is safe; its wait is bounded
+      // like every other wait of the kernel.
+      const unsigned int grid = gridDim.x;
+      const bool has_tail = args.tail_tiles > 0;
+      const bool quantises = args.fp8_output != nullptr;
+      const unsigned int barriers = (has_tail ? 1U : 0U) + (quantises ? 1U : 0U);
+      unsigned int passed = 0;
+      bool alive = *reinterpret_cast<volatile int *>(&epilogue_gave_up) == 0;
+      const auto grid_barrier = [&]() -> bool {
+        ++passed;
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (epilogue_thread == 0) {
+          // (barriers + 1) * grid increments a launch, the last of which wraps the word to zero.
+          atomicInc(args.grid_counter, (barriers + 1U) * grid - 1U);
+          const long long start = clock64();
+          bool arrived = true;
+          while (*reinterpret_cast<volatile unsigned int *>(args.grid_counter) < passed * grid) {
+            if (clock64() - start > ptx::wait_cycle_limit) {
+              arrived = false;
+              atomicExch(args.device_error, 6);
+              break;
+            }
+          }
+          __threadfence();
+          tail_is_last = arrived ? 1 : 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        return *reinterpret_cast<volatile int *>(&tail_is_last) != 0;
+      };
+      if (has_tail && alive) {
+        alive = grid_barrier();
+        if (alive) {
+          // (tail tile, 32-row chunk) units dealt round the grid: sum the K pieces in piece
+          // order and finish like a whole tile.
+          const int tail_width = args.tail_tiles * tile_features;
+          const int chunks = (args.rows + 31) / 32;
+          const int units = args.tail_tiles * chunks;
+          for (int unit = static_cast<int>(blockIdx.x); unit < units; unit += static_cast<int>(grid)) {
+            const int tail_tile = unit / chunks;
+            const int chunk = unit - tail_tile * chunks;
+            const int tail_feature = tail_tile * tile_features + quarter * 32 + lane;
+            float values[32];
+#pragma unroll
+            for (int column = 0; column < 32; ++column)
+              values[column] = 0.0F;
+            // Rows past the end read the last row again (and are dropped at the store), so the
+            // 32 loads of a piece are unconditional and all in flight together.
+            // Three pieces' loads are issued before the first add (one L2 round trip for all of
+            // them); the adds stay in piece order.
+            for (int first_piece = 0; first_piece < args.tail_splits; first_piece += 3) {
+              float fetched[3][32];
+#pragma unroll
+              for (int offset = 0; offset < 3; ++offset) {
+                if (first_piece + offset < args.tail_splits) {    // uniform
+                  const float *source =
+                      args.tail_partial +
+                      static_cast<size_t>(first_piece + offset) * args.rows * tail_width +
+                      tail_feature;
+#pragma unroll
+                  for (int column = 0; column < 32; ++column) {
+                    const int row = min(chunk * 32 + column, args.rows - 1);
+                    fetched[offset][column] =
+                        __ldcg(source + static_cast<size_t>(row) * tail_width);
+                  }
+                }
+              }
+#pragma unroll
+              for (int offset = 0; offset < 3; ++offset) {
+                if (first_piece + offset < args.tail_splits) {
+#pragma unroll
+                  for (int column = 0; column < 32; ++column)
+                    values[column] += fetched[offset][column];
+                }
+              }
+            }
+            gated_chunk(args, values, chunk, args.tiles - args.tail_tiles + tail_tile, quarter,
+                        lane, scale, exchange + exchange_parity * (128 * 16), gated_amax);
+            exchange_parity ^= 1;
+          }
+        }
+      }
+      // One atomic per warp and launch: the largest magnitude this warp wrote.
+#pragma unroll
+      for (int offset = 16; offset > 0; offset >>= 1)
+        gated_amax = fmaxf(gated_amax, __shfl_xor_sync(0xFFFFFFFFU, gated_amax, offset));
+      if (lane == 0 && gated_amax > 0.0F)
+        atomicMax(args.amax_bits, __float_as_uint(gated_amax));
+      if (quantises && alive) {
+        alive = grid_barrier();
+        if (alive) {
+          const float tensor_amax =
+              __uint_as_float(*reinterpret_cast<volatile unsigned int *>(args.amax_bits));
+          const float quant_scale = tensor_amax > 0.0F ? tensor_amax / 448.0F : 1.0F;
+          const float inverse_scale = 1.0F / quant_scale;
+          if (blockIdx.x == 0 && epilogue_thread == 0)
+            *args.scale_out = quant_scale;
+          const size_t groups = static_cast<size_t>(args.rows) * args.gated_width / 8;
+          const size_t share = (groups + grid - 1) / grid;
+          const size_t first = share * blockIdx.x;
+          const size_t last = first + share < groups ? first + share : groups;
+          // Eight 16-byte loads in flight per thread: the rows come from L2, and a loop of
+          // dependent load-convert-store steps would pay its latency once per step.
+          const uint4 *source = reinterpret_cast<const uint4 *>(args.output);
+          uint2 *destination = reinterpret_cast<uint2 *>(args.fp8_output);
+          for (size_t base = first; base < last; base += 8 * 128) {
+            uint4 raw[8];
+#pragma unroll
+            for (int step = 0; step < 8; ++step) {
+              const size_t group = base + step * 128 + epilogue_thread;
+              raw[step] = make_uint4(0, 0, 0, 0);
+              if (group < last)
+                raw[step] = __ldcg(source + group);
+            }
+#pragma unroll
+            for (int step = 0; step < 8; ++step) {
+              const size_t group = base + step * 128 + epilogue_thread;
+              if (group < last) {
+                const __nv_bfloat162 *pairs = reinterpret_cast<const __nv_bfloat162 *>(&raw[step]);
+                const float2 a = __bfloat1622float2(pairs[0]);
+                const float2 b = __bfloat1622float2(pairs[1]);
+                const float2 c = __bfloat1622float2(pairs[2]);
+                const float2 d = __bfloat1622float2(pairs[3]);
+                __nv_fp8x4_e4m3 low(make_float4(a.x * inverse_scale, a.y * inverse_scale,
+                                                b.x * inverse_scale, b.y * inverse_scale));
+                __nv_fp8x4_e4m3 high(make_float4(c.x * inverse_scale, c.y * inverse_scale,
+                                                 d.x * inverse_scale, d.y * inverse_scale));
+                uint2 packed;
+                packed.x = low.__x;
+                packed.y = high.__x;
+                destination[group] = packed;
+              }
+            }
+          }
+        }
+      }
+      if (barriers > 0 && epilogue_thread == 0 && passed == barriers)
+        atomicInc(args.grid_counter, (barriers + 1U) * grid - 1U);   // the round that wraps to zero
     }
   }
 
@@ -475,7 +724,7 @@ int launch_variant(const LinearPlan &plan, const KernelArguments &arguments, cud
   const int ctas = items < plan.ctas ? items : plan.ctas;
   return launch_chained(fp8_linear_kernel<padded_rows, mode, wide>,
                         dim3(static_cast<unsigned>(ctas)),
-                        dim3(linear_threads), dynamic_bytes, stream, false, plan.weight_map,
+                        dim3(linear_threads), dynamic_bytes, stream, mode == 3, plan.weight_map,
                         plan.input_map, arguments) == cudaSuccess
              ? 0
              : -11;
@@ -522,6 +771,11 @@ KernelArguments base_arguments(const LinearPlan &plan, int *device_error, bool s
 
 } // namespace
 
+void schedule_linear_shape(LinearPlan *plan, int rows, int input_width, int output_width,
+                           int requested_splits, int element_bytes) {
+  schedule_linear(plan, rows, input_width, output_width, requested_splits, element_bytes);
+}
+
 std::size_t linear_partial_bytes_for(int rows, int input_width, int output_width,
                                      int element_bytes) {
   if (rows <= 0 || rows > 256 || input_width <= 0 || output_width <= 0)
@@ -566,6 +820,57 @@ int make_linear_plan(LinearPlan *plan, const void *fp8_input, const void *fp8_we
   return 0;
 }
 
+int make_gated_linear_plan(LinearPlan *plan, const void *fp8_input, const void *fp8_weight,
+                           int rows, int input_width, int gated_width, const char **error,
+                           int element_bytes) {
+  if (gated_width <= 0 || gated_width % (tile_features / 2) != 0) {
+    if (error != nullptr)
+      *error = "gated linear width must be a multiple of 64";
+    return -7;
+  }
+  LinearPlan result{};
+  const int status = make_linear_plan(&result, fp8_input, fp8_weight, rows, input_width,
+                                      2 * gated_width, 1, error, element_bytes);
+  if (status != 0)
+    return status;
+  const uint64_t row_bytes = static_cast<uint64_t>(input_width) * element_bytes;
+  if (!encode_byte_matrix(&result.weight_map, fp8_weight, row_bytes,
+                          static_cast<uint64_t>(2) * gated_width, tile_features / 2)) {
+    if (error != nullptr)
+      *error = "cuTensorMapEncodeTiled failed";
+    return -5;
+  }
+  result.gated_width = gated_width;
+  *plan = result;
+  return 0;
+}
+
+int launch_linear_gated(const LinearPlan &plan, const float *input_scale,
+                        const float *weight_scale, void *bf16_activated, unsigned int *amax_bits,
+                        void *fp8_output, float *scale_out, float *tail_partial,
+                        unsigned int *grid_counter, int *device_error, cudaStream_t stream) {
+  if (plan.gated_width <= 0 || bf16_activated == nullptr || amax_bits == nullptr ||
+      grid_counter == nullptr || (fp8_output != nullptr && scale_out == nullptr)) {
+    return -13;
+  }
+  KernelArguments arguments = base_arguments(plan, device_error, false);
+  arguments.input_scale = input_scale;
+  arguments.weight_scale = weight_scale;
+  arguments.output = static_cast<__nv_bfloat16 *>(bf16_activated);
+  arguments.amax_bits = amax_bits;
+  arguments.grid_counter = grid_counter;
+  arguments.fp8_output = static_cast<unsigned char *>(fp8_output);
+  arguments.scale_out = scale_out;
+  arguments.gated_width = plan.gated_width;
+  if (plan.tail_tiles > 0 && tail_partial != nullptr) {
+    arguments.tail_partial = tail_partial;
+    arguments.tail_tiles = plan.tail_tiles;
+    arguments.tail_splits = plan.tail_splits;
+    arguments.tail_k_blocks_per_split = plan.tail_k_blocks_per_split;
+  }
+  return launch_mode<3>(plan, arguments, stream);
+}
+
 std::size_t linear_partial_bytes(const LinearPlan &plan) {
   if (plan.splits <= 1)
     return linear_tail_bytes(plan);
@@ -574,6 +879,8 @@ std::size_t linear_partial_bytes(const LinearPlan &plan) {
 
 int launch_linear_bf16(const LinearPlan &plan, const float *input_scale, const float *weight_scale,
                        void *bf16_output, float *partial, int *device_error, cudaStream_t stream) {
+  if (plan.gated_width != 0)
+    return -13;   // a gated plan's weight map has 64-row boxes
   if (plan.splits == 1 && plan.tail_tiles > 0 && partial != nullptr) {
     const int status = launch_linear_bf16_tail(plan, input_scale, weight_scale, bf16_output,
                                                partial, device_error, stream);

@@ -35,6 +35,10 @@ struct LinearPlan {
   int tail_splits{1};
   int tail_k_blocks_per_split{0};
   int element_bytes{1};     // 1: e4m3 operands; 2: bf16 operands (scales are then ignored)
+  // Gated plan (make_gated_linear_plan): the weight is [gate rows | up rows], output_width is
+  // 2 * gated_width, a tile pairs 64 gate features with their 64 up features and weight_map's
+  // box is 64 rows. Only launch_linear_gated takes such a plan.
+  int gated_width{0};
 };
 
 // Returns 0 or a negative error; `error` (may be null) receives a static message.
@@ -45,9 +49,35 @@ int make_linear_plan(LinearPlan *plan, const void *fp8_input, const void *fp8_we
                      int input_width, int output_width, int requested_splits, const char **error,
                      int element_bytes = 1);
 
+// The gate_up linear with GeGLU in its epilogue. `fp8_weight` is [2 * gated_width, input_width]
+// with the gate rows first; gated_width must be a multiple of 64.
+int make_gated_linear_plan(LinearPlan *plan, const void *fp8_input, const void *fp8_weight,
+                           int rows, int input_width, int gated_width, const char **error,
+                           int element_bytes = 1);
+
+// activated[row, j] = bf16(gelu_tanh(g) * u) with g = bf16(acc_gate[row, j] * x_scale * w_scale)
+// and u likewise from the up rows: the values launch_linear_bf16 followed by the GeGLU kernel
+// produce (cuda/ops.cu:228-284), without the [rows, 2 * gated_width] round trip. The largest
+// |activated| is folded into *amax_bits with atomicMax (float bits; the caller zeroes it).
+// With `fp8_output` set the launch also does the activation quantisation that follows in the
+// reference (cuda/layer_runner.cu:331-347): *scale_out = max / 448 (1 when 0) and
+// fp8_output[rows, gated_width] = e4m3(activated / scale).
+// `tail_partial` (linear_tail_bytes(plan) bytes; may be null, the plan's K-cut tail is then not
+// used) holds the pieces of the tail tiles between the kernel's phases. `grid_counter` is one word
+// that is zero on entry and zero again on return; the kernel's grid-wide barriers count on it,
+// which is why the launch is cooperative (every CTA resident: one per SM).
+int launch_linear_gated(const LinearPlan &plan, const float *input_scale,
+                        const float *weight_scale, void *bf16_activated, unsigned int *amax_bits,
+                        void *fp8_output, float *scale_out, float *tail_partial,
+                        unsigned int *grid_counter, int *device_error, cudaStream_t stream);
+
 // Bytes of fp32 scratch a plan needs when it splits K (0 when splits == 1):
 // [splits, rows, output_width].
 std::size_t linear_partial_bytes(const LinearPlan &plan);
+
+// The schedule alone (tiles, K pieces, tail) for a shape: no tensor maps, usable without a device.
+void schedule_linear_shape(LinearPlan *plan, int rows, int input_width, int output_width,
+                           int requested_splits, int element_bytes = 1);
 
 // The same figure from the shape alone (no tensor maps, usable without a device).
 std::size_t linear_partial_bytes_for(int rows, int input_width, int output_width,

@@ -34,6 +34,17 @@ struct KernelArguments {
   int tail_tiles;
   int tail_splits;
   int tail_k_blocks_per_split;
+  // Mode 3 (gated): a tile is 64 gate features and the 64 up features that go with them; the
+  // epilogue writes bf16(gelu(gate) * up) [rows, gated_width] to `output` and folds the largest
+  // magnitude into `amax_bits`. K-cut tail tiles leave their pieces in tail_partial; after a
+  // grid-wide barrier (grid_counter, zero between launches) all CTAs share the work of summing
+  // and finishing them. With fp8_output set, a second barrier makes the maximum final and the
+  // CTAs quantise the rows: scale = max / 448 to scale_out, e4m3 rows to fp8_output.
+  unsigned int *amax_bits;
+  unsigned int *grid_counter;
+  unsigned char *fp8_output;
+  float *scale_out;
+  int gated_width;
 };
 
 struct WorkItem {

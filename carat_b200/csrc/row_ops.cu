@@ -146,11 +146,6 @@ __device__ __forceinline__ Pack8 round_bf16x8(const Pack8 &values, uint4 *packed
   return rounded;
 }
 
-__device__ __forceinline__ float gelu_tanh(float value) {
-  constexpr float coefficient = 0.7978845608028654F;
-  return 0.5F * value * (1.0F + tanhf(coefficient * (value + 0.044715F * value * value * value)));
-}
-
 // Loads eight values of the row's primary source: a bf16 tensor, or split-K / key-chunk partials
 // summed in a fixed order, scaled and rounded to bf16 exactly like a separate finishing kernel.
 __device__ __forceinline__ Pack8 load_source(const RowArguments &a, size_t row, int column,
@@ -681,6 +676,21 @@ int launch_quant_tensor(const void *input, void *fp8_output, float *scale,
       static_cast<const __nv_bfloat16 *>(input), static_cast<__nv_fp8_e4m3 *>(fp8_output), scale,
       elements);
   return cudaPeekAtLastError() == cudaSuccess ? 0 : -11;
+}
+
+int launch_quantize_rows(const void *bf16_rows, QuantTarget target, size_t elements,
+                         cudaStream_t stream) {
+  if (bf16_rows == nullptr || target.fp8_output == nullptr || target.scale == nullptr ||
+      target.amax_bits == nullptr || elements == 0 || elements % 8 != 0) {
+    return -1;
+  }
+  const unsigned blocks = static_cast<unsigned>((elements / 8 + 255) / 256);
+  return launch_chained(quantize_rows_kernel, dim3(blocks), dim3(256), 0, stream, false,
+                        static_cast<const __nv_bfloat16 *>(bf16_rows),
+                        static_cast<const unsigned int *>(target.amax_bits), target.scale,
+                        static_cast<unsigned char *>(target.fp8_output), elements) == cudaSuccess
+             ? 0
+             : -11;
 }
 
 int launch_embed_norm_quant(const void *embedding, const int *tokens, int vocabulary,

@@ -109,4 +109,19 @@ int launch_layer_output_norm_quant(const void *down, PartialSource source, const
                                    QuantTarget target, int rows, int width, float epsilon,
                                    cudaStream_t stream);
 
+// e4m3 rows from bf16 rows whose tensor-wide maximum is already in target.amax_bits (left there by
+// the producer of the rows, e.g. the gated linear epilogue): scale = max / 448 to target.scale,
+// e4m3(x / scale) to target.fp8_output. No grid barrier; `elements` a multiple of eight.
+int launch_quantize_rows(const void *bf16_rows, QuantTarget target, size_t elements,
+                         cudaStream_t stream);
+
+#ifdef __CUDACC__
+// tanh-form GELU of the reference's GeGLU (cuda/ops.cu:228-284), shared by the stand-alone GeGLU
+// kernel and the gated linear epilogue so that both round identically.
+__device__ __forceinline__ float gelu_tanh(float value) {
+  constexpr float coefficient = 0.7978845608028654F;
+  return 0.5F * value * (1.0F + tanhf(coefficient * (value + 0.044715F * value * value * value)));
+}
+#endif
+
 } // namespace carat_b200

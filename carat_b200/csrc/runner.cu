@@ -16,6 +16,7 @@
 #include "row_ops.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <memory>
@@ -117,6 +118,7 @@ struct RopeTable {
 
 struct LayerPlans {
   LinearPlan qkv, o, gate_up, down;
+  LinearPlan gate_up_gated;   // gate_up with GeGLU in its epilogue (Runner::fused_geglu)
   Int4LinearPlan gate_up_int4, down_int4;   // used instead when the INT4 MLP variant is on
 };
 
@@ -191,6 +193,9 @@ struct carat_b200_runner {
   int int4_group{0};
   DeviceBuffer pre_mlp;      // bf16 [rows, hidden]: input of the INT4 gate_up linear
   DeviceBuffer activated;    // bf16 [rows, intermediate]: input of the INT4 down linear
+  DeviceBuffer gated_rows;   // bf16 [rows, intermediate]: GeGLU rows out of the gated gate_up linear
+  DeviceBuffer grid_counter;   // barrier word of the gated linear; zero between launches
+  bool fused_geglu{false};
   DeviceBuffer unit_scale;   // one fp32 1.0: INT4 partial sums carry no tensor scales
   std::map<std::pair<int, int>, AttentionMaps> verify_maps;  // (layer, depth)
   std::map<int, AttentionMaps> draft_maps;                   // assistant layer
@@ -370,6 +375,15 @@ void build_runner(Runner &runner, const carat_b200_model_config &config,
                                   sizeof(float2));
   runner.projected.allocate(row_hidden);
   runner.gate_up.allocate(static_cast<size_t>(rows) * 2 * config.intermediate_size * 2);
+  // CARAT_B200_FUSED_GEGLU=1 runs gate_up, GeGLU and the activation quantisation as one launch
+  // (launch_linear_gated) instead of linear -> GeGLU kernel. Off by default: measured on the 31B
+  // shapes it is no faster, because the separate GeGLU kernel finishes the linear's K-cut tail
+  // tiles across the whole device for free, while the one-launch form pays two grid-wide
+  // barriers for the same work.
+  const char *fused = std::getenv("CARAT_B200_FUSED_GEGLU");
+  runner.fused_geglu = config.intermediate_size % 64 == 0 && fused != nullptr && fused[0] == '1';
+  runner.gated_rows.allocate(static_cast<size_t>(rows) * config.intermediate_size * 2);
+  runner.grid_counter.allocate(256, true);
   // Split-K partials [splits, rows, features] fp32; plans that would need more are rejected.
   runner.split_partials.allocate(static_cast<size_t>(16) * rows * std::max(hidden, 4096) * 4);
   runner.amax_words = (config.layer_count + 1) * 4;
@@ -462,6 +476,16 @@ StepPlans &verify_plans_for(Runner &runner, int rows) {
                              hidden, 0);
     for (const LinearPlan *plan : {&entry.qkv, &entry.o, &entry.gate_up, &entry.down}) {
       if (linear_partial_bytes(*plan) > runner.split_partials.bytes())
+        throw Failure{"split-K workspace is too small for this model shape"};
+    }
+    if (runner.fused_geglu) {
+      const char *message = "invalid FP8 linear shape";
+      if (make_gated_linear_plan(&entry.gate_up_gated, runner.quantized.get(),
+                                 layer.weights.gate_up, rows, hidden, intermediate,
+                                 &message) != 0) {
+        throw Failure{message};
+      }
+      if (linear_tail_bytes(entry.gate_up_gated) > runner.split_partials.bytes())
         throw Failure{"split-K workspace is too small for this model shape"};
     }
     if (!runner.int4_layers.empty()) {
@@ -925,6 +949,19 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
       continue;
     }
 
+    if (runner.fused_geglu) {
+      // GeGLU, the activation maximum and the e4m3 rows of the down projection all come out of
+      // the gate_up launch.
+      const QuantTarget quantised = target(word + 3);
+      require_launch(launch_linear_gated(plan.gate_up_gated, scales + word + 2, w.gate_up_scale,
+                                         runner.gated_rows.get(), quantised.amax_bits,
+                                         quantised.fp8_output, quantised.scale,
+                                         runner.split_partials.get<float>(),
+                                         runner.grid_counter.get<unsigned int>(),
+                                         runner.device_error, stream),
+                     "FP8 gated linear");
+      runner.launches += 1;
+    } else {
     // 336 feature tiles on 148 SMs leave a short last round; its tiles are cut along K and the
     // GeGLU kernel, which reads the up half anyway, sums the pieces.
     TailSource tail{};
@@ -948,6 +985,7 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
                                       config.intermediate_size, stream),
                    "GeGLU");
     runner.launches += 1;
+    }
 
     const PartialSource down_source = run_linear(runner, plan.down, scales + word + 3,
                                                  w.down_scale, runner.projected.get(), true);

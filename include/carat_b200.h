@@ -90,6 +90,28 @@ CARAT_B200_API int carat_b200_fp8_linear_static(const void *fp8_input,
                                                 void *bf16_output, int rows, int input_width,
                                                 int output_width, void *stream);
 
+/* The gate_up projection with the reference's GeGLU (gelu_tanh_gate_bf16, cuda/ops.cu:228-284;
+ * called between the two MLP linears in cuda/layer_runner.cu:318-347) in the linear's epilogue:
+ * fp8_weight is [2 * gated_width, input_width] e4m3, gate rows first, and
+ *   bf16_activated[row, j] = bf16(gelu_tanh(g) * u),  g = bf16(x_scale * w_scale * acc_gate[row, j]),
+ * u likewise from row gated_width + j: what carat_b200_fp8_linear followed by the GeGLU row
+ * operation gives. *device_amax_bits receives the float bits of the largest |activated|. When
+ * fp8_output is not NULL the same launch also quantises the rows for the down projection:
+ * *device_output_scale = max / 448 (1 when 0), fp8_output[rows, gated_width] = e4m3(x / scale).
+ * gated_width must be a multiple of 64. One cooperative launch (its phases meet at grid-wide
+ * barriers with bounded waits). workspace: carat_b200_fp8_linear_geglu_workspace_bytes() bytes. */
+CARAT_B200_API size_t carat_b200_fp8_linear_geglu_workspace_bytes(int rows, int input_width,
+                                                                  int gated_width);
+CARAT_B200_API int carat_b200_fp8_linear_geglu(const void *fp8_input,
+                                               const float *device_input_scale,
+                                               const void *fp8_weight,
+                                               const float *device_weight_scale,
+                                               void *bf16_activated,
+                                               unsigned int *device_amax_bits, void *fp8_output,
+                                               float *device_output_scale, int rows,
+                                               int input_width, int gated_width, void *workspace,
+                                               size_t workspace_bytes, void *stream);
+
 /* Fused LM head: device_tokens[row] = argmax_n bf16(scale * input[row] . weight[n]), ties to the
  * lowest n, without writing the logits. `device_keys` is rows * 8 bytes of scratch.
  * Replaces run_decode_lm_head + argmax_bf16_rows (cuda/batch_model_runner.cu:840-853,
@@ -181,6 +203,15 @@ CARAT_B200_API int carat_b200_int4_linear_check(const void *bf16_input, const vo
 /* Plain quantisation. */
 CARAT_B200_API int carat_b200_quantize_bf16_to_fp8(const void *bf16_input, void *fp8_output, float *device_scale,
                                     void *device_scratch, int rows, int width, void *stream);
+
+/* The maximum is already known (float bits in *device_amax_bits, e.g. from
+ * carat_b200_fp8_linear_geglu): scale = max / 448 (1 when 0), e4m3(x / scale). One ordinary launch,
+ * no grid barrier; the _from_row_amax form of the reference (include/carat/linear.h:97-99) with
+ * the row maxima already reduced. `elements` a multiple of eight. */
+CARAT_B200_API int carat_b200_quantize_bf16_to_fp8_from_amax(const void *bf16_input,
+                                                             const unsigned int *device_amax_bits,
+                                                             void *fp8_output, float *device_scale,
+                                                             size_t elements, void *stream);
 
 /* Same contract for a tensor of any size (weights at load time): three ordinary launches, the
  * reference's non-cooperative branch (cuda/linear.cu:117-153,261-271; used by

@@ -114,3 +114,69 @@ def test_argmax_ties_take_the_lowest_index(cuda_device):
                                                ptr(tokens), ptr(keys), rows, k, n, None))
     torch.cuda.synchronize()
     assert tokens.cpu().tolist() == [300] * rows
+
+
+GATED_SHAPES = [
+    (120, 5376, 21504, "31B gate_up: 336 tiles, K-cut tail finished by the last piece"),
+    (24, 1024, 64 * 160, "160 tiles, tail round, 32 padded rows"),
+    (5, 256, 192, "three tiles"),
+    (64, 2048, 64 * 300, "300 tiles, 64 padded rows"),
+    (200, 512, 64 * 150, "150 tiles, 256 padded rows"),
+]
+
+
+@pytest.mark.parametrize("rows,k,width,what", GATED_SHAPES)
+def test_gated_linear_equals_linear_then_geglu(cuda_device, rows, k, width, what):
+    """GeGLU in the gate_up linear's epilogue (carat_b200_fp8_linear_geglu) against the two separate
+    operations it replaces, byte for byte: the activated bf16 rows, the tensor maximum, and the
+    e4m3 rows and scale after the quantisation that follows."""
+    library = carat_b200.library()
+    weight, weight_scale = quantised(2 * width, k, 0.05, 11)
+    activation, activation_scale = quantised(rows, k, 1.0, 12)
+    # Separate: linear -> [rows, 2 * width] -> GeGLU + quantise.
+    needed = library.carat_b200_fp8_linear_workspace_bytes(rows, k, 2 * width)
+    workspace = torch.empty(max(needed, 16), dtype=torch.uint8, device="cuda")
+    packed = torch.empty(rows, 2 * width, dtype=torch.bfloat16, device="cuda")
+    check(library.carat_b200_fp8_linear(ptr(activation), ptr(activation_scale), ptr(weight),
+                                        ptr(weight_scale), ptr(packed), rows, k, 2 * width,
+                                        ptr(workspace), needed, None))
+    want_fp8 = torch.empty(rows, width, dtype=torch.uint8, device="cuda")
+    want_scale = torch.zeros(1, device="cuda")
+    scratch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    check(library.carat_b200_gelu_gate_quantize(ptr(packed), ptr(want_fp8), ptr(want_scale),
+                                                ptr(scratch), rows, width, None))
+    # Fused, twice over the same workspace (the barrier word must come back to zero), once with
+    # the quantisation in the same launch and once with it as a separate call.
+    bytes_needed = library.carat_b200_fp8_linear_geglu_workspace_bytes(rows, k, width)
+    gated_workspace = torch.empty(bytes_needed, dtype=torch.uint8, device="cuda")
+    for attempt in range(2):
+        activated = torch.full((rows, width), float("nan"), dtype=torch.bfloat16, device="cuda")
+        amax_bits = torch.full((1,), 12345, dtype=torch.int32, device="cuda")
+        got_fp8 = torch.empty(rows, width, dtype=torch.uint8, device="cuda")
+        got_scale = torch.zeros(1, device="cuda")
+        same_launch = attempt == 0
+        check(library.carat_b200_fp8_linear_geglu(
+            ptr(activation), ptr(activation_scale), ptr(weight), ptr(weight_scale), ptr(activated),
+            ptr(amax_bits), ptr(got_fp8) if same_launch else None,
+            ptr(got_scale) if same_launch else None, rows, k, width, ptr(gated_workspace),
+            bytes_needed, None))
+        if not same_launch:
+            check(library.carat_b200_quantize_bf16_to_fp8_from_amax(
+                ptr(activated), ptr(amax_bits), ptr(got_fp8), ptr(got_scale), rows * width, None))
+        torch.cuda.synchronize()
+        assert not torch.isnan(activated.float()).any(), what
+        assert amax_bits.view(torch.float32).item() == activated.float().abs().max().item(), what
+        # The two paths cut K differently for some features (a tile that is whole here may sit in
+        # the other schedule's K-cut tail), so a sum can land one bf16 ulp away now and then:
+        # nearly every byte equal, the rest one e4m3 step apart.
+        assert torch.equal(got_scale, want_scale), what
+        differing = got_fp8 != want_fp8
+        assert float(differing.float().mean()) < 1e-4, what
+        if bool(differing.any()):
+            a = got_fp8.view(torch.float8_e4m3fn).float()[differing]
+            b = want_fp8.view(torch.float8_e4m3fn).float()[differing]
+            assert float(((a - b).abs() / torch.maximum(a.abs(), b.abs()).clamp_min(2 ** -9)).max()) \
+                <= 0.126, what
+    code = ctypes.c_int(0)
+    check(library.carat_b200_device_error(ctypes.byref(code)))
+    assert code.value == 0
