@@ -424,7 +424,10 @@ def int4_variant(config, runner, timed_run, args, fp8_weight_bytes):
         return {"error": str(error)}
 
 
-NCU_GATE_UP_DRAM_BYTES = 231.912192e6 + 6.525696e6
+# dram__bytes_read.sum + dram__bytes_write.sum of the captured gate_up launch
+# (profiles/fp8_linear_gate_up_120x5376x43008.md, capture of 2026-11-25) and that launch's
+# algorithmic bytes: weights + activations + bf16 output + two scales.
+NCU_GATE_UP_DRAM_BYTES = 231.931904e6 + 6.040832e6
 NCU_GATE_UP_ALGORITHMIC_BYTES = 231211008 + 645120 + 10321920 + 8
 
 
@@ -495,7 +498,9 @@ def linear_roofline(library, config, fp8, peaks):
             # counters stopped); every weight byte is read exactly once whatever the shape, so the
             # figure is scaled to the sweep's mean launch by algorithmic bytes.
             "traffic": total / launches * NCU_GATE_UP_DRAM_BYTES / NCU_GATE_UP_ALGORITHMIC_BYTES,
-            "traffic_source": "ncu capture of the gate_up launch, scaled by algorithmic bytes"}
+            "traffic_source": "profiles/fp8_linear_gate_up_120x5376x43008.md (ncu capture of the "
+                              "gate_up launch, 2026-11-25), scaled to the mean launch by "
+                              "algorithmic bytes"}
 
 
 # --------------------------------------------------------------------------- library baseline
