@@ -178,7 +178,82 @@ def global_ragged(launches=3):
               contexts=bench.context_lengths(seed=3), launches=launches)
 
 
-CASES = {"linear": linear, "gated": gated, "int4": int4, "lm_head": lm_head, "attention": attention, "global": global_attention,
+def prefill(launches=6, slots=24, chunk=8, context=1024):
+    """BF16 prompt prefill on one period of the 31B layer pattern (five sliding layers and one
+    global layer at the real widths, vocabulary 262144): `slots` prompts advance `chunk` tokens a
+    call from `context` resident tokens. Prints the time per call, the same figure for the 60-layer
+    model (ten periods: extrapolated, the LM head is outside the timed calls) and the share of
+    the bf16 weight stream's roofline."""
+    import carat_b200
+    generator = torch.Generator(device="cuda").manual_seed(0)
+
+    def matrix(rows, cols):
+        out = torch.empty(rows, cols, dtype=torch.bfloat16, device="cuda")
+        step = max(1, (64 << 20) // cols)
+        for start in range(0, rows, step):
+            stop = min(rows, start + step)
+            out[start:stop] = (torch.randn(stop - start, cols, device="cuda", generator=generator)
+                               * 0.02).to(torch.bfloat16)
+        return out
+
+    def ones(width):
+        return torch.ones(width, dtype=torch.bfloat16, device="cuda")
+
+    layers = [carat_b200.Gemma4LayerConfig("sliding", 32, 16, 256, 1e4, False) for _ in range(5)]
+    layers.append(carat_b200.Gemma4LayerConfig("global", 32, 4, 512, 1e6, True))
+    config = carat_b200.Gemma4Config(5376, 21504, 262144, 1024, 1e-6, layers)
+    hidden, inter = config.hidden_size, config.intermediate_size
+    bf16 = {"token_embedding": matrix(config.vocabulary_size, hidden), "final_norm": ones(hidden)}
+    weight_bytes = 0
+    for index, layer in enumerate(layers):
+        prefix = f"layer.{index}."
+        for name, width in (("input_norm", hidden), ("q_norm", layer.head_dimension),
+                            ("k_norm", layer.head_dimension), ("post_attention_norm", hidden),
+                            ("pre_mlp_norm", hidden), ("post_mlp_norm", hidden), ("scalar", 1)):
+            bf16[prefix + name] = ones(width)
+        for name, rows, cols in (("qkv", layer.packed_width(), hidden),
+                                 ("o", hidden, layer.query_width()),
+                                 ("gate_up", 2 * inter, hidden), ("down", hidden, inter)):
+            bf16[prefix + name] = matrix(rows, cols)
+            weight_bytes += 2 * rows * cols
+    weights = carat_b200.DeviceWeightArena(bf16)
+    fp8 = carat_b200.Fp8WeightArena.quantize(weights)
+    # A multiple of 128 rows, like the server's 8192: the tensor-core attention needs that.
+    max_context = (context + chunk * (launches + 2) + 64 + 127) // 128 * 128
+    runner = carat_b200.Gemma4BatchModelRunner(config, weights, slots, max_context, fp8)
+    runner.seed_empty_cache_for_benchmark(context)
+    tokens = torch.randint(3, config.vocabulary_size, (slots, max_context),
+                           generator=torch.Generator().manual_seed(1)).tolist()
+    live = list(range(slots))
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    resident = context
+    device_ms = 0.0
+    for launch in range(launches):
+        if launch == 1:
+            start.record()
+        # Every prompt is longer than what becomes resident, so no call ends with the LM head.
+        runner.prefill_slots_chunks(live, [row[:max_context] for row in tokens], chunk)
+        resident += chunk
+        if launch >= 1:
+            device_ms += runner.last_device_ms()[0]
+    stop.record()
+    torch.cuda.synchronize()
+    assert runner.slot_position(0) == resident
+    if launches > 1:
+        wall = start.elapsed_time(stop) / (launches - 1)
+        period = device_ms / (launches - 1)
+        rows = slots * chunk
+        roofline = weight_bytes / 1e9 / (period / 1e3)
+        print(f"bf16 prefill, {slots} slots x {chunk} tokens from context {context}: {period:.2f} ms "
+              f"of device time per call over 6 layers ({weight_bytes / 1e9:.2f} GB of bf16 weights "
+              f"= {roofline:.0f} GB/s; {wall:.2f} ms wall clock through the Python mirror); x10 for "
+              f"60 layers (extrapolated): {10 * period:.1f} ms, "
+              f"{rows / (10 * period / 1e3):.0f} prompt tokens/s")
+    runner.close()
+
+
+CASES = {"prefill": prefill, "linear": linear, "gated": gated, "int4": int4, "lm_head": lm_head, "attention": attention, "global": global_attention,
          "global_ragged": global_ragged}
 
 

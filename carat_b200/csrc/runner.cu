@@ -1090,6 +1090,7 @@ void prefill_step(Runner &runner, const int *tokens, int requests, int depth, co
                                sizeof(int) * (maximum_rows + 4 * runner.batch),
                                cudaMemcpyHostToDevice, stream),
                "copy prefill step inputs");
+  require_cuda(cudaEventRecord(runner.start_event, stream), "record prefill start");
   runner.launches = 0;
   const int hidden = config.hidden_size;
   const float epsilon = config.rms_norm_epsilon;
@@ -1254,7 +1255,11 @@ void prefill_step(Runner &runner, const int *tokens, int requests, int depth, co
   require_cuda(cudaMemcpyAsync(host_results + maximum_rows, runner.device_error, sizeof(int),
                                cudaMemcpyDeviceToHost, stream),
                "copy device error word");
+  require_cuda(cudaEventRecord(runner.stop_event, stream), "record prefill end");
   require_cuda(cudaStreamSynchronize(stream), "synchronize prefill step");
+  require_cuda(cudaEventElapsedTime(&runner.last_verify_ms, runner.start_event, runner.stop_event),
+               "read prefill step time");
+  runner.last_verify_launches = runner.launches;
   if (host_results[maximum_rows] != 0) {
     const int code = host_results[maximum_rows];
     cudaMemsetAsync(runner.device_error, 0, sizeof(int), stream);

@@ -330,3 +330,71 @@ def test_hand_off_is_a_byte_copy_of_the_devices_own_row(pair):
         else:
             source = rows[request * depth + accepted - 1]
             assert torch.equal(table[slot].view(torch.int16), source.view(torch.int16))
+
+
+def test_free_running_generation_on_the_plumbing_case(cuda_device):
+    """The CPU-runnable case end to end: one request, a 64-token prompt, k = 4 drafts a step, 64
+    new tokens with real greedy acceptance, draft -> caps -> verify -> commit in a loop with the
+    reference's host logic. Drafts come from the device's drafter (every third step from a greedy
+    look-ahead instead, so that whole blocks get accepted too). Both sides consume the same
+    proposals; the streams must be identical except where a flagged near-tie decided a row, after
+    which the oracle is re-synchronised to the device's accepted rows and the loop goes on."""
+    from carat_b200.dispatcher import acceptance_cap, commit_speculation
+    config = cs.tiny_config(512)
+    assistant = cs.tiny_assistant()
+    oracle, device, _ = build_pair(config, cs.golden_tiny_weights(config), 1, assistant,
+                                   cs.random_assistant_weights(config, assistant, 1))
+    depth, new_tokens, slot = 5, 64, 0
+    prompt = prompts(config, 1, 64, seed=21)[0]
+    first = None
+    for start in range(0, len(prompt), 8):
+        part = prompt[start:start + 8]
+        first = device.prefill_slot_fp8(slot, part, 8)
+        _, nxt = oracle.verify_greedy_proposals([part], [part[0]], [slot], assume_match=True,
+                                                allow_empty_slot=True)
+        if first != nxt[0]:
+            first = nxt[0]      # a near-tie at the end of prefill: both continue from the oracle's
+    resident = list(prompt)
+    emitted = [first]
+    steps = flagged = resynchronised = accepted_total = draft_rows = draft_same = 0
+    while len(emitted) < new_tokens:
+        last = resident[-1]
+        if steps % 3 == 0:
+            scout = copy.deepcopy(oracle)
+            token, line = first, [first]
+            for _ in range(depth - 1):
+                _, nxt = scout.verify_greedy_proposals([[token]], [token], [slot])
+                token = nxt[0]
+                line.append(token)
+            proposals = line
+        else:
+            proposals = device.draft_four([last], [slot], [first], depth)[0]
+            wanted = oracle.draft([last], [slot], [first], depth)[0]
+            draft_rows += depth - 1
+            draft_same += sum(a == b for a, b in zip(proposals[1:], wanted[1:]))
+        assert proposals[0] == first
+        cap = acceptance_cap(depth, new_tokens - len(emitted), proposals, frozenset())
+        result, trace, step_flags, oracle_result = forced_step(oracle, device, [proposals], [first],
+                                                              [slot], [cap])
+        accepted, next_token = result.accepted_tokens[0], result.next_tokens[0]
+        if step_flags == 0:
+            assert (accepted, next_token) == (oracle_result[0][0], oracle_result[1][0])
+        else:
+            flagged += step_flags
+            resynchronised += (accepted, next_token) != (oracle_result[0][0], oracle_result[1][0])
+        assert 1 <= accepted <= cap
+        kept, shown, first, stopped = commit_speculation(first, proposals[1:accepted], next_token,
+                                                         frozenset())
+        assert not stopped
+        resident += kept
+        emitted += shown
+        accepted_total += accepted
+        steps += 1
+        assert device.slot_position(slot) == oracle.positions[slot] == len(resident)
+    assert len(emitted) == new_tokens
+    print(f"{steps} steps, {accepted_total / steps:.2f} rows accepted a step, {flagged} rows "
+          f"decided by a flagged near-tie, {resynchronised} steps re-synchronised, drafted tokens "
+          f"equal to the oracle's drafter: {draft_same} of {draft_rows}")
+    assert accepted_total > steps           # whole look-ahead blocks were accepted
+    assert flagged <= 12
+    device.close()
