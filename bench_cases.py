@@ -178,22 +178,19 @@ def global_ragged(launches=3):
               contexts=bench.context_lengths(seed=3), launches=launches)
 
 
-def prefill(launches=6, slots=24, chunk=8, context=1024):
-    """BF16 prompt prefill on one period of the 31B layer pattern (five sliding layers and one
-    global layer at the real widths, vocabulary 262144): `slots` prompts advance `chunk` tokens a
-    call from `context` resident tokens. Prints the time per call, the same figure for the 60-layer
-    model (ten periods: extrapolated, the LM head is outside the timed calls) and the share of
-    the bf16 weight stream's roofline."""
+def _period_model(slots, max_context, with_assistant):
+    """One period of the 31B layer pattern (five sliding layers and one global layer at the real
+    widths, vocabulary 262144) with bf16 and e4m3 weights, and the reference-shaped drafter."""
     import carat_b200
     generator = torch.Generator(device="cuda").manual_seed(0)
 
-    def matrix(rows, cols):
+    def matrix(rows, cols, std=0.02):
         out = torch.empty(rows, cols, dtype=torch.bfloat16, device="cuda")
         step = max(1, (64 << 20) // cols)
         for start in range(0, rows, step):
             stop = min(rows, start + step)
             out[start:stop] = (torch.randn(stop - start, cols, device="cuda", generator=generator)
-                               * 0.02).to(torch.bfloat16)
+                               * std).to(torch.bfloat16)
         return out
 
     def ones(width):
@@ -218,9 +215,40 @@ def prefill(launches=6, slots=24, chunk=8, context=1024):
             weight_bytes += 2 * rows * cols
     weights = carat_b200.DeviceWeightArena(bf16)
     fp8 = carat_b200.Fp8WeightArena.quantize(weights)
+    if not with_assistant:
+        runner = carat_b200.Gemma4BatchModelRunner(config, weights, slots, max_context, fp8)
+        return config, runner, weight_bytes, (weights, fp8)
+    assistant_config = carat_b200.Gemma4AssistantConfig()
+    a_hidden, a_inter = assistant_config.hidden_size, assistant_config.intermediate_size
+    a = {"token_embedding": matrix(config.vocabulary_size, a_hidden, 0.05),
+         "pre_projection": matrix(a_hidden, 2 * hidden),
+         "post_projection": matrix(hidden, a_hidden, 0.05), "final_norm": ones(a_hidden)}
+    for index, kind in enumerate(assistant_config.layers):
+        prefix = f"layer.{index}."
+        head_dim = 512 if kind == "global" else 256
+        for name, width in (("input_norm", a_hidden), ("q_norm", head_dim),
+                            ("post_attention_norm", a_hidden), ("pre_mlp_norm", a_hidden),
+                            ("post_mlp_norm", a_hidden), ("scalar", 1)):
+            a[prefix + name] = ones(width)
+        a[prefix + "q"] = matrix(assistant_config.query_heads * head_dim, a_hidden, 0.05)
+        a[prefix + "o"] = matrix(a_hidden, assistant_config.query_heads * head_dim)
+        a[prefix + "gate_up"] = matrix(2 * a_inter, a_hidden, 0.05)
+        a[prefix + "down"] = matrix(a_hidden, a_inter)
+    a_weights = carat_b200.DeviceWeightArena(a)
+    a_fp8 = carat_b200.Fp8WeightArena.quantize(a_weights)
+    runner = carat_b200.Gemma4BatchModelRunner(config, weights, slots, max_context, fp8, a_weights,
+                                               a_fp8, assistant_config)
+    return config, runner, weight_bytes, (weights, fp8, a_weights, a_fp8)
+
+
+def prefill(launches=6, slots=24, chunk=8, context=1024):
+    """BF16 prompt prefill on one period of the 31B layer pattern: `slots` prompts advance `chunk`
+    tokens a call from `context` resident tokens. Prints the device time per call, the same figure
+    for the 60-layer model (ten periods: extrapolated, the LM head is outside the timed calls) and
+    the share of the bf16 weight stream's roofline."""
     # A multiple of 128 rows, like the server's 8192: the tensor-core attention needs that.
     max_context = (context + chunk * (launches + 2) + 64 + 127) // 128 * 128
-    runner = carat_b200.Gemma4BatchModelRunner(config, weights, slots, max_context, fp8)
+    config, runner, weight_bytes, keep = _period_model(slots, max_context, with_assistant=False)
     runner.seed_empty_cache_for_benchmark(context)
     tokens = torch.randint(3, config.vocabulary_size, (slots, max_context),
                            generator=torch.Generator().manual_seed(1)).tolist()
@@ -253,7 +281,81 @@ def prefill(launches=6, slots=24, chunk=8, context=1024):
     runner.close()
 
 
-CASES = {"prefill": prefill, "linear": linear, "gated": gated, "int4": int4, "lm_head": lm_head, "attention": attention, "global": global_attention,
+def serving(launches=72, slots=24):
+    """A request mix through the dispatcher and one replica's scheduler loop on one period of the
+    31B layer pattern with the real drafter: `launches` requests, prompts of 128..1536 tokens of
+    which half share a 512-token prefix, 16..96 new tokens each with real greedy acceptance, a
+    third of them second turns of finished conversations; closed loop (a request is admitted as
+    soon as the router finds it a slot), BF16 prefill in quanta of 64 tokens between decode steps.
+    It shows the path's callers working together at the real widths; its tokens/s belong to a
+    6-layer model, not to the 31B one."""
+    import random
+    import time
+    from carat_b200.dispatcher import (Dispatcher, LocalChannel, ReplicaScheduler, ReplicaWorker,
+                                       Request)
+    max_context = 2048
+    config, runner, _, keep = _period_model(slots, max_context, with_assistant=True)
+    generator = random.Random(3)
+
+    def tokens(count):
+        return [generator.randrange(3, config.vocabulary_size) for _ in range(count)]
+
+    shared = tokens(512)
+    channel = LocalChannel()
+    front = Dispatcher(channel, 1, slots)
+    worker = ReplicaWorker(channel, 0, ReplicaScheduler(runner, slots, depth=5, chunk_tokens=64))
+    first_turns = launches - launches // 3
+    waiting = []
+    for request_id in range(first_turns):
+        length = generator.randint(128, 1536)
+        prompt = (shared + tokens(length - 512)) if request_id % 2 and length > 512 else tokens(length)
+        waiting.append(Request(request_id, prompt, generator.randint(16, 96)))
+    second_turns = launches - first_turns
+    prompt_tokens = sum(len(request.input_ids) for request in waiting)
+    torch.cuda.synchronize()
+    begin = time.perf_counter()
+    for request in waiting:
+        front.submit(request)
+    followed = set()
+    next_id = first_turns
+    rounds = 0
+    while not front.finished() or len(followed) < second_turns:
+        front.poll()
+        worker.step()
+        rounds += 1
+        for request_id, output in list(front.completed.items()):
+            if request_id < first_turns and request_id not in followed and len(followed) < second_turns:
+                parent = front.origin[request_id]
+                history = parent.input_ids + output
+                if len(history) + 8 + 64 < max_context - 16:
+                    followed.add(request_id)
+                    turn = Request(next_id, history + tokens(8), generator.randint(16, 64))
+                    prompt_tokens += len(turn.input_ids)
+                    front.submit(turn)
+                    next_id += 1
+                elif request_id not in followed:
+                    followed.add(request_id)      # too long to continue: counts as handled
+        if rounds > 200000:
+            raise RuntimeError("the request mix did not drain")
+    front.poll()
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - begin
+    emitted = sum(len(output) for output in front.completed.values())
+    metrics = front.aggregate_metrics()
+    print(f"serving mix on a 6-layer 31B-width replica: {len(front.completed)} requests, "
+          f"{prompt_tokens} prompt tokens ({metrics['prefill_tokens']} prefilled, "
+          f"{metrics['prefix_tokens_reused']} reused from cache, {metrics['kv_clones']} slot clones), "
+          f"{emitted} tokens emitted in {seconds:.2f} s = {emitted / seconds:.0f} tokens/s; "
+          f"{metrics['decode_steps']} decode steps, {metrics['accepted_tokens']} verify rows accepted "
+          f"of {metrics['proposed_tokens']} proposed, {metrics['first_token_rejections']} "
+          f"first-token rejections")
+    for index, slot in enumerate(worker.scheduler.slots):
+        if slot.cached_tokens:
+            assert runner.slot_position(index) == len(slot.cached_tokens), index
+    runner.close()
+
+
+CASES = {"prefill": prefill, "serving": serving, "linear": linear, "gated": gated, "int4": int4, "lm_head": lm_head, "attention": attention, "global": global_attention,
          "global_ragged": global_ragged}
 
 

@@ -168,11 +168,13 @@ class _Slot:
 
 class ReplicaScheduler:
     """Drives one runner. `engine` is a Gemma4BatchModelRunner or anything with its methods
-    (reset_slot, clone_slot, prefill_slot_from_prefix, draft_four, verify_greedy_proposals,
-    append_ragged, has_assistant, slot_position)."""
+    (reset_slot, clone_slot, prefill_slots_chunks, draft_four, verify_greedy_proposals,
+    append_ragged, has_assistant, slot_position). `chunk_tokens` is the prefill quantum: how many
+    prompt tokens a slot advances per tick, so that decoding slots are not starved by a long
+    prompt (the reference's idle_prefill_quantum_tokens)."""
 
     def __init__(self, engine, slots: int, depth: int = 5, speculative_minimum_batch: int = 1,
-                 chunk_tokens: int = 1024):
+                 chunk_tokens: int = 64):
         self.engine = engine
         self.slots = [_Slot() for _ in range(slots)]
         self.depth = depth
@@ -228,24 +230,36 @@ class ReplicaScheduler:
             slot.request, slot.decode_ready, slot.age, slot.dirty = None, False, self.clock, True
 
     def tick(self):
-        """One pass: finish every pending prefill, then one decode step over the decode-ready
-        slots. Returns ({request id: tokens emitted this tick}, [request ids finished])."""
+        """One pass: one prefill quantum for every slot whose prompt is not resident yet (all of
+        them in one batched call, like the reference's idle_prefill_batch,
+        src/native_runtime_main.cpp:421-478), then one decode step over the decode-ready slots.
+        Returns ({request id: tokens emitted this tick}, [request ids finished])."""
         emitted: Dict[int, List[int]] = {}
         finished: List[int] = []
+        prefilling = []
         for index, slot in enumerate(self.slots):
             if slot.request is None or slot.decode_ready:
                 continue
-            prompt = slot.request.input_ids
-            resident = len(slot.cached_tokens)
             if slot.inherited_token is not None:
                 first, slot.inherited_token = slot.inherited_token, None
+                emitted.setdefault(slot.request.request_id, []).extend(
+                    self._start_decode(index, first))
+                self._finish_if_done(index, False, finished)
             else:
-                first = self.engine.prefill_slot_from_prefix(index, prompt, resident,
-                                                             self.chunk_tokens)
-                self.metrics["prefill_tokens"] += len(prompt) - resident
-                slot.cached_tokens = list(prompt)
-            emitted.setdefault(slot.request.request_id, []).extend(self._start_decode(index, first))
-            self._finish_if_done(index, False, finished)
+                prefilling.append(index)
+        if prefilling:
+            prompts = [self.slots[index].request.input_ids for index in prefilling]
+            firsts = self.engine.prefill_slots_chunks(prefilling, prompts, self.chunk_tokens)
+            for index, first in zip(prefilling, firsts):
+                slot = self.slots[index]
+                resident = self.engine.slot_position(index)
+                self.metrics["prefill_tokens"] += resident - len(slot.cached_tokens)
+                slot.cached_tokens = list(slot.request.input_ids[:resident])
+                slot.dirty = True
+                if first is not None:
+                    emitted.setdefault(slot.request.request_id, []).extend(
+                        self._start_decode(index, first))
+                    self._finish_if_done(index, False, finished)
         batch = [index for index, slot in enumerate(self.slots)
                  if slot.request is not None and slot.decode_ready]
         if batch:

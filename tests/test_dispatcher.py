@@ -214,12 +214,18 @@ class StandInRunner:
         self.calls["clone"] += 1
         return 0
 
-    def prefill_slot_from_prefix(self, slot, token_ids, cached_prefix_tokens, chunk_tokens=1024):
-        assert self.resident[slot] == list(token_ids[:cached_prefix_tokens]), "prefix not resident"
-        assert cached_prefix_tokens < len(token_ids)
-        self.calls["prefill_tokens"] += len(token_ids) - cached_prefix_tokens
-        self.resident[slot] = list(token_ids)
-        return model_next(self.resident[slot])
+    def prefill_slots_chunks(self, slots, token_ids, chunk_tokens):
+        out = []
+        for slot, tokens in zip(slots, token_ids):
+            resident = len(self.resident[slot])
+            assert self.resident[slot] == list(tokens[:resident]), "prefix not resident"
+            assert resident < len(tokens)
+            advance = min(chunk_tokens, len(tokens) - resident)
+            self.calls["prefill_tokens"] += advance
+            self.resident[slot] = list(tokens[:resident + advance])
+            done = resident + advance == len(tokens)
+            out.append(model_next(self.resident[slot]) if done else None)
+        return out
 
     def append_ragged(self, token_ids, slots):
         self.calls["append"] += 1
