@@ -207,5 +207,10 @@ def check(status: int) -> None:
 
 
 def int_array(values):
+    """A C int array of the values; a ctypes int array is passed through as it is, so a caller
+    that hands the same long sequence to many calls (a prompt, quantum after quantum) can convert
+    it once."""
+    if isinstance(values, ctypes.Array) and values._type_ is c_int:
+        return values
     values = list(values)
     return (c_int * len(values))(*values)

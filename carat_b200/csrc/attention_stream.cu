@@ -81,8 +81,8 @@ __device__ __forceinline__ StreamItem stream_item(const AttentionArguments &a, i
 // index leaves some CTAs with three full chunks and others with one short one, and the kernel
 // takes as long as its busiest CTA. Instead the items that exist are put in descending order of
 // their cache rows (all full chunks first, then every request's last, partial chunk, longest
-// first) and dealt out boustrophedon: round 0 to CTAs 0..G-1, round 1 to G-1..0, and so on, so
-// the CTA that got the larger item of one round gets the smaller of the next. Every CTA computes
+// first) and dealt out boustrophedon: the first G items to CTAs 0..G-1, the next G to G-1..0, and
+// so on, so the CTA that got the larger item of one pass gets the smaller of the next. Every CTA computes
 // the same order from the positions; every role of a CTA then walks the CTA's own short list.
 constexpr int cached_items = 32;
 constexpr int schedule_requests = 64;

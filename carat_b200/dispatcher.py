@@ -163,6 +163,7 @@ class _Slot:
     age: int = 0
     reported: int = 0           # how many cached tokens the router has been told about
     inherited_token: Optional[int] = None   # whole prompt was cached: the source's prediction
+    prompt_array: object = None             # the prompt as a C int array while it is prefilling
     dirty: bool = True
 
 
@@ -195,6 +196,7 @@ class ReplicaScheduler:
         self.clock += 1
         slot.request, slot.output_ids, slot.decode_ready = request, [], False
         slot.inherited_token = None
+        slot.prompt_array = None
         slot.age, slot.dirty = self.clock, True
         # The router decided on its mirror of the table; a source that was decoding has moved on
         # since (its cache only grows while occupied), and a ring cannot be wound back, so a
@@ -216,6 +218,7 @@ class ReplicaScheduler:
 
     def _start_decode(self, index: int, first_token: int) -> List[int]:
         slot = self.slots[index]
+        slot.prompt_array = None
         slot.token_to_append, slot.decode_ready = first_token, True
         slot.output_ids.append(first_token)
         slot.dirty = True
@@ -248,7 +251,12 @@ class ReplicaScheduler:
             else:
                 prefilling.append(index)
         if prefilling:
-            prompts = [self.slots[index].request.input_ids for index in prefilling]
+            # The prompt goes to the engine once per quantum; convert it to a C array once.
+            for index in prefilling:
+                slot = self.slots[index]
+                if slot.prompt_array is None:
+                    slot.prompt_array = capi.int_array(slot.request.input_ids)
+            prompts = [self.slots[index].prompt_array for index in prefilling]
             firsts = self.engine.prefill_slots_chunks(prefilling, prompts, self.chunk_tokens)
             for index, first in zip(prefilling, firsts):
                 slot = self.slots[index]
