@@ -28,6 +28,7 @@ using namespace carat_b200;
 namespace {
 
 constexpr int maximum_depth = 9;       // k = 8 drafts + the forced token
+constexpr int prefill_pieces = 64;     // (slot, eight-token piece) entries one prefill step takes
 constexpr int maximum_rows = 256;      // rows one FP8 linear launch accepts (24 slots x depth 9 = 216)
 constexpr int global_chunk_keys = 1024;
 
@@ -208,6 +209,11 @@ struct carat_b200_runner {
   // ---- BF16 prefill: the target's bf16 matrices, bf16 inputs of its linears, plans per row count
   std::vector<carat_b200_layer_bf16_weights> bf16_layers;
   DeviceBuffer p_normed, p_pre_mlp, p_activated;
+  // Prefill steps may list a slot several times (consecutive eight-token pieces of one prompt),
+  // so their per-request inputs are sized for prefill_pieces entries, not for the batch.
+  DeviceBuffer p_step_inputs, p_request_chunks;
+  PinnedBuffer p_host_inputs;
+  std::map<std::pair<int, int>, AttentionMaps> direct_maps;   // sliding layers read as linear caches
   std::map<int, StepPlans> prefill_plans;
   // ---- drafter precision (CARAT_B200_ASSISTANT_FP8_*): bf16 matrices and their plans
   int assistant_mode{CARAT_B200_ASSISTANT_FP8_ALL};
@@ -679,6 +685,31 @@ const AttentionMaps *verify_attention_maps(Runner &runner, int layer_index, int 
   return &runner.verify_maps.emplace(key, maps).first->second;
 }
 
+// The same for a sliding layer whose rings are read as linear caches (prefill before the first
+// wrap): no staged proposals, the ring's own rows only.
+const AttentionMaps *direct_attention_maps(Runner &runner, int layer_index, int depth) {
+  const LayerState &layer = runner.layers[static_cast<size_t>(layer_index)];
+  const auto &shape = layer.shape;
+  const int padded = attention_padded_rows(shape.query_heads / shape.kv_heads * depth);
+  if ((shape.head_dim != 256 && shape.head_dim != 512) || layer.capacity % 128 != 0 || padded == 0)
+    return nullptr;
+  const auto key = std::make_pair(layer_index, depth);
+  const auto found = runner.direct_maps.find(key);
+  if (found != runner.direct_maps.end())
+    return &found->second;
+  const int stride = runner.score_stride_sliding;
+  AttentionMaps maps;
+  const int status = make_attention_maps(
+      &maps, layer.keys(), layer.values(),
+      static_cast<long long>(runner.batch) * shape.kv_heads * layer.capacity, nullptr, nullptr, 0,
+      runner.queries.get(), static_cast<long long>(runner.queries.bytes() / (2 * shape.head_dim)),
+      runner.scores.get(), static_cast<long long>(runner.scores.bytes() / (2 * stride)), stride,
+      shape.head_dim, padded);
+  if (status != 0)
+    throw Failure{"attention tensor map encoding failed"};
+  return &runner.direct_maps.emplace(key, maps).first->second;
+}
+
 const AttentionMaps *draft_attention_maps(Runner &runner, int assistant_layer) {
   const LayerState &shared = shared_layer(runner, assistant_layer);
   const auto &shape = shared.shape;
@@ -1062,18 +1093,32 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
   }
 }
 
-// One BF16 forward over `depth` prompt tokens of each listed slot, all of them made resident:
+// One BF16 forward over `depth` prompt tokens of each listed entry, all of them made resident:
 // the verify step's layer loop with bf16 linears and no quantisation, every row committed.
+// An entry is a slot; a slot may be listed several times in a row, each entry then being the next
+// `depth` tokens of that slot's prompt. That form needs `linear_rings`: every listed slot's
+// sliding rings are still unwrapped and stay so through this step, so the ring is a linear cache,
+// K and V rows are written in place before the attention runs (as on global layers, and as the
+// reference does before the first wrap, cuda/layer_runner.cu:851-878) and each entry attends
+// causally to everything before it, the earlier entries of its own step included.
 // When `predict` is set the bf16 LM head runs over the step's final-normed rows and
 // predictions_out receives the argmax of every row (requests * depth).
 void prefill_step(Runner &runner, const int *tokens, int requests, int depth, const int *slots,
-                  bool predict, int *predictions_out) {
+                  bool linear_rings, bool predict, int *predictions_out) {
   const auto &config = runner.config;
   const int rows = requests * depth;
-  const StepLayout host = layout_inputs(runner.host_inputs.get<int>(), maximum_rows, runner.batch);
+  if (requests > prefill_pieces || rows > maximum_rows)
+    throw Failure{"invalid batched chunk prefill shape"};
+  const StepLayout host =
+      layout_inputs(runner.p_host_inputs.get<int>(), maximum_rows, prefill_pieces);
   int longest = 0;
+  std::vector<int> advanced(static_cast<size_t>(runner.batch), 0);
   for (int request = 0; request < requests; ++request) {
-    const int position = runner.slot_positions[static_cast<size_t>(slots[request])];
+    const size_t slot = static_cast<size_t>(slots[request]);
+    const int position = runner.slot_positions[slot] + advanced[slot];
+    if (advanced[slot] > 0 && !linear_rings)
+      throw Failure{"invalid batched chunk prefill request"};
+    advanced[slot] += depth;
     for (int token = 0; token < depth; ++token)
       host.tokens[request * depth + token] = tokens[request * depth + token];
     host.positions[request] = position;
@@ -1084,10 +1129,10 @@ void prefill_step(Runner &runner, const int *tokens, int requests, int depth, co
   }
   StepPlans &plans = prefill_plans_for(runner, rows);
   const StepLayout device =
-      layout_inputs(runner.step_inputs.get<int>(), maximum_rows, runner.batch);
+      layout_inputs(runner.p_step_inputs.get<int>(), maximum_rows, prefill_pieces);
   cudaStream_t stream = runner.stream;
-  require_cuda(cudaMemcpyAsync(runner.step_inputs.get(), runner.host_inputs.get<int>(),
-                               sizeof(int) * (maximum_rows + 4 * runner.batch),
+  require_cuda(cudaMemcpyAsync(runner.p_step_inputs.get(), runner.p_host_inputs.get<int>(),
+                               sizeof(int) * (maximum_rows + 4 * prefill_pieces),
                                cudaMemcpyHostToDevice, stream),
                "copy prefill step inputs");
   require_cuda(cudaEventRecord(runner.start_event, stream), "record prefill start");
@@ -1137,7 +1182,8 @@ void prefill_step(Runner &runner, const int *tokens, int requests, int depth, co
     post.max_positions = runner.maximum_context;
     post.epsilon = epsilon;
     post.capacity = layer.capacity;
-    if (shape.global_attention) {
+    const bool in_place = shape.global_attention || linear_rings;
+    if (in_place) {
       post.direct = 1;
       post.key_base = layer.keys();
       post.value_base = layer.values();
@@ -1176,6 +1222,13 @@ void prefill_step(Runner &runner, const int *tokens, int requests, int depth, co
       attention.score_stride = runner.score_stride_global;
       attention.chunk_keys = global_chunk_keys;
       attention.chunks = attention_chunks(longest + depth, global_chunk_keys);
+    } else if (linear_rings) {
+      // Unwrapped ring: rows 0 .. position + depth - 1 in order, all inside the window.
+      attention.window = 0;
+      attention.max_cache_rows = longest + depth;
+      attention.score_stride = runner.score_stride_sliding;
+      attention.chunk_keys = (layer.capacity + 127) / 128 * 128;
+      attention.chunks = 1;
     } else {
       attention.window = config.sliding_window;
       attention.new_keys = layer.staged_keys();
@@ -1189,8 +1242,10 @@ void prefill_step(Runner &runner, const int *tokens, int requests, int depth, co
     }
     attention.stats = runner.attention_stats.get<float2>();
     attention.stats_stride = runner.stats_stride;
-    attention.request_chunks = runner.request_chunks.get<int>();
-    attention.maps = verify_attention_maps(runner, index, depth);
+    attention.request_chunks = runner.p_request_chunks.get<int>();
+    attention.maps = (linear_rings && !shape.global_attention)
+                         ? direct_attention_maps(runner, index, depth)
+                         : verify_attention_maps(runner, index, depth);
     require_launch(attention.maps != nullptr ? launch_attention_tc(attention, stream)
                                              : launch_attention_simt(attention, stream),
                    "prefill attention");
@@ -1199,7 +1254,7 @@ void prefill_step(Runner &runner, const int *tokens, int requests, int depth, co
       const bool counted = attention.maps != nullptr;
       require_launch(launch_quant(nullptr, runner.attention_partials.get<float>(),
                                   attention.chunks,
-                                  counted ? runner.request_chunks.get<int>() : nullptr, depth,
+                                  counted ? runner.p_request_chunks.get<int>() : nullptr, depth,
                                   rows_only(runner.attention_out.get()), rows,
                                   layer.query_width(), stream),
                      "prefill attention rows");
@@ -1233,7 +1288,7 @@ void prefill_step(Runner &runner, const int *tokens, int requests, int depth, co
     runner.launches += 1;
     std::swap(current, other);
   }
-  if (runner.commit_layer_count > 0) {
+  if (runner.commit_layer_count > 0 && !linear_rings) {
     require_launch(launch_commit(runner.commit_layers.get<CommitLayer>(), runner.commit_layer_count,
                                  device.positions, device.caps, device.slots, requests, depth, 0,
                                  stream),
@@ -1740,6 +1795,9 @@ extern "C" int carat_b200_runner_set_bf16_weights(carat_b200_runner *runner,
       runner->p_normed.allocate(rows * runner->config.hidden_size * 2);
       runner->p_pre_mlp.allocate(rows * runner->config.hidden_size * 2);
       runner->p_activated.allocate(rows * runner->config.intermediate_size * 2);
+      runner->p_step_inputs.allocate(sizeof(int) * (rows + 4 * prefill_pieces), true);
+      runner->p_host_inputs.allocate(sizeof(int) * (rows + 4 * prefill_pieces));
+      runner->p_request_chunks.allocate(sizeof(int) * prefill_pieces, true);
     }
   });
 }
@@ -1782,44 +1840,96 @@ extern "C" int carat_b200_runner_prefill_slots_chunks(
       has_prediction[request] = 0;
       predictions[request] = -1;
     }
-    // Walk the chunks in steps of at most eight tokens; a step takes every request that still
-    // has tokens left and as many tokens as the shortest of them has (rows of different requests
-    // never mix in bf16, so the grouping does not change any row).
+    // Walk the chunks in steps. A step is a list of (request, eight-token piece) entries of one
+    // common depth (rows of different entries never mix in bf16, so the grouping does not change
+    // any row). While a prompt's sliding rings are still unwrapped a request may put several
+    // consecutive pieces into one step (up to 256 rows in all): the weights then stream once per
+    // step instead of once per eight tokens. Requests past the first wrap advance one piece a
+    // step, in steps of their own.
     constexpr int step_tokens = 8;
+    const int window = runner->config.sliding_window;
     std::vector<int> cursor = begin;
     const size_t hidden_bytes = static_cast<size_t>(runner->config.hidden_size) * 2;
     for (;;) {
+      std::vector<int> waiting;
+      bool any_linear = false;
+      for (int request = 0; request < requests; ++request) {
+        if (end[static_cast<size_t>(request)] > cursor[static_cast<size_t>(request)])
+          waiting.push_back(request);
+      }
+      if (waiting.empty())
+        break;
+      const auto stays_linear = [&](int request, int pieces, int depth) {
+        return cursor[static_cast<size_t>(request)] + pieces * depth <= window;
+      };
+      for (const int request : waiting) {
+        const int left = end[static_cast<size_t>(request)] - cursor[static_cast<size_t>(request)];
+        any_linear = any_linear || stays_linear(request, 1, std::min(step_tokens, left));
+      }
+      // One kind of request per step: those whose rings stay linear, else the others.
       std::vector<int> active;
       int depth = step_tokens;
-      for (int request = 0; request < requests; ++request) {
+      for (const int request : waiting) {
         const int left = end[static_cast<size_t>(request)] - cursor[static_cast<size_t>(request)];
-        if (left > 0) {
-          active.push_back(request);
-          depth = std::min(depth, left);
+        if (any_linear && !stays_linear(request, 1, std::min(step_tokens, left)))
+          continue;
+        active.push_back(request);
+        depth = std::min(depth, left);
+      }
+      if (any_linear) {
+        // The common depth may have shrunk; drop whoever no longer stays linear at that depth.
+        std::vector<int> kept;
+        for (const int request : active) {
+          if (stays_linear(request, 1, depth))
+            kept.push_back(request);
+        }
+        active.swap(kept);
+      }
+      std::vector<int> pieces(active.size(), 1);
+      if (any_linear) {
+        const int most = std::min(prefill_pieces, maximum_rows / depth);
+        int total = static_cast<int>(active.size());
+        for (bool grew = true; grew && total < most;) {
+          grew = false;
+          for (size_t index = 0; index < active.size() && total < most; ++index) {
+            const int request = active[index];
+            const int left =
+                end[static_cast<size_t>(request)] - cursor[static_cast<size_t>(request)];
+            if ((pieces[index] + 1) * depth <= left &&
+                stays_linear(request, pieces[index] + 1, depth)) {
+              ++pieces[index];
+              ++total;
+              grew = true;
+            }
+          }
         }
       }
-      if (active.empty())
-        break;
       std::vector<int> step_slots;
       std::vector<int> step_ids;
+      std::vector<int> last_entry(active.size(), 0);
       bool predict = false;
-      for (const int request : active) {
-        step_slots.push_back(slots[request]);
-        const int from = cursor[static_cast<size_t>(request)];
-        step_ids.insert(step_ids.end(), token_ids[request] + from, token_ids[request] + from + depth);
-        predict = predict || from + depth == token_counts[request];
-      }
-      std::vector<int> step_predictions(active.size() * static_cast<size_t>(depth), -1);
-      prefill_step(*runner, step_ids.data(), static_cast<int>(active.size()), depth,
-                   step_slots.data(), predict, step_predictions.data());
       for (size_t index = 0; index < active.size(); ++index) {
         const int request = active[index];
-        cursor[static_cast<size_t>(request)] += depth;
+        const int from = cursor[static_cast<size_t>(request)];
+        const int count = pieces[index] * depth;
+        for (int piece = 0; piece < pieces[index]; ++piece)
+          step_slots.push_back(slots[request]);
+        step_ids.insert(step_ids.end(), token_ids[request] + from, token_ids[request] + from + count);
+        last_entry[index] = static_cast<int>(step_slots.size()) - 1;
+        predict = predict || from + count == token_counts[request];
+      }
+      const int entries = static_cast<int>(step_slots.size());
+      std::vector<int> step_predictions(static_cast<size_t>(entries) * depth, -1);
+      prefill_step(*runner, step_ids.data(), entries, depth, step_slots.data(), any_linear, predict,
+                   step_predictions.data());
+      for (size_t index = 0; index < active.size(); ++index) {
+        const int request = active[index];
+        cursor[static_cast<size_t>(request)] += pieces[index] * depth;
         if (cursor[static_cast<size_t>(request)] != token_counts[request])
           continue;
         // The whole prompt is resident: its last row predicts the first generated token and its
         // final-normed hidden row goes to the drafter's table (cuda/batch_model_runner.cu:1106-1124).
-        const size_t row = index * static_cast<size_t>(depth) + static_cast<size_t>(depth) - 1;
+        const size_t row = static_cast<size_t>(last_entry[index]) * depth + depth - 1;
         has_prediction[request] = 1;
         predictions[request] = step_predictions[row];
         require_cuda(cudaMemcpyAsync(
