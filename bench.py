@@ -66,6 +66,22 @@ def context_lengths(seed):
     return torch.randint(128, 6145, (SLOTS,), generator=generator).tolist()
 
 
+def rank_workload(steps, rank, same_seeds=False):
+    """Context lengths and per-step accept lengths of one replica. Weak scaling keeps the work per
+    GPU fixed, so every replica gets the multiset of the single-GPU run (the same KV bytes, the
+    same number of accepted tokens in every step) dealt to its slots in an order of its own;
+    `same_seeds` gives every replica the very same assignment."""
+    contexts = context_lengths(seed=3)
+    lengths = accept_lengths(steps, seed=7)
+    if rank == 0 or same_seeds:
+        return contexts, lengths
+    generator = torch.Generator().manual_seed(1000 + rank)
+    order = torch.randperm(SLOTS, generator=generator).tolist()
+    contexts = [contexts[index] for index in order]
+    shuffled = torch.stack([row[torch.randperm(SLOTS, generator=generator)] for row in lengths])
+    return contexts, shuffled
+
+
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -243,10 +259,9 @@ def run_ours(args, rank, world):
     library = carat_b200.library()
     config, runner, fp8 = build_model(seed=0)
     seed_shift = 0 if args.same_seeds else rank
-    lengths = accept_lengths(args.steps + args.warmup, seed=7 + seed_shift)
+    start_positions, lengths = rank_workload(args.steps + args.warmup, rank, args.same_seeds)
     generator = torch.Generator().manual_seed(11 + seed_shift)
     slots = list(range(SLOTS))
-    start_positions = context_lengths(seed=3 + seed_shift)
 
     def reseed():
         runner.seed_slot_positions(start_positions)
@@ -866,7 +881,8 @@ def main():
                         help="leave the int4_mlp object (the step with INT4 weight-only MLP "
                              "linears, N = 1 only) out")
     parser.add_argument("--same-seeds", action="store_true",
-                        help="N > 1: every rank draws the same contexts and accept lengths "
+                        help="N > 1: every rank gets the very same slot-by-slot assignment instead of "
+                             "the same work in an order of its own "
                              "(separates workload skew from machine effects)")
     parser.add_argument("--skip-cpu", action="store_true",
                         help="leave the cpu_baseline object out (profiling runs)")

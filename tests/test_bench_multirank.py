@@ -2,7 +2,7 @@
 
 Replicas share nothing on the data path (one runner per GPU, slots never migrate), so what has to
 be right is the aggregation: the timed region's duration is the maximum over ranks, the token count
-the sum, every rank takes a different seeded workload, and only rank 0 prints.
+the sum, every rank takes the same amount of work in a different order, and only rank 0 prints.
 """
 import json
 import os
@@ -25,8 +25,7 @@ WORKER = textwrap.dedent("""
     torch.distributed.init_process_group("gloo")
     bench.barrier(world)
     maxima, sums = bench.reduce_max_and_sum(world, [10.0 + rank, 5.0 - rank], [100.0 * (rank + 1)])
-    lengths = bench.accept_lengths(4, seed=7 + rank)
-    contexts = bench.context_lengths(seed=3 + rank)
+    contexts, lengths = bench.rank_workload(4, rank)
     bench.barrier(world)
     with open(os.path.join(os.environ["CARAT_OUT"], f"rank{rank}.json"), "w") as out:
         json.dump({"rank": rank, "maxima": maxima, "sums": sums,
@@ -60,9 +59,13 @@ def test_two_ranks_aggregate_max_time_and_sum_tokens(tmp_path):
     for record in records:
         assert record["maxima"] == [11.0, 5.0]      # slowest rank's time, per entry
         assert record["sums"] == [300.0]            # tokens of all ranks
-    # Each replica draws its own workload from its own seed.
+    # Each replica serves the same amount of work in an order of its own: the same context
+    # lengths on different slots, the same accepted tokens in every step on different slots.
     assert records[0]["lengths"] != records[1]["lengths"]
     assert records[0]["contexts"] != records[1]["contexts"]
+    assert sorted(records[0]["contexts"]) == sorted(records[1]["contexts"])
+    assert [sorted(row) for row in records[0]["lengths"]] == \
+        [sorted(row) for row in records[1]["lengths"]]
     for record in records:
         assert all(1 <= value <= 5 for row in record["lengths"] for value in row)
         assert all(128 <= value <= 6144 for value in record["contexts"])
