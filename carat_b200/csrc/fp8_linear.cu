@@ -724,7 +724,7 @@ int launch_variant(const LinearPlan &plan, const KernelArguments &arguments, cud
   const int ctas = items < plan.ctas ? items : plan.ctas;
   return launch_chained(fp8_linear_kernel<padded_rows, mode, wide>,
                         dim3(static_cast<unsigned>(ctas)),
-                        dim3(linear_threads), dynamic_bytes, stream, mode == 3, plan.weight_map,
+                        dim3(linear_threads), dynamic_bytes, stream, false, plan.weight_map,
                         plan.input_map, arguments) == cudaSuccess
              ? 0
              : -11;

@@ -51,6 +51,8 @@ struct RowArguments {
   __nv_bfloat16 *pass_rows;          // two-launch form: bf16 rows [rows, width] between the launches
   unsigned int *clear_base;
   int clear_words;
+  unsigned int *barrier_word;
+  int *barrier_error;
   int width;
   float epsilon;
 };
@@ -472,7 +474,30 @@ row_kernel(RowArguments a) {
     }
     return;
   }
-  cg::this_grid().sync();
+  if (a.barrier_word != nullptr) {
+    // Every CTA of the grid is resident (the launcher checked the grid against the device's
+    // capacity, and the grid that follows in the chain cannot start before all of these CTAs
+    // have), so counting them in is a barrier: gridDim.x arrivals open it, gridDim.x more (one
+    // per CTA on its way out) wrap the word back to zero for the next launch.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0U) {
+      atomicInc(a.barrier_word, 2U * gridDim.x - 1U);
+      const long long start = clock64();
+      while (*reinterpret_cast<volatile unsigned int *>(a.barrier_word) < gridDim.x) {
+        if (clock64() - start > 4000000000LL) {   // about two seconds: give up, say so
+          if (a.barrier_error != nullptr)
+            atomicExch(a.barrier_error, 7);
+          break;
+        }
+      }
+      atomicInc(a.barrier_word, 2U * gridDim.x - 1U);
+      __threadfence();
+    }
+    __syncthreads();
+  } else {
+    cg::this_grid().sync();
+  }
   const float tensor_amax = __uint_as_float(*reinterpret_cast<volatile unsigned int *>(a.amax_bits));
   const float scale = tensor_amax > 0.0F ? tensor_amax / 448.0F : 1.0F;
   const float inverse_scale = 1.0F / scale;
@@ -554,7 +579,7 @@ int launch_rows_chunks(const RowArguments &arguments, int ctas, cudaStream_t str
   if (ctas <= resident_limit) {
     const cudaError_t status =
         launch_chained(row_kernel<mode, chunks, false>, dim3(static_cast<unsigned>(ctas)),
-                       dim3(row_threads), 0, stream, true, arguments);
+                       dim3(row_threads), 0, stream, arguments.barrier_word == nullptr, arguments);
     return status == cudaSuccess ? 0 : -11;
   }
   if (arguments.pass_rows == nullptr)
@@ -641,6 +666,8 @@ RowArguments base_arguments(QuantTarget target, int width, float epsilon) {
   arguments.scale = target.scale;
   arguments.amax_bits = target.amax_bits;
   arguments.pass_rows = static_cast<__nv_bfloat16 *>(target.two_launch_rows);
+  arguments.barrier_word = target.barrier_word;
+  arguments.barrier_error = target.barrier_error;
   arguments.second_out = static_cast<__nv_bfloat16 *>(target.bf16_output);
   arguments.width = width;
   arguments.epsilon = epsilon;

@@ -197,6 +197,7 @@ struct carat_b200_runner {
   DeviceBuffer gated_rows;   // bf16 [rows, intermediate]: GeGLU rows out of the gated gate_up linear
   DeviceBuffer grid_counter;   // barrier word of the gated linear; zero between launches
   bool fused_geglu{false};
+  bool cooperative_rows{false};   // CARAT_B200_COOPERATIVE_ROWS=1: row kernels as cooperative launches
   DeviceBuffer unit_scale;   // one fp32 1.0: INT4 partial sums carry no tensor scales
   std::map<std::pair<int, int>, AttentionMaps> verify_maps;  // (layer, depth)
   std::map<int, AttentionMaps> draft_maps;                   // assistant layer
@@ -388,6 +389,8 @@ void build_runner(Runner &runner, const carat_b200_model_config &config,
   // barriers for the same work.
   const char *fused = std::getenv("CARAT_B200_FUSED_GEGLU");
   runner.fused_geglu = config.intermediate_size % 64 == 0 && fused != nullptr && fused[0] == '1';
+  const char *cooperative = std::getenv("CARAT_B200_COOPERATIVE_ROWS");
+  runner.cooperative_rows = cooperative != nullptr && cooperative[0] == '1';
   runner.gated_rows.allocate(static_cast<size_t>(rows) * config.intermediate_size * 2);
   runner.grid_counter.allocate(256, true);
   // Split-K partials [splits, rows, features] fp32; plans that would need more are rejected.
@@ -797,8 +800,13 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
   auto *best = reinterpret_cast<unsigned long long *>(amax + runner.amax_words);
   auto *scales = runner.scales.get<float>();
   const auto target = [&](int word) {
-    return QuantTarget{runner.quantized.get(), scales + word, amax + word,
-                       runner.two_launch_rows.get()};
+    QuantTarget made{runner.quantized.get(), scales + word, amax + word,
+                     runner.two_launch_rows.get()};
+    if (!runner.cooperative_rows) {
+      made.barrier_word = runner.grid_counter.get<unsigned int>() + 16;
+      made.barrier_error = runner.device_error;
+    }
+    return made;
   };
   const auto bf16_target = [](void *rows_out) {
     return QuantTarget{nullptr, nullptr, nullptr, nullptr, rows_out};
@@ -1380,7 +1388,12 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
   auto *best = reinterpret_cast<unsigned long long *>(amax + runner.a_amax_words);
   auto *scales = runner.a_scales.get<float>();
   const auto target = [&](int word) {
-    return QuantTarget{runner.a_quantized.get(), scales + word, amax + word};
+    QuantTarget made{runner.a_quantized.get(), scales + word, amax + word};
+    if (!runner.cooperative_rows) {
+      made.barrier_word = runner.grid_counter.get<unsigned int>() + 16;
+      made.barrier_error = runner.device_error;
+    }
+    return made;
   };
   int *draft_tokens = runner.a_proposals.get<int>();  // [depth][requests]
 
