@@ -146,6 +146,8 @@ SIGNATURES = {
     "carat_b200_runner_destroy": (None, [_P]),
     "carat_b200_select_placement": (_I, [_IP, _I, POINTER(SlotView), _I, _I, POINTER(Placement)]),
     "carat_b200_route_request": (_I, [_IP, _I, POINTER(ReplicaView), _I, _I, POINTER(Placement)]),
+    "carat_b200_weights_quantize_int4_mlp": (_I, [_P, _I]),
+    "carat_b200_weights_int4_mlp_layers": (_I, [_P, POINTER(Int4MlpLayer), _I, _IP, _IP]),
     "carat_b200_weights_load": (_I, [c_char_p, POINTER(ModelConfig), POINTER(AssistantConfig), _I,
                                     POINTER(c_void_p)]),
     "carat_b200_weights_destroy": (None, [_P]),

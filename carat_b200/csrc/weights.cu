@@ -12,6 +12,7 @@
 // second stream, so disk, PCIe and the quantiser overlap.
 #include "../../include/carat_b200.h"
 #include "context.cuh"
+#include "int4_linear.cuh"
 #include "row_ops.cuh"
 
 #include <fcntl.h>
@@ -517,8 +518,14 @@ struct carat_b200_weights {
   float *scales{nullptr};              // one fp32 per two-dimensional segment
   std::vector<std::uint64_t> fp8_offsets;   // per segment; ~0 when it has no e4m3 form
   std::uint64_t fp8_bytes{0};
+  // INT4 form of the MLP matrices (carat_b200_weights_quantize_int4_mlp): per layer the reordered
+  // codes and group scales of gate_up and down, in one allocation.
+  unsigned char *int4_arena{nullptr};
+  std::vector<carat_b200_int4_mlp_layer> int4_layers;
+  int int4_group_width{0};
 
   ~carat_b200_weights() {
+    cudaFree(int4_arena);
     cudaFree(scales);
     cudaFree(fp8_arena);
     cudaFree(arena);
@@ -731,5 +738,105 @@ extern "C" int carat_b200_weights_find(const carat_b200_weights *weights, const 
     if (found == weights->by_name.end())
       throw Failure{std::string("missing execution weight ") + name};
     describe(*weights, found->second, segment);
+  });
+}
+
+extern "C" int carat_b200_weights_quantize_int4_mlp(carat_b200_weights *weights,
+                                                    int group_width) {
+  return guarded([&] {
+    if (weights == nullptr || (group_width != 128 && group_width != 256))
+      throw Failure{"invalid BF16 INT4 linear weight shape"};
+    // Layers are the segments "layer.N.gate_up" / "layer.N.down", N = 0, 1, ... without a gap.
+    struct Matrix {
+      size_t segment;
+      std::uint64_t rows, cols;
+    };
+    std::vector<std::pair<Matrix, Matrix>> layers;
+    for (int layer = 0;; ++layer) {
+      const std::string prefix = "layer." + std::to_string(layer) + ".";
+      const auto gate_up = weights->by_name.find(prefix + "gate_up");
+      const auto down = weights->by_name.find(prefix + "down");
+      if (gate_up == weights->by_name.end() || down == weights->by_name.end())
+        break;
+      const Segment &a = weights->plan.segments[gate_up->second];
+      const Segment &b = weights->plan.segments[down->second];
+      if (a.shape.size() != 2 || b.shape.size() != 2 || a.shape[1] % group_width != 0 ||
+          b.shape[1] % group_width != 0 || a.shape[0] % 8 != 0 || b.shape[0] % 8 != 0) {
+        throw Failure{"invalid BF16 INT4 linear weight shape"};
+      }
+      layers.push_back({{gate_up->second, a.shape[0], a.shape[1]},
+                        {down->second, b.shape[0], b.shape[1]}});
+    }
+    if (layers.empty())
+      throw Failure{"missing execution weight layer.0.gate_up"};
+    const auto codes_bytes = [](const Matrix &m) { return align_up(m.rows * m.cols / 2); };
+    const auto scales_bytes = [&](const Matrix &m) {
+      return align_up(m.cols / static_cast<std::uint64_t>(group_width) * m.rows * 2);
+    };
+    std::uint64_t total = 0;
+    std::uint64_t largest = 0;
+    for (const auto &layer : layers) {
+      for (const Matrix *m : {&layer.first, &layer.second}) {
+        total += codes_bytes(*m) + scales_bytes(*m);
+        largest = std::max(largest, codes_bytes(*m));
+      }
+    }
+    cudaFree(weights->int4_arena);
+    weights->int4_arena = nullptr;
+    weights->int4_layers.clear();
+    require_cuda(cudaMalloc(&weights->int4_arena, total), "allocate INT4 weight arena");
+    unsigned char *row_major = nullptr;   // the reference-layout codes, before reordering
+    require_cuda(cudaMalloc(&row_major, largest), "allocate INT4 staging");
+    std::uint64_t offset = 0;
+    int status = 0;
+    for (const auto &layer : layers) {
+      carat_b200_int4_mlp_layer out{};
+      int index = 0;
+      for (const Matrix *m : {&layer.first, &layer.second}) {
+        unsigned char *codes = weights->int4_arena + offset;
+        offset += codes_bytes(*m);
+        unsigned char *scales = weights->int4_arena + offset;
+        offset += scales_bytes(*m);
+        const void *source = weights->arena + weights->plan.segments[m->segment].arena_offset;
+        if (status == 0) {
+          status = launch_int4_quantize(source, row_major, scales, static_cast<int>(m->rows),
+                                        static_cast<int>(m->cols), group_width, nullptr);
+        }
+        if (status == 0)
+          status = launch_int4_reorder(row_major, codes, m->rows * m->cols / 2, nullptr);
+        if (index++ == 0) {
+          out.gate_up_codes = codes;
+          out.gate_up_scales = scales;
+        } else {
+          out.down_codes = codes;
+          out.down_scales = scales;
+        }
+      }
+      weights->int4_layers.push_back(out);
+    }
+    const cudaError_t finished = cudaDeviceSynchronize();
+    cudaFree(row_major);
+    if (status != 0 || finished != cudaSuccess) {
+      weights->int4_layers.clear();
+      throw Failure{"INT4 weight quantization failed"};
+    }
+    weights->int4_group_width = group_width;
+  });
+}
+
+extern "C" int carat_b200_weights_int4_mlp_layers(const carat_b200_weights *weights,
+                                                  carat_b200_int4_mlp_layer *layers, int capacity,
+                                                  int *layer_count, int *group_width) {
+  return guarded([&] {
+    if (weights == nullptr || layer_count == nullptr)
+      throw Failure{"invalid weight segment index"};
+    *layer_count = static_cast<int>(weights->int4_layers.size());
+    if (group_width != nullptr)
+      *group_width = weights->int4_group_width;
+    if (layers != nullptr) {
+      if (capacity < *layer_count)
+        throw Failure{"invalid weight segment index"};
+      std::copy(weights->int4_layers.begin(), weights->int4_layers.end(), layers);
+    }
   });
 }

@@ -278,6 +278,19 @@ class LoadedWeights:
                                              device="cuda"))
         self.bf16 = DeviceWeightArena(tensors)
 
+    def int4_mlp_layers(self, group_width: int = 128):
+        """Quantises every layer's gate_up and down matrices to weight-only INT4 on the device
+        (carat_b200_weights_quantize_int4_mlp) and returns the per-layer array that
+        carat_b200_runner_use_int4_mlp takes; the buffers belong to this object."""
+        check(self._library.carat_b200_weights_quantize_int4_mlp(self._handle, group_width))
+        count = ctypes.c_int(0)
+        check(self._library.carat_b200_weights_int4_mlp_layers(self._handle, None, 0,
+                                                               ctypes.byref(count), None))
+        layers = (capi.Int4MlpLayer * count.value)()
+        check(self._library.carat_b200_weights_int4_mlp_layers(self._handle, layers, count.value,
+                                                               ctypes.byref(count), None))
+        return layers
+
     def find(self, name: str) -> capi.WeightSegment:
         segment = capi.WeightSegment()
         check(self._library.carat_b200_weights_find(self._handle, name.encode(),
@@ -629,6 +642,13 @@ class Gemma4BatchModelRunner:
         if weights is None:
             check(self._library.carat_b200_runner_use_int4_mlp(self._handle, None, 0, 0))
             self._int4 = None
+            return
+        if isinstance(weights, LoadedWeights):
+            # The weight pipeline quantises on the device and keeps the buffers.
+            layers = weights.int4_mlp_layers(group_width)
+            check(self._library.carat_b200_runner_use_int4_mlp(self._handle, layers, len(layers),
+                                                               group_width))
+            self._int4 = (layers, weights)
             return
         hidden = self.config.hidden_size
         intermediate = self.config.intermediate_size

@@ -654,6 +654,20 @@ CARAT_B200_API int carat_b200_weights_segment(const carat_b200_weights *weights,
 /* "missing execution weight NAME" when there is no such segment (WeightPlan::at). */
 CARAT_B200_API int carat_b200_weights_find(const carat_b200_weights *weights, const char *name,
                                            carat_b200_weight_segment *segment);
+/* The weight-only INT4 form of every layer's MLP matrices, built on the device from the loaded
+ * bf16 segments "layer.N.gate_up" / "layer.N.down": codes and group scales with the reference's
+ * rule and layouts (quantize_bf16_int4_kernel, cuda/int4_bf16_linear.cu:95-136), the codes then
+ * reordered for the kernel (the place of cutlass::reorder_tensor, :268-276). group_width 128 or
+ * 256. carat_b200_weights_int4_mlp_layers copies out one entry per layer, ready for
+ * carat_b200_runner_use_int4_mlp (layers may be NULL to ask for the count only). The buffers live
+ * as long as `weights`. */
+CARAT_B200_API int carat_b200_weights_quantize_int4_mlp(carat_b200_weights *weights,
+                                                        int group_width);
+CARAT_B200_API int carat_b200_weights_int4_mlp_layers(const carat_b200_weights *weights,
+                                                      carat_b200_int4_mlp_layer *layers,
+                                                      int capacity, int *layer_count,
+                                                      int *group_width);
+
 /* The plan alone, as text, without touching a device (validate_gemma4_weights and the inspect
  * tool's view): "arena_bytes N" then one line per segment, "NAME shape .. offset N bytes N
  * sources TENSOR@OFFSET ..". *needed receives the size including the terminator; the text is

@@ -274,3 +274,71 @@ def test_load_uploads_and_quantises_like_the_oracle(cuda_device, tmp_path):
             loaded.find("layer.2.qkv")
     finally:
         loaded.close()
+
+
+@pytest.mark.gpu
+def test_int4_mlp_form_comes_out_of_the_pipeline(cuda_device, tmp_path):
+    """carat_b200_weights_quantize_int4_mlp on a loaded model (hidden 256, FFN 512, one layer):
+    the codes and scales are the bytes of the two calls a caller would otherwise make on the bf16
+    segment (quantise in the reference's layout, cuda/int4_bf16_linear.cu:95-136, then reorder),
+    and a runner takes the result as it is."""
+    hidden, inter = 256, 512
+    prefix = "model.language_model.layers.0."
+    tensors = [("model.language_model.embed_tokens.weight", "BF16", (64, hidden)),
+               ("model.language_model.norm.weight", "BF16", (hidden,)),
+               (prefix + "input_layernorm.weight", "BF16", (hidden,)),
+               (prefix + "self_attn.q_norm.weight", "BF16", (64,)),
+               (prefix + "self_attn.k_norm.weight", "BF16", (64,)),
+               (prefix + "self_attn.q_proj.weight", "BF16", (4 * 64, hidden)),
+               (prefix + "self_attn.k_proj.weight", "BF16", (2 * 64, hidden)),
+               (prefix + "self_attn.v_proj.weight", "BF16", (2 * 64, hidden)),
+               (prefix + "self_attn.o_proj.weight", "BF16", (hidden, 4 * 64)),
+               (prefix + "post_attention_layernorm.weight", "BF16", (hidden,)),
+               (prefix + "pre_feedforward_layernorm.weight", "BF16", (hidden,)),
+               (prefix + "mlp.gate_proj.weight", "BF16", (inter, hidden)),
+               (prefix + "mlp.up_proj.weight", "BF16", (inter, hidden)),
+               (prefix + "mlp.down_proj.weight", "BF16", (hidden, inter)),
+               (prefix + "post_feedforward_layernorm.weight", "BF16", (hidden,)),
+               (prefix + "layer_scalar", "BF16", (1,))]
+    generator = torch.Generator().manual_seed(3)
+    data = {name: (torch.randn(shape, generator=generator) * 0.05).to(torch.bfloat16)
+            .view(torch.int16).numpy().tobytes() for name, _, shape in tensors}
+    write_safetensors(tmp_path / "model.safetensors", tensors, data)
+    config = carat_b200.Gemma4Config(hidden, inter, 64, 128, 1e-6, [
+        carat_b200.Gemma4LayerConfig("sliding", 4, 2, 64, 1e4, False)])
+    loaded = carat_b200.LoadedWeights(str(tmp_path), config)
+    library = carat_b200.library()
+    try:
+        layers = loaded.int4_mlp_layers(128)
+        assert len(layers) == 1
+        for name, codes_pointer, scales_pointer in (
+                ("gate_up", layers[0].gate_up_codes, layers[0].gate_up_scales),
+                ("down", layers[0].down_codes, layers[0].down_scales)):
+            weight = loaded.bf16.at(f"layer.0.{name}")
+            rows, cols = weight.shape
+            packed = torch.empty(rows, cols // 2, dtype=torch.uint8, device="cuda")
+            scales = torch.empty(cols // 128, rows, dtype=torch.bfloat16, device="cuda")
+            reordered = torch.empty_like(packed)
+            capi.check(library.carat_b200_int4_quantize_weight(
+                ctypes.c_void_p(weight.data_ptr()), ctypes.c_void_p(packed.data_ptr()),
+                ctypes.c_void_p(scales.data_ptr()), rows, cols, 128, None))
+            capi.check(library.carat_b200_int4_reorder_weight(
+                ctypes.c_void_p(packed.data_ptr()), ctypes.c_void_p(reordered.data_ptr()), rows,
+                cols, None))
+            torch.cuda.synchronize()
+            got_codes = torch.as_tensor(carat_b200.runner._DeviceView(
+                codes_pointer, [rows, cols // 2], "|u1"), device="cuda")
+            got_scales = torch.as_tensor(carat_b200.runner._DeviceView(
+                scales_pointer, [cols // 128, rows], "<i2"), device="cuda")
+            assert torch.equal(got_codes, reordered), name
+            assert torch.equal(got_scales, scales.view(torch.int16)), name
+        runner = carat_b200.Gemma4BatchModelRunner(config, loaded.bf16, 2, 256, loaded.fp8)
+        runner.use_int4_mlp(loaded)
+        tokens = torch.randint(3, 64, (8,), generator=generator).tolist()
+        first = runner.prefill_slot_fp8(0, tokens, 8)
+        assert 0 <= first < 64 and runner.slot_position(0) == 8
+        runner.close()
+        with pytest.raises(carat_b200.CaratError, match="invalid BF16 INT4 linear weight shape"):
+            loaded.int4_mlp_layers(64)
+    finally:
+        loaded.close()
