@@ -282,35 +282,37 @@ def prefill(launches=6, slots=24, chunk=8, context=1024):
 
 
 def prefill_prompt(launches=3, slots=24):
-    """Whole 512-token prompts from empty slots (the rings stay unwrapped, so a step takes up to
-    256 rows: several eight-token pieces of the same prompt): one prompt alone, then `slots`
-    prompts together, on one period of the 31B layer pattern; device time summed over the steps,
-    and the same for ten periods (extrapolated)."""
+    """Whole prompts from empty slots on one period of the 31B layer pattern: a lone 512-token
+    prompt and `slots` of them together (the rings stay unwrapped: a step takes up to 256 rows,
+    many eight-token pieces of one prompt), then a lone 3,072-token prompt and four of them
+    together (past the first 1,024 tokens the sliding layers go wave by wave). Wall clock through
+    the Python mirror, best of `launches`, and the same for ten periods (extrapolated)."""
     import time
-    config, runner, weight_bytes, keep = _period_model(slots, 1024, with_assistant=False)
+    config, runner, weight_bytes, keep = _period_model(slots, 3200, with_assistant=False)
     generator = torch.Generator().manual_seed(2)
-    for count in (1, slots):
-        prompts = torch.randint(3, config.vocabulary_size, (count, 512), generator=generator).tolist()
+    for count, length in ((1, 512), (slots, 512), (1, 3072), (4, 3072)):
+        prompts = torch.randint(3, config.vocabulary_size, (count, length),
+                                generator=generator).tolist()
         best = None
         for _ in range(launches):
             for slot in range(count):
                 runner.reset_slot(slot)
             torch.cuda.synchronize()
             begin = time.perf_counter()
-            device_ms, calls = 0.0, 0
+            calls = 0
             pending = list(range(count))
             while pending:
-                done = runner.prefill_slots_chunks(pending, [prompts[slot] for slot in pending], 512)
-                device_ms += runner.last_device_ms()[0]
+                done = runner.prefill_slots_chunks(pending, [prompts[slot] for slot in pending],
+                                                   length)
                 calls += 1
                 pending = [slot for slot, first in zip(pending, done) if first is None]
             wall = (time.perf_counter() - begin) * 1e3
-            if best is None or wall < best[0]:
-                best = (wall, device_ms, calls)
-        wall, last_step_ms, calls = best
-        print(f"{count} prompt(s) of 512 tokens from empty slots: {wall:.1f} ms wall clock over 6 "
-              f"layers ({count * 512 / wall * 1e3:.0f} prompt tokens/s); x10 for 60 layers "
-              f"(extrapolated): {10 * wall:.0f} ms to the first token")
+            if best is None or wall < best:
+                best = wall
+        print(f"{count} prompt(s) of {length} tokens from empty slots: {best:.1f} ms wall clock over "
+              f"6 layers ({count * length / best * 1e3:.0f} prompt tokens/s); x10 for 60 layers "
+              f"(extrapolated): {10 * best:.0f} ms to the first token, "
+              f"{count * length / (10 * best) * 1e3:.0f} prompt tokens/s")
     runner.close()
 
 

@@ -1112,7 +1112,8 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
 // When `predict` is set the bf16 LM head runs over the step's final-normed rows and
 // predictions_out receives the argmax of every row (requests * depth).
 void prefill_step(Runner &runner, const int *tokens, int requests, int depth, const int *slots,
-                  bool linear_rings, bool predict, int *predictions_out) {
+                  bool linear_rings, const std::vector<int> &waves, bool predict,
+                  int *predictions_out) {
   const auto &config = runner.config;
   const int rows = requests * depth;
   if (requests > prefill_pieces || rows > maximum_rows)
@@ -1124,7 +1125,7 @@ void prefill_step(Runner &runner, const int *tokens, int requests, int depth, co
   for (int request = 0; request < requests; ++request) {
     const size_t slot = static_cast<size_t>(slots[request]);
     const int position = runner.slot_positions[slot] + advanced[slot];
-    if (advanced[slot] > 0 && !linear_rings)
+    if (advanced[slot] > 0 && !linear_rings && waves.size() < 2)
       throw Failure{"invalid batched chunk prefill request"};
     advanced[slot] += depth;
     for (int token = 0; token < depth; ++token)
@@ -1164,6 +1165,7 @@ void prefill_step(Runner &runner, const int *tokens, int requests, int depth, co
                                          epsilon, nullptr, 0, stream),
                  "embedding and input norm");
   runner.launches += 1;
+  int sliding_ordinal = 0;   // index of the layer in the commit table (sliding layers, in order)
   for (int index = 0; index < config.layer_count; ++index) {
     const LayerState &layer = runner.layers[static_cast<size_t>(index)];
     const LayerPlans &plan = plans.layers[static_cast<size_t>(index)];
@@ -1204,8 +1206,14 @@ void prefill_step(Runner &runner, const int *tokens, int requests, int depth, co
       post.head_stride = static_cast<long long>(depth) * shape.head_dim;
       post.slot_stride = post.head_stride * shape.kv_heads;
     }
-    require_launch(launch_qkv_post(post, stream), "QKV post-processing");
-    runner.launches += 1;
+    // Wrapped rings with several pieces of one slot in the step: the pieces of a slot have to see
+    // each other's rows through the ring, so the sliding layers go wave by wave (wave w = the w-th
+    // piece of every slot that has one): post-process, attend, commit this layer's rows, next wave.
+    const bool by_waves = !in_place && waves.size() > 1;
+    if (!by_waves) {
+      require_launch(launch_qkv_post(post, stream), "QKV post-processing");
+      runner.launches += 1;
+    }
 
     AttentionArguments attention{};
     attention.queries = runner.queries.get();
@@ -1254,10 +1262,42 @@ void prefill_step(Runner &runner, const int *tokens, int requests, int depth, co
     attention.maps = (linear_rings && !shape.global_attention)
                          ? direct_attention_maps(runner, index, depth)
                          : verify_attention_maps(runner, index, depth);
-    require_launch(attention.maps != nullptr ? launch_attention_tc(attention, stream)
-                                             : launch_attention_simt(attention, stream),
-                   "prefill attention");
-    runner.launches += attention.maps != nullptr ? attention_tc_launches(attention) : 3;
+    if (by_waves) {
+      const auto *packed_rows = runner.packed.get<unsigned char>();
+      auto *output_rows = runner.attention_out.get<unsigned char>();
+      const size_t packed_row_bytes = static_cast<size_t>(layer.packed_width()) * 2;
+      const size_t output_row_bytes = static_cast<size_t>(layer.query_width()) * 2;
+      const CommitLayer *commit_entry =
+          runner.commit_layers.get<CommitLayer>() + sliding_ordinal;
+      int base = 0;
+      for (const int count : waves) {
+        const size_t first_row = static_cast<size_t>(base) * depth;
+        post.packed = packed_rows + first_row * packed_row_bytes;
+        post.positions = device.positions + base;
+        post.slots = device.slots + base;
+        post.requests = count;
+        require_launch(launch_qkv_post(post, stream), "QKV post-processing");
+        attention.positions = device.positions + base;
+        attention.slots = device.slots + base;
+        attention.requests = count;
+        attention.output = output_rows + first_row * output_row_bytes;
+        require_launch(attention.maps != nullptr ? launch_attention_tc(attention, stream)
+                                                 : launch_attention_simt(attention, stream),
+                       "prefill attention");
+        require_launch(launch_commit(commit_entry, 1, device.positions + base, device.caps + base,
+                                     device.slots + base, count, depth, 0, stream),
+                       "KV commit");
+        runner.launches += 2 + (attention.maps != nullptr ? attention_tc_launches(attention) : 3);
+        base += count;
+      }
+    } else {
+      require_launch(attention.maps != nullptr ? launch_attention_tc(attention, stream)
+                                               : launch_attention_simt(attention, stream),
+                     "prefill attention");
+      runner.launches += attention.maps != nullptr ? attention_tc_launches(attention) : 3;
+    }
+    if (!shape.global_attention)
+      ++sliding_ordinal;
     if (attention.chunks > 1) {
       const bool counted = attention.maps != nullptr;
       require_launch(launch_quant(nullptr, runner.attention_partials.get<float>(),
@@ -1296,7 +1336,7 @@ void prefill_step(Runner &runner, const int *tokens, int requests, int depth, co
     runner.launches += 1;
     std::swap(current, other);
   }
-  if (runner.commit_layer_count > 0 && !linear_rings) {
+  if (runner.commit_layer_count > 0 && !linear_rings && waves.size() < 2) {
     require_launch(launch_commit(runner.commit_layers.get<CommitLayer>(), runner.commit_layer_count,
                                  device.positions, device.caps, device.slots, requests, depth, 0,
                                  stream),
@@ -1899,7 +1939,10 @@ extern "C" int carat_b200_runner_prefill_slots_chunks(
         active.swap(kept);
       }
       std::vector<int> pieces(active.size(), 1);
-      if (any_linear) {
+      {
+        // Past the first wrap every extra piece costs three small launches per sliding layer, so
+        // a slot takes at most `wave_limit` pieces there.
+        constexpr int wave_limit = 32;
         const int most = std::min(prefill_pieces, maximum_rows / depth);
         int total = static_cast<int>(active.size());
         for (bool grew = true; grew && total < most;) {
@@ -1908,8 +1951,9 @@ extern "C" int carat_b200_runner_prefill_slots_chunks(
             const int request = active[index];
             const int left =
                 end[static_cast<size_t>(request)] - cursor[static_cast<size_t>(request)];
-            if ((pieces[index] + 1) * depth <= left &&
-                stays_linear(request, pieces[index] + 1, depth)) {
+            const bool allowed = any_linear ? stays_linear(request, pieces[index] + 1, depth)
+                                            : pieces[index] < wave_limit;
+            if ((pieces[index] + 1) * depth <= left && allowed) {
               ++pieces[index];
               ++total;
               grew = true;
@@ -1917,24 +1961,51 @@ extern "C" int carat_b200_runner_prefill_slots_chunks(
           }
         }
       }
+      // Entry order: slot by slot while the rings are linear; wave by wave otherwise (wave w =
+      // the w-th piece of every request that has one), because a wave is one attention launch.
       std::vector<int> step_slots;
       std::vector<int> step_ids;
       std::vector<int> last_entry(active.size(), 0);
+      std::vector<int> waves;
       bool predict = false;
+      if (any_linear) {
+        for (size_t index = 0; index < active.size(); ++index) {
+          const int request = active[index];
+          const int from = cursor[static_cast<size_t>(request)];
+          const int count = pieces[index] * depth;
+          for (int piece = 0; piece < pieces[index]; ++piece)
+            step_slots.push_back(slots[request]);
+          step_ids.insert(step_ids.end(), token_ids[request] + from,
+                          token_ids[request] + from + count);
+          last_entry[index] = static_cast<int>(step_slots.size()) - 1;
+        }
+      } else {
+        const int deepest = *std::max_element(pieces.begin(), pieces.end());
+        for (int wave = 0; wave < deepest; ++wave) {
+          int members = 0;
+          for (size_t index = 0; index < active.size(); ++index) {
+            if (pieces[index] <= wave)
+              continue;
+            const int request = active[index];
+            const int from = cursor[static_cast<size_t>(request)] + wave * depth;
+            step_slots.push_back(slots[request]);
+            step_ids.insert(step_ids.end(), token_ids[request] + from,
+                            token_ids[request] + from + depth);
+            last_entry[index] = static_cast<int>(step_slots.size()) - 1;
+            ++members;
+          }
+          waves.push_back(members);
+        }
+      }
       for (size_t index = 0; index < active.size(); ++index) {
         const int request = active[index];
-        const int from = cursor[static_cast<size_t>(request)];
-        const int count = pieces[index] * depth;
-        for (int piece = 0; piece < pieces[index]; ++piece)
-          step_slots.push_back(slots[request]);
-        step_ids.insert(step_ids.end(), token_ids[request] + from, token_ids[request] + from + count);
-        last_entry[index] = static_cast<int>(step_slots.size()) - 1;
-        predict = predict || from + count == token_counts[request];
+        predict = predict || cursor[static_cast<size_t>(request)] + pieces[index] * depth ==
+                                 token_counts[request];
       }
       const int entries = static_cast<int>(step_slots.size());
       std::vector<int> step_predictions(static_cast<size_t>(entries) * depth, -1);
-      prefill_step(*runner, step_ids.data(), entries, depth, step_slots.data(), any_linear, predict,
-                   step_predictions.data());
+      prefill_step(*runner, step_ids.data(), entries, depth, step_slots.data(), any_linear, waves,
+                   predict, step_predictions.data());
       for (size_t index = 0; index < active.size(); ++index) {
         const int request = active[index];
         cursor[static_cast<size_t>(request)] += pieces[index] * depth;
