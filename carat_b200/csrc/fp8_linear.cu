@@ -142,7 +142,8 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
   constexpr uint32_t stage_bytes = weight_tile_bytes + input_tile_bytes;
   constexpr uint32_t idesc = wide ? ptx::umma_idesc(1, 1, tile_features, padded_rows)
                                   : ptx::umma_idesc(0, 0, tile_features, padded_rows);
-  constexpr uint32_t tmem_columns = 2 * padded_rows < 32 ? 32 : 2 * padded_rows;
+  // Two accumulators; tensor-memory allocations are powers of two (192 padded rows take 512).
+  constexpr uint32_t tmem_columns = 2 * padded_rows < 32 ? 32 : 2 * padded_rows > 256 ? 512 : 2 * padded_rows;
 
   extern __shared__ unsigned char shared_raw[];
   __shared__ __align__(8) unsigned long long barriers[2 * stages + 4];
@@ -740,6 +741,8 @@ int launch_rows_bucket(const LinearPlan &plan, const KernelArguments &arguments,
     return launch_variant<64, mode, wide>(plan, arguments, stream);
   case 128:
     return launch_variant<128, mode, wide>(plan, arguments, stream);
+  case 192:
+    return launch_variant<192, mode, wide>(plan, arguments, stream);
   case 256:
     return launch_variant<256, mode, wide>(plan, arguments, stream);
   default:

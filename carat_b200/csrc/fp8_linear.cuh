@@ -23,7 +23,7 @@ struct LinearPlan {
   int rows{0};
   int input_width{0};
   int output_width{0};
-  int padded_rows{0};       // UMMA N: 32, 64 or 128
+  int padded_rows{0};       // UMMA N: 32, 64, 128, 192 or 256
   int tiles{0};             // output-feature tiles of 128
   int k_blocks{0};          // 128-byte K blocks
   int ctas{0};              // persistent CTAs (multiprocessor count)

@@ -108,7 +108,7 @@ inline void schedule_linear(LinearPlan *plan, int rows, int input_width, int out
   result.input_width = input_width;
   result.output_width = output_width;
   result.element_bytes = element_bytes;
-  result.padded_rows = rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
+  result.padded_rows = rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : rows <= 192 ? 192 : 256;
   result.tiles = (output_width + tile_features - 1) / tile_features;
   result.k_blocks = (input_width * element_bytes + tile_k_elements - 1) / tile_k_elements;
   result.ctas = device_multiprocessors();
