@@ -584,10 +584,14 @@ scores_stream_kernel(const __grid_constant__ CUtensorMap key_map,
               if (column >= 0 && first_row + slot < last_row)
                 cell[static_cast<size_t>(slot) * a.score_stride] = rounded;
               const float score = visible ? __bfloat162float(rounded) : masked_score;
-              const float larger = fmaxf(maxima[slot], score);
-              sums[slot] = sums[slot] * __expf(maxima[slot] - larger) +
-                           (visible ? __expf(score - larger) : 0.0F);
-              maxima[slot] = larger;
+              // Running (maximum, sum of exp) with one exponential per score: whichever of the
+              // two terms of sum * exp(max - new_max) + exp(score - new_max) has a zero exponent
+              // is exactly 1, the other is exp(-|score - max|).
+              const float difference = score - maxima[slot];
+              const float decay = __expf(-fabsf(difference));
+              sums[slot] = difference > 0.0F ? fmaf(sums[slot], decay, 1.0F)
+                                             : sums[slot] + (visible ? decay : 0.0F);
+              maxima[slot] = fmaxf(maxima[slot], score);
             }
           }
         }
