@@ -389,7 +389,7 @@ PROCESS = textwrap.dedent("""
                      timeout=timedelta(seconds=60))
     channel = StoreChannel(store)
     if rank == 0:
-        front = Dispatcher(channel, world - 1, 3, report_timeout=1.0)
+        front = Dispatcher(channel, world - 1, 3, report_timeout=4.0)
         with open(os.environ["CARAT_REQUESTS"], "rb") as source:
             requests = pickle.load(source)
         for request in requests:
