@@ -708,9 +708,11 @@ class Gemma4BatchModelRunner:
         needed = library.carat_b200_fp8_linear_workspace_bytes(rows, width, vocabulary)
         workspace = torch.empty(max(needed, 16), dtype=torch.uint8, device="cuda")
         stream = torch.cuda.current_stream().cuda_stream
-        check(library.carat_b200_quantize_bf16_to_fp8(hidden.data_ptr(), quantised.data_ptr(),
-                                                      scale.data_ptr(), scratch.data_ptr(), rows,
-                                                      width, stream))
+        # The any-size form of the quantiser (same tensor-wide scale): more rows than the device
+        # holds row CTAs at once (k = 8: 216 rows) do not fit the one-launch form.
+        check(library.carat_b200_quantize_bf16_tensor_to_fp8(
+            hidden.data_ptr(), quantised.data_ptr(), scale.data_ptr(), scratch.data_ptr(),
+            rows * width, stream))
         check(library.carat_b200_fp8_linear(
             quantised.data_ptr(), scale.data_ptr(), fp8.at("token_embedding").data_ptr(),
             fp8.scale("token_embedding").data_ptr(), logits.data_ptr(), rows, width, vocabulary,
