@@ -1895,10 +1895,11 @@ extern "C" int carat_b200_runner_prefill_slots_chunks(
     }
     // Walk the chunks in steps. A step is a list of (request, eight-token piece) entries of one
     // common depth (rows of different entries never mix in bf16, so the grouping does not change
-    // any row). While a prompt's sliding rings are still unwrapped a request may put several
-    // consecutive pieces into one step (up to 256 rows in all): the weights then stream once per
-    // step instead of once per eight tokens. Requests past the first wrap advance one piece a
-    // step, in steps of their own.
+    // any row). A request may put several consecutive pieces into one step (up to 64 entries and
+    // 256 rows in all), so that the weights stream once per step instead of once per eight
+    // tokens: freely while its sliding rings are still unwrapped (the rings are then linear
+    // caches), up to 32 pieces past the first wrap (the sliding layers then go wave by wave, see
+    // prefill_step). The two kinds do not share a step.
     constexpr int step_tokens = 8;
     const int window = runner->config.sliding_window;
     std::vector<int> cursor = begin;
