@@ -485,8 +485,8 @@ fp8_linear_kernel(const __grid_constant__ CUtensorMap weight_map,
       }
     }
     if constexpr (mode == 3) {
-      // Grid-wide phases after the item loop. Every CTA of the launch is resident (cooperative
-      // launch, one CTA per SM) and comes here, so a counter barrier is safe; its wait is bounded
+      // Grid-wide phases after the item loop. Every CTA of the launch is resident (the grid is
+      // at most one CTA per SM) and comes here, so a counter barrier is safe; its wait is bounded
       // like every other wait of the kernel.
       const unsigned int grid = gridDim.x;
       const bool has_tail = args.tail_tiles > 0;

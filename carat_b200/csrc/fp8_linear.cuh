@@ -64,8 +64,8 @@ int make_gated_linear_plan(LinearPlan *plan, const void *fp8_input, const void *
 // fp8_output[rows, gated_width] = e4m3(activated / scale).
 // `tail_partial` (linear_tail_bytes(plan) bytes; may be null, the plan's K-cut tail is then not
 // used) holds the pieces of the tail tiles between the kernel's phases. `grid_counter` is one word
-// that is zero on entry and zero again on return; the kernel's grid-wide barriers count on it,
-// which is why the launch is cooperative (every CTA resident: one per SM).
+// that is zero on entry and zero again on return; the kernel's grid-wide barriers count on it.
+// The grid is one CTA per SM at most, so every CTA is resident; the waits are bounded.
 int launch_linear_gated(const LinearPlan &plan, const float *input_scale,
                         const float *weight_scale, void *bf16_activated, unsigned int *amax_bits,
                         void *fp8_output, float *scale_out, float *tail_partial,

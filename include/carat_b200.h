@@ -98,8 +98,8 @@ CARAT_B200_API int carat_b200_fp8_linear_static(const void *fp8_input,
  * operation gives. *device_amax_bits receives the float bits of the largest |activated|. When
  * fp8_output is not NULL the same launch also quantises the rows for the down projection:
  * *device_output_scale = max / 448 (1 when 0), fp8_output[rows, gated_width] = e4m3(x / scale).
- * gated_width must be a multiple of 64. One cooperative launch (its phases meet at grid-wide
- * barriers with bounded waits). workspace: carat_b200_fp8_linear_geglu_workspace_bytes() bytes. */
+ * gated_width must be a multiple of 64. One launch of at most one CTA per SM (its phases meet at
+ * grid-wide barriers with bounded waits). workspace: carat_b200_fp8_linear_geglu_workspace_bytes() bytes. */
 CARAT_B200_API size_t carat_b200_fp8_linear_geglu_workspace_bytes(int rows, int input_width,
                                                                   int gated_width);
 CARAT_B200_API int carat_b200_fp8_linear_geglu(const void *fp8_input,
