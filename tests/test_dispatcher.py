@@ -463,3 +463,31 @@ def test_router_and_replicas_as_processes_over_a_store(tmp_path, leaver):
         moved = [placements for placements in result["placements"].values() if len(placements) > 1]
         assert moved and all(placements[0][0] == leaver and placements[-1][0] != leaver
                              for placements in moved)
+
+
+def test_a_stale_prefix_decision_falls_back_to_a_fresh_prefill():
+    """The router decides on its mirror of a replica's table; a source slot that was decoding has
+    moved on by the time the replica admits the request. Its cache then no longer is the prefix
+    the router saw, and the request must prefill from an empty slot instead of cloning it."""
+    runner = StandInRunner(3)
+    scheduler = ReplicaScheduler(runner, 3, depth=4)
+    first = Request(1, [5, 6, 7, 8], 40)
+    scheduler.admit(first, 0, None, 0)
+    scheduler.tick()                                   # prefill + first decode step
+    seen = list(scheduler.slots[0].cached_tokens)      # what a router would have mirrored
+    for _ in range(3):
+        scheduler.tick()                               # ... and the slot decodes on
+    assert len(scheduler.slots[0].cached_tokens) > len(seen)
+    follower = Request(2, seen + [9, 9], 6)
+    scheduler.admit(follower, 1, 0, len(seen))         # the router's (stale) decision: clone slot 0
+    assert scheduler.metrics["stale_prefix_fallbacks"] == 1
+    assert scheduler.metrics["kv_clones"] == 0
+    outputs = {1: [], 2: []}
+    for _ in range(60):
+        emitted, _ = scheduler.tick()
+        for request_id, tokens in emitted.items():
+            outputs[request_id] += tokens
+        if scheduler.idle():
+            break
+    assert outputs[2] == greedy_stream(follower.input_ids, 6)
+    assert runner.calls["clone"] == 0
