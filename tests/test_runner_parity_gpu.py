@@ -398,3 +398,51 @@ def test_free_running_generation_on_the_plumbing_case(cuda_device):
     assert accepted_total > steps           # whole look-ahead blocks were accepted
     assert flagged <= 12
     device.close()
+
+
+def test_ring_wraps_during_the_step(cuda_device):
+    """Slots a few tokens below the window whose verify rows run past it (positions 124..127 with
+    a window of 128 and depth 5): every query still sees exactly the model's window, the rule
+    this build applies uniformly (the reference does so too except for a cohort of slots that
+    all stand at one and the same such position, where its staged path sees a few keys more).
+    Checked against the oracle, which applies the window everywhere."""
+    config = cs.tiny_config(512)
+    assistant = cs.tiny_assistant()
+    oracle, device, _ = build_pair(config, cs.golden_tiny_weights(config), 4, assistant,
+                                   cs.random_assistant_weights(config, assistant, 1))
+    depth = 5
+    lengths = [124, 125, 126, 127]
+    texts = [prompts(config, 1, length, seed=40 + index)[0] for index, length in enumerate(lengths)]
+    firsts = []
+    for slot, text in enumerate(texts):
+        for start in range(0, len(text), 8):
+            part = text[start:start + 8]
+            got = device.prefill_slot_fp8(slot, part, 8)
+            _, nxt = oracle.verify_greedy_proposals([part], [part[0]], [slot], assume_match=True,
+                                                    allow_empty_slot=True)
+        firsts.append(nxt[0])
+        assert device.slot_position(slot) == oracle.positions[slot] == lengths[slot]
+    slots = [0, 1, 2, 3]
+    generator = torch.Generator().manual_seed(77)
+    flagged = 0
+    for step in range(3):       # the first step crosses the wrap, the next ones run past it
+        proposals = [[firsts[row]] + torch.randint(3, config.vocab, (depth - 1,),
+                                                   generator=generator).tolist()
+                     for row in range(4)]
+        caps = [depth, 3, depth, 2]
+        result, trace, step_flags, _ = forced_step(oracle, device, proposals, firsts, slots, caps, 1)
+        flagged += step_flags
+        hidden = device.last_final_hidden(4 * depth)
+        assert rms_relative_error(hidden, trace.final_hidden) < TOLERANCE
+        assert cosine(hidden, trace.final_hidden) > 0.99
+        firsts = list(result.next_tokens)
+        for slot in slots:
+            assert device.slot_position(slot) == oracle.positions[slot]
+    for index, layer in enumerate(config.layers):
+        capacity = config.capacity(index)
+        assert rms_relative_error(device.key_cache(index, capacity), oracle.keys[index]) < TOLERANCE
+        assert rms_relative_error(device.value_cache(index, capacity),
+                                  oracle.values[index]) < TOLERANCE
+    print(f"flagged near-tie rows: {flagged}")
+    assert flagged <= 8
+    device.close()
