@@ -316,6 +316,42 @@ def prefill_prompt(launches=3, slots=24):
     runner.close()
 
 
+def single(launches=1, slots=24):
+    """One request alone, as the batch-1 configuration describes it: a 512-token prompt, k = 4,
+    256 new tokens with real greedy acceptance, through the scheduler loop (BF16 prefill, then
+    draft -> verify -> commit), on one period of the 31B layer pattern with the real drafter.
+    Prints the time to the first token and the decode rate of this 6-layer model."""
+    import random
+    import time
+    from carat_b200.dispatcher import ReplicaScheduler, Request
+    config, runner, _, keep = _period_model(slots, 1024, with_assistant=True)
+    generator = random.Random(5)
+    for attempt in range(launches + 1):                # the first pass warms plans and maps up
+        for slot in range(slots):
+            runner.reset_slot(slot)
+        scheduler = ReplicaScheduler(runner, slots, depth=5, chunk_tokens=512)
+        prompt = [generator.randrange(3, config.vocabulary_size) for _ in range(512)]
+        scheduler.admit(Request(attempt, prompt, 256), 0, None, 0)
+        torch.cuda.synchronize()
+        begin = time.perf_counter()
+        first_token_at = None
+        emitted = 0
+        while not scheduler.idle():
+            tokens, _ = scheduler.tick()
+            emitted += sum(len(row) for row in tokens.values())
+            if first_token_at is None and emitted > 0:
+                first_token_at = time.perf_counter() - begin
+        total = time.perf_counter() - begin
+    metrics = scheduler.metrics
+    print(f"one request, prompt 512, 256 new tokens, k = 4 on a 6-layer 31B-width replica: first "
+          f"token after {first_token_at * 1e3:.1f} ms, {emitted} tokens in {total * 1e3:.0f} ms "
+          f"({(emitted - 1) / (total - first_token_at):.0f} tokens/s after the first), "
+          f"{metrics['speculative_cycles']} speculative cycles, {metrics['accepted_tokens']} rows "
+          f"accepted of {metrics['proposed_tokens']} proposed")
+    assert emitted == 256 and runner.slot_position(0) == len(scheduler.slots[0].cached_tokens)
+    runner.close()
+
+
 def serving(launches=72, slots=24):
     """A request mix through the dispatcher and one replica's scheduler loop on one period of the
     31B layer pattern with the real drafter: `launches` requests, prompts of 128..1536 tokens of
@@ -390,7 +426,7 @@ def serving(launches=72, slots=24):
     runner.close()
 
 
-CASES = {"prefill": prefill, "prefill_prompt": prefill_prompt, "serving": serving, "linear": linear, "gated": gated, "int4": int4, "lm_head": lm_head, "attention": attention, "global": global_attention,
+CASES = {"prefill": prefill, "prefill_prompt": prefill_prompt, "single": single, "serving": serving, "linear": linear, "gated": gated, "int4": int4, "lm_head": lm_head, "attention": attention, "global": global_attention,
          "global_ragged": global_ragged}
 
 
