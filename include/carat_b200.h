@@ -75,7 +75,7 @@ CARAT_B200_API size_t carat_b200_fp8_linear_workspace_bytes(int rows, int input_
  *  - The first call on each device looks the array's device address up, and the first call of
  *    each shape class (row bucket 32 / 64 / 128 / 192 / 256, with or without split-K) configures its
  *    kernel; under lazy module loading the very first call also makes the driver load the module
- *    that holds the 8 MiB. Make those first calls during set-up, before any stream capture.
+ *    that holds the 8 MiB. Make those first calls during set-up.
  *  - All calls on a device share the one array: calls that overlap on the GPU (different streams,
  *    no dependency) race on it. Nothing in it has to be zero between calls; every launch
  *    overwrites the part it reads. Every GPU that loads the library holds the array until exit.
