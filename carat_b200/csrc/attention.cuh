@@ -64,6 +64,10 @@ struct AttentionArguments {
                              // otherwise the consumer of `chunk_partials` does the sum
   int draft;                 // 1: drafter semantics (depth == 1, no proposal rows, the first
                              //    min(position + 1, capacity) cache rows are visible)
+  // Optional, one-kernel path only (attention_fused_applies): a word, zero on entry, that receives
+  // the float bits of the largest |output| as written (bf16-rounded), so that the quantiser for
+  // the o projection needs no pass of its own over the rows to find it.
+  unsigned int *amax_bits;
 };
 
 // Plain CUDA-core implementation of the three phases. It is the bring-up path and the on-device

@@ -644,18 +644,27 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
         const int component = half * 128 + thread;
         int token = 0;
         int local_head = 0;
+        float largest = 0.0F;
 #pragma unroll
         for (int row = 0; row < fused_rows; ++row) {
           if (row < rows) {
             const size_t out_row = static_cast<size_t>(item.request) * a.depth + token;
             const size_t column =
                 static_cast<size_t>(item.kv_head * group + local_head) * fused_dimension + component;
-            output[out_row * width + column] = __float2bfloat16_rn(__uint_as_float(values[row]));
+            const __nv_bfloat16 rounded = __float2bfloat16_rn(__uint_as_float(values[row]));
+            output[out_row * width + column] = rounded;
+            largest = fmaxf(largest, fabsf(__bfloat162float(rounded)));
             if (++token == a.depth) {
               token = 0;
               ++local_head;
             }
           }
+        }
+        if (a.amax_bits != nullptr) {
+          // Non-negative floats order like their bit patterns.
+          const unsigned int bits = __reduce_max_sync(0xFFFFFFFFU, __float_as_uint(largest));
+          if (lane == 0)
+            atomicMax(a.amax_bits, bits);
         }
         ptx::tcgen05_fence_before_thread_sync();
       }

@@ -198,6 +198,9 @@ struct carat_b200_runner {
   DeviceBuffer grid_counter;   // barrier word of the gated linear; zero between launches
   bool fused_geglu{false};
   bool cooperative_rows{false};   // CARAT_B200_COOPERATIVE_ROWS=1: row kernels as cooperative launches
+  bool attention_amax{true};      // the one-kernel attention also finds the largest |output|, so
+                                  // the quantiser after it is one pass without a grid barrier
+                                  // (CARAT_B200_ATTENTION_AMAX=0: the row kernel finds it)
   DeviceBuffer unit_scale;   // one fp32 1.0: INT4 partial sums carry no tensor scales
   std::map<std::pair<int, int>, AttentionMaps> verify_maps;  // (layer, depth)
   std::map<int, AttentionMaps> draft_maps;                   // assistant layer
@@ -391,6 +394,8 @@ void build_runner(Runner &runner, const carat_b200_model_config &config,
   runner.fused_geglu = config.intermediate_size % 64 == 0 && fused != nullptr && fused[0] == '1';
   const char *cooperative = std::getenv("CARAT_B200_COOPERATIVE_ROWS");
   runner.cooperative_rows = cooperative != nullptr && cooperative[0] == '1';
+  const char *attention_amax = std::getenv("CARAT_B200_ATTENTION_AMAX");
+  runner.attention_amax = attention_amax == nullptr || attention_amax[0] != '0';
   runner.gated_rows.allocate(static_cast<size_t>(rows) * config.intermediate_size * 2);
   runner.grid_counter.allocate(256, true);
   // Split-K partials [splits, rows, features] fp32; plans that would need more are rejected.
@@ -907,6 +912,11 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
     attention.stats_stride = runner.stats_stride;
     attention.request_chunks = runner.request_chunks.get<int>();
     attention.maps = verify_attention_maps(runner, index, depth);
+    // The one-kernel attention leaves the largest |output| in the quantiser's (still zero) word.
+    const bool amax_known = runner.attention_amax && attention.maps != nullptr &&
+                            attention_tc_launches(attention) == 1;
+    if (amax_known)
+      attention.amax_bits = target(word + 1).amax_bits;
     require_launch(attention.maps != nullptr ? launch_attention_tc(attention, stream)
                                              : launch_attention_simt(attention, stream),
                    "verify attention");
@@ -914,13 +924,19 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
 
     // The tensor-core path writes only the chunks a request has rows in and says how many.
     const bool counted = attention.chunks > 1 && attention.maps != nullptr;
-    require_launch(launch_quant(attention.chunks > 1 ? nullptr : runner.attention_out.get(),
-                                attention.chunks > 1 ? runner.attention_partials.get<float>()
-                                                     : nullptr,
-                                attention.chunks,
-                                counted ? runner.request_chunks.get<int>() : nullptr, depth,
-                                target(word + 1), rows, layer.query_width(), stream),
-                   "attention output quantisation");
+    if (amax_known) {
+      require_launch(launch_quantize_rows(runner.attention_out.get(), target(word + 1),
+                                          static_cast<size_t>(rows) * layer.query_width(), stream),
+                     "attention output quantisation");
+    } else {
+      require_launch(launch_quant(attention.chunks > 1 ? nullptr : runner.attention_out.get(),
+                                  attention.chunks > 1 ? runner.attention_partials.get<float>()
+                                                       : nullptr,
+                                  attention.chunks,
+                                  counted ? runner.request_chunks.get<int>() : nullptr, depth,
+                                  target(word + 1), rows, layer.query_width(), stream),
+                     "attention output quantisation");
+    }
     runner.launches += 1;
 
     const PartialSource o_source = run_linear(runner, plan.o, scales + word + 1, w.o_scale,
@@ -1504,18 +1520,28 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
       attention.stats_stride = runner.stats_stride;
       attention.request_chunks = runner.request_chunks.get<int>();
       attention.maps = draft_attention_maps(runner, index);
+      const bool amax_known = runner.attention_amax && attention.maps != nullptr &&
+                              attention_tc_launches(attention) == 1;
+      if (amax_known)
+        attention.amax_bits = target(word).amax_bits;
       require_launch(attention.maps != nullptr ? launch_attention_tc(attention, stream)
                                                : launch_attention_simt(attention, stream),
                      "assistant attention");
       runner.launches += attention.maps != nullptr ? attention_tc_launches(attention) : 3;
       const bool counted = attention.chunks > 1 && attention.maps != nullptr;
-      require_launch(launch_quant(attention.chunks > 1 ? nullptr : runner.a_attention_out.get(),
-                                  attention.chunks > 1 ? runner.a_attention_partials.get<float>()
-                                                       : nullptr,
-                                  attention.chunks,
-                                  counted ? runner.request_chunks.get<int>() : nullptr, 1,
-                                  target(word), requests, query_width, stream),
-                     "assistant attention quantisation");
+      if (amax_known) {
+        require_launch(launch_quantize_rows(runner.a_attention_out.get(), target(word),
+                                            static_cast<size_t>(requests) * query_width, stream),
+                       "assistant attention quantisation");
+      } else {
+        require_launch(launch_quant(attention.chunks > 1 ? nullptr : runner.a_attention_out.get(),
+                                    attention.chunks > 1 ? runner.a_attention_partials.get<float>()
+                                                         : nullptr,
+                                    attention.chunks,
+                                    counted ? runner.request_chunks.get<int>() : nullptr, 1,
+                                    target(word), requests, query_width, stream),
+                       "assistant attention quantisation");
+      }
       runner.launches += 1;
       const PartialSource o_source = run_linear(runner, plan.o, scales + word, w.o_scale,
                                                 runner.a_linear_out.get(), true);
