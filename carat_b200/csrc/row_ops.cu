@@ -4,6 +4,7 @@
 #include "launch.cuh"
 
 #include <cooperative_groups.h>
+#include <cstdint>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
@@ -474,31 +475,36 @@ row_kernel(RowArguments a) {
     }
     return;
   }
+  float tensor_amax = 0.0F;
   if (a.barrier_word != nullptr) {
     // Every CTA of the grid is resident (the launcher checked the grid against the device's
     // capacity, and the grid that follows in the chain cannot start before all of these CTAs
-    // have), so counting them in is a barrier: gridDim.x arrivals open it, gridDim.x more (one
-    // per CTA on its way out) wrap the word back to zero for the next launch.
-    __threadfence();
-    __syncthreads();
+    // have), so counting them in is a barrier. The count sits in the word after the maximum
+    // (both zero on entry, eight-byte aligned as a pair): one thread a CTA publishes the CTA's
+    // maximum, counts the CTA in, and polls both words with one load, so the value it sees with
+    // the full count already holds every CTA's maximum. Nothing else crosses the barrier.
     if (threadIdx.x == 0U) {
-      atomicInc(a.barrier_word, 2U * gridDim.x - 1U);
+      __threadfence();   // the atomicMax above is performed before the arrival below
+      atomicAdd(a.barrier_word, 1U);
+      const auto *pair = reinterpret_cast<volatile unsigned long long *>(a.amax_bits);
       const long long start = clock64();
-      while (*reinterpret_cast<volatile unsigned int *>(a.barrier_word) < gridDim.x) {
+      unsigned long long seen = *pair;
+      while (static_cast<unsigned int>(seen >> 32) < gridDim.x) {
         if (clock64() - start > 4000000000LL) {   // about two seconds: give up, say so
           if (a.barrier_error != nullptr)
             atomicExch(a.barrier_error, 7);
           break;
         }
+        seen = *pair;
       }
-      atomicInc(a.barrier_word, 2U * gridDim.x - 1U);
-      __threadfence();
+      scratch[parity * row_warps] = __uint_as_float(static_cast<unsigned int>(seen));
     }
     __syncthreads();
+    tensor_amax = scratch[parity * row_warps];
   } else {
     cg::this_grid().sync();
+    tensor_amax = __uint_as_float(*reinterpret_cast<volatile unsigned int *>(a.amax_bits));
   }
-  const float tensor_amax = __uint_as_float(*reinterpret_cast<volatile unsigned int *>(a.amax_bits));
   const float scale = tensor_amax > 0.0F ? tensor_amax / 448.0F : 1.0F;
   const float inverse_scale = 1.0F / scale;
   if (blockIdx.x == 0U && threadIdx.x == 0U)
@@ -607,6 +613,12 @@ template <RowMode mode> int launch_rows(RowArguments arguments, int rows, cudaSt
                          (arguments.second_out != nullptr || arguments.first_out != nullptr);
   if (rows <= 0 || arguments.width <= 0 || arguments.width % 8 != 0 || !(quantised || bf16_only))
     return -1;
+  // The barrier count is read together with the maximum: one aligned eight-byte pair.
+  if (arguments.barrier_word != nullptr &&
+      (arguments.barrier_word != arguments.amax_bits + 1 ||
+       reinterpret_cast<uintptr_t>(arguments.amax_bits) % 8 != 0)) {
+    return -1;
+  }
   int parts = 1;
   if constexpr (mode == RowMode::geglu) {
     // Wide rows: two CTAs a row when the halves stay multiples of eight columns and the grid

@@ -24,7 +24,10 @@ struct QuantTarget {
   // When fp8_output is null the call stops after the bf16 row: it is stored here and nothing is
   // quantised (the consumer is a linear with bf16 activations; scale and amax_bits are unused).
   void *bf16_output = nullptr;
-  // Optional word (zero between launches) for the one-launch form's grid barrier. With it the
+  // Optional word for the one-launch form's grid barrier: it must be the word right after
+  // `amax_bits`, the pair eight-byte aligned and zero on entry (the kernel reads both with one
+  // load; the count stays in the word afterwards, so the caller clears the pair before its next
+  // use). With it the
   // kernel counts its CTAs in on this word and is launched as an ordinary kernel; without it the
   // launch is cooperative and uses the cooperative-groups grid barrier. The difference matters in
   // a chain: a cooperative launch does not overlap with its neighbours under programmatic

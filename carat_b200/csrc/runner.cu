@@ -400,7 +400,8 @@ void build_runner(Runner &runner, const carat_b200_model_config &config,
   runner.grid_counter.allocate(256, true);
   // Split-K partials [splits, rows, features] fp32; plans that would need more are rejected.
   runner.split_partials.allocate(static_cast<size_t>(16) * rows * std::max(hidden, 4096) * 4);
-  runner.amax_words = (config.layer_count + 1) * 4;
+  // One (maximum, barrier count) pair of words per quantisation of a step.
+  runner.amax_words = (config.layer_count + 1) * 4 * 2;
   runner.scratch_words.allocate(static_cast<size_t>(runner.amax_words + 2 * rows) * 4, true);
   runner.scales.allocate(static_cast<size_t>(runner.amax_words) * 4, true);
   runner.step_inputs.allocate(sizeof(int) * (rows + 4 * batch), true);
@@ -458,7 +459,7 @@ void build_runner(Runner &runner, const carat_b200_model_config &config,
                              runner.score_stride_global * 2);
     runner.a_gate_up.allocate(static_cast<size_t>(batch) * 2 * assistant->intermediate_size * 2);
     runner.a_previous_hidden.allocate(static_cast<size_t>(batch) * hidden * 2);
-    runner.a_amax_words = 2 + 4 * assistant->layer_count;
+    runner.a_amax_words = (2 + 4 * assistant->layer_count) * 2;
     runner.a_scratch_words.allocate(static_cast<size_t>(runner.a_amax_words + 2 * batch) * 4, true);
     runner.a_scales.allocate(static_cast<size_t>(runner.a_amax_words) * 4, true);
     runner.a_concat.allocate(static_cast<size_t>(batch) * 2 * hidden * 2);
@@ -805,10 +806,10 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
   auto *best = reinterpret_cast<unsigned long long *>(amax + runner.amax_words);
   auto *scales = runner.scales.get<float>();
   const auto target = [&](int word) {
-    QuantTarget made{runner.quantized.get(), scales + word, amax + word,
+    QuantTarget made{runner.quantized.get(), scales + word, amax + 2 * word,
                      runner.two_launch_rows.get()};
     if (!runner.cooperative_rows) {
-      made.barrier_word = runner.grid_counter.get<unsigned int>() + 16;
+      made.barrier_word = amax + 2 * word + 1;
       made.barrier_error = runner.device_error;
     }
     return made;
@@ -1444,9 +1445,9 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
   auto *best = reinterpret_cast<unsigned long long *>(amax + runner.a_amax_words);
   auto *scales = runner.a_scales.get<float>();
   const auto target = [&](int word) {
-    QuantTarget made{runner.a_quantized.get(), scales + word, amax + word};
+    QuantTarget made{runner.a_quantized.get(), scales + word, amax + 2 * word};
     if (!runner.cooperative_rows) {
-      made.barrier_word = runner.grid_counter.get<unsigned int>() + 16;
+      made.barrier_word = amax + 2 * word + 1;
       made.barrier_error = runner.device_error;
     }
     return made;
