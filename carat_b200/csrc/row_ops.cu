@@ -149,52 +149,67 @@ __device__ __forceinline__ Pack8 round_bf16x8(const Pack8 &values, uint4 *packed
   return rounded;
 }
 
-// Loads eight values of the row's primary source: a bf16 tensor, or split-K / key-chunk partials
-// summed in a fixed order, scaled and rounded to bf16 exactly like a separate finishing kernel.
-__device__ __forceinline__ Pack8 load_source(const RowArguments &a, size_t row, int column,
-                                             size_t rows, float partial_scale) {
-  if (a.splits <= 0)
-    return load_bf16x8(a.input + row * a.width + column);
-  Pack8 sum;
+// Loads a thread's `chunks` groups of eight values of the row's primary source: a bf16 tensor, or
+// split-K / key-chunk partials summed in a fixed order (piece 0 first), scaled and rounded to bf16
+// exactly like a separate finishing kernel. The loads of all groups are issued together, a few
+// pieces at a time (as many as the registers hold): a loop that loads and adds group by group, or
+// piece by piece, pays one L2 round trip per turn.
+template <int chunks>
+__device__ __forceinline__ void load_source(const RowArguments &a, size_t row, int column_base,
+                                            int column_end, size_t rows, float partial_scale,
+                                            Pack8 (&values)[chunks]) {
+  if (a.splits <= 0) {
 #pragma unroll
-  for (int index = 0; index < 8; ++index)
-    sum.v[index] = 0.0F;
-  // Four pieces at a time, all loads before the first add: a loop that loads and adds piece by
-  // piece pays one L2 round trip per piece.
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+      const int column = column_base + (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+      if (column < column_end)
+        values[chunk] = load_bf16x8(a.input + row * a.width + column);
+    }
+    return;
+  }
+  constexpr int batch = chunks <= 2 ? 4 : chunks <= 4 ? 2 : 1;
   int pieces = a.splits;
   if (a.valid_splits != nullptr)
     pieces = min(pieces, a.valid_splits[row / a.rows_per_group]);
-  for (int first = 0; first < pieces; first += 4) {
-    float4 low[4];
-    float4 high[4];
+  for (int first = 0; first < pieces; first += batch) {
+    float4 low[chunks][batch];
+    float4 high[chunks][batch];
 #pragma unroll
-    for (int offset = 0; offset < 4; ++offset) {
-      low[offset] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-      high[offset] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-      if (first + offset < pieces) {
-        const float *source =
-            a.partial + (static_cast<size_t>(first + offset) * rows + row) * a.width + column;
-        low[offset] = *reinterpret_cast<const float4 *>(source);
-        high[offset] = *reinterpret_cast<const float4 *>(source + 4);
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+      const int column = column_base + (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+#pragma unroll
+      for (int offset = 0; offset < batch; ++offset) {
+        low[chunk][offset] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+        high[chunk][offset] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+        if (column < column_end && first + offset < pieces) {
+          const float *source =
+              a.partial + (static_cast<size_t>(first + offset) * rows + row) * a.width + column;
+          low[chunk][offset] = *reinterpret_cast<const float4 *>(source);
+          high[chunk][offset] = *reinterpret_cast<const float4 *>(source + 4);
+        }
       }
     }
 #pragma unroll
-    for (int offset = 0; offset < 4; ++offset) {
-      sum.v[0] += low[offset].x;
-      sum.v[1] += low[offset].y;
-      sum.v[2] += low[offset].z;
-      sum.v[3] += low[offset].w;
-      sum.v[4] += high[offset].x;
-      sum.v[5] += high[offset].y;
-      sum.v[6] += high[offset].z;
-      sum.v[7] += high[offset].w;
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+#pragma unroll
+      for (int offset = 0; offset < batch; ++offset) {
+        values[chunk].v[0] += low[chunk][offset].x;
+        values[chunk].v[1] += low[chunk][offset].y;
+        values[chunk].v[2] += low[chunk][offset].z;
+        values[chunk].v[3] += low[chunk][offset].w;
+        values[chunk].v[4] += high[chunk][offset].x;
+        values[chunk].v[5] += high[chunk][offset].y;
+        values[chunk].v[6] += high[chunk][offset].z;
+        values[chunk].v[7] += high[chunk][offset].w;
+      }
     }
   }
-  Pack8 rounded;
 #pragma unroll
-  for (int index = 0; index < 8; ++index)
-    rounded.v[index] = __bfloat162float(__float2bfloat16_rn(sum.v[index] * partial_scale));
-  return rounded;
+  for (int chunk = 0; chunk < chunks; ++chunk)
+#pragma unroll
+    for (int index = 0; index < 8; ++index)
+      values[chunk].v[index] =
+          __bfloat162float(__float2bfloat16_rn(values[chunk].v[index] * partial_scale));
 }
 
 // Every thread owns `chunks` groups of eight consecutive columns, group c at column
@@ -258,62 +273,74 @@ row_kernel(RowArguments a) {
   if (a.splits > 0 && a.input_scale != nullptr)
     partial_scale = a.input_scale[0] * a.weight_scale[0];
 
-  // ---- load: the bf16-exact starting row (and the residual) into registers
+  // ---- load: the bf16-exact starting row (and the residual) into registers. No store happens
+  // before the last load of this phase has been issued (a store could alias a later load as far
+  // as the compiler knows, and would then hold that load back by a round trip to memory); the
+  // rows some modes keep in bf16 are stored by the loop after it.
   Pack8 values[chunks];
   uint4 residual_raw[chunks];
 #pragma unroll
   for (int chunk = 0; chunk < chunks; ++chunk) {
-    const int column = column_base + (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
     residual_raw[chunk] = make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int index = 0; index < 8; ++index)
       values[chunk].v[index] = 0.0F;
-    if (column >= column_end)
-      continue;
-    if constexpr (mode == RowMode::embed_norm) {
-      const int token = a.tokens[row];
-      const float scale = __bfloat162float(__float2bfloat16_rn(sqrtf(width_value)));
-      Pack8 raw = values[chunk];
-      if (token >= 0 && token < a.vocabulary)
-        raw = load_bf16x8(a.embedding + static_cast<size_t>(token) * width + column);
+  }
+  constexpr bool from_source = mode == RowMode::norm || mode == RowMode::plain || two_norms;
+  if constexpr (from_source) {
+    if constexpr (two_norms) {
 #pragma unroll
-      for (int index = 0; index < 8; ++index)
-        raw.v[index] *= scale;
-      uint4 packed;
-      values[chunk] = round_bf16x8(raw, &packed);
-      *reinterpret_cast<uint4 *>(a.first_out + row * width + column) = packed;
-    } else if constexpr (mode == RowMode::embed_concat) {
-      // `width` is the concatenated width: scaled embedding row, then the carried hidden state.
-      const int half = width / 2;
-      if (column < half) {
-        const int token = a.tokens[row];
-        const float scale =
-            __bfloat162float(__float2bfloat16_rn(sqrtf(static_cast<float>(half))));
+      for (int chunk = 0; chunk < chunks; ++chunk) {
+        const int column = column_base + (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+        if (column < column_end)
+          residual_raw[chunk] = *reinterpret_cast<const uint4 *>(a.residual + row * width + column);
+      }
+    }
+    load_source<chunks>(a, row, column_base, column_end, rows, partial_scale, values);
+  } else if constexpr (mode == RowMode::embed_norm || mode == RowMode::embed_concat) {
+    // embed_concat: `width` is the concatenated width, scaled embedding row then the carried
+    // hidden state.
+    const int embedded = mode == RowMode::embed_norm ? width : width / 2;
+    const int token = a.tokens[row];
+    const float scale =
+        __bfloat162float(__float2bfloat16_rn(sqrtf(static_cast<float>(embedded))));
+    size_t source_row = row;
+    if constexpr (mode == RowMode::embed_concat) {
+      if (a.row_indices != nullptr)
+        source_row = static_cast<size_t>(a.row_indices[row]);
+    }
+#pragma unroll
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+      const int column = column_base + (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+      if (column >= column_end)
+        continue;
+      if (column < embedded) {
         Pack8 raw = values[chunk];
         if (token >= 0 && token < a.vocabulary)
-          raw = load_bf16x8(a.embedding + static_cast<size_t>(token) * half + column);
+          raw = load_bf16x8(a.embedding + static_cast<size_t>(token) * embedded + column);
 #pragma unroll
         for (int index = 0; index < 8; ++index)
           raw.v[index] *= scale;
         uint4 packed;
         values[chunk] = round_bf16x8(raw, &packed);
       } else {
-        const size_t source_row =
-            a.row_indices != nullptr ? static_cast<size_t>(a.row_indices[row]) : row;
-        values[chunk] = load_bf16x8(a.input + source_row * half + (column - half));
+        values[chunk] = load_bf16x8(a.input + source_row * embedded + (column - embedded));
       }
-      if (a.second_out != nullptr) {   // bf16 consumer: keep the concatenated row
-        uint4 packed;
-        (void)round_bf16x8(values[chunk], &packed);
-        *reinterpret_cast<uint4 *>(a.second_out + row * width + column) = packed;
-      }
-    } else if constexpr (mode == RowMode::geglu) {
-      const __nv_bfloat16 *packed_row = a.input + row * 2 * width;
+    }
+  } else {   // GeGLU
+    const __nv_bfloat16 *packed_row = a.input + row * 2 * width;
+    float tail_scale = 1.0F;
+    if (a.tail_partial != nullptr)
+      tail_scale = a.input_scale[0] * a.weight_scale[0];
+#pragma unroll
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+      const int column = column_base + (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+      if (column >= column_end)
+        continue;
       const Pack8 gate = load_bf16x8(packed_row + column);
       Pack8 up;
       if (a.tail_partial != nullptr && width + column >= a.tail_first_column) {
         // Same finish as the linear's own epilogue: sum of the pieces, scaled, rounded to bf16.
-        const float tail_scale = a.input_scale[0] * a.weight_scale[0];
         Pack8 sum;
 #pragma unroll
         for (int index = 0; index < 8; ++index)
@@ -360,20 +387,26 @@ row_kernel(RowArguments a) {
         product.v[index] = gelu_tanh(gate.v[index]) * up.v[index];
       uint4 packed;
       values[chunk] = round_bf16x8(product, &packed);
-      if (a.second_out != nullptr)
-        *reinterpret_cast<uint4 *>(a.second_out + row * width + column) = packed;
-    } else {
-      values[chunk] = load_source(a, row, column, rows, partial_scale);
-      if constexpr (mode == RowMode::plain) {
-        __nv_bfloat16 *rows_out = a.first_out != nullptr ? a.first_out : a.second_out;
-        if (rows_out != nullptr) {
-          uint4 packed;
-          (void)round_bf16x8(values[chunk], &packed);
-          *reinterpret_cast<uint4 *>(rows_out + row * width + column) = packed;
-        }
+    }
+  }
+  {
+    __nv_bfloat16 *rows_out = nullptr;
+    if constexpr (mode == RowMode::embed_norm)
+      rows_out = a.first_out;
+    else if constexpr (mode == RowMode::embed_concat || mode == RowMode::geglu)
+      rows_out = a.second_out;
+    else if constexpr (mode == RowMode::plain)
+      rows_out = a.first_out != nullptr ? a.first_out : a.second_out;
+    if (rows_out != nullptr) {
+#pragma unroll
+      for (int chunk = 0; chunk < chunks; ++chunk) {
+        const int column = column_base + (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+        if (column >= column_end)
+          continue;
+        uint4 packed;
+        (void)round_bf16x8(values[chunk], &packed);   // already bf16-exact: repack
+        *reinterpret_cast<uint4 *>(rows_out + row * width + column) = packed;
       }
-      if constexpr (two_norms)
-        residual_raw[chunk] = *reinterpret_cast<const uint4 *>(a.residual + row * width + column);
     }
   }
 
