@@ -332,13 +332,28 @@ row_kernel(RowArguments a) {
     float tail_scale = 1.0F;
     if (a.tail_partial != nullptr)
       tail_scale = a.input_scale[0] * a.weight_scale[0];
+    // Gate and (outside the linear's K-cut tail tiles) up columns of every group first, in one
+    // round trip; the tail columns, whose sums come from a loop over the pieces, after them.
+    uint4 gate_raw[chunks];
+    uint4 up_raw[chunks];
+#pragma unroll
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+      const int column = column_base + (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
+      gate_raw[chunk] = make_uint4(0, 0, 0, 0);
+      up_raw[chunk] = make_uint4(0, 0, 0, 0);
+      if (column < column_end) {
+        gate_raw[chunk] = *reinterpret_cast<const uint4 *>(packed_row + column);
+        if (!(a.tail_partial != nullptr && width + column >= a.tail_first_column))
+          up_raw[chunk] = *reinterpret_cast<const uint4 *>(packed_row + width + column);
+      }
+    }
 #pragma unroll
     for (int chunk = 0; chunk < chunks; ++chunk) {
       const int column = column_base + (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;
       if (column >= column_end)
         continue;
-      const Pack8 gate = load_bf16x8(packed_row + column);
-      Pack8 up;
+      const Pack8 gate = unpack_bf16x8(gate_raw[chunk]);
+      Pack8 up = unpack_bf16x8(up_raw[chunk]);
       if (a.tail_partial != nullptr && width + column >= a.tail_first_column) {
         // Same finish as the linear's own epilogue: sum of the pieces, scaled, rounded to bf16.
         Pack8 sum;
@@ -378,8 +393,6 @@ row_kernel(RowArguments a) {
           sum.v[index] *= tail_scale;
         uint4 unused;
         up = round_bf16x8(sum, &unused);
-      } else {
-        up = load_bf16x8(packed_row + width + column);
       }
       Pack8 product;
 #pragma unroll
