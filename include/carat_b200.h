@@ -265,7 +265,8 @@ CARAT_B200_API int carat_b200_rope_tables(void *bf16_cosine, void *bf16_sine, in
 /* Q: per-head rmsnorm * weight -> bf16 -> rotate-half RoPE -> bf16, stored
  * [requests, query_heads, depth, head_dim]. K likewise, V = rmsnorm without weight (from the K
  * slice when key_equals_value); both stored [requests, kv_heads, depth, head_dim].
- * packed rows are [Q | K | V] (V absent when key_equals_value). head_dim is 64, 256 or 512.
+ * packed rows are [Q | K | V] (V absent when key_equals_value). head_dim is 64, 256 or 512. Every
+ * tensor pointer must be 16-byte aligned (head vectors move in 8- and 16-byte pieces).
  * Replaces Gemma4QkvPostprocessor::run_prefill_uniform (include/carat/qkv.h:40-47,
  * cuda/qkv.cu:387-475). */
 CARAT_B200_API int carat_b200_qkv_postprocess(const void *bf16_packed, const void *bf16_query_norm,
