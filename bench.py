@@ -84,16 +84,56 @@ def rank_workload(steps, rank, same_seeds=False):
 
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
+    """SM clock and throttle reasons while the timed region runs. NVML is read from a thread of
+    this process every 10 ms (a sample is there within milliseconds, also when eight ranks start
+    at once); where the NVML binding is missing, `nvidia-smi -lms 200` runs beside the bench, which
+    needs a region of a second or more to see anything. Nothing is ever set, only read."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40),
+                   ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
     def __init__(self, device_index):
         self.device_index = device_index
         self.process = None
         self.path = None
+        self.thread = None
+        self.stop_flag = None
+        self.samples = []          # (sm MHz, reason bit mask)
+        self.maximum = None
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.device_index).uuid)
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.device_index)
+
+    def _sample_loop(self, pynvml, handle):
+        while not self.stop_flag.is_set():
+            try:
+                clock = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+                mask = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.samples.append((float(clock), int(mask)))
+            except Exception:
+                pass
+            self.stop_flag.wait(0.01)
 
     def start(self):
+        try:
+            import threading
+            pynvml, handle = self._nvml_handle()
+            self.maximum = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            self.stop_flag = threading.Event()
+            self.thread = threading.Thread(target=self._sample_loop, args=(pynvml, handle),
+                                           daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             handle = tempfile.NamedTemporaryFile(prefix="clocks", suffix=".csv", delete=False)
             self.path = handle.name
@@ -106,37 +146,48 @@ class ClockSampler:
 
     def stop(self):
         result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
-        if self.process is None:
-            return result
-        self.process.terminate()
-        try:
-            self.process.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.process.kill()
         clocks, reasons, maximum = [], set(), None
-        try:
-            for line in open(self.path):
-                fields = [field.strip() for field in line.split(",")]
-                if len(fields) < 9:
-                    continue
-                try:
-                    clocks.append(float(fields[1]))
-                    maximum = float(fields[2])
-                except ValueError:
-                    continue
-                for name, value in zip(("hw_slowdown", "hw_thermal_slowdown",
-                                        "sw_thermal_slowdown", "sw_power_cap"), fields[5:9]):
-                    if value.lower().startswith("active"):
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            maximum = self.maximum
+            for clock, mask in self.samples:
+                clocks.append(clock)
+                for name, bit in self.REASON_BITS:
+                    if mask & bit:
                         reasons.add(name)
-            os.unlink(self.path)
-        except OSError:
-            pass
+            result["source"] = "nvml, 10 ms"
+        elif self.process is not None:
+            self.process.terminate()
+            try:
+                self.process.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.process.kill()
+            try:
+                for line in open(self.path):
+                    fields = [field.strip() for field in line.split(",")]
+                    if len(fields) < 9:
+                        continue
+                    try:
+                        clocks.append(float(fields[1]))
+                        maximum = float(fields[2])
+                    except ValueError:
+                        continue
+                    for name, value in zip(("hw_slowdown", "hw_thermal_slowdown",
+                                            "sw_thermal_slowdown", "sw_power_cap"), fields[5:9]):
+                        if value.lower().startswith("active"):
+                            reasons.add(name)
+                os.unlink(self.path)
+            except OSError:
+                pass
+            result["source"] = "nvidia-smi, 200 ms"
         if clocks:
             clocks.sort()
             busy = clocks[len(clocks) // 2:]   # upper half: samples taken under load
             result["sm_mhz"] = busy[len(busy) // 2]
             result["sm_max_mhz"] = maximum
             result["reasons"] = sorted(reasons)
+            result["samples"] = len(clocks)
         return result
 
 
