@@ -167,7 +167,7 @@ __device__ __forceinline__ void load_source(const RowArguments &a, size_t row, i
     }
     return;
   }
-  constexpr int batch = chunks <= 2 ? 4 : chunks <= 4 ? 2 : 1;
+  constexpr int batch = chunks <= 1 ? 8 : chunks <= 2 ? 4 : chunks <= 4 ? 2 : 1;
   int pieces = a.splits;
   if (a.valid_splits != nullptr)
     pieces = min(pieces, a.valid_splits[row / a.rows_per_group]);
@@ -678,7 +678,9 @@ template <RowMode mode> int launch_rows(RowArguments arguments, int rows, cudaSt
     const int groups = (span / 8 + row_threads - 1) / row_threads;
     const int ctas = rows * parts;
     int status = -2;
-    if (groups <= 2)
+    if (groups <= 1)
+      status = launch_rows_chunks<mode, 1>(arguments, ctas, stream);
+    else if (groups <= 2)
       status = launch_rows_chunks<mode, 2>(arguments, ctas, stream);
     else if (groups <= 4)
       status = launch_rows_chunks<mode, 4>(arguments, ctas, stream);
