@@ -460,7 +460,9 @@ void build_runner(Runner &runner, const carat_b200_model_config &config,
     runner.a_gate_up.allocate(static_cast<size_t>(batch) * 2 * assistant->intermediate_size * 2);
     runner.a_previous_hidden.allocate(static_cast<size_t>(batch) * hidden * 2);
     runner.a_amax_words = (2 + 4 * assistant->layer_count) * 2;
-    runner.a_scratch_words.allocate(static_cast<size_t>(runner.a_amax_words + 2 * batch) * 4, true);
+    // One set of scratch words per draft iteration, so that one clear serves the whole call.
+    runner.a_scratch_words.allocate(
+        static_cast<size_t>(runner.a_amax_words + 2 * batch) * 4 * maximum_depth, true);
     runner.a_scales.allocate(static_cast<size_t>(runner.a_amax_words) * 4, true);
     runner.a_concat.allocate(static_cast<size_t>(batch) * 2 * hidden * 2);
     runner.a_normed.allocate(a_row_hidden);
@@ -1441,7 +1443,13 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
   const int hidden = config.hidden_size;
   const int a_hidden = assistant.hidden_size;
   const float epsilon = assistant.rms_norm_epsilon;
-  auto *amax = runner.a_scratch_words.get<unsigned int>();
+  // Every iteration has scratch words of its own (maxima, barrier counts, packed argmax keys), all
+  // cleared here: a clear between two iterations would cut the chain of dependent launches.
+  auto *scratch = runner.a_scratch_words.get<unsigned int>();
+  const size_t scratch_stride = static_cast<size_t>(runner.a_amax_words) + 2 * runner.batch;
+  require_cuda(cudaMemsetAsync(scratch, 0, sizeof(int) * scratch_stride * depth, stream),
+               "clear assistant scratch");
+  unsigned int *amax = scratch;
   auto *best = reinterpret_cast<unsigned long long *>(amax + runner.a_amax_words);
   auto *scales = runner.a_scales.get<float>();
   const auto target = [&](int word) {
@@ -1456,9 +1464,8 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
 
   if (runner.assistant_mode == CARAT_B200_ASSISTANT_FP8_ALL) {
   for (int draft_index = 0; draft_index < depth; ++draft_index) {
-    require_cuda(cudaMemsetAsync(amax, 0, sizeof(int) * (runner.a_amax_words + 2 * runner.batch),
-                                 stream),
-                 "clear assistant scratch");
+    amax = scratch + draft_index * scratch_stride;
+    best = reinterpret_cast<unsigned long long *>(amax + runner.a_amax_words);
     const int *input_tokens =
         draft_index == 0 ? device_tokens : draft_tokens + (draft_index - 1) * requests;
     require_launch(launch_embed_concat_quant(
@@ -1603,9 +1610,8 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
   };
   const int head_word = 0;
   for (int draft_index = 0; draft_index < depth; ++draft_index) {
-    require_cuda(cudaMemsetAsync(amax, 0, sizeof(int) * (runner.a_amax_words + 2 * runner.batch),
-                                 stream),
-                 "clear assistant scratch");
+    amax = scratch + draft_index * scratch_stride;
+    best = reinterpret_cast<unsigned long long *>(amax + runner.a_amax_words);
     const int *input_tokens =
         draft_index == 0 ? device_tokens : draft_tokens + (draft_index - 1) * requests;
     require_launch(launch_embed_concat_quant(
