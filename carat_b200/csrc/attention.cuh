@@ -64,6 +64,11 @@ struct AttentionArguments {
                              // otherwise the consumer of `chunk_partials` does the sum
   int draft;                 // 1: drafter semantics (depth == 1, no proposal rows, the first
                              //    min(position + 1, capacity) cache rows are visible)
+  // 1: the cache rows this call reads and `positions` / `slots` were last written before the
+  // chain of dependent launches this call is part of began (a verify or draft step: the rings
+  // change only in the commit at its end). The one-kernel path then requests its first key tiles
+  // before it waits for the previous grid. 0 (any other caller): nothing is read early.
+  int cache_static;
   // Optional, one-kernel path only (attention_fused_applies): a word, zero on entry, that receives
   // the float bits of the largest |output| as written (bf16-rounded), so that the quantiser for
   // the o projection needs no pass of its own over the rows to find it.

@@ -200,7 +200,10 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
   ptx::tcgen05_fence_after_thread_sync();
   const uint32_t tmem_base = tmem_base_slot;
   const uint32_t tmem_output = tmem_base + 2 * fused_rows;
-  grid_dependency_wait();
+  // The producer thread waits further down, after its early loads; the rest of its warp has
+  // nothing to wait for.
+  if (warp != 0)
+    grid_dependency_wait();
 
   // The TMA and MMA roles are single threads whose loop bodies are the critical path of the whole
   // kernel (a dependent instruction costs a handful of cycles and there is nothing to hide it), so
@@ -212,6 +215,27 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
       RingCursor cursor;
       bool healthy = true;
       int local = 0;
+      // Cache rows that no grid of this chain writes can be on their way while the previous grid
+      // still runs: the first item's key tiles, into the stages they will be consumed from (the
+      // proposal keys, which the previous grid produces, keep the four stages before them).
+      int early_stages = 0;
+      if (a.cache_static != 0 && static_cast<int>(blockIdx.x) < args.items) {
+        const FusedItem item = fused_item(a, static_cast<int>(blockIdx.x));
+        const int reserved = item.proposals > 0 ? 4 : 0;
+        RingCursor ahead;
+        for (int skip = 0; skip < reserved; ++skip)
+          ahead.advance();
+        early_stages = min(fused_stages - reserved, item.cache_tiles * 4);
+        const int cache_row0 = static_cast<int>(item.cache_row0);
+        for (int early = 0; early < early_stages; ++early) {
+          ptx::mbarrier_arrive_expect_tx(full_bar + 8U * ahead.stage, fused_stage_bytes);
+          ptx::tma_load_2d(ring + ahead.stage * fused_stage_bytes, &key_map, (early & 3) * 64,
+                           cache_row0 + (early >> 2) * fused_tile_keys,
+                           full_bar + 8U * ahead.stage, stream_policy);
+          ahead.advance();
+        }
+      }
+      grid_dependency_wait();
       for (int index = static_cast<int>(blockIdx.x); index < args.items && healthy;
            index += static_cast<int>(gridDim.x), ++local) {
         const FusedItem item = fused_item(a, index);
@@ -249,6 +273,11 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
           const int row = cache_row0 + tile * fused_tile_keys;
 #pragma unroll
           for (int sub = 0; sub < 4; ++sub) {
+            if (early_stages > 0) {   // requested before the wait (first item only)
+              --early_stages;
+              cursor.advance();
+              continue;
+            }
             if (!ptx::mbarrier_wait_checked(empty_bar + 8U * cursor.stage, cursor.phase ^ 1U, abort_flag,
                               args.device_error, 31)) {
               healthy = false;

@@ -198,6 +198,8 @@ struct carat_b200_runner {
   DeviceBuffer grid_counter;   // barrier word of the gated linear; zero between launches
   bool fused_geglu{false};
   bool cooperative_rows{false};   // CARAT_B200_COOPERATIVE_ROWS=1: row kernels as cooperative launches
+  bool early_keys{true};          // the one-kernel attention requests its first cache tiles before
+                                  // the previous grid has finished (CARAT_B200_EARLY_KEYS=0: after)
   bool attention_amax{true};      // the one-kernel attention also finds the largest |output|, so
                                   // the quantiser after it is one pass without a grid barrier
                                   // (CARAT_B200_ATTENTION_AMAX=0: the row kernel finds it)
@@ -394,6 +396,8 @@ void build_runner(Runner &runner, const carat_b200_model_config &config,
   runner.fused_geglu = config.intermediate_size % 64 == 0 && fused != nullptr && fused[0] == '1';
   const char *cooperative = std::getenv("CARAT_B200_COOPERATIVE_ROWS");
   runner.cooperative_rows = cooperative != nullptr && cooperative[0] == '1';
+  const char *early_keys = std::getenv("CARAT_B200_EARLY_KEYS");
+  runner.early_keys = early_keys == nullptr || early_keys[0] != '0';
   const char *attention_amax = std::getenv("CARAT_B200_ATTENTION_AMAX");
   runner.attention_amax = attention_amax == nullptr || attention_amax[0] != '0';
   runner.gated_rows.allocate(static_cast<size_t>(rows) * config.intermediate_size * 2);
@@ -902,6 +906,8 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
       attention.chunks = attention_chunks(longest + depth, global_chunk_keys);
     } else {
       attention.window = config.sliding_window;
+      // The rings change only in the commit at the end of the step.
+      attention.cache_static = runner.early_keys ? 1 : 0;
       attention.new_keys = layer.staged_keys();
       attention.new_values = layer.staged_values();
       attention.new_request_stride = post.slot_stride;
@@ -1520,6 +1526,8 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
       attention.capacity = shared.capacity;
       attention.window = shape.global_attention ? 0 : config.sliding_window;
       attention.draft = 1;
+      // Drafting reads the target's caches and writes none.
+      attention.cache_static = runner.early_keys ? 1 : 0;
       attention.max_cache_rows = std::min(longest, shared.capacity);
       attention.score_stride = runner.score_stride_global;
       attention.chunk_keys = global_chunk_keys;
@@ -1663,6 +1671,8 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
       attention.capacity = shared.capacity;
       attention.window = shape.global_attention ? 0 : config.sliding_window;
       attention.draft = 1;
+      // Drafting reads the target's caches and writes none.
+      attention.cache_static = runner.early_keys ? 1 : 0;
       attention.max_cache_rows = std::min(longest, shared.capacity);
       attention.score_stride = runner.score_stride_global;
       attention.chunk_keys = global_chunk_keys;

@@ -2,7 +2,9 @@
 launch (the default: the next kernel's prologue overlaps the previous kernel's tail), without it
 (CARAT_B200_PDL=0: plain stream order) and with the row kernels as cooperative launches
 (CARAT_B200_COOPERATIVE_ROWS=1); nor on whether the largest attention output is found by
-the attention kernel or by the quantiser after it (CARAT_B200_ATTENTION_AMAX=0). A kernel that touched another kernel's data before its
+the attention kernel or by the quantiser after it (CARAT_B200_ATTENTION_AMAX=0), or on whether
+the attention kernel requests its first cache tiles before the previous grid has finished
+(CARAT_B200_EARLY_KEYS=0). A kernel that touched another kernel's data before its
 griddepcontrol.wait, or a barrier word shared wrongly between launches, would show up as
 different tokens between these runs. Full size (31B shapes, 24 slots), each mode in a process
 of its own because the switches are read once per process.
@@ -50,7 +52,7 @@ def run_mode(tmp_path, **switches):
     script.write_text(SCRIPT)
     environment = dict(os.environ)
     for name in ("CARAT_B200_PDL", "CARAT_B200_COOPERATIVE_ROWS", "CARAT_B200_FUSED_GEGLU",
-                 "CARAT_B200_ATTENTION_AMAX"):
+                 "CARAT_B200_ATTENTION_AMAX", "CARAT_B200_EARLY_KEYS"):
         environment.pop(name, None)
     environment.update(switches)
     done = subprocess.run([sys.executable, str(script), ROOT], capture_output=True, text=True,
@@ -66,3 +68,4 @@ def test_results_do_not_depend_on_the_launch_mode(cuda_device, tmp_path):
     assert run_mode(tmp_path, CARAT_B200_PDL="0") == default
     assert run_mode(tmp_path, CARAT_B200_COOPERATIVE_ROWS="1") == default
     assert run_mode(tmp_path, CARAT_B200_ATTENTION_AMAX="0") == default
+    assert run_mode(tmp_path, CARAT_B200_EARLY_KEYS="0") == default
