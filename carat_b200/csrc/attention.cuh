@@ -64,7 +64,11 @@ struct AttentionArguments {
                              // otherwise the consumer of `chunk_partials` does the sum
   int draft;                 // 1: drafter semantics (depth == 1, no proposal rows, the first
                              //    min(position + 1, capacity) cache rows are visible)
-  // 1: the cache rows this call reads and `positions` / `slots` were last written before the
+  // 1: `positions` and `slots` were last written before the chain of dependent launches this
+  // call is part of began (the runner's step inputs, copied in ahead of the first kernel): the
+  // kernels then read them, and lay out their work, before they wait for the previous grid.
+  int inputs_static;
+  // 1 (needs inputs_static): the cache rows this call reads and `positions` / `slots` were last written before the
   // chain of dependent launches this call is part of began (a verify or draft step: the rings
   // change only in the commit at its end). The one-kernel path then requests its first key tiles
   // before it waits for the previous grid. 0 (any other caller): nothing is read early.

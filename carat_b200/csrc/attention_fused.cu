@@ -219,7 +219,8 @@ attention_fused_kernel(const __grid_constant__ CUtensorMap key_map,
       // still runs: the first item's key tiles, into the stages they will be consumed from (the
       // proposal keys, which the previous grid produces, keep the four stages before them).
       int early_stages = 0;
-      if (a.cache_static != 0 && static_cast<int>(blockIdx.x) < args.items) {
+      if (a.inputs_static != 0 && a.cache_static != 0 &&
+          static_cast<int>(blockIdx.x) < args.items) {
         const FusedItem item = fused_item(a, static_cast<int>(blockIdx.x));
         const int reserved = item.proposals > 0 ? 4 : 0;
         RingCursor ahead;

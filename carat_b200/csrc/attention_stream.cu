@@ -327,8 +327,13 @@ scores_stream_kernel(const __grid_constant__ CUtensorMap key_map,
   __syncthreads();
   ptx::tcgen05_fence_after_thread_sync();
   const uint32_t tmem_base = tmem_base_slot;
+  // The schedule depends on the requests' positions only; when those are the step's inputs it is
+  // laid out while the previous grid still runs.
+  if (a.inputs_static != 0)
+    build_schedule(a, schedule);
   grid_dependency_wait();
-  build_schedule(a, schedule);
+  if (a.inputs_static == 0)
+    build_schedule(a, schedule);
   __syncthreads();
 
   if (warp == 0) {
@@ -747,8 +752,13 @@ values_stream_kernel(const __grid_constant__ CUtensorMap value_map,
   __syncthreads();
   ptx::tcgen05_fence_after_thread_sync();
   const uint32_t tmem_base = tmem_base_slot;
+  // The schedule depends on the requests' positions only; when those are the step's inputs it is
+  // laid out while the previous grid still runs.
+  if (a.inputs_static != 0)
+    build_schedule(a, schedule);
   grid_dependency_wait();
-  build_schedule(a, schedule);
+  if (a.inputs_static == 0)
+    build_schedule(a, schedule);
   __syncthreads();
 
   if (warp == 0) {

@@ -882,6 +882,7 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
     runner.launches += 1;
 
     AttentionArguments attention{};
+    attention.inputs_static = runner.early_keys ? 1 : 0;   // positions and slots: step inputs
     attention.queries = runner.queries.get();
     attention.key_cache = layer.keys();
     attention.value_cache = layer.values();
@@ -1508,6 +1509,7 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
                      "assistant query post-processing");
       runner.launches += 1;
       AttentionArguments attention{};
+      attention.inputs_static = runner.early_keys ? 1 : 0;   // positions and slots: step inputs
       attention.queries = runner.a_queries.get();
       attention.key_cache = shared.keys();
       attention.value_cache = shared.values();
@@ -1653,6 +1655,7 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
                      "assistant query post-processing");
       runner.launches += 1;
       AttentionArguments attention{};
+      attention.inputs_static = runner.early_keys ? 1 : 0;   // positions and slots: step inputs
       attention.queries = runner.a_queries.get();
       attention.key_cache = shared.keys();
       attention.value_cache = shared.values();
