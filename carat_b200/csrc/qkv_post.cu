@@ -150,9 +150,27 @@ template <int per> __global__ void qkv_post_kernel(QkvPostArguments a) {
   // The norm weights are static: they are fetched while the projection still runs.
   load_halves<per>(static_cast<const __nv_bfloat16 *>(is_query ? a.query_norm : a.key_norm), lane,
                    with.weight_low, with.weight_high);
+  // Position-dependent operands: before the wait when the positions are inputs of the step.
+  int position = 0;
+  bool in_table = false;
+  const auto fetch_rope = [&] {
+    position = a.positions[request] + token;
+    in_table = position >= 0 && position < a.max_positions;
+    if (in_table) {
+      load_halves<per>(static_cast<const __nv_bfloat16 *>(a.cosine) +
+                           static_cast<size_t>(position) * dimension,
+                       lane, with.cosine_low, with.cosine_high);
+      load_halves<per>(static_cast<const __nv_bfloat16 *>(a.sine) +
+                           static_cast<size_t>(position) * dimension,
+                       lane, with.sine_low, with.sine_high);
+    }
+  };
+  if (a.inputs_static != 0)
+    fetch_rope();
   grid_dependency_wait();
+  if (a.inputs_static == 0)
+    fetch_rope();
 
-  const int position = a.positions[request] + token;
   const auto *packed_row =
       static_cast<const __nv_bfloat16 *>(a.packed) + static_cast<size_t>(row) * packed_width;
   float low[per];
@@ -165,14 +183,8 @@ template <int per> __global__ void qkv_post_kernel(QkvPostArguments a) {
   if (separate_value)
     load_halves<per>(packed_row + query_width + kv_width + kv_head * dimension, lane, value_low,
                      value_high);
-  if (position < 0 || position >= a.max_positions)
+  if (!in_table)
     return;
-  load_halves<per>(static_cast<const __nv_bfloat16 *>(a.cosine) +
-                       static_cast<size_t>(position) * dimension,
-                   lane, with.cosine_low, with.cosine_high);
-  load_halves<per>(static_cast<const __nv_bfloat16 *>(a.sine) +
-                       static_cast<size_t>(position) * dimension,
-                   lane, with.sine_low, with.sine_high);
 
   const float inverse_rms = inverse_rms_of<per>(low, high, a.epsilon);
   float out_low[per];

@@ -40,6 +40,9 @@ struct QkvPostArguments {
   int key_equals_value;
   int max_positions;           // rows in the cos/sin tables
   float epsilon;
+  int inputs_static;           // 1: positions (and slots) were written before the chain of
+                               // dependent launches began; the kernel then fetches them and the
+                               // cos/sin rows while the previous grid still runs
 };
 
 int launch_qkv_post(const QkvPostArguments &arguments, cudaStream_t stream);

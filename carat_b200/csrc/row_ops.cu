@@ -256,6 +256,10 @@ row_kernel(RowArguments a) {
         next_weight_raw[chunk] = *reinterpret_cast<const uint4 *>(a.next_norm_weight + column);
     }
   }
+  // The layer scalar is a weight like the norm vectors: fetched before the wait as well.
+  [[maybe_unused]] float layer_scale = 1.0F;
+  if constexpr (mode == RowMode::layer_output)
+    layer_scale = __bfloat162float(*a.scalar);
   grid_dependency_wait();
 
   if constexpr (mode == RowMode::embed_norm && !two_launches) {
@@ -432,9 +436,6 @@ row_kernel(RowArguments a) {
       for (int index = 0; index < 8; ++index)
         square_sum += values[chunk].v[index] * values[chunk].v[index];
     const float inverse_rms = rsqrtf(block_sum(square_sum, scratch, parity) / width_value + a.epsilon);
-    float layer_scale = 1.0F;
-    if constexpr (mode == RowMode::layer_output)
-      layer_scale = __bfloat162float(*a.scalar);
 #pragma unroll
     for (int chunk = 0; chunk < chunks; ++chunk) {
       const int column = column_base + (chunk * row_threads + static_cast<int>(threadIdx.x)) * 8;

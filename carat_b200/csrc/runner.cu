@@ -848,6 +848,7 @@ void verify_step(Runner &runner, const int *proposals, int requests, int depth,
     run_linear(runner, plan.qkv, scales + word, w.qkv_scale, runner.packed.get(), false);
 
     QkvPostArguments post{};
+    post.inputs_static = runner.early_keys ? 1 : 0;   // positions: step inputs
     post.packed = runner.packed.get();
     post.query_norm = w.q_norm;
     post.key_norm = w.k_norm;
