@@ -99,3 +99,24 @@ def test_step_byte_accounting_matches_the_published_figures():
     positions = [4096] * bench.SLOTS
     per_slot = 50 * 16384 * 1024 + 10 * 8192 * (4096 + bench.DEPTH)
     assert bench.step_kv_bytes(config, positions) == bench.SLOTS * per_slot
+
+
+def test_clock_sampler_reports_nothing_without_a_gpu_and_decodes_nvml_samples():
+    sys.path.insert(0, ROOT)
+    import bench
+    sampler = bench.ClockSampler(0)
+    sampler.start()          # no NVML device and no nvidia-smi here: must not raise
+    empty = sampler.stop()
+    assert empty["sm_mhz"] is None and empty["reasons"] == []
+
+    # The decoding of NVML samples (clock, reason bit mask), without a device behind it.
+    import threading
+    decoded = bench.ClockSampler(0)
+    decoded.thread = threading.Thread(target=lambda: None)
+    decoded.thread.start()
+    decoded.stop_flag = threading.Event()
+    decoded.maximum = 1965.0
+    decoded.samples = [(300.0, 0), (1950.0, 0x4), (1965.0, 0x4), (1965.0, 0)]
+    result = decoded.stop()
+    assert result["sm_mhz"] == 1965.0 and result["sm_max_mhz"] == 1965.0
+    assert result["reasons"] == ["sw_power_cap"] and result["samples"] == 4
