@@ -643,9 +643,20 @@ __global__ void finalize_split_k_kernel(const float *partial, const float *input
   const float scale = input_scale != nullptr ? input_scale[0] * weight_scale[0] : 1.0F;
   for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
        index < elements; index += static_cast<size_t>(blockDim.x) * gridDim.x) {
+    // Four pieces a round trip, added in piece order.
     float sum = 0.0F;
-    for (int split = 0; split < splits; ++split)
-      sum += partial[static_cast<size_t>(split) * elements + index];
+    for (int first = 0; first < splits; first += 4) {
+      float piece[4];
+#pragma unroll
+      for (int offset = 0; offset < 4; ++offset)
+        piece[offset] = first + offset < splits
+                            ? partial[static_cast<size_t>(first + offset) * elements + index]
+                            : 0.0F;
+#pragma unroll
+      for (int offset = 0; offset < 4; ++offset)
+        if (first + offset < splits)
+          sum += piece[offset];
+    }
     output[index] = __float2bfloat16_rn(sum * scale);
   }
 }
@@ -661,8 +672,18 @@ __global__ void finalize_tail_kernel(const float *partial, const float *input_sc
   for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
        index < elements; index += static_cast<size_t>(blockDim.x) * gridDim.x) {
     float sum = 0.0F;
-    for (int piece = 0; piece < pieces; ++piece)
-      sum += partial[static_cast<size_t>(piece) * elements + index];
+    for (int first = 0; first < pieces; first += 4) {
+      float piece[4];
+#pragma unroll
+      for (int offset = 0; offset < 4; ++offset)
+        piece[offset] = first + offset < pieces
+                            ? partial[static_cast<size_t>(first + offset) * elements + index]
+                            : 0.0F;
+#pragma unroll
+      for (int offset = 0; offset < 4; ++offset)
+        if (first + offset < pieces)
+          sum += piece[offset];
+    }
     const size_t row = index / tail_width;
     const size_t column = index - row * tail_width;
     output[row * output_width + first_column + column] = __float2bfloat16_rn(sum * scale);
