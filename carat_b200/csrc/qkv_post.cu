@@ -153,7 +153,10 @@ template <int per> __global__ void qkv_post_kernel(QkvPostArguments a) {
   // Position-dependent operands: before the wait when the positions are inputs of the step.
   int position = 0;
   bool in_table = false;
+  long long owner = request;
   const auto fetch_rope = [&] {
+    if (a.direct && !is_query)
+      owner = a.slots[request];
     position = a.positions[request] + token;
     in_table = position >= 0 && position < a.max_positions;
     if (in_table) {
@@ -212,7 +215,6 @@ template <int per> __global__ void qkv_post_kernel(QkvPostArguments a) {
     value_low[index] *= inverse_value_rms;
     value_high[index] *= inverse_value_rms;
   }
-  const long long owner = a.direct ? a.slots[request] : request;
   const int cache_row = a.direct ? position % a.capacity : token;
   const size_t destination = static_cast<size_t>(owner * a.slot_stride + kv_head * a.head_stride) +
                              static_cast<size_t>(cache_row) * dimension;
@@ -227,7 +229,8 @@ __global__ void query_post_kernel(const __nv_bfloat16 *projected, const __nv_bfl
                                   const __nv_bfloat16 *cosine_table,
                                   const __nv_bfloat16 *sine_table, __nv_bfloat16 *queries,
                                   const int *positions, int position_offset, int requests,
-                                  int query_heads, int max_positions, float epsilon) {
+                                  int query_heads, int max_positions, float epsilon,
+                                  bool inputs_static) {
   constexpr int dimension = per * 64;
   grid_dependency_launch();
   const int warp = static_cast<int>(blockIdx.x) * (blockDim.x / 32) + (threadIdx.x / 32);
@@ -237,17 +240,27 @@ __global__ void query_post_kernel(const __nv_bfloat16 *projected, const __nv_bfl
   const int request = warp / query_heads;
   RopeOperands<per> with;
   load_halves<per>(weight, lane, with.weight_low, with.weight_high);
+  bool in_table = false;
+  const auto fetch_rope = [&] {
+    const int position = positions[request] + position_offset;
+    in_table = position >= 0 && position < max_positions;
+    if (in_table) {
+      load_halves<per>(cosine_table + static_cast<size_t>(position) * dimension, lane,
+                       with.cosine_low, with.cosine_high);
+      load_halves<per>(sine_table + static_cast<size_t>(position) * dimension, lane,
+                       with.sine_low, with.sine_high);
+    }
+  };
+  if (inputs_static)
+    fetch_rope();
   grid_dependency_wait();
-  const int position = positions[request] + position_offset;
+  if (!inputs_static)
+    fetch_rope();
   float low[per];
   float high[per];
   load_halves<per>(projected + static_cast<size_t>(warp) * dimension, lane, low, high);
-  if (position < 0 || position >= max_positions)
+  if (!in_table)
     return;
-  load_halves<per>(cosine_table + static_cast<size_t>(position) * dimension, lane,
-                   with.cosine_low, with.cosine_high);
-  load_halves<per>(sine_table + static_cast<size_t>(position) * dimension, lane, with.sine_low,
-                   with.sine_high);
   const float inverse_rms = inverse_rms_of<per>(low, high, epsilon);
   float out_low[per];
   float out_high[per];
@@ -304,7 +317,7 @@ int launch_qkv_post(const QkvPostArguments &a, cudaStream_t stream) {
 int launch_query_post(const void *projected, const void *query_norm, const void *cosine,
                       const void *sine, void *queries, const int *positions, int position_offset,
                       int requests, int query_heads, int head_dim, int max_positions,
-                      float epsilon, cudaStream_t stream) {
+                      float epsilon, cudaStream_t stream, bool inputs_static) {
   if (projected == nullptr || query_norm == nullptr || cosine == nullptr || sine == nullptr ||
       queries == nullptr || positions == nullptr || requests <= 0 || query_heads <= 0 ||
       !aligned16(projected, query_norm, cosine, sine, queries)) {
@@ -320,15 +333,18 @@ int launch_query_post(const void *projected, const void *query_norm, const void 
   switch (head_dim) {
   case 64:
     launch_chained(query_post_kernel<1>, dim3(blocks), dim3(128), 0, stream, false, p, w, c, s, q,
-                   positions, position_offset, requests, query_heads, max_positions, epsilon);
+                   positions, position_offset, requests, query_heads, max_positions, epsilon,
+                   inputs_static);
     break;
   case 256:
     launch_chained(query_post_kernel<4>, dim3(blocks), dim3(128), 0, stream, false, p, w, c, s, q,
-                   positions, position_offset, requests, query_heads, max_positions, epsilon);
+                   positions, position_offset, requests, query_heads, max_positions, epsilon,
+                   inputs_static);
     break;
   case 512:
     launch_chained(query_post_kernel<8>, dim3(blocks), dim3(128), 0, stream, false, p, w, c, s, q,
-                   positions, position_offset, requests, query_heads, max_positions, epsilon);
+                   positions, position_offset, requests, query_heads, max_positions, epsilon,
+                   inputs_static);
     break;
   default:
     return -3;

@@ -49,9 +49,10 @@ int launch_qkv_post(const QkvPostArguments &arguments, cudaStream_t stream);
 
 // Query-only variant for the drafter (cuda/qkv.cu run_query_ragged): one row per request,
 // rotated at positions[r] + position_offset. Output [requests, query_heads, 1, head_dim].
+// inputs_static: as in QkvPostArguments.
 int launch_query_post(const void *projected, const void *query_norm, const void *cosine,
                       const void *sine, void *queries, const int *positions, int position_offset,
                       int requests, int query_heads, int head_dim, int max_positions,
-                      float epsilon, cudaStream_t stream);
+                      float epsilon, cudaStream_t stream, bool inputs_static = false);
 
 } // namespace carat_b200

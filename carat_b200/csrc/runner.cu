@@ -1506,7 +1506,8 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
       require_launch(launch_query_post(runner.a_projected.get(), w.q_norm, rope.cosine.get(),
                                        rope.sine.get(), runner.a_queries.get(), device_context,
                                        draft_index, requests, assistant.query_heads,
-                                       shape.head_dim, runner.maximum_context, epsilon, stream),
+                                       shape.head_dim, runner.maximum_context, epsilon, stream,
+                                       runner.early_keys),
                      "assistant query post-processing");
       runner.launches += 1;
       AttentionArguments attention{};
@@ -1652,7 +1653,8 @@ void draft_step(Runner &runner, const int *last_tokens, const int *slots, const 
       require_launch(launch_query_post(runner.a_projected.get(), w.q_norm, rope.cosine.get(),
                                        rope.sine.get(), runner.a_queries.get(), device_context,
                                        draft_index, requests, assistant.query_heads,
-                                       shape.head_dim, runner.maximum_context, epsilon, stream),
+                                       shape.head_dim, runner.maximum_context, epsilon, stream,
+                                       runner.early_keys),
                      "assistant query post-processing");
       runner.launches += 1;
       AttentionArguments attention{};
